@@ -1,0 +1,112 @@
+#include "host.h"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+namespace mlf {
+
+static thread_local char g_err[1024] = {0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return 0;
+  set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
+  return -1;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                 uint64_t ld, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+  EncodeTiledFn fn = get_encode_fn();
+  MLF_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled entry point not available");
+  MLF_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base %p not 16-byte aligned", base);
+  MLF_REQUIRE((ld * elem_bytes) % 16 == 0, "TMA row pitch %llu bytes not a multiple of 16",
+              (unsigned long long)(ld * elem_bytes));
+  MLF_REQUIRE(box_inner <= 256 && box_outer <= 256, "TMA box too large");
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                           : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MLF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (inner=%llu outer=%llu ld=%llu box=%ux%u)",
+              (int)r, (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)ld,
+              box_inner, box_outer);
+  return 0;
+}
+
+static int* g_status[64] = {nullptr};
+static int g_sms[64] = {0};
+static std::mutex g_mu;
+
+int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status[dev]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 256);
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!g_sms[dev]) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    g_sms[dev] = n > 0 ? n : 148;
+  }
+  return g_sms[dev];
+}
+
+}  // namespace mlf
+
+MLF_API const char* mlf_last_error() { return mlf::g_err; }
+
+// Reads and clears the device status word (synchronises the device). 0 = no kernel reported a
+// timed-out wait or a rejected index since the last call.
+MLF_API int mlf_read_status(int clear) {
+  int* p = mlf::device_status_word();
+  if (!p) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (clear && v != 0) cudaMemset(p, 0, sizeof(int));
+  return v;
+}
+
+MLF_API int mlf_sm_count() { return mlf::sm_count(); }

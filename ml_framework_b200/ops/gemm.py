@@ -1,0 +1,134 @@
+"""bf16 GEMM on the tcgen05 kernel, plus the plain-PyTorch oracle used on CPU and in tests.
+
+``gemm(a, b)`` computes ``alpha * A @ B^T`` where each operand is given either K-major
+(``[rows, K]``, the contraction index contiguous) or MN-major (``[K, rows]``). The three
+training products of a linear layer ``y = x W^T`` (W ``[out, in]``) are therefore
+
+* forward  ``y  = gemm(x,  W)``                       (both K-major)
+* dgrad    ``dx = gemm(dy, W, b_mn=True)``            (W read as ``[K=out, N=in]``)
+* wgrad    ``dW = gemm(dy, x, a_mn=True, b_mn=True)`` (dy read as ``[K=tokens, M=out]``)
+
+Reference semantics: ``Tensor.Matmul`` (src/MLFramework/Tensor/TensorExtensions.cs:429-504),
+``TensorMathExtensions.MatMul(transposeA, transposeB)``
+(src/MLFramework/Layers/TensorParallel/TensorMathExtensions.cs:21).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import (EPI_ACCUM, EPI_BIAS, EPI_DGELU_MUL, EPI_DSWIGLU, EPI_GELU, EPI_OUT_FP32,
+                    EPI_RESIDUAL, EPI_STORE_PRE, EPI_SWIGLU, GemmArgs, GemmComm)
+
+__all__ = ["gemm", "gemm_reference", "gelu_tanh_ref", "dgelu_tanh_ref"]
+
+
+def gelu_tanh_ref(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+def dgelu_tanh_ref(x: torch.Tensor) -> torch.Tensor:
+    k0, k1 = 0.7978845608028654, 0.044715
+    u = k0 * (x + k1 * x ** 3)
+    t = torch.tanh(u)
+    return 0.5 * (1 + t) + 0.5 * x * (1 - t * t) * k0 * (1 + 3 * k1 * x * x)
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, aux_in=None, flags=0, alpha=1.0,
+                   prev_out=None):
+    """fp32 PyTorch statement of what the kernel computes. Returns (out_fp32, pre_fp32)."""
+    A = a.float().t() if a_mn else a.float()
+    B = b.float().t() if b_mn else b.float()
+    v = alpha * (A @ B.t())
+    if flags & EPI_BIAS:
+        v = v + bias.float()
+    pre = v.clone()
+    if flags & EPI_GELU:
+        v = gelu_tanh_ref(v)
+    if flags & EPI_RESIDUAL:
+        v = v + aux_in.float()
+    if flags & EPI_DGELU_MUL:
+        v = v * dgelu_tanh_ref(aux_in.float())
+    if flags & EPI_SWIGLU:
+        g, u = v[:, 0::2], v[:, 1::2]
+        v = torch.nn.functional.silu(g) * u
+    if flags & EPI_DSWIGLU:
+        gu = aux_in.float()
+        g, u = gu[:, 0::2], gu[:, 1::2]
+        sg = torch.sigmoid(g)
+        out = torch.empty(v.shape[0], v.shape[1] * 2, dtype=torch.float32, device=v.device)
+        out[:, 0::2] = v * u * sg * (1 + g * (1 - sg))
+        out[:, 1::2] = v * g * sg
+        v = out
+    if flags & EPI_ACCUM:
+        v = v + prev_out.float()
+    return v, pre
+
+
+def _rows_k(t: torch.Tensor, mn: bool):
+    if t.dim() != 2:
+        raise ValueError("gemm operands must be 2-D")
+    if t.stride(1) != 1:
+        raise ValueError("gemm operands must have a contiguous last dimension")
+    return (t.shape[1], t.shape[0]) if mn else (t.shape[0], t.shape[1])
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+         aux_in: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
+         flags: int = 0, alpha: float = 1.0, out_dtype: torch.dtype = torch.bfloat16,
+         tile_n: int = 0, max_ctas: int = 0, comm: Optional[GemmComm] = None,
+         m_override: Optional[int] = None, n_override: Optional[int] = None) -> torch.Tensor:
+    """``out = epilogue(alpha * A @ B^T)``; see the module docstring for operand layouts.
+
+    ``m_override`` / ``n_override`` give the logical row count of an operand that is gathered
+    inside the kernel (``comm.gather_operand``), where ``a`` / ``b`` only hold the local shard.
+    """
+    M, K = _rows_k(a, a_mn)
+    N, Kb = _rows_k(b, b_mn)
+    if m_override is not None:
+        M = m_override
+    if n_override is not None:
+        N = n_override
+    if K != Kb:
+        raise ValueError(f"contraction mismatch: {K} vs {Kb}")
+    if bias is not None:
+        flags |= EPI_BIAS
+    if out_dtype == torch.float32:
+        flags |= EPI_OUT_FP32
+    out_cols = N // 2 if flags & EPI_SWIGLU else (2 * N if flags & EPI_DSWIGLU else N)
+    if not a.is_cuda:
+        v, pre = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, aux_in=aux_in, flags=flags,
+                                alpha=alpha, prev_out=out)
+        if aux_out is not None and flags & EPI_STORE_PRE:
+            aux_out.copy_(pre.to(aux_out.dtype))
+        res = v.to(out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm expects bf16 operands on the GPU")
+    if out is None:
+        out = torch.empty((M, out_cols), dtype=out_dtype, device=a.device)
+    elif out.stride(-1) != 1:
+        raise ValueError("out must have a contiguous last dimension")
+    args = GemmArgs()
+    args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.bias = bias.data_ptr() if bias is not None else None
+    args.aux_in = aux_in.data_ptr() if aux_in is not None else None
+    args.aux_out = aux_out.data_ptr() if aux_out is not None else None
+    args.M, args.N, args.K = M, N, K
+    args.lda, args.ldb, args.ldo = a.stride(0), b.stride(0), out.stride(0)
+    args.ld_aux_in = aux_in.stride(0) if aux_in is not None else 0
+    args.ld_aux_out = aux_out.stride(0) if aux_out is not None else 0
+    args.a_mn, args.b_mn = int(a_mn), int(b_mn)
+    args.flags, args.alpha = flags, alpha
+    args.tile_n, args.max_ctas = tile_n, max_ctas
+    args.comm = C.pointer(comm) if comm is not None else None
+    rc = _lib.get().mlf_gemm_bf16(C.byref(args), C.c_uint64(_lib.stream_handle()))
+    _lib.check(rc, "mlf_gemm_bf16")
+    return out

@@ -1,0 +1,117 @@
+"""Micro-benchmarks of the native kernels against the measured roofline.
+
+Usage: ``python -m ml_framework_b200.utils.kernel_bench gemm|attn|elementwise [--json out]``
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, a write of a 256 MB buffer
+between timed launches to flush L2, median of the timed launches. Peaks come from
+``MEASURED_PEAKS.json`` at the repository root when present (else 6650 GB/s, 1590 TFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+from pathlib import Path
+
+import torch
+
+
+def peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+_flush_buf = None
+
+
+def flush_l2():
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush_buf.zero_()
+
+
+def time_cuda(fn, iters: int = 10, warmup: int = 3, flush: bool = True) -> float:
+    """Median milliseconds per call of ``fn``."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    return statistics.median(ts)
+
+
+GEMM_SHAPES = [
+    # (name, M, N, K, a_mn, b_mn)
+    ("gpt1.3b qkv fwd", 8192, 6144, 2048, False, False),
+    ("gpt1.3b proj fwd", 8192, 2048, 2048, False, False),
+    ("gpt1.3b fc1 fwd", 8192, 8192, 2048, False, False),
+    ("gpt1.3b fc2 fwd", 8192, 2048, 8192, False, False),
+    ("gpt1.3b fc1 dgrad", 8192, 2048, 8192, False, True),
+    ("gpt1.3b fc1 wgrad", 8192, 2048, 8192, True, True),
+    ("gpt1.3b lm head", 8192, 50304, 2048, False, False),
+    ("llama8b tp8 gate_up", 32768, 3584, 4096, False, False),
+    ("llama8b tp8 down", 32768, 4096, 1792, False, False),
+    ("square 8192", 8192, 8192, 8192, False, False),
+    ("decode m=256 qkv", 256, 768, 4096, False, False),
+]
+
+
+def bench_gemm(args) -> list[dict]:
+    from ..ops.gemm import gemm
+    pk = peaks()
+    rows = []
+    for name, M, N, K, a_mn, b_mn in GEMM_SHAPES:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_cuda(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
+        A = a.t() if a_mn else a
+        Bt = b if b_mn else b.t()
+        ms_ref = time_cuda(lambda: torch.matmul(A, Bt, out=out))
+        tf = 2.0 * M * N * K / ms / 1e9
+        tf_ref = 2.0 * M * N * K / ms_ref / 1e9
+        rows.append({"shape": name, "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+                     "frac_of_" + pk["source"]: round(tf / pk["bf16_tflops"], 3),
+                     "cublas_ms": round(ms_ref, 4), "cublas_tflops": round(tf_ref, 1),
+                     "vs_cublas": round(ms_ref / ms, 3)})
+        print(rows[-1], flush=True)
+        del a, b, out
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "elementwise"])
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    if args.what == "gemm":
+        rows = bench_gemm(args)
+    elif args.what == "attn":
+        from .kernel_bench_attn import bench_attn
+        rows = bench_attn(args)
+    else:
+        from .kernel_bench_attn import bench_elementwise
+        rows = bench_elementwise(args)
+    from .. import _lib
+    rows.append({"kernel_status": _lib.read_status(True)})
+    if args.json:
+        os.makedirs(os.path.dirname(args.json) or ".", exist_ok=True)
+        Path(args.json).write_text(json.dumps(rows, indent=1))
+
+
+if __name__ == "__main__":
+    main()
