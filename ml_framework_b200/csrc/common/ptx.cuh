@@ -96,6 +96,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-collective form for warps that go on to execute .sync.aligned instructions: the outcome
+// is made uniform across the warp, so either every lane continues or every lane unwinds.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* err_word, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, err_word, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------------------------
 // proxy / memory fences
 // ---------------------------------------------------------------------------------

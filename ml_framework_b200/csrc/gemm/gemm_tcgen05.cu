@@ -405,7 +405,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tile_coords(t, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
       const int m = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
-      if (!mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
+      if (!mbar_wait_warp(tfull_bar(acc), acc_ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after_sync();
       const bool row_ok = m < p.M;
       // output row pointer (possibly on a peer)

@@ -1,0 +1,265 @@
+// LayerNorm and RMSNorm, forward and backward, bf16 activations with fp32 statistics.
+//
+// One warp owns one row at a time and keeps it in registers as packed bf16 (NV 16-byte
+// vectors per lane), so x is read from HBM exactly once per pass. The backward pass adds the
+// per-row contributions to gamma/beta gradients into a per-CTA shared-memory accumulator with
+// shared atomics and writes one partial per CTA; a second tiny kernel sums the partials.
+//
+// The reference has no norm kernels (its AMP rules only name layernorm as an fp32 op,
+// src/MLFramework/Amp/DefaultAmpRules.cs:48-110); these are required by the GPT and Llama
+// model families.
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+#include "../mlf_api.h"
+
+namespace mlf {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// D = NV * 256. rms != 0 selects RMSNorm (no mean subtraction, no beta).
+template <int NV>
+__global__ void __launch_bounds__(256)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps, int rms) {
+  constexpr int D = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * D);
+    uint4 xv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) xv[i] = xr[i * 32 + lane];
+    float s = 0.f;
+    if (!rms) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float f[8];
+        unpack8(xv[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += f[j];
+      }
+      s = warp_sum(s) * (1.f / D);
+    }
+    const float mean = rms ? 0.f : s;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8];
+      unpack8(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = f[j] - mean;
+        ss += d * d;
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(ss) * (1.f / D) + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + (long long)row * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+    const uint4* br = reinterpret_cast<const uint4*>(beta);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8], g[8], b[8];
+      unpack8(xv[i], f);
+      unpack8(gr[i * 32 + lane], g);
+      if (beta) unpack8(br[i * 32 + lane], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = (f[j] - mean) * rstd * g[j] + (beta ? b[j] : 0.f);
+      yr[i * 32 + lane] = pack8(f);
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms) {
+  constexpr int D = NV * 256;
+  extern __shared__ float acc[];  // [2][D]
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * D);
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + (long long)row * D);
+    uint4 xv[NV], dv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      xv[i] = xr[i * 32 + lane];
+      dv[i] = dr[i * 32 + lane];
+    }
+    const float mean = rms ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8], d[8], g[8];
+      unpack8(xv[i], f);
+      unpack8(dv[i], d);
+      unpack8(gr[i * 32 + lane], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (f[j] - mean) * rstd;
+        const float dxh = d[j] * g[j];
+        c1 += dxh;
+        c2 += dxh * xh;
+      }
+    }
+    c1 = rms ? 0.f : warp_sum(c1) * (1.f / D);
+    c2 = warp_sum(c2) * (1.f / D);
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (long long)row * D);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float f[8], d[8], g[8], o[8];
+      unpack8(xv[i], f);
+      unpack8(dv[i], d);
+      unpack8(gr[i * 32 + lane], g);
+      const int col = (i * 32 + lane) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (f[j] - mean) * rstd;
+        const float dxh = d[j] * g[j];
+        o[j] = rstd * (dxh - c1 - xh * c2);
+        atomicAdd(&acc[col + j], d[j] * xh);
+        if (!rms) atomicAdd(&acc[D + col + j], d[j]);
+      }
+      dxr[i * 32 + lane] = pack8(o);
+    }
+  }
+  __syncthreads();
+  float* po = partials + (long long)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) po[i] = acc[i];
+}
+
+// dgamma[c] = sum_g partials[g][0][c]; dbeta likewise. Output bf16 or fp32, optional accumulate.
+__global__ void norm_bwd_finalize_kernel(const float* __restrict__ partials, int nparts, int D,
+                                         void* dgamma, void* dbeta, int out_fp32, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float g = 0.f, b = 0.f;
+  for (int p = 0; p < nparts; ++p) {
+    g += partials[(long long)p * 2 * D + c];
+    b += partials[(long long)p * 2 * D + D + c];
+  }
+  if (out_fp32) {
+    float* dg = static_cast<float*>(dgamma);
+    dg[c] = g + (accumulate ? dg[c] : 0.f);
+    if (dbeta) {
+      float* db = static_cast<float*>(dbeta);
+      db[c] = b + (accumulate ? db[c] : 0.f);
+    }
+  } else {
+    __nv_bfloat16* dg = static_cast<__nv_bfloat16*>(dgamma);
+    dg[c] = __float2bfloat16(g + (accumulate ? __bfloat162float(dg[c]) : 0.f));
+    if (dbeta) {
+      __nv_bfloat16* db = static_cast<__nv_bfloat16*>(dbeta);
+      db[c] = __float2bfloat16(b + (accumulate ? __bfloat162float(db[c]) : 0.f));
+    }
+  }
+}
+
+template <int NV>
+static int launch_fwd(const void* x, const void* g, const void* b, void* y, float* mean, float* rstd, int rows,
+                      float eps, int rms, cudaStream_t st) {
+  const int grid = min((rows + 7) / 8, sm_count() * 8);
+  norm_fwd_kernel<NV><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
+                                            static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(y), mean,
+                                            rstd, rows, eps, rms);
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <int NV>
+static int launch_bwd(const void* x, const void* dy, const void* g, const float* mean, const float* rstd, void* dx,
+                      float* partials, int grid, int rows, int rms, cudaStream_t st) {
+  constexpr int smem = 2 * NV * 256 * 4;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && !attr_set[dev & 63]) {
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(norm_bwd_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set[dev & 63] = true;
+  }
+  norm_bwd_kernel<NV><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                               static_cast<const __nv_bfloat16*>(dy),
+                                               static_cast<const __nv_bfloat16*>(g), mean, rstd,
+                                               static_cast<__nv_bfloat16*>(dx), partials, rows, rms);
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace mlf
+
+using namespace mlf;
+
+#define MLF_NORM_DISPATCH(NVVAL, CALL)                      \
+  switch (NVVAL) {                                          \
+    case 1: return CALL(1); case 2: return CALL(2); case 3: return CALL(3); case 4: return CALL(4); \
+    case 6: return CALL(6); case 8: return CALL(8); case 12: return CALL(12); case 16: return CALL(16); \
+    case 20: return CALL(20); case 24: return CALL(24); case 32: return CALL(32);                   \
+    default: break;                                         \
+  }
+
+// y = norm(x) * gamma (+ beta). D must be a multiple of 256 from {256..1024, 1536, 2048, 3072,
+// 4096, 5120, 6144, 8192}. mean/rstd (fp32 [rows]) may be null for inference.
+MLF_API int mlf_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                         int rows, int D, float eps, int rms, uint64_t stream) {
+  MLF_REQUIRE(D % 256 == 0, "norm: D=%d must be a multiple of 256", D);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define CALL(NV) launch_fwd<NV>(x, gamma, beta, y, mean, rstd, rows, eps, rms, st)
+  MLF_NORM_DISPATCH(D / 256, CALL)
+#undef CALL
+  set_error("norm: unsupported D=%d", D);
+  return -2;
+}
+
+// Number of fp32 elements the caller must provide as `partials` scratch for mlf_norm_bwd.
+MLF_API long long mlf_norm_bwd_scratch_elems(int rows, int D) {
+  const int grid = min((rows + 7) / 8, sm_count() * 2);
+  return (long long)grid * 2 * D;
+}
+
+MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                         void* dx, void* dgamma, void* dbeta, float* partials, int rows, int D, int rms,
+                         int grads_fp32, int accumulate, uint64_t stream) {
+  MLF_REQUIRE(D % 256 == 0, "norm: D=%d must be a multiple of 256", D);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = min((rows + 7) / 8, sm_count() * 2);
+  int rc = -2;
+  bool matched = true;
+  switch (D / 256) {
+#define CASE(NV) case NV: rc = launch_bwd<NV>(x, dy, gamma, mean, rstd, dx, partials, grid, rows, rms, st); break;
+    CASE(1) CASE(2) CASE(3) CASE(4) CASE(6) CASE(8) CASE(12) CASE(16) CASE(20) CASE(24) CASE(32)
+#undef CASE
+    default: matched = false;
+  }
+  MLF_REQUIRE(matched, "norm: unsupported D=%d", D);
+  if (rc) return rc;
+  norm_bwd_finalize_kernel<<<(D + 255) / 256, 256, 0, st>>>(partials, grid, D, dgamma, rms ? nullptr : dbeta,
+                                                            grads_fp32, accumulate);
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,1 +1,3 @@
-
+from .gpt import GPT, GPTConfig  # noqa: F401
+from .llama import Llama, LlamaConfig  # noqa: F401
+from .mlp import MLP  # noqa: F401

@@ -1,0 +1,50 @@
+"""tcgen05 attention forward/backward against an fp32 PyTorch reference."""
+import pytest
+import torch
+
+from ml_framework_b200.ops import native
+from ml_framework_b200.ops.reference import attention_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6)).item()
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal", [(1, 128, 1, 1, True), (2, 256, 4, 4, True), (1, 320, 4, 2, True),
+                                              (2, 200, 2, 2, False), (1, 1024, 8, 2, True)])
+def test_flash_fwd(B, S, Hq, Hkv, causal):
+    torch.manual_seed(0)
+    D = 128
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    q = qkv[:, :Hq * D].view(B * S, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].view(B * S, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(B * S, Hkv, D)
+    out, lse = native.flash_fwd(q, k, v, B, S, causal=causal)
+    ref, ref_lse = attention_ref(q.reshape(B, S, Hq, D), k.reshape(B, S, Hkv, D), v.reshape(B, S, Hkv, D), causal=causal)
+    torch.cuda.synchronize()
+    assert _rel(out.view(B, S, Hq, D), ref) < 2e-2
+    assert (lse - ref_lse).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal", [(1, 128, 1, 1, True), (2, 256, 4, 4, True), (1, 320, 4, 2, True),
+                                              (1, 200, 2, 2, False)])
+def test_flash_bwd(B, S, Hq, Hkv, causal):
+    torch.manual_seed(1)
+    D = 128
+    q = torch.randn(B * S, Hq, D, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B * S, Hkv, D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B * S, Hkv, D, device="cuda").to(torch.bfloat16)
+    do = torch.randn(B * S, Hq, D, device="cuda").to(torch.bfloat16)
+    out, lse = native.flash_fwd(q, k, v, B, S, causal=causal)
+    dq, dk, dv = native.flash_bwd(q, k, v, out, do, lse, B, S, causal=causal)
+    qf = q.float().reshape(B, S, Hq, D).requires_grad_()
+    kf = k.float().reshape(B, S, Hkv, D).requires_grad_()
+    vf = v.float().reshape(B, S, Hkv, D).requires_grad_()
+    ref, _ = attention_ref(qf, kf, vf, causal=causal)
+    ref.backward(do.float().reshape(B, S, Hq, D))
+    torch.cuda.synchronize()
+    assert _rel(dv.view(B, S, Hkv, D), vf.grad) < 3e-2
+    assert _rel(dk.view(B, S, Hkv, D), kf.grad) < 3e-2
+    assert _rel(dq.view(B, S, Hq, D), qf.grad) < 3e-2
