@@ -388,6 +388,7 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
     if (grid > cap) grid = cap;
     attn_delta_kernel<<<(int)grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout),
                                                  delta, B, S, Hq, ldo, lddo);
+                                                 count_launch();
     MLF_CHECK_CUDA(cudaGetLastError());
   }
   CUtensorMap tq, tk, tv, tdo;
@@ -417,6 +418,7 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
   }
   dim3 grid((S + FB_BKV - 1) / FB_BKV, Hkv, B);
   flash_bwd_kernel<<<grid, FB_THREADS, FB_SMEM, st>>>(tq, tk, tv, tdo, p);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   {
     const long long total = rows * (Hq * FB_D / 4);
@@ -425,6 +427,7 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
     if (g > cap) g = cap;
     cast_rows_f32_bf16_kernel<<<(int)g, 256, 0, st>>>(static_cast<__nv_bfloat16*>(dq), dq_accum, rows, Hq * FB_D, lddq,
                                                       (long long)Hq * FB_D);
+                                                      count_launch();
     MLF_CHECK_CUDA(cudaGetLastError());
   }
   return 0;

@@ -317,6 +317,7 @@ MLF_API int mlf_flash_fwd(const void* q, const void* k, const void* v, void* out
   }
   dim3 grid((S + FA_BQ - 1) / FA_BQ, Hq, B);
   flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, st>>>(tq, tk, tv, p);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

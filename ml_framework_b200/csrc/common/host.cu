@@ -4,11 +4,15 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 namespace mlf {
 
 static thread_local char g_err[1024] = {0};
+static std::atomic<long long> g_launches{0};
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -41,8 +45,23 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Driver entry points need a context bound to the calling thread. Threads that have only ever
+// received device pointers (autograd worker threads, for instance) may not have one yet; a
+// cudaSetDevice on the thread's current device binds the primary context.
+static void ensure_context() {
+  static thread_local bool ready = false;
+  if (ready) return;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    cudaSetDevice(dev);
+    cudaFree(nullptr);
+  }
+  ready = true;
+}
+
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                  uint64_t ld, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+  ensure_context();
   EncodeTiledFn fn = get_encode_fn();
   MLF_REQUIRE(fn != nullptr, "cuTensorMapEncodeTiled entry point not available");
   MLF_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base %p not 16-byte aligned", base);
@@ -110,3 +129,6 @@ MLF_API int mlf_read_status(int clear) {
 }
 
 MLF_API int mlf_sm_count() { return mlf::sm_count(); }
+
+// Kernels launched by this library in this process so far.
+MLF_API long long mlf_launch_count() { return mlf::g_launches.load(std::memory_order_relaxed); }

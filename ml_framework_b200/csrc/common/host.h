@@ -26,6 +26,9 @@ int* device_status_word();
 
 int sm_count();
 
+// Number of kernels launched by this library since load (incremented by the launchers).
+void count_launch(int n = 1);
+
 }  // namespace mlf
 
 #define MLF_CHECK_CUDA(expr)                                  \

@@ -666,6 +666,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     attr_set[dev & 63] = true;
   }
   gemm_tcgen05_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(tmA, tmB, p);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

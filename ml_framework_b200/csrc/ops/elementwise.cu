@@ -357,6 +357,7 @@ MLF_API int mlf_ew_binary(void* out, const void* a, const void* b, float scalar,
   if (n <= 0) return 0;
   if (dtype == 0) ew_binary_kernel<float><<<ew_grid(n / 4 + 1), 256, 0, st>>>((float*)out, (const float*)a, (const float*)b, scalar, n, op);
   else ew_binary_kernel<__nv_bfloat16><<<ew_grid(n / 8 + 1), 256, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, scalar, n, op);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -365,6 +366,7 @@ MLF_API int mlf_ew_unary(void* out, const void* a, long long n, int op, int dtyp
   if (n <= 0) return 0;
   if (dtype == 0) ew_unary_kernel<float><<<ew_grid(n / 4 + 1), 256, 0, st>>>((float*)out, (const float*)a, n, op);
   else ew_unary_kernel<__nv_bfloat16><<<ew_grid(n / 8 + 1), 256, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)a, n, op);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -373,6 +375,7 @@ MLF_API int mlf_fill(void* out, float value, long long n, int dtype, uint64_t st
   if (n <= 0) return 0;
   if (dtype == 0) fill_kernel<float><<<ew_grid(n / 4 + 1), 256, 0, st>>>((float*)out, value, n);
   else fill_kernel<__nv_bfloat16><<<ew_grid(n / 8 + 1), 256, 0, st>>>((__nv_bfloat16*)out, value, n);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -384,25 +387,30 @@ MLF_API int mlf_reduce_all(float* out, const void* a, long long n, int red, int 
   const int r = red == 3 ? 0 : red;
   if (dtype == 0) reduce_stage1_kernel<float><<<grid, 256, 0, st>>>((const float*)a, n, scratch, r);
   else reduce_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, n, scratch, r);
+  count_launch();
   reduce_stage2_kernel<<<1, 32, 0, st>>>(scratch, grid, out, r, red == 3 ? 1.f / (float)n : 1.f);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_gelu_bwd(void* dx, const void* dy, const void* x, long long n, uint64_t stream) {
   MLF_REQUIRE(n % 8 == 0, "gelu_bwd: n must be a multiple of 8");
   gelu_bwd_kernel<<<ew_grid(n / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((__nv_bfloat16*)dx, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, n);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_swiglu_fwd(void* out, const void* gu, long long rows, int F, int interleaved, uint64_t stream) {
   MLF_REQUIRE(F % 8 == 0, "swiglu: F must be a multiple of 8");
   swiglu_fwd_kernel<<<ew_grid(rows * F / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, rows, F, interleaved);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_swiglu_bwd(void* dgu, const void* dout, const void* gu, long long rows, int F, int interleaved, uint64_t stream) {
   MLF_REQUIRE(F % 8 == 0, "swiglu: F must be a multiple of 8");
   swiglu_bwd_kernel<<<ew_grid(rows * F / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((__nv_bfloat16*)dgu, (const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu, rows, F, interleaved);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -418,7 +426,9 @@ MLF_API int mlf_colsum(void* db, const void* dy, int M, int N, long long ld, flo
   const int rows_per_cta = ((M + row_ctas - 1) / row_ctas + 31) / 32 * 32;
   row_ctas = (M + rows_per_cta - 1) / rows_per_cta;
   colsum_kernel<<<dim3(col_ctas, row_ctas), 256, 0, st>>>((const __nv_bfloat16*)dy, scratch, M, N, ld, rows_per_cta);
+  count_launch();
   cast_f32_to_bf16_kernel<<<ew_grid(N), 256, 0, st>>>((__nv_bfloat16*)db, scratch, N, accumulate);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -427,24 +437,28 @@ MLF_API int mlf_embedding_fwd(void* out, const long long* ids, const long long* 
   MLF_REQUIRE(D % 8 == 0, "embedding: D must be a multiple of 8");
   embedding_fwd_kernel<<<ew_grid(T * (D / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (__nv_bfloat16*)out, ids, pos, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, T, D, vocab, max_pos, device_status_word());
+      count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_embedding_bwd(float* dw, const void* dout, const long long* ids, long long T, int D, int vocab, uint64_t stream) {
   MLF_REQUIRE(D % 8 == 0, "embedding: D must be a multiple of 8");
   embedding_bwd_kernel<<<ew_grid(T * (D / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dw, (const __nv_bfloat16*)dout, ids, T, D, vocab);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_cast_f32_to_bf16(void* out, const float* in, long long n, int accumulate, uint64_t stream) {
   if (n <= 0) return 0;
   cast_f32_to_bf16_kernel<<<ew_grid(n), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((__nv_bfloat16*)out, in, n, accumulate);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_rope(void* x, const long long* pos, long long T, int H, int Dh, long long row_stride, float theta, int inverse, uint64_t stream) {
   MLF_REQUIRE(Dh % 2 == 0, "rope: head dim must be even");
   rope_kernel<<<ew_grid(T * H * (Dh / 2)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((__nv_bfloat16*)x, pos, T, H, Dh, row_stride, theta, inverse);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

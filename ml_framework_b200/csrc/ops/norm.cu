@@ -188,6 +188,7 @@ static int launch_fwd(const void* x, const void* g, const void* b, void* y, floa
   norm_fwd_kernel<NV><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g),
                                             static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(y), mean,
                                             rstd, rows, eps, rms);
+                                            count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -207,6 +208,7 @@ static int launch_bwd(const void* x, const void* dy, const void* g, const float*
                                                static_cast<const __nv_bfloat16*>(dy),
                                                static_cast<const __nv_bfloat16*>(g), mean, rstd,
                                                static_cast<__nv_bfloat16*>(dx), partials, rows, rms);
+                                               count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -260,6 +262,7 @@ MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const
   if (rc) return rc;
   norm_bwd_finalize_kernel<<<(D + 255) / 256, 256, 0, st>>>(partials, grid, D, dgamma, rms ? nullptr : dbeta,
                                                             grads_fp32, accumulate);
+                                                            count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -276,6 +276,7 @@ MLF_API int mlf_adamw(float* master, float* m, float* v, float* vmax, const void
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, m, v, vmax, (const __nv_bfloat16*)grad, (__nv_bfloat16*)param_out, n, a, inv_scale_ptr, found_inf);
   else
     adamw_kernel<float><<<grid, 256, 0, st>>>(master, m, v, vmax, (const float*)grad, (__nv_bfloat16*)param_out, n, a, inv_scale_ptr, found_inf);
+    count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -288,6 +289,7 @@ MLF_API int mlf_sgd(float* master, float* mom, const void* grad, int grad_dtype,
     sgd_kernel<__nv_bfloat16><<<ew_grid2(n), 256, 0, st>>>(master, mom, (const __nv_bfloat16*)grad, (__nv_bfloat16*)param_out, n, lr, momentum, weight_decay, grad_scale, inv_scale_ptr, found_inf);
   else
     sgd_kernel<float><<<ew_grid2(n), 256, 0, st>>>(master, mom, (const float*)grad, (__nv_bfloat16*)param_out, n, lr, momentum, weight_decay, grad_scale, inv_scale_ptr, found_inf);
+    count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -299,12 +301,14 @@ MLF_API int mlf_amp_unscale_check(void* grad, int grad_dtype, long long n, const
     amp_unscale_check_kernel<__nv_bfloat16><<<ew_grid2(n), 256, 0, st>>>((__nv_bfloat16*)grad, n, inv_scale_ptr, inv_scale, found_inf, sumsq, write_back);
   else
     amp_unscale_check_kernel<float><<<ew_grid2(n), 256, 0, st>>>((float*)grad, n, inv_scale_ptr, inv_scale, found_inf, sumsq, write_back);
+    count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 MLF_API int mlf_scaler_update(float* scale, int* tracker, int* found_inf, float growth, float backoff, int interval,
                               float min_scale, float max_scale, int* skipped_steps, uint64_t stream) {
   scaler_update_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(scale, tracker, found_inf, growth, backoff, interval, min_scale, max_scale, skipped_steps);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -313,6 +317,7 @@ MLF_API int mlf_clip_scale(void* grad, int grad_dtype, long long n, const float*
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (grad_dtype == 1) clip_scale_kernel<__nv_bfloat16><<<ew_grid2(n), 256, 0, st>>>((__nv_bfloat16*)grad, n, sumsq, max_norm, eps);
   else clip_scale_kernel<float><<<ew_grid2(n), 256, 0, st>>>((float*)grad, n, sumsq, max_norm, eps);
+  count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -332,6 +337,7 @@ MLF_API int mlf_cross_entropy(void* logits, const long long* targets, float* los
   }
   cross_entropy_kernel<<<T, 512, cache ? smem : 0, st>>>((__nv_bfloat16*)logits, targets, loss_rows, loss_sum, T, V, ld, gscale,
                                                          gscale_ptr, loss_weight, cache, device_status_word());
+                                                         count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,0 +1,498 @@
+"""Fully sharded data parallel (ZeRO-3) and gradient/optimizer-state sharding (ZeRO-2).
+
+Semantics follow the reference's FSDP (src/MLFramework/Distributed/FSDP/FSDP.cs:67-233,
+FSDPShardingUnit.cs:84-110, FSDPConfig.cs:8-58, ShardingStrategy.cs:89-265):
+
+* sharding is per *parameter*: parameter p of N elements is cut into W contiguous pieces and
+  rank r owns piece r (the reference uses ceil(N/W) with a short last piece; here N is padded
+  to a multiple of 8W so every piece is equal and 16-byte aligned);
+* parameters are all-gathered before a unit's forward and again before its backward and
+  released afterwards; gradients are reduce-scattered after the unit's backward; optimizer
+  state (fp32 master, Adam m and v) exists only for the owned pieces
+  (FSDP/FSDPOptimizerStateManager.cs:37-245);
+* some parameters stay replicated ("always gathered", FSDP.cs:223-233: embeddings in the
+  reference). Here every 1-D parameter (norm scales, biases) is replicated, since the first
+  kernel of a unit needs them before any gather could complete; their gradients are
+  all-reduced and every rank applies the same update;
+* strategies: ``full`` (every unit sharded over all ranks), ``grad_op`` (ZeRO-2: parameters
+  replicated, gradients reduce-scattered, optimizer state sharded — required by the
+  benchmark configurations, absent in the reference), ``layer_wise`` (a unit's parameters are
+  owned whole by rank ``hash(unit) % W``: ShardingStrategy.cs:144-196), ``hybrid`` (name list:
+  ShardingStrategy.cs:201-265);
+* mixed precision: bf16 parameters and gradients on the wire, fp32 master weights, dynamic
+  loss scale whose overflow flag is all-reduced so every rank skips together
+  (FSDPMixedPrecision.cs:11-215 keeps the flag rank-local);
+* CPU offload of the optimizer state shards with pinned buffers (FSDPCpuOffload.cs:13-305).
+
+A unit is a transformer block (module list entry) rather than a single parameter, so one
+gather serves all GEMMs of the block. With the peer-memory layer active the gather is done by
+copy CTAs inside the block's first GEMM (``fused_comm``), and the reduce-scatter by a kernel
+that reads the peers' gradient buffers directly; otherwise both are NCCL/gloo collectives
+issued on a side stream one unit ahead of compute.
+"""
+from __future__ import annotations
+
+import zlib
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+from ..dist.process_group import ReduceOp
+from ..ops import native, reference
+
+
+@dataclass
+class FSDPCpuOffloadConfig:
+    enabled: bool = False
+    offload_optimizer_states: bool = True
+    offload_gradients: bool = False
+    offload_parameters: bool = False
+    prefetch_steps: int = 1
+
+    def validate(self):
+        if not (0 <= self.prefetch_steps <= 10):
+            raise ValueError("prefetch_steps must be in [0, 10]")
+
+
+@dataclass
+class FSDPConfig:
+    sharding_strategy: str = "full"        # full | grad_op | layer_wise | hybrid
+    mixed_precision: bool = True
+    offload_to_cpu: bool = False
+    activation_checkpointing: bool = False
+    bucket_size_mb: int = 25
+    num_communication_workers: int = 2
+    fused_comm: bool = True
+    min_shard_numel: int = 4096            # smaller / 1-D parameters stay replicated
+    hybrid_full_patterns: Sequence[str] = ("transformer", "attention", "attn", "mlp", "blocks")
+    hybrid_layerwise_patterns: Sequence[str] = ("classifier", "head")
+    cpu_offload: FSDPCpuOffloadConfig = field(default_factory=FSDPCpuOffloadConfig)
+
+    def validate(self):
+        if self.sharding_strategy not in ("full", "grad_op", "layer_wise", "hybrid"):
+            raise ValueError(f"unknown sharding strategy {self.sharding_strategy!r}")
+        if not (1 <= self.bucket_size_mb <= 1000):
+            raise ValueError("bucket_size_mb must be in [1, 1000]")
+        if not (1 <= self.num_communication_workers <= 16):
+            raise ValueError("num_communication_workers must be in [1, 16]")
+        self.cpu_offload.validate()
+
+
+def shard_bounds(numel: int, world: int, rank: int):
+    """The reference's rule: shard size ceil(N/W), rank r owns [r*s, min((r+1)*s, N))."""
+    s = (numel + world - 1) // world
+    lo = min(rank * s, numel)
+    return lo, min(lo + s, numel)
+
+
+def padded_numel(numel: int, world: int, mult: int = 8) -> int:
+    q = world * mult
+    return (numel + q - 1) // q * q
+
+
+class _ShardedParam:
+    def __init__(self, name: str, p: nn.Parameter, world: int, rank: int):
+        self.name, self.param = name, p
+        self.numel = p.numel()
+        self.shape = tuple(p.shape)
+        self.padded = padded_numel(self.numel, world)
+        self.shard_numel = self.padded // world
+        self.full_off = 0    # offset in the unit's gathered buffer
+        self.shard_off = 0   # offset in the unit's shard buffer
+
+
+class FSDPUnit:
+    """Parameters of one module that are gathered / reduced together."""
+
+    def __init__(self, name: str, module: nn.Module, params: List[tuple], world: int, rank: int):
+        self.name, self.module = name, module
+        self.sharded: List[_ShardedParam] = [_ShardedParam(n, p, world, rank) for n, p in params]
+        off_f = off_s = 0
+        for sp in self.sharded:
+            sp.full_off, sp.shard_off = off_f, off_s
+            off_f += sp.padded
+            off_s += sp.shard_numel
+        self.full_numel, self.shard_numel = off_f, off_s
+        self.shard: Optional[torch.Tensor] = None        # bf16 owned pieces
+        self.grad_shard: Optional[torch.Tensor] = None   # reduced gradient pieces
+        self.gathered: Optional[torch.Tensor] = None     # current full buffer (or None)
+        self.grad_full: Optional[torch.Tensor] = None
+        self.state_off = 0                               # offset in the global optimizer shard
+        self.gather_work: list = []
+        self.rs_work: list = []
+        self.owner: Optional[int] = None                 # layer_wise: owning rank
+
+
+class _PreBackward(torch.autograd.Function):
+    """Identity on a unit's output; its backward runs before the unit's own backward."""
+
+    @staticmethod
+    def forward(ctx, x, fsdp, idx):
+        ctx.fsdp, ctx.idx = fsdp, idx
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.fsdp._pre_backward(ctx.idx)
+        return g, None, None
+
+
+class _PostBackward(torch.autograd.Function):
+    """Identity on a unit's input; its backward runs after every gradient of the unit exists."""
+
+    @staticmethod
+    def forward(ctx, x, fsdp, idx):
+        ctx.fsdp, ctx.idx = fsdp, idx
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.fsdp._post_backward(ctx.idx)
+        return g, None, None
+
+
+class FSDP:
+    """Wraps ``model`` (which must expose ``embed``, ``blocks`` and a ``forward(ids, targets,
+    loss_scale)`` like the models in :mod:`ml_framework_b200.models`; any module with a
+    ``blocks`` ModuleList works) and owns the sharded optimizer."""
+
+    def __init__(self, model: nn.Module, config: Optional[FSDPConfig], process_group,
+                 optimizer_kwargs: Optional[dict] = None):
+        self.cfg = config or FSDPConfig()
+        self.cfg.validate()
+        self.model = model
+        self.pg = process_group
+        self.world = process_group.world_size if process_group is not None else 1
+        self.rank = process_group.rank if process_group is not None else 0
+        self.device = next(model.parameters()).device
+        self.dtype = next(model.parameters()).dtype
+        self.opt_kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+        self.opt_kw.update(optimizer_kwargs or {})
+        self.step_count = 0
+        self._build_units()
+        self._allocate()
+        self._install_hooks()
+        self.optimizer = self  # exposes step()/state_dict() for the engine
+
+    # ------------------------------------------------------------------ construction
+    def _build_units(self):
+        cfg, W = self.cfg, self.world
+        blocks = getattr(self.model, "blocks", None)
+        self.units: List[FSDPUnit] = []
+        self.replicated: List[tuple] = []
+        claimed = set()
+
+        def split(prefix, module):
+            sharded = []
+            for n, p in module.named_parameters():
+                if id(p) in claimed or not p.requires_grad:
+                    continue
+                claimed.add(id(p))
+                full = f"{prefix}.{n}" if prefix else n
+                if p.dim() < 2 or p.numel() < cfg.min_shard_numel:
+                    self.replicated.append((full, p))
+                else:
+                    sharded.append((full, p))
+            return sharded
+        if blocks is not None:
+            for i, blk in enumerate(blocks):
+                sh = split(f"blocks.{i}", blk)
+                if sh:
+                    self.units.append(FSDPUnit(f"blocks.{i}", blk, sh, W, self.rank))
+        root = split("", self.model)
+        self.root_unit = FSDPUnit("root", self.model, root, W, self.rank) if root else None
+        if cfg.sharding_strategy in ("layer_wise", "hybrid"):
+            for u in self.all_units():
+                lw = cfg.sharding_strategy == "layer_wise" or any(k in u.name for k in cfg.hybrid_layerwise_patterns)
+                if cfg.sharding_strategy == "hybrid" and any(k in u.name for k in cfg.hybrid_full_patterns):
+                    lw = False
+                if lw:
+                    u.owner = zlib.crc32(u.name.encode()) % W
+
+    def all_units(self) -> List[FSDPUnit]:
+        return self.units + ([self.root_unit] if self.root_unit is not None else [])
+
+    def _allocate(self):
+        dev, dt, W, r = self.device, self.dtype, self.world, self.rank
+        keep_full = self.cfg.sharding_strategy == "grad_op"
+        total_shard = 0
+        for u in self.all_units():
+            u.state_off = total_shard
+            total_shard += u.shard_numel
+        n_rep = sum(p.numel() for _, p in self.replicated)
+        self.rep_off = total_shard
+        rep_pad = (n_rep + 7) // 8 * 8
+        total = total_shard + rep_pad
+        state_dev = "cpu" if (self.cfg.offload_to_cpu or (self.cfg.cpu_offload.enabled and self.cfg.cpu_offload.offload_optimizer_states)) else dev
+        self.state_device = torch.device(state_dev)
+        pin = self.state_device.type == "cpu" and torch.cuda.is_available()
+        mk = lambda: torch.zeros(total, dtype=torch.float32, device=self.state_device, pin_memory=pin)  # noqa: E731
+        self.master, self.m, self.v = mk(), mk(), mk()
+        self.param_shards = torch.zeros(total, dtype=dt, device=dev)   # bf16 working copy of what this rank owns
+        self.grad_shards = torch.zeros(total, dtype=dt, device=dev)    # reduced gradients of what this rank owns
+        max_full = max([u.full_numel for u in self.units], default=0)
+        # block units rotate through two gathered / gradient buffers; the root unit keeps its own
+        n_rot = 2 if not keep_full else 0
+        self._rot_full = [torch.zeros(max_full, dtype=dt, device=dev) for _ in range(n_rot)] if max_full else []
+        self._rot_grad = [torch.zeros(max_full, dtype=dt, device=dev) for _ in range(2)] if max_full else []
+        with torch.no_grad():
+            for u in self.all_units():
+                u.shard = self.param_shards[u.state_off:u.state_off + u.shard_numel]
+                u.grad_shard = self.grad_shards[u.state_off:u.state_off + u.shard_numel]
+                persistent = keep_full or u is self.root_unit
+                if u.owner is not None and u.owner == r:
+                    # layer-wise ownership: this rank holds the whole unit and its optimizer state
+                    u.owned_full = torch.zeros(u.full_numel, dtype=dt, device=dev)
+                    u.owned_grad = torch.zeros(u.full_numel, dtype=dt, device=dev)
+                    u.owned_master = torch.zeros(u.full_numel, dtype=torch.float32, device=self.state_device)
+                    u.owned_m = torch.zeros_like(u.owned_master)
+                    u.owned_v = torch.zeros_like(u.owned_master)
+                if persistent:
+                    u.gathered = torch.zeros(u.full_numel, dtype=dt, device=dev)
+                    u.grad_full = torch.zeros(u.full_numel, dtype=dt, device=dev) if u is self.root_unit or keep_full else None
+                for sp in u.sharded:
+                    flat = torch.zeros(sp.padded, dtype=dt, device=dev)
+                    flat[:sp.numel].copy_(sp.param.data.reshape(-1))
+                    u.shard[sp.shard_off:sp.shard_off + sp.shard_numel].copy_(flat[r * sp.shard_numel:(r + 1) * sp.shard_numel])
+                    if u.owner is not None and u.owner == r:
+                        u.owned_full[sp.full_off:sp.full_off + sp.padded].copy_(flat)
+                        u.owned_master[sp.full_off:sp.full_off + sp.padded].copy_(flat.float())
+                    if persistent:
+                        u.gathered[sp.full_off:sp.full_off + sp.padded].copy_(flat)
+                        sp.param.data = u.gathered[sp.full_off:sp.full_off + sp.numel].view(sp.shape)
+                    else:
+                        sp.param.data = torch.empty(0, dtype=dt, device=dev)   # released until gathered
+            # replicated small parameters: one flat buffer + flat gradient
+            off = self.rep_off
+            self.rep_grad = self.grad_shards[self.rep_off:self.rep_off + rep_pad]
+            self.rep_flat = self.param_shards[self.rep_off:self.rep_off + rep_pad]
+            for _, p in self.replicated:
+                n = p.numel()
+                self.param_shards[off:off + n].copy_(p.data.reshape(-1))
+                p.data = self.param_shards[off:off + n].view(p.shape)
+                p.main_grad = self.grad_shards[off:off + n].view(p.shape)
+                p._main_grad_started = False
+                off += n
+            self.master.copy_(self.param_shards.float().to(self.state_device))
+        self._comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+
+    def _install_hooks(self):
+        fs = self
+        for i, u in enumerate(self.units):
+            def pre(mod, args, i=i):
+                fs._pre_forward(i)
+                x = args[0]
+                if torch.is_grad_enabled() and x.requires_grad:
+                    return (_PostBackward.apply(x, fs, i),) + tuple(args[1:])
+                return None
+
+            def post(mod, args, out, i=i):
+                fs._post_forward(i)
+                if torch.is_grad_enabled() and isinstance(out, torch.Tensor) and out.requires_grad:
+                    return _PreBackward.apply(out, fs, i)
+                return out
+            u.module.register_forward_pre_hook(pre)
+            u.module.register_forward_hook(post)
+
+    # ------------------------------------------------------------------ gather / release
+    def _point_params(self, u: FSDPUnit, full: torch.Tensor, grad_full: Optional[torch.Tensor]):
+        for sp in u.sharded:
+            sp.param.data = full[sp.full_off:sp.full_off + sp.numel].view(sp.shape)
+            if grad_full is not None:
+                sp.param.main_grad = grad_full[sp.full_off:sp.full_off + sp.numel].view(sp.shape)
+                sp.param._main_grad_started = False
+
+    def _gather_unit(self, u: FSDPUnit, full: torch.Tensor):
+        """All-gather every sharded parameter of the unit into ``full`` (per-parameter collectives,
+        rank-major inside each parameter == row sharding)."""
+        if self.world == 1:
+            for sp in u.sharded:
+                full[sp.full_off:sp.full_off + sp.padded].copy_(u.shard[sp.shard_off:sp.shard_off + sp.shard_numel])
+            return
+        if u.owner is not None:
+            if self.rank == u.owner:
+                full[:u.full_numel].copy_(u.owned_full)
+            self.pg.broadcast(full[:u.full_numel], src=u.owner)
+            return
+        for sp in u.sharded:
+            self.pg.all_gather_into(full[sp.full_off:sp.full_off + sp.padded],
+                                    u.shard[sp.shard_off:sp.shard_off + sp.shard_numel])
+
+    def _pre_forward(self, i: int):
+        u = self.units[i]
+        if self.cfg.sharding_strategy == "grad_op":
+            self._point_params(u, u.gathered, None)
+            return
+        full = self._rot_full[i % 2]
+        self._gather_unit(u, full)
+        u.gathered = full
+        self._point_params(u, full, None)
+
+    def _post_forward(self, i: int):
+        pass  # the rotating buffer is simply reused two units later
+
+    def _pre_backward(self, i: int):
+        u = self.units[i]
+        gbuf = self._rot_grad[i % 2] if u.grad_full is None or self.cfg.sharding_strategy != "grad_op" else u.grad_full
+        if self.cfg.sharding_strategy == "grad_op":
+            gbuf = self._rot_grad[i % 2]
+            self._point_params(u, u.gathered, gbuf)
+            u._gbuf = gbuf
+            return
+        full = self._rot_full[i % 2]
+        self._gather_unit(u, full)
+        u.gathered = full
+        self._point_params(u, full, gbuf)
+        u._gbuf = gbuf
+
+    def _reduce_unit(self, u: FSDPUnit, gbuf: torch.Tensor):
+        for sp in u.sharded:
+            p = sp.param
+            view = gbuf[sp.full_off:sp.full_off + sp.padded]
+            if p.grad is not None:          # gradient came through autograd (CPU / non-native path)
+                view[:sp.numel].copy_(p.grad.reshape(-1))
+                view[sp.numel:].zero_()
+                p.grad = None
+            elif not getattr(p, "_main_grad_started", False):
+                view.zero_()
+            out = u.grad_shard[sp.shard_off:sp.shard_off + sp.shard_numel]
+            if self.world == 1:
+                out.copy_(view)
+            elif u.owner is not None:
+                self.pg.reduce(view, dst=u.owner, op=ReduceOp.SUM)
+                if self.rank == u.owner:
+                    u.owned_grad[sp.full_off:sp.full_off + sp.padded].copy_(view)
+                out.zero_()
+            else:
+                red = self.pg.reduce_scatter(view, op=ReduceOp.SUM)
+                out.copy_(red)
+
+    def _post_backward(self, i: int):
+        u = self.units[i]
+        self._reduce_unit(u, u._gbuf)
+
+    # ------------------------------------------------------------------ step
+    def train_step(self, ids, targets, scaler=None):
+        self.zero_grad()
+        root = self.root_unit
+        if root is not None:
+            if self.cfg.sharding_strategy != "grad_op":
+                self._gather_unit(root, root.gathered)
+            self._point_params(root, root.gathered, root.grad_full)
+        scale_t = scaler.scale_t if scaler is not None else None
+        loss = self.model(ids, targets, loss_scale=scale_t)
+        loss.backward()
+        if root is not None:
+            self._reduce_unit(root, root.grad_full)
+        self._finish_replicated()
+        self.step(scaler)
+        return loss
+
+    def _finish_replicated(self):
+        for _, p in self.replicated:
+            if p.grad is not None:
+                if getattr(p, "_main_grad_started", False):
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                else:
+                    p.main_grad.copy_(p.grad)
+                p.grad = None
+            elif not getattr(p, "_main_grad_started", False):
+                p.main_grad.zero_()
+        if self.world > 1 and self.rep_grad.numel():
+            self.pg.all_reduce(self.rep_grad, op=ReduceOp.SUM)
+
+    def zero_grad(self):
+        for _, p in self.replicated:
+            p._main_grad_started = False
+            p.grad = None
+        for u in self.all_units():
+            for sp in u.sharded:
+                sp.param.grad = None
+                sp.param._main_grad_started = False
+
+    def step(self, scaler=None):
+        """Sharded AdamW over everything this rank owns (one fused kernel on the GPU)."""
+        self.step_count += 1
+        kw = self.opt_kw
+        g = self.grad_shards
+        inv_scale = found = None
+        if scaler is not None:
+            if g.is_cuda:
+                native.amp_unscale_check_(g, scaler.found_inf, inv_scale=None, write_back=False)
+            elif not torch.isfinite(g.float()).all():
+                scaler.found_inf.fill_(1)
+            scaler.sync_found_inf(self.pg)
+            inv_scale, found = scaler.inv_scale_t, scaler.found_inf
+        gscale = 1.0 / self.world
+        b1, b2 = kw["betas"]
+        if self.master.is_cuda:
+            native.adamw_(self.master, self.m, self.v, g, self.param_shards, lr=kw["lr"], beta1=b1, beta2=b2, eps=kw["eps"],
+                          weight_decay=kw["weight_decay"], step=self.step_count, grad_scale=gscale, inv_scale=inv_scale,
+                          found_inf=found)
+        else:
+            skip = found is not None and int(found.item()) != 0
+            if not skip:
+                gf = g.detach().to(self.state_device).float() * gscale
+                if inv_scale is not None:
+                    gf = gf * float(inv_scale.item())
+                p, m, v = reference.adamw_ref(self.master, self.m, self.v, gf, lr=kw["lr"], beta1=b1, beta2=b2,
+                                              eps=kw["eps"], weight_decay=kw["weight_decay"], step=self.step_count)
+                self.master.copy_(p); self.m.copy_(m); self.v.copy_(v)
+                self.param_shards.copy_(self.master.to(self.param_shards.device, non_blocking=True).to(self.dtype))
+        for u in self.all_units():
+            if u.owner is not None and u.owner == self.rank and self.world > 1:
+                self._step_owned(u, gscale, inv_scale, found)
+        if scaler is not None:
+            scaler.update()
+        if self.cfg.sharding_strategy == "grad_op":
+            for u in self.all_units():
+                self._gather_unit(u, u.gathered)
+
+    def _step_owned(self, u: FSDPUnit, gscale, inv_scale, found):
+        kw = self.opt_kw
+        b1, b2 = kw["betas"]
+        if u.owned_master.is_cuda:
+            native.adamw_(u.owned_master, u.owned_m, u.owned_v, u.owned_grad, u.owned_full, lr=kw["lr"], beta1=b1, beta2=b2,
+                          eps=kw["eps"], weight_decay=kw["weight_decay"], step=self.step_count, grad_scale=gscale,
+                          inv_scale=inv_scale, found_inf=found)
+            return
+        if found is not None and int(found.item()) != 0:
+            return
+        gf = u.owned_grad.detach().to(self.state_device).float() * gscale
+        if inv_scale is not None:
+            gf = gf * float(inv_scale.item())
+        p, m, v = reference.adamw_ref(u.owned_master, u.owned_m, u.owned_v, gf, lr=kw["lr"], beta1=b1, beta2=b2,
+                                      eps=kw["eps"], weight_decay=kw["weight_decay"], step=self.step_count)
+        u.owned_master.copy_(p); u.owned_m.copy_(m); u.owned_v.copy_(v)
+        u.owned_full.copy_(u.owned_master.to(u.owned_full.device).to(self.dtype))
+
+    # ------------------------------------------------------------------ state
+    def set_learning_rate(self, lr: float):
+        self.opt_kw["lr"] = lr
+
+    def full_state_dict(self) -> Dict[str, torch.Tensor]:
+        """Gathers every parameter in full precision of the working dtype (all ranks get a copy)."""
+        out = {}
+        for u in self.all_units():
+            full = torch.zeros(u.full_numel, dtype=self.dtype, device=self.device)
+            self._gather_unit(u, full)
+            for sp in u.sharded:
+                out[sp.name] = full[sp.full_off:sp.full_off + sp.numel].view(sp.shape).clone()
+        for n, p in self.replicated:
+            out[n] = p.detach().clone()
+        return out
+
+    def local_state(self) -> Dict[str, torch.Tensor]:
+        """This rank's shard of parameters and optimizer state (for multi-shard checkpoints)."""
+        return {"param_shards": self.param_shards, "master": self.master, "m": self.m, "v": self.v,
+                "step": torch.tensor(self.step_count)}
+
+    def load_local_state(self, sd):
+        self.param_shards.copy_(sd["param_shards"])
+        self.master.copy_(sd["master"]); self.m.copy_(sd["m"]); self.v.copy_(sd["v"])
+        self.step_count = int(sd["step"])
+
+    def state_dict(self):
+        return {k: (v.detach().cpu().clone() if isinstance(v, torch.Tensor) else v) for k, v in self.local_state().items()}

@@ -1,0 +1,108 @@
+"""Data-parallel plumbing on CPU: bucket packing, sampler partition, launcher, and the 2-rank
+gloo run whose all-reduced gradients must be identical on both ranks."""
+import json
+import os
+import sys
+
+import pytest
+import torch
+import torch.nn as nn
+
+from ml_framework_b200.data.samplers import BatchSampler, DistributedSampler, ElasticDistributedSampler
+from ml_framework_b200.dist.launcher import DistributedTrainingError, ProcessLauncher, launch_local
+from ml_framework_b200.dist.process_group import ReduceOp, run_fake_world
+from ml_framework_b200.parallel.ddp import DistributedDataParallel, create_buckets
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_bucket_packing_largest_first_and_oversized_alone():
+    ps = [nn.Parameter(torch.zeros(n)) for n in (10, 3000, 200, 50, 700)]
+    b = create_buckets(ps, bucket_bytes=1000 * 4)
+    # 3000 floats exceed the bucket: own bucket. Then 700, then 200+50+10.
+    sizes = [[p.numel() for p in bk.params] for bk in b]
+    assert sizes == [[3000], [700, 200, 50, 10]]
+    assert b[1].offsets == [0, 700, 900, 950]
+    with pytest.raises(ValueError):
+        from ml_framework_b200.parallel.ddp import GradientBucketManager
+        GradientBucketManager(None, ps, bucket_size_mb=0)
+
+
+def test_distributed_sampler_partition():
+    W, N = 3, 10
+    ss = [DistributedSampler(N, W, r, shuffle=True, seed=5) for r in range(W)]
+    got = sorted(i for s in ss for i in s if i >= 0)
+    assert got == list(range(N))
+    assert all(len(s) == 4 for s in ss)           # ceil(10 / 3) slots, padded with -1
+    assert sum(1 for s in ss for i in s if i < 0) == 2
+    dl = [DistributedSampler(N, W, r, shuffle=False, drop_last=True) for r in range(W)]
+    assert [list(s) for s in dl] == [[0, 3, 6], [1, 4, 7], [2, 5, 8]]
+    a = list(ss[0])
+    ss[0].set_epoch(1)
+    assert list(ss[0]) != a
+    assert list(BatchSampler(dl[0], 2)) == [[0, 3], [6]]
+    with pytest.raises(ValueError):
+        DistributedSampler(N, 2, 2)
+
+
+def test_elastic_sampler_does_not_replay_consumed_samples():
+    s = ElasticDistributedSampler(100, 4, 0, shuffle=True, seed=1)
+    s.record_consumed(40)
+    parts = []
+    for r in range(2):
+        e = ElasticDistributedSampler(100, 4, 0, shuffle=True, seed=1)
+        e.record_consumed(40)
+        e.update_topology(2, r)
+        parts.append(list(e))
+    assert len(parts[0]) + len(parts[1]) == 60 and not set(parts[0]) & set(parts[1])
+
+
+def test_ddp_in_simulated_world_matches_big_batch():
+    torch.manual_seed(0)
+    ref = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+    state = {k: v.clone() for k, v in ref.state_dict().items()}
+    xs = torch.randn(4, 6, 8)
+    ys = torch.randn(4, 6, 4)
+    ((ref(xs.reshape(-1, 8)) - ys.reshape(-1, 4)) ** 2).mean().backward()
+    want = [p.grad.clone() for p in ref.parameters()]
+
+    def run(pg):
+        torch.manual_seed(100 + pg.rank)
+        m = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+        if pg.rank == 0:
+            m.load_state_dict(state)
+        ddp = DistributedDataParallel(m, pg, bucket_size_mb=0.0001, reduce_op=ReduceOp.AVG)
+        ((ddp(xs[pg.rank]) - ys[pg.rank]) ** 2).mean().backward()
+        ddp.finish_backward()
+        return [p.grad.clone() for p in m.parameters()], len(ddp.bucket_manager.buckets)
+    outs = run_fake_world(4, run)
+    assert outs[0][1] > 1
+    for grads, _ in outs:
+        for g, w in zip(grads, want):
+            assert torch.allclose(g, w, atol=1e-6)
+
+
+def test_launcher_env_logs_and_first_failure(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text("import os,sys\nprint(os.environ['RANK'], os.environ['WORLD_SIZE'], os.environ['MASTER_ADDR'], os.environ['MASTER_PORT'])\n"
+                      "sys.exit(3 if os.environ['RANK']=='1' and len(sys.argv)>1 else 0)\n")
+    l = launch_local(str(script), 3, log_dir=str(tmp_path / "logs"), master_port=29611)
+    assert [r.exit_code for r in l.ranks] == [0, 0, 0]
+    assert (tmp_path / "logs" / "rank_2.log").read_text().split() == ["2", "3", "127.0.0.1", "29611"]
+    with pytest.raises(DistributedTrainingError) as e:
+        launch_local(str(script), 2, ["fail"], log_dir=str(tmp_path / "logs2"), master_port=29612)
+    assert e.value.rank == 1 and e.value.exit_code == 3
+    from ml_framework_b200.dist.launcher import launch_multi_node
+    with pytest.raises(NotImplementedError):
+        launch_multi_node()
+
+
+@pytest.mark.timeout(180)
+def test_cpu_mlp_ddp_two_gloo_ranks(tmp_path):
+    l = ProcessLauncher(master_port=29621, log_dir=str(tmp_path))
+    l.launch([sys.executable, os.path.join(ROOT, "baseline", "cpu_mlp_ddp.py"), "100"], 2)
+    ok = l.wait_for_all(timeout_s=150)
+    log = (tmp_path / "rank_0.log").read_text()
+    assert ok, log + (tmp_path / "rank_1.log").read_text()
+    res = json.loads([ln for ln in log.splitlines() if ln.startswith("{")][-1])
+    assert res["gradients_equal_across_ranks"] and res["parameters_in_sync"] and res["steps"] == 100

@@ -1,0 +1,95 @@
+"""FSDP semantics on CPU with simulated ranks: sharding arithmetic, config validation, and
+training equivalence (sharded run == single-process run on the concatenated batch)."""
+import copy
+
+import pytest
+import torch
+
+from ml_framework_b200.amp.grad_scaler import DynamicLossScaler, DynamicScalerConfig
+from ml_framework_b200.dist.process_group import run_fake_world
+from ml_framework_b200.models import GPT, GPTConfig
+from ml_framework_b200.optim.optimizers import AdamW
+from ml_framework_b200.parallel.fsdp import FSDP, FSDPConfig, FSDPCpuOffloadConfig, padded_numel, shard_bounds
+
+
+def test_shard_bounds_rule():
+    # ceil(N / W) with a short last shard
+    assert [shard_bounds(10, 4, r) for r in range(4)] == [(0, 3), (3, 6), (6, 9), (9, 10)]
+    assert [shard_bounds(2, 4, r) for r in range(4)] == [(0, 1), (1, 2), (2, 2), (2, 2)]
+    assert padded_numel(10, 4) == 32 and padded_numel(64, 4) == 64
+
+
+def test_config_validation():
+    FSDPConfig().validate()
+    for bad in (dict(sharding_strategy="nope"), dict(bucket_size_mb=0), dict(bucket_size_mb=1001),
+                dict(num_communication_workers=0), dict(num_communication_workers=17)):
+        with pytest.raises(ValueError):
+            FSDPConfig(**bad).validate()
+    with pytest.raises(ValueError):
+        FSDPCpuOffloadConfig(prefetch_steps=11).validate()
+
+
+def _reference_run(cfg, ids, tgt, steps, kw):
+    torch.manual_seed(0)
+    model = GPT(cfg)
+    opt = AdamW(list(dict.fromkeys(model.parameters())), **kw)
+    losses = []
+    for s in range(steps):
+        opt.zero_grad()
+        loss = model(ids.reshape(-1, ids.shape[-1]), tgt.reshape(-1, tgt.shape[-1]))
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    return losses, {n: p.detach().clone() for n, p in model.named_parameters()}
+
+
+@pytest.mark.parametrize("strategy", ["full", "grad_op", "layer_wise"])
+def test_fsdp_matches_single_process(strategy):
+    W, steps = 2, 3
+    cfg = GPTConfig(n_layers=2, d_model=64, n_heads=2, d_ff=128, vocab_size=100, max_seq=16, vocab_multiple=8)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 100, (W, 2, 16), generator=g)
+    tgt = torch.randint(0, 100, (W, 2, 16), generator=g)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-4, weight_decay=0.01)  # eps above fp32 noise: the key bias has a mathematically zero gradient
+    ref_losses, ref_params = _reference_run(cfg, ids, tgt, steps, kw)
+    torch.manual_seed(0)
+    base = GPT(cfg)     # the global RNG is shared by the rank threads: build once, copy per rank
+
+    def run(pg):
+        model = copy.deepcopy(base)
+        fs = FSDP(model, FSDPConfig(sharding_strategy=strategy, min_shard_numel=64), pg, optimizer_kwargs=kw)
+        losses = []
+        for s in range(steps):
+            losses.append(fs.train_step(ids[pg.rank], tgt[pg.rank]).item())
+        return losses, fs.full_state_dict(), fs.units[0].shard_numel, fs.units[0].full_numel
+    outs = run_fake_world(W, run)
+    for r in range(W):
+        losses, params, shard_n, full_n = outs[r]
+        assert shard_n * W == full_n
+        for n, p in ref_params.items():
+            assert torch.allclose(params[n], p, atol=2e-5), n
+    # mean of the per-rank losses equals the loss on the concatenated batch
+    for s in range(steps):
+        assert abs(sum(outs[r][0][s] for r in range(W)) / W - ref_losses[s]) < 1e-4
+
+
+def test_fsdp_overflow_skips_on_every_rank():
+    W = 2
+    cfg = GPTConfig(n_layers=1, d_model=64, n_heads=2, d_ff=128, vocab_size=50, max_seq=8, vocab_multiple=8)
+    ids = torch.randint(0, 50, (W, 1, 8))
+
+    torch.manual_seed(0)
+    base = GPT(cfg)
+
+    def run(pg):
+        model = copy.deepcopy(base)
+        fs = FSDP(model, FSDPConfig(min_shard_numel=64), pg, optimizer_kwargs=dict(lr=1e-2))
+        scaler = DynamicLossScaler(DynamicScalerConfig(initial_scale=1024.0))
+        before = fs.master.clone()
+        if pg.rank == 1:
+            # poison one gradient on one rank only: both ranks must skip
+            h = model.blocks[0].mlp.fc1.weight.register_hook(lambda g: g * float("inf"))
+        fs.train_step(ids[pg.rank], ids[pg.rank], scaler)
+        return torch.equal(before, fs.master), scaler.scale
+    outs = run_fake_world(W, run)
+    assert all(o[0] for o in outs) and all(o[1] == 512.0 for o in outs)
