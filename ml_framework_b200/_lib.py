@@ -33,6 +33,7 @@ class GemmComm(C.Structure):
         ("gathered", C.c_void_p), ("flags", C.c_void_p), ("counters", C.c_void_p),
         ("scatter_out", C.c_int), ("rows_per_owner", C.c_int),
         ("out_peer", C.c_void_p * 8),
+        ("extra_segs", C.c_void_p), ("n_extra", C.c_int), ("_pad1", C.c_int),
     ]
 
 

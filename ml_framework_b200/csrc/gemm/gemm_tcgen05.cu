@@ -65,6 +65,8 @@ struct GemmKernelParams {
   void* gathered;
   uint32_t* flags_ready;
   uint32_t* counters;
+  const void* extra_segs;   // {src, dst, bytes} triples copied after the gated chunks, no flags
+  int n_extra;
   // scatter
   int scatter_out, rows_per_owner;
   void* out_peer[8];
@@ -137,6 +139,18 @@ struct CopyPiece {
 __device__ __forceinline__ void chunk_slice(const GemmKernelParams& p, int n_flags, int first_local, int i,
                                             int cta, int& c, const char*& src, char*& dst, long long& lo,
                                             long long& hi) {
+  if (i >= n_flags) {
+    // un-gated extra segment (prefetch for later kernels)
+    const long long* sg = static_cast<const long long*>(p.extra_segs) + 3 * (i - n_flags);
+    c = -1;
+    src = reinterpret_cast<const char*>(sg[0]);
+    dst = reinterpret_cast<char*>(sg[1]);
+    const long long n16e = sg[2] / 16;
+    const long long pere = (n16e + p.n_copy_ctas - 1) / p.n_copy_ctas;
+    lo = min(n16e, pere * cta) * 16;
+    hi = min(n16e, pere * (cta + 1)) * 16;
+    return;
+  }
   c = first_local + i;
   if (c >= n_flags) c -= n_flags;
   const int row0 = c * p.flag_rows;
@@ -156,7 +170,7 @@ __device__ __forceinline__ CopyPiece next_piece(const GemmKernelParams& p, int n
                                                 int cta, CopyCursor& cur) {
   CopyPiece pc;
   pc.valid = false;
-  if (cur.i >= n_flags) return pc;
+  if (cur.i >= n_flags + p.n_extra) return pc;
   int c;
   const char* src;
   char* dst;
@@ -189,8 +203,8 @@ __device__ void gather_copy_role(const GemmKernelParams& p) {
   int abort_local = 0;
   volatile int* abort_flag = &abort_local;
 
-  const int n_flags = (p.total_rows + p.flag_rows - 1) / p.flag_rows;
-  const int first_local = (p.rank * p.rows_per_rank) / p.flag_rows;
+  const int n_flags = p.gather_operand != 0 ? (p.total_rows + p.flag_rows - 1) / p.flag_rows : 0;
+  const int first_local = p.gather_operand != 0 ? (p.rank * p.rows_per_rank) / p.flag_rows : 0;
   const int cta = blockIdx.x;
   CopyCursor lc{0, 0}, sc{0, 0};
   int issued = 0;  // pieces whose load has been issued
@@ -214,7 +228,7 @@ __device__ void gather_copy_role(const GemmKernelParams& p) {
     if (!mbar_wait(bar0 + 8u * slot, ph, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG)) break;
     if (pc.bytes) bulk_store(pc.dst, base + slot * kCopyPiece, pc.bytes);
     tma_store_commit();
-    if (pc.last_of_chunk) {
+    if (pc.last_of_chunk && pc.chunk >= 0) {
       tma_store_wait_all<0>();
       fence_proxy_async_all();
       __threadfence();
@@ -252,12 +266,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
 
-  if (p.gather_operand != 0 && (int)blockIdx.x < p.n_copy_ctas) {
+  if ((int)blockIdx.x < p.n_copy_ctas) {
     gather_copy_role(p);
     return;
   }
-  const int cta = blockIdx.x - (p.gather_operand != 0 ? p.n_copy_ctas : 0);
-  const int n_ctas = gridDim.x - (p.gather_operand != 0 ? p.n_copy_ctas : 0);
+  const int cta = blockIdx.x - p.n_copy_ctas;
+  const int n_ctas = gridDim.x - p.n_copy_ctas;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -716,9 +730,17 @@ MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
   const void* a_base = a->a;
   const void* b_base = a->b;
   int n_copy = 0;
+  if (cm && !cm->gather_operand && cm->n_extra > 0) {
+    MLF_REQUIRE(cm->n_copy_ctas >= 1 && cm->n_copy_ctas < sms, "n_copy_ctas out of range");
+    p.n_copy_ctas = n_copy = cm->n_copy_ctas;
+    p.extra_segs = cm->extra_segs;
+    p.n_extra = cm->n_extra;
+  }
   if (cm && cm->gather_operand) {
     MLF_REQUIRE(cm->world >= 1 && cm->world <= 8, "world %d out of range", cm->world);
     MLF_REQUIRE(cm->n_copy_ctas >= 1 && cm->n_copy_ctas < sms, "n_copy_ctas out of range");
+    p.extra_segs = cm->extra_segs;
+    p.n_extra = cm->n_extra;
     MLF_REQUIRE(cm->flag_rows > 0 && cm->flag_rows % (gatherA ? BM : BN) == 0,
                 "flag_rows %d must be a multiple of the tile extent %d", cm->flag_rows, gatherA ? BM : BN);
     MLF_REQUIRE(cm->rows_per_rank % cm->flag_rows == 0, "rows_per_rank must be a multiple of flag_rows");

@@ -43,6 +43,12 @@ typedef struct MlfGemmComm {
   int scatter_out;          // 1 = route rows: out_peer[owner] + (rank*rows_per_owner + local_row)*ldo
   int rows_per_owner;       // output rows owned by each rank
   void* out_peer[8];        // out_peer[r] = rank r's partial buffer [W, rows_per_owner, ldo]
+  // ---- piggy-backed copies: {src, dst, bytes} int64 triples (device array) the copy CTAs move
+  //      after the gated chunks, with no ready flags (consumers are later kernels on the stream).
+  //      May be used with gather_operand == 0 (n_copy_ctas must then still be set).
+  const void* extra_segs;
+  int n_extra;
+  int _pad1;
 } MlfGemmComm;
 
 typedef struct MlfGemmArgs {

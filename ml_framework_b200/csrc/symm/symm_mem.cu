@@ -1,0 +1,357 @@
+// Symmetric (peer-mapped) memory and the collectives that run over it.
+//
+// Every rank allocates buffers of identical size, exports them as CUDA IPC handles, and maps
+// every peer's buffer into its own address space, so a kernel can load from / store to any
+// rank's copy directly over NVLink (through NVSwitch every peer is one hop away). On top of
+// that this file provides:
+//   * a device-side barrier over a signal pad (bounded wait, error status instead of a hang),
+//   * reduce-scatter of gradient buckets by direct peer reads with unscale and overflow
+//     detection fused (each rank sums its slice of all W copies in fp32),
+//   * two-shot all-reduce for DDP buckets (reduce own slice, then store it to every peer),
+//   * one-shot all-reduce for small latency-bound messages (tensor-parallel decode).
+// Kernels that wait on peers are separate launches from kernels that move data, so the data
+// kernels can be validated on one GPU with every "rank" buffer local.
+//
+// Reference semantics: ring reduce-scatter / all-gather
+// (src/MLFramework/Distributed/RingAllReduce.cs:86-163, FSDP/ReduceScatterOperation.cs:54-125),
+// bucket all-reduce (src/MLFramework/Distributed/GradientBucket.cs:112-126), algorithm choice by
+// message size (src/MLFramework/Communication/Optimizations/AlgorithmSelector.cs:24-65). On
+// NVSwitch ring / tree schedules bring nothing: small messages go one-shot, large ones two-shot.
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+#include "../mlf_api.h"
+
+namespace mlf {
+
+struct PeerPtrs {
+  void* p[8];
+};
+
+// ------------------------------------------------------------------------------------------
+// barrier: pad[r] is rank r's signal pad (uint32 [8 x 32] : slot s*32 written by rank s).
+// ------------------------------------------------------------------------------------------
+__global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, int* err) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    uint32_t* remote = static_cast<uint32_t*>(pads.p[t]) + rank * 32;
+    __threadfence_system();
+    st_release_sys(remote, epoch);
+  }
+  if (t < world) {
+    const uint32_t* mine = static_cast<const uint32_t*>(pads.p[rank]) + t * 32;
+    wait_flag_ge_sys(mine, epoch, err, ERR_WAIT_PEER_FLAG);
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------
+// segment table: the same layout on every rank
+// ------------------------------------------------------------------------------------------
+struct ReduceSeg {
+  long long src_off;   // element offset of this rank's slice inside every rank's full buffer
+  long long dst_off;   // element offset in the local output
+  long long numel;     // elements in the slice
+};
+
+// out[dst_off + i] = scale * sum_r bufs[r][src_off + i]   (bf16 in, bf16 or fp32 out)
+// found_inf is raised when a reduced value is not finite; sumsq accumulates the squared norm.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+rs_reduce_kernel(PeerPtrs bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out, float scale,
+                 const float* scale_ptr, int* found_inf, float* sumsq) {
+  const float sc = scale * (scale_ptr ? *scale_ptr : 1.f);
+  float acc_sq = 0.f;
+  bool bad = false;
+  for (int s = 0; s < n_segs; ++s) {
+    const ReduceSeg sg = segs[s];
+    const long long nvec = sg.numel / 8;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+      float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      uint4 v[8];
+      // issue all peer loads first (start with the next rank so the links are used evenly)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (k < world) {
+          int r = rank + 1 + k;
+          if (r >= world) r -= world;
+          v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[r]) + sg.src_off + i * 8);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (k < world) {
+          float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
+          a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] *= sc;
+        if (!isfinite(a[j])) bad = true;
+        acc_sq += a[j] * a[j];
+      }
+      OutT* o = out + sg.dst_off + i * 8;
+      if (sizeof(OutT) == 2) {
+        uint4 w;
+        w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
+        *reinterpret_cast<uint4*>(o) = w;
+      } else {
+        reinterpret_cast<float4*>(o)[0] = make_float4(a[0], a[1], a[2], a[3]);
+        reinterpret_cast<float4*>(o)[1] = make_float4(a[4], a[5], a[6], a[7]);
+      }
+    }
+  }
+  if (found_inf && __any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(found_inf, 1);
+  if (sumsq) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc_sq += __shfl_xor_sync(0xffffffffu, acc_sq, o);
+    if ((threadIdx.x & 31) == 0 && isfinite(acc_sq)) atomicAdd(sumsq, acc_sq);
+  }
+}
+
+// Two-shot all-reduce, in place over symmetric buffers: rank r reduces slice r of all copies and
+// stores the result into slice r of every rank's buffer. A barrier must separate it from the
+// producers before and from the consumers after.
+__global__ void __launch_bounds__(256)
+ar_two_shot_kernel(PeerPtrs bufs, int world, int rank, long long numel, float scale) {
+  const long long per = ((numel / 8 + world - 1) / world) * 8;
+  const long long lo = per * rank;
+  const long long hi = lo + per < numel ? lo + per : numel;
+  const long long nvec = hi > lo ? (hi - lo) / 8 : 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        int r = rank + 1 + k;
+        if (r >= world) r -= world;
+        v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[r]) + lo + i * 8);
+      }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
+        a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+      }
+    uint4 w;
+    w.x = pack_bf16x2(a[0] * scale, a[1] * scale); w.y = pack_bf16x2(a[2] * scale, a[3] * scale);
+    w.z = pack_bf16x2(a[4] * scale, a[5] * scale); w.w = pack_bf16x2(a[6] * scale, a[7] * scale);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        int r = rank + 1 + k;
+        if (r >= world) r -= world;
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[r]) + lo + i * 8) = w;
+      }
+  }
+}
+
+// One-shot all-reduce for small messages: every rank reads all W copies and writes its own
+// private output (no second exchange). in: symmetric staging buffers; out: local tensor.
+__global__ void __launch_bounds__(256)
+ar_one_shot_kernel(PeerPtrs bufs, int world, int rank, __nv_bfloat16* out, long long numel, const __nv_bfloat16* residual) {
+  const long long nvec = numel / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[k]) + i * 8);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
+        a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+      }
+    if (residual) {
+      const uint4 rr = *reinterpret_cast<const uint4*>(residual + i * 8);
+      float2 f0 = unpack_bf16x2(rr.x), f1 = unpack_bf16x2(rr.y), f2 = unpack_bf16x2(rr.z), f3 = unpack_bf16x2(rr.w);
+      a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = w;
+  }
+}
+
+// out[row, :] = sum_w partial[w, row, :] (+ bias) (+ residual): the second half of GEMM->reduce-
+// scatter, where peers have stored their partial tiles into this rank's [W, rows, cols] buffer.
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const __nv_bfloat16* partial, int world, long long rows, int cols, __nv_bfloat16* out, long long ldo,
+                    const __nv_bfloat16* bias, const __nv_bfloat16* residual, long long ldr) {
+  const int vpr = cols / 8;
+  const long long total = rows * vpr;
+  const long long plane = rows * (long long)cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int w = 0; w < world; ++w) {
+      const uint4 v = *reinterpret_cast<const uint4*>(partial + w * plane + r * cols + c);
+      float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+      a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+    }
+    if (bias) {
+      const uint4 v = *reinterpret_cast<const uint4*>(bias + c);
+      float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+      a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+    }
+    if (residual) {
+      const uint4 v = *reinterpret_cast<const uint4*>(residual + r * ldr + c);
+      float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+      a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = w;
+  }
+}
+
+// Plain multi-segment copy from peers (all-gather without a GEMM attached).
+struct CopySegHost {
+  const void* src;
+  void* dst;
+  long long bytes;
+};
+__global__ void __launch_bounds__(256) peer_copy_kernel(const CopySegHost* segs, int n_segs) {
+  for (int s = 0; s < n_segs; ++s) {
+    const CopySegHost sg = segs[s];
+    const uint4* src = static_cast<const uint4*>(sg.src);
+    uint4* dst = static_cast<uint4*>(sg.dst);
+    const long long n = sg.bytes / 16;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long step = (long long)gridDim.x * blockDim.x;
+    for (; i + 3 * step < n; i += 4 * step) {
+      const uint4 a = src[i], b = src[i + step], c = src[i + 2 * step], d = src[i + 3 * step];
+      dst[i] = a; dst[i + step] = b; dst[i + 2 * step] = c; dst[i + 3 * step] = d;
+    }
+    for (; i < n; i += step) dst[i] = src[i];
+  }
+}
+
+}  // namespace mlf
+
+using namespace mlf;
+
+// ---- allocation and IPC --------------------------------------------------------------------
+MLF_API int mlf_symm_alloc(long long bytes, void** ptr, unsigned char* handle64) {
+  MLF_REQUIRE(bytes > 0 && ptr && handle64, "symm_alloc: bad arguments");
+  void* p = nullptr;
+  MLF_CHECK_CUDA(cudaMalloc(&p, (size_t)bytes));
+  MLF_CHECK_CUDA(cudaMemset(p, 0, (size_t)bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return check_cuda(e, "cudaIpcGetMemHandle");
+  }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return 0;
+}
+MLF_API int mlf_symm_open(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  MLF_CHECK_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+MLF_API int mlf_symm_close(void* ptr) {
+  MLF_CHECK_CUDA(cudaIpcCloseMemHandle(ptr));
+  return 0;
+}
+MLF_API int mlf_symm_free(void* ptr) {
+  MLF_CHECK_CUDA(cudaFree(ptr));
+  return 0;
+}
+
+static PeerPtrs to_peers(void* const* ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
+  return pp;
+}
+
+// ---- collectives ---------------------------------------------------------------------------
+MLF_API int mlf_symm_barrier(void* const* pads, int rank, int world, unsigned int epoch, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, "symm_barrier: bad rank/world");
+  symm_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(pads, world), rank, world, epoch,
+                                                                            device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// segs: device array of {src_off, dst_off, numel} (elements; multiples of 8). out_fp32 selects
+// the output type. scale_ptr / found_inf / sumsq are optional device pointers.
+MLF_API int mlf_rs_reduce(void* const* bufs, int world, int rank, const void* segs, int n_segs, void* out, int out_fp32,
+                          float scale, const float* scale_ptr, int* found_inf, float* sumsq, long long total_numel,
+                          uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8, "rs_reduce: world must be 1..8");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  long long g = (total_numel / 8 + 255) / 256;
+  const long long cap = (long long)sm_count() * 4;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  if (out_fp32)
+    rs_reduce_kernel<float><<<(int)g, 256, 0, st>>>(to_peers(bufs, world), world, rank, static_cast<const ReduceSeg*>(segs),
+                                                    n_segs, static_cast<float*>(out), scale, scale_ptr, found_inf, sumsq);
+  else
+    rs_reduce_kernel<__nv_bfloat16><<<(int)g, 256, 0, st>>>(to_peers(bufs, world), world, rank,
+                                                            static_cast<const ReduceSeg*>(segs), n_segs,
+                                                            static_cast<__nv_bfloat16*>(out), scale, scale_ptr, found_inf, sumsq);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+MLF_API int mlf_ar_two_shot(void* const* bufs, int world, int rank, long long numel, float scale, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && numel % 8 == 0, "ar_two_shot: numel must be a multiple of 8");
+  long long g = (numel / 8 / world + 255) / 256;
+  const long long cap = (long long)sm_count() * 4;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  ar_two_shot_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(bufs, world), world, rank, numel, scale);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+MLF_API int mlf_ar_one_shot(void* const* bufs, int world, int rank, void* out, long long numel, const void* residual,
+                            uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && numel % 8 == 0, "ar_one_shot: numel must be a multiple of 8");
+  long long g = (numel / 8 + 255) / 256;
+  const long long cap = (long long)sm_count() * 2;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  ar_one_shot_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      to_peers(bufs, world), world, rank, static_cast<__nv_bfloat16*>(out), numel, static_cast<const __nv_bfloat16*>(residual));
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+MLF_API int mlf_sum_partials(const void* partial, int world, long long rows, int cols, void* out, long long ldo,
+                             const void* bias, const void* residual, long long ldr, uint64_t stream) {
+  MLF_REQUIRE(cols % 8 == 0 && ldo % 8 == 0, "sum_partials: cols and pitch must be multiples of 8");
+  long long g = (rows * (cols / 8) + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  sum_partials_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(partial), world, rows, cols, static_cast<__nv_bfloat16*>(out), ldo,
+      static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual), ldr);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// segs: device array of {src, dst, bytes} (bytes multiple of 16).
+MLF_API int mlf_peer_copy(const void* segs, int n_segs, int ctas, uint64_t stream) {
+  if (n_segs <= 0) return 0;
+  if (ctas <= 0) ctas = sm_count();
+  peer_copy_kernel<<<ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const CopySegHost*>(segs), n_segs);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,168 @@
+"""Symmetric memory: buffers of equal size on every rank, each mapped into every peer.
+
+``SymmetricMemory(pg)`` is created once per process group. ``alloc(nbytes)`` is collective: each
+rank allocates with the native layer, the CUDA IPC handles are exchanged through the process
+group, and every rank maps every peer's buffer. The result is a :class:`SymmBuffer` with a
+local tensor view and the table of peer pointers the fused kernels take. With a single rank
+(or in ``emulate`` mode on one GPU, used by tests) all "peer" buffers are local allocations.
+
+Collectives over these buffers (device barrier, reduce-scatter with fused unscale/overflow
+check, two-shot / one-shot all-reduce, peer copy) are thin wrappers over
+``csrc/symm/symm_mem.cu``. The reference's counterparts are its NCCL / ring backends
+(src/MLFramework/Communication/Backends/NCCLBackend.cs:157-309,
+src/MLFramework/Distributed/RingAllReduce.cs:30-163) and its placeholder GPUDirect probe
+(src/MLFramework/Communication/Optimizations/GPUDirectManager.cs:22-28).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _lib
+
+
+class _RawCuda:
+    """Adapter exposing a raw device pointer through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def tensor_from_ptr(ptr: int, nbytes: int, device) -> torch.Tensor:
+    return torch.as_tensor(_RawCuda(ptr, nbytes), device=device)
+
+
+class SymmBuffer:
+    def __init__(self, local_ptr: int, peer_ptrs: List[int], nbytes: int, device, rank: int):
+        self.nbytes, self.rank, self.world = nbytes, rank, len(peer_ptrs)
+        self.ptrs = peer_ptrs                     # ptrs[r] = address of rank r's buffer in this process
+        self.local = tensor_from_ptr(local_ptr, nbytes, device)
+        self._arr = (C.c_void_p * 8)(*[C.c_void_p(p) for p in peer_ptrs] + [None] * (8 - len(peer_ptrs)))
+
+    def view(self, dtype: torch.dtype, numel: Optional[int] = None, offset_bytes: int = 0) -> torch.Tensor:
+        t = self.local[offset_bytes:]
+        t = t.view(dtype)
+        return t if numel is None else t[:numel]
+
+    def peer_table(self, offset_bytes: int = 0):
+        if offset_bytes == 0:
+            return self._arr
+        return (C.c_void_p * 8)(*[C.c_void_p(p + offset_bytes) for p in self.ptrs] + [None] * (8 - self.world))
+
+    def peer_view(self, r: int, dtype: torch.dtype, device) -> torch.Tensor:
+        """Tensor over rank r's buffer as mapped here (debug / tests; loads cross NVLink)."""
+        return tensor_from_ptr(self.ptrs[r], self.nbytes, device).view(dtype)
+
+
+class SymmetricMemory:
+    def __init__(self, pg=None, device=None, emulate_world: int = 0):
+        self.pg = pg
+        self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+        self.emulate = emulate_world > 0
+        self.world = emulate_world if self.emulate else (pg.world_size if pg is not None else 1)
+        self.rank = 0 if (self.emulate or pg is None) else pg.rank
+        self._lib = _lib.get()
+        self._owned: List[int] = []
+        self._opened: List[int] = []
+        self._epoch = 0
+        self._pad: Optional[SymmBuffer] = None
+
+    # ---- allocation
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        nbytes = (nbytes + 255) // 256 * 256
+        if self.emulate:
+            raise RuntimeError("use alloc_emulated() in emulate mode")
+        ptr = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        _lib.check(self._lib.mlf_symm_alloc(C.c_longlong(nbytes), C.byref(ptr), handle), "mlf_symm_alloc")
+        self._owned.append(ptr.value)
+        if self.world == 1:
+            return SymmBuffer(ptr.value, [ptr.value], nbytes, self.device, 0)
+        handles = self.pg.all_gather_object(bytes(handle))
+        peers = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                peers.append(ptr.value)
+                continue
+            hb = (C.c_ubyte * 64).from_buffer_copy(h)
+            pp = C.c_void_p()
+            _lib.check(self._lib.mlf_symm_open(hb, C.byref(pp)), "mlf_symm_open")
+            self._opened.append(pp.value)
+            peers.append(pp.value)
+        return SymmBuffer(ptr.value, peers, nbytes, self.device, self.rank)
+
+    def alloc_emulated(self, nbytes: int) -> List[SymmBuffer]:
+        """One GPU, ``emulate_world`` local buffers: returns the per-"rank" views of the same table."""
+        nbytes = (nbytes + 255) // 256 * 256
+        ptrs = []
+        for _ in range(self.world):
+            ptr = C.c_void_p()
+            handle = (C.c_ubyte * 64)()
+            _lib.check(self._lib.mlf_symm_alloc(C.c_longlong(nbytes), C.byref(ptr), handle), "mlf_symm_alloc")
+            self._owned.append(ptr.value)
+            ptrs.append(ptr.value)
+        return [SymmBuffer(ptrs[r], ptrs, nbytes, self.device, r) for r in range(self.world)]
+
+    # ---- synchronisation
+    def barrier(self, stream=None):
+        """Device-side barrier on the current stream: returns immediately on the host; kernels
+        queued after it run only once every rank has reached the same point."""
+        if self.world == 1 or self.emulate:
+            return
+        if self._pad is None:
+            self._pad = self.alloc(8 * 32 * 4)
+            self.pg.barrier()
+        self._epoch += 1
+        rc = self._lib.mlf_symm_barrier(self._pad.peer_table(), self.rank, self.world, C.c_uint(self._epoch),
+                                        C.c_uint64(_lib.stream_handle(stream)))
+        _lib.check(rc, "mlf_symm_barrier")
+
+    # ---- collectives
+    def rs_reduce(self, buf: SymmBuffer, segs_dev: torch.Tensor, n_segs: int, out: torch.Tensor, total_numel: int, *,
+                  rank: Optional[int] = None, scale: float = 1.0, scale_ptr: Optional[torch.Tensor] = None,
+                  found_inf: Optional[torch.Tensor] = None, sumsq: Optional[torch.Tensor] = None, offset_bytes: int = 0):
+        r = self.rank if rank is None else rank
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+        rc = self._lib.mlf_rs_reduce(buf.peer_table(offset_bytes), self.world, r, p(segs_dev), n_segs, p(out),
+                                     int(out.dtype == torch.float32), C.c_float(scale), p(scale_ptr), p(found_inf), p(sumsq),
+                                     C.c_longlong(total_numel), C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_rs_reduce")
+
+    def all_reduce_two_shot(self, buf: SymmBuffer, numel: int, scale: float = 1.0, rank: Optional[int] = None,
+                            offset_bytes: int = 0):
+        r = self.rank if rank is None else rank
+        rc = self._lib.mlf_ar_two_shot(buf.peer_table(offset_bytes), self.world, r, C.c_longlong(numel), C.c_float(scale),
+                                       C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_ar_two_shot")
+
+    def all_reduce_one_shot(self, buf: SymmBuffer, out: torch.Tensor, numel: int, residual: Optional[torch.Tensor] = None,
+                            rank: Optional[int] = None, offset_bytes: int = 0):
+        r = self.rank if rank is None else rank
+        rc = self._lib.mlf_ar_one_shot(buf.peer_table(offset_bytes), self.world, r, C.c_void_p(out.data_ptr()),
+                                       C.c_longlong(numel), C.c_void_p(residual.data_ptr()) if residual is not None else None,
+                                       C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_ar_one_shot")
+
+    def peer_copy(self, segs_dev: torch.Tensor, n_segs: int, ctas: int = 0):
+        rc = self._lib.mlf_peer_copy(C.c_void_p(segs_dev.data_ptr()), n_segs, ctas, C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_peer_copy")
+
+    def close(self):
+        torch.cuda.synchronize()
+        for p in self._opened:
+            self._lib.mlf_symm_close(C.c_void_p(p))
+        for p in self._owned:
+            self._lib.mlf_symm_free(C.c_void_p(p))
+        self._opened, self._owned = [], []
+
+
+def make_reduce_segs(segs: Sequence[tuple], device) -> torch.Tensor:
+    """Device table of (src_off, dst_off, numel) int64 triples for :meth:`SymmetricMemory.rs_reduce`."""
+    return torch.tensor([list(s) for s in segs], dtype=torch.int64, device=device).contiguous()
+
+
+def make_copy_segs(segs: Sequence[tuple], device) -> torch.Tensor:
+    """Device table of (src_ptr, dst_ptr, bytes) int64 triples for :meth:`SymmetricMemory.peer_copy`."""
+    return torch.tensor([list(s) for s in segs], dtype=torch.int64, device=device).contiguous()
