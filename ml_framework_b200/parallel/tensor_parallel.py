@@ -1,0 +1,603 @@
+"""Tensor parallelism (Megatron style) with optional sequence parallelism.
+
+Layer semantics follow the reference (src/MLFramework/Layers/TensorParallel/ColumnParallelLinear.cs:54-143,
+RowParallelLinear.cs:55-167, *WithInputGather.cs): a column-parallel linear holds the weight
+shard ``[out/W, in]`` and bias shard ``[out/W]`` (``out % W == 0``), computes
+``Y_local = X W_shard^T + b_shard`` and optionally all-gathers the output on the last dimension;
+a row-parallel linear holds ``[out, in/W]`` (``in % W == 0``), takes an input that is already split
+on the last dimension (or slices it), sums the partial products over ranks and adds the unsharded
+bias once, after the reduction. Init: N(0, sqrt(2 / (in + out))).
+
+Backward is complete here, unlike the reference whose column backward omits the all-reduce of
+dX (Layers/TensorParallel/ColumnParallelLinearGrad.cs:120-166): the f / g operators of Megatron
+are autograd functions (identity forward + all-reduce backward, and vice versa).
+
+With ``sequence_parallel`` activations between blocks are sharded over tokens ``[T/W, d]``; the
+column layer then computes all-gather(X) -> GEMM and the row layer GEMM -> reduce-scatter. On
+GPUs with peer-mapped memory these run as ONE kernel each (copy CTAs pulling the peers' token
+chunks while tensor-core CTAs consume them; epilogue stores routed to the owning rank), see
+``csrc/gemm/gemm_tcgen05.cu``. Otherwise they are process-group collectives around the GEMM.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import _lib
+from ..dist.process_group import ReduceOp
+from ..ops import functional as Fm
+from ..ops.gemm import gemm
+
+
+# ------------------------------------------------------------------ context
+class TPContext:
+    """Tensor-parallel group state: communicator, rank, and the fused-kernel resources."""
+
+    def __init__(self, pg, symm=None, fused: bool = True, n_copy_ctas: int = 16):
+        self.pg = pg
+        self.world = pg.world_size if pg is not None else 1
+        self.rank = pg.rank if pg is not None else 0
+        self.symm = symm
+        self.fused = bool(fused and symm is not None and self.world > 1)
+        self.n_copy_ctas = n_copy_ctas
+        self._bufs: Dict[tuple, object] = {}
+        self._flags: Dict[int, torch.Tensor] = {}
+
+    def symm_buffer(self, key: str, nbytes: int):
+        k = (key, nbytes)
+        if k not in self._bufs:
+            self._bufs[k] = self.symm.alloc(nbytes)
+        return self._bufs[k]
+
+    def flags(self, n: int, device) -> torch.Tensor:
+        if n not in self._flags:
+            self._flags[n] = torch.zeros(2 * n, dtype=torch.int32, device=device)
+        return self._flags[n]
+
+
+_GLOBAL: Optional[TPContext] = None
+
+
+def initialize(pg, symm=None, fused: bool = True) -> TPContext:
+    """``TensorParallel.Initialize`` (src/MLFramework/Layers/TensorParallel/TensorParallel.cs:53)."""
+    global _GLOBAL
+    _GLOBAL = TPContext(pg, symm, fused)
+    return _GLOBAL
+
+
+def get_context() -> TPContext:
+    if _GLOBAL is None:
+        raise RuntimeError("tensor parallelism is not initialised")
+    return _GLOBAL
+
+
+def get_world_size() -> int:
+    return get_context().world
+
+
+def get_rank() -> int:
+    return get_context().rank
+
+
+# ------------------------------------------------------------------ f / g and SP operators
+class _CopyToTP(torch.autograd.Function):      # f: identity forward, all-reduce backward
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        if ctx.tp.world > 1:
+            ctx.tp.pg.all_reduce(g, ReduceOp.SUM)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):  # g: all-reduce forward, identity backward
+    @staticmethod
+    def forward(ctx, x, tp):
+        x = x.contiguous()
+        if tp.world > 1:
+            tp.pg.all_reduce(x, ReduceOp.SUM)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _GatherLastDim(torch.autograd.Function):  # all-gather on last dim fwd, slice bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.pg.all_gather(x, dim=-1) if tp.world > 1 else x
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        return (g.chunk(tp.world, dim=-1)[tp.rank].contiguous() if tp.world > 1 else g), None
+
+
+class _GatherTokens(torch.autograd.Function):   # SP: all-gather tokens fwd, reduce-scatter bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.pg.all_gather(x, dim=0) if tp.world > 1 else x
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        return (tp.pg.reduce_scatter(g.contiguous(), ReduceOp.SUM, dim=0) if tp.world > 1 else g), None
+
+
+class _ScatterTokens(torch.autograd.Function):  # SP: reduce-scatter tokens fwd, all-gather bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return tp.pg.reduce_scatter(x.contiguous(), ReduceOp.SUM, dim=0) if tp.world > 1 else x
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        return (tp.pg.all_gather(g.contiguous(), dim=0) if tp.world > 1 else g), None
+
+
+def copy_to_tp_region(x, tp): return _CopyToTP.apply(x, tp)
+def reduce_from_tp_region(x, tp): return _ReduceFromTP.apply(x, tp)
+def gather_last_dim(x, tp): return _GatherLastDim.apply(x, tp)
+def gather_tokens(x, tp): return _GatherTokens.apply(x, tp)
+def scatter_tokens(x, tp): return _ScatterTokens.apply(x, tp)
+
+
+# ------------------------------------------------------------------ fused kernels (GPU, peer memory)
+def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: str, bias=None, flags=0, aux_out=None):
+    """out[T, N] = all_gather_tokens(x_shard)[T, K] @ w[N, K]^T in one kernel. Returns (out, x_full)."""
+    rows, K = x_shard.shape
+    W, T = tp.world, x_shard.shape[0] * tp.world
+    stage = tp.symm_buffer(key + ".ag_stage", rows * K * 2)
+    stage.view(torch.bfloat16, rows * K).view(rows, K).copy_(x_shard)
+    tp.symm.barrier()                                   # every peer's stage is written
+    x_full = torch.empty(T, K, dtype=torch.bfloat16, device=x_shard.device)
+    flag_rows = 128
+    while rows % flag_rows:
+        flag_rows //= 2
+    nfl = T // max(flag_rows, 1)
+    fl = tp.flags(nfl, x_shard.device)
+    fl.zero_()
+    cm = _lib.GemmComm()
+    cm.gather_operand, cm.world, cm.rank, cm.n_copy_ctas = 1, W, tp.rank, tp.n_copy_ctas
+    cm.rows_per_rank, cm.flag_rows, cm.row_bytes = rows, flag_rows, K * 2
+    for r in range(W):
+        cm.src[r] = stage.ptrs[r]
+    cm.gathered, cm.flags, cm.counters = x_full.data_ptr(), fl.data_ptr(), fl[nfl:].data_ptr()
+    out = gemm(x_shard, w, comm=cm, m_override=T, bias=bias, flags=flags, aux_out=aux_out)
+    return out, x_full
+
+
+def _fused_gemm_rs(tp: TPContext, a: torch.Tensor, b: torch.Tensor, key: str, *, b_mn=False, bias=None, residual=None):
+    """out[T/W, N] = reduce_scatter_tokens(a[T, K] @ B^T): epilogue stores routed to the owners, then a local sum."""
+    T = a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    W = tp.world
+    rows = T // W
+    part = tp.symm_buffer(key + ".rs_part", W * rows * N * 2)
+    tp.symm.barrier()                                   # previous consumers of the partial buffers are done
+    cm = _lib.GemmComm()
+    cm.scatter_out, cm.rows_per_owner, cm.world, cm.rank = 1, rows, W, tp.rank
+    for r in range(W):
+        cm.out_peer[r] = part.ptrs[r]
+    dummy = part.view(torch.bfloat16, rows * N).view(rows, N)
+    gemm(a, b, b_mn=b_mn, out=dummy, comm=cm, m_override=T)
+    tp.symm.barrier()                                   # every peer's partial tiles have landed
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)
+    import ctypes as C
+    rc = _lib.get().mlf_sum_partials(C.c_void_p(part.local.data_ptr()), W, C.c_longlong(rows), N, C.c_void_p(out.data_ptr()),
+                                     C.c_longlong(N), C.c_void_p(bias.data_ptr()) if bias is not None else None,
+                                     C.c_void_p(residual.data_ptr()) if residual is not None else None,
+                                     C.c_longlong(residual.stride(0) if residual is not None else 0),
+                                     C.c_uint64(_lib.stream_handle()))
+    _lib.check(rc, "mlf_sum_partials")
+    return out
+
+
+class _ColumnSPFused(torch.autograd.Function):
+    """Sequence-parallel column linear on the fused kernels: AG->GEMM forward, GEMM->RS backward."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w, b, tp, key):
+        out, x_full = _fused_ag_gemm(tp, x_shard, w, key, bias=b)
+        ctx.save_for_backward(x_full, w)
+        ctx.tp, ctx.key, ctx.b = tp, key, b
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx_shard = _fused_gemm_rs(ctx.tp, dy, w, ctx.key + ".bwd", b_mn=True)
+        dw = Fm._wgrad(dy, x_full, w)
+        db = Fm._bgrad(dy, ctx.b)
+        return dx_shard, dw, db, None, None
+
+
+class _RowSPFused(torch.autograd.Function):
+    """Sequence-parallel row linear: GEMM->RS forward (bias / residual added after the sum), AG->GEMM backward."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, residual, tp, key):
+        out = _fused_gemm_rs(tp, x, w, key, bias=b, residual=residual)
+        ctx.save_for_backward(x, w)
+        ctx.tp, ctx.key, ctx.b, ctx.has_res = tp, key, b, residual is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, w = ctx.saved_tensors
+        dy_shard = dy_shard.contiguous()
+        # dX[T, in/W] = all_gather(dY)[T, out] @ W[out, in/W]  (W read as [K=out, N=in/W])
+        tp = ctx.tp
+        rows = dy_shard.shape[0]
+        dy_full = tp.pg.all_gather(dy_shard, dim=0) if not tp.fused else None
+        if dy_full is None:
+            # fused gather of dY needs a K-major B operand; W is MN-major here, so gather with the
+            # copy kernel path of ag_gemm and run the dgrad on the gathered buffer.
+            _, dy_full = _fused_ag_gemm_only(tp, dy_shard, ctx.key + ".bwd")
+        dx = gemm(dy_full, w, b_mn=True)
+        dw = Fm._wgrad(dy_full, x, w)
+        db = None
+        if ctx.b is not None:
+            db = Fm._bgrad(dy_full, ctx.b)      # identical on every rank (bias is replicated)
+        return dx, dw, db, (dy_shard if ctx.has_res else None), None, None
+
+
+def _fused_ag_gemm_only(tp: TPContext, x_shard: torch.Tensor, key: str):
+    """All-gather of token shards through peer memory (no GEMM attached)."""
+    rows, K = x_shard.shape
+    W = tp.world
+    stage = tp.symm_buffer(key + ".ag_stage", rows * K * 2)
+    stage.view(torch.bfloat16, rows * K).view(rows, K).copy_(x_shard)
+    tp.symm.barrier()
+    full = torch.empty(W * rows, K, dtype=torch.bfloat16, device=x_shard.device)
+    from ..dist.symm import make_copy_segs
+    segs = make_copy_segs([(stage.ptrs[(tp.rank + i) % W], full.data_ptr() + ((tp.rank + i) % W) * rows * K * 2, rows * K * 2)
+                           for i in range(W)], x_shard.device)
+    tp.symm.peer_copy(segs, W)
+    return None, full
+
+
+# ------------------------------------------------------------------ layers
+def _init_weight(out_f: int, in_f: int, rows: int, cols: int, dtype, device, seed: int = 42):
+    std = math.sqrt(2.0 / (in_f + out_f))
+    return torch.empty(rows, cols, dtype=dtype, device=device).normal_(0.0, std)
+
+
+class ColumnParallelLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, gather_output: bool = False,
+                 sequence_parallel: bool = False, tp: Optional[TPContext] = None, dtype=None, device=None, name: str = ""):
+        super().__init__()
+        self.tp = tp or get_context()
+        W = self.tp.world
+        if out_features % W != 0:
+            raise ValueError(f"out_features {out_features} must be divisible by the tensor-parallel size {W}")
+        self.in_features, self.out_features, self.local_out = in_features, out_features, out_features // W
+        self.gather_output, self.sequence_parallel = gather_output, sequence_parallel
+        self.weight = nn.Parameter(_init_weight(out_features, in_features, self.local_out, in_features, dtype, device))
+        self.bias = nn.Parameter(torch.zeros(self.local_out, dtype=dtype, device=device)) if bias else None
+        self.key = name or f"col{id(self)}"
+
+    def local_weight_shape(self):
+        return (self.local_out, self.in_features)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        tp = self.tp
+        if self.sequence_parallel:
+            x2 = x.reshape(-1, x.shape[-1])
+            if tp.fused and Fm._native(x2, self.weight):
+                y = _ColumnSPFused.apply(x2, self.weight, self.bias, tp, self.key)
+            else:
+                y = Fm.linear(gather_tokens(x2, tp), self.weight, self.bias)
+        else:
+            y = Fm.linear(copy_to_tp_region(x, tp), self.weight, self.bias)
+        if self.gather_output:
+            y = gather_last_dim(y, tp)
+        return y
+
+
+class RowParallelLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, input_is_parallel: bool = True,
+                 sequence_parallel: bool = False, tp: Optional[TPContext] = None, dtype=None, device=None, name: str = ""):
+        super().__init__()
+        self.tp = tp or get_context()
+        W = self.tp.world
+        if in_features % W != 0:
+            raise ValueError(f"in_features {in_features} must be divisible by the tensor-parallel size {W}")
+        self.in_features, self.out_features, self.local_in = in_features, out_features, in_features // W
+        self.input_is_parallel, self.sequence_parallel = input_is_parallel, sequence_parallel
+        self.weight = nn.Parameter(_init_weight(out_features, in_features, out_features, self.local_in, dtype, device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        self.key = name or f"row{id(self)}"
+
+    def local_weight_shape(self):
+        return (self.out_features, self.local_in)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        tp = self.tp
+        if not self.input_is_parallel:
+            x = x.chunk(tp.world, dim=-1)[tp.rank].contiguous()
+        if self.sequence_parallel:
+            x2 = x.reshape(-1, x.shape[-1])
+            if tp.fused and Fm._native(x2, self.weight):
+                return _RowSPFused.apply(x2, self.weight, self.bias, residual, tp, self.key)
+            y = scatter_tokens(Fm.linear(x2, self.weight), tp)
+        else:
+            y = reduce_from_tp_region(Fm.linear(x, self.weight), tp)
+        if self.bias is not None:
+            y = y + self.bias          # once, after the reduction
+        if residual is not None:
+            y = y + residual
+        return y
+
+
+class ColumnParallelLinearWithInputGather(ColumnParallelLinear):
+    """Input arrives split on the last dimension and is all-gathered first."""
+
+    def forward(self, x):
+        return super().forward(gather_last_dim(x, self.tp))
+
+
+class RowParallelLinearWithInputGather(RowParallelLinear):
+    """Input arrives split on the last dimension across ranks *and* is gathered then re-sliced
+    (used when the producer's split does not match this layer's)."""
+
+    def forward(self, x, residual=None):
+        full = gather_last_dim(x, self.tp)
+        return super().forward(full.chunk(self.tp.world, dim=-1)[self.tp.rank].contiguous(), residual)
+
+
+class Conv2dOutputParallel(nn.Module):
+    """Output channels split over ranks; optional gather on the channel dim
+    (src/MLFramework/Layers/TensorParallel/Conv2dOutputParallel.cs:45-128)."""
+
+    def __init__(self, in_ch, out_ch, kernel_size, stride=1, padding=0, bias=True, gather_output=True, tp=None):
+        super().__init__()
+        self.tp = tp or get_context()
+        if out_ch % self.tp.world:
+            raise ValueError("out_channels must be divisible by the tensor-parallel size")
+        self.conv = nn.Conv2d(in_ch, out_ch // self.tp.world, kernel_size, stride, padding, bias=bias)
+        self.gather_output = gather_output
+
+    def forward(self, x):
+        y = self.conv(copy_to_tp_region(x, self.tp))
+        if self.gather_output and self.tp.world > 1:
+            y = _GatherLastDim.apply(y.movedim(1, -1).contiguous(), self.tp).movedim(-1, 1)
+        return y
+
+
+class Conv2dInputParallel(nn.Module):
+    """Input channels split over ranks; partial outputs all-reduced, bias added once
+    (Conv2dInputParallel.cs:44-118)."""
+
+    def __init__(self, in_ch, out_ch, kernel_size, stride=1, padding=0, bias=True, input_is_parallel=True, tp=None):
+        super().__init__()
+        self.tp = tp or get_context()
+        if in_ch % self.tp.world:
+            raise ValueError("in_channels must be divisible by the tensor-parallel size")
+        self.conv = nn.Conv2d(in_ch // self.tp.world, out_ch, kernel_size, stride, padding, bias=False)
+        self.bias = nn.Parameter(torch.zeros(out_ch)) if bias else None
+        self.input_is_parallel = input_is_parallel
+
+    def forward(self, x):
+        if not self.input_is_parallel:
+            x = x.chunk(self.tp.world, dim=1)[self.tp.rank]
+        y = reduce_from_tp_region(self.conv(x), self.tp)
+        return y + self.bias.view(1, -1, 1, 1) if self.bias is not None else y
+
+
+class TPMLP(nn.Module):
+    """Column -> activation -> Row block (``TPMLPFactory.CreateMLPBlock``, TPMLPFactory.cs:20-140)."""
+
+    def __init__(self, dim, hidden, activation="gelu", bias=True, tp=None, dtype=None, device=None):
+        super().__init__()
+        self.fc1 = ColumnParallelLinear(dim, hidden, bias, tp=tp, dtype=dtype, device=device)
+        self.fc2 = RowParallelLinear(hidden, dim, bias, tp=tp, dtype=dtype, device=device)
+        self.activation = activation
+
+    def forward(self, x):
+        h = self.fc1(x)
+        h = torch.relu(h) if self.activation == "relu" else F.gelu(h, approximate="tanh")
+        return self.fc2(h)
+
+
+# ------------------------------------------------------------------ vocabulary-parallel head
+class _VocabParallelCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w_shard, targets, tp, vocab, loss_scale):
+        Vl = w_shard.shape[0]
+        lo = tp.rank * Vl
+        logits = F.linear(h, w_shard).float()
+        valid_cols = max(0, min(Vl, vocab - lo))
+        if valid_cols < Vl:
+            logits[:, valid_cols:] = float("-inf")
+        mx = logits.max(dim=-1).values
+        if tp.world > 1:
+            tp.pg.all_reduce(mx, ReduceOp.MAX)
+        ex = torch.exp(logits - mx[:, None])
+        se = ex.sum(-1)
+        t = targets.reshape(-1)
+        mine = (t >= lo) & (t < lo + Vl)
+        tl = torch.zeros_like(mx)
+        idx = (t - lo).clamp(0, Vl - 1)
+        tl[mine] = logits[torch.arange(len(t), device=t.device)[mine], idx[mine]]
+        if tp.world > 1:
+            tp.pg.all_reduce(se, ReduceOp.SUM)
+            tp.pg.all_reduce(tl, ReduceOp.SUM)
+        loss = (torch.log(se) + mx - tl).sum() / t.numel()
+        p = ex / se[:, None]
+        p[torch.arange(len(t), device=t.device)[mine], idx[mine]] -= 1.0
+        scale = 1.0 / t.numel()
+        dlogits = (p * scale).to(h.dtype)
+        if loss_scale is not None:
+            dlogits = dlogits * loss_scale.to(dlogits.dtype)
+        ctx.save_for_backward(h, w_shard, dlogits)
+        ctx.tp = tp
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        h, w, dl = ctx.saved_tensors
+        if Fm._native(h, w):
+            dh = gemm(dl, w, b_mn=True)
+            dw = Fm._wgrad(dl, h, w)
+        else:
+            dh = dl.float() @ w.float()
+            dw = (dl.float().t() @ h.float()).to(w.dtype)
+            dh = dh.to(h.dtype)
+        if ctx.tp.world > 1:
+            ctx.tp.pg.all_reduce(dh, ReduceOp.SUM)
+        return dh, dw, None, None, None, None
+
+
+def vocab_parallel_lm_loss(h, w_shard, targets, tp: TPContext, vocab: int, loss_scale=None):
+    """Cross-entropy with the LM head split over the vocabulary: only three small all-reduces
+    (row max, sum of exponentials, target logit) cross the ranks; full logits never do."""
+    return _VocabParallelCE.apply(h.reshape(-1, h.shape[-1]), w_shard, targets, tp, vocab, loss_scale)
+
+
+class VocabParallelEmbedding(nn.Module):
+    def __init__(self, vocab: int, dim: int, tp: Optional[TPContext] = None, dtype=None, device=None, init_std=0.02):
+        super().__init__()
+        self.tp = tp or get_context()
+        W = self.tp.world
+        self.vocab = vocab
+        self.local_v = (vocab + W - 1) // W
+        self.lo = self.tp.rank * self.local_v
+        self.weight = nn.Parameter(torch.empty(self.local_v, dim, dtype=dtype, device=device).normal_(0, init_std))
+
+    def forward(self, ids):
+        mask = (ids >= self.lo) & (ids < self.lo + self.local_v)
+        local = (ids - self.lo).clamp(0, self.local_v - 1)
+        out = F.embedding(local, self.weight) * mask[..., None].to(self.weight.dtype)
+        return reduce_from_tp_region(out, self.tp)
+
+
+# ------------------------------------------------------------------ gradient utilities
+class TPGradientManager:
+    """DP-group gradient sync, global-norm clipping reduced over the TP group, consistency checks
+    (src/MLFramework/Layers/TensorParallel/TPGradientManager.cs:24-135)."""
+
+    def __init__(self, tp: TPContext, dp_group=None):
+        self.tp, self.dp = tp, dp_group
+
+    def synchronize_gradients(self, params: Iterable[nn.Parameter]):
+        if self.dp is None or self.dp.world_size == 1:
+            return
+        grads = [p.grad for p in params if p.grad is not None]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        self.dp.all_reduce(flat, ReduceOp.AVG)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+
+    def clip_gradients_by_norm(self, params: Iterable[nn.Parameter], max_norm: float, replicated: Optional[set] = None):
+        """Sharded parameters contribute their local squares, replicated ones only on TP rank 0,
+        and the sum is all-reduced over the TP group before scaling."""
+        params = [p for p in params if p.grad is not None]
+        ss = torch.zeros((), device=params[0].device) if params else torch.zeros(())
+        for p in params:
+            if replicated is not None and id(p) in replicated and self.tp.rank != 0:
+                continue
+            ss = ss + p.grad.float().pow(2).sum()
+        if self.tp.world > 1:
+            ss = ss.reshape(1)
+            self.tp.pg.all_reduce(ss, ReduceOp.SUM)
+            ss = ss.squeeze(0)
+        norm = ss.sqrt()
+        coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0)
+        for p in params:
+            p.grad.mul_(coef.to(p.grad.dtype))
+        return norm
+
+    def verify_gradients(self, params: Iterable[nn.Parameter]) -> bool:
+        return all(p.grad is None or bool(torch.isfinite(p.grad).all()) for p in params)
+
+
+# ------------------------------------------------------------------ model analysis / conversion
+@dataclass
+class LayerAnalysisResult:
+    name: str
+    parallelism: str           # column | row | replicate
+    params: int
+    local_params: int
+
+
+class TPModelAnalyzer:
+    """Decides which linear layers become column- or row-parallel: projections that expand
+    (qkv, fc1, gate/up) are column, projections that contract back (proj, fc2, down) are row
+    (src/MLFramework/Conversion/TPModelAnalyzer.cs)."""
+
+    COLUMN = ("qkv", "q_proj", "k_proj", "v_proj", "fc1", "gate", "up", "gate_up", "c_attn", "c_fc")
+    ROW = ("proj", "o_proj", "fc2", "down", "c_proj")
+
+    def analyze(self, model: nn.Module, world: int) -> List[LayerAnalysisResult]:
+        out = []
+        for name, m in model.named_modules():
+            if not hasattr(m, "weight") or not isinstance(getattr(m, "weight"), torch.Tensor) or m.weight.dim() != 2:
+                continue
+            leaf = name.rsplit(".", 1)[-1]
+            n = m.weight.numel() + (m.bias.numel() if getattr(m, "bias", None) is not None else 0)
+            if leaf in self.COLUMN and m.weight.shape[0] % world == 0:
+                out.append(LayerAnalysisResult(name, "column", n, n // world))
+            elif leaf in self.ROW and m.weight.shape[1] % world == 0:
+                out.append(LayerAnalysisResult(name, "row", n, m.weight.numel() // world + (m.bias.numel() if getattr(m, "bias", None) is not None else 0)))
+            else:
+                out.append(LayerAnalysisResult(name, "replicate", n, n))
+        return out
+
+
+class TPMemoryEstimator:
+    @staticmethod
+    def estimate(analysis: List[LayerAnalysisResult], bytes_per_param: int = 2, optimizer_bytes_per_param: int = 12):
+        local = sum(a.local_params for a in analysis)
+        total = sum(a.params for a in analysis)
+        return {"total_params": total, "local_params": local, "param_bytes": local * bytes_per_param,
+                "optimizer_bytes": local * optimizer_bytes_per_param, "savings": 1.0 - local / max(total, 1)}
+
+
+class TPModelConverter:
+    """Rewrites the linear layers of a dense model in place into their parallel forms, slicing the
+    existing weights so the parallel model computes the same function."""
+
+    def __init__(self, tp: TPContext, sequence_parallel: bool = False):
+        self.tp, self.sp = tp, sequence_parallel
+
+    def convert(self, model: nn.Module) -> nn.Module:
+        plan = {a.name: a.parallelism for a in TPModelAnalyzer().analyze(model, self.tp.world)}
+        W, r = self.tp.world, self.tp.rank
+        for name, module in list(model.named_modules()):
+            for cn, child in list(module.named_children()):
+                full = f"{name}.{cn}" if name else cn
+                kind = plan.get(full)
+                if kind not in ("column", "row") or isinstance(child, (ColumnParallelLinear, RowParallelLinear)):
+                    continue
+                w, b = child.weight.data, (child.bias.data if getattr(child, "bias", None) is not None else None)
+                if kind == "column":
+                    new = ColumnParallelLinear(w.shape[1], w.shape[0], b is not None, False, self.sp, self.tp, w.dtype, w.device, full)
+                    new.weight.data.copy_(w.chunk(W, 0)[r])
+                    if b is not None:
+                        new.bias.data.copy_(b.chunk(W, 0)[r])
+                else:
+                    new = RowParallelLinear(w.shape[1], w.shape[0], b is not None, True, self.sp, self.tp, w.dtype, w.device, full)
+                    new.weight.data.copy_(w.chunk(W, 1)[r])
+                    if b is not None:
+                        new.bias.data.copy_(b)
+                setattr(module, cn, new)
+        return model

@@ -1,0 +1,133 @@
+"""Tensor-parallel layers on simulated ranks: forward equals the dense layer, backward equals the
+dense gradients (including dX through the column layer), sequence-parallel variants, vocabulary-
+parallel loss, model conversion, DeviceMesh rules."""
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ml_framework_b200.dist.mesh import DeviceMesh, ParallelismDimension
+from ml_framework_b200.dist.process_group import run_fake_world
+from ml_framework_b200.parallel import tensor_parallel as tpm
+
+
+def test_device_mesh_rules():
+    m = DeviceMesh((2, 4), rank=5)          # data=2, tensor=4, row-major, last dim fastest
+    assert m.coord.coords == (1, 1) and m.coord_to_rank((1, 1)) == 5
+    assert m.tp_group_ranks() == [4, 5, 6, 7] and m.dp_group_ranks() == [1, 5]
+    assert m.tp_world_size == 4 and m.dp_world_size == 2 and m.tp_rank == 1 and m.dp_rank == 1
+    assert m.ranks_with_index(ParallelismDimension.TENSOR, 0) == [0, 4]
+    assert m.all_groups(1) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    m3 = DeviceMesh((2, 2, 2), rank=3)
+    assert m3.coord.coords == (0, 1, 1) and m3.pp_group_ranks() == [2, 3] and m3.pp_world_size == 2
+    for r in range(8):
+        assert m3.coord_to_rank(m3.rank_to_coord(r)) == r
+    with pytest.raises(ValueError):
+        DeviceMesh((2, 2), rank=4)
+    with pytest.raises(ValueError):
+        m.coord_to_rank((2, 0))
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_column_row_mlp_matches_dense(sp):
+    W, T, D, H = 4, 8, 16, 32
+    torch.manual_seed(0)
+    w1, b1 = torch.randn(H, D) * 0.3, torch.randn(H) * 0.1
+    w2, b2 = torch.randn(D, H) * 0.3, torch.randn(D) * 0.1
+    x = torch.randn(T, D)
+    dy = torch.randn(T, D)
+    xr = x.clone().requires_grad_()
+    w1r, b1r, w2r, b2r = [t.clone().requires_grad_() for t in (w1, b1, w2, b2)]
+    yr = F.linear(F.gelu(F.linear(xr, w1r, b1r), approximate="tanh"), w2r, b2r)
+    yr.backward(dy)
+
+    def run(pg):
+        tp = tpm.TPContext(pg, None, fused=False)
+        fc1 = tpm.ColumnParallelLinear(D, H, True, sequence_parallel=sp, tp=tp)
+        fc2 = tpm.RowParallelLinear(H, D, True, sequence_parallel=sp, tp=tp)
+        r = pg.rank
+        with torch.no_grad():
+            fc1.weight.copy_(w1.chunk(W, 0)[r]); fc1.bias.copy_(b1.chunk(W, 0)[r])
+            fc2.weight.copy_(w2.chunk(W, 1)[r]); fc2.bias.copy_(b2)
+        xin = (x.chunk(W, 0)[r] if sp else x).clone().requires_grad_()
+        y = fc2(F.gelu(fc1(xin), approximate="tanh"))
+        y.backward(dy.chunk(W, 0)[r] if sp else dy)
+        return y.detach(), xin.grad, fc1.weight.grad, fc1.bias.grad, fc2.weight.grad, fc2.bias.grad
+    outs = run_fake_world(W, run)
+    y = torch.cat([o[0] for o in outs]) if sp else outs[0][0]
+    dx = torch.cat([o[1] for o in outs]) if sp else outs[0][1]
+    assert torch.allclose(y, yr, atol=1e-5) and torch.allclose(dx, xr.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([o[2] for o in outs]), w1r.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([o[3] for o in outs]), b1r.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([o[4] for o in outs], 1), w2r.grad, atol=1e-5)
+    b2g = sum(o[5] for o in outs) if sp else outs[0][5]      # SP: each rank saw its token shard only
+    assert torch.allclose(b2g, b2r.grad, atol=1e-5)
+
+
+def test_shape_validation_and_gather_output():
+    def run(pg):
+        tp = tpm.TPContext(pg, None, fused=False)
+        with pytest.raises(ValueError):
+            tpm.ColumnParallelLinear(8, 10, tp=tp)
+        with pytest.raises(ValueError):
+            tpm.RowParallelLinear(10, 8, tp=tp)
+        col = tpm.ColumnParallelLinear(8, 12, False, gather_output=True, tp=tp)
+        assert col.local_weight_shape() == (4, 8)
+        return col(torch.ones(2, 8)).shape
+    assert run_fake_world(3, run) == [torch.Size([2, 12])] * 3
+
+
+def test_vocab_parallel_loss_and_embedding():
+    W, T, D, V = 2, 6, 8, 10
+    torch.manual_seed(1)
+    h = torch.randn(T, D)
+    w = torch.randn(12, D)       # padded vocabulary 12, 10 valid
+    tg = torch.randint(0, V, (T,))
+    hr, wr = h.clone().requires_grad_(), w.clone().requires_grad_()
+    F.cross_entropy(F.linear(hr, wr)[:, :V], tg).backward()
+    ref_loss = F.cross_entropy(F.linear(h, w)[:, :V], tg)
+
+    def run(pg):
+        tp = tpm.TPContext(pg, None, fused=False)
+        hh = h.clone().requires_grad_()
+        ws = w.chunk(W, 0)[pg.rank].clone().requires_grad_()
+        loss = tpm.vocab_parallel_lm_loss(hh, ws, tg, tp, V)
+        loss.backward()
+        emb = tpm.VocabParallelEmbedding(12, D, tp)
+        with torch.no_grad():
+            emb.weight.copy_(w.chunk(W, 0)[pg.rank])
+        return loss.item(), hh.grad, ws.grad, emb(tg)
+    outs = run_fake_world(W, run)
+    assert abs(outs[0][0] - ref_loss.item()) < 1e-5
+    assert torch.allclose(outs[0][1], hr.grad, atol=1e-5)
+    assert torch.allclose(torch.cat([o[2] for o in outs]), wr.grad, atol=1e-5)
+    assert torch.allclose(outs[1][3], w[tg], atol=1e-6)
+
+
+def test_converter_and_analyzer():
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1, self.fc2, self.other = nn.Linear(8, 16), nn.Linear(16, 8), nn.Linear(8, 3)
+
+        def forward(self, x):
+            return self.other(self.fc2(torch.relu(self.fc1(x))))
+    torch.manual_seed(2)
+    dense = Net()
+    x = torch.randn(4, 8)
+    want = dense(x)
+    rep = tpm.TPModelAnalyzer().analyze(dense, 2)
+    kinds = {a.name: a.parallelism for a in rep}
+    assert kinds == {"fc1": "column", "fc2": "row", "other": "replicate"}
+    est = tpm.TPMemoryEstimator.estimate(rep)
+    assert 0.3 < est["savings"] < 0.5
+
+    def run(pg):
+        tp = tpm.TPContext(pg, None, fused=False)
+        m = tpm.TPModelConverter(tp).convert(copy.deepcopy(dense))
+        assert isinstance(m.fc1, tpm.ColumnParallelLinear) and isinstance(m.fc2, tpm.RowParallelLinear)
+        return m(x)
+    for y in run_fake_world(2, run):
+        assert torch.allclose(y, want, atol=1e-5)
