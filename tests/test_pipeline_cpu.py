@@ -1,0 +1,120 @@
+"""Pipeline parallelism: partitioner, micro-batch manager, GPipe / 1F1B order, and gradient
+equality of a 4-stage pipeline (threads + in-process communicator, and gloo-free simulated p2p)
+against the same network on one device."""
+import copy
+import threading
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ml_framework_b200.dist.process_group import run_fake_world
+from ml_framework_b200.parallel.pipeline import (ActivationCheckpointManager, CheckpointStrategy, GPipeScheduler,
+                                                 LayerPartitioner, LocalPipelineCommunicator, MicroBatchManager,
+                                                 OneFOneBScheduler, PartitionMode, PipelineConfig, PipelineStats,
+                                                 PipelineValidator, ProcessGroupPipelineCommunicator, SchedulingStrategy,
+                                                 build_stage, make_scheduler)
+
+
+def _layers(seed=0):
+    torch.manual_seed(seed)
+    dims = [12, 16, 16, 16, 16, 16, 16, 8]
+    out = []
+    for i in range(len(dims) - 1):
+        out.append(nn.Sequential(nn.Linear(dims[i], dims[i + 1]), nn.Tanh()))
+    return out
+
+
+def test_partitioner_modes():
+    ls = _layers()
+    u = LayerPartitioner(PartitionMode.UNIFORM).partition(ls, 3)
+    assert u.boundaries == [(0, 3), (3, 5), (5, 7)]
+    m = LayerPartitioner(PartitionMode.MANUAL, [1, 5, 1]).partition(ls, 3)
+    assert m.boundaries == [(0, 1), (1, 6), (6, 7)]
+    a = LayerPartitioner().partition(ls, 4)
+    assert len(a.boundaries) == 4 and a.boundaries[0][0] == 0 and a.boundaries[-1][1] == 7
+    assert max(a.costs) <= 2.2 * (sum(a.costs) / 4)
+    with pytest.raises(ValueError):
+        LayerPartitioner().partition(ls, 8)
+    with pytest.raises(ValueError):
+        LayerPartitioner(PartitionMode.MANUAL, [3, 3]).partition(ls, 2)
+
+
+def test_micro_batch_manager_and_schedules():
+    mb = MicroBatchManager(4)
+    parts = mb.split_batch(torch.arange(10).reshape(10, 1))
+    assert [p.shape[0] for p in parts] == [2, 2, 2, 4]          # last takes the remainder
+    assert torch.equal(mb.combine_outputs(parts), torch.arange(10).reshape(10, 1))
+    with pytest.raises(ValueError):
+        mb.split_batch(torch.zeros(3, 1))
+    p = nn.Parameter(torch.zeros(2))
+    for g in (1.0, 3.0):
+        p.grad = torch.full((2,), g)
+        MicroBatchManager.accumulate_gradients(mb, [p])
+    assert torch.equal(mb.get_accumulated_gradients()[0], torch.full((2,), 1.0))   # (1 + 3) / 4
+    cfg = PipelineConfig(num_stages=4, micro_batches=8)
+    stage = build_stage(_layers(), 1, 4)
+    s = OneFOneBScheduler(stage, None, cfg)
+    order = s.order()
+    assert order[:2] == [("F", 0), ("F", 1)] and order[2:6] == [("F", 2), ("B", 0), ("F", 3), ("B", 1)]
+    assert s.max_live_activations() == 3 and [o for o in order if o[0] == "B"] == [("B", i) for i in range(8)]
+    g = GPipeScheduler(stage, None, cfg).order()
+    assert g[:8] == [("F", i) for i in range(8)] and g[8:] == [("B", i) for i in reversed(range(8))]
+    assert abs(PipelineStats(stages=4, micro_batches=16).bubble_fraction - 3 / 19) < 1e-9
+    ck = ActivationCheckpointManager(CheckpointStrategy.SELECTIVE, 2)
+    assert [ck.should_checkpoint(i) for i in range(4)] == [False, True, False, True]
+    assert PipelineValidator.validate_configuration(PipelineConfig(num_stages=9), 7, 2) != []
+
+
+def _reference(layers, x, y):
+    net = nn.Sequential(*copy.deepcopy(layers))
+    loss = F.mse_loss(net(x), y)
+    loss.backward()
+    return loss.item(), [p.grad.clone() for p in net.parameters()]
+
+
+@pytest.mark.parametrize("schedule", [SchedulingStrategy.GPIPE, SchedulingStrategy.ONE_F_ONE_B])
+@pytest.mark.parametrize("ckpt", [CheckpointStrategy.STORE_ALL, CheckpointStrategy.RECOMPUTE_ALL])
+def test_pipeline_matches_single_device(schedule, ckpt):
+    P, N = 4, 4
+    layers = _layers(1)
+    x, y = torch.randn(8, 12), torch.randn(8, 8)
+    ref_loss, ref_grads = _reference(layers, x, y)
+    comm = LocalPipelineCommunicator(P)
+    cfg = PipelineConfig(num_stages=P, micro_batches=N, schedule=schedule, checkpoint_strategy=ckpt)
+    results = [None] * P
+
+    def run(r):
+        stage = build_stage(copy.deepcopy(layers), r, P, LayerPartitioner(PartitionMode.UNIFORM))
+        sch = make_scheduler(stage, comm.view(r), cfg, loss_fn=F.mse_loss)
+        loss = sch.train_iteration(x if r == 0 else None, y if r == P - 1 else None)
+        results[r] = (loss, [p.grad.clone() for p in stage.parameters()])
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(P)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert all(r is not None for r in results)
+    grads = [g for r in results for g in r[1]]
+    assert abs(results[-1][0].item() - ref_loss) < 1e-6
+    assert PipelineValidator.validate_gradients(grads, ref_grads, atol=1e-6)
+
+
+def test_pipeline_over_process_group_p2p():
+    P, N = 2, 4
+    layers = _layers(2)
+    x, y = torch.randn(8, 12), torch.randn(8, 8)
+    ref_loss, ref_grads = _reference(layers, x, y)
+
+    def run(pg):
+        r = pg.rank
+        stage = build_stage(copy.deepcopy(layers), r, P, LayerPartitioner(PartitionMode.UNIFORM))
+        comm = ProcessGroupPipelineCommunicator(pg, use_side_stream=False)
+        a, b = LayerPartitioner(PartitionMode.UNIFORM).partition(layers, P).boundaries[r]
+        in_dim = layers[a][0].in_features
+        sch = make_scheduler(stage, comm, PipelineConfig(num_stages=P, micro_batches=N), loss_fn=F.mse_loss,
+                             act_shape_fn=lambda _x: (8 // N, in_dim), act_dtype=torch.float32)
+        loss = sch.train_iteration(x if r == 0 else None, y if r == P - 1 else None)
+        return loss, [p.grad.clone() for p in stage.parameters()]
+    outs = run_fake_world(P, run)
+    grads = [g for o in outs for g in o[1]]
+    assert abs(outs[-1][0].item() - ref_loss) < 1e-6 and PipelineValidator.validate_gradients(grads, ref_grads, atol=1e-6)
