@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3",
-    "--expt-relaxed-constexpr",
+    "--expt-relaxed-constexpr", "--use_fast_math",
     "-Xptxas", "-v",
     "-DMLF_BUILD",
 ]

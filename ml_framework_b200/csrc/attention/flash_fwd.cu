@@ -8,7 +8,10 @@
 //                             PV = P V  (M128 N128 K64) into a second TMEM tile
 //   warps 2..5  softmax: one query row per thread straight out of TMEM (no shuffles), running
 //               max / sum in the log2 domain, P written as bf16 into 128B-swizzled shared memory
-//               as the A operand of the PV product, output accumulated in registers.
+//               as the A operand of the PV product. The output accumulates in TMEM across key
+//               tiles (PV issued with accumulate); it is only rescaled (TMEM load, multiply, TMEM
+//               store) when a row's maximum has grown by more than 2^8 since the last rescale, so
+//               the common iteration touches TMEM only to read S.
 // Q/K/V are addressed through 2-D tensor maps over [tokens, features], so packed QKV
 // buffers (row pitch 3*H*128) and GQA layouts need no copies. The same kernel serves training
 // (contiguous sequences) and prefill; the paged variant lives in paged_attn.cu.
@@ -161,7 +164,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < FA_BKV / 16; ++k) {
           const uint64_t ad = make_smem_desc_sw128(sP + k * 32, 16, 1024);
           const uint64_t bd = make_smem_desc_sw128(sV + k * 2048, FA_V_BYTES / 2, 1024);
-          umma_bf16_ss(tPV, ad, bd, idesc_pv, k != 0);
+          umma_bf16_ss(tPV, ad, bd, idesc_pv, (j | k) != 0);
         }
         umma_commit(pv_full);
         umma_commit(kv_empty(s));
@@ -172,10 +175,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int r = q * 32 + lane;         // row inside the tile
     const int qi = q0 + r;               // query position in the sequence
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    float o[FA_D];
-#pragma unroll
-    for (int i = 0; i < FA_D; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m_used = 0.f;                  // the maximum P and O are currently expressed against
+    float l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait_warp(s_full(j & 1), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
@@ -183,8 +184,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int k0 = j * FA_BKV;
       const bool need_mask = (p.causal && k0 + FA_BKV - 1 > q0) || (k0 + FA_BKV > p.S);
       const uint32_t tSj = tS + 64 * (j & 1) + lane_off;
-      // pass 1: row maximum (TMEM reads are cheap; reading twice keeps register pressure low)
-      float mx = m;
+      // pass 1: row maximum of this tile
+      float mx = -INFINITY;
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
         uint32_t t[32];
@@ -200,10 +201,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           mx = fmaxf(mx, v * p.scale_log2);
         }
       }
-      const float m_use = mx == -INFINITY ? 0.f : mx;
-      const float alpha = exp2f(m - m_use);  // m = -inf on the first tile -> 0
+      bool pv_waited = false;
+      if (j == 0) {
+        m_used = mx == -INFINITY ? 0.f : mx;
+      } else {
+        const bool grow = mx > m_used + 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          // rescale the accumulator in TMEM; PV of the previous tile must have landed first
+          if (!mbar_wait_warp(pv_full, (j - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+          pv_waited = true;
+          tc_fence_after_sync();
+          const float f = grow ? exp2f(m_used - mx) : 1.f;
+#pragma unroll
+          for (int c = 0; c < FA_D / 32; ++c) {
+            uint32_t t[32];
+            tmem_ld_32x32b_x32(tPV + c * 32 + lane_off, t);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * f);
+            tmem_st_32x32b_x32(tPV + c * 32 + lane_off, t);
+          }
+          tmem_wait_st();
+          l *= f;
+          if (grow) m_used = mx;
+        }
+      }
+      if (j > 0 && !pv_waited) {
+        // P's shared-memory tile is still being read by the previous PV product until this fires
+        if (!mbar_wait_warp(pv_full, (j - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+      }
+      // pass 2: P = exp2(S*c - m_used) as bf16 into 128B-swizzled shared memory
       float rs = 0.f;
-      // pass 2: P = exp2(S*c - max) as bf16 into 128B-swizzled shared memory
       const uint32_t rowaddr = sP + r * 128;
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
@@ -213,8 +241,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float v0 = __uint_as_float(t[2 * i]) * p.scale_log2 - m_use;
-          float v1 = __uint_as_float(t[2 * i + 1]) * p.scale_log2 - m_use;
+          float v0 = __uint_as_float(t[2 * i]) * p.scale_log2 - m_used;
+          float v1 = __uint_as_float(t[2 * i + 1]) * p.scale_log2 - m_used;
           if (need_mask) {
             const int kj = k0 + 32 * hlf + 2 * i;
             if (kj >= p.S || (p.causal && kj > qi)) v0 = -INFINITY;
@@ -232,40 +260,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                        : "memory");
         }
       }
-      l = l * alpha + rs;
-      m = mx;
+      l += rs;
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_full);
-      // rescale what we have while the PV product runs
-#pragma unroll
-      for (int i = 0; i < FA_D; ++i) o[i] *= alpha;
-      if (!mbar_wait_warp(pv_full, j & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+    }
+    if (ok && n_kv > 0) ok = mbar_wait_warp(pv_full, (n_kv - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN);
+    if (ok) {
       tc_fence_after_sync();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = qi < p.S;
+      __nv_bfloat16* orow = p.out + (row_base + qi) * p.ldo + (long long)h * FA_D;
 #pragma unroll
       for (int c = 0; c < FA_D / 32; ++c) {
         uint32_t t[32];
         tmem_ld_32x32b_x32(tPV + c * 32 + lane_off, t);
         tmem_wait_ld();
+        if (row_ok) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(t[i]);
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(t[8 * v + 0]) * inv, __uint_as_float(t[8 * v + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(t[8 * v + 2]) * inv, __uint_as_float(t[8 * v + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(t[8 * v + 4]) * inv, __uint_as_float(t[8 * v + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(t[8 * v + 6]) * inv, __uint_as_float(t[8 * v + 7]) * inv);
+            reinterpret_cast<uint4*>(orow + 32 * c)[v] = w;
+          }
+        }
       }
-      tc_fence_before_sync();
+      if (row_ok && p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
     }
-    if (ok && qi < p.S) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.out + (row_base + qi) * p.ldo + (long long)h * FA_D;
-#pragma unroll
-      for (int c = 0; c < FA_D / 8; ++c) {
-        uint4 w;
-        w.x = pack_bf16x2(o[8 * c + 0] * inv, o[8 * c + 1] * inv);
-        w.y = pack_bf16x2(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
-        w.z = pack_bf16x2(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
-        w.w = pack_bf16x2(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
-        reinterpret_cast<uint4*>(orow)[c] = w;
-      }
-      if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qi] = (m + log2f(l)) * 0.6931471805599453f;
-    }
+    tc_fence_before_sync();
   }
 
   tc_fence_before_sync();

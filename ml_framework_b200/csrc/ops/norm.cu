@@ -89,27 +89,46 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
-template <int NV>
+// Backward. Each warp walks rows with a grid stride. Gamma / beta gradient contributions are kept
+// per lane in registers when they fit (MODE 0: D <= 2048, row cached in registers too; MODE 1:
+// RMSNorm up to D = 5120, row re-read from L1/L2 for the second pass) and only folded into a
+// per-CTA shared-memory accumulator once per kernel. MODE 2 (everything else) adds every row's
+// contribution to shared memory directly.
+template <int NV, int MODE>
 __global__ void __launch_bounds__(256)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                 float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms) {
   constexpr int D = NV * 256;
+  constexpr int NK = MODE == 0 ? NV : 1;          // cached row vectors
+  constexpr int NG = MODE <= 1 ? NV : 1;          // register dgamma partials
+  constexpr int NB = MODE == 0 ? NV : 1;          // register dbeta partials
   extern __shared__ float acc[];  // [2][D]
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) acc[i] = 0.f;
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   const uint4* gr = reinterpret_cast<const uint4*>(gamma);
+  float dg[NG][8], db[NB][8];
+#pragma unroll
+  for (int i = 0; i < NG; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dg[i][j] = 0.f;
+#pragma unroll
+  for (int i = 0; i < NB; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) db[i][j] = 0.f;
   for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * D);
     const uint4* dr = reinterpret_cast<const uint4*>(dy + (long long)row * D);
-    uint4 xv[NV], dv[NV];
+    uint4 xv[NK], dv[NK];
+    if (MODE == 0) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      xv[i] = xr[i * 32 + lane];
-      dv[i] = dr[i * 32 + lane];
+      for (int i = 0; i < NK; ++i) {
+        xv[i] = xr[i * 32 + lane];
+        dv[i] = dr[i * 32 + lane];
+      }
     }
     const float mean = rms ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
@@ -117,8 +136,8 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       float f[8], d[8], g[8];
-      unpack8(xv[i], f);
-      unpack8(dv[i], d);
+      unpack8(MODE == 0 ? xv[MODE == 0 ? i : 0] : xr[i * 32 + lane], f);
+      unpack8(MODE == 0 ? dv[MODE == 0 ? i : 0] : dr[i * 32 + lane], d);
       unpack8(gr[i * 32 + lane], g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -126,6 +145,8 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         const float dxh = d[j] * g[j];
         c1 += dxh;
         c2 += dxh * xh;
+        if (MODE <= 1) dg[MODE <= 1 ? i : 0][j] += d[j] * xh;
+        if (MODE == 0) db[MODE == 0 ? i : 0][j] += d[j];
       }
     }
     c1 = rms ? 0.f : warp_sum(c1) * (1.f / D);
@@ -134,19 +155,32 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       float f[8], d[8], g[8], o[8];
-      unpack8(xv[i], f);
-      unpack8(dv[i], d);
+      unpack8(MODE == 0 ? xv[MODE == 0 ? i : 0] : xr[i * 32 + lane], f);
+      unpack8(MODE == 0 ? dv[MODE == 0 ? i : 0] : dr[i * 32 + lane], d);
       unpack8(gr[i * 32 + lane], g);
       const int col = (i * 32 + lane) * 8;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float xh = (f[j] - mean) * rstd;
-        const float dxh = d[j] * g[j];
-        o[j] = rstd * (dxh - c1 - xh * c2);
-        atomicAdd(&acc[col + j], d[j] * xh);
-        if (!rms) atomicAdd(&acc[D + col + j], d[j]);
+        o[j] = rstd * (d[j] * g[j] - c1 - xh * c2);
+        if (MODE == 2) {
+          atomicAdd(&acc[col + j], d[j] * xh);
+          if (!rms) atomicAdd(&acc[D + col + j], d[j]);
+        }
+        if (MODE == 1 && !rms) atomicAdd(&acc[D + col + j], d[j]);
       }
       dxr[i * 32 + lane] = pack8(o);
+    }
+  }
+  if (MODE <= 1) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int col = (i * 32 + lane) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&acc[col + j], dg[MODE <= 1 ? i : 0][j]);
+        if (MODE == 0 && !rms) atomicAdd(&acc[D + col + j], db[MODE == 0 ? i : 0][j]);
+      }
     }
   }
   __syncthreads();
@@ -154,29 +188,38 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) po[i] = acc[i];
 }
 
-// dgamma[c] = sum_g partials[g][0][c]; dbeta likewise. Output bf16 or fp32, optional accumulate.
-__global__ void norm_bwd_finalize_kernel(const float* __restrict__ partials, int nparts, int D,
-                                         void* dgamma, void* dbeta, int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+// dgamma[c] = sum_g partials[g][0][c]; dbeta likewise. 32 columns x 8 partial-lanes per CTA.
+__global__ void __launch_bounds__(256)
+norm_bwd_finalize_kernel(const float* __restrict__ partials, int nparts, int D, void* dgamma, void* dbeta,
+                         int out_fp32, int accumulate) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
   float g = 0.f, b = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    g += partials[(long long)p * 2 * D + c];
-    b += partials[(long long)p * 2 * D + D + c];
-  }
+  if (c < D)
+    for (int p = pl; p < nparts; p += 8) {
+      g += partials[(long long)p * 2 * D + c];
+      b += partials[(long long)p * 2 * D + D + c];
+    }
+  sg[pl][cl] = g;
+  sb[pl][cl] = b;
+  __syncthreads();
+  if (pl != 0 || c >= D) return;
+#pragma unroll
+  for (int k = 1; k < 8; ++k) { g += sg[k][cl]; b += sb[k][cl]; }
   if (out_fp32) {
-    float* dg = static_cast<float*>(dgamma);
-    dg[c] = g + (accumulate ? dg[c] : 0.f);
+    float* dgp = static_cast<float*>(dgamma);
+    dgp[c] = g + (accumulate ? dgp[c] : 0.f);
     if (dbeta) {
-      float* db = static_cast<float*>(dbeta);
-      db[c] = b + (accumulate ? db[c] : 0.f);
+      float* dbp = static_cast<float*>(dbeta);
+      dbp[c] = b + (accumulate ? dbp[c] : 0.f);
     }
   } else {
-    __nv_bfloat16* dg = static_cast<__nv_bfloat16*>(dgamma);
-    dg[c] = __float2bfloat16(g + (accumulate ? __bfloat162float(dg[c]) : 0.f));
+    __nv_bfloat16* dgp = static_cast<__nv_bfloat16*>(dgamma);
+    dgp[c] = __float2bfloat16(g + (accumulate ? __bfloat162float(dgp[c]) : 0.f));
     if (dbeta) {
-      __nv_bfloat16* db = static_cast<__nv_bfloat16*>(dbeta);
-      db[c] = __float2bfloat16(b + (accumulate ? __bfloat162float(db[c]) : 0.f));
+      __nv_bfloat16* dbp = static_cast<__nv_bfloat16*>(dbeta);
+      dbp[c] = __float2bfloat16(b + (accumulate ? __bfloat162float(dbp[c]) : 0.f));
     }
   }
 }
@@ -197,14 +240,15 @@ template <int NV>
 static int launch_bwd(const void* x, const void* dy, const void* g, const float* mean, const float* rstd, void* dx,
                       float* partials, int grid, int rows, int rms, cudaStream_t st) {
   constexpr int smem = 2 * NV * 256 * 4;
+  constexpr int MODE = NV <= 8 ? 0 : (NV <= 20 ? 1 : 2);
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (smem > 48 * 1024 && !attr_set[dev & 63]) {
-    MLF_CHECK_CUDA(cudaFuncSetAttribute(norm_bwd_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(norm_bwd_kernel<NV, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[dev & 63] = true;
   }
-  norm_bwd_kernel<NV><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
+  norm_bwd_kernel<NV, MODE><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
                                                static_cast<const __nv_bfloat16*>(dy),
                                                static_cast<const __nv_bfloat16*>(g), mean, rstd,
                                                static_cast<__nv_bfloat16*>(dx), partials, rows, rms);
@@ -240,7 +284,7 @@ MLF_API int mlf_norm_fwd(const void* x, const void* gamma, const void* beta, voi
 
 // Number of fp32 elements the caller must provide as `partials` scratch for mlf_norm_bwd.
 MLF_API long long mlf_norm_bwd_scratch_elems(int rows, int D) {
-  const int grid = min((rows + 7) / 8, sm_count() * 2);
+  const int grid = min((rows + 7) / 8, sm_count());
   return (long long)grid * 2 * D;
 }
 
@@ -249,7 +293,7 @@ MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const
                          int grads_fp32, int accumulate, uint64_t stream) {
   MLF_REQUIRE(D % 256 == 0, "norm: D=%d must be a multiple of 256", D);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = min((rows + 7) / 8, sm_count() * 2);
+  const int grid = min((rows + 7) / 8, sm_count());
   int rc = -2;
   bool matched = true;
   switch (D / 256) {
@@ -260,7 +304,7 @@ MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const
   }
   MLF_REQUIRE(matched, "norm: unsupported D=%d", D);
   if (rc) return rc;
-  norm_bwd_finalize_kernel<<<(D + 255) / 256, 256, 0, st>>>(partials, grid, D, dgamma, rms ? nullptr : dbeta,
+  norm_bwd_finalize_kernel<<<(D + 31) / 32, 256, 0, st>>>(partials, grid, D, dgamma, rms ? nullptr : dbeta,
                                                             grads_fp32, accumulate);
                                                             count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());

@@ -59,7 +59,7 @@ class SymmBuffer:
 class SymmetricMemory:
     def __init__(self, pg=None, device=None, emulate_world: int = 0):
         self.pg = pg
-        self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.emulate = emulate_world > 0
         self.world = emulate_world if self.emulate else (pg.world_size if pg is not None else 1)
         self.rank = 0 if (self.emulate or pg is None) else pg.rank

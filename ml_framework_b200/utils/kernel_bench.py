@@ -93,13 +93,30 @@ def bench_gemm(args) -> list[dict]:
     return rows
 
 
+def run_gemm_small() -> list[dict]:
+    """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
+    from ..ops.gemm import gemm
+    a = torch.randn(8192, 2048, device="cuda").to(torch.bfloat16)
+    b = torch.randn(8192, 2048, device="cuda").to(torch.bfloat16)
+    out = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        gemm(a, b, out=out)
+    torch.cuda.synchronize()
+    return [{"ran": "gemm 8192x8192x2048 x2"}]
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "attn", "elementwise", "attn_small", "gemm_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
         rows = bench_gemm(args)
+    elif args.what == "attn_small":
+        from .kernel_bench_attn import run_attn_small
+        rows = run_attn_small()
+    elif args.what == "gemm_small":
+        rows = run_gemm_small()
     elif args.what == "attn":
         from .kernel_bench_attn import bench_attn
         rows = bench_attn(args)

@@ -67,3 +67,19 @@ def bench_elementwise(args):
     dyb = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
     add("colsum 8192x8192", time_cuda(lambda: native.colsum(dyb)), 8192 * 8192 * 2)
     return rows
+
+
+def run_attn_small():
+    """Two forward + backward launches on B=2, S=2048, 16 heads (Q/K/V/dO 134 MB > L2): the case
+    profiled with ncu."""
+    from ..ops import native
+    B, S, H, D = 2, 2048, 16, 128
+    T = B * S
+    qkv = torch.randn(T, 3 * H * D, device="cuda").to(torch.bfloat16)
+    q, k, v = (qkv[:, i * H * D:(i + 1) * H * D].view(T, H, D) for i in range(3))
+    do = torch.randn(T, H, D, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        out, lse = native.flash_fwd(q, k, v, B, S)
+        native.flash_bwd(q, k, v, out, do, lse, B, S)
+    torch.cuda.synchronize()
+    return [{"ran": "attn fwd+bwd x2"}]
