@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels in this tree use:
-// mbarrier, TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05 (TMEM
+// mbarrier, TMA tile loads (each CTA fetches its own copy of a tile), tcgen05 (TMEM
 // allocation, MMA, commit, load) and system-scope flag loads/stores for peer memory.
 //
 // Every wait in here is bounded: a wait that runs past its cycle budget records a
@@ -117,7 +117,7 @@ __device__ __forceinline__ void fence_proxy_async_all() {
 }
 
 // ---------------------------------------------------------------------------------
-// TMA (tile mode, no multicast)
+// TMA (tile mode; one destination CTA per copy)
 // ---------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");

@@ -26,6 +26,36 @@ from .._lib import (EPI_ACCUM, EPI_BIAS, EPI_DGELU_MUL, EPI_DSWIGLU, EPI_GELU, E
 __all__ = ["gemm", "gemm_reference", "gelu_tanh_ref", "dgelu_tanh_ref"]
 
 
+_piggyback = None
+
+
+def set_piggyback(segs: torch.Tensor, n_segs: int, n_copy_ctas: int = 16, on_attached=None, min_flops: float = 2e10):
+    """Queue a table of {src, dst, bytes} peer copies to ride on the next large plain GEMM: that
+    launch gives ``n_copy_ctas`` of its CTAs to the copies (bulk async copies over NVLink) while
+    the rest compute. Used to prefetch the next FSDP unit's parameters."""
+    global _piggyback
+    _piggyback = (segs, n_segs, n_copy_ctas, on_attached, min_flops)
+
+
+def clear_piggyback():
+    """Drop a queued piggyback that no GEMM picked up (the caller then copies by itself)."""
+    global _piggyback
+    _piggyback = None
+
+
+def _take_piggyback(M, N, K, comm):
+    global _piggyback
+    if _piggyback is None or comm is not None or 2.0 * M * N * K < _piggyback[4]:
+        return None
+    segs, n, ctas, cb, _ = _piggyback
+    _piggyback = None
+    cm = GemmComm()
+    cm.n_copy_ctas, cm.extra_segs, cm.n_extra = ctas, segs.data_ptr(), n
+    if cb is not None:
+        cb()
+    return cm
+
+
 def gelu_tanh_ref(x: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.gelu(x, approximate="tanh")
 
@@ -128,6 +158,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.a_mn, args.b_mn = int(a_mn), int(b_mn)
     args.flags, args.alpha = flags, alpha
     args.tile_n, args.max_ctas = tile_n, max_ctas
+    if comm is None and _piggyback is not None:
+        comm = _take_piggyback(M, N, K, comm)
     args.comm = C.pointer(comm) if comm is not None else None
     rc = _lib.get().mlf_gemm_bf16(C.byref(args), C.c_uint64(_lib.stream_handle()))
     _lib.check(rc, "mlf_gemm_bf16")

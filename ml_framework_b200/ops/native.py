@@ -285,3 +285,57 @@ def flash_bwd(q, k, v, o, dout, lse, B: int, S: int, *, causal: bool = True, sca
                          ll(dq.stride(0)), ll(dk.stride(0)), ll(dv.stride(0)), C.c_float(scale), int(causal), _st())
     _lib.check(rc, "mlf_flash_bwd")
     return dq, dk, dv
+
+
+# ------------------------------------------------------------------ paged attention / KV cache
+def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                 max_seq_len: int, *, scale: Optional[float] = None, split_tokens: int = 512) -> torch.Tensor:
+    """One query token per sequence against its paged KV cache.
+
+    q [B, Hq, 128]; kv_cache [num_blocks, 2, block_size, Hkv, 128]; block_table int32 [B, max_blocks];
+    seq_lens int32 [B] (cached tokens including the current one). ``max_seq_len`` (host int, an upper
+    bound of seq_lens) fixes the number of splits so the launch shape does not depend on device data.
+    """
+    B, Hq, D = q.shape
+    nb, two, bs, Hkv, D2 = kv_cache.shape
+    assert D == 128 and D2 == 128 and two == 2 and q.is_contiguous() and kv_cache.is_contiguous()
+    out = torch.empty_like(q)
+    L = _L()
+    L.mlf_paged_decode_ws_elems.restype = C.c_longlong
+    st = (max(split_tokens, 128) + 127) // 128 * 128
+    splits = max(1, (max_seq_len + st - 1) // st)
+    ws = scratch("paged_decode", L.mlf_paged_decode_ws_elems(B, Hq, splits) * 4, q.device) if splits > 1 else None
+    scale = scale if scale is not None else D ** -0.5
+    rc = L.mlf_paged_decode(_p(q), _p(kv_cache), _p(block_table), _p(seq_lens), _p(out), _p(ws), B, Hq, Hkv, bs,
+                            block_table.shape[1], nb, int(max_seq_len), st, C.c_float(scale), _st())
+    _lib.check(rc, "mlf_paged_decode")
+    return out
+
+
+def kv_cache_write(kv_cache: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor):
+    """Scatter k, v [T, Hkv, 128] into cache slots (slot = block * block_size + offset; < 0 skips)."""
+    nb, _, bs, Hkv, D = kv_cache.shape
+    T = k.shape[0]
+    assert k.stride(2) == 1 and k.stride(1) == D and v.stride(2) == 1 and v.stride(1) == D
+    rc = _L().mlf_kv_cache_write(_p(kv_cache), _p(k), _p(v), _p(slots.contiguous()), C.c_longlong(T), Hkv, bs, nb,
+                                 C.c_longlong(k.stride(0)), C.c_longlong(v.stride(0)), _st())
+    _lib.check(rc, "mlf_kv_cache_write")
+
+
+def kv_gather(kv_cache: torch.Tensor, block_table_row: torch.Tensor, length: int):
+    """Contiguous (k, v) [length, Hkv, 128] of one sequence from its pages."""
+    nb, _, bs, Hkv, D = kv_cache.shape
+    k = torch.empty(length, Hkv, D, dtype=kv_cache.dtype, device=kv_cache.device)
+    v = torch.empty_like(k)
+    rc = _L().mlf_kv_gather(_p(kv_cache), _p(block_table_row.contiguous()), int(length), Hkv, bs, nb, _p(k), _p(v), _st())
+    _lib.check(rc, "mlf_kv_gather")
+    return k, v
+
+
+def argmax_rows(logits: torch.Tensor, vocab: int) -> torch.Tensor:
+    """Greedy sampling: int64 argmax over the first ``vocab`` columns of bf16 ``logits`` [rows, ld]."""
+    assert logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype == torch.bfloat16
+    out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    rc = _L().mlf_argmax_rows(_p(logits), C.c_longlong(logits.shape[0]), C.c_longlong(logits.stride(0)), int(vocab), _p(out), _st())
+    _lib.check(rc, "mlf_argmax_rows")
+    return out

@@ -171,8 +171,18 @@ class FSDP:
         self.opt_kw = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
         self.opt_kw.update(optimizer_kwargs or {})
         self.step_count = 0
+        self._rot_owner = {}
+        self.symm = None
+        self.fused = False
+        if (self.cfg.fused_comm and self.world > 1 and self.device.type == "cuda"
+                and self.cfg.sharding_strategy in ("full", "grad_op")):
+            from ..dist.symm import SymmetricMemory
+            self.symm = SymmetricMemory(process_group, self.device)
+            self.fused = True
         self._build_units()
         self._allocate()
+        if self.fused:
+            self._setup_fused()
         self._install_hooks()
         self.optimizer = self  # exposes step()/state_dict() for the engine
 
@@ -230,13 +240,22 @@ class FSDP:
         pin = self.state_device.type == "cpu" and torch.cuda.is_available()
         mk = lambda: torch.zeros(total, dtype=torch.float32, device=self.state_device, pin_memory=pin)  # noqa: E731
         self.master, self.m, self.v = mk(), mk(), mk()
-        self.param_shards = torch.zeros(total, dtype=dt, device=dev)   # bf16 working copy of what this rank owns
+        esz = torch.empty(0, dtype=dt).element_size()
+        self._symm_bufs = {}
+
+        def symm_or_local(name, numel):
+            if self.fused and numel > 0:
+                b = self.symm.alloc(numel * esz)
+                self._symm_bufs[name] = b
+                return b.view(dt, numel)
+            return torch.zeros(numel, dtype=dt, device=dev)
+        self.param_shards = symm_or_local("param_shards", total)      # bf16 working copy of what this rank owns
         self.grad_shards = torch.zeros(total, dtype=dt, device=dev)    # reduced gradients of what this rank owns
         max_full = max([u.full_numel for u in self.units], default=0)
         # block units rotate through two gathered / gradient buffers; the root unit keeps its own
         n_rot = 2 if not keep_full else 0
         self._rot_full = [torch.zeros(max_full, dtype=dt, device=dev) for _ in range(n_rot)] if max_full else []
-        self._rot_grad = [torch.zeros(max_full, dtype=dt, device=dev) for _ in range(2)] if max_full else []
+        self._rot_grad = [symm_or_local(f"rot_grad{k}", max_full) for k in range(2)] if max_full else []
         with torch.no_grad():
             for u in self.all_units():
                 u.shard = self.param_shards[u.state_off:u.state_off + u.shard_numel]
@@ -251,7 +270,7 @@ class FSDP:
                     u.owned_v = torch.zeros_like(u.owned_master)
                 if persistent:
                     u.gathered = torch.zeros(u.full_numel, dtype=dt, device=dev)
-                    u.grad_full = torch.zeros(u.full_numel, dtype=dt, device=dev) if u is self.root_unit or keep_full else None
+                    u.grad_full = symm_or_local(f"grad_full.{u.name}", u.full_numel) if u is self.root_unit else None
                 for sp in u.sharded:
                     flat = torch.zeros(sp.padded, dtype=dt, device=dev)
                     flat[:sp.numel].copy_(sp.param.data.reshape(-1))
@@ -277,6 +296,34 @@ class FSDP:
                 off += n
             self.master.copy_(self.param_shards.float().to(self.state_device))
         self._comm_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+
+    def _setup_fused(self):
+        """Device-resident segment tables for the peer-copy gather and the peer-read reduce-scatter."""
+        from ..dist.symm import make_copy_segs, make_reduce_segs
+        esz = self.param_shards.element_size()
+        pb = self._symm_bufs["param_shards"]
+        W, r = self.world, self.rank
+        for u in self.all_units():
+            copy, red = [], []
+            for sp in u.sharded:
+                for i in range(W):
+                    src_rank = (r + i) % W          # own shard first, then the peers in ring order
+                    src = pb.ptrs[src_rank] + (u.state_off + sp.shard_off) * esz
+                    dst_off = (sp.full_off + src_rank * sp.shard_numel) * esz
+                    copy.append((src, dst_off, sp.shard_numel * esz))
+                red.append((sp.full_off + r * sp.shard_numel, u.state_off + sp.shard_off, sp.shard_numel))
+            u._copy_rel = copy                       # dst is relative to the gathered buffer's base
+            u._copy_tables = {}
+            u._red_segs = make_reduce_segs(red, self.device)
+            u._red_numel = sum(x[2] for x in red)
+        self._grad_buf_of = {}
+
+    def _copy_table(self, u: "FSDPUnit", full: torch.Tensor) -> torch.Tensor:
+        from ..dist.symm import make_copy_segs
+        key = full.data_ptr()
+        if key not in u._copy_tables:
+            u._copy_tables[key] = make_copy_segs([(s, key + d, n) for s, d, n in u._copy_rel], self.device)
+        return u._copy_tables[key]
 
     def _install_hooks(self):
         fs = self
@@ -311,6 +358,15 @@ class FSDP:
             for sp in u.sharded:
                 full[sp.full_off:sp.full_off + sp.padded].copy_(u.shard[sp.shard_off:sp.shard_off + sp.shard_numel])
             return
+        if self.fused:
+            from ..ops import gemm as gemm_mod
+            if getattr(u, "_prefetched_into", None) == full.data_ptr():
+                u._prefetched_into = None            # already gathered by copy CTAs riding on an earlier GEMM
+                return
+            gemm_mod.clear_piggyback()               # a queued prefetch nobody picked up must not fire later
+            tbl = self._copy_table(u, full)
+            self.symm.peer_copy(tbl, tbl.shape[0], ctas=32)
+            return
         if u.owner is not None:
             if self.rank == u.owner:
                 full[:u.full_numel].copy_(u.owned_full)
@@ -320,6 +376,18 @@ class FSDP:
             self.pg.all_gather_into(full[sp.full_off:sp.full_off + sp.padded],
                                     u.shard[sp.shard_off:sp.shard_off + sp.shard_numel])
 
+    def _schedule_prefetch(self, j: int):
+        """Attach the gather of unit j to the next large GEMM: its copy CTAs pull unit j's shards
+        from the peers over NVLink while the tensor-core CTAs of that GEMM compute."""
+        if not self.fused or not (0 <= j < len(self.units)) or self.cfg.sharding_strategy == "grad_op":
+            return
+        from ..ops import gemm as gemm_mod
+        u = self.units[j]
+        full = self._rot_full[j % 2]
+        tbl = self._copy_table(u, full)
+        gemm_mod.set_piggyback(tbl, tbl.shape[0], n_copy_ctas=16,
+                               on_attached=lambda u=u, full=full: setattr(u, "_prefetched_into", full.data_ptr()))
+
     def _pre_forward(self, i: int):
         u = self.units[i]
         if self.cfg.sharding_strategy == "grad_op":
@@ -327,8 +395,10 @@ class FSDP:
             return
         full = self._rot_full[i % 2]
         self._gather_unit(u, full)
+        self._rot_owner[i % 2] = i
         u.gathered = full
         self._point_params(u, full, None)
+        self._schedule_prefetch(i + 1)
 
     def _post_forward(self, i: int):
         pass  # the rotating buffer is simply reused two units later
@@ -342,12 +412,30 @@ class FSDP:
             u._gbuf = gbuf
             return
         full = self._rot_full[i % 2]
-        self._gather_unit(u, full)
+        if self._rot_owner.get(i % 2) != i:          # the last units of the forward pass are still resident
+            self._gather_unit(u, full)
+            self._rot_owner[i % 2] = i
         u.gathered = full
         self._point_params(u, full, gbuf)
         u._gbuf = gbuf
+        if self._rot_owner.get((i - 1) % 2) != i - 1:
+            self._schedule_prefetch(i - 1)
+
+    def _reduce_unit_fused(self, u: FSDPUnit, gbuf: torch.Tensor, found_inf=None):
+        """Reduce-scatter by peer reads: barrier (every rank has finished this unit's backward),
+        then each rank sums its slices of all W gradient buffers straight out of peer memory."""
+        for sp in u.sharded:
+            if not getattr(sp.param, "_main_grad_started", False):
+                gbuf[sp.full_off:sp.full_off + sp.padded].zero_()
+        name = next(k for k, b in self._symm_bufs.items() if b.local.data_ptr() == gbuf.data_ptr())
+        buf = self._symm_bufs[name]
+        self.symm.barrier()
+        self.symm.rs_reduce(buf, u._red_segs, u._red_segs.shape[0], self.grad_shards, u._red_numel, found_inf=found_inf)
 
     def _reduce_unit(self, u: FSDPUnit, gbuf: torch.Tensor):
+        if self.fused:
+            self._reduce_unit_fused(u, gbuf, getattr(self, "_found_inf", None))
+            return
         for sp in u.sharded:
             p = sp.param
             view = gbuf[sp.full_off:sp.full_off + sp.padded]
@@ -376,6 +464,8 @@ class FSDP:
     # ------------------------------------------------------------------ step
     def train_step(self, ids, targets, scaler=None):
         self.zero_grad()
+        self._found_inf = scaler.found_inf if scaler is not None else None
+        self._rot_owner = {}                          # shards changed at the last optimizer step
         root = self.root_unit
         if root is not None:
             if self.cfg.sharding_strategy != "grad_op":
@@ -446,6 +536,8 @@ class FSDP:
                 self._step_owned(u, gscale, inv_scale, found)
         if scaler is not None:
             scaler.update()
+        if self.fused:
+            self.symm.barrier()      # peers may read the updated shards only after every rank's update
         if self.cfg.sharding_strategy == "grad_op":
             for u in self.all_units():
                 self._gather_unit(u, u.gathered)

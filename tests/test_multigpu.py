@@ -1,0 +1,23 @@
+"""Multi-GPU tests: run only where at least two GPUs are visible (one process per GPU via torchrun)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(script, n, port, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "tests", script)]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fsdp_fused_matches_nccl_two_ranks():
+    r = _torchrun("fsdp_worker.py", 2, 29741)
+    assert r.returncode == 0 and "FSDP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
