@@ -1,0 +1,217 @@
+"""Model executor for the continuous-batching scheduler: a Llama-style decoder running on the paged
+KV cache with the native kernels (GEMM with fused SwiGLU / residual epilogues, RMSNorm, RoPE,
+KV-cache write, FlashAttention-style prefill, paged decode, greedy sampling).
+
+``execute_batch`` is the ``IModelExecutor.ExecuteBatchAsync`` of the reference
+(src/MLFramework/Inference/ContinuousBatching/IModelExecutor.cs:8-16). Its attention path is what
+``PagedAttentionLayer.ComputeAttention`` describes (src/MLFramework/Inference/PagedAttention/Layers/
+PagedAttentionLayer.cs:102-144: project, update the KV cache block by block, attend over the
+sequence's blocks, output projection) with the parts the reference stubs out (copy into blocks,
+gather from blocks, the CUDA kernel) implemented.
+
+Tensor parallel serving: every rank holds ``n_heads / W`` query heads, ``n_kv_heads / W`` KV heads and
+``d_ff / W`` FFN columns; the partial outputs of the o- and down-projections are summed over ranks
+by the one-shot in-kernel all-reduce over peer memory (latency bound: 2 MiB per layer at batch 256)
+or a process-group all-reduce. Rank 0 runs the scheduler and broadcasts each iteration's plan.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..models.llama import Llama, LlamaConfig
+from ..ops import native, reference
+from ..ops.gemm import gemm
+from .. import _lib
+from .kv_cache import KVCacheBlockManager
+from .scheduler import Batch, BatchOutput, Request, RequestState
+
+
+@dataclass
+class ExecutorConfig:
+    max_batch: int = 256
+    max_seq_len: int = 4096
+    prefill_chunk: int = 2048
+    decode_split_tokens: int = 512
+
+
+class PagedLlamaExecutor:
+    def __init__(self, model: Llama, kv: KVCacheBlockManager, config: Optional[ExecutorConfig] = None, tp=None):
+        self.m, self.kv, self.cfg, self.tp = model, kv, config or ExecutorConfig(), tp
+        self.mc: LlamaConfig = model.cfg
+        p = next(model.parameters())
+        self.device, self.dtype = p.device, p.dtype
+        self.native = p.is_cuda and p.dtype == torch.bfloat16 and self.mc.head_dim == 128
+        W = tp.world if tp is not None else 1
+        self.hq, self.hkv = self.mc.n_heads // W, self.mc.n_kv_heads // W
+        self.max_blocks = (self.cfg.max_seq_len + kv.block_size - 1) // kv.block_size
+        self.tokens_generated = 0
+
+    # ---- tensor-parallel reduction of partial projections
+    def _reduce(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        if self.tp is None or self.tp.world == 1:
+            return partial + residual if residual is not None else partial
+        tp = self.tp
+        if tp.fused and partial.is_cuda:
+            n = partial.numel()
+            buf = tp.symm_buffer("serve.ar", self.cfg.max_batch * max(self.cfg.prefill_chunk, 1) * self.mc.d_model * 2
+                                 if n * 2 > (1 << 22) else (1 << 22))
+            buf.view(partial.dtype, n).copy_(partial.reshape(-1))
+            tp.symm.barrier()
+            out = torch.empty_like(partial)
+            tp.symm.all_reduce_one_shot(buf, out, n, residual=residual)
+            tp.symm.barrier()
+            return out
+        from ..dist.process_group import ReduceOp
+        tp.pg.all_reduce(partial, ReduceOp.SUM)
+        return partial + residual if residual is not None else partial
+
+    # ---- one transformer block over T tokens
+    def _block(self, li: int, blk, x: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, attend):
+        mc = self.mc
+        D = mc.head_dim
+        attn = blk.attn if hasattr(blk, "attn") else None
+        qkv_w = attn.qkv.weight if attn is not None else blk.qkv.weight
+        o_w = attn.proj.weight if attn is not None else blk.o.weight
+        gu_w = blk.mlp.gate_up.weight if hasattr(blk, "mlp") else blk.gate_up.weight
+        dn_w = blk.mlp.down.weight if hasattr(blk, "mlp") else blk.down.weight
+        cache = self.kv.caches[li]
+        T = x.shape[0]
+        if self.native:
+            h, _, _ = native.norm_fwd(x, blk.norm1.weight, None, mc.norm_eps, True, want_stats=False)
+            qkv = gemm(h, qkv_w)
+            q = qkv[:, :self.hq * D].view(T, self.hq, D)
+            k = qkv[:, self.hq * D:(self.hq + self.hkv) * D].view(T, self.hkv, D)
+            v = qkv[:, (self.hq + self.hkv) * D:].view(T, self.hkv, D)
+            native.rope_(q, positions, mc.rope_theta)
+            native.rope_(k, positions, mc.rope_theta)
+            native.kv_cache_write(cache, k, v, slots)
+            a = attend(li, q, k, v)
+            x = self._reduce(gemm(a.reshape(T, self.hq * D), o_w), x) if self.tp is not None and self.tp.world > 1 else \
+                gemm(a.reshape(T, self.hq * D), o_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
+            h, _, _ = native.norm_fwd(x, blk.norm2.weight, None, mc.norm_eps, True, want_stats=False)
+            hid = gemm(h, gu_w, flags=_lib.EPI_SWIGLU)
+            if self.tp is not None and self.tp.world > 1:
+                return self._reduce(gemm(hid, dn_w), x)
+            return gemm(hid, dn_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
+        # ---- PyTorch statement of the same block (CPU / fp32)
+        h, _ = reference.rms_norm_ref(x, blk.norm1.weight, mc.norm_eps)
+        qkv = F.linear(h.to(x.dtype), qkv_w)
+        q = qkv[:, :self.hq * D].reshape(T, self.hq, D)
+        k = qkv[:, self.hq * D:(self.hq + self.hkv) * D].reshape(T, self.hkv, D)
+        v = qkv[:, (self.hq + self.hkv) * D:].reshape(T, self.hkv, D)
+        q = reference.rope_ref(q, positions, mc.rope_theta).to(x.dtype)
+        k = reference.rope_ref(k, positions, mc.rope_theta).to(x.dtype)
+        flat = cache.view(-1, 2, self.kv.block_size, self.hkv, D)
+        ok = slots >= 0
+        blk_i, off = slots[ok] // self.kv.block_size, slots[ok] % self.kv.block_size
+        flat[blk_i, 0, off] = k[ok]
+        flat[blk_i, 1, off] = v[ok]
+        a = attend(li, q, k, v)
+        x = self._reduce(F.linear(a.reshape(T, self.hq * D).to(x.dtype), o_w), x)
+        h, _ = reference.rms_norm_ref(x, blk.norm2.weight, mc.norm_eps)
+        gu = F.linear(h.to(x.dtype), gu_w)
+        hid = (F.silu(gu[:, 0::2].float()) * gu[:, 1::2].float()).to(x.dtype)
+        return self._reduce(F.linear(hid, dn_w), x)
+
+    def _embed(self, ids: torch.Tensor) -> torch.Tensor:
+        return self.m.embed(ids)
+
+    def _logits_argmax(self, x_last: torch.Tensor) -> torch.Tensor:
+        mc = self.mc
+        if self.native:
+            h, _, _ = native.norm_fwd(x_last.contiguous(), self.m.norm_f.weight, None, mc.norm_eps, True, want_stats=False)
+            logits = gemm(h, self.m.lm_head)
+            if self.tp is not None and self.tp.world > 1:
+                full = self.tp.pg.all_gather(logits, dim=-1)
+                return full[:, :mc.vocab_size].float().argmax(-1)
+            return native.argmax_rows(logits, mc.vocab_size)
+        h, _ = reference.rms_norm_ref(x_last, self.m.norm_f.weight, mc.norm_eps)
+        logits = F.linear(h.to(x_last.dtype), self.m.lm_head)
+        if self.tp is not None and self.tp.world > 1:
+            logits = self.tp.pg.all_gather(logits, dim=-1)
+        return logits[:, :mc.vocab_size].float().argmax(-1)
+
+    # ---- prefill of one request chunk
+    @torch.no_grad()
+    def _prefill(self, r: Request) -> Optional[int]:
+        start = r.prefilled
+        chunk = r.prompt_tokens[start:start + self.cfg.prefill_chunk]
+        n = len(chunk)
+        slots, _ = self.kv.append_tokens(r.id, n)
+        if slots is None:
+            raise MemoryError(f"KV cache exhausted while prefilling request {r.id}")
+        dev = self.device
+        ids = torch.tensor(chunk, dtype=torch.int64, device=dev)
+        pos = torch.arange(start, start + n, dtype=torch.int64, device=dev)
+        slots = slots.to(dev)
+        table, _ = self.kv.build_tables([r.id], self.max_blocks, dev)
+        total = start + n
+
+        def attend(li, q, k, v):
+            if start == 0:
+                kk, vv = k, v
+            elif self.native:
+                kk, vv = native.kv_gather(self.kv.caches[li], table[0], total)
+            else:
+                nb = (total + self.kv.block_size - 1) // self.kv.block_size
+                c = self.kv.caches[li][table[0, :nb].long()]
+                kk = c[:, 0].reshape(-1, self.hkv, self.mc.head_dim)[:total]
+                vv = c[:, 1].reshape(-1, self.hkv, self.mc.head_dim)[:total]
+            if self.native and start == 0:
+                out, _ = native.flash_fwd(q, kk, vv, 1, n, causal=True, want_lse=False)
+                return out
+            o, _ = reference.attention_ref(q[None], kk[None], vv[None], causal=True, start_pos=start)
+            return o[0].to(q.dtype)
+        x = self._embed(ids[None])[0]
+        for li, blk in enumerate(self.m.blocks):
+            x = self._block(li, blk, x, pos, slots, attend)
+        r.prefilled = total
+        if r.prefilled >= len(r.prompt_tokens):
+            return int(self._logits_argmax(x[-1:])[0])
+        return None
+
+    # ---- one decode step for a set of requests
+    @torch.no_grad()
+    def _decode(self, reqs: List[Request]) -> List[int]:
+        dev = self.device
+        B = len(reqs)
+        last = torch.tensor([r.generated[-1] if r.generated else r.prompt_tokens[-1] for r in reqs], dtype=torch.int64, device=dev)
+        lens_before = [self.kv.get_sequence_length(r.id) for r in reqs]
+        slot_list = []
+        for r in reqs:
+            s, _ = self.kv.append_tokens(r.id, 1)
+            if s is None:
+                raise MemoryError(f"KV cache exhausted while decoding request {r.id}")
+            slot_list.append(s)
+        slots = torch.cat(slot_list).to(dev)
+        pos = torch.tensor(lens_before, dtype=torch.int64, device=dev)
+        table, lens = self.kv.build_tables([r.id for r in reqs], self.max_blocks, dev)
+        max_len = max(lens_before) + 1
+
+        def attend(li, q, k, v):
+            if self.native:
+                return native.paged_decode(q.contiguous(), self.kv.caches[li], table, lens, max_len,
+                                           split_tokens=self.cfg.decode_split_tokens)
+            return reference.paged_attention_ref(q, self.kv.caches[li], table.cpu(), lens.cpu().tolist()).to(q.dtype)
+        x = self._embed(last[None])[0]
+        for li, blk in enumerate(self.m.blocks):
+            x = self._block(li, blk, x, pos, slots, attend)
+        return self._logits_argmax(x).tolist()
+
+    # ---- scheduler entry point
+    def execute_batch(self, batch: Batch) -> BatchOutput:
+        out: Dict[int, int] = {}
+        for r in batch.prefill:
+            tok = self._prefill(r)
+            if tok is not None:
+                out[r.id] = tok
+        if batch.decode:
+            toks = self._decode(batch.decode)
+            for r, t in zip(batch.decode, toks):
+                out[r.id] = int(t)
+        self.tokens_generated += len(out)
+        return BatchOutput(out)

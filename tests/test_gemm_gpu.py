@@ -126,3 +126,23 @@ def test_gather_and_scatter_emulated_ranks():
     for r in range(W):
         _check(parts[r][2], ref[r * (M // W):(r + 1) * (M // W)], K)
         assert parts[r][0].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_cta_pair_kernel(a_mn, b_mn):
+    """tile_n=512 selects the 256 x 256 CTA-pair (cta_group::2) kernel."""
+    torch.manual_seed(5)
+    M, N, K = 1280, 768, 448
+    a = _mk(M, K, a_mn, "cuda")
+    b = _mk(N, K, b_mn, "cuda", 0.1)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=512, bias=bias, flags=_lib.EPI_GELU)
+    ref, _ = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, flags=_lib.EPI_BIAS | _lib.EPI_GELU)
+    torch.cuda.synchronize()
+    _check(out, ref, K)
+    # odd sizes: M and N tails inside a pair tile
+    a = _mk(1000, 320, False, "cuda")
+    b = _mk(600, 320, False, "cuda")
+    out = gemm(a, b, tile_n=512)
+    ref, _ = gemm_reference(a, b)
+    _check(out, ref, 320)

@@ -1,0 +1,194 @@
+"""Serving stack on CPU: native block manager / table / sharing, request queue, capacity,
+completion rules, continuous-batching scheduler with a mock executor (incl. a failing one),
+and the paged Llama executor against plain full-sequence greedy decoding."""
+import threading
+import time
+
+import pytest
+import torch
+
+from ml_framework_b200.models import Llama, LlamaConfig
+from ml_framework_b200.serving.executor import ExecutorConfig, PagedLlamaExecutor
+from ml_framework_b200.serving.kv_cache import (BeamSearchBlockSharing, BlockShareManager, BlockTable, KVCacheBlockManager,
+                                                SpeculativeDecodingSharing)
+from ml_framework_b200.serving.scheduler import (BatchConstraints, BatchOutput, CapacityConstraints, CapacityManager,
+                                                 CompletionConfiguration, CompletionDetector, CompletionReason,
+                                                 ContinuousBatchScheduler, ContinuousBatchSchedulerClient,
+                                                 PagedAttentionScheduler, PrefillConfiguration, PrefillHandler, Priority,
+                                                 Request, RequestQueue, SchedulerConfiguration)
+
+
+def test_block_manager_allocation_and_stats():
+    m = KVCacheBlockManager(8, 16, allocate_cache=False)
+    assert m.allocate_block(1).block_ids == [0]
+    r = m.allocate_blocks(1, 3)
+    assert r.success and r.block_ids == [1, 2, 3] and m.get_sequence_blocks(1) == [0, 1, 2, 3]
+    bad = m.allocate_blocks(2, 5)                      # all-or-nothing
+    assert not bad.success and m.free_blocks == 4 and m.get_sequence_blocks(2) == []
+    assert m.free_sequence_blocks(1) == 4 and m.free_blocks == 8
+    st = m.get_stats()
+    assert (st.total_blocks, st.allocated_blocks, st.total_allocations, st.total_frees, st.failed_allocations) == (8, 0, 4, 4, 1)
+    assert m.allocate_block(3).block_ids == [4]        # FIFO free list: freed blocks go to the back
+    with pytest.raises(ValueError):
+        KVCacheBlockManager(0, 16, allocate_cache=False)
+
+
+def test_append_tokens_table_and_lengths():
+    m = KVCacheBlockManager(6, 4, allocate_cache=False)
+    slots, cow = m.append_tokens(7, 6)
+    assert slots.tolist() == [0, 1, 2, 3, 4, 5] and cow is None and m.get_sequence_length(7) == 6
+    slots, _ = m.append_tokens(7, 3)
+    assert slots.tolist() == [6, 7, 8] and m.get_sequence_blocks(7) == [0, 1, 2]
+    t = BlockTable(m)
+    assert t.get_block(7, 5) == 1 and t.get_sequence_length(7) == 9
+    with pytest.raises(IndexError):
+        t.get_block(7, 100)
+    table, lens = m.build_tables([7, 99], 4)
+    assert table.tolist() == [[0, 1, 2, -1], [-1, -1, -1, -1]] and lens.tolist() == [9, 0]
+    assert m.append_tokens(8, 100)[0] is None and m.get_stats().failed_allocations == 1
+    assert m.truncate(7, 4) == 2 and m.get_sequence_blocks(7) == [0]
+
+
+def test_prefix_sharing_copy_on_write_beams_and_speculation():
+    m = KVCacheBlockManager(16, 4, head_dim=8, num_layers=1, num_kv_heads=1, device="cpu", dtype=torch.float32)
+    m.append_tokens(1, 6)                               # blocks 0 (full), 1 (2 of 4 used)
+    m.caches[0][1].fill_(3.0)
+    sh = BlockShareManager(m)
+    assert sh.share_prefix(1, 2, 6) == 1                # only the whole block is shared
+    assert sh.get_reference_count(0) == 2 and m.get_sequence_length(2) == 4
+    beams = BeamSearchBlockSharing(m)
+    beams.initialize_beams(1, [10, 11])
+    assert m.reference_count(1) == 3
+    slots, cow = beams.on_beam_divergence(10)           # writes into a shared partial block -> copy first
+    assert cow is not None and cow[0] == 1 and m.reference_count(1) == 2
+    assert torch.equal(m.caches[0][cow[1]], m.caches[0][1]) and slots.tolist() == [cow[1] * 4 + 2]
+    beams.cleanup_beams(1)
+    assert m.reference_count(1) == 1
+    spec = SpeculativeDecodingSharing(m)
+    spec.allocate_speculative_blocks(1, 7)
+    assert m.get_sequence_length(1) == 13
+    spec.verify_speculation(1, 2)
+    assert m.get_sequence_length(1) == 8 and len(m.get_sequence_blocks(1)) == 2
+    sh.register_prefix([5, 6, 7, 8], 1)
+    assert sh.find_prefix([5, 6, 7, 8, 9]) == (1, 4) and sh.find_prefix([5, 6]) is None
+    free_before = m.free_blocks
+    sh.release_sequence(1)
+    assert m.free_blocks == free_before + 1             # block 0 is still held by sequence 2
+
+
+def test_queue_capacity_completion_and_admission():
+    q = RequestQueue()
+    rs = [Request([1], priority=p) for p in (Priority.LOW, Priority.URGENT, Priority.NORMAL, Priority.URGENT)]
+    for r in rs:
+        q.enqueue(r)
+    assert q.mark_cancelled(rs[3].id)
+    got = q.get_requests(10, lambda r: True)
+    assert [r.id for r in got] == [rs[1].id, rs[2].id, rs[0].id]
+    assert rs[3].future.result(0).reason == CompletionReason.CANCELLED
+    q.enqueue(Request([1] * 10)); q.enqueue(Request([1]))
+    assert len(q.get_requests(5, lambda r: len(r.prompt_tokens) < 5)) == 0     # head does not fit: nobody jumps the queue
+    cap = CapacityManager(CapacityConstraints(max_batch_size=2, max_memory_bytes=10_000, buffer_ratio=0.1), bytes_per_token=10)
+    a, b, c = Request([0] * 100, max_tokens=300), Request([0] * 100, max_tokens=300), Request([0] * 10, max_tokens=10)
+    assert cap.try_allocate(a) and cap.try_allocate(b) and not cap.try_allocate(c)   # slots exhausted
+    cap.release(a.id)
+    big = Request([0] * 500, max_tokens=500)
+    assert not cap.try_allocate(big) and cap.try_allocate(c)                          # 9000 usable bytes
+    det = CompletionDetector(CompletionConfiguration(eos_token_id=2, max_response_length=50), detokenize=lambda t: "".join(map(str, t)))
+    r = Request([1, 1], max_tokens=3, stop_strings=("77",))
+    assert det.check(r) is None
+    r.generated = [5, 2]
+    assert det.check(r) == CompletionReason.EOS
+    r.generated = [7, 7]
+    assert det.check(r) == CompletionReason.STOP_STRING
+    r.generated = [5, 5, 5]
+    assert det.check(r) == CompletionReason.MAX_TOKENS
+    r.cancelled = True
+    assert det.check(r) == CompletionReason.CANCELLED
+    m = KVCacheBlockManager(10, 16, allocate_cache=False)
+    adm = PagedAttentionScheduler(m, reserved_blocks=2)
+    assert adm.can_admit(100, 28) and not adm.can_admit(100, 29)
+    m.allocate_blocks(1, 8)
+    assert adm.should_apply_backpressure() and adm.recommended_max_sequence_length(1) == 0
+    ph = PrefillHandler(PrefillConfiguration(chunk_size=4, prompt_cache_entries=1), clock=lambda: 0.0)
+    rr = Request(list(range(10)))
+    assert ph.next_chunk(rr) == [0, 1, 2, 3] and ph.needs_prefill(rr)
+    ph.cache_store([1, 2], "a"); ph.cache_store([3], "b")
+    assert ph.cache_lookup([1, 2]) is None and ph.cache_lookup([3]) == "b"
+
+
+class MockExecutor:
+    """Emits prompt_len + k as the k-th token and EOS (2) after ``eos_after`` tokens."""
+
+    def __init__(self, eos_after=4, fail_on=None):
+        self.eos_after, self.fail_on, self.calls, self.batch_sizes = eos_after, fail_on, 0, []
+
+    def execute_batch(self, batch):
+        self.calls += 1
+        self.batch_sizes.append(len(batch.requests))
+        if self.fail_on is not None and self.calls == self.fail_on:
+            raise RuntimeError("model blew up")
+        out = {}
+        for r in batch.requests:
+            r.prefilled = len(r.prompt_tokens)
+            k = len(r.generated)
+            out[r.id] = 2 if k + 1 >= self.eos_after else 100 + k
+        return BatchOutput(out)
+
+
+class Tok:
+    def encode(self, s): return [ord(c) % 50 + 3 for c in s]
+    def decode(self, t): return " ".join(map(str, t))
+
+
+def test_scheduler_end_to_end_with_mock_executor():
+    ex = MockExecutor(eos_after=4)
+    s = ContinuousBatchScheduler(ex, None, SchedulerConfiguration(max_batch_size=3))
+    reqs = [Request([1, 2, 3], max_tokens=10) for _ in range(7)] + [Request([1], max_tokens=2)]
+    futs = [s.enqueue(r) for r in reqs]
+    s.run_until_idle()
+    res = [f.result(0) for f in futs]
+    assert all(r.reason == CompletionReason.EOS and r.tokens == [100, 101, 102, 2] for r in res[:7])
+    assert res[7].reason == CompletionReason.MAX_TOKENS and res[7].tokens == [100, 101]
+    assert max(ex.batch_sizes) == 3 and s.metrics.snapshot()["completed"] == 8
+    assert s.metrics.snapshot()["reasons"] == {"eos": 7, "max_tokens": 1}
+    assert all(r.ttft_s is not None and r.latency_s >= r.ttft_s for r in res)
+
+
+def test_scheduler_survives_executor_failure_and_background_loop():
+    ex = MockExecutor(eos_after=3, fail_on=2)
+    s = ContinuousBatchScheduler(ex, None, SchedulerConfiguration(max_batch_size=2))
+    client = ContinuousBatchSchedulerClient(s, Tok())
+    s.start()
+    try:
+        a = client.submit("hello", 8)
+        b = client.submit("world", 8)
+        ra, rb = a.future.result(5), b.future.result(5)
+        assert {ra.reason, rb.reason} == {CompletionReason.ERROR} and "blew up" in ra.error
+        ok = client.generate_text("again", 8, timeout_s=5)
+        assert ok.reason == CompletionReason.EOS and ok.text == "100 101 2"
+        assert client.statistics()["errors"] == {"RuntimeError": 1} and client.status()["running"] == 0
+        c = client.submit("x", 1000)
+        assert client.cancel(c.id) and c.future.result(5).reason in (CompletionReason.CANCELLED, CompletionReason.EOS)
+    finally:
+        s.stop()
+
+
+def test_paged_llama_executor_matches_full_sequence_greedy():
+    torch.manual_seed(0)
+    cfg = LlamaConfig(n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128, vocab_size=50, max_seq=64, vocab_multiple=8)
+    model = Llama(cfg).eval()
+    kv = KVCacheBlockManager(64, 4, head_dim=16, num_layers=2, num_kv_heads=2, device="cpu", dtype=torch.float32)
+    ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=64, prefill_chunk=5))
+    s = ContinuousBatchScheduler(ex, kv, SchedulerConfiguration(max_batch_size=4), completion=CompletionConfiguration(eos_token_id=-1))
+    prompts = [[3, 7, 11, 2, 9, 30, 4], [5, 6], [40, 41, 42, 43, 44, 45, 46, 47, 48, 1, 2]]
+    reqs = [Request(p, max_tokens=6) for p in prompts]
+    futs = [s.enqueue(r) for r in reqs]
+    s.run_until_idle()
+    for p, f in zip(prompts, futs):
+        seq = list(p)
+        for _ in range(6):
+            with torch.no_grad():
+                logits = model(torch.tensor([seq]))
+            seq.append(int(logits[0, -1].argmax()))
+        assert f.result(0).tokens == seq[len(p):], (p, f.result(0).tokens, seq[len(p):])
+    assert kv.get_stats().allocated_blocks == 0          # everything released after completion
