@@ -1,0 +1,169 @@
+"""Failure detection, retry, elastic rescaling - all injected on the host (a rank that raises, a
+worker that stops sending heartbeats, a dropped message); nothing here touches a GPU."""
+import pytest
+import torch
+
+from ml_framework_b200.dist.elastic import (AdaptiveLearningRateScheduler, DataRedistributor, ElasticCoordinator, ElasticError,
+                                            ElasticTrainingConfig, ElasticWorker, LRAdaptationStrategy, RescaleType, WorkerStatus)
+from ml_framework_b200.dist.fault_tolerance import (AlgorithmSelector, ChunkManager, CollectiveAlgorithm, CommunicationConfig,
+                                                    ErrorRecoveryManager, FaultTolerantCommunication, HealthMonitor, NCCLConfig,
+                                                    RankHealth, RecoveryStrategy, RingAllReduce, TimeoutManager,
+                                                    create_data_parallel_groups, create_pipeline_groups, create_split_groups)
+from ml_framework_b200.dist.process_group import (CommunicationError, CommunicationTimeout, RankMismatchError, ReduceOp,
+                                                  run_fake_world)
+from ml_framework_b200.data.samplers import ElasticDistributedSampler
+
+
+class FlakyPG:
+    rank, world_size = 0, 2
+
+    def __init__(self, fail_times, exc):
+        self.fail_times, self.exc, self.calls = fail_times, exc, 0
+
+    def all_reduce(self, t, op=None):
+        self.calls += 1
+        if self.calls <= self.fail_times:
+            raise self.exc
+        return t * 2
+
+
+def test_retry_timeout_and_abort_strategies():
+    sleeps = []
+    ft = FaultTolerantCommunication(FlakyPG(2, IOError("link")), CommunicationConfig(max_retries=3, retry_delay_ms=100), sleep=sleeps.append)
+    assert ft.all_reduce(torch.ones(1)).item() == 2 and ft.retries == 2 and sleeps == [0.1, 0.1]
+    ft = FaultTolerantCommunication(FlakyPG(5, CommunicationTimeout("slow")), CommunicationConfig(max_retries=2, retry_delay_ms=0), sleep=lambda s: None)
+    with pytest.raises(CommunicationTimeout):
+        ft.all_reduce(torch.ones(1))
+    assert ft.pg.calls == 3
+    ft = FaultTolerantCommunication(FlakyPG(1, RankMismatchError("bad")), sleep=lambda s: None)
+    with pytest.raises(RankMismatchError):
+        ft.all_reduce(torch.ones(1))
+    assert ft.pg.calls == 1 and ft.recovery.get_statistics()["by_strategy"] == {"abort": 1}
+    rec = ErrorRecoveryManager()
+    assert rec.handle_error("x", KeyError("?")) == RecoveryStrategy.ABORT
+
+
+def test_a_rank_that_never_joins_times_out_the_others():
+    def run(pg):
+        if pg.rank == 1:
+            return "absent"                       # never calls the collective
+        with pytest.raises(CommunicationTimeout):
+            pg.all_reduce(torch.ones(2))
+        return "timed out"
+    assert run_fake_world(2, run, timeout_s=0.3) == ["timed out", "absent"]
+
+    def run2(pg):                                  # a rank that raises before the collective
+        if pg.rank == 0:
+            pg.drop_next = True
+        try:
+            pg.barrier()
+            return "ok"
+        except CommunicationError as e:
+            return type(e).__name__
+    assert run_fake_world(2, run2, timeout_s=0.3) == ["CommunicationError", "CommunicationTimeout"]
+
+
+def test_health_monitor_and_timeout_manager():
+    now = [0.0]
+    hm = HealthMonitor(3, clock=lambda: now[0])
+    now[0] = 31.0
+    hm.update_heartbeat(0)
+    assert hm.status(0) == RankHealth.HEALTHY and hm.status(1) == RankHealth.UNRESPONSIVE
+    now[0] = 61.0
+    hm.update_heartbeat(0)
+    assert hm.status(2) == RankHealth.FAILED and hm.get_healthy_ranks() == [0] and hm.get_failed_ranks() == [1, 2]
+    tm = TimeoutManager(clock=lambda: now[0])
+    h = tm.start_timeout(5)
+    now[0] = 67.0
+    assert tm.is_expired(h)
+    tm.extend_timeout(h, 10)
+    assert not tm.is_expired(h)
+    tm.cancel_timeout(h)
+    assert not tm.is_expired(h)
+
+
+def test_ring_all_reduce_matches_sum_and_chunking():
+    cm = ChunkManager(10, 4)
+    assert cm.sizes == [3, 3, 2, 2] and cm.offsets == [0, 3, 6, 8]
+    data = [torch.arange(10, dtype=torch.float32) * (r + 1) for r in range(4)]
+    want = sum(data)
+
+    def run(pg):
+        t = data[pg.rank].clone()
+        RingAllReduce(pg).all_reduce(t, ReduceOp.SUM)
+        a = data[pg.rank].clone()
+        RingAllReduce(pg).all_reduce(a, ReduceOp.AVG)
+        return t, a
+    for t, a in run_fake_world(4, run):
+        assert torch.equal(t, want) and torch.allclose(a, want / 4)
+
+
+def test_algorithm_selection_groups_and_nccl_env():
+    s = AlgorithmSelector(nvswitch=False)
+    assert s.select_all_reduce(1024, 8) == CollectiveAlgorithm.RECURSIVE_DOUBLING
+    assert s.select_all_reduce(512 * 1024, 16) == CollectiveAlgorithm.RABENSEIFNER
+    assert s.select_all_reduce(8 << 20, 8) == CollectiveAlgorithm.RING and s.select_all_reduce(64 << 20, 8) == CollectiveAlgorithm.TREE
+    nv = AlgorithmSelector()
+    assert nv.select_all_reduce(2 << 20, 8) == CollectiveAlgorithm.ONE_SHOT and nv.select_all_reduce(64 << 20, 8) == CollectiveAlgorithm.TWO_SHOT
+    assert create_split_groups(8, 4) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert create_pipeline_groups(8, 4) == [[0, 2, 4, 6], [1, 3, 5, 7]]
+    assert create_data_parallel_groups(8, 2) == [[0, 2, 4, 6], [1, 3, 5, 7]]
+    env = NCCLConfig.create_debug().apply({})
+    assert env["NCCL_DEBUG"] == "INFO" and env["NCCL_BLOCKING_WAIT"] == "1" and env["NCCL_BUFFSIZE"] == str(4 << 20)
+
+
+def test_elastic_lifecycle_heartbeat_failure_and_debounce():
+    now = [0.0]
+    cfg = ElasticTrainingConfig(min_workers=1, stability_window_ms=1000, worker_heartbeat_timeout_ms=500, failure_tolerance_percentage=50)
+    coord = ElasticCoordinator(cfg, clock=lambda: now[0])
+    samplers = {w: ElasticDistributedSampler(100, 1, 0, shuffle=False) for w in "abc"}
+
+    class Opt:
+        lr = 0.1
+        def set_learning_rate(self, lr): self.lr = lr
+    opts = {w: Opt() for w in "abc"}
+    workers = {w: ElasticWorker(w, coord, samplers[w], AdaptiveLearningRateScheduler(0.1, 1), opts[w]) for w in "abc"}
+    workers["a"].connect_to_cluster()
+    now[0] = 0.2
+    workers["b"].connect_to_cluster()              # rapid change: the window restarts, only one event fires
+    assert coord.poll() is None
+    now[0] = 1.0
+    for w in "ab":
+        workers[w].heartbeat()
+    assert coord.poll() is None
+    now[0] = 1.3
+    for w in "ab":
+        workers[w].heartbeat()
+    ev = coord.poll()
+    assert ev is not None and ev.kind == RescaleType.SCALE_UP and ev.new.world_size == 2 and len(coord.events) == 1
+    assert workers["a"].status == WorkerStatus.ACTIVE and (workers["a"].rank, workers["b"].rank) == (0, 1)
+    assert abs(opts["a"].lr - 0.2) < 1e-12 and len(samplers["b"]) == 50
+    # worker b stops sending heartbeats: detected, unregistered, one scale-down event after the window
+    now[0] = 1.6
+    workers["a"].heartbeat()
+    now[0] = 1.9
+    workers["a"].heartbeat()
+    assert coord.check_health() == ["b"]
+    now[0] = 2.2
+    workers["a"].heartbeat()
+    assert coord.poll() is None
+    now[0] = 2.6
+    workers["a"].heartbeat()
+    now[0] = 3.0
+    workers["a"].heartbeat()
+    ev = coord.poll()
+    assert ev.kind == RescaleType.SCALE_DOWN and ev.removed == ["b"] and workers["a"].world_size == 1
+    # a second failure crosses the 50 % tolerance
+    workers["c"].connect_to_cluster()
+    with pytest.raises(ElasticError, match="tolerance"):
+        coord.unregister_worker("c", graceful=False)
+
+
+def test_lr_adaptation_and_data_plan():
+    s = AdaptiveLearningRateScheduler(0.1, 4, LRAdaptationStrategy.SQUARE_ROOT)
+    assert abs(s.adapt_learning_rate(16) - 0.2) < 1e-12 and s.transition_learning_rate(0.1, 0.2, 5, 10) == pytest.approx(0.15)
+    plan = DataRedistributor().calculate_plan(100, 4, 2)
+    moved = sum(t.end - t.start for t in plan)
+    assert moved == 75 and all(t.src_rank != t.dst_rank for t in plan)
+    with pytest.raises(ValueError):
+        ElasticTrainingConfig(min_workers=0).validate()
