@@ -482,7 +482,7 @@ using namespace mlf;
 
 MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream);
 
-static int g_use_2cta = 0;
+static int g_use_2cta = 1;
 // Selects the CTA-pair kernel for large plain GEMMs (tile_n == 0). tile_n == 512 always selects it.
 MLF_API void mlf_set_gemm_2cta(int on) { g_use_2cta = on; }
 MLF_API int mlf_get_gemm_2cta() { return g_use_2cta; }

@@ -9,8 +9,10 @@
 // shared between CTAs through the copy engine: every CTA fetches exactly the bytes it owns.
 //
 // Synchronisation (all barriers live at the same shared-memory offsets in both CTAs):
-//   full[s]   in the leader, count 2: each CTA's producer arrives with its own byte count and its
-//             TMA loads complete on the leader's barrier (2-SM form of the TMA load).
+//   full[s]   in the leader, count 1: the leader's producer arrives with the byte count of both
+//             CTAs' loads; every load of the pair completes on that barrier (2-SM form of the TMA
+//             load). A peer load may land before the leader's arrive of the same phase, never in
+//             an earlier phase: the peer refills a stage only after the MMAs that read it are done.
 //   empty[s]  in each CTA: the leader commits twice after the k-block's MMAs, once to its own and
 //             once to the peer's barrier (address translated with mapa).
 //   tfull[a]  in each CTA (same double commit), tempty[a] in the leader, count 8: the four
@@ -107,7 +109,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T2_STAGES; ++s) {
-      mbar_init(full_bar(s), 2);
+      mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -152,7 +154,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint32_t sa = smem_base + s * T2_STAGE;
           const uint32_t sb = sa + T2_STAGE_A;
           const uint32_t lead_full = mapa_u32(full_bar(s), 0);
-          mbar_arrive_expect_tx_cluster(lead_full, T2_STAGE);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * T2_STAGE);
           const int k0 = kb * BK;
           if (!p.a_mn) {
             tma_load_2d_pair(sa, &tmA, k0, m0, lead_full);

@@ -1,0 +1,221 @@
+"""CUDA graphs: capture after warm-up, validate, replay, fall back to eager.
+
+Covers the reference's graph manager (src/MLFramework/HAL/CUDA/Graphs/CUDAGraphManager.cs:40-109:
+3 warm-up iterations, 512 MB pool, GetOrCaptureGraph, ExecuteGraphOrFallback), capture object
+(CUDAGraphCapture.cs:30-57), validation rules (Validation/Rules/*: control flow, dynamic memory,
+empty graph, I/O, synchronisation), fallback handler (Fallback/CUDAGraphFallbackHandler.cs:56),
+weight updater (ICUDAGraphWeightUpdater.cs) and the capture-safe fixed-address pool
+(HAL/CUDA/Memory/CUDAGraphMemoryPool.cs:24-98, 256-byte alignment).
+
+Launch-bound loops here (one decode iteration is ~300 launches of a few microseconds each) are the
+target: a captured decode step replays as one graph launch. Inputs live in static buffers from the
+pool; ``replay`` copies new inputs in, launches and returns the static outputs.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+class GraphMemoryPool:
+    """Bump allocator over one device slab; addresses stay fixed for the life of the pool so that a
+    captured graph's pointers stay valid. ``reset`` rewinds; blocks may be returned in LIFO order."""
+
+    ALIGN = 256
+
+    def __init__(self, capacity_bytes: int = 512 << 20, device: Optional[torch.device] = None):
+        self.capacity = capacity_bytes
+        self.device = device if device is not None else (torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu"))
+        self._slab: Optional[torch.Tensor] = None
+        self._off = 0
+        self.peak = 0
+        self._blocks: List[Tuple[int, int]] = []
+
+    def _ensure(self):
+        if self._slab is None:
+            self._slab = torch.empty(self.capacity, dtype=torch.uint8, device=self.device)
+
+    def allocate(self, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        self._ensure()
+        esz = torch.empty((), dtype=dtype).element_size()
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = (n * esz + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        if self._off + nbytes > self.capacity:
+            raise MemoryError(f"graph memory pool exhausted: {self._off + nbytes} > {self.capacity} bytes")
+        t = self._slab[self._off:self._off + n * esz].view(dtype).view(*shape)
+        self._blocks.append((self._off, nbytes))
+        self._off += nbytes
+        self.peak = max(self.peak, self._off)
+        return t
+
+    def return_block(self, t: torch.Tensor) -> bool:
+        if not self._blocks:
+            return False
+        off, nbytes = self._blocks[-1]
+        if self._slab.data_ptr() + off == t.data_ptr():
+            self._blocks.pop()
+            self._off = off
+            return True
+        return False
+
+    def reset(self):
+        self._off = 0
+        self._blocks.clear()
+
+    def stats(self) -> Dict[str, int]:
+        return {"capacity": self.capacity, "used": self._off, "peak": self.peak, "blocks": len(self._blocks)}
+
+
+class ValidationSeverity(enum.Enum):
+    WARNING = 1
+    ERROR = 2
+
+
+@dataclass
+class ValidationIssue:
+    rule: str
+    message: str
+    severity: ValidationSeverity = ValidationSeverity.ERROR
+
+
+@dataclass
+class CapturedOp:
+    """What a capture recorded about one operation, for validation."""
+    name: str
+    kind: str = "kernel"      # kernel | memcpy | memset | host | alloc | free | sync | io | branch
+
+
+class GraphValidator:
+    """Rules over a list of recorded ops: a graph must not be empty, allocate or free device memory,
+    depend on host-side control flow, perform host I/O, or synchronise the device."""
+
+    def validate(self, ops: Sequence[CapturedOp]) -> List[ValidationIssue]:
+        issues: List[ValidationIssue] = []
+        if not ops:
+            issues.append(ValidationIssue("EmptyGraph", "capture recorded no operations"))
+        for op in ops:
+            if op.kind in ("alloc", "free"):
+                issues.append(ValidationIssue("DynamicMemory", f"{op.name}: device memory management inside a capture"))
+            elif op.kind == "branch":
+                issues.append(ValidationIssue("ControlFlow", f"{op.name}: data-dependent host control flow cannot be replayed"))
+            elif op.kind == "io":
+                issues.append(ValidationIssue("IOOperation", f"{op.name}: host I/O inside a capture"))
+            elif op.kind == "sync":
+                issues.append(ValidationIssue("Synchronization", f"{op.name}: device / stream synchronisation inside a capture"))
+            elif op.kind == "host":
+                issues.append(ValidationIssue("HostCallback", f"{op.name}: host callback", ValidationSeverity.WARNING))
+        return issues
+
+    def is_valid(self, ops: Sequence[CapturedOp]) -> bool:
+        return not any(i.severity == ValidationSeverity.ERROR for i in self.validate(ops))
+
+
+@dataclass
+class CaptureOptions:
+    warmup_iterations: int = 3
+    pool_bytes: int = 512 << 20
+    enable_fallback: bool = True
+    max_capture_failures: int = 3
+
+
+class CapturedGraph:
+    def __init__(self, graph, static_inputs: List[torch.Tensor], static_outputs, name: str):
+        self.graph, self.static_inputs, self.static_outputs, self.name = graph, static_inputs, static_outputs, name
+        self.replays = 0
+
+    def replay(self, *inputs: torch.Tensor):
+        for dst, src in zip(self.static_inputs, inputs):
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        self.replays += 1
+        return self.static_outputs
+
+    def update_weights(self, pairs: Sequence[Tuple[torch.Tensor, torch.Tensor]]):
+        """In-place weight refresh: the graph holds addresses, so new values are copied into the old
+        storage (the reference's weight-updater contract)."""
+        with torch.no_grad():
+            for old, new in pairs:
+                old.copy_(new)
+
+
+class CUDAGraphManager:
+    """``run(name, fn, *inputs)``: eager for the first ``warmup_iterations`` calls, then captured once
+    per (name, input signature) and replayed; capture failures fall back to eager permanently after
+    ``max_capture_failures``."""
+
+    def __init__(self, options: Optional[CaptureOptions] = None):
+        self.opt = options or CaptureOptions()
+        self._graphs: Dict[Tuple, CapturedGraph] = {}
+        self._calls: Dict[Tuple, int] = {}
+        self._failures: Dict[str, int] = {}
+        self._pool_handle = None
+        self.fallbacks = 0
+
+    @staticmethod
+    def _sig(name: str, inputs: Sequence[torch.Tensor]) -> Tuple:
+        return (name,) + tuple((tuple(t.shape), t.dtype, t.device.index) for t in inputs)
+
+    def capture(self, name: str, fn: Callable, inputs: Sequence[torch.Tensor]) -> CapturedGraph:
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA graphs need a CUDA device")
+        static_in = [t.clone() for t in inputs]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn(*static_in)                                   # settle lazy initialisation off the main stream
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        if self._pool_handle is None:
+            self._pool_handle = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(g, pool=self._pool_handle):
+            out = fn(*static_in)
+        cg = CapturedGraph(g, static_in, out, name)
+        self._graphs[self._sig(name, inputs)] = cg
+        return cg
+
+    def run(self, name: str, fn: Callable, *inputs: torch.Tensor):
+        key = self._sig(name, inputs)
+        cg = self._graphs.get(key)
+        if cg is not None:
+            return cg.replay(*inputs)
+        n = self._calls.get(key, 0)
+        self._calls[key] = n + 1
+        can_capture = torch.cuda.is_available() and all(t.is_cuda for t in inputs) \
+            and self._failures.get(name, 0) < self.opt.max_capture_failures
+        if n < self.opt.warmup_iterations or not can_capture:
+            if n >= self.opt.warmup_iterations:
+                self.fallbacks += 1
+            return fn(*inputs)
+        try:
+            cg = self.capture(name, fn, inputs)
+            return cg.replay(*inputs)
+        except Exception:
+            self._failures[name] = self._failures.get(name, 0) + 1
+            if not self.opt.enable_fallback:
+                raise
+            self.fallbacks += 1
+            return fn(*inputs)
+
+    def stats(self) -> Dict[str, int]:
+        return {"graphs": len(self._graphs), "fallbacks": self.fallbacks,
+                "replays": sum(g.replays for g in self._graphs.values())}
+
+    def clear(self):
+        self._graphs.clear()
+        self._calls.clear()
+
+
+def capture_graph(manager: CUDAGraphManager, name: Optional[str] = None):
+    """Decorator form (the reference's ``[CaptureGraph]`` attribute and proxy)."""
+    def deco(fn):
+        def wrapped(*inputs):
+            return manager.run(name or fn.__name__, fn, *inputs)
+        wrapped.__wrapped__ = fn
+        return wrapped
+    return deco
