@@ -165,7 +165,7 @@ def main():
         ids = host_ids[i % n_batches].to(dev, non_blocking=True)
         tgt = host_tgt[i % n_batches].to(dev, non_blocking=True)
         loss = step_fn(ids, tgt)
-        losses.append(float(loss.float().cpu()))
+        losses.append(float(loss.detach().float().cpu()))
     f1.record()
     barrier()
     ms_e2e = f0.elapsed_time(f1) / args.steps
