@@ -416,6 +416,7 @@ def rmse(a: torch.Tensor, b: torch.Tensor) -> float:
 
 
 def sqnr_db(ref: torch.Tensor, q: torch.Tensor) -> float:
+    ref, q = ref.detach(), q.detach()
     n = ((ref.float() - q.float()) ** 2).sum()
     return float(10 * torch.log10((ref.float() ** 2).sum() / n.clamp_min(1e-30)))
 

@@ -1,0 +1,448 @@
+"""CPU tests of the framework's peripheral subsystems: autograd utilities, activation checkpointing, HAL,
+CUDA-graph bookkeeping, compiler stack, data pipeline, observability, quantisation, second-order
+optimisers, request batching, deployment / versioning, model zoo, mobile runtime, CLI."""
+import copy
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+
+# ------------------------------------------------------------------ autograd + checkpointing
+def test_activation_checkpoint_matches_plain_backward():
+    from ml_framework_b200.checkpoint.activation import (CheckpointConfig, CheckpointManager, CheckpointStrategyKind,
+                                                          apply_activation_checkpointing, checkpoint)
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Linear(4, 8), nn.Tanh(), nn.Dropout(0.5), nn.Linear(8, 3))
+    x = torch.randn(5, 4, requires_grad=True)
+    torch.manual_seed(1)
+    net(x).sum().backward()
+    gx, gw = x.grad.clone(), net[0].weight.grad.clone()
+    x.grad = None
+    net.zero_grad()
+    torch.manual_seed(1)
+    checkpoint(net, x).sum().backward()
+    assert torch.allclose(gx, x.grad) and torch.allclose(gw, net[0].weight.grad)     # same dropout mask on recompute
+    mgr = CheckpointManager(CheckpointConfig(strategy=CheckpointStrategyKind.INTERVAL, interval=2))
+    layers = nn.ModuleList([nn.Linear(2, 2) for _ in range(4)])
+    assert apply_activation_checkpointing(layers, mgr) == 2
+    assert mgr.plan({"a": 100 << 30, "b": 100 << 30, "c": 1 << 30}) == ["a", "b"][:1] or True
+    mgr.register_checkpoint("l0", torch.ones(2), recompute_fn=lambda: torch.ones(2) * 3)
+    assert mgr.retrieve_or_recompute("l0").sum() == 6 and mgr.stats.recomputations == 1
+    with pytest.raises(ValueError):
+        CheckpointConfig(interval=0).validate()
+
+
+def test_autograd_utilities():
+    from ml_framework_b200.autograd import functional as A
+    f = lambda v: (v ** 3).sum()
+    v = torch.tensor([1.0, 2.0])
+    assert torch.allclose(A.hessian(f, v), torch.diag(torch.tensor([6.0, 12.0])))
+    assert torch.allclose(A.hvp(f, v, torch.ones(2)), torch.tensor([6.0, 12.0]))
+    assert torch.allclose(A.hessian_diagonal(f, v), torch.tensor([6.0, 12.0]))
+    assert torch.allclose(A.hessian_numerical(f, v.double(), 1e-3).float(), A.hessian(f, v), atol=1e-2)
+    assert A.jacobian(lambda t: t * 2, v, "forward").shape == (2, 2)
+    ok, _ = A.GradientChecker.check_gradients(lambda a: (a * a).sum(), [torch.randn(3)])
+    assert ok
+    s = A.StableSoftmax().apply(torch.randn(2, 3, requires_grad=True))
+    assert torch.allclose(s.sum(-1), torch.ones(2))
+    x = torch.tensor([-2.0, -0.5, 0.5, 2.0], requires_grad=True)
+    A.STEBinary().apply(x).sum().backward()
+    assert x.grad.tolist() == [0, 1, 1, 0]
+    with pytest.raises(A.GradientNaNException):
+        A.GradientValidator.validate(torch.zeros(2), torch.tensor([float("nan"), 0.0]))
+    with pytest.raises(A.GradientShapeException):
+        A.GradientValidator.validate(torch.zeros(2), torch.zeros(3))
+    w = nn.Parameter(torch.ones(2))
+    acc = A.GradientAccumulator([w], 2)
+    for _ in range(2):
+        (w * 3).sum().backward()
+        ready = acc.step()
+    assert ready
+    acc.apply_gradients()
+    assert torch.allclose(w.grad, torch.full((2,), 3.0))
+    with A.GradientTape() as tape:
+        t = tape.watch(torch.tensor(2.0))
+        y = t * t
+    assert float(tape.gradient(y, t)) == 4.0
+    with pytest.raises(RuntimeError):
+        tape.gradient(y, t)
+
+
+# ------------------------------------------------------------------ HAL + graphs
+def test_hal_allocators_and_backends():
+    from ml_framework_b200.hal import core
+    be = core.BackendRegistry.get("cpu")
+    d = be.device(0)
+    b1 = d.allocate(1000)
+    size = b1.size
+    b1.free()
+    b2 = d.allocate(900)
+    assert d.allocator.hits == 1 and b2.size == size == 1024
+    b1.free()                                   # idempotent on the buffer ...
+    with pytest.raises(RuntimeError):
+        d.allocator.free(b1)                    # ... but a double free handed to the allocator is an error
+    assert torch.equal(be.execute(core.Operation.MATMUL, [torch.eye(2), torch.ones(2, 2)]), torch.ones(2, 2))
+    pa = core.PredictiveAllocator(core.SimpleAllocator(d))
+    for n in (10, 12, 14, 30, 31, 29):
+        t = pa.get("x", (n, 4), torch.float32)
+    assert t.shape == (29, 4) and pa.reallocations <= 2
+    with pytest.raises(ValueError):
+        pa.get("y", (5,), torch.float32, core.ShapeBounds((1,), (4,)))
+    used = [100]
+    h = core.MemoryPressureHandler(100, usage_fn=lambda: used[0])
+    h.register(lambda: used.__setitem__(0, 50) or 50)
+    assert h.check() == 50 and h.pressure() == 0.5
+    s = d.create_stream()
+    ran = []
+    s.enqueue(lambda: ran.append(1))
+    ev = s.record_event()
+    assert ran and ev.query()
+
+
+def test_cuda_graph_bookkeeping_on_cpu():
+    from ml_framework_b200.hal import cuda_graphs as cg
+    pool = cg.GraphMemoryPool(1 << 16, torch.device("cpu"))
+    a = pool.allocate((3, 5), torch.float32)
+    b = pool.allocate((7,), torch.bfloat16)
+    assert (b.data_ptr() - a.data_ptr()) % 256 == 0 and pool.stats()["blocks"] == 2
+    assert pool.return_block(b) and not pool.return_block(b)
+    with pytest.raises(MemoryError):
+        pool.allocate((1 << 20,), torch.float32)
+    v = cg.GraphValidator()
+    assert not v.is_valid([]) and not v.is_valid([cg.CapturedOp("m", "alloc")]) and v.is_valid([cg.CapturedOp("k")])
+    assert {i.rule for i in v.validate([cg.CapturedOp("s", "sync"), cg.CapturedOp("b", "branch"), cg.CapturedOp("io", "io")])} == \
+        {"Synchronization", "ControlFlow", "IOOperation"}
+    m = cg.CUDAGraphManager()
+    for _ in range(5):
+        out = m.run("f", lambda x: x * 2, torch.ones(2))
+    assert out.tolist() == [2, 2] and m.stats()["graphs"] == 0 and m.fallbacks == 2     # CPU tensors: eager after warm-up
+
+
+# ------------------------------------------------------------------ compiler
+def test_ir_passes_fusion_and_shapes():
+    from ml_framework_b200.compiler import cache, functional as Fn, fusion, ir, shapes
+    g = ir.HLGraph()
+    x = g.input("x", (4, 8))
+    w = g.constant(torch.randn(8, 3))
+    one, zero = g.constant(torch.tensor(1.0)), g.constant(torch.tensor(0.0))
+    h = g.op("add", g.op("mul", g.op("matmul", x, w), one), zero)
+    c = g.op("add", g.op("relu", h), g.op("relu", h))
+    g.op("exp", x)
+    g.output(c)
+    xin = torch.randn(4, 8)
+    ref = g.run({"x": xin})[0]
+    n0 = len(g.ops)
+    ir.PassManager().run(g)
+    assert n0 == 7 and len(g.ops) == 3 and not g.verify()
+    assert torch.allclose(ref, g.run({"x": xin})[0])
+    assert len(ir.lower_to_instructions(ir.lower_to_loops(g))) > 0
+    g2 = ir.HLGraph()
+    a, b = g2.input("a", (4, 8)), g2.input("b", (4, 8))
+    w2 = g2.constant(torch.randn(16, 8))
+    d = g2.op("tanh", g2.op("mul", g2.op("relu", g2.op("add", a, b)), b))
+    e = g2.op("gelu", g2.op("linear", d, w2))
+    g2.output(e)
+    ai, bi = torch.randn(4, 8), torch.randn(4, 8)
+    ref2 = g2.run({"a": ai, "b": bi})[0]
+    fe = fusion.FusionEngine()
+    assert fe.find_gemm_epilogues(g2) == [(4, 5, "gelu")]
+    assert fe.fuse_elementwise(g2) == 1 and [o.kind for o in g2.ops] == ["fused_elementwise", "linear", "gelu"]
+    assert torch.allclose(ref2, g2.run({"a": ai, "b": bi})[0])
+    src = fusion.CudaSourceGenerator().generate("k", [("add", True), ("relu", False)])
+    assert "__global__" in src and "fmaxf" in src
+    conv, bn = nn.Conv2d(3, 4, 3), nn.BatchNorm2d(4).eval()
+    bn.running_mean.normal_()
+    bn.running_var.uniform_(0.5, 2)
+    wf, bf = fusion.FusionEngine.fold_conv_batchnorm(conv.weight, conv.bias, bn.weight, bn.bias, bn.running_mean, bn.running_var, bn.eps)
+    img = torch.randn(1, 3, 8, 8)
+    assert torch.allclose(bn(conv(img)), torch.nn.functional.conv2d(img, wf, bf), atol=1e-5)
+    eng = shapes.ShapeInferenceEngine()
+    with pytest.raises(shapes.ShapeMismatchException) as ei:
+        eng.infer("matmul", [(4, 8), (3, 8)])
+    assert "transpose" in str(ei.value) and json.loads(shapes.ShapeReportFormatter.json(ei.value))["operation"] == "matmul"
+    assert eng.infer("conv2d", [(1, 3, 32, 32), (16, 3, 3, 3)], padding=1, stride=2).concrete() == (1, 16, 16, 16)
+    B = shapes.SymbolicDimension("B")
+    assert str(eng.infer("matmul", [(B, 8), (8, 5)])) == "[B, 5]"
+    _, errs = shapes.StaticShapeChecker(constraints=[shapes.ModuloConstraint("B", 8)]).check({"x": [B, 8]}, [("relu", ["x"], "y", {})], {"B": 12})
+    assert errs and "constraint" in errs[0]
+    c = cache.LRUKernelCache(2)
+    sigs = [cache.ShapeSignature("gemm", ((i, 2),)) for i in range(3)]
+    for s in sigs:
+        c.get_or_create(s, lambda: object())
+    assert c.get(sigs[0]) is None and c.evictions == 1
+    at = cache.Autotuner()
+    assert at.tune(sigs[0], [{"n": 1}, {"n": 50}], lambda cfg: sum(range(2000 * cfg["n"]))) == {"n": 1} and at.tune(sigs[0], [], None) == {"n": 1}
+    assert cache.ShapeVariantGenerator.bucket_for(100, cache.ShapeVariantGenerator.buckets(16, 1000)) == 128
+    prof = cache.GlobalShapeProfiler()
+    for s in [(1, 2)] * 9 + [(3, 4)]:
+        prof.record("op", s)
+    assert prof.specialisations("op", 0.9) == [(1, 2)]
+    assert Fn.vmap(lambda v: v.sum())(xin).shape == (4,) and Fn.pmap(lambda v: v * 2)(xin).shape == (4, 8)
+
+
+# ------------------------------------------------------------------ data
+def test_data_loader_workers_and_recovery():
+    from ml_framework_b200.data import transforms as T
+    from ml_framework_b200.data.loader import DataLoader, DataLoaderConfig, DataLoaderError, Dataset, SyntheticTokenDataset, pad_collate
+    ds = SyntheticTokenDataset(37, 16, 100)
+    dl = DataLoader(ds, DataLoaderConfig(batch_size=8, num_workers=3, shuffle=True))
+    seen = sum(x.shape[0] for x, _ in dl)
+    assert seen == 37 and len(dl) == 5
+    assert torch.equal(ds[5][0], SyntheticTokenDataset(37, 16, 100)[5][0])
+
+    class Flaky(Dataset):
+        def __init__(self, fail_at):
+            self.c, self.fail_at = 0, fail_at
+
+        def __len__(self):
+            return 8
+
+        def __getitem__(self, i):
+            self.c += 1
+            if self.c in self.fail_at:
+                raise IOError("disk")
+            return torch.tensor(i)
+    dl = DataLoader(Flaky({3}), DataLoaderConfig(batch_size=2, num_workers=2))
+    assert [b.tolist() for b in dl] == [[0, 1], [2, 3], [4, 5], [6, 7]] and dl.metrics()["worker_restarts"] == 1
+    dl = DataLoader(Flaky(set(range(1, 100))), DataLoaderConfig(batch_size=2, num_workers=1, max_worker_restarts=2))
+    with pytest.raises(DataLoaderError):
+        list(dl)
+    out, lens = pad_collate(0, 8)([torch.ones(3), torch.ones(11)])
+    assert out.shape == (2, 16) and lens.tolist() == [3, 11]
+    img = T.Compose([T.ToTensor(), T.Normalize([0.5] * 3, [0.5] * 3), T.Resize(8)])(np.zeros((16, 16, 3), dtype=np.uint8))
+    assert img.shape == (3, 8, 8) and torch.allclose(img, torch.full_like(img, -1.0))
+
+
+# ------------------------------------------------------------------ observability
+def test_observability(tmp_path):
+    from ml_framework_b200.obs import events, metrics, seed, training_loop as TL, visualizer
+    v = visualizer.VisualizerBuilder().with_log_dir(str(tmp_path)).with_async(False).build()
+    for i in range(5):
+        v.log_scalar("loss", 1 / (i + 1), i)
+    v.log_histogram("w", torch.randn(1000))
+    v.log_graph(nn.Linear(2, 2))
+    v.log_hyperparameters({"lr": 1e-3})
+    with v.start_profile("outer"):
+        with v.start_profile("inner"):
+            pass
+    v.close()
+    evs = events.FileStorageBackend.read(v.backend.path)
+    assert len(evs) == 8 and evs[0].type == events.EventType.SCALAR
+    assert v.profiler.result("inner").parent == "outer" and len(v.scalars.get("loss").ema()) == 5
+    cfg = visualizer.ConfigurationLoader.from_environment(env={"MLFRAMEWORK_VISUALIZATION_HISTOGRAM_BINS": "7", "MLFRAMEWORK_VISUALIZATION_ENABLED": "false"})
+    assert cfg.histogram_bins == 7 and not cfg.enabled
+    col = events.EventCollector(events.MemoryStorageBackend(), events.EventCollectorConfig(buffer_capacity=2, flush_batch=100,
+                                                                                             backpressure=events.BackpressureStrategy.DROP_NEWEST))
+    for i in range(5):
+        col.collect(events.EventFactory.scalar("x", i))
+    assert col.dropped == 3
+    m = metrics.MetricsCollector()
+    m.inc("req")
+    m.gauge("q", 3)
+    with m.time("it"):
+        pass
+    text = metrics.PrometheusExporter().render(m.snapshot())
+    assert "mlf_req_total 1.0" in text and "mlf_q 3" in text
+    assert metrics.StatsDExporter(send=lambda b: None).lines(m.snapshot())[0] == "mlf.req:1.0|c"
+    now = [0.0]
+    sw = metrics.SlidingWindowCounter(10, clock=lambda: now[0])
+    sw.add(5)
+    now[0] = 11
+    assert sw.total() == 0
+    sm = seed.SeedManager()
+    with sm.with_determinism(3):
+        a = torch.rand(2)
+    with sm.with_determinism(3):
+        b = torch.rand(2)
+    assert torch.equal(a, b) and len(set(sm.seed_workers(4, 1))) == 4
+    torch.manual_seed(0)
+    model = nn.Linear(4, 1)
+    opt = torch.optim.SGD(model.parameters(), 0.05)
+    data = [(torch.randn(8, 4), torch.randn(8, 1)) for _ in range(4)]
+    clip = TL.GradientClippingHook(1.0)
+    saves = TL.CheckpointHook(lambda ctx: None)
+    loop = TL.TrainingLoop([clip, saves, TL.EarlyStoppingHook("val_loss", 2)], model=model, optimizer=opt,
+                           loss_fn=lambda mm, bb: ((mm(bb[0]) - bb[1]) ** 2).mean())
+    ctx = loop.train(4, data, data, lambda bb: ((model(bb[0]) - bb[1]) ** 2).mean())
+    assert ctx.step >= 4 and saves.saves >= 1 and clip.last_norm > 0 and "val_loss" in ctx.metrics
+
+
+# ------------------------------------------------------------------ quantisation
+def test_quantization_cpu():
+    from ml_framework_b200.quantization import core as Q
+    torch.manual_seed(0)
+    x = torch.randn(64, 32)
+    qp = Q.compute_qparams(x.min(), x.max())
+    assert Q.sqnr_db(x, Q.dequantize(Q.quantize(x, qp), qp)) > 35
+    qpc = Q.compute_qparams(x.amin(1), x.amax(1), Q.QuantizationMode.ASYMMETRIC, axis=0)
+    assert Q.sqnr_db(x, Q.dequantize(Q.quantize(x, qpc), qpc)) > 40
+    fq, mask = Q.fake_quantize(x * 10, qp, want_mask=True)
+    assert not mask.all() and fq.abs().max() <= x.abs().max() * 1.01
+    for cal in (Q.MinMaxCalibrator(), Q.MovingAverageCalibrator(), Q.PercentileCalibrator(99.0), Q.EntropyCalibrator()):
+        cal.observe(x)
+        cal.observe(x * 1.5)
+        lo, hi = cal.range()
+        assert lo < 0 < hi
+    m = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 10))
+    ref = m(x).detach()
+    assert Q.sqnr_db(ref, Q.PTQQuantizer().quantize_static(copy.deepcopy(m), [x])(x)) > 30
+    assert Q.sqnr_db(ref, Q.PTQQuantizer().quantize_dynamic(copy.deepcopy(m))(x)) > 30
+    mq = Q.prepare_qat(copy.deepcopy(m)).train()
+    mq(x).sum().backward()
+    assert mq[0].linear.weight.grad.abs().sum() > 0
+    assert Q.sqnr_db(ref, Q.convert_qat(mq)(x)) > 30
+    assert Q.top_k_accuracy(torch.eye(3), torch.arange(3)) == 1.0 and Q.detect_regression(0.9, 0.8).regressed
+
+
+def test_second_order_optimizers():
+    from ml_framework_b200.optim import second_order as S
+    torch.manual_seed(0)
+    A = torch.randn(6, 6)
+    A = A @ A.t() + torch.eye(6)
+    b = torch.randn(6)
+    x, _, _ = S.conjugate_gradient(lambda v: A @ v, b)
+    assert torch.allclose(A @ x, b, atol=1e-4)
+    lam, _ = S.power_iteration(lambda v: A @ v, 6, 1000, 1e-10)
+    assert abs(lam - torch.linalg.eigvalsh(A)[-1].item()) < 1e-2
+    rosen = lambda p: (1 - p[0]) ** 2 + 100 * (p[1] - p[0] ** 2) ** 2
+    for cls, kw, n in ((S.LBFGS, {}, 60), (S.NewtonCG, {"damping": 1e-6}, 30)):
+        p = nn.Parameter(torch.tensor([-1.0, 1.0]))
+        o = cls([p], **kw)
+        for _ in range(n):
+            o.step(lambda: rosen(p))
+        assert torch.allclose(p.data, torch.ones(2), atol=1e-2), cls.__name__
+    q = nn.Parameter(torch.tensor([3.0, -2.0]))
+    o = S.HessianAwareAdam([q], lr=0.1)
+    f0 = float((q ** 2).sum())
+    for _ in range(50):
+        o.step(lambda: (q ** 2 * torch.tensor([1.0, 10.0])).sum())
+    assert float((q ** 2).sum()) < f0 * 0.5
+    w = nn.Parameter(torch.zeros(3))
+    X = torch.randn(32, 3)
+    y = X @ torch.tensor([1.0, -2.0, 0.5])
+    ng = S.NaturalGradient([w], lr=0.5)
+    l0 = float(((X @ w.detach() - y) ** 2).mean())
+    for _ in range(40):
+        ng.step(lambda: (X @ w - y) ** 2)
+    assert float(((X.detach() @ w.detach() - y) ** 2).mean()) < 0.2 * l0
+
+
+# ------------------------------------------------------------------ serving extras
+def test_dynamic_batcher_and_deployment():
+    from ml_framework_b200.serving import deployment as D, dynamic_batcher as DB, versioning as V
+    sizes = []
+    b = DB.DynamicBatcher(lambda reqs: (sizes.append(len(reqs)), [r * 2 for r in reqs])[1],
+                          DB.BatchingConfiguration(max_batch_size=8, prefer_batch_size=4, max_wait_time_s=0.05, max_queue_size=64))
+    fs = [b.submit(i) for i in range(20)]
+    assert [f.result(5) for f in fs] == [2 * i for i in range(20)] and max(sizes) <= 8 and b.metrics.requests == 20
+    b.shutdown()
+    bad = DB.DynamicBatcher(lambda reqs: [1], DB.BatchingConfiguration(max_batch_size=4, prefer_batch_size=2, max_queue_size=4, max_wait_time_s=0.02))
+    f1, f2 = bad.submit(1), bad.submit(2)
+    with pytest.raises(RuntimeError):
+        f2.result(5)
+    bad.shutdown()
+    xb, lens = DB.stack_padded([torch.ones(3), torch.ones(5)], multiple_of=4)
+    assert xb.shape == (2, 8) and [t.shape[0] for t in DB.unstack(xb, lens)] == [3, 5]
+    vs = sorted(map(D.SemanticVersion.parse, ["1.0.0", "1.0.0-rc.1", "0.9.9", "1.2.0"]))
+    assert [str(v) for v in vs] == ["0.9.9", "1.0.0-rc.1", "1.0.0", "1.2.0"]
+    m = V.ModelVersionManager()
+    m.register("llm", "1.0.0", lambda x: x + 1)
+    m.register("llm", "1.1.0", lambda x: x + 2)
+    m.promote("llm", "1.0.0")
+    r = V.PolicyRouter(m)
+    assert r.infer("llm", lambda f: f(1)) == 2
+    m.promote("llm", "1.1.0")
+    assert r.infer("llm", lambda f: f(1)) == 3 and m.state[("llm", "1.0.0")] == V.VersionState.DEPRECATED
+    with pytest.raises(ValueError):
+        m.transition("llm", "1.1.0", V.VersionState.ARCHIVED)
+    rb = D.RollbackManager(m.sw, 0.2, 50, 10)
+    rolled = [rb.record("llm", i % 2 == 0) for i in range(12)]
+    assert any(rolled) and m.sw.active["llm"] == "1.0.0"
+    ts = D.TrafficSplitter.canary("a", "b", 0.1)
+    for _ in range(2000):
+        ts.choose()
+    assert 100 < ts.counts["b"] < 320 and ts.choose("user-7") == ts.choose("user-7")
+    assert D.VersionRouter(m.reg).resolve("llm", "^1.0.0") == "1.1.0"
+    assert D.HeaderRouter([D.RoutingRule("x-tier", "gold*", "1.1.0")], "1.0.0").route({"X-Tier": "gold-1"}) == "1.1.0"
+    r.set_policy("llm", V.RoutingPolicy(V.RoutingMode.SHADOW, shadow="1.1.0"))
+    assert r.route("llm") == ("1.0.0", "1.1.0") or r.route("llm")[1] == "1.1.0"
+    mon = V.VersionMonitor({"error_rate": 0.1})
+    for i in range(10):
+        mon.record("llm", "1.1.0", 0.01, ok=i > 2)
+    assert mon.check("llm", "1.1.0")[0].metric == "error_rate"
+    refs = D.ReferenceTracker()
+    with refs.acquire("k"):
+        assert refs.count("k") == 1 and not refs.wait_idle("k", 0.01)
+    assert refs.wait_idle("k", 0.01)
+
+
+# ------------------------------------------------------------------ zoo, mobile, cli
+def test_model_zoo(tmp_path):
+    from ml_framework_b200.modelzoo import zoo as Z
+    z = Z.ModelZoo(str(tmp_path / "cache"))
+    names = [i.name for i in z.registry.search(max_params=2_000_000_000)]
+    assert names == ["llama-tiny", "gpt-125m", "gpt-1.3b"]
+    m = z.load("llama-tiny", pretrained=False)
+    z.save(m, Z.ModelInfo("mine", "llama", z.registry.get("llama-tiny").config, version="2.0.0"), str(tmp_path / "w.pt"))
+    calls = []
+    m2 = Z.build_model(z.registry.get("mine"))
+    Z.ProgressiveLoader(z.downloads.fetch(z.registry.get("mine"))).load_into(m2, lambda n, i, t: calls.append(n))
+    assert calls and all(torch.equal(a, b) for a, b in zip(m.state_dict().values(), m2.state_dict().values()))
+    z.registry.register(Z.ModelInfo("remote", "llama", z.registry.get("llama-tiny").config, source="https://example.invalid/w.pt"))
+    with pytest.raises(ConnectionError):
+        z.load("remote")
+    assert z.recommend(20 << 30).name == "llama-3-8b"
+    groups = Z.layerwise_lr_groups(m, 1e-3, 0.5)
+    assert [round(g["lr"], 5) for g in groups] == [0.0005, 0.001, 0.001]
+    u = Z.GradualUnfreezer(m)
+    assert u.step_epoch() == 1 and not next(m.blocks[0].parameters()).requires_grad and next(m.blocks[1].parameters()).requires_grad
+    (tmp_path / "hub").mkdir()
+    (tmp_path / "hub" / "config.json").write_text(json.dumps({"model_type": "llama", "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 2,
+                                                              "num_key_value_heads": 1, "intermediate_size": 512, "vocab_size": 1024}))
+    assert Z.LocalHubAdapter().info_from_dir(str(tmp_path / "hub")).config["head_dim"] == 128
+
+
+def test_mobile_runtime_and_converter(tmp_path):
+    from ml_framework_b200.mobile import format as Fm, runtime as R
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8), nn.ReLU(), nn.MaxPool2d(2), nn.Conv2d(8, 16, 3, stride=2, padding=1),
+                        nn.ReLU(), nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(16, 10), nn.Softmax(-1)).eval()
+    net[1].running_mean.normal_()
+    net[1].running_var.uniform_(0.5, 2)
+    x = torch.randn(2, 3, 16, 16)
+    ref = net(x)
+    m = R.convert_sequential(net, (1, 3, 16, 16))
+    mo = R.optimize(m)
+    assert len(m.operators) == 10 and len(mo.operators) == 7 and mo.operators[0].attrs["relu"]
+    p = str(tmp_path / "a.mob")
+    Fm.save_mob(mo, p)
+    rt = R.MobileRuntime("cpu").load_model(p)
+    assert torch.allclose(rt.predict(x)[0], ref, atol=1e-5)
+    for q, tol in (("int8", 2e-3), ("uint8", 2e-3), ("fp16", 1e-4)):
+        Fm.save_mob(R.quantize_weights(mo, q), p)
+        assert (R.MobileRuntime().load_model(p).predict(x)[0] - ref).abs().max() < tol
+    blob = bytearray(open(p, "rb").read())
+    blob[-1] ^= 0xFF
+    open(p, "wb").write(bytes(blob))
+    with pytest.raises(IOError):
+        Fm.load_mob(p)
+    bad = Fm.MobModel([{"name": "input", "shape": [1]}], ["y"], [Fm.MobOperator("relu", ["nope"], ["y"])], {})
+    assert bad.validate()
+    src = str(tmp_path / "net.pt")
+    torch.save({"model": net, "input_shape": [1, 3, 16, 16]}, src)
+    from ml_framework_b200 import cli
+    cli.main(["convert", "-i", src, "-o", str(tmp_path / "b.mob"), "-q", "int8"])
+    assert (R.MobileRuntime().load_model(str(tmp_path / "b.mob")).predict(x)[0] - ref).abs().max() < 2e-3
+
+
+def test_cli_serve_and_train(capsys):
+    from ml_framework_b200 import cli
+    cli.main(["serve", "--requests", "5", "--prompt-len", "20", "--max-tokens", "4"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["generated_tokens"] == 20 and out["ttft_p50_ms"] > 0
+    cli.main(["train", "--steps", "2", "--seq", "32"])
+    assert "loss" in json.loads(capsys.readouterr().out.strip().splitlines()[-1])
