@@ -310,6 +310,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 using namespace mlf;
 
+MLF_API int mlf_flash_fwd_ws(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
+                             int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
+                             uint64_t stream);
+
+static int g_flash_ws = 1;
+// 1 (default): sequences of at least 256 tokens use the two-tile ping-pong kernel; 0: always the single-tile kernel.
+MLF_API void mlf_set_flash_ws(int on) { g_flash_ws = on; }
+
 // q: [B*S, *] bf16 with Hq heads of 128 starting at q and row pitch ldq (elements); k, v likewise
 // with Hkv heads. out: [B*S, Hq*128] pitch ldo. lse: fp32 [B, Hq, S] or null.
 MLF_API int mlf_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
@@ -317,6 +325,8 @@ MLF_API int mlf_flash_fwd(const void* q, const void* k, const void* v, void* out
                           uint64_t stream) {
   MLF_REQUIRE(B > 0 && S > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "flash_fwd: bad shape");
   MLF_REQUIRE(ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "flash_fwd: out must be 16-byte aligned");
+  if (g_flash_ws && S >= 256 && scale > 0.f)
+    return mlf_flash_fwd_ws(q, k, v, out, lse, B, S, Hq, Hkv, ldq, ldk, ldv, ldo, scale, causal, stream);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   CUtensorMap tq, tk, tv;
   int rc;

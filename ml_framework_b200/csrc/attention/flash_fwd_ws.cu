@@ -1,0 +1,367 @@
+// Self-attention forward, head_dim 128: two 128-row query tiles per CTA, ping-ponged.
+//
+// One CTA = 256 query rows of one (batch, head) as two tiles of 128. 320 threads:
+//   warp 0        TMA producer: both Q tiles once, then K and V tiles of 128 keys through 2-stage rings
+//   warp 1        MMA issuer (one thread). Per key tile j and query tile t:
+//                   S_t = Q_t K_j^T   (M128 N128 K128, operands in shared memory)  -> TMEM S_t
+//                   O_t += P_t V_j    (M128 N128 K128, P read from TENSOR MEMORY, V from shared memory)
+//                 issued in the order PV_0(j), S_0(j+1), PV_1(j), S_1(j+1) so that the tensor pipe
+//                 works on one tile while the other tile's softmax runs
+//   warps 2..5    softmax of tile 0: one query row per thread; reads S_0 from TMEM into registers,
+//                 running max / sum in the log2 domain, writes P_0 as packed bf16 back over S_0
+//   warps 6..9    softmax of tile 1
+// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each; P_t occupies the first 64
+// columns of S_t. The MMAs of one thread execute in issue order, so S_t(j+1) overwrites P_t(j)
+// only after PV_t(j) has read it. O is rescaled lazily: only when a row's maximum has grown by
+// more than 2^8 since the value P and O are expressed against (then O_t is read, scaled and
+// written back by its softmax warps, after PV_t(j-1) has completed).
+// Per SM and key tile: 4 x 128x128x128 of tensor work against 2 x 16384 exponentials.
+//
+// Math reference: StandardPagedAttentionKernel.ComputePagedAttention
+// (src/MLFramework/Inference/PagedAttention/Kernels/StandardPagedAttentionKernel.cs:21-84;
+// causal rule :219-255).
+#include <float.h>
+
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+#include "../mlf_api.h"
+
+namespace mlf {
+
+int cached_tmap_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                     uint32_t bi, uint32_t bo);
+
+constexpr int W_BQ = 128;                       // rows per query tile
+constexpr int W_BKV = 128;
+constexpr int W_D = 128;
+constexpr int W_THREADS = 320;
+constexpr int W_TILE_BYTES = 128 * 128 * 2;     // 32 KB: two 64-column blocks of 16 KB
+constexpr int W_STAGES = 2;
+constexpr int W_SMEM = 2 * W_TILE_BYTES + 2 * W_STAGES * W_TILE_BYTES + 256;
+constexpr int W_TMEM_COLS = 512;
+
+struct FlashWsParams {
+  __nv_bfloat16* out;
+  float* lse;
+  long long ldo;
+  int B, S, Hq, Hkv;
+  int causal;
+  float scale_log2;
+  int* err;
+};
+
+__global__ void __launch_bounds__(W_THREADS, 1)
+flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const FlashWsParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sQ = sbase;                                  // 2 tiles
+  const uint32_t sK = sQ + 2 * W_TILE_BYTES;                  // W_STAGES tiles
+  const uint32_t sV = sK + W_STAGES * W_TILE_BYTES;           // W_STAGES tiles
+  const uint32_t bars = sV + W_STAGES * W_TILE_BYTES;
+  // barriers: q_full[2] k_full[2] v_full[2] k_empty[2] v_empty[2] s_full[2] p_full[2] pv_done[2]
+  auto q_full = [&](int t) { return bars + 8u * t; };
+  auto k_full = [&](int s) { return bars + 8u * (2 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (4 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (6 + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (8 + s); };
+  auto s_full = [&](int t) { return bars + 8u * (10 + t); };
+  auto p_full = [&](int t) { return bars + 8u * (12 + t); };
+  auto pv_done = [&](int t) { return bars + 8u * (14 + t); };
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + (bars - sbase) + 8 * 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_pairs = (p.S + 2 * W_BQ - 1) / (2 * W_BQ);
+  const int pair = n_pairs - 1 - (int)blockIdx.x;             // longest rows first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int q0 = pair * 2 * W_BQ;
+  const long long row_base = (long long)b * p.S;
+  // key tiles each query tile needs
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qs = q0 + t * W_BQ;
+    int n = (p.S + W_BKV - 1) / W_BKV;
+    if (p.causal) n = min(n, (qs + W_BQ + W_BKV - 1) / W_BKV);
+    n_t[t] = qs < p.S ? n : 0;
+  }
+  const int n_kv = max(n_t[0], n_t[1]);
+
+  if ((sbase & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_INDEX);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full(i), 1);
+      mbar_init(k_full(i), 1);
+      mbar_init(v_full(i), 1);
+      mbar_init(k_empty(i), 1);
+      mbar_init(v_empty(i), 1);
+      mbar_init(s_full(i), 1);
+      mbar_init(p_full(i), 128);
+      mbar_init(pv_done(i), 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), W_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  auto tS = [&](int t) { return tmem_base + 128u * t; };
+  auto tO = [&](int t) { return tmem_base + 256u + 128u * t; };
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      for (int t = 0; t < 2; ++t) {
+        mbar_expect_tx(q_full(t), W_TILE_BYTES);
+        const int qrow = (int)(row_base + q0 + t * W_BQ);
+        tma_load_2d(sQ + t * W_TILE_BYTES, &tmQ, h * W_D, qrow, q_full(t));
+        tma_load_2d(sQ + t * W_TILE_BYTES + W_TILE_BYTES / 2, &tmQ, h * W_D + 64, qrow, q_full(t));
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int krow = (int)(row_base + j * W_BKV);
+        if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        mbar_expect_tx(k_full(s), W_TILE_BYTES);
+        tma_load_2d(sK + s * W_TILE_BYTES, &tmK, hkv * W_D, krow, k_full(s));
+        tma_load_2d(sK + s * W_TILE_BYTES + W_TILE_BYTES / 2, &tmK, hkv * W_D + 64, krow, k_full(s));
+        if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+        mbar_expect_tx(v_full(s), W_TILE_BYTES);
+        tma_load_2d(sV + s * W_TILE_BYTES, &tmV, hkv * W_D, krow, v_full(s));
+        tma_load_2d(sV + s * W_TILE_BYTES + W_TILE_BYTES / 2, &tmV, hkv * W_D + 64, krow, v_full(s));
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, W_BKV, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(128, W_D, 0, 1);
+      auto issue_s = [&](int t, int j) {
+        const uint32_t q = sQ + t * W_TILE_BYTES, k = sK + (j & 1) * W_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < W_D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (W_TILE_BYTES / 2) + (kk & 3) * 32;
+          umma_bf16_ss(tS(t), make_smem_desc_sw128(q + off, 16, 1024), make_smem_desc_sw128(k + off, 16, 1024), idesc_s, kk != 0);
+        }
+        umma_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, int j) {
+        const uint32_t v = sV + (j & 1) * W_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < W_BKV / 16; ++kk)
+          umma_bf16_ts(tO(t), tS(t) + 8u * kk, make_smem_desc_sw128(v + kk * 2048, W_TILE_BYTES / 2, 1024), idesc_pv, (j | kk) != 0);
+        umma_commit(pv_done(t));
+      };
+      bool ok = true;
+      // prologue: S_0(0), S_1(0)
+      if (n_kv > 0) {
+        ok = mbar_wait(k_full(0), 0, abort_flag, p.err, ERR_WAIT_ATTN);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (n_t[t] == 0) continue;
+          ok = mbar_wait(q_full(t), 0, abort_flag, p.err, ERR_WAIT_ATTN);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s(t, 0);
+        }
+        if (ok) umma_commit(k_empty(0));          // K_0 consumed by both tiles' S
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        bool k_next_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < n_t[t]) {
+            if (!mbar_wait(p_full(t), j & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+            if (!mbar_wait(v_full(s), ph, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+            tc_fence_after_sync();
+            issue_pv(t, j);
+          }
+          if (j + 1 < n_t[t]) {
+            if (!k_next_ready) {
+              if (!mbar_wait(k_full((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+              k_next_ready = true;
+              tc_fence_after_sync();
+            }
+            issue_s(t, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit(v_empty(s));                               // V_j consumed by both tiles' PV
+        if (j + 1 < n_kv) umma_commit(k_empty((j + 1) & 1));   // K_{j+1} consumed by both tiles' S
+      }
+    }
+  } else {
+    // ===================== softmax warpgroups =====================
+    const int t = (warp - 2) >> 2;            // query tile of this warpgroup
+    const int q = warp & 3;                   // TMEM lane quarter this warp may access
+    const int r = q * 32 + lane;
+    const int qi = q0 + t * W_BQ + r;
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const int n_mine = n_t[t];
+    float m_used = 0.f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_mine; ++j) {
+      if (!mbar_wait_warp(s_full(t), j & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = j * W_BKV;
+      const bool need_mask = (p.causal && k0 + W_BKV - 1 > q0 + t * W_BQ) || (k0 + W_BKV > p.S);
+      uint32_t sv[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS(t) + 32 * c + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
+      tmem_wait_ld();
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const int kj = k0 + i;
+          float v = __uint_as_float(sv[i]);
+          if (kj >= p.S || (p.causal && kj > qi)) v = -INFINITY;
+          sv[i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          m0 = fmaxf(m0, __uint_as_float(sv[i]));
+          m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
+          m2 = fmaxf(m2, __uint_as_float(sv[i + 2]));
+          m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      }
+      mx *= p.scale_log2;                      // scale > 0: max commutes with the scaling
+      if (j == 0) {
+        m_used = mx == -INFINITY ? 0.f : mx;
+      } else {
+        const bool grow = mx > m_used + 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          if (!mbar_wait_warp(pv_done(t), (j - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+          tc_fence_after_sync();
+          const float f = grow ? exp2f(m_used - mx) : 1.f;
+#pragma unroll
+          for (int c = 0; c < W_D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tO(t) + c * 32 + lane_off, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st_32x32b_x32(tO(t) + c * 32 + lane_off, o);
+          }
+          l *= f;
+          if (grow) m_used = mx;
+        }
+      }
+      // P = exp2(S * c - m_used), packed bf16 pairs, back into the first 64 columns of S_t
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[64 * c + 2 * i]), p.scale_log2, -m_used));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[64 * c + 2 * i + 1]), p.scale_log2, -m_used));
+          rs0 += p0;
+          rs1 += p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x32(tS(t) + 32 * c + lane_off, pk);
+      }
+      l += rs0 + rs1;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(p_full(t));
+    }
+    if (ok && n_mine > 0) ok = mbar_wait_warp(pv_done(t), (n_mine - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN);
+    if (ok && n_mine > 0) {
+      tc_fence_after_sync();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = qi < p.S;
+      __nv_bfloat16* orow = p.out + (row_base + qi) * p.ldo + (long long)h * W_D;
+#pragma unroll
+      for (int c = 0; c < W_D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tO(t) + c * 32 + lane_off, o);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+            reinterpret_cast<uint4*>(orow + 32 * c)[v] = w;
+          }
+        }
+      }
+      if (row_ok && p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
+    }
+    tc_fence_before_sync();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, W_TMEM_COLS);
+  }
+}
+
+}  // namespace mlf
+
+using namespace mlf;
+
+// Same arguments as mlf_flash_fwd.
+MLF_API int mlf_flash_fwd_ws(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
+                             int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
+                             uint64_t stream) {
+  MLF_REQUIRE(B > 0 && S > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "flash_fwd: bad shape");
+  MLF_REQUIRE(scale > 0.f, "flash_fwd: softmax scale must be positive");
+  MLF_REQUIRE(ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "flash_fwd: out must be 16-byte aligned");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tk, tv;
+  int rc;
+  const uint64_t rows = (uint64_t)B * S;
+  if ((rc = cached_tmap_bf16(&tq, q, (uint64_t)Hq * W_D, rows, ldq, 64, W_BQ))) return rc;
+  if ((rc = cached_tmap_bf16(&tk, k, (uint64_t)Hkv * W_D, rows, ldk, 64, W_BKV))) return rc;
+  if ((rc = cached_tmap_bf16(&tv, v, (uint64_t)Hkv * W_D, rows, ldv, 64, W_BKV))) return rc;
+  FlashWsParams p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.ldo = ldo;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = device_status_word();
+  MLF_REQUIRE(p.err != nullptr, "no device status word");
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM));
+    attr_set[dev & 63] = true;
+  }
+  dim3 grid((S + 2 * W_BQ - 1) / (2 * W_BQ), Hq, B);
+  flash_fwd_ws_kernel<<<grid, W_THREADS, W_SMEM, st>>>(tq, tk, tv, p);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(CT * CT) conv2d_kernel(float* __restrict__ out
   }
 }
 
-// mode 0 = max, 1 = average (count includes padding = 0: divide by the window's in-bounds size)
+// mode 0 = max, 1 = average over the in-bounds part of the window, 2 = average over the full k x k window (padding counts as zeros)
 __global__ void __launch_bounds__(256) pool2d_kernel(float* __restrict__ out, const float* __restrict__ in, int NC, int H, int W, int OH,
                                                      int OW, int k, int stride, int pad, int mode) {
   const long long total = (long long)NC * OH * OW;
@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(256) pool2d_kernel(float* __restrict__ out, co
         ++cnt;
       }
     }
-    out[i] = mode == 0 ? m : (cnt ? s / cnt : 0.f);
+    out[i] = mode == 0 ? m : (mode == 1 ? (cnt ? s / cnt : 0.f) : s / (float)(k * k));
   }
 }
 

@@ -91,6 +91,8 @@ class MobileRuntime:
         a = op.attrs
         k = a.get("kernel", 2)
         st, pd = a.get("stride", k), a.get("padding", 0)
+        if mode == 1 and a.get("count_include_pad", False):
+            mode = 2
         if self.native:
             from .. import _lib
             N, Cc, H, W = x.shape
@@ -98,7 +100,7 @@ class MobileRuntime:
             out = self.pool.get((N, Cc, OH, OW))
             _lib.check(_lib.get().mlf_pool2d_f32(_p(out), _p(x.contiguous()), N * Cc, H, W, k, st, pd, mode, C.c_uint64(_lib.stream_handle())), "mlf_pool2d_f32")
             return out
-        return F.max_pool2d(x, k, st, pd) if mode == 0 else F.avg_pool2d(x, k, st, pd, count_include_pad=False)
+        return F.max_pool2d(x, k, st, pd) if mode == 0 else F.avg_pool2d(x, k, st, pd, count_include_pad=(mode == 2))
 
     def _bn(self, x, op):
         g, b, m, v = (self.weights[n] for n in op.inputs[1:5])
@@ -234,7 +236,7 @@ def convert_sequential(model: nn.Module, input_shape: Sequence[int], name: str =
             k = m.kernel_size if isinstance(m.kernel_size, int) else m.kernel_size[0]
             s = m.stride if isinstance(m.stride, int) else m.stride[0]
             pd = m.padding if isinstance(m.padding, int) else m.padding[0]
-            ops.append(MobOperator("avg_pool2d", [cur], [out], {"kernel": k, "stride": s, "padding": pd}))
+            ops.append(MobOperator("avg_pool2d", [cur], [out], {"kernel": k, "stride": s, "padding": pd, "count_include_pad": bool(m.count_include_pad)}))
         elif isinstance(m, nn.AdaptiveAvgPool2d): ops.append(MobOperator("global_avg_pool", [cur], [out]))
         elif isinstance(m, nn.Flatten): ops.append(MobOperator("flatten", [cur], [out]))
         elif isinstance(m, nn.Softmax): ops.append(MobOperator("softmax", [cur], [out], {"dim": -1}))

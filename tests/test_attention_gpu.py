@@ -28,6 +28,29 @@ def test_flash_fwd(B, S, Hq, Hkv, causal):
     assert (lse - ref_lse).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("ws", [0, 1])
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal,amp", [(2, 256, 2, 2, True, 1.0), (1, 384, 2, 1, False, 1.0), (1, 320, 4, 2, True, 1.0),
+                                                  (1, 2048, 4, 2, True, 1.0), (1, 1024, 2, 2, True, 4.0), (1, 1000, 2, 2, False, 4.0)])
+def test_flash_fwd_kernel_variants(ws, B, S, Hq, Hkv, causal, amp):
+    """Both forward kernels (single tile; two tiles ping-ponged with P in tensor memory) on the same inputs.
+    ``amp`` scales Q so that row maxima grow quickly along the keys and the lazy rescale of O runs."""
+    from ml_framework_b200 import _lib
+    torch.manual_seed(2)
+    D = 128
+    q = (torch.randn(B * S, Hq, D, device="cuda") * amp).to(torch.bfloat16)
+    k = torch.randn(B * S, Hkv, D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B * S, Hkv, D, device="cuda").to(torch.bfloat16)
+    _lib.get().mlf_set_flash_ws(ws)
+    try:
+        out, lse = native.flash_fwd(q, k, v, B, S, causal=causal)
+        torch.cuda.synchronize()
+    finally:
+        _lib.get().mlf_set_flash_ws(1)
+    ref, ref_lse = attention_ref(q.reshape(B, S, Hq, D), k.reshape(B, S, Hkv, D), v.reshape(B, S, Hkv, D), causal=causal)
+    assert _rel(out.view(B, S, Hq, D), ref) < 2e-2
+    assert (lse - ref_lse).abs().max().item() < 2e-2
+
+
 @pytest.mark.parametrize("B,S,Hq,Hkv,causal", [(1, 128, 1, 1, True), (2, 256, 4, 4, True), (1, 320, 4, 2, True),
                                               (1, 200, 2, 2, False)])
 def test_flash_bwd(B, S, Hq, Hkv, causal):
