@@ -1,15 +1,16 @@
 // Self-attention forward, head_dim 128: two 128-row query tiles per CTA, ping-ponged.
 //
-// One CTA = 256 query rows of one (batch, head) as two tiles of 128. 320 threads:
+// One CTA = 256 query rows of one (batch, head) as two tiles of 128. 384 threads in three warpgroups;
+// the control warpgroup hands most of its registers to the softmax warpgroups (setmaxnreg):
 //   warp 0        TMA producer: both Q tiles once, then K and V tiles of 128 keys through 2-stage rings
 //   warp 1        MMA issuer (one thread). Per key tile j and query tile t:
 //                   S_t = Q_t K_j^T   (M128 N128 K128, operands in shared memory)  -> TMEM S_t
 //                   O_t += P_t V_j    (M128 N128 K128, P read from TENSOR MEMORY, V from shared memory)
 //                 issued in the order PV_0(j), S_0(j+1), PV_1(j), S_1(j+1) so that the tensor pipe
 //                 works on one tile while the other tile's softmax runs
-//   warps 2..5    softmax of tile 0: one query row per thread; reads S_0 from TMEM into registers,
+//   warps 4..7    softmax of tile 0: one query row per thread; reads S_0 from TMEM into registers,
 //                 running max / sum in the log2 domain, writes P_0 as packed bf16 back over S_0
-//   warps 6..9    softmax of tile 1
+//   warps 8..11   softmax of tile 1
 // TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each; P_t occupies the first 64
 // columns of S_t. The MMAs of one thread execute in issue order, so S_t(j+1) overwrites P_t(j)
 // only after PV_t(j) has read it. O is rescaled lazily: only when a row's maximum has grown by
@@ -34,7 +35,7 @@ int cached_tmap_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_
 constexpr int W_BQ = 128;                       // rows per query tile
 constexpr int W_BKV = 128;
 constexpr int W_D = 128;
-constexpr int W_THREADS = 320;
+constexpr int W_THREADS = 384;   // warps 0..3 control (TMA, MMA, two idle), 4..7 softmax of tile 0, 8..11 softmax of tile 1
 constexpr int W_TILE_BYTES = 128 * 128 * 2;     // 32 KB: two 64-column blocks of 16 KB
 constexpr int W_STAGES = 2;
 constexpr int W_SMEM = 2 * W_TILE_BYTES + 2 * W_STAGES * W_TILE_BYTES + 256;
@@ -74,9 +75,11 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_pairs = (p.S + 2 * W_BQ - 1) / (2 * W_BQ);
-  const int pair = n_pairs - 1 - (int)blockIdx.x;             // longest rows first
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  // 1-D grid ordered by work: all (batch, head) of the longest query pair first, the shortest last
+  const int hb = p.Hq * p.B;
+  const int pair = p.causal ? n_pairs - 1 - (int)blockIdx.x / hb : (int)blockIdx.x / hb;
+  const int h = ((int)blockIdx.x % hb) % p.Hq;
+  const int b = ((int)blockIdx.x % hb) / p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = pair * 2 * W_BQ;
   const long long row_base = (long long)b * p.S;
@@ -120,6 +123,8 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto tS = [&](int t) { return tmem_base + 128u * t; };
   auto tO = [&](int t) { return tmem_base + 256u + 128u * t; };
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
@@ -202,9 +207,11 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (j + 1 < n_kv) umma_commit(k_empty((j + 1) & 1));   // K_{j+1} consumed by both tiles' S
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ===================== softmax warpgroups =====================
-    const int t = (warp - 2) >> 2;            // query tile of this warpgroup
+    const int t = (warp - 4) >> 2;            // query tile of this warpgroup
     const int q = warp & 3;                   // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;
     const int qi = q0 + t * W_BQ + r;
@@ -221,64 +228,74 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS(t) + 32 * c + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
       tmem_wait_ld();
-      float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
           const int kj = k0 + i;
-          float v = __uint_as_float(sv[i]);
-          if (kj >= p.S || (p.causal && kj > qi)) v = -INFINITY;
-          sv[i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          if (kj >= p.S || (p.causal && kj > qi)) sv[i] = __float_as_uint(-INFINITY);
         }
-      } else {
+      }
+      if (j == 0) {
+        // first tile: the reference maximum comes from a pass of its own
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 128; i += 4) {
-          m0 = fmaxf(m0, __uint_as_float(sv[i]));
-          m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
-          m2 = fmaxf(m2, __uint_as_float(sv[i + 2]));
-          m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
+        for (int i = 0; i < 128; i += 8) {
+          m0 = fmax3(m0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+          m2 = fmax3(m2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+          m3 = fmax3(m3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
         }
-        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      }
-      mx *= p.scale_log2;                      // scale > 0: max commutes with the scaling
-      if (j == 0) {
+        const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2;   // scale > 0: max commutes with the scaling
         m_used = mx == -INFINITY ? 0.f : mx;
-      } else {
-        const bool grow = mx > m_used + 8.f;
-        if (__any_sync(0xffffffffu, grow)) {
-          if (!mbar_wait_warp(pv_done(t), (j - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
-          tc_fence_after_sync();
-          const float f = grow ? exp2f(m_used - mx) : 1.f;
-#pragma unroll
-          for (int c = 0; c < W_D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(tO(t) + c * 32 + lane_off, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st_32x32b_x32(tO(t) + c * 32 + lane_off, o);
-          }
-          l *= f;
-          if (grow) m_used = mx;
-        }
       }
-      // P = exp2(S * c - m_used), packed bf16 pairs, back into the first 64 columns of S_t
+      // One fused pass: P = exp2(S * c - m_used) against the maximum the row is ALREADY expressed
+      // against, while the tile's own maximum is computed on the side (the maximum runs on the
+      // integer/compare pipe under the shadow of the exponentials). If some row's maximum has
+      // grown by more than 2^8 the pass is repeated once after O, l and m_used have been brought
+      // up to date; S is still in registers. Exponents stay below 2^8 in every accepted pass.
       float rs0 = 0.f, rs1 = 0.f;
+      uint32_t pk[64];
+      float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[32];
+      for (int i = 0; i < 64; ++i) {
+        const float s0 = __uint_as_float(sv[2 * i]), s1 = __uint_as_float(sv[2 * i + 1]);
+        if (i & 1) m1 = fmax3(m1, s0, s1); else m0 = fmax3(m0, s0, s1);
+        const float p0 = exp2f(fmaf(s0, p.scale_log2, -m_used));
+        const float p1 = exp2f(fmaf(s1, p.scale_log2, -m_used));
+        rs0 += p0;
+        rs1 += p1;
+        pk[i] = pack_bf16x2(p0, p1);
+      }
+      const float mx = fmaxf(m0, m1) * p.scale_log2;
+      const bool grow = j > 0 && mx > m_used + 8.f;
+      if (__any_sync(0xffffffffu, grow)) {
+        if (!mbar_wait_warp(pv_done(t), (j - 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+        tc_fence_after_sync();
+        const float f = grow ? exp2f(m_used - mx) : 1.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = exp2f(fmaf(__uint_as_float(sv[64 * c + 2 * i]), p.scale_log2, -m_used));
-          const float p1 = exp2f(fmaf(__uint_as_float(sv[64 * c + 2 * i + 1]), p.scale_log2, -m_used));
+        for (int c = 0; c < W_D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tO(t) + c * 32 + lane_off, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st_32x32b_x32(tO(t) + c * 32 + lane_off, o);
+        }
+        l *= f;
+        if (grow) m_used = mx;
+        rs0 = 0.f;
+        rs1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_used));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_used));
           rs0 += p0;
           rs1 += p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tmem_st_32x32b_x32(tS(t) + 32 * c + lane_off, pk);
       }
+      tmem_st_32x32b_x32(tS(t) + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+      tmem_st_32x32b_x32(tS(t) + 32 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
       l += rs0 + rs1;
       tmem_wait_st();
       tc_fence_before_sync();
@@ -359,7 +376,7 @@ MLF_API int mlf_flash_fwd_ws(const void* q, const void* k, const void* v, void* 
     MLF_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM));
     attr_set[dev & 63] = true;
   }
-  dim3 grid((S + 2 * W_BQ - 1) / (2 * W_BQ), Hq, B);
+  dim3 grid(((S + 2 * W_BQ - 1) / (2 * W_BQ)) * Hq * B);
   flash_fwd_ws_kernel<<<grid, W_THREADS, W_SMEM, st>>>(tq, tk, tv, p);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
