@@ -90,6 +90,8 @@ def get() -> C.CDLL:
             _build.build()
         lib = C.CDLL(str(_LIB_PATH))
         lib.mlf_last_error.restype = C.c_char_p
+        if os.environ.get("MLF_FLASH_BWD_WS") is not None:
+            lib.mlf_set_flash_bwd_ws(int(os.environ["MLF_FLASH_BWD_WS"]))
         if os.environ.get("MLF_FLASH_WS") is not None:
             lib.mlf_set_flash_ws(int(os.environ["MLF_FLASH_WS"]))
         if os.environ.get("MLF_GEMM_2CTA") is not None:

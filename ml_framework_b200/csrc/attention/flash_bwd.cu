@@ -54,8 +54,8 @@ struct FlashBwdParams {
 
 // delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
 __global__ void __launch_bounds__(256)
-attn_delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delta, int B, int S, int H, long long ldo,
-                  long long lddo) {
+attn_delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delta, const float* lse, float* lse2, int B, int S,
+                  int H, long long ldo, long long lddo) {
   const long long total = (long long)B * S * H;
   const int lane = threadIdx.x & 31;
   for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
@@ -71,6 +71,7 @@ attn_delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delt
     if (lane == 0) {
       const long long b = t / S, sidx = t % S;
       delta[(b * H + h) * S + sidx] = s;
+      if (lse2) lse2[(b * H + h) * S + sidx] = lse[(b * H + h) * S + sidx] * 1.4426950408889634f;
     }
   }
 }
@@ -363,9 +364,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 using namespace mlf;
 
-// Bytes of fp32 scratch the caller must provide: dq accumulator [B*S, Hq*128] + delta [B, Hq, S].
+namespace mlf {
+int launch_flash_bwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                        float* dq_accum, void* dk, void* dv, const float* lse2, const float* delta, long long lddk, long long lddv,
+                        int B, int S, int Hq, int Hkv, float scale, int causal, cudaStream_t st);
+}
+
+static int g_flash_bwd_ws = 1;
+// 1 (default): sequences of at least 128 tokens (a multiple of 4) use the 128 x 128 warpgroup kernel; 0: the 128 x 64 kernel.
+MLF_API void mlf_set_flash_bwd_ws(int on) { g_flash_bwd_ws = on; }
+
+// Bytes of fp32 scratch the caller must provide: dq accumulator [B*S, Hq*128] + delta [B, Hq, S] +
+// logsumexp in the log2 domain [B, Hq, S] + 256 floats of slack (the last tile's statistics are
+// fetched as whole 512-byte pieces).
 MLF_API long long mlf_flash_bwd_scratch_bytes(int B, int S, int Hq) {
-  return ((long long)B * S * Hq * FB_D + (long long)B * Hq * S) * 4;
+  return ((long long)B * S * Hq * FB_D + 2 * (long long)B * Hq * S + 256) * 4;
 }
 
 // q/k/v/o/dout: bf16 token-major views (row pitches in elements). dq/dk/dv: bf16 outputs with
@@ -380,6 +393,8 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
   const long long rows = (long long)B * S;
   float* dq_accum = static_cast<float*>(scratch);
   float* delta = dq_accum + rows * Hq * FB_D;
+  float* lse2 = delta + rows * Hq + 128;        // 16-byte aligned when S % 4 == 0; 128 floats of slack after each array
+  const bool use_ws = g_flash_bwd_ws && S >= 128 && S % 4 == 0 && ((reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(lse2)) & 15) == 0;
   MLF_CHECK_CUDA(cudaMemsetAsync(dq_accum, 0, sizeof(float) * rows * Hq * FB_D, st));
   {
     const long long warps = rows * Hq;
@@ -387,12 +402,19 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
     const long long cap = (long long)sm_count() * 8;
     if (grid > cap) grid = cap;
     attn_delta_kernel<<<(int)grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout),
-                                                 delta, B, S, Hq, ldo, lddo);
+                                                 delta, lse, use_ws ? lse2 : nullptr, B, S, Hq, ldo, lddo);
                                                  count_launch();
     MLF_CHECK_CUDA(cudaGetLastError());
   }
   CUtensorMap tq, tk, tv, tdo;
   int rc;
+  if (use_ws) {
+    if ((rc = cached_tmap_bf16(&tq, q, (uint64_t)Hq * FB_D, rows, ldq, 64, 128))) return rc;
+    if ((rc = cached_tmap_bf16(&tk, k, (uint64_t)Hkv * FB_D, rows, ldk, 64, 128))) return rc;
+    if ((rc = cached_tmap_bf16(&tv, v, (uint64_t)Hkv * FB_D, rows, ldv, 64, 128))) return rc;
+    if ((rc = cached_tmap_bf16(&tdo, dout, (uint64_t)Hq * FB_D, rows, lddo, 64, 128))) return rc;
+    if ((rc = launch_flash_bwd_ws(tq, tk, tv, tdo, dq_accum, dk, dv, lse2, delta, lddk, lddv, B, S, Hq, Hkv, scale, causal, st))) return rc;
+  } else {
   if ((rc = cached_tmap_bf16(&tq, q, (uint64_t)Hq * FB_D, rows, ldq, 64, FB_BQ))) return rc;
   if ((rc = cached_tmap_bf16(&tk, k, (uint64_t)Hkv * FB_D, rows, ldk, 64, FB_BKV))) return rc;
   if ((rc = cached_tmap_bf16(&tv, v, (uint64_t)Hkv * FB_D, rows, ldv, 64, FB_BKV))) return rc;
@@ -420,6 +442,7 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
   flash_bwd_kernel<<<grid, FB_THREADS, FB_SMEM, st>>>(tq, tk, tv, tdo, p);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
+  }
   {
     const long long total = rows * (Hq * FB_D / 4);
     long long g = (total + 255) / 256;

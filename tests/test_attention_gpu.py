@@ -51,9 +51,20 @@ def test_flash_fwd_kernel_variants(ws, B, S, Hq, Hkv, causal, amp):
     assert (lse - ref_lse).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("ws", [1, 0])
 @pytest.mark.parametrize("B,S,Hq,Hkv,causal", [(1, 128, 1, 1, True), (2, 256, 4, 4, True), (1, 320, 4, 2, True),
-                                              (1, 200, 2, 2, False)])
-def test_flash_bwd(B, S, Hq, Hkv, causal):
+                                              (1, 200, 2, 2, False), (1, 1024, 4, 2, True), (2, 640, 2, 1, False)])
+def test_flash_bwd(ws, B, S, Hq, Hkv, causal):
+    """Both backward kernels (128 x 64 tiles; 128 x 128 tiles with warpgroup roles) against autograd in fp32."""
+    from ml_framework_b200 import _lib
+    _lib.get().mlf_set_flash_bwd_ws(ws)
+    try:
+        _flash_bwd_case(B, S, Hq, Hkv, causal)
+    finally:
+        _lib.get().mlf_set_flash_bwd_ws(1)
+
+
+def _flash_bwd_case(B, S, Hq, Hkv, causal):
     torch.manual_seed(1)
     D = 128
     q = torch.randn(B * S, Hq, D, device="cuda").to(torch.bfloat16)
