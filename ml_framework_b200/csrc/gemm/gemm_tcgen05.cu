@@ -50,163 +50,6 @@ struct GemmCfg {
 };
 
 // ------------------------------------------------------------------------------------------
-// copy role (gather side)
-// ------------------------------------------------------------------------------------------
-// One thread per copy CTA drives a ring of shared-memory buffers with bulk async copies:
-// peer global -> shared (completion on an mbarrier), then shared -> local global (bulk group).
-// kCopyLookahead loads of kCopyPiece bytes are kept in flight per CTA, which is what it takes
-// to cover NVLink latency at full bandwidth with a handful of CTAs.
-constexpr int kCopyPiece = 16384;
-constexpr int kCopyBufs = 11;
-constexpr int kCopyLookahead = 8;
-
-__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-               ::"l"(gdst), "r"(smem_src), "r"(bytes)
-               : "memory");
-}
-
-struct CopyCursor {
-  int i;            // chunk iteration (rotated order)
-  long long off;    // byte offset inside this CTA's slice of the chunk
-};
-
-struct CopyPiece {
-  const char* src;
-  char* dst;
-  uint32_t bytes;
-  int chunk;
-  bool last_of_chunk;
-  bool valid;
-};
-
-__device__ __forceinline__ void chunk_slice(const GemmKernelParams& p, int n_flags, int first_local, int i,
-                                            int cta, int& c, const char*& src, char*& dst, long long& lo,
-                                            long long& hi) {
-  if (i >= n_flags) {
-    // un-gated extra segment (prefetch for later kernels)
-    const long long* sg = static_cast<const long long*>(p.extra_segs) + 3 * (i - n_flags);
-    c = -1;
-    src = reinterpret_cast<const char*>(sg[0]);
-    dst = reinterpret_cast<char*>(sg[1]);
-    const long long n16e = sg[2] / 16;
-    const long long pere = (n16e + p.n_copy_ctas - 1) / p.n_copy_ctas;
-    lo = min(n16e, pere * cta) * 16;
-    hi = min(n16e, pere * (cta + 1)) * 16;
-    return;
-  }
-  c = first_local + i;
-  if (c >= n_flags) c -= n_flags;
-  const int row0 = c * p.flag_rows;
-  const int rows = min(p.flag_rows, p.total_rows - row0);
-  const int owner = min(row0 / p.rows_per_rank, p.world - 1);
-  src = static_cast<const char*>(p.src[owner]) + (long long)(row0 - owner * p.rows_per_rank) * p.row_bytes;
-  dst = static_cast<char*>(p.gathered) + (long long)row0 * p.row_bytes;
-  const long long n16 = (long long)rows * p.row_bytes / 16;
-  const long long per = (n16 + p.n_copy_ctas - 1) / p.n_copy_ctas;
-  lo = min(n16, per * cta) * 16;
-  hi = min(n16, per * (cta + 1)) * 16;
-}
-
-// Returns the piece at the cursor and advances it. Chunks whose slice is empty for this CTA
-// still yield one zero-byte piece so the chunk's completion counter is bumped.
-__device__ __forceinline__ CopyPiece next_piece(const GemmKernelParams& p, int n_flags, int first_local,
-                                                int cta, CopyCursor& cur) {
-  CopyPiece pc;
-  pc.valid = false;
-  if (cur.i >= n_flags + p.n_extra) return pc;
-  int c;
-  const char* src;
-  char* dst;
-  long long lo, hi;
-  chunk_slice(p, n_flags, first_local, cur.i, cta, c, src, dst, lo, hi);
-  const long long pos = lo + cur.off;
-  const long long remain = hi - pos;
-  pc.valid = true;
-  pc.chunk = c;
-  pc.bytes = (uint32_t)(remain > kCopyPiece ? kCopyPiece : (remain > 0 ? remain : 0));
-  pc.src = src + pos;
-  pc.dst = dst + pos;
-  pc.last_of_chunk = remain <= kCopyPiece;
-  if (pc.last_of_chunk) {
-    cur.i += 1;
-    cur.off = 0;
-  } else {
-    cur.off += kCopyPiece;
-  }
-  return pc;
-}
-
-__device__ void gather_copy_role(const GemmKernelParams& p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar0 = base + kCopyBufs * kCopyPiece;
-  if (threadIdx.x != 0) return;
-  for (int b = 0; b < kCopyBufs; ++b) mbar_init(bar0 + 8u * b, 1);
-  mbar_fence_init();
-  int abort_local = 0;
-  volatile int* abort_flag = &abort_local;
-
-  const int n_flags = p.gather_operand != 0 ? (p.total_rows + p.flag_rows - 1) / p.flag_rows : 0;
-  const int first_local = p.gather_operand != 0 ? (p.rank * p.rows_per_rank) / p.flag_rows : 0;
-  const int cta = blockIdx.x;
-  CopyCursor lc{0, 0}, sc{0, 0};
-  int issued = 0;  // pieces whose load has been issued
-  // prologue: fill the lookahead window
-  for (; issued < kCopyLookahead; ++issued) {
-    CopyPiece pc = next_piece(p, n_flags, first_local, cta, lc);
-    if (!pc.valid) break;
-    const int slot = issued % kCopyBufs;
-    if (pc.bytes) {
-      mbar_expect_tx(bar0 + 8u * slot, pc.bytes);
-      bulk_load(base + slot * kCopyPiece, pc.src, pc.bytes, bar0 + 8u * slot);
-    } else {
-      mbar_arrive(bar0 + 8u * slot);
-    }
-  }
-  for (int i = 0;; ++i) {
-    CopyPiece pc = next_piece(p, n_flags, first_local, cta, sc);
-    if (!pc.valid) break;
-    const int slot = i % kCopyBufs;
-    const uint32_t ph = (i / kCopyBufs) & 1;
-    if (!mbar_wait(bar0 + 8u * slot, ph, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG)) break;
-    if (pc.bytes) bulk_store(pc.dst, base + slot * kCopyPiece, pc.bytes);
-    tma_store_commit();
-    if (pc.last_of_chunk && pc.chunk >= 0) {
-      tma_store_wait_all<0>();
-      fence_proxy_async_all();
-      __threadfence();
-      const uint32_t old = atomicAdd(&p.counters[pc.chunk], 1u);
-      if (old + 1 == (uint32_t)p.n_copy_ctas) {
-        __threadfence();
-        st_release_gpu(&p.flags_ready[pc.chunk], 1u);
-      }
-    }
-    // keep the window full: the slot about to be reused was read by the store issued
-    // (kCopyBufs - kCopyLookahead) iterations ago at the latest.
-    CopyPiece nx = next_piece(p, n_flags, first_local, cta, lc);
-    if (nx.valid) {
-      tma_store_wait_read<kCopyBufs - kCopyLookahead - 1>();
-      const int nslot = issued % kCopyBufs;
-      if (nx.bytes) {
-        mbar_expect_tx(bar0 + 8u * nslot, nx.bytes);
-        bulk_load(base + nslot * kCopyPiece, nx.src, nx.bytes, bar0 + 8u * nslot);
-      } else {
-        mbar_arrive(bar0 + 8u * nslot);
-      }
-      ++issued;
-    }
-  }
-  tma_store_wait_all<0>();
-}
-
-// ------------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------------
 template <int BN>
@@ -489,9 +332,8 @@ MLF_API int mlf_get_gemm_2cta() { return g_use_2cta; }
 
 MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
   MLF_REQUIRE(a != nullptr, "null args");
-  if (a->comm == nullptr && (a->tile_n == 512 ||
-                             (g_use_2cta && a->tile_n == 0 && a->M >= 1024 && a->N >= 1024 &&
-                              (long long)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 64))) {
+  if (a->tile_n == 512 || (g_use_2cta && a->tile_n == 0 && a->M >= 1024 && a->N >= 1024 &&
+                           (long long)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 64)) {
     const int rc2 = mlf_gemm_bf16_2cta(a, stream);
     if (rc2 != -4) return rc2;
   }

@@ -34,7 +34,8 @@ constexpr int T2_STAGE_A = BM * BK * 2;          // 16 KB
 constexpr int T2_STAGE_B = T2_BNH * BK * 2;      // 16 KB
 constexpr int T2_STAGE = T2_STAGE_A + T2_STAGE_B;
 constexpr int T2_STAGES = 6;
-constexpr int T2_SMEM = T2_STAGES * T2_STAGE + 1024 + 256;
+constexpr int T2_STG_BYTES = 128 * 64 * 2;     // epilogue staging: 128 rows x 64 bf16 columns, 128B-swizzled
+constexpr int T2_SMEM = T2_STAGES * T2_STAGE + 1024 /*barriers*/ + 2 * T2_STG_BYTES + 1024 /*align*/;
 constexpr int T2_TMEM_COLS = 512;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -90,7 +91,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const GemmKernelParams p) {
+                         const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmPre,
+                         const GemmKernelParams p, const int tma_epilogue) {
+  // Copy CTAs come in whole clusters (their count is even) and never touch the cluster barrier.
+  if ((int)blockIdx.x < p.n_copy_ctas) {
+    gather_copy_role(p);
+    return;
+  }
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -99,7 +106,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   auto empty_bar = [&](int s) { return bar_base + 8u * (T2_STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T2_STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * T2_STAGES + 2 + a); };
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_al + T2_STAGES * T2_STAGE + 8 * (2 * T2_STAGES + 4));
+  const uint32_t epi_bar = bar_base + 8u * (2 * T2_STAGES + 4);      // the four epilogue warps meet here (128 arrivals)
+  const uint32_t stg_base = bar_base + 1024u;                        // two staging buffers
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_al + T2_STAGES * T2_STAGE + 8 * (2 * T2_STAGES + 5));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -116,6 +125,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 8);
     }
+    mbar_init(epi_bar, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -133,8 +143,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const int pair = blockIdx.x >> 1;
-  const int n_pairs = gridDim.x >> 1;
+  const int pair = ((int)blockIdx.x - p.n_copy_ctas) >> 1;
+  const int n_pairs = ((int)gridDim.x - p.n_copy_ctas) >> 1;
   const int num_tiles = p.tiles_m * p.tiles_n;   // tiles of 256 x 256
   const int num_kb = (p.K + BK - 1) / BK;
 
@@ -145,10 +155,19 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t ph = 0;
       for (int t = pair; t < num_tiles; t += n_pairs) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, 0, 0, tm, tn);
+        tile_coords(t, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
         const int m0 = tm * 256 + (int)rank * BM;
         const int n0 = tn * T2_BN + (int)rank * T2_BNH;
         bool ok = true;
+        if (p.gather_operand != 0) {
+          // this CTA's 128 rows of the gathered operand must have landed
+          const int r0 = p.gather_operand == 1 ? m0 : n0;
+          const int r1 = min(p.total_rows, r0 + 128) - 1;
+          for (int c = r0 / p.flag_rows; c <= r1 / p.flag_rows && ok; ++c)
+            ok = wait_flag_ge_gpu(&p.flags_ready[c], 1u, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
           const uint32_t sa = smem_base + s * T2_STAGE;
@@ -216,18 +235,120 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const bool out_fp32 = (p.flags & MLF_EPI_OUT_FP32) != 0;
     const bool swiglu = (p.flags & MLF_EPI_SWIGLU) != 0;
     const bool dswiglu = (p.flags & MLF_EPI_DSWIGLU) != 0;
+    uint32_t epi_units = 0;
     int it = 0;
     for (int t = pair; t < num_tiles; t += n_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, 0, 0, tm, tn);
+      tile_coords(t, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
       const int m = tm * 256 + (int)rank * BM + q * 32 + lane;
       const int n0 = tn * T2_BN;
       if (!mbar_wait_warp(tfull_bar(acc), acc_ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after_sync();
       const bool row_ok = m < p.M;
-      char* out_row = row_ok ? static_cast<char*>(p.out) + (long long)m * p.ldo * (out_fp32 ? 4 : 2) : nullptr;
+      char* out_row = nullptr;
+      if (row_ok) {
+        const int esz = out_fp32 ? 4 : 2;
+        if (p.scatter_out) {               // rows routed to their owner's partial buffer (possibly on a peer)
+          const int owner = min(m / p.rows_per_owner, p.world - 1);
+          const long long lr = (long long)p.rank * p.rows_per_owner + (m - owner * p.rows_per_owner);
+          out_row = static_cast<char*>(p.out_peer[owner]) + lr * p.ldo * esz;
+        } else {
+          out_row = static_cast<char*>(p.out) + (long long)m * p.ldo * esz;
+        }
+      }
+      if (tma_epilogue) {
+        // Outputs leave through shared memory and TMA stores: each thread writes its row's 64
+        // columns (128 bytes) into a swizzled staging tile, the four warps meet, one thread hands
+        // the tile to the copy engine. Two staging tiles alternate; the elected thread makes sure
+        // the previous store has finished reading before the meeting point that releases its tile.
+        const int r = q * 32 + lane;
+        const bool elected = warp == 2 && lane == 0;
+        const int m_tile = tm * 256 + (int)rank * BM;
+        bool ok = true;
+        auto emit = [&](const float (&v)[64], const CUtensorMap* tmap, int x) -> bool {
+          const uint32_t buf = stg_base + (epi_units & 1u) * T2_STG_BYTES;
+          const uint32_t rowaddr = buf + r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t addr = rowaddr + (((uint32_t)c ^ (uint32_t)(r & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(v[8 * c], v[8 * c + 1])),
+                         "r"(pack_bf16x2(v[8 * c + 2], v[8 * c + 3])), "r"(pack_bf16x2(v[8 * c + 4], v[8 * c + 5])),
+                         "r"(pack_bf16x2(v[8 * c + 6], v[8 * c + 7])) : "memory");
+          }
+          fence_proxy_async_smem();
+          if (elected) tma_store_wait_read<0>();
+          mbar_arrive(epi_bar);
+          if (!mbar_wait_warp(epi_bar, epi_units & 1u, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) return false;
+          if (elected) {
+            tma_store_2d(tmap, buf, x, m_tile);
+            tma_store_commit();
+          }
+          ++epi_units;
+          return true;
+        };
+#pragma unroll 1
+        for (int g = 0; g < T2_BN / 64 && ok; ++g) {
+          const int nb = n0 + 64 * g;
+          if (nb >= p.N) break;
+          float v[64];
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            uint32_t t32[32];
+            tmem_ld_32x32b_x32(tmem_base + acc * T2_BN + g * 64 + h2 * 32 + ((uint32_t)(q * 32) << 16), t32);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[32 * h2 + j] = __uint_as_float(t32[j]) * p.alpha;
+          }
+          const int nvalid = min(64, p.N - nb);
+          if (p.flags & MLF_EPI_BIAS) {
+            if (nvalid == 64 && ((reinterpret_cast<uintptr_t>(p.bias + nb) & 15) == 0)) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias + nb) + c);
+                const float2 f0 = unpack_bf16x2(w.x), f1 = unpack_bf16x2(w.y), f2 = unpack_bf16x2(w.z), f3 = unpack_bf16x2(w.w);
+                v[8 * c + 0] += f0.x; v[8 * c + 1] += f0.y; v[8 * c + 2] += f1.x; v[8 * c + 3] += f1.y;
+                v[8 * c + 4] += f2.x; v[8 * c + 5] += f2.y; v[8 * c + 6] += f3.x; v[8 * c + 7] += f3.y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 64; ++j)
+                if (j < nvalid) v[j] += __bfloat162float(p.bias[nb + j]);
+            }
+          }
+          if (p.flags & MLF_EPI_STORE_PRE) {
+            ok = emit(v, &tmPre, nb);
+            if (!ok) break;
+          }
+          if (p.flags & MLF_EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = gelu_tanh(v[j]);
+          }
+          if (p.flags & (MLF_EPI_RESIDUAL | MLF_EPI_DGELU_MUL)) {
+            const bool resid = (p.flags & MLF_EPI_RESIDUAL) != 0;
+            const __nv_bfloat16* ar = p.aux_in + (long long)m * p.ld_aux_in + nb;
+            if (row_ok && nvalid == 64 && ((reinterpret_cast<uintptr_t>(ar) & 15) == 0)) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const uint4 w = reinterpret_cast<const uint4*>(ar)[c];
+                const float2 f0 = unpack_bf16x2(w.x), f1 = unpack_bf16x2(w.y), f2 = unpack_bf16x2(w.z), f3 = unpack_bf16x2(w.w);
+                const float a8[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[8 * c + j] = resid ? v[8 * c + j] + a8[j] : v[8 * c + j] * dgelu_tanh(a8[j]);
+              }
+            } else if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                const float a1 = j < nvalid ? __bfloat162float(ar[j]) : 0.f;
+                v[j] = resid ? v[j] + a1 : v[j] * dgelu_tanh(a1);
+              }
+            }
+          }
+          ok = emit(v, &tmOut, nb);
+        }
+        if (!ok) break;
+      } else {
 #pragma unroll 1
       for (int c = 0; c < T2_BN / 32; ++c) {
         uint32_t r[32];
@@ -237,10 +358,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!row_ok || nb >= p.N) continue;
         gemm_epilogue_chunk(p, m, nb, r, out_row, out_fp32, swiglu, dswiglu);
       }
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
     }
+    if (tma_epilogue && warp == 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until the copies have read it
   }
 
   // ===================== teardown =====================
@@ -262,11 +385,18 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
 using namespace mlf;
 
-// Plain GEMM (no in-kernel communication) on CTA pairs. Same arguments as mlf_gemm_bf16; returns
-// -4 without launching when the problem is not a fit (caller then uses the single-CTA kernel).
+// GEMM on CTA pairs, with the same in-kernel communication options as the single-CTA kernel (copy
+// CTAs that gather an operand or prefetch extra segments; an epilogue that routes rows to their
+// owners). Same arguments as mlf_gemm_bf16; returns -4 without launching when the problem is not a
+// fit (the caller then uses the single-CTA kernel).
 MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   MLF_REQUIRE(a != nullptr, "null args");
-  if (a->comm != nullptr || a->M < 256 || a->N < 256) return -4;
+  if (a->M < 256 || a->N < 256) return -4;
+  const MlfGemmComm* cm = a->comm;
+  const bool gatherA = cm && cm->gather_operand == 1;
+  const bool gatherB = cm && cm->gather_operand == 2;
+  if (cm && cm->gather_operand && (cm->flag_rows <= 0 || cm->flag_rows % 128 != 0)) return -4;
+  if (cm && cm->scatter_out && cm->rows_per_owner % 128 != 0) return -4;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   GemmKernelParams p;
   memset(&p, 0, sizeof(p));
@@ -285,14 +415,65 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   if ((a->flags & MLF_EPI_BIAS)) MLF_REQUIRE(a->bias, "MLF_EPI_BIAS without bias");
   if ((a->flags & (MLF_EPI_RESIDUAL | MLF_EPI_DGELU_MUL | MLF_EPI_DSWIGLU))) MLF_REQUIRE(a->aux_in, "epilogue needs aux_in");
   if ((a->flags & MLF_EPI_STORE_PRE)) MLF_REQUIRE(a->aux_out, "MLF_EPI_STORE_PRE without aux_out");
+  const int sms_all = a->max_ctas > 0 ? a->max_ctas : sm_count();
+  const void* a_base = a->a;
+  const void* b_base = a->b;
+  int n_copy = 0;
+  if (cm && (cm->gather_operand || cm->n_extra > 0)) {
+    MLF_REQUIRE(cm->n_copy_ctas >= 1 && cm->n_copy_ctas + 2 < sms_all, "n_copy_ctas out of range");
+    n_copy = (cm->n_copy_ctas + 1) & ~1;          // whole clusters
+    p.n_copy_ctas = n_copy;
+    p.extra_segs = cm->extra_segs;
+    p.n_extra = cm->n_extra;
+  }
+  if (cm && cm->gather_operand) {
+    MLF_REQUIRE(cm->world >= 1 && cm->world <= 8, "world %d out of range", cm->world);
+    MLF_REQUIRE(cm->rows_per_rank % cm->flag_rows == 0, "rows_per_rank must be a multiple of flag_rows");
+    MLF_REQUIRE(cm->row_bytes % 16 == 0, "row_bytes must be a multiple of 16");
+    MLF_REQUIRE(!(gatherA && a->a_mn) && !(gatherB && a->b_mn), "gathered operand must be K-major");
+    p.gather_operand = cm->gather_operand;
+    p.world = cm->world; p.rank = cm->rank;
+    p.rows_per_rank = cm->rows_per_rank; p.flag_rows = cm->flag_rows; p.row_bytes = cm->row_bytes;
+    p.total_rows = gatherA ? a->M : a->N;
+    for (int r = 0; r < 8; ++r) p.src[r] = cm->src[r];
+    p.gathered = cm->gathered;
+    p.flags_ready = cm->flags; p.counters = cm->counters;
+    // start with the tiles whose rows are already local
+    if (gatherA) { a_base = cm->gathered; p.rot_m = (cm->rank * cm->rows_per_rank) / 256; }
+    else { b_base = cm->gathered; p.rot_n = (cm->rank * cm->rows_per_rank) / T2_BN; }
+    if (p.rot_m >= p.tiles_m) p.rot_m = 0;
+    if (p.rot_n >= p.tiles_n) p.rot_n = 0;
+  }
+  if (cm && cm->scatter_out) {
+    MLF_REQUIRE(cm->world >= 1 && cm->world <= 8, "world %d out of range", cm->world);
+    p.scatter_out = 1; p.rows_per_owner = cm->rows_per_owner;
+    p.world = cm->world; p.rank = cm->rank;
+    for (int r = 0; r < 8; ++r) p.out_peer[r] = cm->out_peer[r];
+    p.rot_m = (((cm->rank + 1) % cm->world) * cm->rows_per_owner) / 256;   // remote traffic starts first
+    if (p.rot_m >= p.tiles_m) p.rot_m = 0;
+  }
   CUtensorMap tmA, tmB;
   int rc;
-  if (!a->a_mn) rc = cached_tmap_bf16(&tmA, a->a, a->K, a->M, a->lda, BK, BM);
-  else rc = cached_tmap_bf16(&tmA, a->a, a->M, a->K, a->lda, 64, BK);
+  if (!a->a_mn) rc = cached_tmap_bf16(&tmA, a_base, a->K, a->M, a->lda, BK, BM);
+  else rc = cached_tmap_bf16(&tmA, a_base, a->M, a->K, a->lda, 64, BK);
   if (rc) return rc;
-  if (!a->b_mn) rc = cached_tmap_bf16(&tmB, a->b, a->K, a->N, a->ldb, BK, T2_BNH);
-  else rc = cached_tmap_bf16(&tmB, a->b, a->N, a->K, a->ldb, 64, BK);
+  if (!a->b_mn) rc = cached_tmap_bf16(&tmB, b_base, a->K, a->N, a->ldb, BK, T2_BNH);
+  else rc = cached_tmap_bf16(&tmB, b_base, a->N, a->K, a->ldb, 64, BK);
   if (rc) return rc;
+  // Outputs go through TMA stores when they are plain bf16 rows this GPU owns.
+  CUtensorMap tmOut = tmA, tmPre = tmA;
+  int tma_epi = 0;
+  if (!(a->flags & (MLF_EPI_OUT_FP32 | MLF_EPI_SWIGLU | MLF_EPI_DSWIGLU | MLF_EPI_ACCUM)) && !(cm && cm->scatter_out) && a->ldo % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 &&
+      (!(a->flags & MLF_EPI_STORE_PRE) || (a->ld_aux_out % 8 == 0 && (reinterpret_cast<uintptr_t>(a->aux_out) & 15) == 0))) {
+    rc = cached_tmap_bf16(&tmOut, a->out, a->N, a->M, a->ldo, 64, 128);
+    if (rc) return rc;
+    if (a->flags & MLF_EPI_STORE_PRE) {
+      rc = cached_tmap_bf16(&tmPre, a->aux_out, a->N, a->M, a->ld_aux_out, 64, 128);
+      if (rc) return rc;
+    }
+    tma_epi = 1;
+  }
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -300,7 +481,7 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
     MLF_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM));
     attr_set[dev & 63] = true;
   }
-  const int sms = a->max_ctas > 0 ? a->max_ctas : sm_count();
+  const int sms = sms_all - n_copy;
   const int num_tiles = p.tiles_m * p.tiles_n;
   static int max_clusters[64] = {0};
   if (!max_clusters[dev & 63]) {
@@ -321,7 +502,7 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   if (pairs > max_clusters[dev & 63]) pairs = max_clusters[dev & 63];
   if (pairs > num_tiles) pairs = num_tiles;
   if (pairs < 1) pairs = 1;
-  gemm_tcgen05_2cta_kernel<<<2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, p);
+  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, p, tma_epi);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

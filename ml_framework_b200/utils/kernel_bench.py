@@ -93,6 +93,37 @@ def bench_gemm(args) -> list[dict]:
     return rows
 
 
+def bench_gemm_epilogues(args) -> list[dict]:
+    """The GPT-1.3B forward / backward GEMMs with the epilogues the model runs them with, against the plain product."""
+    from .. import _lib
+    from ..ops.gemm import gemm
+    rows = []
+    M = 8192
+    cases = [("proj", 2048, 2048, [("plain", 0), ("bias", _lib.EPI_BIAS), ("residual", _lib.EPI_RESIDUAL), ("bias+residual", _lib.EPI_BIAS | _lib.EPI_RESIDUAL)]),
+             ("qkv", 6144, 2048, [("plain", 0), ("bias", _lib.EPI_BIAS)]),
+             ("fc1", 8192, 2048, [("plain", 0), ("bias+gelu", _lib.EPI_BIAS | _lib.EPI_GELU),
+                                  ("bias+gelu+store_pre", _lib.EPI_BIAS | _lib.EPI_GELU | _lib.EPI_STORE_PRE), ("dgelu_mul", _lib.EPI_DGELU_MUL)])]
+    for name, N, K, variants in cases:
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+        aux = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+        pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for vname, fl in variants:
+            kw = {}
+            if fl & _lib.EPI_BIAS:
+                kw["bias"] = bias
+            if fl & (_lib.EPI_RESIDUAL | _lib.EPI_DGELU_MUL):
+                kw["aux_in"] = aux
+            if fl & _lib.EPI_STORE_PRE:
+                kw["aux_out"] = pre
+            ms = time_cuda(lambda: gemm(a, b, out=out, flags=fl, **kw))
+            rows.append({"gemm": name, "epilogue": vname, "M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(2.0 * M * N * K / ms / 1e9, 1)})
+            print(rows[-1], flush=True)
+    return rows
+
+
 def run_gemm_small() -> list[dict]:
     """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
     from ..ops.gemm import gemm
@@ -107,11 +138,13 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "elementwise", "attn_small", "gemm_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
         rows = bench_gemm(args)
+    elif args.what == "gemm_epi":
+        rows = bench_gemm_epilogues(args)
     elif args.what == "attn_small":
         from .kernel_bench_attn import run_attn_small
         rows = run_attn_small()

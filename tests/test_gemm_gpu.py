@@ -83,9 +83,11 @@ def test_epilogues():
     _check(out, ref, K)
 
 
-def test_gather_and_scatter_emulated_ranks():
+@pytest.mark.parametrize("tile_n", [256, 512])
+def test_gather_and_scatter_emulated_ranks(tile_n):
     """The fused-communication paths with every 'peer' buffer on this GPU: one launch, copy
-    CTAs and compute CTAs of the same grid, as the multi-GPU path runs them."""
+    CTAs and compute CTAs of the same grid, as the multi-GPU path runs them. tile_n 512 is the
+    CTA-pair kernel."""
     import ctypes as C
     torch.manual_seed(3)
     W = 4
@@ -108,9 +110,9 @@ def test_gather_and_scatter_emulated_ranks():
             cm.src[r] = shards[r].data_ptr()
         cm.gathered, cm.flags, cm.counters = gathered.data_ptr(), flags.data_ptr(), counters.data_ptr()
         if operand == 1:
-            out = gemm(shards[1], b, comm=cm, m_override=M, tile_n=256)
+            out = gemm(shards[1], b, comm=cm, m_override=M, tile_n=tile_n)
         else:
-            out = gemm(a, shards[1], comm=cm, n_override=N, tile_n=256)
+            out = gemm(a, shards[1], comm=cm, n_override=N, tile_n=tile_n)
         torch.cuda.synchronize()
         assert torch.equal(gathered, full)
         _check(out, ref, K)
@@ -121,7 +123,7 @@ def test_gather_and_scatter_emulated_ranks():
     for r in range(W):
         cm.out_peer[r] = parts[r].data_ptr()
     dummy = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    gemm(a, b, out=dummy, comm=cm)
+    gemm(a, b, out=dummy, comm=cm, tile_n=tile_n)
     torch.cuda.synchronize()
     for r in range(W):
         _check(parts[r][2], ref[r * (M // W):(r + 1) * (M // W)], K)

@@ -21,3 +21,9 @@ def _torchrun(script, n, port, timeout=600):
 def test_fsdp_fused_matches_nccl_two_ranks():
     r = _torchrun("fsdp_worker.py", 2, 29741)
     assert r.returncode == 0 and "FSDP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_fused_matches_nccl_two_ranks():
+    r = _torchrun("tp_worker.py", 2, 29743)
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
