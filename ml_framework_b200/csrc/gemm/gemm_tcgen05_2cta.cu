@@ -92,7 +92,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmPre,
-                         const GemmKernelParams p, const int tma_epilogue) {
+                         const __grid_constant__ CUtensorMap tmAux, const GemmKernelParams p, const int tma_epilogue,
+                         const int tma_aux) {
   // Copy CTAs come in whole clusters (their count is even) and never touch the cluster barrier.
   if ((int)blockIdx.x < p.n_copy_ctas) {
     gather_copy_role(p);
@@ -107,8 +108,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * T2_STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * T2_STAGES + 2 + a); };
   const uint32_t epi_bar = bar_base + 8u * (2 * T2_STAGES + 4);      // the four epilogue warps meet here (128 arrivals)
+  const uint32_t aux_bar = bar_base + 8u * (2 * T2_STAGES + 5);      // aux_in tile landed in the staging buffer
   const uint32_t stg_base = bar_base + 1024u;                        // two staging buffers
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_al + T2_STAGES * T2_STAGE + 8 * (2 * T2_STAGES + 5));
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_al + T2_STAGES * T2_STAGE + 8 * (2 * T2_STAGES + 6));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -126,6 +128,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       mbar_init(tempty_bar(a), 8);
     }
     mbar_init(epi_bar, 128);
+    mbar_init(aux_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -267,6 +270,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const bool elected = warp == 2 && lane == 0;
         const int m_tile = tm * 256 + (int)rank * BM;
         bool ok = true;
+        // aux_in (residual / dGELU input) comes in through the same staging tile, fetched by the copy
+        // engine one unit ahead: unit u's tile may be overwritten once the store of unit u-2 has
+        // finished reading, which the meeting point of unit u-1 guarantees.
+        auto prefetch_aux = [&](uint32_t unit, int x, int y) {
+          mbar_expect_tx(aux_bar, T2_STG_BYTES);
+          tma_load_2d(stg_base + (unit & 1u) * T2_STG_BYTES, &tmAux, x, y, aux_bar);
+        };
+        if (tma_aux && elected && epi_units == 0) prefetch_aux(0, n0, m_tile);
         auto emit = [&](const float (&v)[64], const CUtensorMap* tmap, int x) -> bool {
           const uint32_t buf = stg_base + (epi_units & 1u) * T2_STG_BYTES;
           const uint32_t rowaddr = buf + r * 128;
@@ -284,6 +295,18 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (elected) {
             tma_store_2d(tmap, buf, x, m_tile);
             tma_store_commit();
+            if (tma_aux) {                       // next unit: next column group of this tile, or the first of the next tile
+              int nx = x + 64, ny = m_tile;
+              bool have = nx < n0 + T2_BN && nx < p.N;
+              if (!have && t + n_pairs < num_tiles) {
+                int tm2, tn2;
+                tile_coords(t + n_pairs, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm2, tn2);
+                nx = tn2 * T2_BN;
+                ny = tm2 * 256 + (int)rank * BM;
+                have = true;
+              }
+              if (have) prefetch_aux(epi_units + 1, nx, ny);
+            }
           }
           ++epi_units;
           return true;
@@ -328,7 +351,20 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (p.flags & (MLF_EPI_RESIDUAL | MLF_EPI_DGELU_MUL)) {
             const bool resid = (p.flags & MLF_EPI_RESIDUAL) != 0;
             const __nv_bfloat16* ar = p.aux_in + (long long)m * p.ld_aux_in + nb;
-            if (row_ok && nvalid == 64 && ((reinterpret_cast<uintptr_t>(ar) & 15) == 0)) {
+            if (tma_aux) {
+              if (!mbar_wait_warp(aux_bar, epi_units & 1u, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+              const uint32_t rowaddr = stg_base + (epi_units & 1u) * T2_STG_BYTES + r * 128;
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                uint4 w;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                             : "r"(rowaddr + (((uint32_t)c ^ (uint32_t)(r & 7)) << 4)));
+                const float2 f0 = unpack_bf16x2(w.x), f1 = unpack_bf16x2(w.y), f2 = unpack_bf16x2(w.z), f3 = unpack_bf16x2(w.w);
+                const float a8[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[8 * c + j] = resid ? v[8 * c + j] + a8[j] : v[8 * c + j] * dgelu_tanh(a8[j]);
+              }
+            } else if (row_ok && nvalid == 64 && ((reinterpret_cast<uintptr_t>(ar) & 15) == 0)) {
 #pragma unroll
               for (int c = 0; c < 8; ++c) {
                 const uint4 w = reinterpret_cast<const uint4*>(ar)[c];
@@ -461,8 +497,8 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   else rc = cached_tmap_bf16(&tmB, b_base, a->N, a->K, a->ldb, 64, BK);
   if (rc) return rc;
   // Outputs go through TMA stores when they are plain bf16 rows this GPU owns.
-  CUtensorMap tmOut = tmA, tmPre = tmA;
-  int tma_epi = 0;
+  CUtensorMap tmOut = tmA, tmPre = tmA, tmAux = tmA;
+  int tma_epi = 0, tma_aux = 0;
   if (!(a->flags & (MLF_EPI_OUT_FP32 | MLF_EPI_SWIGLU | MLF_EPI_DSWIGLU | MLF_EPI_ACCUM)) && !(cm && cm->scatter_out) && a->ldo % 8 == 0 &&
       (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 &&
       (!(a->flags & MLF_EPI_STORE_PRE) || (a->ld_aux_out % 8 == 0 && (reinterpret_cast<uintptr_t>(a->aux_out) & 15) == 0))) {
@@ -473,6 +509,12 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
       if (rc) return rc;
     }
     tma_epi = 1;
+    if ((a->flags & (MLF_EPI_RESIDUAL | MLF_EPI_DGELU_MUL)) && !(a->flags & MLF_EPI_STORE_PRE) && a->ld_aux_in % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(a->aux_in) & 15) == 0) {
+      rc = cached_tmap_bf16(&tmAux, a->aux_in, a->N, a->M, a->ld_aux_in, 64, 128);
+      if (rc) return rc;
+      tma_aux = 1;
+    }
   }
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -502,7 +544,7 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   if (pairs > max_clusters[dev & 63]) pairs = max_clusters[dev & 63];
   if (pairs > num_tiles) pairs = num_tiles;
   if (pairs < 1) pairs = 1;
-  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, p, tma_epi);
+  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, tmAux, p, tma_epi, tma_aux);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
