@@ -89,11 +89,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// Output tensor maps of the row owners when the epilogue routes rows to peers (GEMM -> reduce-scatter).
+struct alignas(64) PeerMaps {
+  CUtensorMap m[8];
+};
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmPre,
-                         const __grid_constant__ CUtensorMap tmAux, const GemmKernelParams p, const int tma_epilogue,
-                         const int tma_aux) {
+                         const __grid_constant__ CUtensorMap tmAux, const __grid_constant__ PeerMaps peer_maps,
+                         const GemmKernelParams p, const int tma_epilogue, const int tma_aux) {
   // Copy CTAs come in whole clusters (their count is even) and never touch the cluster barrier.
   if ((int)blockIdx.x < p.n_copy_ctas) {
     gather_copy_role(p);
@@ -293,7 +298,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           mbar_arrive(epi_bar);
           if (!mbar_wait_warp(epi_bar, epi_units & 1u, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) return false;
           if (elected) {
-            tma_store_2d(tmap, buf, x, m_tile);
+            if (p.scatter_out) {                 // the whole 128-row block belongs to one owner (possibly a peer)
+              const int owner = min(m_tile / p.rows_per_owner, p.world - 1);
+              tma_store_2d(&peer_maps.m[owner], buf, x, p.rank * p.rows_per_owner + (m_tile - owner * p.rows_per_owner));
+            } else {
+              tma_store_2d(tmap, buf, x, m_tile);
+            }
             tma_store_commit();
             if (tma_aux) {                       // next unit: next column group of this tile, or the first of the next tile
               int nx = x + 64, ny = m_tile;
@@ -498,12 +508,23 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   if (rc) return rc;
   // Outputs go through TMA stores when they are plain bf16 rows this GPU owns.
   CUtensorMap tmOut = tmA, tmPre = tmA, tmAux = tmA;
+  PeerMaps peer_maps;                        // only read by the kernel when rows are routed
+  memset(&peer_maps, 0, sizeof(peer_maps));
   int tma_epi = 0, tma_aux = 0;
-  if (!(a->flags & (MLF_EPI_OUT_FP32 | MLF_EPI_SWIGLU | MLF_EPI_DSWIGLU | MLF_EPI_ACCUM)) && !(cm && cm->scatter_out) && a->ldo % 8 == 0 &&
-      (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 &&
+  const bool scatter = cm && cm->scatter_out;
+  if (!(a->flags & (MLF_EPI_OUT_FP32 | MLF_EPI_SWIGLU | MLF_EPI_DSWIGLU | MLF_EPI_ACCUM)) && a->ldo % 8 == 0 &&
+      (scatter || (reinterpret_cast<uintptr_t>(a->out) & 15) == 0) &&
       (!(a->flags & MLF_EPI_STORE_PRE) || (a->ld_aux_out % 8 == 0 && (reinterpret_cast<uintptr_t>(a->aux_out) & 15) == 0))) {
-    rc = cached_tmap_bf16(&tmOut, a->out, a->N, a->M, a->ldo, 64, 128);
-    if (rc) return rc;
+    if (scatter) {
+      for (int r = 0; r < cm->world; ++r) {
+        MLF_REQUIRE((reinterpret_cast<uintptr_t>(cm->out_peer[r]) & 15) == 0, "partial buffers must be 16-byte aligned");
+        rc = cached_tmap_bf16(&peer_maps.m[r], cm->out_peer[r], a->N, (uint64_t)cm->world * cm->rows_per_owner, a->ldo, 64, 128);
+        if (rc) return rc;
+      }
+    } else {
+      rc = cached_tmap_bf16(&tmOut, a->out, a->N, a->M, a->ldo, 64, 128);
+      if (rc) return rc;
+    }
     if (a->flags & MLF_EPI_STORE_PRE) {
       rc = cached_tmap_bf16(&tmPre, a->aux_out, a->N, a->M, a->ld_aux_out, 64, 128);
       if (rc) return rc;
@@ -544,7 +565,7 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   if (pairs > max_clusters[dev & 63]) pairs = max_clusters[dev & 63];
   if (pairs > num_tiles) pairs = num_tiles;
   if (pairs < 1) pairs = 1;
-  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, tmAux, p, tma_epi, tma_aux);
+  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, tmAux, peer_maps, p, tma_epi, tma_aux);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
