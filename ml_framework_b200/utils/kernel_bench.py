@@ -124,6 +124,41 @@ def bench_gemm_epilogues(args) -> list[dict]:
     return rows
 
 
+def run_fused_small() -> list[dict]:
+    """The fused communication + GEMM kernel on ONE GPU with emulated ranks (every "peer" buffer lives on this
+    GPU): all-gather of A fused into the GEMM (copy CTAs + compute CTAs in one grid), then a GEMM whose
+    epilogue routes row blocks to four owners' partial buffers. M = 8192, N = 4096, K = 4096, world 4.
+    This is the case profiled with ncu (a multi-rank run is never profiled)."""
+    from .. import _lib
+    from ..ops.gemm import gemm
+    W, M, N, K = 4, 8192, 4096, 4096
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    shards = [a[r * M // W:(r + 1) * M // W].clone() for r in range(W)]
+    out = None
+    for _ in range(2):
+        gathered = torch.zeros_like(a)
+        flag_rows = 256
+        flags = torch.zeros(M // flag_rows, dtype=torch.int32, device="cuda")
+        counters = torch.zeros_like(flags)
+        cm = _lib.GemmComm()
+        cm.gather_operand, cm.world, cm.rank, cm.n_copy_ctas = 1, W, 1, 16
+        cm.rows_per_rank, cm.flag_rows, cm.row_bytes = M // W, flag_rows, K * 2
+        for r in range(W):
+            cm.src[r] = shards[r].data_ptr()
+        cm.gathered, cm.flags, cm.counters = gathered.data_ptr(), flags.data_ptr(), counters.data_ptr()
+        out = gemm(shards[1], b, comm=cm, m_override=M)
+        parts = [torch.zeros(W, M // W, N, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+        cs = _lib.GemmComm()
+        cs.scatter_out, cs.rows_per_owner, cs.world, cs.rank = 1, M // W, W, 2
+        for r in range(W):
+            cs.out_peer[r] = parts[r].data_ptr()
+        gemm(a, b, out=torch.empty(M, N, device="cuda", dtype=torch.bfloat16), comm=cs)
+    torch.cuda.synchronize()
+    ok = bool(torch.equal(gathered, a))
+    return [{"ran": "fused gather-GEMM + scatter-GEMM x2 (emulated world 4)", "gather_exact": ok}]
+
+
 def run_gemm_small() -> list[dict]:
     """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
     from ..ops.gemm import gemm
@@ -138,7 +173,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -148,6 +183,9 @@ def main():
     elif args.what == "attn_small":
         from .kernel_bench_attn import run_attn_small
         rows = run_attn_small()
+    elif args.what == "fused_small":
+        rows = run_fused_small()
+        print(rows)
     elif args.what == "gemm_small":
         rows = run_gemm_small()
     elif args.what == "attn":
