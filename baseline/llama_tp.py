@@ -88,7 +88,7 @@ class Model(nn.Module):
             x = b(x)
         logits = self.head(_CopyIn.apply(self.nf(x))).float()                  # [B, S, V / W]
         # vocab-parallel cross entropy: max and sum-exp reduced over the group
-        m = logits.amax(-1)
+        m = logits.detach().amax(-1)
         dist.all_reduce(m, op=dist.ReduceOp.MAX)
         se = (logits - m[..., None]).exp().sum(-1)
         se = _AllReduce.apply(se)
@@ -101,6 +101,10 @@ class Model(nn.Module):
 def build(cfg, dev, ids, tgt):
     W, rank = dist.get_world_size(), dist.get_rank()
     model = Model(cfg, W, rank, dev)
+    with torch.no_grad():
+        for prm in model.parameters():
+            if prm.dim() >= 2:
+                prm.normal_(0.0, 0.02)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
     n_params = sum(p.numel() for p in model.parameters()) * W
 
