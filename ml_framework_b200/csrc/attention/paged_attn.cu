@@ -88,30 +88,39 @@ paged_decode_kernel(const PagedDecodeParams p) {
 
   for (int c0 = t_lo; c0 < t_hi; c0 += P_SUB) {
     const int cn = min(P_SUB, t_hi - c0);
-    // ---- scores for up to 128 tokens: 8 tokens per step, 16 lanes per token
-    for (int i = tg; i < P_SUB; i += 8) {
-      float s[G];
+    // ---- scores for up to 128 tokens: 8 tokens per step, 16 lanes per token; the 16-byte loads of
+    // four steps are issued together so that four rows per thread are in flight (the kernel is
+    // bound by memory latency x bytes in flight, not by arithmetic)
+#pragma unroll 1
+    for (int i0 = tg; i0 < P_SUB; i0 += 32) {
+      uint4 u[4];
 #pragma unroll
-      for (int g = 0; g < G; ++g) s[g] = 0.f;
-      if (i < cn) {
-        const int t = c0 + i;
-        int blk = bt[t / p.block_size];
-        if (blk < 0 || blk >= p.num_blocks) { atomicCAS(p.err, 0, ERR_BAD_INDEX); blk = 0; }
-        const __nv_bfloat16* kr = p.cache + blk * blk_stride + ((long long)(t % p.block_size) * p.Hkv + hkv) * PD + dl * 8;
-        const uint4 u = *reinterpret_cast<const uint4*>(kr);
-        float k[8];
-        float2 a = unpack_bf16x2(u.x), bb = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-        k[0] = a.x; k[1] = a.y; k[2] = bb.x; k[3] = bb.y; k[4] = c.x; k[5] = c.y; k[6] = d.x; k[7] = d.y;
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) s[g] += qreg[g][j] * k[j];
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + 8 * e;
+        u[e] = make_uint4(0, 0, 0, 0);
+        if (i < cn) {
+          const int t = c0 + i;
+          int blk = bt[t / p.block_size];
+          if (blk < 0 || blk >= p.num_blocks) { atomicCAS(p.err, 0, ERR_BAD_INDEX); blk = 0; }
+          u[e] = *reinterpret_cast<const uint4*>(p.cache + blk * blk_stride + ((long long)(t % p.block_size) * p.Hkv + hkv) * PD + dl * 8);
+        }
       }
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + 8 * e;
+        float s[G];
+        float k[8];
+        const float2 a = unpack_bf16x2(u[e].x), bb = unpack_bf16x2(u[e].y), c = unpack_bf16x2(u[e].z), d = unpack_bf16x2(u[e].w);
+        k[0] = a.x; k[1] = a.y; k[2] = bb.x; k[3] = bb.y; k[4] = c.x; k[5] = c.y; k[6] = d.x; k[7] = d.y;
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-        if (dl == 0) s_p[g][i] = i < cn ? s[g] : -INFINITY;
+        for (int g = 0; g < G; ++g) {
+          s[g] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s[g] += qreg[g][j] * k[j];
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+          if (dl == 0) s_p[g][i] = i < cn ? s[g] : -INFINITY;
+        }
       }
     }
     __syncthreads();
@@ -147,20 +156,33 @@ paged_decode_kernel(const PagedDecodeParams p) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[g][j] *= al;
     }
-    for (int i = tg; i < cn; i += 8) {
-      const int t = c0 + i;
-      int blk = bt[t / p.block_size];
-      if (blk < 0 || blk >= p.num_blocks) blk = 0;
-      const __nv_bfloat16* vr = p.cache + blk * blk_stride + v_off + ((long long)(t % p.block_size) * p.Hkv + hkv) * PD + dl * 8;
-      const uint4 u = *reinterpret_cast<const uint4*>(vr);
-      float v[8];
-      float2 a = unpack_bf16x2(u.x), bb = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-      v[0] = a.x; v[1] = a.y; v[2] = bb.x; v[3] = bb.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+#pragma unroll 1
+    for (int i0 = tg; i0 < cn; i0 += 32) {
+      uint4 u[4];
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pw = s_p[g][i];
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + 8 * e;
+        u[e] = make_uint4(0, 0, 0, 0);
+        if (i < cn) {
+          const int t = c0 + i;
+          int blk = bt[t / p.block_size];
+          if (blk < 0 || blk >= p.num_blocks) blk = 0;
+          u[e] = *reinterpret_cast<const uint4*>(p.cache + blk * blk_stride + v_off + ((long long)(t % p.block_size) * p.Hkv + hkv) * PD + dl * 8);
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] += pw * v[j];
+      for (int e = 0; e < 4; ++e) {
+        const int i = i0 + 8 * e;
+        if (i >= cn) break;
+        float v[8];
+        const float2 a = unpack_bf16x2(u[e].x), bb = unpack_bf16x2(u[e].y), c = unpack_bf16x2(u[e].z), d = unpack_bf16x2(u[e].w);
+        v[0] = a.x; v[1] = a.y; v[2] = bb.x; v[3] = bb.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float pw = s_p[g][i];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[g][j] += pw * v[j];
+        }
       }
     }
     __syncthreads();

@@ -36,6 +36,8 @@ class ExecutorConfig:
     max_seq_len: int = 4096
     prefill_chunk: int = 2048
     decode_split_tokens: int = 512
+    use_cuda_graphs: bool = True       # decode steps replay a captured graph per (batch bucket, length bucket)
+    graph_warmup_steps: int = 2
 
 
 class PagedLlamaExecutor:
@@ -49,6 +51,10 @@ class PagedLlamaExecutor:
         self.hq, self.hkv = self.mc.n_heads // W, self.mc.n_kv_heads // W
         self.max_blocks = (self.cfg.max_seq_len + kv.block_size - 1) // kv.block_size
         self.tokens_generated = 0
+        self._graphs = None
+        if self.native and self.cfg.use_cuda_graphs and (tp is None or tp.world == 1):
+            from ..hal.cuda_graphs import CaptureOptions, CUDAGraphManager
+            self._graphs = CUDAGraphManager(CaptureOptions(warmup_iterations=self.cfg.graph_warmup_steps))
 
     # ---- tensor-parallel reduction of partial projections
     def _reduce(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
@@ -175,23 +181,8 @@ class PagedLlamaExecutor:
         return None
 
     # ---- one decode step for a set of requests
-    @torch.no_grad()
-    def _decode(self, reqs: List[Request]) -> List[int]:
-        dev = self.device
-        B = len(reqs)
-        last = torch.tensor([r.generated[-1] if r.generated else r.prompt_tokens[-1] for r in reqs], dtype=torch.int64, device=dev)
-        lens_before = [self.kv.get_sequence_length(r.id) for r in reqs]
-        slot_list = []
-        for r in reqs:
-            s, _ = self.kv.append_tokens(r.id, 1)
-            if s is None:
-                raise MemoryError(f"KV cache exhausted while decoding request {r.id}")
-            slot_list.append(s)
-        slots = torch.cat(slot_list).to(dev)
-        pos = torch.tensor(lens_before, dtype=torch.int64, device=dev)
-        table, lens = self.kv.build_tables([r.id for r in reqs], self.max_blocks, dev)
-        max_len = max(lens_before) + 1
-
+    def _decode_core(self, last, pos, slots, table, lens, max_len: int) -> torch.Tensor:
+        """Device-only part of a decode step (no host reads): embed, all blocks, head, arg-max."""
         def attend(li, q, k, v):
             if self.native:
                 return native.paged_decode(q.contiguous(), self.kv.caches[li], table, lens, max_len,
@@ -200,7 +191,55 @@ class PagedLlamaExecutor:
         x = self._embed(last[None])[0]
         for li, blk in enumerate(self.m.blocks):
             x = self._block(li, blk, x, pos, slots, attend)
-        return self._logits_argmax(x).tolist()
+        return self._logits_argmax(x)
+
+    @staticmethod
+    def _bucket(n: int, lo: int = 1) -> int:
+        b = lo
+        while b < n:
+            b *= 2
+        return b
+
+    @torch.no_grad()
+    def _decode(self, reqs: List[Request]) -> List[int]:
+        dev = self.device
+        B = len(reqs)
+        last_l = [r.generated[-1] if r.generated else r.prompt_tokens[-1] for r in reqs]
+        lens_before = [self.kv.get_sequence_length(r.id) for r in reqs]
+        slot_list = []
+        for r in reqs:
+            s, _ = self.kv.append_tokens(r.id, 1)
+            if s is None:
+                raise MemoryError(f"KV cache exhausted while decoding request {r.id}")
+            slot_list.append(s)
+        table, lens = self.kv.build_tables([r.id for r in reqs], self.max_blocks, dev)
+        max_len = max(lens_before) + 1
+        if self._graphs is None:
+            last = torch.tensor(last_l, dtype=torch.int64, device=dev)
+            slots = torch.cat(slot_list).to(dev)
+            pos = torch.tensor(lens_before, dtype=torch.int64, device=dev)
+            return self._decode_core(last, pos, slots, table, lens, max_len).tolist()
+        # Graph path: pad the batch to a power of two and the length bound to a multiple of 512 so that a
+        # handful of captured graphs covers every step. Padding rows write nowhere (slot -1) and attend to
+        # one token of block 0; their outputs are dropped.
+        Bp = self._bucket(B)
+        Lp = min(self._bucket(max_len, 512), max(self.cfg.max_seq_len, 512))
+        pad = Bp - B
+        host = torch.empty(3, Bp, dtype=torch.int64, pin_memory=True)
+        host[0, :B] = torch.tensor(last_l, dtype=torch.int64)
+        host[1, :B] = torch.tensor(lens_before, dtype=torch.int64)
+        host[2, :B] = torch.cat(slot_list).to(torch.int64).cpu()
+        if pad:
+            host[0, B:] = 0
+            host[1, B:] = 0
+            host[2, B:] = -1
+        devt = host.to(dev, non_blocking=True)
+        if pad:
+            table = torch.cat([table, table.new_zeros(pad, table.shape[1])], 0)
+            lens = torch.cat([lens, lens.new_ones(pad)], 0)
+        fn = lambda a, b_, c, t, l: self._decode_core(a, b_, c, t, l, Lp)
+        out = self._graphs.run(f"decode_L{Lp}", fn, devt[0], devt[1], devt[2], table.contiguous(), lens.contiguous())
+        return out[:B].tolist()
 
     # ---- scheduler entry point
     def execute_batch(self, batch: Batch) -> BatchOutput:
