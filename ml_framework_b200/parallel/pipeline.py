@@ -513,3 +513,102 @@ class PipelineValidator:
     def validate_gradients(pipeline_grads: Sequence[torch.Tensor], reference_grads: Sequence[torch.Tensor], atol=1e-5) -> bool:
         return len(pipeline_grads) == len(reference_grads) and all(
             torch.allclose(a, b, atol=atol) for a, b in zip(pipeline_grads, reference_grads))
+
+
+# ------------------------------------------------------------------ streams for compute / communication overlap
+class StreamManager:
+    """Round-robin pools of compute and communication CUDA streams with named events
+    (src/MLFramework/Pipeline/StreamManager.cs:51-141). On a CPU device every stream is ``None`` and
+    events complete immediately."""
+
+    def __init__(self, device=None, num_compute: int = 2, num_comm: int = 2):
+        self.device = torch.device(device) if device is not None else (torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu"))
+        cuda = self.device.type == "cuda"
+        self.compute = [torch.cuda.Stream(self.device) if cuda else None for _ in range(max(1, num_compute))]
+        self.comm = [torch.cuda.Stream(self.device, priority=-1) if cuda else None for _ in range(max(1, num_comm))]
+        self._events = {}
+
+    def compute_stream(self, micro_batch: int):
+        return self.compute[micro_batch % len(self.compute)]
+
+    def comm_stream(self, micro_batch: int):
+        return self.comm[micro_batch % len(self.comm)]
+
+    def record_event(self, name: str, stream):
+        if stream is None:
+            self._events[name] = None
+            return
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        self._events[name] = ev
+
+    def wait_for_event(self, name: str, stream):
+        if name not in self._events:
+            raise KeyError(f"event {name!r} was never recorded")
+        ev = self._events[name]
+        if ev is not None and stream is not None:
+            stream.wait_event(ev)
+
+    def synchronize(self):
+        for s in self.compute + self.comm:
+            if s is not None:
+                s.synchronize()
+
+
+class AsyncPipelineExecutor:
+    """Runs a stage's forward / backward of micro-batch ``i`` on compute stream ``i mod n`` and its sends /
+    receives on communication stream ``i mod n``, ordering the two with events, so that the transfer of one
+    micro-batch overlaps the computation of the next (src/MLFramework/Pipeline/AsyncPipelineExecutor.cs:76-320)."""
+
+    def __init__(self, stage: "PipelineStage", comm, streams: Optional[StreamManager] = None):
+        self.stage, self.comm = stage, comm
+        self.streams = streams or StreamManager(next(stage.parameters()).device)
+        self._outs = {}
+
+    def _on(self, stream):
+        import contextlib
+        return torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext()
+
+    def forward_async(self, x: torch.Tensor, micro_batch: int) -> torch.Tensor:
+        cs = self.streams.compute_stream(micro_batch)
+        if f"recv_f{micro_batch}" in self.streams._events:
+            self.streams.wait_for_event(f"recv_f{micro_batch}", cs)
+        with self._on(cs):
+            y = self.stage(x)
+        self.streams.record_event(f"fwd{micro_batch}", cs)
+        self._outs[micro_batch] = (x, y)
+        return y
+
+    def send_async(self, t: torch.Tensor, micro_batch: int, direction: str = "forward"):
+        ms = self.streams.comm_stream(micro_batch)
+        self.streams.wait_for_event(f"{'fwd' if direction == 'forward' else 'bwd'}{micro_batch}", ms)
+        with self._on(ms):
+            (self.comm.send_forward if direction == "forward" else self.comm.send_backward)(t)
+        self.streams.record_event(f"send_{direction[0]}{micro_batch}", ms)
+
+    def receive_async(self, like: torch.Tensor, micro_batch: int, direction: str = "forward") -> torch.Tensor:
+        ms = self.streams.comm_stream(micro_batch)
+        with self._on(ms):
+            t = (self.comm.recv_forward if direction == "forward" else self.comm.recv_backward)(tuple(like.shape), like.dtype, like.device)
+        self.streams.record_event(f"recv_{direction[0]}{micro_batch}", ms)
+        return t
+
+    def backward_async(self, grad_out: torch.Tensor, micro_batch: int) -> Optional[torch.Tensor]:
+        cs = self.streams.compute_stream(micro_batch)
+        x, y = self._outs.pop(micro_batch)
+        if f"recv_b{micro_batch}" in self.streams._events:
+            self.streams.wait_for_event(f"recv_b{micro_batch}", cs)
+        with self._on(cs):
+            y.backward(grad_out)
+        self.streams.record_event(f"bwd{micro_batch}", cs)
+        return x.grad if x.requires_grad else None
+
+    def sync_compute(self):
+        for s in self.streams.compute:
+            if s is not None:
+                s.synchronize()
+
+    def sync_comm(self):
+        for s in self.streams.comm:
+            if s is not None:
+                s.synchronize()

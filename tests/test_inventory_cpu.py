@@ -446,3 +446,103 @@ def test_cli_serve_and_train(capsys):
     assert out["generated_tokens"] == 20 and out["ttft_p50_ms"] > 0
     cli.main(["train", "--steps", "2", "--seq", "32"])
     assert "loss" in json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+
+
+# ------------------------------------------------------------------ communicator façade, FSDP state, TP checkpoints, stream manager
+def test_communicator_p2p_and_group_helpers():
+    from ml_framework_b200.dist import communicator as Cm
+    from ml_framework_b200.dist.process_group import run_fake_world
+
+    def body(pg):
+        c = Cm.Communicator(pg)
+        r = pg.rank
+        a = c.all_reduce(torch.tensor([float(r)]))
+        g = c.all_gather(torch.tensor([[r]]), dim=1)
+        ring = Cm.ring_send_recv(pg, torch.tensor([r]))
+        if r == 0:
+            Cm.send_with_header(pg, torch.arange(6).view(2, 3), 1)
+        got = None
+        if r == 1:
+            info = Cm.probe(pg, 0)
+            assert info.shape == (2, 3) and info.count == 6 and info.dtype == torch.int64
+            got = Cm.recv_probed(pg, info)
+        sc = Cm.scatter(pg, [torch.tensor([10 * i]) for i in range(pg.world_size)] if r == 0 else None, torch.tensor([0]))
+        ga = Cm.gather(pg, torch.tensor([r * 2]))
+        return a.item(), g.tolist(), ring.item(), None if got is None else got.tolist(), sc.item(), None if ga is None else [x.item() for x in ga]
+    out = run_fake_world(3, body)
+    assert out[0] == (3.0, [[0, 1, 2]], 2, None, 0, [0, 2, 4])
+    assert out[1][3] == [[0, 1, 2], [3, 4, 5]] and out[1][4] == 10 and out[2][2] == 1 and out[2][4] == 20
+    assert Cm.split_groups(8, 2)[1] == [2, 3] and Cm.pipeline_groups(8, 4)[1] == [1, 3, 5, 7] and Cm.data_parallel_groups(8, 2)[0] == [0, 2, 4, 6]
+    with pytest.raises(ValueError):
+        Cm.split_groups(6, 4)
+    world = Cm.CommunicatorFactory.create("mock", world_size=2)
+    assert len(world) == 2 and world[1].rank == 1
+
+
+def test_fsdp_checkpoint_and_optimizer_state_roundtrip(tmp_path):
+    from ml_framework_b200.dist.process_group import run_fake_world
+    from ml_framework_b200.models import GPT, GPTConfig
+    from ml_framework_b200.parallel import fsdp_state as FS
+    from ml_framework_b200.parallel.fsdp import FSDP, FSDPConfig
+    cfg = GPTConfig(n_layers=2, d_model=64, n_heads=2, d_ff=128, vocab_size=100, max_seq=16, vocab_multiple=8)
+    torch.manual_seed(0)
+    base = GPT(cfg)
+    g = torch.Generator().manual_seed(3)
+    ids, tgt = torch.randint(0, 100, (2, 2, 16), generator=g), torch.randint(0, 100, (2, 2, 16), generator=g)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-4, weight_decay=0.01)
+
+    def run(pg):
+        fs = FSDP(copy.deepcopy(base), FSDPConfig(min_shard_numel=64), pg, optimizer_kwargs=kw)
+        for _ in range(2):
+            fs.train_step(ids[pg.rank], tgt[pg.rank])
+        ck = FS.FSDPCheckpoint(fs, str(tmp_path), max_checkpoints=2)
+        for s in (1, 2, 3):
+            ck.save(0, s)
+        before = {k: v.clone() for k, v in fs.full_state_dict().items()}
+        l3 = float(fs.train_step(ids[pg.rank], tgt[pg.rank]).detach())
+        fs2 = FSDP(copy.deepcopy(base), FSDPConfig(min_shard_numel=64), pg, optimizer_kwargs=kw)
+        meta = FS.FSDPCheckpoint(fs2, str(tmp_path)).load()
+        after = fs2.full_state_dict()
+        same = all(torch.allclose(before[k].float(), after[k].float(), atol=1e-6) for k in before)
+        l3b = float(fs2.train_step(ids[pg.rank], tgt[pg.rank]).detach())
+        full = FS.gather_optimizer_state(fs2, dst=None)
+        return same, abs(l3 - l3b) < 1e-5, meta["step"], ck.list(), "blocks.0.attn.qkv.weight" in full
+    for same, cont, step, have, named in run_fake_world(2, run):
+        assert same and cont and step == 3 and have == [(0, 2), (0, 3)] and named
+
+
+def test_tp_checkpoints_and_validator(tmp_path):
+    from ml_framework_b200.checkpoint import tp as TP
+    from ml_framework_b200.checkpoint.distributed import DistributedCheckpoint
+    from ml_framework_b200.dist.process_group import run_fake_world
+
+    def body(pg):
+        st = {"l0.qkv.weight": torch.full((4, 8), float(pg.rank)), "l0.o.weight": torch.full((8, 4), float(pg.rank)), "norm.weight": torch.ones(8)}
+        m = TP.TPCheckpointManager(str(tmp_path / "tp"), pg)
+        m.save(5, st)
+        back = m.load()
+        c = TP.TPCheckpointManager(str(tmp_path / "tpc"), pg, centralized=True)
+        c.save(5, st)
+        cb = c.load()
+        full = TP.DistributedTPCheckpoint(str(tmp_path / "tp" / "step_000000005")).load_full()
+        return all(torch.equal(back[k], st[k]) and torch.equal(cb[k], st[k]) for k in st), {k: tuple(v.shape) for k, v in full.items()}
+    for ok, shapes in run_fake_world(2, body):
+        assert ok and shapes == {"l0.qkv.weight": (8, 8), "l0.o.weight": (8, 8), "norm.weight": (8,)}
+    full = {"w.weight": torch.arange(16.0).view(4, 4)}
+    assert torch.equal(TP.split_tp_state(full, {"w.weight": 1}, 2, 1)["w.weight"], full["w.weight"][:, 2:])
+    ck = DistributedCheckpoint(str(tmp_path / "ms"))
+    ck.save("t1", {"a": torch.ones(4)})
+    v = TP.CheckpointValidator()
+    prefix = ck._prefix("t1")
+    assert v.validate(prefix, {"a": torch.ones(4)}, world_size=1).ok
+    bad = v.validate(prefix, {"missing": torch.ones(1)}, world_size=4)
+    assert not bad.ok and bad.warnings
+
+
+def test_stream_manager_and_async_pipeline_executor_cpu():
+    from ml_framework_b200.parallel.pipeline import AsyncPipelineExecutor, LocalPipelineCommunicator, PipelineStage, StreamManager
+    sm = StreamManager("cpu", 2, 2)
+    sm.record_event("e", sm.compute_stream(0))
+    sm.wait_for_event("e", sm.comm_stream(1))
+    with pytest.raises(KeyError):
+        sm.wait_for_event("nope", None)
