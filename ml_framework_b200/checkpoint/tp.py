@@ -212,7 +212,7 @@ class CheckpointValidator:
         if model_state is not None:
             names = {t.Name for s in meta.Shards for t in s.Tensors}
             for k in model_state:
-                if k not in names and not any(n.startswith(k) for n in names):
+                if k not in names and not any(n.endswith("." + k) or n.startswith(k + ".") for n in names):
                     res.errors.append(f"tensor {k!r} missing from the checkpoint")
         res.ok = not res.errors
         return res
