@@ -33,3 +33,9 @@ def test_tensor_parallel_fused_matches_nccl_two_ranks():
 def test_pipeline_1f1b_and_gpipe_over_nccl_two_stages():
     r = _torchrun("pp_worker.py", 2, 29745)
     assert r.returncode == 0 and "PP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_serving_two_ranks():
+    r = _torchrun("serve_tp_worker.py", 2, 29747)
+    assert r.returncode == 0 and "SERVE_TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
