@@ -4,8 +4,8 @@
 // call the library's C symbols directly and have no device allocator to hand: a C or C++ service
 // that links the shared object without PyTorch has no caching allocator, and one that sits in a
 // latency-critical loop cannot afford cudaMalloc / cudaFree, which synchronise the whole device.
-// mlf_colsum() makes its caller supply an fp32 work buffer of N elements; this variant keeps that
-// work buffer inside the library instead.
+// mlf_colsum() makes its caller supply a work buffer (mlf_colsum_scratch_bytes); this variant keeps
+// its work buffer inside the library instead.
 //
 // Contract
 //   * db    bf16 [N]        out: db[n] = sum_m dy[m, n]   (added to the old db when accumulate != 0)

@@ -235,9 +235,14 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(__nv_bfloat16* dgu, con
 
 // ------------------------------------------------------------------------------------------
 // column sum (bias gradient): db[n] = sum_m dy[m, n]; dy bf16 [M, N] with pitch ld.
-// Each CTA owns 64 columns x a slab of rows; partial sums meet in global fp32 atomics.
+// One launch, no atomics on the data: each CTA owns 64 columns x a slab of rows and writes its fp32
+// partial sums to part[slab][N]; the CTA that finishes last for a column block (a counter per block,
+// reset by that CTA) adds the slabs in slab order and writes bf16. The order of the additions is
+// fixed, so the result is the same from run to run.
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* dy, float* acc, int M, int N, long long ld, int rows_per_cta) {
+__global__ void __launch_bounds__(256) colsum_kernel(__nv_bfloat16* __restrict__ db, const __nv_bfloat16* __restrict__ dy,
+                                                     float* __restrict__ part, unsigned int* __restrict__ counters, int M, int N,
+                                                     long long ld, int rows_per_cta, int accumulate) {
   const int col0 = blockIdx.x * 64;
   const int r0 = blockIdx.y * rows_per_cta;
   const int r1 = min(M, r0 + rows_per_cta);
@@ -257,6 +262,7 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* dy, fl
         if (col0 + cl + j < N) s[j] += __bfloat162float(dy[(long long)r * ld + col0 + cl + j]);
   }
   __shared__ float sm[32][65];
+  __shared__ int s_last;
 #pragma unroll
   for (int j = 0; j < 8; ++j) sm[rl][cl + j] = s[j];
   __syncthreads();
@@ -264,8 +270,21 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* dy, fl
     float t = 0.f;
 #pragma unroll 8
     for (int r = 0; r < 32; ++r) t += sm[r][threadIdx.x];
-    if (col0 + threadIdx.x < N) atomicAdd(&acc[col0 + threadIdx.x], t);
+    if (col0 + threadIdx.x < N) part[(long long)blockIdx.y * N + col0 + threadIdx.x] = t;
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&counters[blockIdx.x], 1u) == gridDim.y - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x < 64 && col0 + threadIdx.x < N) {
+    float t = 0.f;
+    for (int y = 0; y < (int)gridDim.y; ++y) t += __ldcg(part + (long long)y * N + col0 + threadIdx.x);
+    __nv_bfloat16* o = db + col0 + threadIdx.x;
+    *o = __float2bfloat16(t + (accumulate ? __bfloat162float(*o) : 0.f));
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] = 0u;      // ready for the next launch on this stream
 }
 __global__ void cast_f32_to_bf16_kernel(__nv_bfloat16* out, const float* in, long long n, int accumulate) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -414,20 +433,33 @@ MLF_API int mlf_swiglu_bwd(void* dgu, const void* dout, const void* gu, long lon
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
-// db (bf16 [N]) = column sums of dy. scratch: fp32 [N], zeroed here.
-MLF_API int mlf_colsum(void* db, const void* dy, int M, int N, long long ld, float* scratch, int accumulate, uint64_t stream) {
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  MLF_REQUIRE(ld % 8 == 0, "colsum: pitch must be a multiple of 8 elements");
-  MLF_CHECK_CUDA(cudaMemsetAsync(scratch, 0, sizeof(float) * N, st));
-  const int col_ctas = (N + 63) / 64;
-  int row_ctas = (sm_count() * 4 + col_ctas - 1) / col_ctas;
+static void colsum_shape(int M, int N, int& col_ctas, int& row_ctas, int& rows_per_cta) {
+  col_ctas = (N + 63) / 64;
+  row_ctas = (sm_count() * 4 + col_ctas - 1) / col_ctas;
   if (row_ctas > (M + 31) / 32) row_ctas = (M + 31) / 32;
   if (row_ctas < 1) row_ctas = 1;
-  const int rows_per_cta = ((M + row_ctas - 1) / row_ctas + 31) / 32 * 32;
+  rows_per_cta = ((M + row_ctas - 1) / row_ctas + 31) / 32 * 32;
   row_ctas = (M + rows_per_cta - 1) / rows_per_cta;
-  colsum_kernel<<<dim3(col_ctas, row_ctas), 256, 0, st>>>((const __nv_bfloat16*)dy, scratch, M, N, ld, rows_per_cta);
-  count_launch();
-  cast_f32_to_bf16_kernel<<<ew_grid(N), 256, 0, st>>>((__nv_bfloat16*)db, scratch, N, accumulate);
+}
+// Scratch layout of mlf_colsum: ceil(N / 64) counters (uint32, zero before the first use; the kernel
+// leaves them zero), padded to 256 bytes, then row_ctas x N floats of partial sums.
+MLF_API long long mlf_colsum_scratch_bytes(int M, int N) {
+  int c, r, rp;
+  colsum_shape(M, N, c, r, rp);
+  return (((long long)c * 4 + 255) / 256) * 256 + (long long)r * N * 4;
+}
+// db (bf16 [N]) = column sums of dy (+ db when accumulate). One launch; calls that share a scratch
+// buffer must be ordered on one stream.
+MLF_API int mlf_colsum(void* db, const void* dy, int M, int N, long long ld, void* scratch, int accumulate, uint64_t stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  MLF_REQUIRE(ld % 8 == 0, "colsum: pitch must be a multiple of 8 elements");
+  MLF_REQUIRE(scratch != nullptr && M > 0 && N > 0, "colsum: bad arguments");
+  int col_ctas, row_ctas, rows_per_cta;
+  colsum_shape(M, N, col_ctas, row_ctas, rows_per_cta);
+  unsigned int* counters = static_cast<unsigned int*>(scratch);
+  float* part = reinterpret_cast<float*>(static_cast<char*>(scratch) + (((long long)col_ctas * 4 + 255) / 256) * 256);
+  colsum_kernel<<<dim3(col_ctas, row_ctas), 256, 0, st>>>((__nv_bfloat16*)db, (const __nv_bfloat16*)dy, part, counters, M, N, ld,
+                                                          rows_per_cta, accumulate);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

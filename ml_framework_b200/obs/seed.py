@@ -28,7 +28,7 @@ class DeterministicModeFlags(enum.IntFlag):
 KNOWN_NON_DETERMINISTIC_OPERATIONS = {
     "flash_bwd (dQ accumulated with fp32 atomics across key tiles)": "bitwise run-to-run differences in dQ at the 1e-6 level",
     "embedding_bwd (fp32 atomics on repeated token ids)": "order of accumulation for repeated ids",
-    "colsum / norm_bwd parameter gradients (fp32 atomics across row slabs)": "order of slab accumulation",
+    "norm_bwd parameter gradients (fp32 atomics across row slabs)": "order of slab accumulation",
     "index_add / scatter_add (PyTorch)": "atomics",
 }
 

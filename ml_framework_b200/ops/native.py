@@ -153,8 +153,15 @@ def colsum(dy: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: boo
     assert dy.dim() == 2 and dy.stride(1) == 1
     M, N = dy.shape
     out = torch.empty(N, dtype=torch.bfloat16, device=dy.device) if out is None else out
-    sc = scratch("colsum", N * 4, dy.device)
-    _lib.check(_L().mlf_colsum(_p(out), _p(dy), M, N, C.c_longlong(dy.stride(0)), _p(sc), int(accumulate), _st()), "mlf_colsum")
+    L = _L()
+    L.mlf_colsum_scratch_bytes.restype = C.c_longlong
+    need = int(L.mlf_colsum_scratch_bytes(M, N))
+    key = ("colsum0", dy.device.index)
+    sc = _scratch.get(key)
+    if sc is None or sc.numel() < need:                  # zero-filled once: the kernel keeps its counters at zero
+        sc = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dy.device)
+        _scratch[key] = sc
+    _lib.check(L.mlf_colsum(_p(out), _p(dy), M, N, C.c_longlong(dy.stride(0)), _p(sc), int(accumulate), _st()), "mlf_colsum")
     return out
 
 
