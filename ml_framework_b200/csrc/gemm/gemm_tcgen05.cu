@@ -332,8 +332,9 @@ MLF_API int mlf_get_gemm_2cta() { return g_use_2cta; }
 
 MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
   MLF_REQUIRE(a != nullptr, "null args");
-  if (a->tile_n == 512 || (g_use_2cta && a->tile_n == 0 && a->M >= 1024 && a->N >= 1024 &&
-                           (long long)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 64)) {
+  // CTA pairs for everything with at least 16 pair tiles (split-K fills the GPU when tiles alone cannot)
+  if (a->tile_n == 512 || (g_use_2cta && a->tile_n == 0 && a->M >= 512 && a->N >= 512 &&
+                           (long long)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 16)) {
     const int rc2 = mlf_gemm_bf16_2cta(a, stream);
     if (rc2 != -4) return rc2;
   }

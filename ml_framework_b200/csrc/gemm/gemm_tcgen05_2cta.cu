@@ -94,11 +94,19 @@ struct alignas(64) PeerMaps {
   CUtensorMap m[8];
 };
 
+// TMA reduction store: global[tile] += shared[tile], element type taken from the tensor map (bf16).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tm, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmPre,
                          const __grid_constant__ CUtensorMap tmAux, const __grid_constant__ PeerMaps peer_maps,
-                         const GemmKernelParams p, const int tma_epilogue, const int tma_aux) {
+                         const GemmKernelParams p, const int tma_epilogue, const int tma_aux, const int k_splits,
+                         const int reduce_out) {
   // Copy CTAs come in whole clusters (their count is even) and never touch the cluster barrier.
   if ((int)blockIdx.x < p.n_copy_ctas) {
     gather_copy_role(p);
@@ -153,8 +161,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   const int pair = ((int)blockIdx.x - p.n_copy_ctas) >> 1;
   const int n_pairs = ((int)gridDim.x - p.n_copy_ctas) >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;   // tiles of 256 x 256
-  const int num_kb = (p.K + BK - 1) / BK;
+  // Work items: (tile, k-split). Splits of one tile are consecutive items, their partial products meet in
+  // global memory through TMA reduction stores (the host cleared or kept `out` accordingly).
+  const int num_tiles = p.tiles_m * p.tiles_n * k_splits;   // tiles of 256 x 256, times splits
+  const int num_kb_all = (p.K + BK - 1) / BK;
+  const int kb_per = (num_kb_all + k_splits - 1) / k_splits;
 
   if (warp == 0) {
     // ===================== TMA producer (both CTAs) =====================
@@ -163,7 +174,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t ph = 0;
       for (int t = pair; t < num_tiles; t += n_pairs) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
+        tile_coords(t / k_splits, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
+        const int kb0 = (t % k_splits) * kb_per, kb1 = min(num_kb_all, kb0 + kb_per);
+        if (kb0 >= kb1) continue;
         const int m0 = tm * 256 + (int)rank * BM;
         const int n0 = tn * T2_BN + (int)rank * T2_BNH;
         bool ok = true;
@@ -176,7 +189,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (!ok) break;
           fence_proxy_async_all();
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
           const uint32_t sa = smem_base + s * T2_STAGE;
           const uint32_t sb = sa + T2_STAGE_A;
@@ -210,13 +223,15 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += n_pairs, ++it) {
+      for (int t = pair; t < num_tiles && ok; t += n_pairs) {
+        const int kb0 = (t % k_splits) * kb_per, kb1 = min(num_kb_all, kb0 + kb_per);
+        if (kb0 >= kb1) continue;
         const int acc = it & 1;
         const uint32_t acc_ph = (it >> 1) & 1;
         if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * T2_BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(s), ph, abort_flag, p.err, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_base + s * T2_STAGE;
@@ -225,7 +240,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = make_smem_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t bd = make_smem_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            umma_bf16_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss_pair(d_tmem, ad, bd, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit_pair(mapa_u32(empty_bar(s), 0));
           umma_commit_pair(mapa_u32(empty_bar(s), 1));
@@ -235,6 +250,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           umma_commit_pair(mapa_u32(tfull_bar(acc), 0));
           umma_commit_pair(mapa_u32(tfull_bar(acc), 1));
         }
+        ++it;
       }
     }
   } else {
@@ -245,11 +261,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const bool dswiglu = (p.flags & MLF_EPI_DSWIGLU) != 0;
     uint32_t epi_units = 0;
     int it = 0;
-    for (int t = pair; t < num_tiles; t += n_pairs, ++it) {
+    for (int t = pair; t < num_tiles; t += n_pairs) {
+      if ((t % k_splits) * kb_per >= min(num_kb_all, (t % k_splits) * kb_per + kb_per)) continue;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
+      tile_coords(t / k_splits, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm, tn);
       const int m = tm * 256 + (int)rank * BM + q * 32 + lane;
       const int n0 = tn * T2_BN;
       if (!mbar_wait_warp(tfull_bar(acc), acc_ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL)) break;
@@ -301,6 +318,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (p.scatter_out) {                 // the whole 128-row block belongs to one owner (possibly a peer)
               const int owner = min(m_tile / p.rows_per_owner, p.world - 1);
               tma_store_2d(&peer_maps.m[owner], buf, x, p.rank * p.rows_per_owner + (m_tile - owner * p.rows_per_owner));
+            } else if (reduce_out) {
+              tma_reduce_add_2d(tmap, buf, x, m_tile);
             } else {
               tma_store_2d(tmap, buf, x, m_tile);
             }
@@ -310,7 +329,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               bool have = nx < n0 + T2_BN && nx < p.N;
               if (!have && t + n_pairs < num_tiles) {
                 int tm2, tn2;
-                tile_coords(t + n_pairs, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm2, tn2);
+                tile_coords((t + n_pairs) / k_splits, p.tiles_m, p.tiles_n, p.rot_m, p.rot_n, tm2, tn2);
                 nx = tn2 * T2_BN;
                 ny = tm2 * 256 + (int)rank * BM;
                 have = true;
@@ -408,6 +427,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
+      ++it;
     }
     if (tma_epilogue && warp == 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until the copies have read it
   }
@@ -512,7 +532,8 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   memset(&peer_maps, 0, sizeof(peer_maps));
   int tma_epi = 0, tma_aux = 0;
   const bool scatter = cm && cm->scatter_out;
-  if (!(a->flags & (MLF_EPI_OUT_FP32 | MLF_EPI_SWIGLU | MLF_EPI_DSWIGLU | MLF_EPI_ACCUM)) && a->ldo % 8 == 0 &&
+  const bool plain = (a->flags & ~MLF_EPI_ACCUM) == 0 && cm == nullptr;      // nothing but (optionally) out += product
+  if (!(a->flags & (MLF_EPI_OUT_FP32 | MLF_EPI_SWIGLU | MLF_EPI_DSWIGLU)) && (!(a->flags & MLF_EPI_ACCUM) || plain) && a->ldo % 8 == 0 &&
       (scatter || (reinterpret_cast<uintptr_t>(a->out) & 15) == 0) &&
       (!(a->flags & MLF_EPI_STORE_PRE) || (a->ld_aux_out % 8 == 0 && (reinterpret_cast<uintptr_t>(a->aux_out) & 15) == 0))) {
     if (scatter) {
@@ -565,7 +586,29 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   if (pairs > max_clusters[dev & 63]) pairs = max_clusters[dev & 63];
   if (pairs > num_tiles) pairs = num_tiles;
   if (pairs < 1) pairs = 1;
-  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, tmAux, peer_maps, p, tma_epi, tma_aux);
+  // Split K when the tiles alone cannot fill the GPU (weight gradients of narrow layers: few tiles, long K).
+  // Splits add their partial products into `out` with TMA reduction stores.
+  int k_splits = 1;
+  if (plain && tma_epi) {
+    const int kb_all = (a->K + BK - 1) / BK;
+    int avail = sms / 2;
+    if (avail > max_clusters[dev & 63]) avail = max_clusters[dev & 63];
+    double best = (double)((num_tiles + avail - 1) / avail);
+    for (int ks = 2; ks <= 8; ++ks) {
+      if (kb_all / ks < 8) break;
+      const double cost = (double)((num_tiles * ks + avail - 1) / avail) / ks;
+      if (cost < best * 0.9) { best = cost; k_splits = ks; }
+    }
+  }
+  const int reduce_out = (k_splits > 1 || (a->flags & MLF_EPI_ACCUM)) ? 1 : 0;
+  if (k_splits > 1 && !(a->flags & MLF_EPI_ACCUM))
+    MLF_CHECK_CUDA(cudaMemset2DAsync(a->out, (size_t)a->ldo * 2, 0, (size_t)a->N * 2, (size_t)a->M, st));
+  pairs = sms / 2;
+  if (pairs > max_clusters[dev & 63]) pairs = max_clusters[dev & 63];
+  if (pairs > num_tiles * k_splits) pairs = num_tiles * k_splits;
+  if (pairs < 1) pairs = 1;
+  gemm_tcgen05_2cta_kernel<<<n_copy + 2 * pairs, kGemmThreads, T2_SMEM, st>>>(tmA, tmB, tmOut, tmPre, tmAux, peer_maps, p, tma_epi, tma_aux,
+                                                                              k_splits, reduce_out);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

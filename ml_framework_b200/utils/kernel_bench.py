@@ -65,6 +65,12 @@ GEMM_SHAPES = [
     ("gpt1.3b lm head", 8192, 50304, 2048, False, False),
     ("llama8b tp8 gate_up", 32768, 3584, 4096, False, False),
     ("llama8b tp8 down", 32768, 4096, 1792, False, False),
+    ("llama8b tp8 qkv", 32768, 768, 4096, False, False),
+    ("llama8b tp8 o", 32768, 4096, 512, False, False),
+    ("llama8b tp8 o wgrad", 4096, 512, 32768, True, True),
+    ("llama8b tp8 qkv wgrad", 768, 4096, 32768, True, True),
+    ("llama8b tp8 gate_up dgrad", 32768, 4096, 3584, False, True),
+    ("llama8b tp8 lm head", 32768, 16032, 4096, False, False),
     ("square 8192", 8192, 8192, 8192, False, False),
     ("decode m=256 qkv", 256, 768, 4096, False, False),
 ]

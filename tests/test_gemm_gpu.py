@@ -148,3 +148,22 @@ def test_cta_pair_kernel(a_mn, b_mn):
     out = gemm(a, b, tile_n=512)
     ref, _ = gemm_reference(a, b)
     _check(out, ref, 320)
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(4096, 512, 8192, True, True), (768, 4096, 8192, True, True), (1024, 1024, 4096, False, False),
+                                            (520, 1000, 2112, False, True)])
+def test_split_k_and_accumulate_pair_kernel(M, N, K, a_mn, b_mn):
+    """Few tiles and a long K: the CTA-pair kernel splits K and the splits meet in `out` through TMA reduction
+    stores; with the accumulate flag the product is added to what `out` held."""
+    torch.manual_seed(4)
+    a = _mk(M, K, a_mn, "cuda", 0.25)
+    b = _mk(N, K, b_mn, "cuda", 0.25)
+    ref, _ = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    _check(out, ref, K)
+    prev = (torch.randn(M, N, device="cuda") * ref.abs().mean()).to(torch.bfloat16)
+    out2 = prev.clone()
+    gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out2, flags=_lib.EPI_ACCUM)
+    torch.cuda.synchronize()
+    _check(out2, ref + prev.float(), K)
