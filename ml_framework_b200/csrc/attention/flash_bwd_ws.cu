@@ -7,8 +7,10 @@
 //   P^T  = exp2(S^T c - lse)        -> packed bf16 into TENSOR MEMORY over S^T (A operand of dV)
 //   dS^T = P^T o (dP^T - delta) c   -> packed bf16 into shared memory        (operand of dK and dQ)
 //   dV  += P^T  dO       dK  += dS^T Q                 (M128 N128 K128)
-//   dQ   = dS   K        (M = query rows)  -> read out by its own warpgroup, added to the fp32 dQ
-//                                            buffer with 16-byte vector reductions (one row per thread)
+//   dQ   = dS   K        (M = query rows)  -> read out by its own warpgroup into swizzled staging tiles
+//                                            and added to the fp32 dQ buffer by TMA reduction stores
+//                                            (per-thread reductions saturate the L2 atomic path and
+//                                            the load/store unit the other warpgroup needs)
 // The same 128B-swizzled tiles serve as K-major or MN-major operands through their descriptors, so
 // nothing is ever transposed in memory.
 //
@@ -35,7 +37,8 @@ constexpr int G_THREADS = 384;
 constexpr int G_TILE = G_T * G_D * 2;          // 32 KB: two 64-column blocks of 16 KB
 constexpr int G_HALF = G_TILE / 2;
 constexpr int G_STATS = 2 * G_T * 4;           // lse (log2 domain) | delta, fp32, per stage
-constexpr int G_SMEM = 7 * G_TILE + 2 * G_STATS + 256;
+constexpr int G_DQ_STG = G_T * 32 * 4;         // dQ staging tile: 128 rows x 32 fp32 columns, 128B-swizzled
+constexpr int G_SMEM = 7 * G_TILE + 2 * G_STATS + 256;   // K, V, Q x 2, dO, dS, 2 staging tiles (= 1 tile)
 constexpr int G_TMEM_COLS = 512;
 
 struct FlashBwdWsParams {
@@ -55,32 +58,30 @@ __device__ __forceinline__ void bulk_g2s(uint32_t smem_dst, const void* src, uin
                ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 __global__ void __launch_bounds__(G_THREADS, 1)
 flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const FlashBwdWsParams p) {
+                    const __grid_constant__ CUtensorMap tmDQ, const FlashBwdWsParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const uint32_t sK = sbase;
   const uint32_t sV = sK + G_TILE;
-  auto sQ = [&](int s) { return sV + G_TILE + (uint32_t)s * 2u * G_TILE; };
-  auto sdO = [&](int s) { return sQ(s) + G_TILE; };
-  const uint32_t sdS = sV + 5u * G_TILE;
-  const uint32_t sStats = sdS + G_TILE;                     // stage s at + s * G_STATS
+  auto sQ = [&](int s) { return sV + G_TILE + (uint32_t)s * G_TILE; };
+  const uint32_t sdO = sV + 3u * G_TILE;                  // single buffer: reloaded once dV of the previous tile has read it
+  const uint32_t sdS = sV + 4u * G_TILE;
+  const uint32_t sStg = sV + 5u * G_TILE;                  // two dQ staging tiles of 16 KB
+  const uint32_t sStats = sStg + G_TILE;                    // stage s at + s * G_STATS
   const uint32_t bars = sStats + 2 * G_STATS;
-  // barriers: kv_full, q_full[2], q_empty[2], s_full, dp_full, p_full, ds_full, dq_full, dq_empty
+  // barriers: kv_full, q_full[2], q_empty[2], s_full, dp_full, p_full, ds_full, dq_full, dq_empty, do_full, do_empty, stg_bar
   const uint32_t kv_full = bars;
   auto q_full = [&](int s) { return bars + 8u * (1 + s); };
   auto q_empty = [&](int s) { return bars + 8u * (3 + s); };
   const uint32_t s_full = bars + 8u * 5, dp_full = bars + 8u * 6, p_full = bars + 8u * 7, ds_full = bars + 8u * 8,
-                 dq_full = bars + 8u * 9, dq_empty = bars + 8u * 10;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + (bars - sbase) + 8 * 11);
+                 dq_full = bars + 8u * 9, dq_empty = bars + 8u * 10, do_full = bars + 8u * 11, do_empty = bars + 8u * 12,
+                 stg_bar = bars + 8u * 13;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + (bars - sbase) + 8 * 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
-  const float* stats = reinterpret_cast<const float*>(smem + (sStats - sbase));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -113,6 +114,9 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(ds_full, 128);
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 128);
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
+    mbar_init(stg_bar, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -144,13 +148,15 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const int q0 = (qt0 + it % per_head) * G_T;
           const int qrow = (int)(row_base + q0);
           const long long sidx = ((long long)b * p.Hq + h) * p.S + q0;
-          mbar_expect_tx(q_full(s), 2 * G_TILE + G_STATS);
+          mbar_expect_tx(q_full(s), G_TILE + G_STATS);
           tma_load_2d(sQ(s), &tmQ, h * G_D, qrow, q_full(s));
           tma_load_2d(sQ(s) + G_HALF, &tmQ, h * G_D + 64, qrow, q_full(s));
-          tma_load_2d(sdO(s), &tmdO, h * G_D, qrow, q_full(s));
-          tma_load_2d(sdO(s) + G_HALF, &tmdO, h * G_D + 64, qrow, q_full(s));
           bulk_g2s(sStats + s * G_STATS, p.lse2 + sidx, G_T * 4, q_full(s));
           bulk_g2s(sStats + s * G_STATS + G_T * 4, p.delta + sidx, G_T * 4, q_full(s));
+          if (!mbar_wait(do_empty, (it & 1) ^ 1u, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+          mbar_expect_tx(do_full, G_TILE);
+          tma_load_2d(sdO, &tmdO, h * G_D, qrow, do_full);
+          tma_load_2d(sdO + G_HALF, &tmdO, h * G_D + 64, qrow, do_full);
         }
       }
     } else if (warp == 1) {
@@ -172,8 +178,12 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_fence_after_sync();
           issue_kk(t_S, sK, sQ(0));
           umma_commit(s_full);
-          issue_kk(t_dP, sV, sdO(0));
-          umma_commit(dp_full);
+          ok = mbar_wait(do_full, 0, abort_flag, p.err, ERR_WAIT_ATTN);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_kk(t_dP, sV, sdO);
+            umma_commit(dp_full);
+          }
         }
         for (int it = 0; it < n_it && ok; ++it) {
           const int s = it & 1;
@@ -181,7 +191,8 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_fence_after_sync();
 #pragma unroll
           for (int k = 0; k < G_T / 16; ++k)     // dV += P^T dO   (A from tensor memory)
-            umma_bf16_ts(t_dV, t_S + 8u * k, make_smem_desc_sw128(sdO(s) + k * 2048, G_HALF, 1024), idesc_kn, (it | k) != 0);
+            umma_bf16_ts(t_dV, t_S + 8u * k, make_smem_desc_sw128(sdO + k * 2048, G_HALF, 1024), idesc_kn, (it | k) != 0);
+          umma_commit(do_empty);                   // dO of this tile has been read (dP^T earlier, dV now)
           const bool more = it + 1 < n_it;
           if (more) {                              // S^T of the next tile goes in behind dV
             if (!mbar_wait(q_full(s ^ 1), ((it + 1) >> 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
@@ -207,8 +218,9 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           umma_commit(q_empty(s));
           if (more) {                              // dP^T of the next tile needs the dQ columns back
             if (!mbar_wait(dq_empty, it & 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
+            if (!mbar_wait(do_full, (it + 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) break;
             tc_fence_after_sync();
-            issue_kk(t_dP, sV, sdO(s ^ 1));
+            issue_kk(t_dP, sV, sdO);
             umma_commit(dp_full);
           }
         }
@@ -225,35 +237,42 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int it = 0; it < n_it; ++it) {
       const int s = it & 1;
       const int q0 = (qt0 + it % per_head) * G_T;
-      const float* st = stats + s * (G_STATS / 4);
       const bool need_mask = (p.causal && q0 < k0 + G_T - 1) || (q0 + G_T > p.S) || (k0 + G_T > p.S);
       // the statistics arrive with Q / dO on q_full
       if (!mbar_wait_warp(q_full(s), (it >> 1) & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
       if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t pk[64];
-      {
-        uint32_t sv[128];
+      const uint32_t st_addr = sStats + s * G_STATS;     // shared-window address of this stage's statistics
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_S + 32 * c + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
+      for (int hh = 0; hh < 2; ++hh) {
+        // 64 columns at a time: S^T from tensor memory and the 64 row statistics from shared memory are
+        // all requested up front (explicit shared-space vector loads, issued back to back) so that
+        // their latencies overlap instead of preceding every group of four exponentials
+        uint32_t sv[64];
+        tmem_ld_32x32b_x32(t_S + 64 * hh + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld_32x32b_x32(t_S + 64 * hh + 32 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        float4 ls[16];
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4)
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(ls[c4].x), "=f"(ls[c4].y), "=f"(ls[c4].z), "=f"(ls[c4].w)
+                       : "r"(st_addr + (64 * hh + 4 * c4) * 4));
         tmem_wait_ld();
+        if (need_mask) {                         // diagonal / ragged tiles only: masked scores become -inf, exp2 gives 0
 #pragma unroll
-        for (int c4 = 0; c4 < 32; ++c4) {
-          const float4 ls = *reinterpret_cast<const float4*>(st + 4 * c4);
-          float pr[4];
-          pr[0] = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 0]), p.scale_log2, -ls.x));
-          pr[1] = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 1]), p.scale_log2, -ls.y));
-          pr[2] = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 2]), p.scale_log2, -ls.z));
-          pr[3] = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 3]), p.scale_log2, -ls.w));
-          if (need_mask) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int qi = q0 + 4 * c4 + e;
-              if (qi >= p.S || kv_i >= p.S || (p.causal && qi < kv_i)) pr[e] = 0.f;
-            }
+          for (int i = 0; i < 64; ++i) {
+            const int qi = q0 + 64 * hh + i;
+            if (qi >= p.S || kv_i >= p.S || (p.causal && qi < kv_i)) sv[i] = __float_as_uint(-INFINITY);
           }
-          pk[2 * c4] = pack_bf16x2(pr[0], pr[1]);
-          pk[2 * c4 + 1] = pack_bf16x2(pr[2], pr[3]);
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 0]), p.scale_log2, -ls[c4].x));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 1]), p.scale_log2, -ls[c4].y));
+          const float p2 = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 2]), p.scale_log2, -ls[c4].z));
+          const float p3 = exp2f(fmaf(__uint_as_float(sv[4 * c4 + 3]), p.scale_log2, -ls[c4].w));
+          pk[32 * hh + 2 * c4] = pack_bf16x2(p0, p1);
+          pk[32 * hh + 2 * c4 + 1] = pack_bf16x2(p2, p3);
         }
       }
       tmem_st_32x32b_x32(t_S + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
@@ -269,11 +288,16 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint32_t dp[64];
         tmem_ld_32x32b_x32(t_dP + 64 * hh + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
         tmem_ld_32x32b_x32(t_dP + 64 * hh + 32 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+        float4 dls[16];
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4)
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(dls[c4].x), "=f"(dls[c4].y), "=f"(dls[c4].z), "=f"(dls[c4].w)
+                       : "r"(st_addr + (G_T + 64 * hh + 4 * c4) * 4));
         tmem_wait_ld();
         uint32_t dsk[32];
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 dl = *reinterpret_cast<const float4*>(st + G_T + 64 * hh + 4 * c4);
+          const float4 dl = dls[c4];
           const uint32_t pa = pk[32 * hh + 2 * c4], pb = pk[32 * hh + 2 * c4 + 1];
           const float d0 = __uint_as_float(pa << 16) * (__uint_as_float(dp[4 * c4 + 0]) - dl.x) * p.scale;
           const float d1 = __uint_as_float(pa & 0xffff0000u) * (__uint_as_float(dp[4 * c4 + 1]) - dl.y) * p.scale;
@@ -332,6 +356,8 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int qd = warp & 3;
     const int r = qd * 32 + lane;
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const bool elected = warp == 8 && lane == 0;
+    uint32_t units = 0;                        // staging tiles handed to the copy engine so far
     for (int it = 0; it < n_it; ++it) {
       const int h = hkv * group + it / per_head;
       const int q0 = (qt0 + it % per_head) * G_T;
@@ -343,14 +369,35 @@ flash_bwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(dq_empty);
-      if (q0 + r < p.S) {
-        float* row = p.dq_accum + (row_base + q0 + r) * (long long)(p.Hq * G_D) + h * G_D;
+      // Rows past the end of this sequence would land in the next sequence's rows: they add zeros.
+      const bool row_ok = q0 + r < p.S;
+      bool ok = true;
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
-          red_add_v4(row + 4 * c, __uint_as_float(dq[4 * c]), __uint_as_float(dq[4 * c + 1]), __uint_as_float(dq[4 * c + 2]),
-                     __uint_as_float(dq[4 * c + 3]));
+      for (int u = 0; u < 4; ++u) {            // four 32-column units of 128 bytes per row
+        const uint32_t buf = sStg + (units & 1u) * G_DQ_STG;
+        const uint32_t rowaddr = buf + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t addr = rowaddr + (((uint32_t)c ^ (uint32_t)(r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(row_ok ? dq[32 * u + 4 * c] : 0u),
+                       "r"(row_ok ? dq[32 * u + 4 * c + 1] : 0u), "r"(row_ok ? dq[32 * u + 4 * c + 2] : 0u),
+                       "r"(row_ok ? dq[32 * u + 4 * c + 3] : 0u) : "memory");
+        }
+        fence_proxy_async_smem();
+        if (elected) tma_store_wait_read<0>();  // the previous unit's tile has been read: its buffer is free after the meeting point
+        mbar_arrive(stg_bar);
+        if (!mbar_wait_warp(stg_bar, units & 1u, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
+        if (elected) {
+          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                       ::"l"(reinterpret_cast<uint64_t>(&tmDQ)), "r"(buf), "r"(h * G_D + 32 * u), "r"((int)(row_base + q0))
+                       : "memory");
+          tma_store_commit();
+        }
+        ++units;
       }
+      if (!ok) break;
     }
+    if (elected) tma_store_wait_all<0>();
     tc_fence_before_sync();
   }
 
@@ -390,8 +437,14 @@ int launch_flash_bwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
     MLF_CHECK_CUDA(cudaFuncSetAttribute(flash_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM));
     attr_set[dev & 63] = true;
   }
+  // fp32 dQ accumulator as a 2-D tensor [tokens, Hq * 128]: tiles of 32 columns x 128 rows, 128B swizzle
+  CUtensorMap tdq;
+  {
+    const int rc = make_tmap_2d(&tdq, dq_accum, 4, (uint64_t)Hq * G_D, (uint64_t)B * S, (uint64_t)Hq * G_D, 32, 128, true);
+    if (rc) return rc;
+  }
   dim3 grid(((S + G_T - 1) / G_T) * Hkv * B);
-  flash_bwd_ws_kernel<<<grid, G_THREADS, G_SMEM, st>>>(tq, tk, tv, tdo, p);
+  flash_bwd_ws_kernel<<<grid, G_THREADS, G_SMEM, st>>>(tq, tk, tv, tdo, tdq, p);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
