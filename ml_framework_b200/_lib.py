@@ -96,6 +96,8 @@ def get() -> C.CDLL:
             lib.mlf_set_flash_ws(int(os.environ["MLF_FLASH_WS"]))
         if os.environ.get("MLF_GEMM_2CTA") is not None:
             lib.mlf_set_gemm_2cta(int(os.environ["MLF_GEMM_2CTA"]))
+        if os.environ.get("MLF_GEMM_SMALL_M_SPLIT") is not None:
+            lib.mlf_set_gemm_small_m_split(int(os.environ["MLF_GEMM_SMALL_M_SPLIT"]))
         _lib = lib
         return lib
 

@@ -11,9 +11,9 @@
 // src/MLFramework/Inference/PagedAttention/Kernels/StandardPagedAttentionKernel.cs:21-84, with the
 // block-table gather folded in, which the reference leaves outside the kernel and stubs,
 // PagedAttentionLayer.cs:368-389). The kernel is HBM-bound: a CTA owns one (sequence, kv head,
-// split) and streams K and V rows with 16-byte loads, 16 lanes per token row, sharing every
-// loaded row between the G = Hq/Hkv query heads of the group. Long sequences are split over
-// grid.z (flash-decoding) and merged by a second small kernel.
+// split), stages K and V rows in shared memory with asynchronous 16-byte copies (16 lanes per token
+// row) and shares every row between the G = Hq/Hkv query heads of the group. Sequences are split
+// over grid.z (flash-decoding) and merged by a second small kernel.
 //
 // kv_cache_write: scatter new K/V rows into their slots (PagedAttentionLayer.UpdateKVCache :244-296).
 // kv_gather: copy a sequence's pages into a contiguous buffer (for chunked prefill over a cached prefix).
@@ -27,7 +27,11 @@ namespace mlf {
 
 constexpr int PD = 128;           // head dim
 constexpr int P_THREADS = 128;
-constexpr int P_SUB = 128;        // tokens per inner chunk
+constexpr int P_SUB = 128;        // granularity of the host's split size
+constexpr int P_CH = 64;          // tokens per staged chunk
+constexpr int P_STAGES = 2;
+constexpr int P_CH_BYTES = P_CH * PD * 2;               // 16 KB: one chunk of K (or V) rows of one kv head
+constexpr int P_SMEM = 2 * P_STAGES * P_CH_BYTES;       // K ring + V ring
 constexpr int P_MAXG = 8;         // max query heads per kv head
 
 struct PagedDecodeParams {
@@ -37,25 +41,58 @@ struct PagedDecodeParams {
   const int* seq_lens;            // [B]
   __nv_bfloat16* out;             // [B, Hq, 128]
   float* ws;                      // [B, Hkv, splits, G, 130] (m, l, o[128]) when splits > 1
-  int B, Hq, Hkv, G, block_size, max_blocks, num_blocks, split_tokens, splits;
+  int B, Hq, Hkv, G, block_size, bs_shift, max_blocks, num_blocks, split_tokens, splits;   // bs_shift: log2(block_size) or -1
   float scale_log2;
   int* err;
 };
 
+// 16-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros (rows past the sequence end)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8, fp32) += A(16x16, bf16, row) B(16x8, bf16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Byte offset of 16-byte column `c16` (0..15) of token row `row` inside a staged chunk: rows are
+// 256 bytes, columns XOR-swizzled with the row so that the eight rows of an 8 x 8 matrix fetch
+// (same column, consecutive rows) fall into eight different bank groups.
+__device__ __forceinline__ uint32_t chunk_off(int row, int c16) { return (uint32_t)(row * 256 + ((c16 ^ (row & 7)) << 4)); }
+
+// The kernel is bound by bytes in flight, not by arithmetic: K and V rows are staged through shared
+// memory with asynchronous 16-byte copies (two chunks of 64 tokens of K and of V, up to 64 KB per
+// CTA, in flight while the previous chunk is multiplied), so the amount outstanding does not depend
+// on registers. The G query heads of the group are the (zero-padded) 16 rows of a warp-level
+// m16n8k16 tensor-core product: one query token gives at most 8 rows, far below the 64-row minimum
+// of the tcgen05 path, and this way a chunk costs a warp ~100 instructions instead of ~1000 scalar
+// ones. Each warp owns 16 tokens of every chunk with its own running (max, sum, output); the four
+// warps merge at the end. Each sequence divides its own length evenly over the launch's splits.
 template <int G>
 __global__ void __launch_bounds__(P_THREADS)
 paged_decode_kernel(const PagedDecodeParams p) {
+  extern __shared__ __align__(128) uint8_t p_dsm[];
   const int b = blockIdx.x, hkv = blockIdx.y, sp = blockIdx.z;
   const int len = p.seq_lens[b];
-  const int t_lo = sp * p.split_tokens;
-  const int t_hi = min(len, t_lo + p.split_tokens);
-  const int tid = threadIdx.x;
-  const int tg = tid >> 4;        // token group 0..7
-  const int dl = tid & 15;        // 16 lanes x 8 elements = 128
-  __shared__ float s_q[G][PD];
-  __shared__ float s_p[G][P_SUB];
-  __shared__ float s_red[8][G][PD + 2];
-  __shared__ float s_m[G], s_l[G], s_alpha[G];
+  int per = (len + p.splits - 1) / p.splits;
+  per = (per + P_CH - 1) / P_CH * P_CH;
+  const int t_lo = sp * per;
+  const int t_hi = min(len, t_lo + per);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tg = tid >> 4;        // loader: token group 0..7
+  const int dl = tid & 15;        // loader: 16-byte column of the row
 
   float* ws = p.ws ? p.ws + ((((long long)b * p.Hkv + hkv) * p.splits + sp) * G) * (PD + 2) : nullptr;
   if (t_lo >= t_hi) {
@@ -67,143 +104,150 @@ paged_decode_kernel(const PagedDecodeParams p) {
     }
     return;
   }
-  for (int i = tid; i < G * PD; i += P_THREADS)
-    s_q[i / PD][i % PD] = __bfloat162float(p.q[((long long)b * p.Hq + hkv * G) * PD + i]) * p.scale_log2;
-  if (tid < G) { s_m[tid] = -INFINITY; s_l[tid] = 0.f; }
-  float acc[G][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
-  __syncthreads();
-  float qreg[G][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) qreg[g][j] = s_q[g][dl * 8 + j];
-
   const long long blk_stride = 2LL * p.block_size * p.Hkv * PD;   // elements per physical block
   const long long v_off = (long long)p.block_size * p.Hkv * PD;
   const int* bt = p.block_table + (long long)b * p.max_blocks;
+  const uint32_t sK = smem_u32(p_dsm), sV = sK + P_STAGES * P_CH_BYTES;
+  const int n_ch = (t_hi - t_lo + P_CH - 1) / P_CH;
 
-  for (int c0 = t_lo; c0 < t_hi; c0 += P_SUB) {
-    const int cn = min(P_SUB, t_hi - c0);
-    // ---- scores for up to 128 tokens: 8 tokens per step, 16 lanes per token; the 16-byte loads of
-    // four steps are issued together so that four rows per thread are in flight (the kernel is
-    // bound by memory latency x bytes in flight, not by arithmetic)
-#pragma unroll 1
-    for (int i0 = tg; i0 < P_SUB; i0 += 32) {
-      uint4 u[4];
+  // one commit group per chunk (its K and V rows), also when the chunk does not exist, so that the
+  // group arithmetic of the waits below is the same in every iteration
+  auto issue = [&](int c) {
+    if (c < n_ch) {
+      const uint32_t stage = (c % P_STAGES) * P_CH_BYTES;
+      const int tbase = t_lo + c * P_CH;
+      int tt[P_CH / 8], lb[P_CH / 8], blk[P_CH / 8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = i0 + 8 * e;
-        u[e] = make_uint4(0, 0, 0, 0);
-        if (i < cn) {
-          const int t = c0 + i;
-          int blk = bt[t / p.block_size];
-          if (blk < 0 || blk >= p.num_blocks) { atomicCAS(p.err, 0, ERR_BAD_INDEX); blk = 0; }
-          u[e] = *reinterpret_cast<const uint4*>(p.cache + blk * blk_stride + ((long long)(t % p.block_size) * p.Hkv + hkv) * PD + dl * 8);
-        }
+      for (int e = 0; e < P_CH / 8; ++e) {     // the table entries first: eight independent loads
+        const int t = tbase + tg + 8 * e;
+        tt[e] = t < t_hi ? t : t_lo;
+        lb[e] = p.bs_shift >= 0 ? (tt[e] >> p.bs_shift) : (tt[e] / p.block_size);
+        blk[e] = bt[lb[e]];
       }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = i0 + 8 * e;
-        float s[G];
-        float k[8];
-        const float2 a = unpack_bf16x2(u[e].x), bb = unpack_bf16x2(u[e].y), c = unpack_bf16x2(u[e].z), d = unpack_bf16x2(u[e].w);
-        k[0] = a.x; k[1] = a.y; k[2] = bb.x; k[3] = bb.y; k[4] = c.x; k[5] = c.y; k[6] = d.x; k[7] = d.y;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          s[g] = 0.f;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) s[g] += qreg[g][j] * k[j];
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-          if (dl == 0) s_p[g][i] = i < cn ? s[g] : -INFINITY;
-        }
+      for (int e = 0; e < P_CH / 8; ++e) {
+        const int i = tg + 8 * e;
+        const int sz = tbase + i < t_hi ? 16 : 0;
+        if (blk[e] < 0 || blk[e] >= p.num_blocks) { atomicCAS(p.err, 0, ERR_BAD_INDEX); blk[e] = 0; }
+        const __nv_bfloat16* src = p.cache + blk[e] * blk_stride + ((long long)(tt[e] - lb[e] * p.block_size) * p.Hkv + hkv) * PD + dl * 8;
+        const uint32_t off = stage + chunk_off(i, dl);
+        cp_async16(sK + off, src, sz);
+        cp_async16(sV + off, src + v_off, sz);
       }
     }
-    __syncthreads();
-    // ---- online softmax bookkeeping: one warp per head (G <= 8 heads over 4 warps)
-    for (int g = tid >> 5; g < G; g += P_THREADS / 32) {
-      const int lane = tid & 31;
-      float mx = -INFINITY;
-      for (int i = lane; i < P_SUB; i += 32) mx = fmaxf(mx, s_p[g][i]);
+    cp_async_commit();
+  };
+  issue(0);
+  issue(1);
+
+  // Q as the A operand: row = lane / 4 is the head of the group (rows >= G and rows 8..15 are zero)
+  const int qrow = lane >> 2, qcol = (lane & 3) * 2;
+  uint32_t qa[PD / 16][2];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_old = s_m[g];
-      const float m_new = fmaxf(m_old, mx);
-      float sum = 0.f;
-      for (int i = lane; i < P_SUB; i += 32) {
-        const float e = exp2f(s_p[g][i] - m_new);
-        s_p[g][i] = e;
-        sum += e;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      if (lane == 0) {
-        const float alpha = exp2f(m_old - m_new);
-        s_alpha[g] = alpha;
-        s_l[g] = s_l[g] * alpha + sum;
-        s_m[g] = m_new;
-      }
+  for (int ks = 0; ks < PD / 16; ++ks) {
+    qa[ks][0] = qa[ks][1] = 0u;
+    if (qrow < G) {
+      const __nv_bfloat16* qp = p.q + ((long long)b * p.Hq + hkv * G + qrow) * PD + ks * 16 + qcol;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
     }
-    __syncthreads();
-    // ---- acc = acc * alpha + P V
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float al = s_alpha[g];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[g][j] *= al;
-    }
-#pragma unroll 1
-    for (int i0 = tg; i0 < cn; i0 += 32) {
-      uint4 u[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = i0 + 8 * e;
-        u[e] = make_uint4(0, 0, 0, 0);
-        if (i < cn) {
-          const int t = c0 + i;
-          int blk = bt[t / p.block_size];
-          if (blk < 0 || blk >= p.num_blocks) blk = 0;
-          u[e] = *reinterpret_cast<const uint4*>(p.cache + blk * blk_stride + v_off + ((long long)(t % p.block_size) * p.Hkv + hkv) * PD + dl * 8);
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = i0 + 8 * e;
-        if (i >= cn) break;
-        float v[8];
-        const float2 a = unpack_bf16x2(u[e].x), bb = unpack_bf16x2(u[e].y), c = unpack_bf16x2(u[e].z), d = unpack_bf16x2(u[e].w);
-        v[0] = a.x; v[1] = a.y; v[2] = bb.x; v[3] = bb.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float pw = s_p[g][i];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[g][j] += pw * v[j];
-        }
-      }
-    }
-    __syncthreads();
   }
-  // ---- reduce the 8 token groups
+  float o[PD / 8][4];
 #pragma unroll
-  for (int g = 0; g < G; ++g)
+  for (int nt = 0; nt < PD / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;     // of row qrow, over this warp's tokens (l: this thread's columns only)
+
+  for (int c = 0; c < n_ch; ++c) {
+    const int cn = min(P_CH, t_hi - t_lo - c * P_CH);
+    const uint32_t kst = sK + (c % P_STAGES) * P_CH_BYTES, vst = sV + (c % P_STAGES) * P_CH_BYTES;
+    const int tok0 = warp * 16;              // this warp's 16 tokens of the chunk
+    const bool active = tok0 < cn;           // warp-uniform
+    cp_async_wait<1>();                      // chunk c: one younger group may still be in flight
+    __syncthreads();
+    float sacc[2][4];
+    if (active) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s_red[tg][g][dl * 8 + j] = acc[g][j];
+      for (int nt = 0; nt < 2; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < PD / 16; ks += 2) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          uint32_t kb[4];                    // (b0, b1) of k-step ks and of k-step ks + 1
+          ldsm_x4(kst + chunk_off(tok0 + nt * 8 + (lane & 7), ks * 2 + (lane >> 3)), kb);
+          mma_16816(sacc[nt], qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
+          mma_16816(sacc[nt], qa[ks + 1][0], 0u, qa[ks + 1][1], 0u, kb[2], kb[3]);
+        }
+      }
+      // online softmax of row qrow: this thread holds columns nt * 8 + qcol + {0, 1}
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const bool valid = tok0 + nt * 8 + qcol + j < cn;
+          sacc[nt][j] = valid ? sacc[nt][j] * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, sacc[nt][j]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);           // finite: the warp has at least one valid token
+      const float alpha = exp2f(m_run - m_new);
+      m_run = m_new;
+      float ps = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) { sacc[nt][j] = exp2f(sacc[nt][j] - m_new); ps += sacc[nt][j]; }
+      l_run = l_run * alpha + ps;
+#pragma unroll
+      for (int nt = 0; nt < PD / 8; ++nt) { o[nt][0] *= alpha; o[nt][1] *= alpha; }
+    }
+    if (active) {
+      // P (16 heads x 16 tokens) as the A operand; rows 8..15 stay zero
+      const uint32_t pa0 = pack_bf16x2(sacc[0][0], sacc[0][1]), pa2 = pack_bf16x2(sacc[1][0], sacc[1][1]);
+#pragma unroll
+      for (int nt = 0; nt < PD / 8; nt += 2) {
+        uint32_t vb[4];                      // (b0, b1) of output columns nt * 8.. and of (nt + 1) * 8..
+        ldsm_x4_trans(vst + chunk_off(tok0 + (lane & 7) + ((lane >> 3) & 1) * 8, nt + (lane >> 4)), vb);
+        mma_16816(o[nt], pa0, 0u, pa2, 0u, vb[0], vb[1]);
+        mma_16816(o[nt + 1], pa0, 0u, pa2, 0u, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();                         // the stage is free
+    issue(c + 2);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // ---- merge the four warps (the staging rings are free now): s_red[warp][g][m, l, o[128]]
+  float (*s_red)[G][PD + 2] = reinterpret_cast<float (*)[G][PD + 2]>(p_dsm);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (qrow < G) {
+    if ((lane & 3) == 0) { s_red[warp][qrow][0] = m_run; s_red[warp][qrow][1] = l_run; }
+#pragma unroll
+    for (int nt = 0; nt < PD / 8; ++nt) {
+      s_red[warp][qrow][2 + nt * 8 + qcol] = o[nt][0];
+      s_red[warp][qrow][2 + nt * 8 + qcol + 1] = o[nt][1];
+    }
+  }
   __syncthreads();
   for (int i = tid; i < G * PD; i += P_THREADS) {
     const int g = i / PD, d = i % PD;
-    float o = 0.f;
+    float M = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o += s_red[k][g][d];
+    for (int w = 0; w < P_THREADS / 32; ++w) M = fmaxf(M, s_red[w][g][0]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < P_THREADS / 32; ++w) {
+      const float f = exp2f(s_red[w][g][0] - M);       // a warp without tokens has m = -inf, l = 0, o = 0
+      acc += f * s_red[w][g][2 + d];
+      l += f * s_red[w][g][1];
+    }
     if (ws) {
-      ws[g * (PD + 2) + 2 + d] = o;
-      if (d == 0) { ws[g * (PD + 2)] = s_m[g]; ws[g * (PD + 2) + 1] = s_l[g]; }
+      ws[g * (PD + 2) + 2 + d] = acc;
+      if (d == 0) { ws[g * (PD + 2)] = M; ws[g * (PD + 2) + 1] = l; }
     } else {
-      const float l = s_l[g];
-      p.out[((long long)b * p.Hq + hkv * G + g) * PD + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+      p.out[((long long)b * p.Hq + hkv * G + g) * PD + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
     }
   }
 }
@@ -321,15 +365,27 @@ MLF_API int mlf_paged_decode(const void* q, const void* cache, const int* block_
   p.ws = splits > 1 ? ws : nullptr;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.block_size = block_size; p.max_blocks = max_blocks; p.num_blocks = num_blocks;
   p.split_tokens = split_tokens; p.splits = splits;
+  p.bs_shift = -1;
+  for (int sh = 0; sh < 16; ++sh) if ((1 << sh) == block_size) p.bs_shift = sh;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = device_status_word();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid(B, Hkv, splits);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(paged_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(paged_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(paged_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(paged_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    attr_set[dev & 63] = true;
+  }
   switch (G) {
-    case 1: paged_decode_kernel<1><<<grid, P_THREADS, 0, st>>>(p); break;
-    case 2: paged_decode_kernel<2><<<grid, P_THREADS, 0, st>>>(p); break;
-    case 4: paged_decode_kernel<4><<<grid, P_THREADS, 0, st>>>(p); break;
-    default: paged_decode_kernel<8><<<grid, P_THREADS, 0, st>>>(p); break;
+    case 1: paged_decode_kernel<1><<<grid, P_THREADS, P_SMEM, st>>>(p); break;
+    case 2: paged_decode_kernel<2><<<grid, P_THREADS, P_SMEM, st>>>(p); break;
+    case 4: paged_decode_kernel<4><<<grid, P_THREADS, P_SMEM, st>>>(p); break;
+    default: paged_decode_kernel<8><<<grid, P_THREADS, P_SMEM, st>>>(p); break;
   }
   count_launch();
   if (splits > 1) {

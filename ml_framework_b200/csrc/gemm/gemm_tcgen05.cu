@@ -329,12 +329,19 @@ static int g_use_2cta = 1;
 // Selects the CTA-pair kernel for large plain GEMMs (tile_n == 0). tile_n == 512 always selects it.
 MLF_API void mlf_set_gemm_2cta(int on) { g_use_2cta = on; }
 MLF_API int mlf_get_gemm_2cta() { return g_use_2cta; }
+static int g_small_m_split = 1;
+// Routes plain GEMMs with M <= 256 and a large weight to the split-K CTA-pair kernel.
+MLF_API void mlf_set_gemm_small_m_split(int on) { g_small_m_split = on; }
 
 MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
   MLF_REQUIRE(a != nullptr, "null args");
-  // CTA pairs for everything with at least 16 pair tiles (split-K fills the GPU when tiles alone cannot)
-  if (a->tile_n == 512 || (g_use_2cta && a->tile_n == 0 && a->M >= 512 && a->N >= 512 &&
-                           (long long)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 16)) {
+  // CTA pairs for everything with at least 16 pair tiles (split-K fills the GPU when tiles alone cannot).
+  // Few rows against a large weight (a decode step: M <= 256) is a weight-streaming problem: one row of
+  // tiles cannot occupy the GPU, so the pair kernel splits K and every SM streams a slice of the weight.
+  const bool plain_out = (a->flags & ~MLF_EPI_ACCUM) == 0 && a->comm == nullptr;
+  const bool small_m = g_small_m_split && a->tile_n == 0 && plain_out && a->M <= 256 && a->N >= 1024 && a->K >= 1024;
+  if (a->tile_n == 512 || small_m ||
+      (g_use_2cta && a->tile_n == 0 && a->M >= 512 && a->N >= 512 && (long long)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 16)) {
     const int rc2 = mlf_gemm_bf16_2cta(a, stream);
     if (rc2 != -4) return rc2;
   }

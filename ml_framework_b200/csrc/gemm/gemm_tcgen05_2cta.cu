@@ -457,8 +457,9 @@ using namespace mlf;
 // fit (the caller then uses the single-CTA kernel).
 MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
   MLF_REQUIRE(a != nullptr, "null args");
-  if (a->M < 256 || a->N < 256) return -4;
   const MlfGemmComm* cm = a->comm;
+  // fewer than 256 rows only as a plain product (optionally accumulated), where K is split over the pairs
+  if (a->N < 256 || (a->M < 256 && ((a->flags & ~MLF_EPI_ACCUM) != 0 || cm != nullptr))) return -4;
   const bool gatherA = cm && cm->gather_operand == 1;
   const bool gatherB = cm && cm->gather_operand == 2;
   if (cm && cm->gather_operand && (cm->flag_rows <= 0 || cm->flag_rows % 128 != 0)) return -4;

@@ -301,7 +301,8 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
 
     q [B, Hq, 128]; kv_cache [num_blocks, 2, block_size, Hkv, 128]; block_table int32 [B, max_blocks];
     seq_lens int32 [B] (cached tokens including the current one). ``max_seq_len`` (host int, an upper
-    bound of seq_lens) fixes the number of splits so the launch shape does not depend on device data.
+    bound of seq_lens) fixes the number of splits so the launch shape does not depend on device data;
+    ``split_tokens`` <= 0 picks the split count from the batch size (enough CTAs to fill the GPU).
     """
     B, Hq, D = q.shape
     nb, two, bs, Hkv, D2 = kv_cache.shape
@@ -309,6 +310,11 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
     out = torch.empty_like(q)
     L = _L()
     L.mlf_paged_decode_ws_elems.restype = C.c_longlong
+    if split_tokens <= 0:
+        # automatic: about two waves of CTAs (three resident per SM on 148 SMs), at least 128 tokens per split
+        want = max(1, -(-888 // (B * Hkv)))
+        want = min(want, max(1, (max_seq_len + 127) // 128))
+        split_tokens = -(-max_seq_len // want)
     st = (max(split_tokens, 128) + 127) // 128 * 128
     splits = max(1, (max_seq_len + st - 1) // st)
     ws = scratch("paged_decode", L.mlf_paged_decode_ws_elems(B, Hq, splits) * 4, q.device) if splits > 1 else None

@@ -35,7 +35,7 @@ class ExecutorConfig:
     max_batch: int = 256
     max_seq_len: int = 4096
     prefill_chunk: int = 2048
-    decode_split_tokens: int = 512
+    decode_split_tokens: int = 0          # 0: chosen from the batch size
     use_cuda_graphs: bool = True       # decode steps replay a captured graph per (batch bucket, length bucket)
     graph_warmup_steps: int = 2
 
@@ -96,12 +96,22 @@ class PagedLlamaExecutor:
             native.rope_(k, positions, mc.rope_theta)
             native.kv_cache_write(cache, k, v, slots)
             a = attend(li, q, k, v)
-            x = self._reduce(gemm(a.reshape(T, self.hq * D), o_w), x) if self.tp is not None and self.tp.world > 1 else \
-                gemm(a.reshape(T, self.hq * D), o_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
+            multi = self.tp is not None and self.tp.world > 1
+            # A decode step (few rows, whole weights) streams weights: plain products let the GEMM split K over
+            # all SMs, the residual stream takes the product as an accumulation, SwiGLU runs as its own pass.
+            few_rows = T <= 256
+            if multi:
+                x = self._reduce(gemm(a.reshape(T, self.hq * D), o_w), x)
+            elif few_rows:
+                gemm(a.reshape(T, self.hq * D), o_w, out=x, flags=_lib.EPI_ACCUM)
+            else:
+                x = gemm(a.reshape(T, self.hq * D), o_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
             h, _, _ = native.norm_fwd(x, blk.norm2.weight, None, mc.norm_eps, True, want_stats=False)
-            hid = gemm(h, gu_w, flags=_lib.EPI_SWIGLU)
-            if self.tp is not None and self.tp.world > 1:
+            hid = native.swiglu_fwd(gemm(h, gu_w), interleaved=True) if few_rows else gemm(h, gu_w, flags=_lib.EPI_SWIGLU)
+            if multi:
                 return self._reduce(gemm(hid, dn_w), x)
+            if few_rows:
+                return gemm(hid, dn_w, out=x, flags=_lib.EPI_ACCUM)
             return gemm(hid, dn_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
         # ---- PyTorch statement of the same block (CPU / fp32)
         h, _ = reference.rms_norm_ref(x, blk.norm1.weight, mc.norm_eps)

@@ -165,6 +165,67 @@ def run_fused_small() -> list[dict]:
     return [{"ran": "fused gather-GEMM + scatter-GEMM x2 (emulated world 4)", "gather_exact": ok}]
 
 
+DECODE_SHAPES = [
+    # Llama-8B weights against one decode step of 64 sequences (M = 64): (name, N, K)
+    ("llama8b decode qkv", 6144, 4096),
+    ("llama8b decode o", 4096, 4096),
+    ("llama8b decode gate_up", 28672, 4096),
+    ("llama8b decode down", 4096, 14336),
+    ("llama8b tp8 decode gate_up", 3584, 4096),
+    ("llama8b tp8 decode down", 4096, 1792),
+]
+
+
+def bench_gemm_decode(args) -> list[dict]:
+    """Few-row GEMMs of a decode step: the weight is read once, so the bound is weight bytes / HBM bandwidth.
+    Columns: the split-K CTA-pair route, the single-CTA route, and torch.matmul (cuBLAS)."""
+    from .. import _lib
+    from ..ops.gemm import gemm
+    pk = peaks()
+    rows = []
+    lib = _lib.get()
+    for M in (64, 256):
+        for name, N, K in DECODE_SHAPES:
+            a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            lib.mlf_set_gemm_small_m_split(1)
+            ms = time_cuda(lambda: gemm(a, b, out=out), iters=20)
+            lib.mlf_set_gemm_small_m_split(0)
+            ms_1 = time_cuda(lambda: gemm(a, b, out=out), iters=20)
+            lib.mlf_set_gemm_small_m_split(1)
+            ms_ref = time_cuda(lambda: torch.matmul(a, b.t(), out=out), iters=20)
+            bound_ms = (N * K + M * K + M * N) * 2 / (pk["hbm_gbs"] * 1e9) * 1e3
+            rows.append({"shape": name, "M": M, "N": N, "K": K, "split_k_ms": round(ms, 4), "single_cta_ms": round(ms_1, 4),
+                         "cublas_ms": round(ms_ref, 4), "hbm_bound_ms": round(bound_ms, 4),
+                         "frac_of_" + pk["source"] + "_hbm": round(bound_ms / ms, 3)})
+            print(rows[-1], flush=True)
+    return rows
+
+
+def bench_paged_decode(args) -> list[dict]:
+    """Paged-attention decode (block 16) on Llama-8B head shapes; bound = K and V bytes of the cached tokens / HBM bandwidth."""
+    from ..ops import native
+    pk = peaks()
+    rows = []
+    bs, D = 16, 128
+    for name, B, Hq, Hkv, ln in [("llama8b B64 ctx576", 64, 32, 8, 576), ("llama8b B256 ctx1024", 256, 32, 8, 1024),
+                                 ("llama8b tp8 B64 ctx576", 64, 4, 1, 576), ("llama8b B8 ctx4096", 8, 32, 8, 4096)]:
+        nblk = (ln + bs - 1) // bs
+        cache = torch.randn(B * nblk, 2, bs, Hkv, D, device="cuda").to(torch.bfloat16)
+        table = torch.randperm(B * nblk, device="cuda").to(torch.int32).view(B, nblk)
+        sl = torch.full((B,), ln, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+        max_len = (ln + 511) // 512 * 512
+        ms = time_cuda(lambda: native.paged_decode(q, cache, table, sl, max_len, split_tokens=0), iters=20)
+        ms512 = time_cuda(lambda: native.paged_decode(q, cache, table, sl, max_len, split_tokens=512), iters=20)
+        bound = B * ln * 2 * Hkv * D * 2 / (pk["hbm_gbs"] * 1e9) * 1e3
+        rows.append({"shape": name, "auto_split_ms": round(ms, 4), "split512_ms": round(ms512, 4), "hbm_bound_ms": round(bound, 4),
+                     "frac_of_" + pk["source"] + "_hbm": round(bound / ms, 3)})
+        print(rows[-1], flush=True)
+    return rows
+
+
 def run_gemm_small() -> list[dict]:
     """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
     from ..ops.gemm import gemm
@@ -179,7 +240,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -194,6 +255,10 @@ def main():
         print(rows)
     elif args.what == "gemm_small":
         rows = run_gemm_small()
+    elif args.what == "gemm_decode":
+        rows = bench_gemm_decode(args)
+    elif args.what == "paged":
+        rows = bench_paged_decode(args)
     elif args.what == "attn":
         from .kernel_bench_attn import bench_attn
         rows = bench_attn(args)

@@ -167,3 +167,22 @@ def test_split_k_and_accumulate_pair_kernel(M, N, K, a_mn, b_mn):
     gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out2, flags=_lib.EPI_ACCUM)
     torch.cuda.synchronize()
     _check(out2, ref + prev.float(), K)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (64, 6144, 4096), (200, 1024, 14336), (256, 3584, 4096)])
+def test_few_rows_split_k(M, N, K):
+    """A decode-step product (few rows, a large weight) takes the split-K CTA-pair route; also as an
+    accumulation into the residual stream."""
+    torch.manual_seed(6)
+    a = _mk(M, K, False, "cuda", 0.25)
+    b = _mk(N, K, False, "cuda", 0.25)
+    ref, _ = gemm_reference(a, b)
+    out = gemm(a, b)
+    torch.cuda.synchronize()
+    _check(out, ref, K)
+    x = (torch.randn(M, N, device="cuda") * ref.abs().mean()).to(torch.bfloat16)
+    x0 = x.clone()
+    gemm(a, b, out=x, flags=_lib.EPI_ACCUM)
+    torch.cuda.synchronize()
+    _check(x, ref + x0.float(), K)
+    assert _lib.read_status() == 0

@@ -36,6 +36,9 @@ def test_paged_decode_matches_contiguous(B, Hq, Hkv, lens):
     # a smaller split size exercises the merge kernel
     out2 = native.paged_decode(q, cache, table, sl, max_len, split_tokens=128)
     assert (out2.float() - ref).abs().max().item() < 2e-2 * (ref.abs().max().item() + 1e-3)
+    # split count chosen from the batch size
+    out3 = native.paged_decode(q, cache, table, sl, max_len, split_tokens=0)
+    assert (out3.float() - ref).abs().max().item() < 2e-2 * (ref.abs().max().item() + 1e-3)
 
 
 def test_kv_cache_write_gather_and_argmax():
