@@ -3,7 +3,8 @@
 // One warp owns one row at a time and keeps it in registers as packed bf16 (NV 16-byte
 // vectors per lane), so x is read from HBM exactly once per pass. The backward pass adds the
 // per-row contributions to gamma/beta gradients into a per-CTA shared-memory accumulator with
-// shared atomics and writes one partial per CTA; a second tiny kernel sums the partials.
+// shared atomics and writes one partial per CTA; a second tiny kernel sums the partials. The wide
+// model dimensions (2048 and 4096) use a backward kernel with whole-CTA rows instead.
 //
 // The reference has no norm kernels (its AMP rules only name layernorm as an fp32 op,
 // src/MLFramework/Amp/DefaultAmpRules.cs:48-110); these are required by the GPT and Llama
@@ -188,6 +189,112 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) po[i] = acc[i];
 }
 
+// Backward for D = NVT * 2048 (the model widths 2048 and 4096): a CTA of 256 threads owns
+// R rows at a time and every thread a fixed set of 8 * NVT columns, so gamma sits in registers as
+// fp32, the gamma / beta gradient partials need only 16 * NVT registers, and R rows of x and dy
+// (R * 12 KB per CTA at D = 2048) are in flight per CTA while several CTAs share an SM. The two row
+// sums meet across the eight warps through a double-buffered shared array: one barrier per R rows.
+template <int NVT, int R>
+__global__ void __launch_bounds__(256, 2)
+norm_bwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                    const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                    const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                    float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms) {
+  constexpr int D = NVT * 2048;
+  __shared__ float red[2][8][2 * R];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float g[NVT][8], dg[NVT][8], db[NVT][8];
+#pragma unroll
+  for (int v = 0; v < NVT; ++v) {
+    unpack8(reinterpret_cast<const uint4*>(gamma)[v * 256 + tid], g[v]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dg[v][j] = db[v][j] = 0.f;
+  }
+  const float inv_d = 1.f / D;
+  int buf = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, buf ^= 1) {
+    uint4 xv[R][NVT], dv[R][NVT];
+    float mean[R], rstd[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool ok = row0 + r < rows;
+      const long long base = (long long)(ok ? row0 + r : row0) * (D / 8);
+#pragma unroll
+      for (int v = 0; v < NVT; ++v) {
+        xv[r][v] = reinterpret_cast<const uint4*>(x)[base + v * 256 + tid];
+        dv[r][v] = ok ? reinterpret_cast<const uint4*>(dy)[base + v * 256 + tid] : make_uint4(0, 0, 0, 0);
+      }
+      mean[r] = rms ? 0.f : mean_in[ok ? row0 + r : row0];
+      rstd[r] = rstd_in[ok ? row0 + r : row0];
+    }
+    float c[2 * R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float c1 = 0.f, c2 = 0.f;
+      const float nm = -mean[r] * rstd[r];
+#pragma unroll
+      for (int v = 0; v < NVT; ++v) {
+        float f[8], d[8];
+        unpack8(xv[r][v], f);
+        unpack8(dv[r][v], d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = fmaf(f[j], rstd[r], nm);
+          const float dxh = d[j] * g[v][j];
+          c1 += dxh;
+          c2 = fmaf(dxh, xh, c2);
+          dg[v][j] = fmaf(d[j], xh, dg[v][j]);
+          db[v][j] += d[j];
+        }
+      }
+      c[2 * r] = warp_sum(c1);
+      c[2 * r + 1] = warp_sum(c2);
+    }
+    if (lane < 2 * R) {
+      float mine = c[0];
+#pragma unroll
+      for (int k = 1; k < 2 * R; ++k) mine = lane == k ? c[k] : mine;
+      red[buf][warp][lane] = mine;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2 * R; ++k) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += red[buf][w][k];
+      c[k] = t * inv_d;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) break;
+      const float c1 = rms ? 0.f : c[2 * r], c2 = c[2 * r + 1];
+      const float nm = -mean[r] * rstd[r];
+#pragma unroll
+      for (int v = 0; v < NVT; ++v) {
+        float f[8], d[8], o[8];
+        unpack8(xv[r][v], f);
+        unpack8(dv[r][v], d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = fmaf(f[j], rstd[r], nm);
+          o[j] = rstd[r] * (fmaf(d[j], g[v][j], -c1) - xh * c2);
+        }
+        reinterpret_cast<uint4*>(dx)[(long long)(row0 + r) * (D / 8) + v * 256 + tid] = pack8(o);
+      }
+    }
+  }
+  float* po = partials + (long long)blockIdx.x * 2 * D;
+#pragma unroll
+  for (int v = 0; v < NVT; ++v) {
+    float4* pg = reinterpret_cast<float4*>(po + (v * 256 + tid) * 8);
+    float4* pb = reinterpret_cast<float4*>(po + D + (v * 256 + tid) * 8);
+    pg[0] = make_float4(dg[v][0], dg[v][1], dg[v][2], dg[v][3]);
+    pg[1] = make_float4(dg[v][4], dg[v][5], dg[v][6], dg[v][7]);
+    pb[0] = make_float4(db[v][0], db[v][1], db[v][2], db[v][3]);
+    pb[1] = make_float4(db[v][4], db[v][5], db[v][6], db[v][7]);
+  }
+}
+
 // dgamma[c] = sum_g partials[g][0][c]; dbeta likewise. 32 columns x 8 partial-lanes per CTA.
 __global__ void __launch_bounds__(256)
 norm_bwd_finalize_kernel(const float* __restrict__ partials, int nparts, int D, void* dgamma, void* dbeta,
@@ -282,10 +389,20 @@ MLF_API int mlf_norm_fwd(const void* x, const void* gamma, const void* beta, voi
   return -2;
 }
 
+// CTAs of the backward kernel: whole-CTA rows for the wide model dimensions, warp rows otherwise.
+static int norm_bwd_grid(int rows, int D, bool* cta_rows) {
+  const bool wide = D == 2048 || D == 4096;
+  if (cta_rows) *cta_rows = wide;
+  if (wide) {
+    const int r = D == 2048 ? 4 : 2;
+    return min((rows + r - 1) / r, 2 * sm_count());
+  }
+  return min((rows + 7) / 8, sm_count());
+}
+
 // Number of fp32 elements the caller must provide as `partials` scratch for mlf_norm_bwd.
 MLF_API long long mlf_norm_bwd_scratch_elems(int rows, int D) {
-  const int grid = min((rows + 7) / 8, sm_count());
-  return (long long)grid * 2 * D;
+  return (long long)norm_bwd_grid(rows, D, nullptr) * 2 * D;
 }
 
 MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
@@ -293,9 +410,23 @@ MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const
                          int grads_fp32, int accumulate, uint64_t stream) {
   MLF_REQUIRE(D % 256 == 0, "norm: D=%d must be a multiple of 256", D);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = min((rows + 7) / 8, sm_count());
+  bool cta_rows = false;
+  const int grid = norm_bwd_grid(rows, D, &cta_rows);
   int rc = -2;
   bool matched = true;
+  if (cta_rows) {
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+    const __nv_bfloat16* dyp = static_cast<const __nv_bfloat16*>(dy);
+    const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(gamma);
+    __nv_bfloat16* dxp = static_cast<__nv_bfloat16*>(dx);
+    switch (D / 2048) {
+      case 1: norm_bwd_cta_kernel<1, 4><<<grid, 256, 0, st>>>(xp, dyp, gp, mean, rstd, dxp, partials, rows, rms); break;
+      default: norm_bwd_cta_kernel<2, 2><<<grid, 256, 0, st>>>(xp, dyp, gp, mean, rstd, dxp, partials, rows, rms); break;
+    }
+    count_launch();
+    MLF_CHECK_CUDA(cudaGetLastError());
+    rc = 0;
+  } else
   switch (D / 256) {
 #define CASE(NV) case NV: rc = launch_bwd<NV>(x, dy, gamma, mean, rstd, dx, partials, grid, rows, rms, st); break;
     CASE(1) CASE(2) CASE(3) CASE(4) CASE(6) CASE(8) CASE(12) CASE(16) CASE(20) CASE(24) CASE(32)

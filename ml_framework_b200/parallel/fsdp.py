@@ -256,6 +256,9 @@ class FSDP:
         n_rot = 2 if not keep_full else 0
         self._rot_full = [torch.zeros(max_full, dtype=dt, device=dev) for _ in range(n_rot)] if max_full else []
         self._rot_grad = [symm_or_local(f"rot_grad{k}", max_full) for k in range(2)] if max_full else []
+        # One rank: a shard is the whole parameter, so block units compute on their shards and write
+        # gradients into their gradient shards directly (nothing to gather, nothing to reduce).
+        self._alias_shards = self.world == 1 and self.cfg.sharding_strategy == "full"
         with torch.no_grad():
             for u in self.all_units():
                 u.shard = self.param_shards[u.state_off:u.state_off + u.shard_numel]
@@ -393,6 +396,10 @@ class FSDP:
         if self.cfg.sharding_strategy == "grad_op":
             self._point_params(u, u.gathered, None)
             return
+        if self._alias_shards:
+            u.gathered = u.shard
+            self._point_params(u, u.shard, None)
+            return
         full = self._rot_full[i % 2]
         self._gather_unit(u, full)
         self._rot_owner[i % 2] = i
@@ -405,6 +412,10 @@ class FSDP:
 
     def _pre_backward(self, i: int):
         u = self.units[i]
+        if self._alias_shards:
+            u.gathered, u._gbuf = u.shard, u.grad_shard
+            self._point_params(u, u.shard, u.grad_shard)
+            return
         gbuf = self._rot_grad[i % 2] if u.grad_full is None or self.cfg.sharding_strategy != "grad_op" else u.grad_full
         if self.cfg.sharding_strategy == "grad_op":
             gbuf = self._rot_grad[i % 2]
@@ -447,7 +458,8 @@ class FSDP:
                 view.zero_()
             out = u.grad_shard[sp.shard_off:sp.shard_off + sp.shard_numel]
             if self.world == 1:
-                out.copy_(view)
+                if out.data_ptr() != view.data_ptr():     # a single rank writes gradients straight into its shard
+                    out.copy_(view)
             elif u.owner is not None:
                 self.pg.reduce(view, dst=u.owner, op=ReduceOp.SUM)
                 if self.rank == u.owner:

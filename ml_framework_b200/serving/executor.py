@@ -36,6 +36,7 @@ class ExecutorConfig:
     max_seq_len: int = 4096
     prefill_chunk: int = 2048
     decode_split_tokens: int = 0          # 0: chosen from the batch size
+    max_prefill_tokens: int = 8192        # first chunks of equal length are prefilled together up to this many tokens
     use_cuda_graphs: bool = True       # decode steps replay a captured graph per (batch bucket, length bucket)
     graph_warmup_steps: int = 2
 
@@ -190,6 +191,38 @@ class PagedLlamaExecutor:
             return int(self._logits_argmax(x[-1:])[0])
         return None
 
+    # ---- first chunks of several requests in one pass (equal lengths: one batched causal attention)
+    @torch.no_grad()
+    def _prefill_many(self, reqs: List[Request], n: int) -> Dict[int, int]:
+        dev = self.device
+        B = len(reqs)
+        slot_list = []
+        for r in reqs:
+            s, _ = self.kv.append_tokens(r.id, n)
+            if s is None:
+                raise MemoryError(f"KV cache exhausted while prefilling request {r.id}")
+            slot_list.append(s)
+        ids = torch.tensor([r.prompt_tokens[:n] for r in reqs], dtype=torch.int64, device=dev)
+        pos = torch.arange(n, dtype=torch.int64, device=dev).repeat(B)
+        slots = torch.cat(slot_list).to(dev)
+
+        def attend(li, q, k, v):
+            out, _ = native.flash_fwd(q, k, v, B, n, causal=True, want_lse=False)
+            return out
+        x = self._embed(ids).reshape(B * n, -1)
+        for li, blk in enumerate(self.m.blocks):
+            x = self._block(li, blk, x, pos, slots, attend)
+        done = []
+        for i, r in enumerate(reqs):
+            r.prefilled = n
+            if r.prefilled >= len(r.prompt_tokens):
+                done.append(i)
+        if not done:
+            return {}
+        rows = torch.tensor([i * n + n - 1 for i in done], dtype=torch.int64, device=dev)
+        toks = self._logits_argmax(x[rows]).tolist()
+        return {reqs[i].id: int(t) for i, t in zip(done, toks)}
+
     # ---- one decode step for a set of requests
     def _decode_core(self, last, pos, slots, table, lens, max_len: int) -> torch.Tensor:
         """Device-only part of a decode step (no host reads): embed, all blocks, head, arg-max."""
@@ -254,7 +287,23 @@ class PagedLlamaExecutor:
     # ---- scheduler entry point
     def execute_batch(self, batch: Batch) -> BatchOutput:
         out: Dict[int, int] = {}
-        for r in batch.prefill:
+        singles = list(batch.prefill)
+        if self.native and len(singles) > 1:
+            # group the requests that start their prompt now by the length of their first chunk
+            groups: Dict[int, List[Request]] = {}
+            for r in singles:
+                if r.prefilled == 0:
+                    groups.setdefault(min(len(r.prompt_tokens), self.cfg.prefill_chunk), []).append(r)
+            singles = [r for r in singles if r.prefilled != 0]
+            for n, rs in groups.items():
+                per = max(1, self.cfg.max_prefill_tokens // max(n, 1))
+                for i in range(0, len(rs), per):
+                    part = rs[i:i + per]
+                    if len(part) == 1 or n < 1:
+                        singles.extend(part)
+                    else:
+                        out.update(self._prefill_many(part, n))
+        for r in singles:
             tok = self._prefill(r)
             if tok is not None:
                 out[r.id] = tok

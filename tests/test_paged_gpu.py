@@ -87,3 +87,29 @@ def test_executor_cuda_graph_decode_matches_eager():
     same = sum(a == b for x, y in zip(outs[False], outs[True]) for a, b in zip(x, y))
     total = sum(len(x) for x in outs[False])
     assert all(len(x) == 12 for x in outs[True]) and same >= 0.9 * total, (same, total)
+
+
+def test_batched_prefill_matches_one_by_one():
+    """First chunks of equal length prefilled in one pass give the tokens of request-by-request prefill."""
+    from ml_framework_b200.modelzoo.zoo import build_model, default_registry
+    from ml_framework_b200.serving.executor import ExecutorConfig, PagedLlamaExecutor
+    from ml_framework_b200.serving.kv_cache import KVCacheBlockManager
+    from ml_framework_b200.serving.scheduler import (BatchConstraints, CompletionConfiguration, ContinuousBatchScheduler, Request,
+                                                     SchedulerConfiguration)
+    torch.manual_seed(0)
+    model = build_model(default_registry().get("llama-tiny"), "cuda", torch.bfloat16).eval()
+    mc = model.cfg
+    prompts = [[(11 * i + 5 * j) % (mc.vocab_size - 1) + 1 for j in range(40 if i < 4 else 23)] for i in range(6)]
+    outs = {}
+    for budget in (1, 8192):         # 1: every request on its own
+        kv = KVCacheBlockManager(256, 16, mc.head_dim, mc.n_layers, mc.n_kv_heads, device="cuda", dtype=torch.bfloat16)
+        ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=256, prefill_chunk=64, use_cuda_graphs=False,
+                                                          max_prefill_tokens=budget))
+        sched = ContinuousBatchScheduler(ex, kv, SchedulerConfiguration(max_batch_size=8, warmup_iterations=0), BatchConstraints(max_batch_size=8),
+                                         completion=CompletionConfiguration(eos_token_id=-1, default_max_tokens=6))
+        futs = [sched.enqueue(Request(list(p), max_tokens=6)) for p in prompts]
+        sched.run_until_idle()
+        outs[budget] = [f.result(1).tokens for f in futs]
+    same = sum(a == b for x, y in zip(outs[1], outs[8192]) for a, b in zip(x, y))
+    total = sum(len(x) for x in outs[1])
+    assert all(len(x) == 6 for x in outs[8192]) and same >= 0.9 * total, (same, total)
