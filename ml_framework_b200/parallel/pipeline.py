@@ -295,13 +295,23 @@ class ProcessGroupPipelineCommunicator:
     def __init__(self, pg, use_side_stream: bool = True):
         self.pg, self.rank = pg, pg.rank
         self.stream = None
+        self._pending: list = []
         if use_side_stream and torch.cuda.is_available() and str(getattr(pg, "backend", "")).lower().endswith("nccl"):
             self.stream = torch.cuda.Stream()
 
     def _run(self, ops):
         if self.stream is None:
-            for w in self.pg.batch_isend_irecv(ops):
-                w.wait()
+            # Host-blocking backends: only receives are waited for here. A send completes when the peer posts
+            # its receive, which in 1F1B can be after the peer's own send to this rank, so sends stay pending
+            # (tensor kept alive) and are collected later.
+            works = self.pg.batch_isend_irecv(ops)
+            for (kind, t, _), w in zip(ops, works):
+                if kind == "recv":
+                    w.wait()
+                else:
+                    self._pending.append((w, t))
+            while len(self._pending) > 64:
+                self._pending.pop(0)[0].wait()
             return
         self.stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.stream):
@@ -334,6 +344,8 @@ class ProcessGroupPipelineCommunicator:
         return buf
 
     def barrier(self):
+        while self._pending:
+            self._pending.pop(0)[0].wait()
         self.pg.barrier()
 
 
