@@ -175,6 +175,125 @@ ar_one_shot_kernel(PeerPtrs bufs, int world, int rank, __nv_bfloat16* out, long 
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Synchronisation whose epoch lives in device memory, so that a captured CUDA graph replays it:
+// pads as above (one signal slot per peer), plus a local {epoch, finished-CTA count} pair. Every
+// CTA reads the epoch of this launch (previous + 1); CTA 0 signals the peers; everybody waits for
+// all peers' signals; the last CTA to finish publishes the new epoch. All ranks must run the same
+// sequence of such launches.
+// ------------------------------------------------------------------------------------------
+struct SyncState {
+  uint32_t epoch;
+  uint32_t done;
+};
+
+__device__ __forceinline__ uint32_t sync_enter(const PeerPtrs& pads, SyncState* st, int rank, int world, int* err) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(&st->epoch) + 1u;
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  const int t = threadIdx.x;
+  if (blockIdx.x == 0 && t < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(pads.p[t]) + rank * 32, e);
+  }
+  if (t < world) wait_flag_ge_sys(static_cast<const uint32_t*>(pads.p[rank]) + t * 32, e, err, ERR_WAIT_PEER_FLAG);
+  __syncthreads();
+  return e;
+}
+
+__device__ __forceinline__ void sync_leave(SyncState* st, uint32_t e) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&st->done, 1u) == gridDim.x - 1) {
+      st->done = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&st->epoch) = e;
+    }
+  }
+}
+
+// One-shot all-reduce with the arrival synchronisation inside: the producers of bufs[*] (the kernels
+// before this one on every rank's stream) are complete once all peers have signalled.
+__global__ void __launch_bounds__(256)
+ar_one_shot_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, int world, int rank, __nv_bfloat16* out, long long numel,
+                        const __nv_bfloat16* residual, int* err) {
+  const uint32_t e = sync_enter(pads, st, rank, world, err);
+  const long long nvec = numel / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[k]) + i * 8);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
+        a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+      }
+    if (residual) {
+      const uint4 rr = *reinterpret_cast<const uint4*>(residual + i * 8);
+      float2 f0 = unpack_bf16x2(rr.x), f1 = unpack_bf16x2(rr.y), f2 = unpack_bf16x2(rr.z), f3 = unpack_bf16x2(rr.w);
+      a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = w;
+  }
+  sync_leave(st, e);
+}
+
+// Greedy sampling over a vocabulary split across ranks. Step 1 (every rank): best (value, global index)
+// of each row of the local logits into this rank's staging buffer. Step 2: synchronise, read all
+// ranks' candidates, keep the best (lowest index on ties).
+struct ArgmaxCand {
+  float value;
+  int index;
+};
+
+__global__ void __launch_bounds__(256)
+argmax_local_kernel(const __nv_bfloat16* logits, long long ld, int cols, int index_base, int vocab, ArgmaxCand* cand) {
+  const long long r = blockIdx.x;
+  const __nv_bfloat16* row = logits + r * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < cols && index_base + i < vocab; i += blockDim.x) {
+    const float v = __bfloat162float(row[i]);
+    if (v > best) { best = v; bi = index_base + i; }
+  }
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  sv[threadIdx.x] = best;
+  si[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float ov = sv[threadIdx.x + s];
+      const int oi = si[threadIdx.x + s];
+      if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) { sv[threadIdx.x] = ov; si[threadIdx.x] = oi; }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { cand[r].value = sv[0]; cand[r].index = si[0]; }
+}
+
+__global__ void __launch_bounds__(256)
+argmax_combine_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, int world, int rank, long long rows, long long* out, int* err) {
+  const uint32_t e = sync_enter(pads, st, rank, world, err);
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = 0; k < world; ++k) {
+      const ArgmaxCand c = static_cast<const ArgmaxCand*>(bufs.p[k])[r];
+      if (c.value > best || (c.value == best && c.index < bi)) { best = c.value; bi = c.index; }
+    }
+    out[r] = bi == 0x7fffffff ? 0 : bi;
+  }
+  sync_leave(st, e);
+}
+
 // out[row, :] = sum_w partial[w, row, :] (+ bias) (+ residual): the second half of GEMM->reduce-
 // scatter, where peers have stored their partial tiles into this rank's [W, rows, cols] buffer.
 __global__ void __launch_bounds__(256)
@@ -326,6 +445,40 @@ MLF_API int mlf_ar_one_shot(void* const* bufs, int world, int rank, void* out, l
   if (g < 1) g = 1;
   ar_one_shot_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       to_peers(bufs, world), world, rank, static_cast<__nv_bfloat16*>(out), numel, static_cast<const __nv_bfloat16*>(residual));
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// One-shot all-reduce that synchronises inside the kernel (no host-side epoch: replayable from a CUDA
+// graph). pads: every rank's signal pad (1 KB of slots); state: this rank's 8-byte {epoch, count} pair,
+// zero-initialised. Callers alternate between two staging buffers from one call to the next.
+MLF_API int mlf_ar_one_shot_sync(void* const* bufs, void* const* pads, void* state, int world, int rank, void* out, long long numel,
+                                 const void* residual, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && numel % 8 == 0 && state != nullptr, "ar_one_shot_sync: bad arguments");
+  long long g = (numel / 8 + 255) / 256;
+  const long long cap = (long long)sm_count();
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  ar_one_shot_sync_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      to_peers(bufs, world), to_peers(pads, world), static_cast<SyncState*>(state), world, rank, static_cast<__nv_bfloat16*>(out), numel,
+      static_cast<const __nv_bfloat16*>(residual), device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Arg-max over a vocabulary split across ranks: logits [rows, cols] are this rank's columns
+// [index_base, index_base + cols) of the vocabulary; bufs[r] holds rank r's candidates (8 bytes per row).
+MLF_API int mlf_tp_argmax(const void* logits, long long rows, long long ld, int cols, int index_base, int vocab, void* const* bufs,
+                          void* const* pads, void* state, int world, int rank, long long* out, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && rows > 0 && state != nullptr, "tp_argmax: bad arguments");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  argmax_local_kernel<<<(int)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, cols, index_base, vocab,
+                                                 static_cast<ArgmaxCand*>(bufs[rank]));
+  count_launch();
+  argmax_combine_sync_kernel<<<1, 256, 0, st>>>(to_peers(bufs, world), to_peers(pads, world), static_cast<SyncState*>(state), world, rank,
+                                                rows, out, device_status_word());
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

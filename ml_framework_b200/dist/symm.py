@@ -145,6 +145,36 @@ class SymmetricMemory:
                                        C.c_uint64(_lib.stream_handle()))
         _lib.check(rc, "mlf_ar_one_shot")
 
+    # ---- graph-replayable variants: the epoch is kept on the device (see mlf_ar_one_shot_sync)
+    def _sync_pad(self) -> SymmBuffer:
+        if getattr(self, "_gpad", None) is None:
+            self._gpad = self.alloc(2048)          # [0, 1024): signal slots written by peers; [1024, 1032): local {epoch, count}
+            self.pg.barrier()
+        return self._gpad
+
+    def all_reduce_one_shot_sync(self, buf: SymmBuffer, out: torch.Tensor, numel: int, residual: Optional[torch.Tensor] = None,
+                                 offset_bytes: int = 0):
+        """Sum of every rank's ``buf`` (at ``offset_bytes``) into ``out`` (+ residual); waits inside the kernel for
+        all ranks to reach the call, so the producers of the buffers are complete. Alternate between two
+        staging offsets from one call to the next: nothing waits at the end."""
+        pad = self._sync_pad()
+        rc = self._lib.mlf_ar_one_shot_sync(buf.peer_table(offset_bytes), pad.peer_table(), C.c_void_p(pad.ptrs[self.rank] + 1024),
+                                            self.world, self.rank, C.c_void_p(out.data_ptr()), C.c_longlong(numel),
+                                            C.c_void_p(residual.data_ptr()) if residual is not None else None,
+                                            C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_ar_one_shot_sync")
+
+    def tp_argmax(self, logits: torch.Tensor, index_base: int, vocab: int, cand: SymmBuffer) -> torch.Tensor:
+        """Arg-max over a vocabulary split across ranks (``logits`` = this rank's columns starting at ``index_base``)."""
+        pad = self._sync_pad()
+        rows, cols = logits.shape
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+        rc = self._lib.mlf_tp_argmax(C.c_void_p(logits.data_ptr()), C.c_longlong(rows), C.c_longlong(logits.stride(0)), cols, index_base,
+                                     vocab, cand.peer_table(), pad.peer_table(), C.c_void_p(pad.ptrs[self.rank] + 1024), self.world,
+                                     self.rank, C.c_void_p(out.data_ptr()), C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_tp_argmax")
+        return out
+
     def peer_copy(self, segs_dev: torch.Tensor, n_segs: int, ctas: int = 0):
         rc = self._lib.mlf_peer_copy(C.c_void_p(segs_dev.data_ptr()), n_segs, ctas, C.c_uint64(_lib.stream_handle()))
         _lib.check(rc, "mlf_peer_copy")

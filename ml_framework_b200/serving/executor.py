@@ -53,11 +53,33 @@ class PagedLlamaExecutor:
         self.max_blocks = (self.cfg.max_seq_len + kv.block_size - 1) // kv.block_size
         self.tokens_generated = 0
         self._graphs = None
-        if self.native and self.cfg.use_cuda_graphs and (tp is None or tp.world == 1):
+        self._ar_calls = 0
+        if self.native and self.cfg.use_cuda_graphs and (tp is None or tp.world == 1 or tp.fused):
             from ..hal.cuda_graphs import CaptureOptions, CUDAGraphManager
             self._graphs = CUDAGraphManager(CaptureOptions(warmup_iterations=self.cfg.graph_warmup_steps))
 
     # ---- tensor-parallel reduction of partial projections
+    def _ar_staging(self, T: int):
+        """[T, d_model] view of one of two alternating peer-visible staging buffers for a row-parallel product.
+        Two per transformer block, so a step (eager or a replayed graph) always starts on the same one."""
+        tp = self.tp
+        nbytes = max(self.cfg.max_batch, self.cfg.prefill_chunk, self.cfg.max_prefill_tokens) * self.mc.d_model * 2
+        nbytes = (nbytes + 255) // 256 * 256
+        buf = tp.symm_buffer("serve.ar2", 2 * nbytes)
+        off = (self._ar_calls % 2) * nbytes
+        self._ar_calls += 1
+        return buf, off, buf.view(torch.bfloat16, T * self.mc.d_model, off).view(T, self.mc.d_model)
+
+    def _row_parallel(self, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """residual + sum over ranks of a @ w^T: the product lands in the staging buffer, one kernel
+        synchronises with the peers and adds their partial sums."""
+        T = a.shape[0]
+        buf, off, stage = self._ar_staging(T)
+        gemm(a, w, out=stage)
+        out = torch.empty_like(residual)
+        self.tp.symm.all_reduce_one_shot_sync(buf, out, T * self.mc.d_model, residual=residual, offset_bytes=off)
+        return out
+
     def _reduce(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         if self.tp is None or self.tp.world == 1:
             return partial + residual if residual is not None else partial
@@ -101,7 +123,10 @@ class PagedLlamaExecutor:
             # A decode step (few rows, whole weights) streams weights: plain products let the GEMM split K over
             # all SMs, the residual stream takes the product as an accumulation, SwiGLU runs as its own pass.
             few_rows = T <= 256
-            if multi:
+            sync_ar = multi and self.tp.fused
+            if sync_ar:
+                x = self._row_parallel(a.reshape(T, self.hq * D), o_w, x)
+            elif multi:
                 x = self._reduce(gemm(a.reshape(T, self.hq * D), o_w), x)
             elif few_rows:
                 gemm(a.reshape(T, self.hq * D), o_w, out=x, flags=_lib.EPI_ACCUM)
@@ -109,6 +134,8 @@ class PagedLlamaExecutor:
                 x = gemm(a.reshape(T, self.hq * D), o_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
             h, _, _ = native.norm_fwd(x, blk.norm2.weight, None, mc.norm_eps, True, want_stats=False)
             hid = native.swiglu_fwd(gemm(h, gu_w), interleaved=True) if few_rows else gemm(h, gu_w, flags=_lib.EPI_SWIGLU)
+            if sync_ar:
+                return self._row_parallel(hid, dn_w, x)
             if multi:
                 return self._reduce(gemm(hid, dn_w), x)
             if few_rows:
@@ -135,6 +162,22 @@ class PagedLlamaExecutor:
         return self._reduce(F.linear(hid, dn_w), x)
 
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
+        tp = self.tp
+        if self.native and tp is not None and tp.world > 1 and tp.fused and hasattr(self.m.embed, "local_v"):
+            # vocabulary-parallel lookup summed over the ranks by the in-kernel-synchronised all-reduce (a staging
+            # buffer of its own: used once per step, far from its previous use)
+            emb = self.m.embed
+            T, d = ids.numel(), self.mc.d_model
+            cap = max(self.cfg.max_batch, self.cfg.prefill_chunk, self.cfg.max_prefill_tokens)
+            buf = tp.symm_buffer("serve.embed", (cap * d * 2 + 255) // 256 * 256)
+            stage = buf.view(torch.bfloat16, T * d).view(T, d)
+            flat = ids.reshape(-1)
+            mask = (flat >= emb.lo) & (flat < emb.lo + emb.local_v)
+            local = (flat - emb.lo).clamp(0, emb.local_v - 1)
+            stage.copy_(F.embedding(local, emb.weight) * mask[:, None].to(emb.weight.dtype))
+            out = torch.empty(T, d, dtype=torch.bfloat16, device=ids.device)
+            tp.symm.all_reduce_one_shot_sync(buf, out, T * d)
+            return out.view(*ids.shape, d)
         return self.m.embed(ids)
 
     def _logits_argmax(self, x_last: torch.Tensor) -> torch.Tensor:
@@ -142,6 +185,9 @@ class PagedLlamaExecutor:
         if self.native:
             h, _, _ = native.norm_fwd(x_last.contiguous(), self.m.norm_f.weight, None, mc.norm_eps, True, want_stats=False)
             logits = gemm(h, self.m.lm_head)
+            if self.tp is not None and self.tp.world > 1 and self.tp.fused:
+                cand = self.tp.symm_buffer("serve.argmax", max(self.cfg.max_batch, 1) * 8)
+                return self.tp.symm.tp_argmax(logits, self.tp.rank * logits.shape[1], mc.vocab_size, cand)
             if self.tp is not None and self.tp.world > 1:
                 full = self.tp.pg.all_gather(logits, dim=-1)
                 return full[:, :mc.vocab_size].float().argmax(-1)

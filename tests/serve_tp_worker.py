@@ -1,7 +1,8 @@
 """Worker for the multi-GPU serving test (one process per GPU, launched by torchrun): a tensor-parallel Llama served
 with continuous batching over the paged KV cache. Rank 0 runs the scheduler and broadcasts each iteration's plan;
-the partial sums of the row-parallel projections are reduced once with the one-shot peer-memory kernel and once
-with a process-group all-reduce; both runs must generate the same tokens."""
+the partial sums of the row-parallel projections are reduced with the one-shot peer-memory kernel (eagerly, and
+with decode steps replayed from CUDA graphs) and with a process-group all-reduce; all runs must generate the same
+tokens."""
 import os
 import sys
 
@@ -30,14 +31,15 @@ def main():
     prompts = [[(11 * i + 5 * j) % (cfg.vocab_size - 1) + 1 for j in range(18 + 7 * i)] for i in range(5)]
     symm = SymmetricMemory(pg)
     outs = {}
-    for mode, fused in (("fused", True), ("nccl", False)):
+    for mode, fused, graphs in (("fused", True, False), ("fused+graphs", True, True), ("nccl", False, False)):
         torch.manual_seed(100 + r)
         tp = TPContext(pg, symm if fused else None, fused)
         model = LlamaTP(cfg, tp, sequence_parallel=False, dtype=torch.bfloat16, device=dev).eval()
         for p in model.replicated_parameters():
             pg.broadcast(p.data, src=0)
         kv = KVCacheBlockManager(128, 16, cfg.head_dim, cfg.n_layers, cfg.n_kv_heads // W, device=dev, dtype=torch.bfloat16)
-        ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=256, prefill_chunk=64, use_cuda_graphs=False), tp=tp)
+        ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=256, prefill_chunk=64, use_cuda_graphs=graphs,
+                                                          graph_warmup_steps=1), tp=tp)
         if r == 0:
             leader = TPLeaderExecutor(ex, pg)
             sched = ContinuousBatchScheduler(leader, kv, SchedulerConfiguration(max_batch_size=8, warmup_iterations=0), BatchConstraints(max_batch_size=8),
@@ -54,10 +56,11 @@ def main():
         assert _lib.read_status(True) == 0, f"kernel status after {mode}"
         pg.barrier()
     if r == 0:
-        assert all(len(t) == 10 for t in outs["fused"]), outs
-        same = sum(a == b for x, y in zip(outs["fused"], outs["nccl"]) for a, b in zip(x, y))
         total = sum(len(x) for x in outs["nccl"])
-        assert same >= 0.9 * total, (same, total, outs)
+        for mode in ("fused", "fused+graphs"):
+            assert all(len(t) == 10 for t in outs[mode]), outs
+            same = sum(a == b for x, y in zip(outs[mode], outs["nccl"]) for a, b in zip(x, y))
+            assert same >= 0.9 * total, (mode, same, total, outs)
         print("SERVE_TP_WORKER_OK", same, total)
     destroy_process_group()
 
