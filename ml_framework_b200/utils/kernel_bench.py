@@ -226,6 +226,22 @@ def bench_paged_decode(args) -> list[dict]:
     return rows
 
 
+def run_paged_small() -> list[dict]:
+    """Two launches of the paged decode kernel at B = 256, ctx 1024 (K / V of the cached tokens: 1.07 GB > L2):
+    the case profiled with ncu."""
+    from ..ops import native
+    bs, D, B, Hq, Hkv, ln = 16, 128, 256, 32, 8, 1024
+    nblk = ln // bs
+    cache = torch.randn(B * nblk, 2, bs, Hkv, D, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(B * nblk, device="cuda").to(torch.int32).view(B, nblk)
+    sl = torch.full((B,), ln, dtype=torch.int32, device="cuda")
+    q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        native.paged_decode(q, cache, table, sl, ln, split_tokens=0)
+    torch.cuda.synchronize()
+    return [{"ran": "paged decode B256 ctx1024 x2"}]
+
+
 def run_gemm_small() -> list[dict]:
     """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
     from ..ops.gemm import gemm
@@ -240,7 +256,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -259,6 +275,8 @@ def main():
         rows = bench_gemm_decode(args)
     elif args.what == "paged":
         rows = bench_paged_decode(args)
+    elif args.what == "paged_small":
+        rows = run_paged_small()
     elif args.what == "attn":
         from .kernel_bench_attn import bench_attn
         rows = bench_attn(args)
