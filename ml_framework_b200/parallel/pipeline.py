@@ -288,6 +288,14 @@ class _LocalView:
     def recv_backward(self, shape=None, dtype=None, device=None): return self.c.recv(self.rank + 1, self.rank, "bwd")
     def barrier(self): self.c.barrier()
 
+    def send_forward_recv_backward(self, t, shape=None, dtype=None, device=None):
+        self.send_forward(t)
+        return self.recv_backward()
+
+    def send_backward_recv_forward(self, t, shape=None, dtype=None, device=None):
+        self.send_backward(t)
+        return self.recv_forward()
+
 
 class ProcessGroupPipelineCommunicator:
     """Stage-to-stage transfers over a process group (stage s == group rank s)."""
@@ -359,18 +367,30 @@ class _ScheduleBase:
         self.act_shape_fn, self.act_dtype = act_shape_fn, act_dtype
         self.stats = PipelineStats(stages=stage.total_stages, micro_batches=config.micro_batches)
         self._saved: Dict[int, tuple] = {}
+        self._out_spec: Dict[int, tuple] = {}
         self.losses: List[torch.Tensor] = []
+
+    def _act_spec(self, x_local=None):
+        st = self.stage
+        shape = self.act_shape_fn(x_local) if self.act_shape_fn else None
+        return shape, self.act_dtype or next(st.parameters()).dtype, next(st.parameters()).device
 
     # one micro-batch forward on this stage
     def _forward(self, mb: int, x_local: Optional[torch.Tensor], target: Optional[torch.Tensor]):
         st = self.stage
-        t0 = time.perf_counter()
         if st.is_first:
             x = x_local
         else:
-            shape = self.act_shape_fn(x_local) if self.act_shape_fn else None
-            dev = next(st.parameters()).device
-            x = self.comm.recv_forward(shape, self.act_dtype or next(st.parameters()).dtype, dev)
+            x = self.comm.recv_forward(*self._act_spec(x_local))
+        y = self._forward_compute(mb, x, target)
+        if not st.is_last:
+            self.comm.send_forward(y.detach())
+
+    def _forward_compute(self, mb: int, x: torch.Tensor, target: Optional[torch.Tensor]):
+        """Runs the stage on one micro-batch (input already here); returns the stage output."""
+        st = self.stage
+        t0 = time.perf_counter()
+        if not st.is_first:
             x = x.detach().requires_grad_(True)
         recompute = self.ckpt.should_checkpoint(mb, x.numel() * x.element_size())
         if recompute:
@@ -386,11 +406,22 @@ class _ScheduleBase:
                 if loss is not None:
                     self._saved[mb] = (x, loss, False, target)
                     self.losses.append(loss.detach())
-        else:
-            self.comm.send_forward(y.detach())
+        self._out_spec[mb] = (tuple(y.shape), y.dtype, y.device)
         self.stats.forward_time_s += time.perf_counter() - t0
+        return y
 
     def _backward(self, mb: int):
+        st = self.stage
+        g = None
+        if not st.is_last:
+            g = self.comm.recv_backward(*self._out_spec[mb])
+        dx = self._backward_compute(mb, g)
+        if not st.is_first:
+            self.comm.send_backward(dx)
+
+    def _backward_compute(self, mb: int, g: Optional[torch.Tensor]):
+        """Backward of one micro-batch given the gradient of the stage output (None on the last stage);
+        returns the gradient of the stage input (None on the first stage)."""
         st = self.stage
         t0 = time.perf_counter()
         x, y, recompute, target = self._saved.pop(mb)
@@ -402,12 +433,9 @@ class _ScheduleBase:
         if st.is_last:
             (y / self.cfg.micro_batches).backward() if self.loss_fn is not None else y.backward(torch.ones_like(y) / self.cfg.micro_batches)
         else:
-            dev = y.device
-            g = self.comm.recv_backward(tuple(y.shape), y.dtype, dev)
-            y.backward(g)
-        if not st.is_first:
-            self.comm.send_backward(x.grad)
+            y.backward(g.reshape(y.shape))
         self.stats.backward_time_s += time.perf_counter() - t0
+        return None if st.is_first else x.grad
 
     def order(self) -> List[Tuple[str, int]]:
         raise NotImplementedError
@@ -450,6 +478,51 @@ class OneFOneBScheduler(_ScheduleBase):
         while b < n:
             seq.append(("B", b)); b += 1
         return seq
+
+    def train_iteration(self, inputs: Optional[torch.Tensor], targets: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """1F1B with paired transfers in the steady state: a stage hands its output forward and takes the
+        gradient of an earlier micro-batch back in ONE batched point-to-point group (and the mirror image
+        after each backward). Separate blocking sends in opposite directions between two neighbours wait on
+        each other once a message exceeds the transport's buffering; paired groups cannot."""
+        n, p, r = self.cfg.micro_batches, self.stage.total_stages, self.stage.rank
+        st, comm = self.stage, self.comm
+        if not hasattr(comm, "send_forward_recv_backward"):
+            return super().train_iteration(inputs, targets)
+        mbm = MicroBatchManager(n)
+        xs = mbm.split_batch(inputs) if inputs is not None else [None] * n
+        ts = mbm.split_batch(targets) if targets is not None else [None] * n
+        self.losses = []
+        spec = self._act_spec(None) if (not st.is_first or not st.is_last) else None
+        warm = min(p - r - 1, n)
+        steady = n - warm
+        for i in range(warm):
+            x = xs[i] if st.is_first else comm.recv_forward(*spec)
+            y = self._forward_compute(i, x, ts[i])
+            if not st.is_last:
+                comm.send_forward(y.detach())
+        x = None
+        if steady > 0:
+            x = xs[warm] if st.is_first else comm.recv_forward(*spec)
+        for i in range(steady):
+            f = warm + i
+            y = self._forward_compute(f, x, ts[f])
+            g = None if st.is_last else comm.send_forward_recv_backward(y.detach(), *self._out_spec[i])
+            dx = self._backward_compute(i, g)
+            last_fwd = i == steady - 1
+            if st.is_first:
+                x = None if last_fwd else xs[f + 1]
+            elif last_fwd:
+                comm.send_backward(dx)
+            else:
+                x = comm.send_backward_recv_forward(dx, *spec)
+        for b in range(steady, n):
+            g = None if st.is_last else comm.recv_backward(*self._out_spec[b])
+            dx = self._backward_compute(b, g)
+            if not st.is_first:
+                comm.send_backward(dx)
+        if st.is_last and self.losses:
+            return torch.stack(self.losses).mean()
+        return None
 
     def max_live_activations(self) -> int:
         live = peak = 0
