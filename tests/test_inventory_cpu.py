@@ -546,3 +546,29 @@ def test_stream_manager_and_async_pipeline_executor_cpu():
     sm.wait_for_event("e", sm.comm_stream(1))
     with pytest.raises(KeyError):
         sm.wait_for_event("nope", None)
+
+
+def test_config_loader_file_env_and_validation(tmp_path):
+    """Component config dataclasses load from a mapping / JSON / YAML file with environment overrides and run
+    their own validation."""
+    import pytest
+    from ml_framework_b200.config import load_config, save_config, to_dict
+    from ml_framework_b200.parallel.fsdp import FSDPConfig
+    from ml_framework_b200.parallel.pipeline import PipelineConfig, SchedulingStrategy
+    from ml_framework_b200.serving.executor import ExecutorConfig
+    pc = load_config(PipelineConfig, {"num_stages": 4, "micro_batches": 16, "schedule": "gpipe"})
+    assert pc.num_stages == 4 and pc.schedule == SchedulingStrategy.GPIPE
+    p = tmp_path / "pipe.yaml"
+    save_config(pc, p)
+    again = load_config(PipelineConfig, p, env_prefix="MLF_PIPELINE", environ={"MLF_PIPELINE_MICRO_BATCHES": "8"})
+    assert again.micro_batches == 8 and again.num_stages == 4 and to_dict(again)["schedule"] == SchedulingStrategy.GPIPE.value
+    with pytest.raises(ValueError):
+        load_config(PipelineConfig, {"num_stages": 0})
+    with pytest.raises(KeyError):
+        load_config(PipelineConfig, {"stages": 2})
+    j = tmp_path / "exec.json"
+    j.write_text('{"max_batch": 64, "use_cuda_graphs": false}')
+    ec = load_config(ExecutorConfig, j, env_prefix="MLF_EXEC", environ={"MLF_EXEC_USE_CUDA_GRAPHS": "true"})
+    assert ec.max_batch == 64 and ec.use_cuda_graphs is True
+    with pytest.raises(ValueError):
+        load_config(FSDPConfig, {"sharding_strategy": "diagonal"})
