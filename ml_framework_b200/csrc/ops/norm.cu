@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(256)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-                float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms) {
+                float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms,
+                const __nv_bfloat16* __restrict__ dx_add /* optional: added to dx (gradient of a skip connection) */) {
   constexpr int D = NV * 256;
   constexpr int NK = MODE == 0 ? NV : 1;          // cached row vectors
   constexpr int NG = MODE <= 1 ? NV : 1;          // register dgamma partials
@@ -170,6 +171,12 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         }
         if (MODE == 1 && !rms) atomicAdd(&acc[D + col + j], d[j]);
       }
+      if (dx_add) {
+        float e[8];
+        unpack8(reinterpret_cast<const uint4*>(dx_add + (long long)row * D)[i * 32 + lane], e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += e[j];
+      }
       dxr[i * 32 + lane] = pack8(o);
     }
   }
@@ -199,7 +206,8 @@ __global__ void __launch_bounds__(256, 2)
 norm_bwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                     const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                     const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-                    float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms) {
+                    float* __restrict__ partials /* [grid, 2, D] */, int rows, int rms,
+                    const __nv_bfloat16* __restrict__ dx_add /* optional: added to dx */) {
   constexpr int D = NVT * 2048;
   __shared__ float red[2][8][2 * R];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -213,7 +221,7 @@ norm_bwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   const float inv_d = 1.f / D;
   int buf = 0;
   for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, buf ^= 1) {
-    uint4 xv[R][NVT], dv[R][NVT];
+    uint4 xv[R][NVT], dv[R][NVT], ev[R][NVT];
     float mean[R], rstd[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -223,6 +231,7 @@ norm_bwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
       for (int v = 0; v < NVT; ++v) {
         xv[r][v] = reinterpret_cast<const uint4*>(x)[base + v * 256 + tid];
         dv[r][v] = ok ? reinterpret_cast<const uint4*>(dy)[base + v * 256 + tid] : make_uint4(0, 0, 0, 0);
+        ev[r][v] = dx_add ? reinterpret_cast<const uint4*>(dx_add)[base + v * 256 + tid] : make_uint4(0, 0, 0, 0);
       }
       mean[r] = rms ? 0.f : mean_in[ok ? row0 + r : row0];
       rstd[r] = rstd_in[ok ? row0 + r : row0];
@@ -271,13 +280,14 @@ norm_bwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
       const float nm = -mean[r] * rstd[r];
 #pragma unroll
       for (int v = 0; v < NVT; ++v) {
-        float f[8], d[8], o[8];
+        float f[8], d[8], e[8], o[8];
         unpack8(xv[r][v], f);
         unpack8(dv[r][v], d);
+        unpack8(ev[r][v], e);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float xh = fmaf(f[j], rstd[r], nm);
-          o[j] = rstd[r] * (fmaf(d[j], g[v][j], -c1) - xh * c2);
+          o[j] = fmaf(rstd[r], fmaf(d[j], g[v][j], -c1) - xh * c2, e[j]);
         }
         reinterpret_cast<uint4*>(dx)[(long long)(row0 + r) * (D / 8) + v * 256 + tid] = pack8(o);
       }
@@ -295,25 +305,29 @@ norm_bwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   }
 }
 
-// dgamma[c] = sum_g partials[g][0][c]; dbeta likewise. 32 columns x 8 partial-lanes per CTA.
-__global__ void __launch_bounds__(256)
+// dgamma[c] = sum_g partials[g][0][c]; dbeta likewise. 32 columns x 32 partial-lanes per CTA (a few hundred
+// partial rows: the kernel is pure load latency, so the rows are spread over 32 warps).
+constexpr int NF_WARPS = 32;
+__global__ void __launch_bounds__(NF_WARPS * 32)
 norm_bwd_finalize_kernel(const float* __restrict__ partials, int nparts, int D, void* dgamma, void* dbeta,
                          int out_fp32, int accumulate) {
-  __shared__ float sg[8][33], sb[8][33];
+  __shared__ float sg[NF_WARPS][33], sb[NF_WARPS][33];
   const int cl = threadIdx.x & 31, pl = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cl;
   float g = 0.f, b = 0.f;
-  if (c < D)
-    for (int p = pl; p < nparts; p += 8) {
+  if (c < D) {
+#pragma unroll 4
+    for (int p = pl; p < nparts; p += NF_WARPS) {
       g += partials[(long long)p * 2 * D + c];
-      b += partials[(long long)p * 2 * D + D + c];
+      if (dbeta) b += partials[(long long)p * 2 * D + D + c];
     }
+  }
   sg[pl][cl] = g;
   sb[pl][cl] = b;
   __syncthreads();
   if (pl != 0 || c >= D) return;
 #pragma unroll
-  for (int k = 1; k < 8; ++k) { g += sg[k][cl]; b += sb[k][cl]; }
+  for (int k = 1; k < NF_WARPS; ++k) { g += sg[k][cl]; b += sb[k][cl]; }
   if (out_fp32) {
     float* dgp = static_cast<float*>(dgamma);
     dgp[c] = g + (accumulate ? dgp[c] : 0.f);
@@ -345,7 +359,7 @@ static int launch_fwd(const void* x, const void* g, const void* b, void* y, floa
 
 template <int NV>
 static int launch_bwd(const void* x, const void* dy, const void* g, const float* mean, const float* rstd, void* dx,
-                      float* partials, int grid, int rows, int rms, cudaStream_t st) {
+                      float* partials, int grid, int rows, int rms, const void* dx_add, cudaStream_t st) {
   constexpr int smem = 2 * NV * 256 * 4;
   constexpr int MODE = NV <= 8 ? 0 : (NV <= 20 ? 1 : 2);
   static bool attr_set[64] = {false};
@@ -358,7 +372,8 @@ static int launch_bwd(const void* x, const void* dy, const void* g, const float*
   norm_bwd_kernel<NV, MODE><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
                                                static_cast<const __nv_bfloat16*>(dy),
                                                static_cast<const __nv_bfloat16*>(g), mean, rstd,
-                                               static_cast<__nv_bfloat16*>(dx), partials, rows, rms);
+                                               static_cast<__nv_bfloat16*>(dx), partials, rows, rms,
+                                               static_cast<const __nv_bfloat16*>(dx_add));
                                                count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -405,9 +420,11 @@ MLF_API long long mlf_norm_bwd_scratch_elems(int rows, int D) {
   return (long long)norm_bwd_grid(rows, D, nullptr) * 2 * D;
 }
 
-MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
-                         void* dx, void* dgamma, void* dbeta, float* partials, int rows, int D, int rms,
-                         int grads_fp32, int accumulate, uint64_t stream) {
+// dx_add (optional, bf16 [rows, D]) is added to dx: the gradient arriving over a skip connection that
+// branched off the normalised tensor's input, so that the sum needs no pass of its own.
+MLF_API int mlf_norm_bwd_add(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                             void* dx, void* dgamma, void* dbeta, float* partials, int rows, int D, int rms,
+                             int grads_fp32, int accumulate, const void* dx_add, uint64_t stream) {
   MLF_REQUIRE(D % 256 == 0, "norm: D=%d must be a multiple of 256", D);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   bool cta_rows = false;
@@ -419,25 +436,32 @@ MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const
     const __nv_bfloat16* dyp = static_cast<const __nv_bfloat16*>(dy);
     const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(gamma);
     __nv_bfloat16* dxp = static_cast<__nv_bfloat16*>(dx);
+    const __nv_bfloat16* addp = static_cast<const __nv_bfloat16*>(dx_add);
     switch (D / 2048) {
-      case 1: norm_bwd_cta_kernel<1, 4><<<grid, 256, 0, st>>>(xp, dyp, gp, mean, rstd, dxp, partials, rows, rms); break;
-      default: norm_bwd_cta_kernel<2, 2><<<grid, 256, 0, st>>>(xp, dyp, gp, mean, rstd, dxp, partials, rows, rms); break;
+      case 1: norm_bwd_cta_kernel<1, 4><<<grid, 256, 0, st>>>(xp, dyp, gp, mean, rstd, dxp, partials, rows, rms, addp); break;
+      default: norm_bwd_cta_kernel<2, 2><<<grid, 256, 0, st>>>(xp, dyp, gp, mean, rstd, dxp, partials, rows, rms, addp); break;
     }
     count_launch();
     MLF_CHECK_CUDA(cudaGetLastError());
     rc = 0;
   } else
   switch (D / 256) {
-#define CASE(NV) case NV: rc = launch_bwd<NV>(x, dy, gamma, mean, rstd, dx, partials, grid, rows, rms, st); break;
+#define CASE(NV) case NV: rc = launch_bwd<NV>(x, dy, gamma, mean, rstd, dx, partials, grid, rows, rms, dx_add, st); break;
     CASE(1) CASE(2) CASE(3) CASE(4) CASE(6) CASE(8) CASE(12) CASE(16) CASE(20) CASE(24) CASE(32)
 #undef CASE
     default: matched = false;
   }
   MLF_REQUIRE(matched, "norm: unsupported D=%d", D);
   if (rc) return rc;
-  norm_bwd_finalize_kernel<<<(D + 31) / 32, 256, 0, st>>>(partials, grid, D, dgamma, rms ? nullptr : dbeta,
+  norm_bwd_finalize_kernel<<<(D + 31) / 32, NF_WARPS * 32, 0, st>>>(partials, grid, D, dgamma, rms ? nullptr : dbeta,
                                                             grads_fp32, accumulate);
                                                             count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+MLF_API int mlf_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                         void* dx, void* dgamma, void* dbeta, float* partials, int rows, int D, int rms,
+                         int grads_fp32, int accumulate, uint64_t stream) {
+  return mlf_norm_bwd_add(x, dy, gamma, mean, rstd, dx, dgamma, dbeta, partials, rows, D, rms, grads_fp32, accumulate, nullptr, stream);
 }

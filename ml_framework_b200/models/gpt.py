@@ -69,8 +69,10 @@ class GPTBlock(nn.Module):
                            out_init_std=out_std)
 
     def forward(self, x):
-        x = self.attn(self.ln1(x), residual=x)
-        x = self.mlp(self.ln2(x), residual=x)
+        h, skip = self.ln1.with_skip(x)
+        x = self.attn(h, residual=skip)
+        h, skip = self.ln2.with_skip(x)
+        x = self.mlp(h, residual=skip)
         return x
 
 

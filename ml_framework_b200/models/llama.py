@@ -77,8 +77,10 @@ class LlamaBlock(nn.Module):
         self.mlp = SwiGLUMLP(cfg.d_model, cfg.d_ff, dtype, device, cfg.init_std, out_std)
 
     def forward(self, x, positions=None):
-        x = self.attn(self.norm1(x), residual=x, positions=positions)
-        x = self.mlp(self.norm2(x), residual=x)
+        h, skip = self.norm1.with_skip(x)
+        x = self.attn(h, residual=skip, positions=positions)
+        h, skip = self.norm2.with_skip(x)
+        x = self.mlp(h, residual=skip)
         return x
 
 

@@ -38,10 +38,12 @@ class LlamaBlockTP(nn.Module):
 
     def forward(self, x, B: int, S: int):
         """x: [T, d] (replicated) or [T/W, d] (sequence parallel) with T = B*S."""
-        h = self.qkv(self.norm1(x))                                   # [T, (hq + 2 hkv) * D]
+        n1, skip = self.norm1.with_skip(x)
+        h = self.qkv(n1)                                              # [T, (hq + 2 hkv) * D]
         a = Fm.attention_packed(h, B, S, self.hq, self.hkv, self.cfg.head_dim, True, self.cfg.rope_theta)
-        x = self.o(a, residual=x)
-        gu = self.gate_up(self.norm2(x))                              # local (gate, up) pairs
+        x = self.o(a, residual=skip)
+        n2, x = self.norm2.with_skip(x)
+        gu = self.gate_up(n2)                                         # local (gate, up) pairs
         if Fm._native(gu):
             from ..ops import native
             hid = _SwiGLU.apply(gu)

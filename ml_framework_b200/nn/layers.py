@@ -54,6 +54,11 @@ class LayerNorm(nn.Module):
     def forward(self, x):
         return Fm.layer_norm(x, self.weight, self.bias, self.eps)
 
+    def with_skip(self, x):
+        """``(norm(x), x)``: use the second value as the residual of the branch so that the backward adds the two
+        gradients of x inside the normalisation's kernel."""
+        return Fm.layer_norm_skip(x, self.weight, self.bias, self.eps)
+
 
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5, dtype=None, device=None):
@@ -63,6 +68,9 @@ class RMSNorm(nn.Module):
 
     def forward(self, x):
         return Fm.rms_norm(x, self.weight, self.eps)
+
+    def with_skip(self, x):
+        return Fm.rms_norm_skip(x, self.weight, self.eps)
 
 
 class Embedding(nn.Module):

@@ -236,6 +236,56 @@ class _NormFn(torch.autograd.Function):
         return dx, dg, (db if not ctx.rms else None), None, None
 
 
+class _NormSkipFn(torch.autograd.Function):
+    """Normalisation that also hands its input on as the skip connection: ``(norm(x), x)``. The backward
+    receives both gradients at once and the kernel adds the skip gradient to the normalisation's input
+    gradient, so the sum at the branch point needs no pass of its own."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, rms):
+        xc = x.contiguous()
+        y, mean, rstd = native.norm_fwd(xc, gamma, beta, eps, rms)
+        ctx.save_for_backward(xc, gamma, mean if mean is not None else rstd, rstd)
+        ctx.rms = rms
+        ctx.gamma_ref, ctx.beta_ref = gamma, beta
+        return y, xc.view_as(xc)
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        x, gamma, mean, rstd = ctx.saved_tensors
+        gt, gacc = _sink(ctx.gamma_ref)
+        bt, _ = _sink(ctx.beta_ref)
+        if dy is None:
+            return dskip, None, None, None, None
+        add = None
+        if dskip is not None:
+            add = dskip.contiguous()
+            if add.dtype != x.dtype:
+                add = add.to(x.dtype)
+        dx, dg, db = native.norm_bwd(x, dy.contiguous(), gamma, None if ctx.rms else mean, rstd, ctx.rms,
+                                     dgamma_out=gt, dbeta_out=bt if not ctx.rms else None, accumulate=gacc, dx_add=add)
+        if gt is not None:
+            _done(ctx.gamma_ref)
+            dg = None
+        if bt is not None and not ctx.rms:
+            _done(ctx.beta_ref)
+            db = None
+        return dx, dg, (db if not ctx.rms else None), None, None
+
+
+def layer_norm_skip(x, gamma, beta, eps: float = 1e-5):
+    """``(layer_norm(x), x)`` with the two gradients summed inside the backward kernel."""
+    if _native(x, gamma, beta) and x.shape[-1] % 256 == 0:
+        return _NormSkipFn.apply(x, gamma, beta, eps, False)
+    return F.layer_norm(x, (x.shape[-1],), gamma, beta, eps), x
+
+
+def rms_norm_skip(x, gamma, eps: float = 1e-5):
+    if _native(x, gamma) and x.shape[-1] % 256 == 0:
+        return _NormSkipFn.apply(x, gamma, None, eps, True)
+    return rms_norm(x, gamma, eps), x
+
+
 def layer_norm(x, gamma, beta, eps: float = 1e-5):
     if _native(x, gamma, beta) and x.shape[-1] % 256 == 0:
         return _NormFn.apply(x, gamma, beta, eps, False)

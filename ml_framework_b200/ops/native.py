@@ -104,10 +104,16 @@ def norm_fwd(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor],
 
 def norm_bwd(x: torch.Tensor, dy: torch.Tensor, gamma: torch.Tensor, mean, rstd, rms: bool,
              dgamma_out: Optional[torch.Tensor] = None, dbeta_out: Optional[torch.Tensor] = None,
-             accumulate: bool = False):
+             accumulate: bool = False, dx_add: Optional[torch.Tensor] = None):
+    """``dx_add`` (same shape as x) is added to the returned dx inside the kernel: the gradient of a skip
+    connection that branched off x."""
     D = x.shape[-1]
     x2, dy2 = x.reshape(-1, D), dy.reshape(-1, D)
     assert x2.is_contiguous() and dy2.is_contiguous()
+    add2 = None
+    if dx_add is not None:
+        add2 = dx_add.reshape(-1, D)
+        assert add2.is_contiguous() and add2.dtype == x2.dtype and add2.shape == x2.shape
     rows = x2.shape[0]
     dx = torch.empty_like(x2)
     dgamma = dgamma_out if dgamma_out is not None else torch.empty(D, dtype=gamma.dtype, device=x.device)
@@ -118,9 +124,9 @@ def norm_bwd(x: torch.Tensor, dy: torch.Tensor, gamma: torch.Tensor, mean, rstd,
     L.mlf_norm_bwd_scratch_elems.restype = C.c_longlong
     n = L.mlf_norm_bwd_scratch_elems(rows, D)
     part = scratch("norm_bwd", n * 4, x.device)
-    rc = L.mlf_norm_bwd(_p(x2), _p(dy2), _p(gamma), _p(mean), _p(rstd), _p(dx), _p(dgamma), _p(dbeta), _p(part),
-                        rows, D, int(rms), int(dgamma.dtype == torch.float32), int(accumulate), _st())
-    _lib.check(rc, "mlf_norm_bwd")
+    rc = L.mlf_norm_bwd_add(_p(x2), _p(dy2), _p(gamma), _p(mean), _p(rstd), _p(dx), _p(dgamma), _p(dbeta), _p(part),
+                            rows, D, int(rms), int(dgamma.dtype == torch.float32), int(accumulate), _p(add2), _st())
+    _lib.check(rc, "mlf_norm_bwd_add")
     return dx.view(x.shape), dgamma, dbeta
 
 

@@ -39,6 +39,10 @@ def test_norm_fwd_bwd(D, rms):
     _close(dg, gf.grad, 3e-2)
     if not rms:
         _close(db, bf.grad, 3e-2)
+    # the gradient of a skip connection added inside the kernel
+    skip = torch.randn(rows, D, device="cuda").to(torch.bfloat16)
+    dx2, _, _ = native.norm_bwd(x, dy, g, mean, rstd, rms, dx_add=skip)
+    _close(dx2, xf.grad + skip.float())
 
 
 def test_elementwise_and_reduce():
