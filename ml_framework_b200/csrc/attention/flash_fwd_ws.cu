@@ -45,7 +45,8 @@ struct FlashWsParams {
   __nv_bfloat16* out;
   float* lse;
   long long ldo;
-  int B, S, Hq, Hkv;
+  int B, S, Hq, Hkv;           // S: query rows per sequence
+  int Skv, qoff;               // key/value rows per sequence; query row i sits at position i + qoff (= Skv - S)
   int causal;
   float scale_log2;
   int* err;
@@ -83,13 +84,14 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = pair * 2 * W_BQ;
   const long long row_base = (long long)b * p.S;
+  const long long kv_row_base = (long long)b * p.Skv;
   // key tiles each query tile needs
   int n_t[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int qs = q0 + t * W_BQ;
-    int n = (p.S + W_BKV - 1) / W_BKV;
-    if (p.causal) n = min(n, (qs + W_BQ + W_BKV - 1) / W_BKV);
+    int n = (p.Skv + W_BKV - 1) / W_BKV;
+    if (p.causal) n = min(n, (qs + p.qoff + W_BQ + W_BKV - 1) / W_BKV);
     n_t[t] = qs < p.S ? n : 0;
   }
   const int n_kv = max(n_t[0], n_t[1]);
@@ -137,7 +139,7 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int krow = (int)(row_base + j * W_BKV);
+        const int krow = (int)(kv_row_base + j * W_BKV);
         if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_ATTN)) break;
         mbar_expect_tx(k_full(s), W_TILE_BYTES);
         tma_load_2d(sK + s * W_TILE_BYTES, &tmK, hkv * W_D, krow, k_full(s));
@@ -223,7 +225,7 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!mbar_wait_warp(s_full(t), j & 1, abort_flag, p.err, ERR_WAIT_ATTN)) { ok = false; break; }
       tc_fence_after_sync();
       const int k0 = j * W_BKV;
-      const bool need_mask = (p.causal && k0 + W_BKV - 1 > q0 + t * W_BQ) || (k0 + W_BKV > p.S);
+      const bool need_mask = (p.causal && k0 + W_BKV - 1 > q0 + t * W_BQ + p.qoff) || (k0 + W_BKV > p.Skv);
       uint32_t sv[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tS(t) + 32 * c + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&sv[32 * c]));
@@ -232,7 +234,7 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
           const int kj = k0 + i;
-          if (kj >= p.S || (p.causal && kj > qi)) sv[i] = __float_as_uint(-INFINITY);
+          if (kj >= p.Skv || (p.causal && kj > qi + p.qoff)) sv[i] = __float_as_uint(-INFINITY);
         }
       }
       if (j == 0) {
@@ -346,25 +348,29 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 using namespace mlf;
 
-// Same arguments as mlf_flash_fwd.
-MLF_API int mlf_flash_fwd_ws(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
-                             int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
-                             uint64_t stream) {
-  MLF_REQUIRE(B > 0 && S > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "flash_fwd: bad shape");
+// Queries [B * Sq rows] against keys / values [B * Skv rows], Skv >= Sq: query row i of a sequence sits at
+// position i + (Skv - Sq), i.e. the queries are the LAST Sq positions (a prompt chunk attending to its cached
+// prefix plus itself). Skv == Sq is plain self-attention.
+MLF_API int mlf_flash_fwd_prefix(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Skv, int Hq,
+                                 int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
+                                 uint64_t stream) {
+  const int S = Sq;
+  MLF_REQUIRE(B > 0 && S > 0 && Skv >= Sq && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "flash_fwd: bad shape");
   MLF_REQUIRE(scale > 0.f, "flash_fwd: softmax scale must be positive");
   MLF_REQUIRE(ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "flash_fwd: out must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   CUtensorMap tq, tk, tv;
   int rc;
-  const uint64_t rows = (uint64_t)B * S;
+  const uint64_t rows = (uint64_t)B * S, kv_rows = (uint64_t)B * Skv;
   if ((rc = cached_tmap_bf16(&tq, q, (uint64_t)Hq * W_D, rows, ldq, 64, W_BQ))) return rc;
-  if ((rc = cached_tmap_bf16(&tk, k, (uint64_t)Hkv * W_D, rows, ldk, 64, W_BKV))) return rc;
-  if ((rc = cached_tmap_bf16(&tv, v, (uint64_t)Hkv * W_D, rows, ldv, 64, W_BKV))) return rc;
+  if ((rc = cached_tmap_bf16(&tk, k, (uint64_t)Hkv * W_D, kv_rows, ldk, 64, W_BKV))) return rc;
+  if ((rc = cached_tmap_bf16(&tv, v, (uint64_t)Hkv * W_D, kv_rows, ldv, 64, W_BKV))) return rc;
   FlashWsParams p;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.lse = lse;
   p.ldo = ldo;
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.Skv = Skv; p.qoff = Skv - Sq;
   p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = device_status_word();
@@ -381,4 +387,11 @@ MLF_API int mlf_flash_fwd_ws(const void* q, const void* k, const void* v, void* 
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+// Same arguments as mlf_flash_fwd.
+MLF_API int mlf_flash_fwd_ws(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
+                             int Hkv, long long ldq, long long ldk, long long ldv, long long ldo, float scale, int causal,
+                             uint64_t stream) {
+  return mlf_flash_fwd_prefix(q, k, v, out, lse, B, S, S, Hq, Hkv, ldq, ldk, ldv, ldo, scale, causal, stream);
 }

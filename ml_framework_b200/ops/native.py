@@ -276,6 +276,24 @@ def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, S: int,
     return out, lse
 
 
+def flash_fwd_prefix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, Sq: int, Skv: int, *, causal: bool = True,
+                     scale: Optional[float] = None) -> torch.Tensor:
+    """Attention of the LAST ``Sq`` positions of each sequence over all ``Skv`` keys / values (a prompt chunk over
+    its cached prefix plus itself). q [B*Sq, Hq, 128]; k, v [B*Skv, Hkv, 128]; token stride arbitrary."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert D == 128 and T == B * Sq and k.shape[0] == B * Skv and v.shape[0] == B * Skv and Skv >= Sq
+    for t in (q, k, v):
+        assert t.stride(2) == 1 and t.stride(1) == D and t.dtype == torch.bfloat16
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    scale = scale if scale is not None else D ** -0.5
+    rc = _L().mlf_flash_fwd_prefix(_p(q), _p(k), _p(v), _p(out), None, B, Sq, Skv, Hq, Hkv, C.c_longlong(q.stride(0)),
+                                   C.c_longlong(k.stride(0)), C.c_longlong(v.stride(0)), C.c_longlong(Hq * D), C.c_float(scale),
+                                   int(causal), _st())
+    _lib.check(rc, "mlf_flash_fwd_prefix")
+    return out
+
+
 def flash_bwd(q, k, v, o, dout, lse, B: int, S: int, *, causal: bool = True, scale: Optional[float] = None,
               dq: Optional[torch.Tensor] = None, dk: Optional[torch.Tensor] = None, dv: Optional[torch.Tensor] = None):
     """Gradients of :func:`flash_fwd`. ``dq/dk/dv`` may be views into a packed dQKV buffer."""

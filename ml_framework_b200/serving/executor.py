@@ -227,6 +227,8 @@ class PagedLlamaExecutor:
             if self.native and start == 0:
                 out, _ = native.flash_fwd(q, kk, vv, 1, n, causal=True, want_lse=False)
                 return out
+            if self.native:                  # a later chunk: its rows are the last n positions of the gathered pages
+                return native.flash_fwd_prefix(q, kk, vv, 1, n, total, causal=True)
             o, _ = reference.attention_ref(q[None], kk[None], vv[None], causal=True, start_pos=start)
             return o[0].to(q.dtype)
         x = self._embed(ids[None])[0]

@@ -82,3 +82,17 @@ def _flash_bwd_case(B, S, Hq, Hkv, causal):
     assert _rel(dv.view(B, S, Hkv, D), vf.grad) < 3e-2
     assert _rel(dk.view(B, S, Hkv, D), kf.grad) < 3e-2
     assert _rel(dq.view(B, S, Hq, D), qf.grad) < 3e-2
+
+
+@pytest.mark.parametrize("B,Sq,Skv,Hq,Hkv", [(1, 64, 64 + 512, 4, 2), (2, 200, 712, 2, 2), (1, 300, 300, 4, 1), (1, 17, 1041, 8, 2)])
+def test_flash_fwd_prefix(B, Sq, Skv, Hq, Hkv):
+    """A chunk of queries at the end of a longer key / value sequence (chunked prefill over a cached prefix)."""
+    torch.manual_seed(2)
+    D = 128
+    q = torch.randn(B * Sq, Hq, D, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B * Skv, Hkv, D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B * Skv, Hkv, D, device="cuda").to(torch.bfloat16)
+    out = native.flash_fwd_prefix(q, k, v, B, Sq, Skv, causal=True)
+    ref, _ = attention_ref(q.view(B, Sq, Hq, D), k.view(B, Skv, Hkv, D), v.view(B, Skv, Hkv, D), causal=True, start_pos=Skv - Sq)
+    torch.cuda.synchronize()
+    assert _rel(out.view(B, Sq, Hq, D), ref) < 2e-2

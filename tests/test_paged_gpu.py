@@ -113,3 +113,29 @@ def test_batched_prefill_matches_one_by_one():
     same = sum(a == b for x, y in zip(outs[1], outs[8192]) for a, b in zip(x, y))
     total = sum(len(x) for x in outs[1])
     assert all(len(x) == 6 for x in outs[8192]) and same >= 0.9 * total, (same, total)
+
+
+def test_chunked_prefill_matches_single_chunk():
+    """A prompt prefilled in chunks (later chunks attend to the cached prefix through the prefix-attention kernel)
+    generates the tokens of the same prompt prefilled at once."""
+    from ml_framework_b200.modelzoo.zoo import build_model, default_registry
+    from ml_framework_b200.serving.executor import ExecutorConfig, PagedLlamaExecutor
+    from ml_framework_b200.serving.kv_cache import KVCacheBlockManager
+    from ml_framework_b200.serving.scheduler import (BatchConstraints, CompletionConfiguration, ContinuousBatchScheduler, Request,
+                                                     SchedulerConfiguration)
+    torch.manual_seed(0)
+    model = build_model(default_registry().get("llama-tiny"), "cuda", torch.bfloat16).eval()
+    mc = model.cfg
+    prompts = [[(13 * i + 7 * j) % (mc.vocab_size - 1) + 1 for j in range(150 + 31 * i)] for i in range(3)]
+    outs = {}
+    for chunk in (512, 64):
+        kv = KVCacheBlockManager(256, 16, mc.head_dim, mc.n_layers, mc.n_kv_heads, device="cuda", dtype=torch.bfloat16)
+        ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=512, prefill_chunk=chunk, use_cuda_graphs=False))
+        sched = ContinuousBatchScheduler(ex, kv, SchedulerConfiguration(max_batch_size=8, warmup_iterations=0), BatchConstraints(max_batch_size=8),
+                                         completion=CompletionConfiguration(eos_token_id=-1, default_max_tokens=6))
+        futs = [sched.enqueue(Request(list(p), max_tokens=6)) for p in prompts]
+        sched.run_until_idle()
+        outs[chunk] = [f.result(1).tokens for f in futs]
+    same = sum(a == b for x, y in zip(outs[512], outs[64]) for a, b in zip(x, y))
+    total = sum(len(x) for x in outs[512])
+    assert all(len(x) == 6 for x in outs[64]) and same >= 0.9 * total, (same, total)
