@@ -295,6 +295,57 @@ kv_cache_write_kernel(__nv_bfloat16* cache, const __nv_bfloat16* k, const __nv_b
   }
 }
 
+// One pass over packed QKV rows [T, (Hq + 2 Hkv) * 128] (pitch ld): rotary embedding (rotate-half, positions
+// pos[T]) in place on the query and key heads, and the rotated keys plus the values written to their cache
+// slots (slot < 0 skips the write). Replaces two rotary launches and the cache write of a serving step.
+__global__ void __launch_bounds__(256)
+rope_kv_write_kernel(__nv_bfloat16* qkv, long long ld, const long long* pos, const long long* slots, __nv_bfloat16* cache, long long T,
+                     int Hq, int Hkv, int block_size, int num_blocks, float theta, int* err) {
+  const int heads = Hq + 2 * Hkv;
+  const long long total = T * heads * 16;                    // 16 threads per head: 4 + 4 elements each
+  const float log_theta = __logf(theta);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int d = (int)(i & 15) * 4;                         // 0..60: pairs (d, d + 64)
+    const long long th = i >> 4;
+    const int h = (int)(th % heads);
+    const long long t = th / heads;
+    __nv_bfloat16* row = qkv + t * ld + (long long)h * PD;
+    uint2 lo = *reinterpret_cast<const uint2*>(row + d);
+    uint2 hi = *reinterpret_cast<const uint2*>(row + d + 64);
+    const bool is_v = h >= Hq + Hkv;
+    if (!is_v) {
+      const float p = (float)pos[t];
+      const float2 a0 = unpack_bf16x2(lo.x), a1 = unpack_bf16x2(lo.y), b0 = unpack_bf16x2(hi.x), b1 = unpack_bf16x2(hi.y);
+      float a[4] = {a0.x, a0.y, a1.x, a1.y}, b[4] = {b0.x, b0.y, b1.x, b1.y};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float inv_freq = __expf(-log_theta * (2.f * (d + j) / PD));
+        float sn, cs;
+        sincosf(p * inv_freq, &sn, &cs);
+        const float x = a[j], y = b[j];
+        a[j] = x * cs - y * sn;
+        b[j] = y * cs + x * sn;
+      }
+      lo.x = pack_bf16x2(a[0], a[1]); lo.y = pack_bf16x2(a[2], a[3]);
+      hi.x = pack_bf16x2(b[0], b[1]); hi.y = pack_bf16x2(b[2], b[3]);
+      *reinterpret_cast<uint2*>(row + d) = lo;
+      *reinterpret_cast<uint2*>(row + d + 64) = hi;
+    }
+    if (h >= Hq) {
+      const long long slot = slots[t];
+      if (slot < 0) continue;
+      const long long blk = slot / block_size;
+      if (blk >= num_blocks) { atomicCAS(err, 0, ERR_BAD_INDEX); continue; }
+      const int off = (int)(slot % block_size);
+      const int hk = is_v ? h - Hq - Hkv : h - Hq;
+      __nv_bfloat16* dst = cache + blk * 2LL * block_size * Hkv * PD + (is_v ? (long long)block_size * Hkv * PD : 0) +
+                           ((long long)off * Hkv + hk) * PD;
+      *reinterpret_cast<uint2*>(dst + d) = lo;
+      *reinterpret_cast<uint2*>(dst + d + 64) = hi;
+    }
+  }
+}
+
 // out_k / out_v [len, Hkv, 128] <- pages of one sequence.
 __global__ void __launch_bounds__(256)
 kv_gather_kernel(const __nv_bfloat16* cache, const int* block_table, int len, int Hkv, int block_size, int num_blocks,
@@ -405,6 +456,21 @@ MLF_API int mlf_kv_cache_write(void* cache, const void* k, const void* v, const 
   kv_cache_write_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(cache), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), slots, T, Hkv,
       block_size, num_blocks, ldk, ldv, device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+MLF_API int mlf_rope_kv_write(void* qkv, long long ld, const long long* pos, const long long* slots, void* cache, long long T, int Hq,
+                              int Hkv, int block_size, int num_blocks, float theta, uint64_t stream) {
+  if (T <= 0) return 0;
+  MLF_REQUIRE(ld % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 7) == 0, "rope_kv_write: rows must be 8-byte aligned");
+  long long g = (T * (Hq + 2 * Hkv) * 16 + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  rope_kv_write_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), ld, pos, slots, static_cast<__nv_bfloat16*>(cache), T, Hq, Hkv, block_size, num_blocks, theta,
+      device_status_word());
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

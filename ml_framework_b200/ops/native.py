@@ -359,6 +359,18 @@ def kv_cache_write(kv_cache: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slo
     _lib.check(rc, "mlf_kv_cache_write")
 
 
+def rope_kv_write_(qkv: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, kv_cache: torch.Tensor, Hq: int, Hkv: int, theta: float):
+    """In place on packed ``qkv`` [T, (Hq + 2 Hkv) * 128]: rotary embedding of the query and key heads; the rotated
+    keys and the values are also written to their cache slots (one launch)."""
+    nb, _, bs, Hc, D = kv_cache.shape
+    assert D == 128 and Hc == Hkv and qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (Hq + 2 * Hkv) * 128
+    assert qkv.dtype == torch.bfloat16 and pos.dtype == torch.int64 and slots.dtype == torch.int64
+    rc = _L().mlf_rope_kv_write(_p(qkv), C.c_longlong(qkv.stride(0)), _p(pos.contiguous()), _p(slots.contiguous()), _p(kv_cache),
+                                C.c_longlong(qkv.shape[0]), Hq, Hkv, bs, nb, C.c_float(theta), _st())
+    _lib.check(rc, "mlf_rope_kv_write")
+    return qkv
+
+
 def kv_gather(kv_cache: torch.Tensor, block_table_row: torch.Tensor, length: int):
     """Contiguous (k, v) [length, Hkv, 128] of one sequence from its pages."""
     nb, _, bs, Hkv, D = kv_cache.shape

@@ -115,9 +115,7 @@ class PagedLlamaExecutor:
             q = qkv[:, :self.hq * D].view(T, self.hq, D)
             k = qkv[:, self.hq * D:(self.hq + self.hkv) * D].view(T, self.hkv, D)
             v = qkv[:, (self.hq + self.hkv) * D:].view(T, self.hkv, D)
-            native.rope_(q, positions, mc.rope_theta)
-            native.rope_(k, positions, mc.rope_theta)
-            native.kv_cache_write(cache, k, v, slots)
+            native.rope_kv_write_(qkv, positions, slots, cache, self.hq, self.hkv, mc.rope_theta)
             a = attend(li, q, k, v)
             multi = self.tp is not None and self.tp.world > 1
             # A decode step (few rows, whole weights) streams weights: plain products let the GEMM split K over

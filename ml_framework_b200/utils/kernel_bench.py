@@ -242,6 +242,34 @@ def run_paged_small() -> list[dict]:
     return [{"ran": "paged decode B256 ctx1024 x2"}]
 
 
+def run_decode_step_small() -> list[dict]:
+    """Llama-8B layer shapes, 4 layers, 64 sequences with 576 cached tokens: a batched prefill, then three decode steps
+    launched eagerly (no graph replay), so that a launch list shows every kernel of a decode step."""
+    from ..modelzoo.zoo import ModelInfo, build_model, default_registry
+    from ..serving.executor import ExecutorConfig, PagedLlamaExecutor
+    from ..serving.kv_cache import KVCacheBlockManager
+    from ..serving.scheduler import Batch, Request
+    info = default_registry().get("llama-3-8b")
+    cfg = dict(info.config)
+    cfg["n_layers"] = 4
+    model = build_model(ModelInfo("llama-8b-4l", "llama", cfg), "cuda", torch.bfloat16).eval()
+    mc = model.cfg
+    B, ctx = 64, 576
+    kv = KVCacheBlockManager(B * (ctx // 16 + 2), 16, mc.head_dim, mc.n_layers, mc.n_kv_heads, device="cuda", dtype=torch.bfloat16)
+    ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=B, max_seq_len=1024, prefill_chunk=1024, use_cuda_graphs=False,
+                                                      max_prefill_tokens=16384))
+    reqs = [Request([(7 * i + 3 * j) % 1000 + 1 for j in range(ctx)], max_tokens=8) for i in range(B)]
+    out = ex.execute_batch(Batch(requests=reqs, prefill=reqs, decode=[]))
+    for r in reqs:
+        r.generated.append(out.generated_tokens[r.id])
+    for _ in range(3):
+        out = ex.execute_batch(Batch(requests=reqs, prefill=[], decode=reqs))
+        for r in reqs:
+            r.generated.append(out.generated_tokens[r.id])
+    torch.cuda.synchronize()
+    return [{"ran": "llama-8b (4 layers) prefill 64 x 576 + 3 decode steps"}]
+
+
 def run_gemm_small() -> list[dict]:
     """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
     from ..ops.gemm import gemm
@@ -256,7 +284,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -277,6 +305,8 @@ def main():
         rows = bench_paged_decode(args)
     elif args.what == "paged_small":
         rows = run_paged_small()
+    elif args.what == "decode_step_small":
+        rows = run_decode_step_small()
     elif args.what == "attn":
         from .kernel_bench_attn import bench_attn
         rows = bench_attn(args)

@@ -139,3 +139,24 @@ def test_chunked_prefill_matches_single_chunk():
     same = sum(a == b for x, y in zip(outs[512], outs[64]) for a, b in zip(x, y))
     total = sum(len(x) for x in outs[512])
     assert all(len(x) == 6 for x in outs[64]) and same >= 0.9 * total, (same, total)
+
+
+def test_fused_rope_and_cache_write_matches_separate_kernels():
+    torch.manual_seed(3)
+    nb, bs, Hq, Hkv, D, T = 12, 16, 4, 2, 128, 45
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    pos = torch.randint(0, 3000, (T,), device="cuda")
+    slots = torch.randperm(nb * bs, device="cuda")[:T].to(torch.int64)
+    slots[5] = -1
+    ref = qkv.clone()
+    q = ref[:, :Hq * D].view(T, Hq, D)
+    k = ref[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
+    v = ref[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    native.rope_(q, pos, 500000.0)
+    native.rope_(k, pos, 500000.0)
+    cache_ref = torch.zeros(nb, 2, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    native.kv_cache_write(cache_ref, k, v, slots)
+    cache = torch.zeros_like(cache_ref)
+    native.rope_kv_write_(qkv, pos, slots, cache, Hq, Hkv, 500000.0)
+    torch.cuda.synchronize()
+    assert torch.equal(qkv, ref) and torch.equal(cache, cache_ref)
