@@ -35,7 +35,8 @@ constexpr int P_SMEM = 2 * P_STAGES * P_CH_BYTES;       // K ring + V ring
 constexpr int P_MAXG = 8;         // max query heads per kv head
 
 struct PagedDecodeParams {
-  const __nv_bfloat16* q;         // [B, Hq, 128]
+  const __nv_bfloat16* q;         // [B, Hq, 128], row pitch ldq elements
+  long long ldq;
   const __nv_bfloat16* cache;
   const int* block_table;         // [B, max_blocks]
   const int* seq_lens;            // [B]
@@ -147,7 +148,7 @@ paged_decode_kernel(const PagedDecodeParams p) {
   for (int ks = 0; ks < PD / 16; ++ks) {
     qa[ks][0] = qa[ks][1] = 0u;
     if (qrow < G) {
-      const __nv_bfloat16* qp = p.q + ((long long)b * p.Hq + hkv * G + qrow) * PD + ks * 16 + qcol;
+      const __nv_bfloat16* qp = p.q + (long long)b * p.ldq + (long long)(hkv * G + qrow) * PD + ks * 16 + qcol;
       qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
       qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
     }
@@ -363,23 +364,38 @@ kv_gather_kernel(const __nv_bfloat16* cache, const int* block_table, int len, in
   }
 }
 
-// Greedy sampling: argmax over the first `vocab` columns of each row of bf16 logits.
-__global__ void __launch_bounds__(256)
-argmax_rows_kernel(const __nv_bfloat16* logits, long long ld, int vocab, long long* out) {
+// Greedy sampling: argmax over the first `vocab` columns of each row of bf16 logits (lowest index on ties).
+// One CTA of 1024 threads per row; 16-byte loads when the rows are 16-byte aligned (vec != 0).
+constexpr int AM_THREADS = 1024;
+__global__ void __launch_bounds__(AM_THREADS)
+argmax_rows_kernel(const __nv_bfloat16* logits, long long ld, int vocab, long long* out, int vec) {
   const long long r = blockIdx.x;
   const __nv_bfloat16* row = logits + r * ld;
   float best = -INFINITY;
-  int bi = 0;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = __bfloat162float(row[i]);
-    if (v > best) { best = v; bi = i; }
+  int bi = 0x7fffffff;
+  int done = 0;
+  if (vec) {
+    const int nv = vocab / 8;
+    for (int i = threadIdx.x; i < nv; i += AM_THREADS) {
+      const uint4 u = reinterpret_cast<const uint4*>(row)[i];
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      const float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (f[j] > best || (f[j] == best && i * 8 + j < bi)) { best = f[j]; bi = i * 8 + j; }
+    }
+    done = nv * 8;
   }
-  __shared__ float sv[256];
-  __shared__ int si[256];
+  for (int i = done + threadIdx.x; i < vocab; i += AM_THREADS) {
+    const float v = __bfloat162float(row[i]);
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  __shared__ float sv[AM_THREADS];
+  __shared__ int si[AM_THREADS];
   sv[threadIdx.x] = best;
   si[threadIdx.x] = bi;
   __syncthreads();
-  for (int s = 128; s > 0; s >>= 1) {
+  for (int s = AM_THREADS / 2; s > 0; s >>= 1) {
     if (threadIdx.x < s) {
       const float ov = sv[threadIdx.x + s];
       const int oi = si[threadIdx.x + s];
@@ -387,7 +403,7 @@ argmax_rows_kernel(const __nv_bfloat16* logits, long long ld, int vocab, long lo
     }
     __syncthreads();
   }
-  if (threadIdx.x == 0) out[r] = si[0];
+  if (threadIdx.x == 0) out[r] = si[0] == 0x7fffffff ? 0 : si[0];
 }
 
 }  // namespace mlf
@@ -397,9 +413,22 @@ using namespace mlf;
 // Workspace floats needed by mlf_paged_decode for a given split count.
 MLF_API long long mlf_paged_decode_ws_elems(int B, int Hq, int splits) { return (long long)B * Hq * splits * (PD + 2); }
 
+MLF_API int mlf_paged_decode_ld(const void* q, long long ldq, const void* cache, const int* block_table, const int* seq_lens, void* out,
+                                float* ws, int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks, int max_seq_len,
+                                int split_tokens, float scale, uint64_t stream);
+
 MLF_API int mlf_paged_decode(const void* q, const void* cache, const int* block_table, const int* seq_lens, void* out, float* ws,
                              int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks, int max_seq_len,
                              int split_tokens, float scale, uint64_t stream) {
+  return mlf_paged_decode_ld(q, (long long)Hq * PD, cache, block_table, seq_lens, out, ws, B, Hq, Hkv, block_size, max_blocks, num_blocks,
+                             max_seq_len, split_tokens, scale, stream);
+}
+
+// q rows may sit inside a wider packed buffer: ldq = elements between consecutive sequences' query rows.
+MLF_API int mlf_paged_decode_ld(const void* q, long long ldq, const void* cache, const int* block_table, const int* seq_lens, void* out,
+                                float* ws, int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks, int max_seq_len,
+                                int split_tokens, float scale, uint64_t stream) {
+  MLF_REQUIRE(ldq % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0, "paged_decode: query rows must be 4-byte aligned");
   MLF_REQUIRE(B > 0 && Hq % Hkv == 0, "paged_decode: bad head counts");
   const int G = Hq / Hkv;
   MLF_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, "paged_decode: group size %d not supported (1, 2, 4, 8)", G);
@@ -410,6 +439,7 @@ MLF_API int mlf_paged_decode(const void* q, const void* cache, const int* block_
   MLF_REQUIRE(splits == 1 || ws != nullptr, "paged_decode: workspace required for %d splits", splits);
   PagedDecodeParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
+  p.ldq = ldq;
   p.cache = static_cast<const __nv_bfloat16*>(cache);
   p.block_table = block_table; p.seq_lens = seq_lens;
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -492,8 +522,9 @@ MLF_API int mlf_kv_gather(const void* cache, const int* block_table, int len, in
 
 MLF_API int mlf_argmax_rows(const void* logits, long long rows, long long ld, int vocab, long long* out, uint64_t stream) {
   if (rows <= 0) return 0;
-  argmax_rows_kernel<<<(int)rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(logits), ld,
-                                                                                   vocab, out);
+  const int vec = (ld % 8 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) ? 1 : 0;
+  argmax_rows_kernel<<<(int)rows, AM_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(logits), ld,
+                                                                                          vocab, out, vec);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

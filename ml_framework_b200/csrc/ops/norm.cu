@@ -90,6 +90,104 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+// Forward for D = NVT * 2048 with whole-CTA rows: 256 threads own 8 * NVT fixed columns each (gamma / beta in
+// registers), R rows are loaded together, and the row sums meet across the eight warps through shared memory.
+// Few rows (a decode step: 64 x 4096) then still occupy one CTA per row group instead of one warp per row.
+template <int NVT, int R>
+__global__ void __launch_bounds__(256)
+norm_fwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                    const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps, int rms) {
+  constexpr int D = NVT * 2048;
+  __shared__ float red[2][2][8][R];          // [iteration parity][sum | centred squares][warp][row]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float g[NVT][8], bt[NVT][8];
+#pragma unroll
+  for (int v = 0; v < NVT; ++v) {
+    unpack8(reinterpret_cast<const uint4*>(gamma)[v * 256 + tid], g[v]);
+    if (beta) unpack8(reinterpret_cast<const uint4*>(beta)[v * 256 + tid], bt[v]);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bt[v][j] = 0.f;
+    }
+  }
+  const float inv_d = 1.f / D;
+  int par = 0;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R, par ^= 1) {
+    uint4 xv[R][NVT];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const long long base = (long long)(row0 + r < rows ? row0 + r : row0) * (D / 8);
+#pragma unroll
+      for (int v = 0; v < NVT; ++v) xv[r][v] = reinterpret_cast<const uint4*>(x)[base + v * 256 + tid];
+    }
+    float mean[R];
+    if (!rms) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float sm = 0.f;
+#pragma unroll
+        for (int v = 0; v < NVT; ++v) {
+          float f[8];
+          unpack8(xv[r][v], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sm += f[j];
+        }
+        sm = warp_sum(sm);
+        if (lane == 0) red[par][0][warp][r] = sm;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[par][0][w][r];
+        mean[r] = t * inv_d;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r) mean[r] = 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float ss = 0.f;
+#pragma unroll
+      for (int v = 0; v < NVT; ++v) {
+        float f[8];
+        unpack8(xv[r][v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = f[j] - mean[r];
+          ss = fmaf(d, d, ss);
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[par][1][warp][r] = ss;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) break;
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += red[par][1][w][r];
+      const float rstd = rsqrtf(t * inv_d + eps);
+      if (tid == 0) {
+        if (mean_out) mean_out[row0 + r] = mean[r];
+        if (rstd_out) rstd_out[row0 + r] = rstd;
+      }
+#pragma unroll
+      for (int v = 0; v < NVT; ++v) {
+        float f[8];
+        unpack8(xv[r][v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = fmaf((f[j] - mean[r]) * rstd, g[v][j], bt[v][j]);
+        reinterpret_cast<uint4*>(y)[(long long)(row0 + r) * (D / 8) + v * 256 + tid] = pack8(f);
+      }
+    }
+  }
+}
+
 // Backward. Each warp walks rows with a grid stride. Gamma / beta gradient contributions are kept
 // per lane in registers when they fit (MODE 0: D <= 2048, row cached in registers too; MODE 1:
 // RMSNorm up to D = 5120, row re-read from L1/L2 for the second pass) and only folded into a
@@ -397,6 +495,28 @@ MLF_API int mlf_norm_fwd(const void* x, const void* gamma, const void* beta, voi
                          int rows, int D, float eps, int rms, uint64_t stream) {
   MLF_REQUIRE(D % 256 == 0, "norm: D=%d must be a multiple of 256", D);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 2048 || D == 4096) {
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+    const __nv_bfloat16* gp = static_cast<const __nv_bfloat16*>(gamma);
+    const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(beta);
+    __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+    const int cap = 4 * sm_count();
+    if (D == 2048) {
+      const int r = rows >= 4 * cap ? 4 : (rows >= 2 * cap ? 2 : 1);      // few rows: one row per CTA, more CTAs
+      const int grid = min((rows + r - 1) / r, cap);
+      if (r == 4) norm_fwd_cta_kernel<1, 4><<<grid, 256, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, eps, rms);
+      else if (r == 2) norm_fwd_cta_kernel<1, 2><<<grid, 256, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, eps, rms);
+      else norm_fwd_cta_kernel<1, 1><<<grid, 256, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, eps, rms);
+    } else {
+      const int r = rows >= 2 * cap ? 2 : 1;
+      const int grid = min((rows + r - 1) / r, cap);
+      if (r == 2) norm_fwd_cta_kernel<2, 2><<<grid, 256, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, eps, rms);
+      else norm_fwd_cta_kernel<2, 1><<<grid, 256, 0, st>>>(xp, gp, bp, yp, mean, rstd, rows, eps, rms);
+    }
+    count_launch();
+    MLF_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
 #define CALL(NV) launch_fwd<NV>(x, gamma, beta, y, mean, rstd, rows, eps, rms, st)
   MLF_NORM_DISPATCH(D / 256, CALL)
 #undef CALL

@@ -330,8 +330,9 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
     """
     B, Hq, D = q.shape
     nb, two, bs, Hkv, D2 = kv_cache.shape
-    assert D == 128 and D2 == 128 and two == 2 and q.is_contiguous() and kv_cache.is_contiguous()
-    out = torch.empty_like(q)
+    assert D == 128 and D2 == 128 and two == 2 and kv_cache.is_contiguous()
+    assert q.stride(2) == 1 and q.stride(1) == D and q.dtype == torch.bfloat16      # sequence pitch (stride 0) is free
+    out = torch.empty(B, Hq, D, dtype=q.dtype, device=q.device)
     L = _L()
     L.mlf_paged_decode_ws_elems.restype = C.c_longlong
     if split_tokens <= 0:
@@ -343,9 +344,9 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
     splits = max(1, (max_seq_len + st - 1) // st)
     ws = scratch("paged_decode", L.mlf_paged_decode_ws_elems(B, Hq, splits) * 4, q.device) if splits > 1 else None
     scale = scale if scale is not None else D ** -0.5
-    rc = L.mlf_paged_decode(_p(q), _p(kv_cache), _p(block_table), _p(seq_lens), _p(out), _p(ws), B, Hq, Hkv, bs,
-                            block_table.shape[1], nb, int(max_seq_len), st, C.c_float(scale), _st())
-    _lib.check(rc, "mlf_paged_decode")
+    rc = L.mlf_paged_decode_ld(_p(q), C.c_longlong(q.stride(0)), _p(kv_cache), _p(block_table), _p(seq_lens), _p(out), _p(ws), B, Hq, Hkv,
+                               bs, block_table.shape[1], nb, int(max_seq_len), st, C.c_float(scale), _st())
+    _lib.check(rc, "mlf_paged_decode_ld")
     return out
 
 

@@ -274,7 +274,7 @@ class PagedLlamaExecutor:
         """Device-only part of a decode step (no host reads): embed, all blocks, head, arg-max."""
         def attend(li, q, k, v):
             if self.native:
-                return native.paged_decode(q.contiguous(), self.kv.caches[li], table, lens, max_len,
+                return native.paged_decode(q, self.kv.caches[li], table, lens, max_len,
                                            split_tokens=self.cfg.decode_split_tokens)
             return reference.paged_attention_ref(q, self.kv.caches[li], table.cpu(), lens.cpu().tolist()).to(q.dtype)
         x = self._embed(last[None])[0]

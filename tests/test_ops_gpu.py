@@ -163,3 +163,20 @@ def test_embedding_and_rope():
     _close(got, want)
     back = native.rope_(got.clone(), pos, 500000.0, inverse=True)
     _close(back, x, 3e-2)
+
+
+@pytest.mark.parametrize("rows,D", [(5001, 2048), (1501, 2048), (64, 4096), (3001, 4096)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_whole_cta_rows(rows, D, rms):
+    """Row counts that select each rows-per-CTA variant of the wide forward kernel."""
+    torch.manual_seed(4)
+    x = (torch.randn(rows, D, device="cuda") * 1.5 + 0.3).to(torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+    b = None if rms else (0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+    y, mean, rstd = native.norm_fwd(x, g, b, 1e-5, rms)
+    if rms:
+        yr, _ = ref.rms_norm_ref(x.float(), g.float(), 1e-5)
+    else:
+        yr, mr, rr = ref.layer_norm_ref(x.float(), g.float(), b.float(), 1e-5)
+        assert (mean - mr.reshape(-1)).abs().max().item() < 1e-3
+    _close(y, yr)
