@@ -250,11 +250,16 @@ __global__ void __launch_bounds__(256) colsum_kernel(__nv_bfloat16* __restrict__
   const int rl = threadIdx.x >> 3;        // 32 row lanes
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col0 + cl + 8 <= N) {
-    for (int r = r0 + rl; r < r1; r += 32) {
-      float f[8];
-      Vec<__nv_bfloat16>::load(dy + (long long)r * ld + col0 + cl, f);
+    for (int r = r0 + rl; r < r1; r += 128) {          // four 16-byte loads per thread in flight
+      uint4 u[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) s[j] += f[j];
+      for (int k = 0; k < 4; ++k)
+        u[k] = r + 32 * k < r1 ? *reinterpret_cast<const uint4*>(dy + (long long)(r + 32 * k) * ld + col0 + cl) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack_bf16x2(u[k].x), b = unpack_bf16x2(u[k].y), c = unpack_bf16x2(u[k].z), d = unpack_bf16x2(u[k].w);
+        s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
+      }
     }
   } else {
     for (int r = r0 + rl; r < r1; r += 32)

@@ -131,6 +131,47 @@ amp_unscale_check_kernel(G* grad, long long n, const float* inv_scale_ptr, float
   if (sumsq && (threadIdx.x & 31) == 0 && isfinite(acc)) atomicAdd(sumsq, acc);
 }
 
+// Read-only check of bf16 gradients (no write-back): 16-byte loads, four per thread in flight.
+__global__ void __launch_bounds__(256)
+amp_check_bf16_vec_kernel(const __nv_bfloat16* grad, long long n, const float* inv_scale_ptr, float inv_scale, int* found_inf,
+                          float* sumsq) {
+  const float s = inv_scale * (inv_scale_ptr ? *inv_scale_ptr : 1.f);
+  const long long nvec = n / 8;
+  const uint4* gv = reinterpret_cast<const uint4*>(grad);
+  float acc = 0.f;
+  bool bad = false;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += 4 * stride) {
+    uint4 u[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) u[k] = i + k * stride < nvec ? gv[i + k * stride] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t w[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // a bf16 is non-finite when its exponent bits are all ones
+        bad |= ((w[j] & 0x7f800000u) == 0x7f800000u) | ((w[j] & 0x00007f80u) == 0x00007f80u);
+        if (sumsq) {
+          const float2 f = unpack_bf16x2(w[j]);
+          acc = fmaf(f.x * s, f.x * s, acc);
+          acc = fmaf(f.y * s, f.y * s, acc);
+        }
+      }
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nvec * 8)) {
+    const float g = __bfloat162float(grad[nvec * 8 + threadIdx.x]) * s;
+    if (!isfinite(g)) bad = true;
+    acc += g * g;
+  }
+  if (!isfinite(s)) bad = true;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(found_inf, 1);
+  if (sumsq && (threadIdx.x & 31) == 0 && isfinite(acc)) atomicAdd(sumsq, acc);
+}
+
 // state: scale[0], growth_tracker (int) ; found_inf is reset to 0 afterwards.
 __global__ void scaler_update_kernel(float* scale, int* tracker, int* found_inf, float growth, float backoff,
                                      int interval, float min_scale, float max_scale, int* skipped_steps) {
@@ -297,7 +338,9 @@ MLF_API int mlf_amp_unscale_check(void* grad, int grad_dtype, long long n, const
                                   int* found_inf, float* sumsq, int write_back, uint64_t stream) {
   if (n <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (grad_dtype == 1)
+  if (grad_dtype == 1 && !write_back && (reinterpret_cast<uintptr_t>(grad) & 15) == 0)
+    amp_check_bf16_vec_kernel<<<ew_grid2(n / 32 + 1), 256, 0, st>>>((const __nv_bfloat16*)grad, n, inv_scale_ptr, inv_scale, found_inf, sumsq);
+  else if (grad_dtype == 1)
     amp_unscale_check_kernel<__nv_bfloat16><<<ew_grid2(n), 256, 0, st>>>((__nv_bfloat16*)grad, n, inv_scale_ptr, inv_scale, found_inf, sumsq, write_back);
   else
     amp_unscale_check_kernel<float><<<ew_grid2(n), 256, 0, st>>>((float*)grad, n, inv_scale_ptr, inv_scale, found_inf, sumsq, write_back);

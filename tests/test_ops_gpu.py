@@ -118,6 +118,19 @@ def test_adamw_and_scaler():
     g2[17] = float("inf")
     native.amp_unscale_check_(g2, found, inv_scale=inv)
     assert found.item() == 1
+    # read-only check of bf16 gradients (vector loads): clean, then one inf, then one nan in the unaligned tail
+    found.zero_()
+    gb = torch.randn(100003, device="cuda").to(torch.bfloat16)
+    ss2 = torch.zeros(1, device="cuda")
+    native.amp_unscale_check_(gb, found, inv_scale=inv, sumsq=ss2, write_back=False)
+    assert found.item() == 0
+    _close(ss2, (gb.float() * 0.5).pow(2).sum(), 1e-3)
+    for bad_at, val in ((4321, float("inf")), (100001, float("nan"))):
+        gbad = gb.clone()
+        gbad[bad_at] = val
+        found.zero_()
+        native.amp_unscale_check_(gbad, found, inv_scale=inv, write_back=False)
+        assert found.item() == 1
     # dynamic loss-scale state machine: back off on overflow, grow after `interval` clean steps
     scale = torch.tensor(1024.0, device="cuda")
     tracker = torch.zeros(1, device="cuda", dtype=torch.int32)
