@@ -235,26 +235,27 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(__nv_bfloat16* dgu, con
 
 // ------------------------------------------------------------------------------------------
 // column sum (bias gradient): db[n] = sum_m dy[m, n]; dy bf16 [M, N] with pitch ld.
-// One launch, no atomics on the data: each CTA owns 64 columns x a slab of rows and writes its fp32
+// One launch, no atomics on the data: each CTA owns 256 columns x a slab of rows and writes its fp32
 // partial sums to part[slab][N]; the CTA that finishes last for a column block (a counter per block,
 // reset by that CTA) adds the slabs in slab order and writes bf16. The order of the additions is
 // fixed, so the result is the same from run to run.
 // ------------------------------------------------------------------------------------------
+constexpr int CS_COLS = 256;     // columns per CTA: a warp reads 512 contiguous bytes of a row
 __global__ void __launch_bounds__(256) colsum_kernel(__nv_bfloat16* __restrict__ db, const __nv_bfloat16* __restrict__ dy,
                                                      float* __restrict__ part, unsigned int* __restrict__ counters, int M, int N,
                                                      long long ld, int rows_per_cta, int accumulate) {
-  const int col0 = blockIdx.x * 64;
+  const int col0 = blockIdx.x * CS_COLS;
   const int r0 = blockIdx.y * rows_per_cta;
   const int r1 = min(M, r0 + rows_per_cta);
-  const int cl = (threadIdx.x & 7) * 8;   // 8 threads x 8 columns = 64 columns
-  const int rl = threadIdx.x >> 3;        // 32 row lanes
+  const int cl = (threadIdx.x & 31) * 8;  // 32 threads x 8 columns = 256 columns
+  const int rl = threadIdx.x >> 5;        // 8 row lanes
   float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col0 + cl + 8 <= N) {
-    for (int r = r0 + rl; r < r1; r += 128) {          // four 16-byte loads per thread in flight
+    for (int r = r0 + rl; r < r1; r += 32) {           // four 16-byte loads per thread in flight
       uint4 u[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        u[k] = r + 32 * k < r1 ? *reinterpret_cast<const uint4*>(dy + (long long)(r + 32 * k) * ld + col0 + cl) : make_uint4(0, 0, 0, 0);
+        u[k] = r + 8 * k < r1 ? *reinterpret_cast<const uint4*>(dy + (long long)(r + 8 * k) * ld + col0 + cl) : make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float2 a = unpack_bf16x2(u[k].x), b = unpack_bf16x2(u[k].y), c = unpack_bf16x2(u[k].z), d = unpack_bf16x2(u[k].w);
@@ -262,19 +263,19 @@ __global__ void __launch_bounds__(256) colsum_kernel(__nv_bfloat16* __restrict__
       }
     }
   } else {
-    for (int r = r0 + rl; r < r1; r += 32)
+    for (int r = r0 + rl; r < r1; r += 8)
       for (int j = 0; j < 8; ++j)
         if (col0 + cl + j < N) s[j] += __bfloat162float(dy[(long long)r * ld + col0 + cl + j]);
   }
-  __shared__ float sm[32][65];
+  __shared__ float sm[8][CS_COLS + 1];
   __shared__ int s_last;
 #pragma unroll
   for (int j = 0; j < 8; ++j) sm[rl][cl + j] = s[j];
   __syncthreads();
-  if (threadIdx.x < 64) {
+  {
     float t = 0.f;
-#pragma unroll 8
-    for (int r = 0; r < 32; ++r) t += sm[r][threadIdx.x];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += sm[r][threadIdx.x];
     if (col0 + threadIdx.x < N) part[(long long)blockIdx.y * N + col0 + threadIdx.x] = t;
   }
   __threadfence();
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(256) colsum_kernel(__nv_bfloat16* __restrict__
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  if (threadIdx.x < 64 && col0 + threadIdx.x < N) {
+  if (col0 + threadIdx.x < N) {
     float t = 0.f;
     for (int y = 0; y < (int)gridDim.y; ++y) t += __ldcg(part + (long long)y * N + col0 + threadIdx.x);
     __nv_bfloat16* o = db + col0 + threadIdx.x;
@@ -439,14 +440,14 @@ MLF_API int mlf_swiglu_bwd(void* dgu, const void* dout, const void* gu, long lon
   return 0;
 }
 static void colsum_shape(int M, int N, int& col_ctas, int& row_ctas, int& rows_per_cta) {
-  col_ctas = (N + 63) / 64;
+  col_ctas = (N + CS_COLS - 1) / CS_COLS;
   row_ctas = (sm_count() * 4 + col_ctas - 1) / col_ctas;
   if (row_ctas > (M + 31) / 32) row_ctas = (M + 31) / 32;
   if (row_ctas < 1) row_ctas = 1;
   rows_per_cta = ((M + row_ctas - 1) / row_ctas + 31) / 32 * 32;
   row_ctas = (M + rows_per_cta - 1) / rows_per_cta;
 }
-// Scratch layout of mlf_colsum: ceil(N / 64) counters (uint32, zero before the first use; the kernel
+// Scratch layout of mlf_colsum: ceil(N / 256) counters (uint32, zero before the first use; the kernel
 // leaves them zero), padded to 256 bytes, then row_ctas x N floats of partial sums.
 MLF_API long long mlf_colsum_scratch_bytes(int M, int N) {
   int c, r, rp;
