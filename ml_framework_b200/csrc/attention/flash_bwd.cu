@@ -52,43 +52,26 @@ struct FlashBwdParams {
   int* err;
 };
 
-// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; sixteen lanes (16 bytes each) per (token, head), four
-// items per half-warp in flight (the kernel is bound by bytes in flight, 64 MB in and 1 MB out).
+// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delta, const float* lse, float* lse2, int B, int S,
                   int H, long long ldo, long long lddo) {
-  constexpr int U = 4;
   const long long total = (long long)B * S * H;
-  const int l16 = threadIdx.x & 15;
-  const long long halves = (long long)gridDim.x * (blockDim.x >> 4);
-  for (long long w0 = (long long)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); w0 < total; w0 += halves * U) {
-    uint4 a[U], g[U];
+  const int lane = threadIdx.x & 31;
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
+       w += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const long long t = w / H;
+    const int h = (int)(w % H);
+    const uint2 a = *reinterpret_cast<const uint2*>(o + t * ldo + h * FB_D + lane * 4);
+    const uint2 g = *reinterpret_cast<const uint2*>(dout + t * lddo + h * FB_D + lane * 4);
+    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
+    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long w = w0 + u * halves;
-      a[u] = g[u] = make_uint4(0, 0, 0, 0);
-      if (w < total) {
-        const long long t = w / H;
-        const int h = (int)(w % H);
-        a[u] = *reinterpret_cast<const uint4*>(o + t * ldo + h * FB_D + l16 * 8);
-        g[u] = *reinterpret_cast<const uint4*>(dout + t * lddo + h * FB_D + l16 * 8);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long w = w0 + u * halves;
-      const float2 a0 = unpack_bf16x2(a[u].x), a1 = unpack_bf16x2(a[u].y), a2 = unpack_bf16x2(a[u].z), a3 = unpack_bf16x2(a[u].w);
-      const float2 g0 = unpack_bf16x2(g[u].x), g1 = unpack_bf16x2(g[u].y), g2 = unpack_bf16x2(g[u].z), g3 = unpack_bf16x2(g[u].w);
-      float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y + a3.x * g3.x + a3.y * g3.y;
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-      if (l16 == 0 && w < total) {
-        const long long t = w / H;
-        const int h = (int)(w % H);
-        const long long b = t / S, sidx = t % S;
-        delta[(b * H + h) * S + sidx] = s;
-        if (lse2) lse2[(b * H + h) * S + sidx] = lse[(b * H + h) * S + sidx] * 1.4426950408889634f;
-      }
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) {
+      const long long b = t / S, sidx = t % S;
+      delta[(b * H + h) * S + sidx] = s;
+      if (lse2) lse2[(b * H + h) * S + sidx] = lse[(b * H + h) * S + sidx] * 1.4426950408889634f;
     }
   }
 }
@@ -417,7 +400,7 @@ MLF_API int mlf_flash_bwd(const void* q, const void* k, const void* v, const voi
     MLF_REQUIRE(((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dout)) & 15) == 0 && ldo % 8 == 0 && lddo % 8 == 0,
                 "flash_bwd: O and dO must be 16-byte aligned with pitches that are multiples of 8");
     const long long warps = rows * Hq;
-    long long grid = (warps + 63) / 64;              // 16 half-warps per CTA, four items each
+    long long grid = (warps + 7) / 8;
     const long long cap = (long long)sm_count() * 8;
     if (grid > cap) grid = cap;
     attn_delta_kernel<<<(int)grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout),
