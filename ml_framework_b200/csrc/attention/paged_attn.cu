@@ -42,6 +42,7 @@ struct PagedDecodeParams {
   const int* seq_lens;            // [B]
   __nv_bfloat16* out;             // [B, Hq, 128]
   float* ws;                      // [B, Hkv, splits, G, 130] (m, l, o[128]) when splits > 1
+  unsigned int* counters;         // [B, Hkv] finished splits (zero between launches); null: a separate merge launch
   int B, Hq, Hkv, G, block_size, bs_shift, max_blocks, num_blocks, split_tokens, splits;   // bs_shift: log2(block_size) or -1
   float scale_log2;
   int* err;
@@ -73,6 +74,37 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 // (same column, consecutive rows) fall into eight different bank groups.
 __device__ __forceinline__ uint32_t chunk_off(int row, int c16) { return (uint32_t)(row * 256 + ((c16 ^ (row & 7)) << 4)); }
 
+// The split that finishes last for a (sequence, kv head) merges all splits' partial results:
+// out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s, and leaves the counter at zero for the next launch.
+template <int G>
+__device__ __forceinline__ void finish_split(const PagedDecodeParams& p, int b, int hkv) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[b * p.Hkv + hkv], 1u) == (unsigned)p.splits - 1u ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int d = threadIdx.x;               // P_THREADS == PD
+  const long long sstride = (long long)G * (PD + 2);
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float* base = p.ws + ((((long long)b * p.Hkv + hkv) * p.splits) * G + g) * (PD + 2);
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, __ldcg(base + sp * sstride));
+    float L = 0.f, o = 0.f;
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float m = __ldcg(base + sp * sstride);
+      if (m == -INFINITY) continue;
+      const float w = exp2f(m - M);
+      L += w * __ldcg(base + sp * sstride + 1);
+      o += w * __ldcg(base + sp * sstride + 2 + d);
+    }
+    p.out[((long long)b * p.Hq + hkv * G + g) * PD + d] = __float2bfloat16(L > 0.f ? o / L : 0.f);
+  }
+  if (threadIdx.x == 0) p.counters[b * p.Hkv + hkv] = 0u;
+}
+
 // The kernel is bound by bytes in flight, not by arithmetic: K and V rows are staged through shared
 // memory with asynchronous 16-byte copies (two chunks of 64 tokens of K and of V, up to 64 KB per
 // CTA, in flight while the previous chunk is multiplied), so the amount outstanding does not depend
@@ -99,6 +131,7 @@ paged_decode_kernel(const PagedDecodeParams p) {
   if (t_lo >= t_hi) {
     if (ws) {
       for (int i = tid; i < G * (PD + 2); i += P_THREADS) ws[i] = (i % (PD + 2)) == 0 ? -INFINITY : 0.f;
+      if (p.counters) finish_split<G>(p, b, hkv);
     } else if (sp == 0) {
       for (int i = tid; i < G * PD; i += P_THREADS)
         p.out[((long long)b * p.Hq + hkv * G) * PD + i] = __float2bfloat16(0.f);
@@ -251,6 +284,7 @@ paged_decode_kernel(const PagedDecodeParams p) {
       p.out[((long long)b * p.Hq + hkv * G + g) * PD + d] = __float2bfloat16(l > 0.f ? acc / l : 0.f);
     }
   }
+  if (ws && p.counters) finish_split<G>(p, b, hkv);
 }
 
 // Merge the per-split partial results: out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s.
@@ -414,20 +448,22 @@ using namespace mlf;
 MLF_API long long mlf_paged_decode_ws_elems(int B, int Hq, int splits) { return (long long)B * Hq * splits * (PD + 2); }
 
 MLF_API int mlf_paged_decode_ld(const void* q, long long ldq, const void* cache, const int* block_table, const int* seq_lens, void* out,
-                                float* ws, int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks, int max_seq_len,
-                                int split_tokens, float scale, uint64_t stream);
+                                float* ws, void* counters, int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks,
+                                int max_seq_len, int split_tokens, float scale, uint64_t stream);
 
 MLF_API int mlf_paged_decode(const void* q, const void* cache, const int* block_table, const int* seq_lens, void* out, float* ws,
                              int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks, int max_seq_len,
                              int split_tokens, float scale, uint64_t stream) {
-  return mlf_paged_decode_ld(q, (long long)Hq * PD, cache, block_table, seq_lens, out, ws, B, Hq, Hkv, block_size, max_blocks, num_blocks,
-                             max_seq_len, split_tokens, scale, stream);
+  return mlf_paged_decode_ld(q, (long long)Hq * PD, cache, block_table, seq_lens, out, ws, nullptr, B, Hq, Hkv, block_size, max_blocks,
+                             num_blocks, max_seq_len, split_tokens, scale, stream);
 }
 
 // q rows may sit inside a wider packed buffer: ldq = elements between consecutive sequences' query rows.
+// counters (optional, B * Hkv zeroed uint32 that the kernel leaves zero): the last split of each (sequence, kv head)
+// merges the splits inside the same launch; without it a second small kernel does.
 MLF_API int mlf_paged_decode_ld(const void* q, long long ldq, const void* cache, const int* block_table, const int* seq_lens, void* out,
-                                float* ws, int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks, int max_seq_len,
-                                int split_tokens, float scale, uint64_t stream) {
+                                float* ws, void* counters, int B, int Hq, int Hkv, int block_size, int max_blocks, int num_blocks,
+                                int max_seq_len, int split_tokens, float scale, uint64_t stream) {
   MLF_REQUIRE(ldq % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0, "paged_decode: query rows must be 4-byte aligned");
   MLF_REQUIRE(B > 0 && Hq % Hkv == 0, "paged_decode: bad head counts");
   const int G = Hq / Hkv;
@@ -444,6 +480,7 @@ MLF_API int mlf_paged_decode_ld(const void* q, long long ldq, const void* cache,
   p.block_table = block_table; p.seq_lens = seq_lens;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ws = splits > 1 ? ws : nullptr;
+  p.counters = splits > 1 ? static_cast<unsigned int*>(counters) : nullptr;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.block_size = block_size; p.max_blocks = max_blocks; p.num_blocks = num_blocks;
   p.split_tokens = split_tokens; p.splits = splits;
   p.bs_shift = -1;
@@ -469,7 +506,7 @@ MLF_API int mlf_paged_decode_ld(const void* q, long long ldq, const void* cache,
     default: paged_decode_kernel<8><<<grid, P_THREADS, P_SMEM, st>>>(p); break;
   }
   count_launch();
-  if (splits > 1) {
+  if (splits > 1 && p.counters == nullptr) {
     paged_decode_merge_kernel<<<B * Hq, 128, 0, st>>>(ws, p.out, B, Hq, Hkv, G, splits);
     count_launch();
   }

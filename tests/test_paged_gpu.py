@@ -39,6 +39,10 @@ def test_paged_decode_matches_contiguous(B, Hq, Hkv, lens):
     # split count chosen from the batch size
     out3 = native.paged_decode(q, cache, table, sl, max_len, split_tokens=0)
     assert (out3.float() - ref).abs().max().item() < 2e-2 * (ref.abs().max().item() + 1e-3)
+    # splits merged by the last split inside the same launch (twice: the counters must come back to zero)
+    for _ in range(2):
+        out4 = native.paged_decode(q, cache, table, sl, max_len, split_tokens=128, fused_merge=True)
+        assert (out4.float() - ref).abs().max().item() < 2e-2 * (ref.abs().max().item() + 1e-3)
 
 
 def test_kv_cache_write_gather_and_argmax():
