@@ -441,7 +441,7 @@ MLF_API int mlf_swiglu_bwd(void* dgu, const void* dout, const void* gu, long lon
 }
 static void colsum_shape(int M, int N, int& col_ctas, int& row_ctas, int& rows_per_cta) {
   col_ctas = (N + CS_COLS - 1) / CS_COLS;
-  row_ctas = (sm_count() * 4 + col_ctas - 1) / col_ctas;
+  row_ctas = (sm_count() * 6 + col_ctas - 1) / col_ctas;      // six CTAs fit per SM (40 registers): one full wave
   if (row_ctas > (M + 31) / 32) row_ctas = (M + 31) / 32;
   if (row_ctas < 1) row_ctas = 1;
   rows_per_cta = ((M + row_ctas - 1) / row_ctas + 31) / 32 * 32;

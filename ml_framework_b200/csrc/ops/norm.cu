@@ -94,7 +94,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 // registers), R rows are loaded together, and the row sums meet across the eight warps through shared memory.
 // Few rows (a decode step: 64 x 4096) then still occupy one CTA per row group instead of one warp per row.
 template <int NVT, int R>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 norm_fwd_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                     const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps, int rms) {

@@ -270,6 +270,24 @@ def run_decode_step_small() -> list[dict]:
     return [{"ran": "llama-8b (4 layers) prefill 64 x 576 + 3 decode steps"}]
 
 
+def run_elementwise_small() -> list[dict]:
+    """LayerNorm forward / backward on 8192 x 2048 and the bias-gradient column sum on 8192 x 8192, two launches each
+    (a few hundred MB on the device): the case profiled with ncu."""
+    from ..ops import native
+    R, D = 8192, 2048
+    x = torch.randn(R, D, device="cuda").to(torch.bfloat16)
+    g = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(D, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(R, D, device="cuda").to(torch.bfloat16)
+    dyb = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        y, mean, rstd = native.norm_fwd(x, g, b, 1e-5, False)
+        native.norm_bwd(x, dy, g, mean, rstd, False, dx_add=dy)
+        native.colsum(dyb)
+    torch.cuda.synchronize()
+    return [{"ran": "layernorm fwd/bwd 8192x2048 + colsum 8192x8192, x2"}]
+
+
 def run_gemm_small() -> list[dict]:
     """Two launches of one 8192 x 8192 x 2048 GEMM (operands 160 MB > L2): the case profiled with ncu."""
     from ..ops.gemm import gemm
@@ -284,7 +302,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small", "elementwise_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -307,6 +325,8 @@ def main():
         rows = run_paged_small()
     elif args.what == "decode_step_small":
         rows = run_decode_step_small()
+    elif args.what == "elementwise_small":
+        rows = run_elementwise_small()
     elif args.what == "attn":
         from .kernel_bench_attn import bench_attn
         rows = bench_attn(args)
