@@ -75,7 +75,7 @@ def main(argv=None):
     s = sub.add_parser("serve"); s.add_argument("--model", default="llama-tiny"); s.add_argument("--requests", type=int, default=16)
     s.add_argument("--rate", type=float, default=0.0); s.add_argument("--prompt-len", type=int, default=32); s.add_argument("--max-tokens", type=int, default=8)
     s.add_argument("--max-batch", type=int, default=16); s.add_argument("--device", default="cpu"); s.set_defaults(fn=_serve)
-    b = sub.add_parser("bench"); b.add_argument("what", choices=["gemm", "attn", "elementwise"]); b.add_argument("--json", default=None); b.set_defaults(fn=_bench)
+    b = sub.add_parser("bench"); b.add_argument("what", choices=["gemm", "gemm_epi", "gemm_decode", "attn", "paged", "elementwise"]); b.add_argument("--json", default=None); b.set_defaults(fn=_bench)
     l = sub.add_parser("launch"); l.add_argument("--nproc", type=int, required=True); l.add_argument("--port", type=int, default=29500)
     l.add_argument("script"); l.add_argument("script_args", nargs=argparse.REMAINDER); l.set_defaults(fn=_launch)
     c = sub.add_parser("convert"); c.add_argument("-i", "--input", required=True); c.add_argument("-o", "--output", required=True)
