@@ -52,25 +52,36 @@ struct FlashBwdParams {
   int* err;
 };
 
-// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head).
+// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head), two such rows per warp in flight.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delta, const float* lse, float* lse2, int B, int S,
                   int H, long long ldo, long long lddo) {
   const long long total = (long long)B * S * H;
   const int lane = threadIdx.x & 31;
-  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
-       w += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const long long t = w / H;
-    const int h = (int)(w % H);
-    const uint2 a = *reinterpret_cast<const uint2*>(o + t * ldo + h * FB_D + lane * 4);
-    const uint2 g = *reinterpret_cast<const uint2*>(dout + t * lddo + h * FB_D + lane * 4);
-    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
-    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w0 < total; w0 += 2 * nwarps) {
+    const long long w1 = w0 + nwarps;
+    const bool two = w1 < total;
+    const long long t0 = w0 / H, t1 = two ? w1 / H : t0;
+    const int h0 = (int)(w0 % H), h1 = two ? (int)(w1 % H) : h0;
+    const uint2 a0v = *reinterpret_cast<const uint2*>(o + t0 * ldo + h0 * FB_D + lane * 4);
+    const uint2 g0v = *reinterpret_cast<const uint2*>(dout + t0 * lddo + h0 * FB_D + lane * 4);
+    const uint2 a1v = *reinterpret_cast<const uint2*>(o + t1 * ldo + h1 * FB_D + lane * 4);
+    const uint2 g1v = *reinterpret_cast<const uint2*>(dout + t1 * lddo + h1 * FB_D + lane * 4);
+    float2 p0 = unpack_bf16x2(a0v.x), p1 = unpack_bf16x2(a0v.y), q0 = unpack_bf16x2(g0v.x), q1 = unpack_bf16x2(g0v.y);
+    float s0 = p0.x * q0.x + p0.y * q0.y + p1.x * q1.x + p1.y * q1.y;
+    p0 = unpack_bf16x2(a1v.x); p1 = unpack_bf16x2(a1v.y); q0 = unpack_bf16x2(g1v.x); q1 = unpack_bf16x2(g1v.y);
+    float s1 = p0.x * q0.x + p0.y * q0.y + p1.x * q1.x + p1.y * q1.y;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) {
+    for (int off = 16; off > 0; off >>= 1) {
+      s0 += __shfl_xor_sync(0xffffffffu, s0, off);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, off);
+    }
+    if (lane < 2 && (lane == 0 || two)) {
+      const long long t = lane ? t1 : t0;
+      const int h = lane ? h1 : h0;
       const long long b = t / S, sidx = t % S;
-      delta[(b * H + h) * S + sidx] = s;
+      delta[(b * H + h) * S + sidx] = lane ? s1 : s0;
       if (lse2) lse2[(b * H + h) * S + sidx] = lse[(b * H + h) * S + sidx] * 1.4426950408889634f;
     }
   }
