@@ -1,6 +1,6 @@
 """Plain PyTorch baseline of the GPT 1.3 B FSDP configuration: torch.nn modules, cuBLAS matmuls,
 SDPA (flash) attention, torch.distributed FSDP (NCCL) full-shard bf16, torch AdamW (fused) and
-torch's GradScaler. None of this repository's kernels or engine are on this path; it is the
+torch's dynamic GradScaler (``ShardedGradScaler`` under FSDP). None of this repository's kernels or engine are on this path; it is the
 "torch.distributed NCCL + cuBLAS implementation of the identical config" the numbers are
 compared with.
 """
@@ -61,16 +61,17 @@ def build(cfg, dev, world, mb, S):
                      device_id=dev, use_orig_params=True,
                      mixed_precision=MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16))
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
-    scale = torch.tensor(65536.0, device=dev)
+    if world > 1:
+        from torch.distributed.fsdp.sharded_grad_scaler import ShardedGradScaler
+        scaler = ShardedGradScaler(init_scale=65536.0)
+    else:
+        scaler = torch.amp.GradScaler("cuda", init_scale=65536.0)
 
     def step(ids, tgt):
         opt.zero_grad(set_to_none=True)
         loss = model(ids, tgt)
-        (loss * scale).backward()
-        inv = 1.0 / scale
-        for p in model.parameters():
-            if p.grad is not None:
-                p.grad.mul_(inv)
-        opt.step()
+        scaler.scale(loss).backward()
+        scaler.step(opt)          # unscale + overflow check + skip-or-apply
+        scaler.update()
         return loss.detach()
     return step, n_params

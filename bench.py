@@ -12,7 +12,9 @@ around K steps, max over ranks); ``e2e`` repeats the measurement through the pub
 ``TrainEngine.step`` API with a pinned-host -> device copy of the step's tokens and a
 device -> host read of the loss inside every timed step. ``--impl torch`` runs the plain
 torch.distributed + cuBLAS implementation of the same configuration (``baseline/gpt_fsdp.py``);
-``--impl reference`` reports why the C# reference cannot run here.
+``--impl reference`` reports why the C# reference cannot run here. After its own arm, ``--impl ours``
+times that torch arm in the same process on the same GPUs (unless ``--no-baseline``) and reports
+``vs_baseline`` = ours / torch together with a ``baseline`` record.
 """
 from __future__ import annotations
 
@@ -25,7 +27,6 @@ import sys
 import threading
 import time
 
-PUBLISHED_BASELINE = None  # the reference publishes no training throughput
 
 
 def _clock_sampler(stop: threading.Event, out: list, gpu_index: int):
@@ -70,6 +71,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the same-box torch comparison arm")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_unavailable()
@@ -101,25 +103,7 @@ def main():
     cfg = GPTConfig.gpt_1_3b() if args.model == "gpt-1.3b" else GPTConfig.tiny()
     S = args.seq or cfg.max_seq
     mb = args.micro_batch
-    torch.manual_seed(1234)
-
-    if args.impl == "torch":
-        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
-        import gpt_fsdp as base
-        step_fn, n_params = base.build(cfg, dev, world, mb, S)
-        launches_fn = lambda: 0  # noqa: E731
-    else:
-        from ml_framework_b200 import _lib
-        from ml_framework_b200.engine import EngineConfig, TrainEngine
-        model = GPT(cfg, dtype=torch.bfloat16, device=dev)
-        n_params = sum(p.numel() for p in model.parameters())
-        eng = TrainEngine(model, EngineConfig(strategy=args.strategy if world > 1 else "none", lr=3e-4,
-                                              fused_comm=not args.no_fused_comm), pg)
-        step_fn = eng.step
-        lib = _lib.get()
-        import ctypes
-        lib.mlf_launch_count.restype = ctypes.c_longlong
-        launches_fn = lambda: int(lib.mlf_launch_count())  # noqa: E731
+    tokens = world * mb * S
 
     g = torch.Generator(device="cpu")
     g.manual_seed(1000 + rank)
@@ -134,76 +118,121 @@ def main():
             torch.distributed.barrier(device_ids=[local])
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        loss = step_fn(dev_ids[i % n_batches], dev_tgt[i % n_batches])
-    barrier()
+    def run_arm(step_fn, launches_fn):
+        """Warm-up, the device-timed region, then the end-to-end region; returns per-step times (max over ranks)."""
+        for i in range(args.warmup):
+            loss = step_fn(dev_ids[i % n_batches], dev_tgt[i % n_batches])
+        barrier()
+        # ---- device-timed region (inputs resident; 2.6 GB of weights + 30 GB of activations per step
+        # stream through a 126 MB L2, so every step starts cold)
+        stop, samples = threading.Event(), []
+        th = None
+        if rank == 0:
+            th = threading.Thread(target=_clock_sampler, args=(stop, samples, local), daemon=True)
+            th.start()
+        l0 = launches_fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            loss = step_fn(dev_ids[i % n_batches], dev_tgt[i % n_batches])
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / args.steps
+        launches = launches_fn() - l0
+        # ---- end-to-end region: H2D of the step's tokens from pinned memory + D2H of the loss, every step
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        losses = []
+        f0.record()
+        for i in range(args.steps):
+            ids = host_ids[i % n_batches].to(dev, non_blocking=True)
+            tgt = host_tgt[i % n_batches].to(dev, non_blocking=True)
+            loss = step_fn(ids, tgt)
+            losses.append(float(loss.detach().float().cpu()))
+        f1.record()
+        barrier()
+        ms_e2e = f0.elapsed_time(f1) / args.steps
+        if th is not None:
+            stop.set()
+            th.join(timeout=3)
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return {"ms": float(t[0]), "ms_e2e": float(t[1]), "launches": launches, "loss": losses[-1] if losses else None,
+                "clocks": _summarise_clocks(samples)}
 
-    # ---- device-timed region (inputs resident; 2.6 GB of weights + 30 GB of activations per step
-    # stream through a 126 MB L2, so every step starts cold)
-    stop, samples = threading.Event(), []
-    th = None
-    if rank == 0:
-        th = threading.Thread(target=_clock_sampler, args=(stop, samples, local), daemon=True)
-        th.start()
-    l0 = launches_fn()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        loss = step_fn(dev_ids[i % n_batches], dev_tgt[i % n_batches])
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = launches_fn() - l0
+    def torch_arm():
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        import gpt_fsdp as base
+        torch.manual_seed(1234)
+        step_fn, n = base.build(cfg, dev, world, mb, S)
+        return run_arm(step_fn, lambda: 0), n
 
-    # ---- end-to-end region: H2D of the step's tokens from pinned memory + D2H of the loss, every step
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    losses = []
-    f0.record()
-    for i in range(args.steps):
-        ids = host_ids[i % n_batches].to(dev, non_blocking=True)
-        tgt = host_tgt[i % n_batches].to(dev, non_blocking=True)
-        loss = step_fn(ids, tgt)
-        losses.append(float(loss.detach().float().cpu()))
-    f1.record()
-    barrier()
-    ms_e2e = f0.elapsed_time(f1) / args.steps
-    if th is not None:
-        stop.set()
-        th.join(timeout=3)
-
-    t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
-    tokens = world * mb * S
     status = 0
-    if args.impl == "ours":
+    base_rec = None
+    if args.impl == "torch":
+        res, n_params = torch_arm()
+    else:
         from ml_framework_b200 import _lib
+        from ml_framework_b200.engine import EngineConfig, TrainEngine
+        torch.manual_seed(1234)
+        model = GPT(cfg, dtype=torch.bfloat16, device=dev)
+        n_params = sum(p.numel() for p in model.parameters())
+        eng = TrainEngine(model, EngineConfig(strategy=args.strategy if world > 1 else "none", lr=3e-4,
+                                              fused_comm=not args.no_fused_comm), pg)
+        lib = _lib.get()
+        import ctypes
+        lib.mlf_launch_count.restype = ctypes.c_longlong
+        res = run_arm(eng.step, lambda: int(lib.mlf_launch_count()))
         status = _lib.read_status(True)
+        if not args.no_baseline:
+            # The comparison arm on the same box, in the same process: the plain torch.distributed (NCCL) +
+            # cuBLAS + SDPA implementation of the same configuration, after this arm's memory is released.
+            eng.close()
+            del eng, model
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            try:
+                b, _ = torch_arm()
+                base_rec = {"impl": "torch (FSDP over NCCL, cuBLAS, SDPA, fused AdamW, GradScaler)", "value": round(tokens / (b["ms"] / 1e3), 1),
+                            "unit": "tokens/s", "ms_per_step": round(b["ms"], 3), "e2e_value": round(tokens / (b["ms_e2e"] / 1e3), 1),
+                            "e2e_ms_per_step": round(b["ms_e2e"], 3), "final_loss": b["loss"], "clocks": b["clocks"]}
+            except Exception as e:  # the headline number stands even if the comparison arm cannot run
+                base_rec = {"impl": "torch", "error": f"{type(e).__name__}: {e}"[:300]}
+    ms, ms_e2e = res["ms"], res["ms_e2e"]
     if rank == 0:
         value = tokens / (ms / 1e3)
+        vs = None
+        if base_rec is not None and base_rec.get("value"):
+            vs = round(value / base_rec["value"], 4)
         out = {
             "metric": "train tokens/s (FSDP full-shard bf16, GPT 1.3B)", "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
             "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
+            "vs_baseline": vs,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
             "impl": args.impl,
             "config": {"model": "gpt-1.3b (24L, d2048, 16h, ffn8192, vocab50257, seq2048)" if args.model == "gpt-1.3b" else args.model,
                        "params": n_params, "global_batch": world * mb, "micro_batch_per_gpu": mb, "seq_len": S,
                        "parallelism": (f"fsdp{world}" if args.strategy == "fsdp" else f"{args.strategy}{world}") if world > 1 else "single",
                        "optimizer": "AdamW fused, fp32 master", "amp": "bf16 + dynamic loss scaler",
-                       "l2": "inputs larger than L2 (weights 2.6 GB + activations stream every step)"},
-            "clocks": _summarise_clocks(samples),
+                       "l2": "inputs larger than L2 (weights 2.6 GB + activations stream every step)",
+                       "baseline": "the reference publishes no training throughput and cannot run here; vs_baseline = value / "
+                                   "the plain torch.distributed NCCL + cuBLAS arm of the same config timed in this same process"},
+            "clocks": res["clocks"],
             "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": 2 * mb * S * 8, "d2h_bytes_per_step": 4},
-            "gpu_launches": launches,
-            "final_loss": losses[-1] if losses else None,
+            "gpu_launches": res["launches"],
+            "final_loss": res["loss"],
             "kernel_status": status,
             "model_tflops_per_gpu": round(cfg.flops_per_token(S) * mb * S / (ms / 1e3) / 1e12, 1),
         }
+        if base_rec is not None:
+            out["baseline"] = base_rec
+            if base_rec.get("e2e_value"):
+                out["e2e"]["vs_baseline"] = round(out["e2e"]["value"] / base_rec["e2e_value"], 4)
         print(json.dumps(out))
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -54,55 +54,10 @@ class DynamicScalerStats:
     skipped_steps: int
 
 
-class StaticLossScaler:
-    """Fixed scale (src/MLFramework/Amp/StaticLossScaler.cs)."""
-
-    def __init__(self, scale: float = 1.0, device="cpu"):
-        if scale <= 0:
-            raise ValueError("scale must be positive")
-        self.device = torch.device(device)
-        self.scale_t = torch.tensor(float(scale), device=self.device)
-        self.inv_scale_t = torch.tensor(1.0 / float(scale), device=self.device)
-        self.found_inf = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.enabled = True
-
-    @property
-    def scale(self) -> float:
-        return float(self.scale_t.item())
-
-    def scale_loss(self, loss):
-        return loss * self.scale_t
-
-    def update(self):
-        self.found_inf.zero_()
-
-    def check_overflow_flag(self) -> bool:
-        return bool(self.found_inf.item())
-
-
-class DynamicLossScaler:
-    def __init__(self, config: Optional[DynamicScalerConfig] = None, device="cpu", **overrides):
-        cfg = config or DynamicScalerConfig()
-        for k, v in overrides.items():
-            setattr(cfg, k, v)
-        cfg.validate()
-        self.cfg = cfg
-        self.enabled = cfg.enabled
-        self.device = torch.device(device)
-        self.scale_t = torch.tensor(float(cfg.initial_scale), device=self.device)
-        self.inv_scale_t = torch.tensor(1.0 / float(cfg.initial_scale), device=self.device)
-        self.tracker = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.found_inf = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.skipped = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.total_steps = 0
-
-    # ---- API
-    @property
-    def scale(self) -> float:
-        return float(self.scale_t.item())
-
-    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
-        return loss * self.scale_t if self.enabled else loss
+class _LossScalerBase:
+    """Gradient-side operations shared by the static and the dynamic scaler (the reference's
+    ``ILossScaler``, src/MLFramework/Amp/ILossScaler.cs:9): both expose ``scale_t``,
+    ``inv_scale_t`` and the ``found_inf`` flag on their device."""
 
     def unscale_gradients(self, grads: Iterable[torch.Tensor], sumsq: Optional[torch.Tensor] = None) -> None:
         """In place ``g *= 1/scale``; raises the found-inf flag on NaN/Inf."""
@@ -137,6 +92,71 @@ class DynamicLossScaler:
         if pg is not None and pg.world_size > 1:
             from ..dist.process_group import ReduceOp
             pg.all_reduce(self.found_inf, op=ReduceOp.MAX)
+
+
+class StaticLossScaler(_LossScalerBase):
+    """Fixed scale (src/MLFramework/Amp/StaticLossScaler.cs)."""
+
+    def __init__(self, scale: float = 1.0, device="cpu"):
+        if scale <= 0:
+            raise ValueError("scale must be positive")
+        self.device = torch.device(device)
+        self.scale_t = torch.tensor(float(scale), device=self.device)
+        self.inv_scale_t = torch.tensor(1.0 / float(scale), device=self.device)
+        self.found_inf = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.enabled = True
+        self.total_steps = 0
+        self.skipped_steps = 0
+
+    @property
+    def scale(self) -> float:
+        return float(self.scale_t.item())
+
+    def scale_loss(self, loss):
+        return loss * self.scale_t
+
+    def update(self):
+        """A fixed scale never changes; a skipped step is only counted."""
+        self.total_steps += 1
+        self.skipped_steps += int(self.found_inf.item()) if self.found_inf.device.type == "cpu" else 0
+        self.found_inf.zero_()
+
+    def get_stats(self) -> "DynamicScalerStats":
+        return DynamicScalerStats(self.scale, 0, self.total_steps, self.skipped_steps)
+
+    def state_dict(self) -> Dict:
+        return {"scale": self.scale, "total_steps": self.total_steps, "skipped": self.skipped_steps}
+
+    def load_state_dict(self, sd: Dict):
+        self.scale_t.fill_(sd["scale"])
+        self.inv_scale_t.fill_(1.0 / sd["scale"])
+        self.total_steps = sd.get("total_steps", 0)
+        self.skipped_steps = sd.get("skipped", 0)
+
+
+class DynamicLossScaler(_LossScalerBase):
+    def __init__(self, config: Optional[DynamicScalerConfig] = None, device="cpu", **overrides):
+        cfg = config or DynamicScalerConfig()
+        for k, v in overrides.items():
+            setattr(cfg, k, v)
+        cfg.validate()
+        self.cfg = cfg
+        self.enabled = cfg.enabled
+        self.device = torch.device(device)
+        self.scale_t = torch.tensor(float(cfg.initial_scale), device=self.device)
+        self.inv_scale_t = torch.tensor(1.0 / float(cfg.initial_scale), device=self.device)
+        self.tracker = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.found_inf = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.skipped = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.total_steps = 0
+
+    # ---- API
+    @property
+    def scale(self) -> float:
+        return float(self.scale_t.item())
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return loss * self.scale_t if self.enabled else loss
 
     def update(self) -> None:
         """Advance the state machine using the found-inf flag, then clear the flag."""

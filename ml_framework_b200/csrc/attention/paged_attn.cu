@@ -118,7 +118,14 @@ __global__ void __launch_bounds__(P_THREADS)
 paged_decode_kernel(const PagedDecodeParams p) {
   extern __shared__ __align__(128) uint8_t p_dsm[];
   const int b = blockIdx.x, hkv = blockIdx.y, sp = blockIdx.z;
-  const int len = p.seq_lens[b];
+  // A length beyond what the row of the block table can describe would index past the table: it is
+  // clamped to the table's capacity and reported, like every other rejected index in this file.
+  int len = p.seq_lens[b];
+  const long long cap = (long long)p.max_blocks * p.block_size;
+  if (len < 0 || len > cap) {
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_INDEX);
+    len = len < 0 ? 0 : (int)cap;
+  }
   int per = (len + p.splits - 1) / p.splits;
   per = (per + P_CH - 1) / P_CH * P_CH;
   const int t_lo = sp * per;
@@ -384,7 +391,7 @@ rope_kv_write_kernel(__nv_bfloat16* qkv, long long ld, const long long* pos, con
 // out_k / out_v [len, Hkv, 128] <- pages of one sequence.
 __global__ void __launch_bounds__(256)
 kv_gather_kernel(const __nv_bfloat16* cache, const int* block_table, int len, int Hkv, int block_size, int num_blocks,
-                 __nv_bfloat16* out_k, __nv_bfloat16* out_v, int* err) {
+                 __nv_bfloat16* out_k, __nv_bfloat16* out_v, int* err) {   // len <= table entries * block_size (checked by the launcher)
   const int vec_per_tok = Hkv * PD / 8;
   const long long total = (long long)len * vec_per_tok;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -543,9 +550,11 @@ MLF_API int mlf_rope_kv_write(void* qkv, long long ld, const long long* pos, con
   return 0;
 }
 
-MLF_API int mlf_kv_gather(const void* cache, const int* block_table, int len, int Hkv, int block_size, int num_blocks, void* out_k,
-                          void* out_v, uint64_t stream) {
+MLF_API int mlf_kv_gather(const void* cache, const int* block_table, int table_len, int len, int Hkv, int block_size, int num_blocks,
+                          void* out_k, void* out_v, uint64_t stream) {
   if (len <= 0) return 0;
+  MLF_REQUIRE((long long)len <= (long long)table_len * block_size,
+              "kv_gather: %d tokens need more than the %d block-table entries given", len, table_len);
   long long g = ((long long)len * (Hkv * PD / 8) + 255) / 256;
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;

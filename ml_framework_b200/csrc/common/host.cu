@@ -97,6 +97,7 @@ int* device_status_word() {
     int* p = nullptr;
     if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
     cudaMemset(p, 0, 256);
+    // offset 8: the wait budget in cycles read by the bounded waits (0 = the compiled default)
     g_status[dev] = p;
   }
   return g_status[dev];
@@ -129,6 +130,18 @@ MLF_API int mlf_read_status(int clear) {
 }
 
 MLF_API int mlf_sm_count() { return mlf::sm_count(); }
+
+// Cycle budget of every bounded device-side wait on the current device (mbarrier, chunk flag and
+// peer flag waits). 0 restores the compiled default (~1.5 s). Takes effect for kernels launched
+// after the call; synchronises the device.
+MLF_API int mlf_set_wait_budget_cycles(long long cycles) {
+  MLF_REQUIRE(cycles >= 0, "set_wait_budget_cycles: negative budget");
+  int* p = mlf::device_status_word();
+  MLF_REQUIRE(p != nullptr, "set_wait_budget_cycles: no status block");
+  MLF_CHECK_CUDA(cudaDeviceSynchronize());
+  MLF_CHECK_CUDA(cudaMemcpy(reinterpret_cast<char*>(p) + 8, &cycles, sizeof(cycles), cudaMemcpyHostToDevice));
+  return 0;
+}
 
 // Kernels launched by this library in this process so far.
 MLF_API long long mlf_launch_count() { return mlf::g_launches.load(std::memory_order_relaxed); }

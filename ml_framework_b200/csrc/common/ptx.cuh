@@ -28,9 +28,18 @@ enum : int {
   ERR_WAIT_ATTN = 8,
 };
 
-// ~1.5 s at 1.3-1.9 GHz; long enough for any legitimate wait, short enough that a
-// lost signal ends the kernel well inside a test timeout.
+// Default budget of a bounded wait: ~1.5 s at 1.3-1.9 GHz; long enough for any legitimate wait,
+// short enough that a lost signal ends the kernel well inside a test timeout.
 constexpr long long kWaitCycleBudget = 2500000000LL;
+
+// The device status block (see device_status_word() on the host side) is 256 bytes: the status
+// word at offset 0 and the wait budget in cycles as a 64-bit value at offset 8, which the host can
+// change at run time (mlf_set_wait_budget_cycles). A wait reads it only once it has to spin.
+__device__ __forceinline__ long long wait_budget(const int* err_word) {
+  if (err_word == nullptr) return kWaitCycleBudget;
+  const long long b = *reinterpret_cast<const volatile long long*>(err_word + 2);
+  return b > 0 ? b : kWaitCycleBudget;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -84,11 +93,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int* err_word, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long budget = wait_budget(err_word);
 #pragma unroll 1
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycleBudget) {
+    if (clock64() - t0 > budget) {
       *abort_flag = 1;
       if (err_word) atomicCAS(err_word, 0, code);
       return false;
@@ -113,13 +123,14 @@ __device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, vo
                                                int* err_word, int code) {
   if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long budget = wait_budget(err_word);
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
       if (mbar_test_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycleBudget) {
+    if (clock64() - t0 > budget) {
       *abort_flag = 1;
       if (err_word) atomicCAS(err_word, 0, code);
       return false;
@@ -357,11 +368,13 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
 // Bounded wait until *p >= want (monotonic epochs). Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* p, uint32_t want, int* err_word,
                                                  int code) {
+  if (static_cast<int32_t>(ld_acquire_sys(p) - want) >= 0) return true;
   const long long t0 = clock64();
+  const long long budget = wait_budget(err_word);
 #pragma unroll 1
   while (true) {
     if (static_cast<int32_t>(ld_acquire_sys(p) - want) >= 0) return true;
-    if (clock64() - t0 > kWaitCycleBudget) {
+    if (clock64() - t0 > budget) {
       if (err_word) atomicCAS(err_word, 0, code);
       return false;
     }
@@ -370,12 +383,14 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* p, uint32_t wan
 }
 __device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* p, uint32_t want,
                                                  volatile int* abort_flag, int* err_word, int code) {
+  if (static_cast<int32_t>(ld_acquire_gpu(p) - want) >= 0) return true;
   const long long t0 = clock64();
+  const long long budget = wait_budget(err_word);
 #pragma unroll 1
   while (true) {
     if (static_cast<int32_t>(ld_acquire_gpu(p) - want) >= 0) return true;
     if (abort_flag && *abort_flag) return false;
-    if (clock64() - t0 > kWaitCycleBudget) {
+    if (clock64() - t0 > budget) {
       if (abort_flag) *abort_flag = 1;
       if (err_word) atomicCAS(err_word, 0, code);
       return false;

@@ -56,12 +56,8 @@ struct ReduceSeg {
 // out[dst_off + i] = scale * sum_r bufs[r][src_off + i]   (bf16 in, bf16 or fp32 out)
 // found_inf is raised when a reduced value is not finite; sumsq accumulates the squared norm.
 template <typename OutT>
-__global__ void __launch_bounds__(256)
-rs_reduce_kernel(PeerPtrs bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out, float scale,
-                 const float* scale_ptr, int* found_inf, float* sumsq) {
-  const float sc = scale * (scale_ptr ? *scale_ptr : 1.f);
-  float acc_sq = 0.f;
-  bool bad = false;
+__device__ __forceinline__ void rs_reduce_body(const PeerPtrs& bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out,
+                                               float sc, bool& bad, float& acc_sq) {
   for (int s = 0; s < n_segs; ++s) {
     const ReduceSeg sg = segs[s];
     const long long nvec = sg.numel / 8;
@@ -101,6 +97,16 @@ rs_reduce_kernel(PeerPtrs bufs, int world, int rank, const ReduceSeg* segs, int 
       }
     }
   }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+rs_reduce_kernel(PeerPtrs bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out, float scale,
+                 const float* scale_ptr, int* found_inf, float* sumsq) {
+  const float sc = scale * (scale_ptr ? *scale_ptr : 1.f);
+  float acc_sq = 0.f;
+  bool bad = false;
+  rs_reduce_body<OutT>(bufs, world, rank, segs, n_segs, out, sc, bad, acc_sq);
   if (found_inf && __any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(found_inf, 1);
   if (sumsq) {
 #pragma unroll
@@ -212,6 +218,113 @@ __device__ __forceinline__ void sync_leave(SyncState* st, uint32_t e) {
       *reinterpret_cast<volatile uint32_t*>(&st->epoch) = e;
     }
   }
+}
+
+// Leave with a handshake: the last CTA of this rank to finish tells every peer that all of this
+// rank's loads from and stores to peer memory for this launch are complete (epoch e + 1) and waits
+// for the same news from every peer, so that when the kernel ends on a rank (a) every peer has
+// finished reading this rank's buffers and (b) everything the peers stored here is visible. The
+// device epoch advances by two per launch.
+__device__ __forceinline__ void sync_leave_all(const PeerPtrs& pads, SyncState* st, int rank, int world, uint32_t e, int* err) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(&st->done, 1u) == gridDim.x - 1 ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(pads.p[t]) + rank * 32, e + 1u);
+    wait_flag_ge_sys(static_cast<const uint32_t*>(pads.p[rank]) + t * 32, e + 1u, err, ERR_WAIT_PEER_FLAG);
+  }
+  __syncthreads();
+  if (t == 0) {
+    st->done = 0;
+    __threadfence();
+    *reinterpret_cast<volatile uint32_t*>(&st->epoch) = e + 1u;
+  }
+}
+
+// Raises the overflow flag of EVERY rank (flags.p[r] = rank r's flag in symmetric memory), so that
+// all ranks skip the optimizer step together without a further collective.
+__device__ __forceinline__ void raise_flag_everywhere(const PeerPtrs& flags, int world, bool bad) {
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) {
+    for (int r = 0; r < world; ++r)
+      if (flags.p[r]) *reinterpret_cast<volatile int*>(flags.p[r]) = 1;
+  }
+}
+
+// Reduce-scatter with both synchronisations inside (replaces barrier + rs_reduce + flag all-reduce):
+// waits until every rank has queued the same launch (their producers, earlier on their streams, are
+// then complete), sums this rank's slices out of all W buffers, raises every rank's overflow flag on
+// a non-finite result, and leaves with the handshake above.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+rs_reduce_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, PeerPtrs flags, int world, int rank, const ReduceSeg* segs, int n_segs,
+                      OutT* out, float scale, const float* scale_ptr, float* sumsq, int* err) {
+  const uint32_t e = sync_enter(pads, st, rank, world, err);
+  const float sc = scale * (scale_ptr ? *scale_ptr : 1.f);
+  float acc_sq = 0.f;
+  bool bad = false;
+  rs_reduce_body<OutT>(bufs, world, rank, segs, n_segs, out, sc, bad, acc_sq);
+  raise_flag_everywhere(flags, world, bad);
+  if (sumsq) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc_sq += __shfl_xor_sync(0xffffffffu, acc_sq, o);
+    if ((threadIdx.x & 31) == 0 && isfinite(acc_sq)) atomicAdd(sumsq, acc_sq);
+  }
+  sync_leave_all(pads, st, rank, world, e, err);
+}
+
+// Two-shot all-reduce of a gradient bucket with both synchronisations inside: rank r sums slice r of
+// all W copies, scales it, checks it for overflow (raising every rank's flag) and stores it into
+// slice r of every rank's buffer. When the kernel ends on a rank its whole buffer holds the result.
+__global__ void __launch_bounds__(256)
+ar_two_shot_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, PeerPtrs flags, int world, int rank, long long numel, float scale,
+                        const float* scale_ptr, int* err) {
+  const uint32_t e = sync_enter(pads, st, rank, world, err);
+  const float sc = scale * (scale_ptr ? *scale_ptr : 1.f);
+  const long long per = ((numel / 8 + world - 1) / world) * 8;
+  const long long lo = per * rank;
+  const long long hi = lo + per < numel ? lo + per : numel;
+  const long long nvec = hi > lo ? (hi - lo) / 8 : 0;
+  bool bad = false;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        int r = rank + 1 + k;
+        if (r >= world) r -= world;
+        v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[r]) + lo + i * 8);
+      }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
+        a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+      }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[j] *= sc;
+      if (!isfinite(a[j])) bad = true;
+    }
+    uint4 w;
+    w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < world) {
+        int r = rank + 1 + k;
+        if (r >= world) r -= world;
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[r]) + lo + i * 8) = w;
+      }
+  }
+  raise_flag_everywhere(flags, world, bad);
+  sync_leave_all(pads, st, rank, world, e, err);
 }
 
 // One-shot all-reduce with the arrival synchronisation inside: the producers of bufs[*] (the kernels
@@ -431,6 +544,52 @@ MLF_API int mlf_ar_two_shot(void* const* bufs, int world, int rank, long long nu
   if (g > cap) g = cap;
   if (g < 1) g = 1;
   ar_two_shot_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(to_peers(bufs, world), world, rank, numel, scale);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Reduce-scatter / two-shot all-reduce that synchronise inside the kernel (see the kernels above).
+// pads / state as for mlf_ar_one_shot_sync; every stream that issues such launches needs a pad and a
+// state of its own, and all ranks must issue the same sequence per pad. flags: every rank's overflow
+// flag (int, in symmetric memory) or null. max_ctas bounds the grid (0 = one CTA per two SMs), so a
+// launch that overlaps compute kernels leaves them most of the SMs.
+MLF_API int mlf_rs_reduce_sync(void* const* bufs, void* const* pads, void* state, void* const* flags, int world, int rank,
+                               const void* segs, int n_segs, void* out, int out_fp32, float scale, const float* scale_ptr, float* sumsq,
+                               long long total_numel, int max_ctas, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && state != nullptr, "rs_reduce_sync: bad arguments");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  long long g = (total_numel / 8 + 255) / 256;
+  const long long cap = max_ctas > 0 ? max_ctas : sm_count() / 2;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  PeerPtrs fl = flags ? to_peers(flags, world) : PeerPtrs{};
+  if (out_fp32)
+    rs_reduce_sync_kernel<float><<<(int)g, 256, 0, st>>>(to_peers(bufs, world), to_peers(pads, world), static_cast<SyncState*>(state), fl,
+                                                         world, rank, static_cast<const ReduceSeg*>(segs), n_segs, static_cast<float*>(out),
+                                                         scale, scale_ptr, sumsq, device_status_word());
+  else
+    rs_reduce_sync_kernel<__nv_bfloat16><<<(int)g, 256, 0, st>>>(to_peers(bufs, world), to_peers(pads, world),
+                                                                 static_cast<SyncState*>(state), fl, world, rank,
+                                                                 static_cast<const ReduceSeg*>(segs), n_segs,
+                                                                 static_cast<__nv_bfloat16*>(out), scale, scale_ptr, sumsq,
+                                                                 device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+MLF_API int mlf_ar_two_shot_sync(void* const* bufs, void* const* pads, void* state, void* const* flags, int world, int rank,
+                                 long long numel, float scale, const float* scale_ptr, int max_ctas, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && numel % 8 == 0 && state != nullptr, "ar_two_shot_sync: bad arguments");
+  long long g = (numel / 8 / world + 255) / 256;
+  const long long cap = max_ctas > 0 ? max_ctas : sm_count() / 2;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  PeerPtrs fl = flags ? to_peers(flags, world) : PeerPtrs{};
+  ar_two_shot_sync_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      to_peers(bufs, world), to_peers(pads, world), static_cast<SyncState*>(state), fl, world, rank, numel, scale, scale_ptr,
+      device_status_word());
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -40,6 +40,7 @@ class ProcessLauncher:
         self.log_dir = Path(log_dir) if log_dir else None
         self.assign_gpus = assign_gpus
         self.ranks: List[RankProcess] = []
+        self._failed_first: Optional[RankProcess] = None   # the rank whose non-zero exit was observed first
 
     def launch(self, argv: Sequence[str], num_processes: int, extra_env: Optional[Dict[str, str]] = None) -> List[RankProcess]:
         if num_processes <= 0:
@@ -75,6 +76,8 @@ class ProcessLauncher:
                     if code is not None:
                         r.exit_code = code
                         pending.discard(r.rank)
+                        if code != 0 and self._failed_first is None:
+                            self._failed_first = r      # before the others are terminated (they then exit with -SIGTERM)
                         if code != 0 and kill_on_failure:
                             self.terminate_all()
                             for o in self.ranks:
@@ -108,6 +111,10 @@ class ProcessLauncher:
         return any(r.exit_code not in (None, 0) for r in self.ranks)
 
     def first_failed_process(self) -> Optional[RankProcess]:
+        """The rank that failed first in time (ProcessLauncher.cs:128-186), not the lowest-numbered rank with a
+        non-zero code: ranks terminated because of that failure also end with a non-zero code."""
+        if self._failed_first is not None:
+            return self._failed_first
         for r in self.ranks:
             if r.exit_code not in (None, 0):
                 return r

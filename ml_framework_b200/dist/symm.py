@@ -146,11 +146,56 @@ class SymmetricMemory:
         _lib.check(rc, "mlf_ar_one_shot")
 
     # ---- graph-replayable variants: the epoch is kept on the device (see mlf_ar_one_shot_sync)
-    def _sync_pad(self) -> SymmBuffer:
-        if getattr(self, "_gpad", None) is None:
-            self._gpad = self.alloc(2048)          # [0, 1024): signal slots written by peers; [1024, 1032): local {epoch, count}
+    def _sync_pad(self, key: str = "main") -> SymmBuffer:
+        """Signal pad + device epoch for one ordered sequence of in-kernel-synchronised launches. Launches
+        that share a pad must be issued in the same order on every rank and on one stream per rank, so a
+        side stream gets a pad of its own (``key``). Collective on first use."""
+        pads = self.__dict__.setdefault("_gpads", {})
+        if key not in pads:
+            pads[key] = self.alloc(2048)           # [0, 1024): signal slots written by peers; [1024, 1032): local {epoch, count}
+            if self.pg is not None and self.world > 1:
+                self.pg.barrier()
+        return pads[key]
+
+    def alloc_flag(self) -> SymmBuffer:
+        """An int32 flag in symmetric memory (the overflow flag every rank can raise on every rank)."""
+        b = self.alloc(256)
+        if self.pg is not None and self.world > 1:
             self.pg.barrier()
-        return self._gpad
+        return b
+
+    def rs_reduce_sync(self, buf: SymmBuffer, segs_dev: torch.Tensor, n_segs: int, out: torch.Tensor, total_numel: int, *,
+                       scale: float = 1.0, scale_ptr: Optional[torch.Tensor] = None, flag: Optional[SymmBuffer] = None,
+                       sumsq: Optional[torch.Tensor] = None, offset_bytes: int = 0, key: str = "main", max_ctas: int = 0,
+                       stream=None):
+        """Reduce-scatter by peer reads whose arrival and departure synchronisation run inside the kernel
+        (no barrier launch, no flag all-reduce): see ``rs_reduce_sync_kernel``."""
+        pad = self._sync_pad(key)
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+        rc = self._lib.mlf_rs_reduce_sync(buf.peer_table(offset_bytes), pad.peer_table(), C.c_void_p(pad.ptrs[self.rank] + 1024),
+                                          flag.peer_table() if flag is not None else None, self.world, self.rank, p(segs_dev), n_segs,
+                                          p(out), int(out.dtype == torch.float32), C.c_float(scale), p(scale_ptr), p(sumsq),
+                                          C.c_longlong(total_numel), max_ctas, C.c_uint64(_lib.stream_handle(stream)))
+        _lib.check(rc, "mlf_rs_reduce_sync")
+
+    def all_reduce_two_shot_sync(self, buf: SymmBuffer, numel: int, *, scale: float = 1.0, scale_ptr: Optional[torch.Tensor] = None,
+                                 flag: Optional[SymmBuffer] = None, offset_bytes: int = 0, key: str = "main", max_ctas: int = 0,
+                                 stream=None):
+        """In-place all-reduce of ``numel`` bf16 elements at ``offset_bytes`` of every rank's ``buf``; the whole
+        buffer holds the (scaled) sum when the launch completes on a rank."""
+        pad = self._sync_pad(key)
+        rc = self._lib.mlf_ar_two_shot_sync(buf.peer_table(offset_bytes), pad.peer_table(), C.c_void_p(pad.ptrs[self.rank] + 1024),
+                                            flag.peer_table() if flag is not None else None, self.world, self.rank,
+                                            C.c_longlong(numel), C.c_float(scale),
+                                            C.c_void_p(scale_ptr.data_ptr()) if scale_ptr is not None else None, max_ctas,
+                                            C.c_uint64(_lib.stream_handle(stream)))
+        _lib.check(rc, "mlf_ar_two_shot_sync")
+
+    def check_status(self):
+        """Reads (and clears) the device status word; a wait on a peer that ran out of its budget raises
+        ``CommunicationTimeout`` (the reference's TimeoutManager -> CommunicationTimeoutException path,
+        src/MLFramework/Communication/FaultTolerance/TimeoutManager.cs:33-90). Synchronises the device."""
+        raise_for_status(_lib.read_status(True))
 
     def all_reduce_one_shot_sync(self, buf: SymmBuffer, out: torch.Tensor, numel: int, residual: Optional[torch.Tensor] = None,
                                  offset_bytes: int = 0):
@@ -186,6 +231,24 @@ class SymmetricMemory:
         for p in self._owned:
             self._lib.mlf_symm_free(C.c_void_p(p))
         self._opened, self._owned = [], []
+
+
+ERR_WAIT_PEER_FLAG, ERR_WAIT_CHUNK_FLAG = 5, 6
+
+
+def raise_for_status(status: int):
+    """Maps a non-zero kernel status to an exception: waits on a peer become ``CommunicationTimeout``."""
+    if status == 0:
+        return
+    from .process_group import CommunicationError, CommunicationTimeout
+    if status in (ERR_WAIT_PEER_FLAG, ERR_WAIT_CHUNK_FLAG):
+        raise CommunicationTimeout(f"a device-side wait on a peer ran out of its cycle budget (kernel status {status})")
+    raise CommunicationError(f"a kernel reported status {status}")
+
+
+def set_wait_budget_cycles(cycles: int):
+    """Cycle budget of every bounded device-side wait on the current device (0 = the default of about 1.5 s)."""
+    _lib.check(_lib.get().mlf_set_wait_budget_cycles(C.c_longlong(int(cycles))), "mlf_set_wait_budget_cycles")
 
 
 def make_reduce_segs(segs: Sequence[tuple], device) -> torch.Tensor:

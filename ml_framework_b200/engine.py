@@ -59,9 +59,10 @@ class TrainEngine:
         self.scaler = DynamicLossScaler(self.cfg.scaler, device=self.device) if self.cfg.loss_scaling else None
         strategy = self.cfg.strategy if self.world > 1 else ("none" if self.cfg.strategy in ("ddp", "zero2") else self.cfg.strategy)
         self.strategy = strategy
-        if strategy in ("fsdp",):
+        if strategy in ("fsdp", "zero2"):
             from .parallel.fsdp import FSDP, FSDPConfig
-            self.fsdp = FSDP(model, FSDPConfig(fused_comm=self.cfg.fused_comm), process_group,
+            self.reducer = None
+            self.fsdp = FSDP(model, FSDPConfig(fused_comm=self.cfg.fused_comm, sharding_strategy="full" if strategy == "fsdp" else "grad_op"), process_group,
                              optimizer_kwargs=dict(lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps,
                                                    weight_decay=self.cfg.weight_decay))
             self.flat = None
@@ -75,11 +76,34 @@ class TrainEngine:
                 if id(p) not in seen:
                     seen.add(id(p))
                     uniq.append(p)
-            self.flat = FlatParams(uniq, grad_dtype=self.cfg.grad_dtype)
+            self.reducer = None
+            self.symm = None
+            grad_alloc = None
+            gdt = self.cfg.grad_dtype or uniq[0].dtype
+            if strategy == "ddp" and self.world > 1:
+                from .parallel.ddp import fused_comm_possible
+                if fused_comm_possible(self.pg, self.device, self.cfg.fused_comm, gdt):
+                    # the flat gradient buffer lives in symmetric memory: buckets are reduced by peer loads / stores
+                    from .dist.symm import SymmetricMemory
+                    self.symm = SymmetricMemory(self.pg, self.device)
+                    holder = {}
+
+                    def grad_alloc(n, dt, holder=holder):
+                        holder["buf"] = self.symm.alloc(n * torch.empty(0, dtype=dt).element_size())
+                        return holder["buf"].view(dt, n)
+            self.flat = FlatParams(uniq, grad_dtype=self.cfg.grad_dtype, grad_alloc=grad_alloc)
             self.optimizer = AdamW(self.flat, lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps,
                                    weight_decay=self.cfg.weight_decay)
             if strategy == "ddp" and self.world > 1:
+                from .parallel.ddp import FlatGradReducer
                 self.pg.broadcast(self.flat.flat, src=0)
+                flag = None
+                if self.symm is not None:
+                    flag = self.symm.alloc_flag()
+                    if self.scaler is not None:
+                        self.scaler.found_inf = flag.view(torch.int32, 1)   # every rank's kernels raise every rank's flag
+                self.reducer = FlatGradReducer(self.flat, self.pg, self.cfg.bucket_size_mb, symm=self.symm,
+                                               symm_buf=holder["buf"] if self.symm is not None else None, flag=flag)
         self.steps = 0
 
     # ------------------------------------------------------------------
@@ -96,24 +120,35 @@ class TrainEngine:
         loss.backward()
         flat.gather_missing_grads()
         grad_scale = 1.0
-        if self.strategy == "ddp" and self.world > 1:
-            from .dist.process_group import ReduceOp
-            self.pg.all_reduce(flat.grad, op=ReduceOp.SUM)
-            grad_scale = 1.0 / self.world
+        checked = False
+        if self.reducer is not None:
+            # buckets were all-reduced (and averaged) from the gradient-ready hooks while backward ran;
+            # this reduces what the hooks could not and waits for the communication stream
+            self.reducer.finish()
+            checked = self.symm is not None      # the in-kernel all-reduce checks every reduced value
         if self.scaler is not None:
             from .ops import native
-            if flat.grad.is_cuda:
-                native.amp_unscale_check_(flat.grad, self.scaler.found_inf, inv_scale=None, write_back=False)
-            elif not torch.isfinite(flat.grad).all():
-                self.scaler.found_inf.fill_(1)
-            if self.world > 1:
-                self.scaler.sync_found_inf(self.pg)
+            if not checked:
+                if flat.grad.is_cuda:
+                    native.amp_unscale_check_(flat.grad, self.scaler.found_inf, inv_scale=None, write_back=False)
+                elif not torch.isfinite(flat.grad).all():
+                    self.scaler.found_inf.fill_(1)
+                if self.world > 1:
+                    self.scaler.sync_found_inf(self.pg)
             self.optimizer.step(grad_scale=grad_scale, inv_scale=self.scaler.inv_scale_t, found_inf=self.scaler.found_inf)
             self.scaler.update()
         else:
             self.optimizer.step(grad_scale=grad_scale)
         self.steps += 1
         return loss
+
+    def close(self):
+        """Releases the peer-mapped buffers of the fused communication paths (collective when they exist)."""
+        if self.fsdp is not None:
+            self.fsdp.close()
+        if getattr(self, "symm", None) is not None:
+            self.symm.close()
+            self.symm = None
 
     def state_dict(self):
         sd = {"steps": self.steps, "optimizer": self.optimizer.state_dict() if hasattr(self.optimizer, "state_dict") else None}

@@ -144,8 +144,25 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise TypeError("gemm expects bf16 operands on the GPU")
     if out is None:
         out = torch.empty((M, out_cols), dtype=out_dtype, device=a.device)
-    elif out.stride(-1) != 1:
-        raise ValueError("out must have a contiguous last dimension")
+    else:
+        # The epilogue's stores are sized from M, N and the pitch: anything else would be written past its end.
+        scatter = comm is not None and bool(comm.scatter_out)
+        want = (int(comm.rows_per_owner) if scatter else M, out_cols)      # routed rows land in the owners' partial buffers
+        if out.dim() != 2 or tuple(out.shape) != want:
+            raise ValueError(f"out has shape {tuple(out.shape)}, the product needs {want}")
+        if out.dtype != out_dtype:
+            raise ValueError(f"out is {out.dtype}, the epilogue writes {out_dtype}")
+        if out.device != a.device:
+            raise ValueError("out is on another device than the operands")
+        if out.stride(-1) != 1 or out.data_ptr() % 16 or (out.stride(0) * out.element_size()) % 16:
+            raise ValueError("out needs a contiguous last dimension, a 16-byte aligned base and a 16-byte multiple row pitch")
+    for name, t, cols in (("aux_in", aux_in, 2 * N if flags & EPI_DSWIGLU else N), ("aux_out", aux_out, N)):
+        if t is None:
+            continue
+        if t.dim() != 2 or t.shape[0] != M or t.shape[1] != cols or t.dtype != torch.bfloat16 or t.device != a.device \
+                or t.stride(-1) != 1:
+            raise ValueError(f"{name} must be a bf16 [{M}, {cols}] tensor on the operands' device with a contiguous last "
+                             f"dimension, got {tuple(t.shape)} {t.dtype}")
     args = GemmArgs()
     args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
     args.bias = bias.data_ptr() if bias is not None else None

@@ -386,7 +386,8 @@ def kv_gather(kv_cache: torch.Tensor, block_table_row: torch.Tensor, length: int
     nb, _, bs, Hkv, D = kv_cache.shape
     k = torch.empty(length, Hkv, D, dtype=kv_cache.dtype, device=kv_cache.device)
     v = torch.empty_like(k)
-    rc = _L().mlf_kv_gather(_p(kv_cache), _p(block_table_row.contiguous()), int(length), Hkv, bs, nb, _p(k), _p(v), _st())
+    row = block_table_row.contiguous()
+    rc = _L().mlf_kv_gather(_p(kv_cache), _p(row), int(row.numel()), int(length), Hkv, bs, nb, _p(k), _p(v), _st())
     _lib.check(rc, "mlf_kv_gather")
     return k, v
 

@@ -250,7 +250,8 @@ class FSDP:
                 return b.view(dt, numel)
             return torch.zeros(numel, dtype=dt, device=dev)
         self.param_shards = symm_or_local("param_shards", total)      # bf16 working copy of what this rank owns
-        self.grad_shards = torch.zeros(total, dtype=dt, device=dev)    # reduced gradients of what this rank owns
+        # reduced gradients of what this rank owns (symmetric on the fused path: its replicated tail is all-reduced in place)
+        self.grad_shards = symm_or_local("grad_shards", total)
         max_full = max([u.full_numel for u in self.units], default=0)
         # block units rotate through two gathered / gradient buffers; the root unit keeps its own
         n_rot = 2 if not keep_full else 0
@@ -320,6 +321,9 @@ class FSDP:
             u._red_segs = make_reduce_segs(red, self.device)
             u._red_numel = sum(x[2] for x in red)
         self._grad_buf_of = {}
+        self._flag = self.symm.alloc_flag()        # overflow flag every rank's reduction kernels raise on every rank
+        self._rs_done = {}                         # gradient buffer address -> event of the reduction that last read it
+        self._sync_key = "fsdp"
 
     def _copy_table(self, u: "FSDPUnit", full: torch.Tensor) -> torch.Tensor:
         from ..dist.symm import make_copy_segs
@@ -419,6 +423,7 @@ class FSDP:
         gbuf = self._rot_grad[i % 2] if u.grad_full is None or self.cfg.sharding_strategy != "grad_op" else u.grad_full
         if self.cfg.sharding_strategy == "grad_op":
             gbuf = self._rot_grad[i % 2]
+            self._wait_grad_buffer(gbuf)
             self._point_params(u, u.gathered, gbuf)
             u._gbuf = gbuf
             return
@@ -427,21 +432,40 @@ class FSDP:
             self._gather_unit(u, full)
             self._rot_owner[i % 2] = i
         u.gathered = full
+        self._wait_grad_buffer(gbuf)
         self._point_params(u, full, gbuf)
         u._gbuf = gbuf
         if self._rot_owner.get((i - 1) % 2) != i - 1:
             self._schedule_prefetch(i - 1)
 
     def _reduce_unit_fused(self, u: FSDPUnit, gbuf: torch.Tensor, found_inf=None):
-        """Reduce-scatter by peer reads: barrier (every rank has finished this unit's backward),
-        then each rank sums its slices of all W gradient buffers straight out of peer memory."""
+        """Reduce-scatter by peer reads on the communication stream, overlapped with the backward of the
+        next unit: ONE launch waits inside the kernel until every rank has queued it (their backward of
+        this unit is then complete), sums this rank's slices of all W gradient buffers straight out of
+        peer memory, raises every rank's overflow flag on a non-finite sum, and leaves once every peer
+        has finished reading this rank's buffer. The compute stream waits for that launch only when the
+        buffer is written again, two units later."""
         for sp in u.sharded:
             if not getattr(sp.param, "_main_grad_started", False):
                 gbuf[sp.full_off:sp.full_off + sp.padded].zero_()
         name = next(k for k, b in self._symm_bufs.items() if b.local.data_ptr() == gbuf.data_ptr())
         buf = self._symm_bufs[name]
-        self.symm.barrier()
-        self.symm.rs_reduce(buf, u._red_segs, u._red_segs.shape[0], self.grad_shards, u._red_numel, found_inf=found_inf)
+        cs = self._comm_stream
+        ready = torch.cuda.Event()
+        ready.record()
+        cs.wait_event(ready)
+        with torch.cuda.stream(cs):
+            self.symm.rs_reduce_sync(buf, u._red_segs, u._red_segs.shape[0], self.grad_shards, u._red_numel, flag=self._flag,
+                                     key=self._sync_key, max_ctas=32)
+            done = torch.cuda.Event()
+            done.record(cs)
+        self._rs_done[gbuf.data_ptr()] = done
+
+    def _wait_grad_buffer(self, gbuf: torch.Tensor):
+        """Before a gradient buffer is written again: the reduction that read it (here and on the peers) must be over."""
+        ev = self._rs_done.pop(gbuf.data_ptr(), None) if self.fused else None
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
 
     def _reduce_unit(self, u: FSDPUnit, gbuf: torch.Tensor):
         if self.fused:
@@ -476,6 +500,10 @@ class FSDP:
     # ------------------------------------------------------------------ step
     def train_step(self, ids, targets, scaler=None):
         self.zero_grad()
+        if self.fused and scaler is not None:
+            flag = self._flag.view(torch.int32, 1)
+            if scaler.found_inf.data_ptr() != flag.data_ptr():
+                scaler.found_inf = flag           # the scaler's flag is the one the reduction kernels raise on every rank
         self._found_inf = scaler.found_inf if scaler is not None else None
         self._rot_owner = {}                          # shards changed at the last optimizer step
         root = self.root_unit
@@ -503,7 +531,19 @@ class FSDP:
             elif not getattr(p, "_main_grad_started", False):
                 p.main_grad.zero_()
         if self.world > 1 and self.rep_grad.numel():
-            self.pg.all_reduce(self.rep_grad, op=ReduceOp.SUM)
+            if self.fused:
+                # in place over every rank's replicated tail, on the communication stream behind the unit reductions
+                cs = self._comm_stream
+                cs.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(cs):
+                    self.symm.all_reduce_two_shot_sync(self._symm_bufs["grad_shards"], self.rep_grad.numel(), flag=self._flag,
+                                                       offset_bytes=self.rep_off * self.rep_grad.element_size(),
+                                                       key=self._sync_key, max_ctas=32)
+            else:
+                self.pg.all_reduce(self.rep_grad, op=ReduceOp.SUM)
+        if self.fused:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)   # every reduction of the step is in grad_shards
+            self._rs_done.clear()
 
     def zero_grad(self):
         for _, p in self.replicated:
@@ -521,11 +561,14 @@ class FSDP:
         g = self.grad_shards
         inv_scale = found = None
         if scaler is not None:
-            if g.is_cuda:
-                native.amp_unscale_check_(g, scaler.found_inf, inv_scale=None, write_back=False)
-            elif not torch.isfinite(g.float()).all():
-                scaler.found_inf.fill_(1)
-            scaler.sync_found_inf(self.pg)
+            if self.fused:
+                pass    # every reduced value was checked by the reduction kernels, which raise the flag on all ranks
+            else:
+                if g.is_cuda:
+                    native.amp_unscale_check_(g, scaler.found_inf, inv_scale=None, write_back=False)
+                elif not torch.isfinite(g.float()).all():
+                    scaler.found_inf.fill_(1)
+                scaler.sync_found_inf(self.pg)
             inv_scale, found = scaler.inv_scale_t, scaler.found_inf
         gscale = 1.0 / self.world
         b1, b2 = kw["betas"]
@@ -571,6 +614,15 @@ class FSDP:
                                       eps=kw["eps"], weight_decay=kw["weight_decay"], step=self.step_count)
         u.owned_master.copy_(p); u.owned_m.copy_(m); u.owned_v.copy_(v)
         u.owned_full.copy_(u.owned_master.to(u.owned_full.device).to(self.dtype))
+
+    def close(self):
+        """Unmaps and frees the symmetric buffers (parameters, gradients and shards living in them become invalid)."""
+        if self.symm is not None:
+            if self.pg is not None and self.world > 1:
+                torch.cuda.synchronize()
+                self.pg.barrier()          # nobody may still be reading this rank's buffers
+            self.symm.close()
+            self.symm = None
 
     # ------------------------------------------------------------------ state
     def set_learning_rate(self, lr: float):

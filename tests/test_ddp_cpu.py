@@ -16,6 +16,13 @@ from ml_framework_b200.parallel.ddp import DistributedDataParallel, create_bucke
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def test_bucket_packing_largest_first_and_oversized_alone():
     ps = [nn.Parameter(torch.zeros(n)) for n in (10, 3000, 200, 50, 700)]
     b = create_buckets(ps, bucket_bytes=1000 * 4)
@@ -99,10 +106,120 @@ def test_launcher_env_logs_and_first_failure(tmp_path):
 
 @pytest.mark.timeout(180)
 def test_cpu_mlp_ddp_two_gloo_ranks(tmp_path):
-    l = ProcessLauncher(master_port=29621, log_dir=str(tmp_path))
+    l = ProcessLauncher(master_port=_free_port(), log_dir=str(tmp_path))
     l.launch([sys.executable, os.path.join(ROOT, "baseline", "cpu_mlp_ddp.py"), "100"], 2)
     ok = l.wait_for_all(timeout_s=150)
     log = (tmp_path / "rank_0.log").read_text()
     assert ok, log + (tmp_path / "rank_1.log").read_text()
     res = json.loads([ln for ln in log.splitlines() if ln.startswith("{")][-1])
     assert res["gradients_equal_across_ranks"] and res["parameters_in_sync"] and res["steps"] == 100
+
+
+def test_ddp_no_sync_keeps_local_gradients_then_matches_big_batch():
+    """One micro-step inside no_sync() plus one synchronised micro-step: inside, gradients stay local
+    (nothing from an earlier step's bucket leaks in); after, they are the average over ranks of the
+    accumulated two-micro-batch gradient."""
+    torch.manual_seed(0)
+    base = nn.Sequential(nn.Linear(6, 12), nn.Tanh(), nn.Linear(12, 3))
+    state = {k: v.clone() for k, v in base.state_dict().items()}
+    W = 2
+    xs, ys = torch.randn(W, 2, 5, 6), torch.randn(W, 2, 5, 3)
+
+    def local_grads(rank, upto):
+        m = nn.Sequential(nn.Linear(6, 12), nn.Tanh(), nn.Linear(12, 3))
+        m.load_state_dict(state)
+        for k in range(upto):
+            ((m(xs[rank, k]) - ys[rank, k]) ** 2).mean().backward()
+        return [p.grad.clone() for p in m.parameters()]
+    want = [sum(g) / W for g in zip(*[local_grads(r, 2) for r in range(W)])]
+
+    def run(pg):
+        m = nn.Sequential(nn.Linear(6, 12), nn.Tanh(), nn.Linear(12, 3))
+        m.load_state_dict(state)
+        ddp = DistributedDataParallel(m, pg, bucket_size_mb=0.0001)
+        # an earlier synchronised step leaves reduced values in the bucket buffers
+        ((ddp(xs[pg.rank, 0]) - ys[pg.rank, 0]) ** 2).mean().backward()
+        ddp.finish_backward()
+        for p in m.parameters():
+            p.grad = None
+        with ddp.no_sync():
+            ((ddp(xs[pg.rank, 0]) - ys[pg.rank, 0]) ** 2).mean().backward()
+            ddp.finish_backward()
+        inside = [p.grad.clone() for p in m.parameters()]
+        ((ddp(xs[pg.rank, 1]) - ys[pg.rank, 1]) ** 2).mean().backward()
+        ddp.finish_backward()
+        return inside, [p.grad.clone() for p in m.parameters()]
+    outs = run_fake_world(W, run)
+    for r, (inside, after) in enumerate(outs):
+        for g, w in zip(inside, local_grads(r, 1)):
+            assert torch.allclose(g, w, atol=1e-6)
+        for g, w in zip(after, want):
+            assert torch.allclose(g, w, atol=1e-6)
+
+
+def test_ddp_first_step_with_unused_bucket_does_not_fail():
+    def run(pg):
+        torch.manual_seed(0)
+        used, unused = nn.Linear(4, 4), nn.Linear(4, 4)
+        m = nn.ModuleList([used, unused])
+        ddp = DistributedDataParallel(m, pg, bucket_size_mb=0.00001, find_unused_parameters=True)
+        used(torch.ones(2, 4) * (pg.rank + 1)).sum().backward()
+        ddp.finish_backward()
+        return used.weight.grad.clone(), [float(p.grad.abs().sum()) for p in unused.parameters()], ddp.unused_parameters()
+    outs = run_fake_world(2, run)
+    assert torch.allclose(outs[0][0], torch.full((4, 4), 3.0)) and outs[0][1] == [0.0, 0.0]
+
+
+def test_flat_grad_reducer_buckets_and_tied_parameter_counts():
+    from ml_framework_b200.parallel.ddp import FlatGradReducer
+    from ml_framework_b200.parallel.flat import FlatParams
+
+    def run(pg):
+        torch.manual_seed(0)
+        ps = [nn.Parameter(torch.zeros(40)), nn.Parameter(torch.zeros(24)), nn.Parameter(torch.zeros(64))]
+        flat = FlatParams(ps)
+        red = FlatGradReducer(flat, pg, bucket_size_mb=64 * 4 / 2 ** 20)
+        assert red.ranges == [(0, 64), (64, 128)]
+        for step in range(3):
+            flat.zero_grad()
+            for p in reversed(ps):
+                uses = 2 if p is ps[0] else 1             # a tied parameter reports once per use
+                for u in range(uses):
+                    if u == 0:
+                        p.main_grad.fill_(float(pg.rank + 1))
+                    else:
+                        p.main_grad.add_(float(pg.rank + 1))
+                    p._main_grad_started = True
+                    p.grad_ready(p)
+                    if step > 0 and p is ps[0] and u == 0:
+                        assert not red.launched[0]          # not before its second use
+            if step > 0:
+                assert red.launched == [True, True]
+            red.finish()
+            assert torch.allclose(ps[0].main_grad, torch.full((40,), 3.0))     # mean of 2 and 4
+            assert torch.allclose(ps[2].main_grad, torch.full((64,), 1.5))
+        return True
+    assert all(run_fake_world(2, run))
+
+
+def test_static_grad_scaler_through_the_grad_scaler_api():
+    from ml_framework_b200.amp.grad_scaler import GradScalerFactory
+    gs = GradScalerFactory.static(128.0)
+    p = nn.Parameter(torch.ones(3))
+    loss = gs.scale_loss((p * 2).sum())
+    loss.backward()
+    assert torch.allclose(p.grad, torch.full((3,), 256.0))
+    assert gs.prepare_gradients([p.grad]) and torch.allclose(p.grad, torch.full((3,), 2.0))
+    assert not gs.check_overflow([p.grad])
+
+    class Opt:
+        def step(self, **kw):
+            self.kw = kw
+    o = Opt()
+    gs.step(o)
+    assert set(o.kw) == {"inv_scale", "found_inf"}
+    gs.update()
+    assert gs.scale == 128.0
+    assert not gs.prepare_gradients([torch.tensor([float("nan")])])
+    gs.update()
+    assert gs.scaler.get_stats().skipped_steps == 1

@@ -24,6 +24,12 @@ def test_fsdp_fused_matches_nccl_two_ranks():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ddp_fused_bucket_all_reduce_matches_nccl_two_ranks():
+    r = _torchrun("ddp_worker.py", 2, 29749)
+    assert r.returncode == 0 and "DDP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_tensor_parallel_fused_matches_nccl_two_ranks():
     r = _torchrun("tp_worker.py", 2, 29743)
     assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -91,3 +91,54 @@ def test_gemm_with_piggybacked_copies_and_partial_sum():
     _lib.check(rc)
     want = part.float().sum(0) + bias.float() + res.float()
     assert torch.allclose(o.float(), want, atol=0.1, rtol=2e-2)
+
+
+def test_in_kernel_synchronised_reductions_single_rank():
+    """World of one: the arrival / departure handshakes run against this rank's own signal pad, so the
+    whole kernel (epoch bookkeeping included) is exercised on one GPU, several launches in a row."""
+    sm = SymmetricMemory()
+    n = 8 * 5000
+    buf = sm.alloc(n * 2)
+    flag = sm.alloc_flag()
+    fl = flag.view(torch.int32, 1)
+    x = torch.randn(n, device="cuda").to(torch.bfloat16)
+    for it in range(3):
+        buf.view(torch.bfloat16, n).copy_(x)
+        out = torch.zeros(n // 2, device="cuda", dtype=torch.bfloat16)
+        segs = make_reduce_segs([(n // 2, 0, n // 2)], "cuda")
+        sm.rs_reduce_sync(buf, segs, 1, out, n // 2, scale=0.5, flag=flag, key="t")
+        assert torch.allclose(out.float(), x[n // 2:].float() * 0.5, atol=1e-2, rtol=1e-2)
+        sm.all_reduce_two_shot_sync(buf, n, scale=0.25, flag=flag, key="t")
+        assert torch.allclose(buf.view(torch.bfloat16, n).float(), x.float() * 0.25, atol=1e-2, rtol=1e-2)
+        assert fl.item() == 0
+    buf.view(torch.bfloat16, n)[17] = float("nan")
+    sm.all_reduce_two_shot_sync(buf, n, flag=flag, key="t")
+    assert fl.item() == 1
+    sm.check_status()
+    sm.close()
+
+
+def test_wait_on_a_silent_peer_runs_out_and_raises_timeout():
+    """Emulated world of two on one GPU in which the "peer" never signals: with a small cycle budget the
+    barrier kernel gives up, leaves ERR_WAIT_PEER_FLAG in the status word, and the host turns that into
+    CommunicationTimeout; afterwards the context is intact and a barrier that is answered passes."""
+    from ml_framework_b200.dist.process_group import CommunicationTimeout
+    from ml_framework_b200.dist.symm import set_wait_budget_cycles
+    lib = _lib.get()
+    sm = SymmetricMemory(emulate_world=2)
+    pads = sm.alloc_emulated(1024)
+    set_wait_budget_cycles(2_000_000)
+    try:
+        _lib.check(lib.mlf_symm_barrier(pads[0].peer_table(), 0, 2, C.c_uint(1), C.c_uint64(_lib.stream_handle())))
+        with pytest.raises(CommunicationTimeout):
+            sm.check_status()
+        assert _lib.read_status(True) == 0
+        # the silent peer finally signals (written from the host side of the test), and the same wait passes
+        pads[0].view(torch.int32, 256)[32] = 2
+        _lib.check(lib.mlf_symm_barrier(pads[0].peer_table(), 0, 2, C.c_uint(2), C.c_uint64(_lib.stream_handle())))
+        sm.check_status()
+    finally:
+        set_wait_budget_cycles(0)
+    y = torch.ones(8, device="cuda") * 2
+    assert y.sum().item() == 16.0
+    sm.close()
