@@ -1,6 +1,10 @@
 """Plain PyTorch baseline of the GPT 1.3 B FSDP configuration: torch.nn modules, cuBLAS matmuls,
-SDPA (flash) attention, torch.distributed FSDP (NCCL) full-shard bf16, torch AdamW (fused) and
-torch's dynamic GradScaler (``ShardedGradScaler`` under FSDP). None of this repository's kernels or engine are on this path; it is the
+SDPA (flash) attention, torch.distributed FSDP (NCCL) full-shard bf16, torch AdamW (fused) with a
+dynamic loss scaler built from torch's own pieces: the overflow test is one ``_foreach_norm`` over the
+gradients (all-reduced under FSDP), the unscale and the skip-on-overflow happen inside the fused AdamW
+kernel through its ``grad_scale`` / ``found_inf`` inputs (the route ``torch.amp.GradScaler`` takes with
+fused optimizers; its own unscale kernel does not accept bf16 gradients), and the scale is updated on
+the device by ``torch._amp_update_scale_``. None of this repository's kernels or engine are on this path; it is the
 "torch.distributed NCCL + cuBLAS implementation of the identical config" the numbers are
 compared with.
 """
@@ -61,17 +65,20 @@ def build(cfg, dev, world, mb, S):
                      device_id=dev, use_orig_params=True,
                      mixed_precision=MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16))
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
-    if world > 1:
-        from torch.distributed.fsdp.sharded_grad_scaler import ShardedGradScaler
-        scaler = ShardedGradScaler(init_scale=65536.0)
-    else:
-        scaler = torch.amp.GradScaler("cuda", init_scale=65536.0)
+    scale = torch.full((), 65536.0, device=dev)
+    growth_tracker = torch.full((), 0, dtype=torch.int32, device=dev)
 
     def step(ids, tgt):
         opt.zero_grad(set_to_none=True)
         loss = model(ids, tgt)
-        scaler.scale(loss).backward()
-        scaler.step(opt)          # unscale + overflow check + skip-or-apply
-        scaler.update()
+        (loss * scale).backward()
+        grads = [p.grad for p in model.parameters() if p.grad is not None]
+        norms = torch.stack(torch._foreach_norm(grads)) if grads else torch.zeros(1, device=dev)
+        found_inf = (~torch.isfinite(norms.float().sum())).float()
+        if world > 1:
+            torch.distributed.all_reduce(found_inf, op=torch.distributed.ReduceOp.MAX)
+        opt.grad_scale, opt.found_inf = scale, found_inf      # fused AdamW unscales in-kernel and skips on overflow
+        opt.step()
+        torch._amp_update_scale_(scale, growth_tracker, found_inf, 2.0, 0.5, 2000)
         return loss.detach()
     return step, n_params

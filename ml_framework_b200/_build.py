@@ -98,7 +98,29 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
         os.replace(tmp, LIB_PATH)
+    DIGEST_PATH.write_text(_tree_digest())
     return LIB_PATH
+
+
+DIGEST_PATH = PKG_DIR / "libmlfb200.so.digest"
+
+
+def _tree_digest() -> str:
+    """Digest of every source and header under ``csrc/`` and of the compiler flags."""
+    h = hashlib.sha1()
+    for p in sorted(list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cpp")) + list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh"))):
+        h.update(str(p.relative_to(CSRC)).encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def stale() -> bool:
+    """True when the built library does not correspond to the sources under ``csrc/`` (by content, so that a copy
+    of the tree with fresh time stamps is not taken for a change)."""
+    if not LIB_PATH.exists() or not DIGEST_PATH.exists():
+        return True
+    return DIGEST_PATH.read_text().strip() != _tree_digest()
 
 
 def resource_report() -> str:

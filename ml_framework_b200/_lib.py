@@ -85,8 +85,12 @@ def get() -> C.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
+        from . import _build
         if not _LIB_PATH.exists() or os.environ.get("MLF_REBUILD") == "1":
-            from . import _build
+            _build.build(force=os.environ.get("MLF_REBUILD") == "1")
+        elif _build.stale():
+            # a source or header is newer than the library: a stale library would be called with the
+            # new argument lists, so rebuild when a compiler is at hand and refuse to load otherwise
             _build.build()
         lib = C.CDLL(str(_LIB_PATH))
         lib.mlf_last_error.restype = C.c_char_p

@@ -17,6 +17,8 @@
 // bucket all-reduce (src/MLFramework/Distributed/GradientBucket.cs:112-126), algorithm choice by
 // message size (src/MLFramework/Communication/Optimizations/AlgorithmSelector.cs:24-65). On
 // NVSwitch ring / tree schedules bring nothing: small messages go one-shot, large ones two-shot.
+#include <float.h>
+
 #include "../common/host.h"
 #include "../common/ptx.cuh"
 #include "../mlf_api.h"
@@ -407,6 +409,130 @@ argmax_combine_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, int worl
   sync_leave(st, e);
 }
 
+// ------------------------------------------------------------------------------------------
+// Cross-entropy over a vocabulary split across ranks (tensor-parallel LM head). Each rank holds the
+// logits of its own vocabulary columns [T, Vl] (global columns lo .. lo + Vl). Step 1 reduces every
+// row to three numbers (local maximum, sum of exponentials against it, the target's logit when the
+// target is one of this rank's columns) in this rank's statistics buffer; step 2 combines the W
+// statistics of a row, writes the row's loss and overwrites the local logits with
+// d loss / d logits * gscale. With do_sync the statistics buffers are peer-mapped and step 2 waits
+// inside the kernel until every rank has finished step 1; otherwise stats.p[r] are local copies
+// (after a process-group all-gather, or W = 1).
+// ------------------------------------------------------------------------------------------
+struct VpStat {
+  float mx, se, tl, pad;
+};
+
+__global__ void __launch_bounds__(256)
+vp_ce_stats_kernel(const __nv_bfloat16* logits, long long ld, const long long* targets, int T, int valid_cols, long long lo,
+                   VpStat* stats, int* err) {
+  __shared__ float red_a[8], red_b[8];
+  const int nvec = valid_cols / 8;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const __nv_bfloat16* row = logits + (long long)t * ld;
+    float mx = -FLT_MAX, se = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 u = reinterpret_cast<const uint4*>(row)[i];
+      float f[8];
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+      float lm = f[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+      if (lm > mx) { se *= __expf(mx - lm); mx = lm; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+    }
+    for (int i = nvec * 8 + threadIdx.x; i < valid_cols; i += blockDim.x) {
+      const float f = __bfloat162float(row[i]);
+      if (f > mx) { se *= __expf(mx - f); mx = f; }
+      se += __expf(f - mx);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, mx, o), os = __shfl_xor_sync(0xffffffffu, se, o);
+      const float nm = fmaxf(mx, om);
+      se = se * __expf(mx - nm) + os * __expf(om - nm);
+      mx = nm;
+    }
+    const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();      // red_* of the previous row are consumed
+    if ((threadIdx.x & 31) == 0) { red_a[w] = mx; red_b[w] = se; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float gm = red_a[0], gsum = red_b[0];
+      for (int k = 1; k < nw; ++k) {
+        const float nm = fmaxf(gm, red_a[k]);
+        gsum = gsum * __expf(gm - nm) + red_b[k] * __expf(red_a[k] - nm);
+        gm = nm;
+      }
+      const long long tg = targets[t] - lo;
+      VpStat st;
+      st.mx = gm; st.se = gsum; st.pad = 0.f;
+      st.tl = (targets[t] >= 0 && tg >= 0 && tg < valid_cols) ? __bfloat162float(row[tg]) : 0.f;
+      *reinterpret_cast<float4*>(stats + t) = *reinterpret_cast<float4*>(&st);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+vp_ce_grad_kernel(__nv_bfloat16* logits, long long ld, int Vl, const long long* targets, int T, int valid_cols, long long lo, long long vocab,
+                  PeerPtrs stats, PeerPtrs pads, SyncState* st, int world, int rank, int do_sync, float* loss_rows, float* loss_sum,
+                  float gscale, const float* gscale_ptr, float loss_weight, int* err) {
+  uint32_t e = 0;
+  if (do_sync) e = sync_enter(pads, st, rank, world, err);
+  __shared__ float s_gm, s_inv, s_ignore;
+  const float gs = gscale * (gscale_ptr ? *gscale_ptr : 1.f);
+  const int nvec = Vl / 8;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long long tgt = targets[t];
+    if (threadIdx.x == 0) {
+      float gm = -FLT_MAX, gsum = 0.f, tl = 0.f;
+      for (int r = 0; r < world; ++r) {
+        const float4 v = *reinterpret_cast<const float4*>(static_cast<const VpStat*>(stats.p[r]) + t);
+        const float nm = fmaxf(gm, v.x);
+        gsum = gsum * __expf(gm - nm) + v.y * __expf(v.x - nm);
+        gm = nm;
+        tl += v.z;
+      }
+      const bool ignore = tgt < 0;
+      if (!ignore && tgt >= vocab) atomicCAS(err, 0, ERR_BAD_INDEX);
+      const float l = (ignore || tgt >= vocab) ? 0.f : gm + __logf(gsum) - tl;
+      if (loss_rows) loss_rows[t] = l;
+      if (loss_sum) atomicAdd(loss_sum, l * loss_weight);
+      s_gm = gm; s_inv = 1.f / gsum; s_ignore = ignore ? 1.f : 0.f;
+    }
+    __syncthreads();
+    const float gm = s_gm, inv = s_inv;
+    const bool ignore = s_ignore != 0.f;
+    const long long tl_col = tgt - lo;
+    __nv_bfloat16* row = logits + (long long)t * ld;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 u = reinterpret_cast<const uint4*>(row)[i];
+      float f[8];
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int col = i * 8 + j;
+        float g = (ignore || col >= valid_cols) ? 0.f : __expf(f[j] - gm) * inv;
+        if (!ignore && (long long)col == tl_col) g -= 1.f;
+        f[j] = g * gs;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]); o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+      reinterpret_cast<uint4*>(row)[i] = o;
+    }
+    for (int col = nvec * 8 + threadIdx.x; col < Vl; col += blockDim.x) {
+      float g = (ignore || col >= valid_cols) ? 0.f : __expf(__bfloat162float(row[col]) - gm) * inv;
+      if (!ignore && (long long)col == tl_col) g -= 1.f;
+      row[col] = __float2bfloat16(g * gs);
+    }
+    __syncthreads();      // s_* are rewritten for the next row
+  }
+  if (do_sync) sync_leave_all(pads, st, rank, world, e, err);
+}
+
 // out[row, :] = sum_w partial[w, row, :] (+ bias) (+ residual): the second half of GEMM->reduce-
 // scatter, where peers have stored their partial tiles into this rank's [W, rows, cols] buffer.
 __global__ void __launch_bounds__(256)
@@ -638,6 +764,63 @@ MLF_API int mlf_tp_argmax(const void* logits, long long rows, long long ld, int 
   count_launch();
   argmax_combine_sync_kernel<<<1, 256, 0, st>>>(to_peers(bufs, world), to_peers(pads, world), static_cast<SyncState*>(state), world, rank,
                                                 rows, out, device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Vocabulary-parallel cross-entropy (see the kernels above). logits [T, ld] bf16 hold this rank's Vl columns of the
+// vocabulary starting at global column lo; they are overwritten with the gradient. stats[r]: rank r's statistics
+// buffer (16 bytes per row); with do_sync != 0 these are peer-mapped and pads / state are a signal pad and its device
+// epoch. loss_sum must be zeroed by the caller.
+MLF_API int mlf_vp_cross_entropy(void* logits, long long ld, int Vl, const long long* targets, int T, long long lo, long long vocab,
+                                 void* const* stats, void* const* pads, void* state, int world, int rank, int do_sync, float* loss_rows,
+                                 float* loss_sum, float gscale, const float* gscale_ptr, float loss_weight, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world && T > 0 && Vl > 0, "vp_cross_entropy: bad arguments");
+  MLF_REQUIRE(ld % 8 == 0 && Vl <= ld && (reinterpret_cast<uintptr_t>(logits) & 15) == 0, "vp_cross_entropy: rows must be 16-byte aligned");
+  MLF_REQUIRE(!do_sync || (pads != nullptr && state != nullptr), "vp_cross_entropy: synchronised form needs pads and state");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  long long vc = vocab - lo;
+  const int valid_cols = (int)(vc < 0 ? 0 : (vc > Vl ? Vl : vc));
+  const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
+  vp_ce_stats_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, targets, T, valid_cols, lo,
+                                           static_cast<VpStat*>(stats[rank]), device_status_word());
+  count_launch();
+  // the synchronised form keeps its grid within one wave so that every CTA's wait on the peers ends together
+  const int grid2 = do_sync ? (T < sm_count() * 4 ? T : sm_count() * 4) : grid;
+  vp_ce_grad_kernel<<<grid2, 256, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ld, Vl, targets, T, valid_cols, lo, vocab,
+                                           to_peers(stats, world), pads ? to_peers(pads, world) : PeerPtrs{}, static_cast<SyncState*>(state),
+                                           world, rank, do_sync, loss_rows, loss_sum, gscale, gscale_ptr, loss_weight, device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// The two steps of mlf_vp_cross_entropy as separate calls, for callers that exchange the statistics themselves
+// (a process-group all-gather between the two).
+MLF_API int mlf_vp_ce_stats(const void* logits, long long ld, int Vl, const long long* targets, int T, long long lo, long long vocab,
+                            void* stats, uint64_t stream) {
+  MLF_REQUIRE(T > 0 && Vl > 0 && ld % 8 == 0 && Vl <= ld && stats != nullptr, "vp_ce_stats: bad arguments");
+  long long vc = vocab - lo;
+  const int valid_cols = (int)(vc < 0 ? 0 : (vc > Vl ? Vl : vc));
+  const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
+  vp_ce_stats_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(logits), ld, targets, T,
+                                                                              valid_cols, lo, static_cast<VpStat*>(stats),
+                                                                              device_status_word());
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+MLF_API int mlf_vp_ce_grad(void* logits, long long ld, int Vl, const long long* targets, int T, long long lo, long long vocab,
+                           void* const* stats, void* const* pads, void* state, int world, int rank, int do_sync, float* loss_rows,
+                           float* loss_sum, float gscale, const float* gscale_ptr, float loss_weight, uint64_t stream) {
+  MLF_REQUIRE(world >= 1 && world <= 8 && T > 0 && Vl > 0 && ld % 8 == 0 && Vl <= ld && do_sync == 0, "vp_ce_grad: bad arguments");
+  long long vc = vocab - lo;
+  const int valid_cols = (int)(vc < 0 ? 0 : (vc > Vl ? Vl : vc));
+  const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
+  vp_ce_grad_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(logits), ld, Vl, targets, T, valid_cols, lo, vocab, to_peers(stats, world), PeerPtrs{}, nullptr, world, rank,
+      0, loss_rows, loss_sum, gscale, gscale_ptr, loss_weight, device_status_word());
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -70,10 +70,11 @@ class LlamaTP(nn.Module):
     def __init__(self, cfg: LlamaConfig, tp: TPContext, sequence_parallel: bool = True, dtype=None, device=None):
         super().__init__()
         self.cfg, self.tp, self.sp = cfg, tp, sequence_parallel
-        self.embed = VocabParallelEmbedding(cfg.padded_vocab, cfg.d_model, tp, dtype, device, cfg.init_std)
+        self.embed = VocabParallelEmbedding(cfg.padded_vocab, cfg.d_model, tp, dtype, device, cfg.init_std,
+                                            local_multiple=128 if tp.world > 1 else 1)
         self.blocks = nn.ModuleList([LlamaBlockTP(cfg, tp, sequence_parallel, dtype, device, i) for i in range(cfg.n_layers)])
         self.norm_f = RMSNorm(cfg.d_model, cfg.norm_eps, dtype, device)
-        Vl = self.embed.local_v
+        Vl = self.embed.local_v        # whole 128-column tiles per rank; columns past the vocabulary are masked in the loss
         self.lm_head = nn.Parameter(torch.empty(Vl, cfg.d_model, dtype=dtype, device=device).normal_(0, cfg.init_std))
 
     def replicated_parameters(self):
@@ -83,38 +84,32 @@ class LlamaTP(nn.Module):
 
     def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None, loss_scale=None):
         B, S = ids.shape
-        x = self.embed(ids).reshape(B * S, -1)
-        if self.sp and self.tp.world > 1:
-            x = x.chunk(self.tp.world, dim=0)[self.tp.rank].contiguous()
-            x = _ScaleGradForSP.apply(x, self.tp)
+        sp = self.sp and self.tp.world > 1
+        x = self.embed(ids, sequence_parallel=sp).reshape(-1, self.cfg.d_model)     # [T, d], or the token shard [T/W, d]
         for blk in self.blocks:
             x = blk(x, B, S)
         x = self.norm_f(x)
-        if self.sp and self.tp.world > 1:
-            x = gather_tokens(x, self.tp)
         if targets is None:
-            return x
-        return vocab_parallel_lm_loss(x, self.lm_head, targets, self.tp, self.cfg.vocab_size, loss_scale)
+            return gather_tokens(x, self.tp) if sp else x
+        return vocab_parallel_lm_loss(x, self.lm_head, targets, self.tp, self.cfg.vocab_size, loss_scale,
+                                      sequence_parallel=sp, key="lm_head")
 
     def sync_replicated_grads(self):
-        """Sum gradients of replicated parameters over the TP group (sequence-parallel mode)."""
+        """Sum gradients of replicated parameters over the TP group (sequence-parallel mode): each rank saw its token
+        shard only. One all-reduce over the concatenated gradients instead of one per norm."""
         if not (self.sp and self.tp.world > 1):
             return
         from ..dist.process_group import ReduceOp
+        gs = []
         for p in self.replicated_parameters():
             g = getattr(p, "main_grad", None) if getattr(p, "_main_grad_started", False) else p.grad
             if g is not None:
-                self.tp.pg.all_reduce(g, ReduceOp.SUM)
-
-
-class _ScaleGradForSP(torch.autograd.Function):
-    """Token-shard slice of a replicated tensor: backward all-gathers the shard gradients."""
-
-    @staticmethod
-    def forward(ctx, x, tp):
-        ctx.tp = tp
-        return x.view_as(x)
-
-    @staticmethod
-    def backward(ctx, g):
-        return g, None
+                gs.append(g)
+        if not gs:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in gs])
+        self.tp.pg.all_reduce(flat, ReduceOp.SUM)
+        off = 0
+        for g in gs:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()

@@ -148,7 +148,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         # The epilogue's stores are sized from M, N and the pitch: anything else would be written past its end.
         scatter = comm is not None and bool(comm.scatter_out)
         want = (int(comm.rows_per_owner) if scatter else M, out_cols)      # routed rows land in the owners' partial buffers
-        if out.dim() != 2 or tuple(out.shape) != want:
+        if out.dim() != 2 or out.shape[1] != want[1] or (out.shape[0] < want[0] if scatter else out.shape[0] != want[0]):
             raise ValueError(f"out has shape {tuple(out.shape)}, the product needs {want}")
         if out.dtype != out_dtype:
             raise ValueError(f"out is {out.dtype}, the epilogue writes {out_dtype}")

@@ -156,8 +156,10 @@ def scatter_tokens(x, tp): return _ScatterTokens.apply(x, tp)
 
 
 # ------------------------------------------------------------------ fused kernels (GPU, peer memory)
-def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: str, bias=None, flags=0, aux_out=None):
-    """out[T, N] = all_gather_tokens(x_shard)[T, K] @ w[N, K]^T in one kernel. Returns (out, x_full)."""
+def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: str, bias=None, flags=0, aux_out=None,
+                   b_mn: bool = False):
+    """out[T, N] = all_gather_tokens(x_shard)[T, K] @ B in one kernel, B = w[N, K]^T or, with ``b_mn``, w[K, N].
+    Returns (out, x_full)."""
     rows, K = x_shard.shape
     W, T = tp.world, x_shard.shape[0] * tp.world
     stage = tp.symm_buffer(key + ".ag_stage", rows * K * 2)
@@ -176,7 +178,7 @@ def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: s
     for r in range(W):
         cm.src[r] = stage.ptrs[r]
     cm.gathered, cm.flags, cm.counters = x_full.data_ptr(), fl.data_ptr(), fl[nfl:].data_ptr()
-    out = gemm(x_shard, w, comm=cm, m_override=T, bias=bias, flags=flags, aux_out=aux_out)
+    out = gemm(x_shard, w, comm=cm, m_override=T, bias=bias, flags=flags, aux_out=aux_out, b_mn=b_mn)
     return out, x_full
 
 
@@ -242,13 +244,12 @@ class _RowSPFused(torch.autograd.Function):
         dy_shard = dy_shard.contiguous()
         # dX[T, in/W] = all_gather(dY)[T, out] @ W[out, in/W]  (W read as [K=out, N=in/W])
         tp = ctx.tp
-        rows = dy_shard.shape[0]
-        dy_full = tp.pg.all_gather(dy_shard, dim=0) if not tp.fused else None
-        if dy_full is None:
-            # fused gather of dY needs a K-major B operand; W is MN-major here, so gather with the
-            # copy kernel path of ag_gemm and run the dgrad on the gathered buffer.
-            _, dy_full = _fused_ag_gemm_only(tp, dy_shard, ctx.key + ".bwd")
-        dx = gemm(dy_full, w, b_mn=True)
+        if tp.fused:
+            # the gathered operand (dY rows) is K-major; W is read as [K = out, N = in/W] (MN-major B)
+            dx, dy_full = _fused_ag_gemm(tp, dy_shard, w, ctx.key + ".bwd", b_mn=True)
+        else:
+            dy_full = tp.pg.all_gather(dy_shard, dim=0)
+            dx = gemm(dy_full, w, b_mn=True)
         dw = Fm._wgrad(dy_full, x, w)
         db = None
         if ctx.b is not None:
@@ -415,74 +416,143 @@ class TPMLP(nn.Module):
 
 
 # ------------------------------------------------------------------ vocabulary-parallel head
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+def local_vocab(vocab: int, world: int, multiple: int = 1) -> int:
+    """Vocabulary rows held by one rank: ceil(vocab / W), rounded up to ``multiple`` (128 gives whole GEMM tiles)."""
+    return _round_up((vocab + world - 1) // world, multiple)
+
+
 class _VocabParallelCE(torch.autograd.Function):
+    """Mean token cross-entropy from this rank's columns of the logits. Only three numbers per row cross
+    the ranks (row maximum, sum of exponentials, the target's logit); full logits never do. On the GPU
+    two kernels do the work (``mlf_vp_cross_entropy``): per-row statistics into a buffer the peers can
+    read, then - after waiting inside the kernel for every rank's statistics - the loss and, in place
+    of the logits, d loss / d logits times the loss scale. The upstream gradient is taken to be 1."""
+
     @staticmethod
-    def forward(ctx, h, w_shard, targets, tp, vocab, loss_scale):
-        Vl = w_shard.shape[0]
+    def forward(ctx, logits, targets, tp, vocab, loss_scale):
+        T, Vl = logits.shape
         lo = tp.rank * Vl
-        logits = F.linear(h, w_shard).float()
+        t = targets.reshape(-1)
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
+            import ctypes as C
+            W = tp.world
+            loss_sum = torch.zeros((), dtype=torch.float32, device=logits.device)
+            pads = state = None
+            if tp.fused and W > 1:
+                buf = tp.symm_buffer("vpce.stats", T * 16)
+                table = buf.peer_table()
+                pad = tp.symm._sync_pad("main")
+                pads, state, sync = pad.peer_table(), C.c_void_p(pad.ptrs[tp.rank] + 1024), 1
+                keep = buf
+            elif W > 1:
+                mine = torch.empty(T, 4, dtype=torch.float32, device=logits.device)
+                table = (C.c_void_p * 8)(*([C.c_void_p(mine.data_ptr())] * W + [None] * (8 - W)))
+                keep, sync = mine, -1          # statistics first, exchange through the process group, then the gradient
+            else:
+                mine = torch.empty(T, 4, dtype=torch.float32, device=logits.device)
+                table = (C.c_void_p * 8)(C.c_void_p(mine.data_ptr()), *([None] * 7))
+                keep, sync = mine, 0
+            lib = _lib.get()
+            args = lambda tb, mode: (C.c_void_p(logits.data_ptr()), C.c_longlong(logits.stride(0)), Vl, C.c_void_p(t.data_ptr()), T,  # noqa: E731
+                                     C.c_longlong(lo), C.c_longlong(vocab), tb, pads, state, W, tp.rank, mode, None,
+                                     C.c_void_p(loss_sum.data_ptr()), C.c_float(1.0 / T),
+                                     C.c_void_p(loss_scale.data_ptr()) if loss_scale is not None else None, C.c_float(1.0 / T),
+                                     C.c_uint64(_lib.stream_handle()))
+            if sync == -1:
+                _lib.check(lib.mlf_vp_ce_stats(C.c_void_p(logits.data_ptr()), C.c_longlong(logits.stride(0)), Vl, C.c_void_p(t.data_ptr()), T,
+                                               C.c_longlong(lo), C.c_longlong(vocab), C.c_void_p(mine.data_ptr()),
+                                               C.c_uint64(_lib.stream_handle())), "mlf_vp_ce_stats")
+                allst = tp.pg.all_gather(mine, dim=0).contiguous()           # [W * T, 4]
+                table = (C.c_void_p * 8)(*[C.c_void_p(allst.data_ptr() + r * T * 16) for r in range(W)] + [None] * (8 - W))
+                keep = allst
+                _lib.check(lib.mlf_vp_ce_grad(*args(table, 0)), "mlf_vp_ce_grad")
+            else:
+                _lib.check(lib.mlf_vp_cross_entropy(*args(table, sync)), "mlf_vp_cross_entropy")
+            ctx.keep = keep
+            ctx.save_for_backward(logits)
+            return loss_sum
+        lg = logits.float()
         valid_cols = max(0, min(Vl, vocab - lo))
         if valid_cols < Vl:
-            logits[:, valid_cols:] = float("-inf")
-        mx = logits.max(dim=-1).values
+            lg = lg.clone()
+            lg[:, valid_cols:] = float("-inf")
+        mx = lg.max(dim=-1).values if valid_cols > 0 else torch.full((T,), -3.0e38)
         if tp.world > 1:
             tp.pg.all_reduce(mx, ReduceOp.MAX)
-        ex = torch.exp(logits - mx[:, None])
+        ex = torch.exp(lg - mx[:, None])
         se = ex.sum(-1)
-        t = targets.reshape(-1)
-        mine = (t >= lo) & (t < lo + Vl)
+        mine = (t >= lo) & (t < lo + valid_cols)
         tl = torch.zeros_like(mx)
         idx = (t - lo).clamp(0, Vl - 1)
-        tl[mine] = logits[torch.arange(len(t), device=t.device)[mine], idx[mine]]
+        rows = torch.arange(len(t), device=t.device)
+        tl[mine] = lg[rows[mine], idx[mine]]
         if tp.world > 1:
             tp.pg.all_reduce(se, ReduceOp.SUM)
             tp.pg.all_reduce(tl, ReduceOp.SUM)
-        loss = (torch.log(se) + mx - tl).sum() / t.numel()
+        keep_row = (t >= 0).to(lg.dtype)
+        loss = ((torch.log(se) + mx - tl) * keep_row).sum() / t.numel()
         p = ex / se[:, None]
-        p[torch.arange(len(t), device=t.device)[mine], idx[mine]] -= 1.0
-        scale = 1.0 / t.numel()
-        dlogits = (p * scale).to(h.dtype)
+        p[rows[mine], idx[mine]] -= 1.0
+        dlogits = (p * keep_row[:, None] * (1.0 / t.numel())).to(logits.dtype)
         if loss_scale is not None:
             dlogits = dlogits * loss_scale.to(dlogits.dtype)
-        ctx.save_for_backward(h, w_shard, dlogits)
-        ctx.tp = tp
+        ctx.save_for_backward(dlogits)
         return loss
 
     @staticmethod
     def backward(ctx, g):
-        h, w, dl = ctx.saved_tensors
-        if Fm._native(h, w):
-            dh = gemm(dl, w, b_mn=True)
-            dw = Fm._wgrad(dl, h, w)
+        (dl,) = ctx.saved_tensors
+        return dl, None, None, None, None
+
+
+def vocab_parallel_cross_entropy(logits, targets, tp: TPContext, vocab: int, loss_scale=None):
+    """Loss from vocabulary-parallel logits ``[T, Vl]`` (this rank's global columns ``rank * Vl ...``). On the GPU
+    the logits' storage is overwritten with their gradient."""
+    return _VocabParallelCE.apply(logits, targets, tp, vocab, loss_scale)
+
+
+def vocab_parallel_lm_loss(h, w_shard, targets, tp: TPContext, vocab: int, loss_scale=None, sequence_parallel: bool = False,
+                           key: str = "lm_head"):
+    """Cross-entropy with the LM head split over the vocabulary. ``h`` is ``[T, d]`` replicated over the ranks, or with
+    ``sequence_parallel`` this rank's token shard ``[T/W, d]``: the head is then a sequence-parallel column linear
+    (all-gather -> GEMM forward, GEMM -> reduce-scatter backward; one kernel each on the fused path), which is what
+    sums the W partial gradients of ``h`` - no further all-reduce."""
+    h2 = h.reshape(-1, h.shape[-1])
+    if sequence_parallel and tp.world > 1:
+        if tp.fused and Fm._native(h2, w_shard):
+            logits = _ColumnSPFused.apply(h2, w_shard, None, tp, key)
         else:
-            dh = dl.float() @ w.float()
-            dw = (dl.float().t() @ h.float()).to(w.dtype)
-            dh = dh.to(h.dtype)
-        if ctx.tp.world > 1:
-            ctx.tp.pg.all_reduce(dh, ReduceOp.SUM)
-        return dh, dw, None, None, None, None
-
-
-def vocab_parallel_lm_loss(h, w_shard, targets, tp: TPContext, vocab: int, loss_scale=None):
-    """Cross-entropy with the LM head split over the vocabulary: only three small all-reduces
-    (row max, sum of exponentials, target logit) cross the ranks; full logits never do."""
-    return _VocabParallelCE.apply(h.reshape(-1, h.shape[-1]), w_shard, targets, tp, vocab, loss_scale)
+            logits = Fm.linear(gather_tokens(h2, tp), w_shard)
+    else:
+        logits = Fm.linear(copy_to_tp_region(h2, tp), w_shard)
+    return vocab_parallel_cross_entropy(logits, targets, tp, vocab, loss_scale)
 
 
 class VocabParallelEmbedding(nn.Module):
-    def __init__(self, vocab: int, dim: int, tp: Optional[TPContext] = None, dtype=None, device=None, init_std=0.02):
+    """Embedding table split over the vocabulary: every rank looks up the ids it owns (zeros for the others) and the
+    partial results are summed over the ranks - an all-reduce, or with ``sequence_parallel`` a reduce-scatter over
+    tokens (its backward all-gathers the token-shard gradients, so every rank's rows see every token)."""
+
+    def __init__(self, vocab: int, dim: int, tp: Optional[TPContext] = None, dtype=None, device=None, init_std=0.02,
+                 local_multiple: int = 1):
         super().__init__()
         self.tp = tp or get_context()
         W = self.tp.world
         self.vocab = vocab
-        self.local_v = (vocab + W - 1) // W
+        self.local_v = local_vocab(vocab, W, local_multiple)
         self.lo = self.tp.rank * self.local_v
         self.weight = nn.Parameter(torch.empty(self.local_v, dim, dtype=dtype, device=device).normal_(0, init_std))
 
-    def forward(self, ids):
+    def forward(self, ids, sequence_parallel: bool = False):
         mask = (ids >= self.lo) & (ids < self.lo + self.local_v)
         local = (ids - self.lo).clamp(0, self.local_v - 1)
         out = F.embedding(local, self.weight) * mask[..., None].to(self.weight.dtype)
+        if sequence_parallel and self.tp.world > 1:
+            return scatter_tokens(out.reshape(-1, out.shape[-1]), self.tp)
         return reduce_from_tp_region(out, self.tp)
 
 

@@ -131,3 +131,42 @@ def test_converter_and_analyzer():
         return m(x)
     for y in run_fake_world(2, run):
         assert torch.allclose(y, want, atol=1e-5)
+
+
+def test_llama_tp_sequence_parallel_matches_plain_tensor_parallel():
+    """Same weight shards, same batch: the sequence-parallel model (token-sharded residual stream, reduce-scatter /
+    all-gather pairs, head fed from token shards) must give the loss and every gradient of the plain tensor-parallel
+    model (replicated activations, all-reduces). Norm scales see token shards under SP: their gradients match after
+    the sum over the group."""
+    from ml_framework_b200.models.llama import LlamaConfig
+    from ml_framework_b200.models.llama_tp import LlamaTP
+    cfg = LlamaConfig(n_layers=2, d_model=32, n_heads=4, n_kv_heads=2, head_dim=8, d_ff=64, vocab_size=50, max_seq=16)
+    W = 2
+    ids = torch.randint(0, 50, (2, 8), generator=torch.Generator().manual_seed(5))
+    tgt = torch.randint(0, 50, (2, 8), generator=torch.Generator().manual_seed(6))
+
+    def run(pg):
+        out = {}
+        for sp in (False, True):
+            tp = tpm.TPContext(pg, None, fused=False)
+            m = LlamaTP(cfg, tp, sequence_parallel=sp, dtype=torch.float32)
+            # ranks are threads here and share torch's global generator: fill the shards from per-rank generators
+            g = torch.Generator().manual_seed(10 + pg.rank)
+            gr = torch.Generator().manual_seed(99)
+            rep = {id(p) for p in m.replicated_parameters()}
+            with torch.no_grad():
+                for p in m.parameters():
+                    if id(p) in rep:
+                        p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=gr))
+                    else:
+                        p.copy_(0.08 * torch.randn(p.shape, generator=g))
+            loss = m(ids, tgt)
+            loss.backward()
+            m.sync_replicated_grads()
+            out[sp] = (loss.item(), {n: p.grad.clone() for n, p in m.named_parameters()})
+        return out
+    for res in run_fake_world(W, run):
+        (l0, g0), (l1, g1) = res[False], res[True]
+        assert abs(l0 - l1) < 1e-5
+        for n in g0:
+            assert torch.allclose(g0[n], g1[n], atol=2e-5, rtol=1e-4), (n, (g0[n] - g1[n]).abs().max())
