@@ -248,6 +248,13 @@ __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32
 struct CopyCursor {
   int i;            // chunk iteration (rotated order)
   long long off;    // byte offset inside this CTA's slice of the chunk
+  // slice of chunk iteration `cached_i` for this CTA, kept in registers: the segment table is read and
+  // the slice bounds are divided out once per chunk, not once per piece
+  int cached_i;
+  int c;
+  const char* src;
+  char* dst;
+  long long lo, hi;
 };
 
 struct CopyPiece {
@@ -294,18 +301,17 @@ __device__ __forceinline__ CopyPiece next_piece(const GemmKernelParams& p, int n
   CopyPiece pc;
   pc.valid = false;
   if (cur.i >= n_flags + p.n_extra) return pc;
-  int c;
-  const char* src;
-  char* dst;
-  long long lo, hi;
-  chunk_slice(p, n_flags, first_local, cur.i, cta, c, src, dst, lo, hi);
-  const long long pos = lo + cur.off;
-  const long long remain = hi - pos;
+  if (cur.cached_i != cur.i) {
+    chunk_slice(p, n_flags, first_local, cur.i, cta, cur.c, cur.src, cur.dst, cur.lo, cur.hi);
+    cur.cached_i = cur.i;
+  }
+  const long long pos = cur.lo + cur.off;
+  const long long remain = cur.hi - pos;
   pc.valid = true;
-  pc.chunk = c;
+  pc.chunk = cur.c;
   pc.bytes = (uint32_t)(remain > kCopyPiece ? kCopyPiece : (remain > 0 ? remain : 0));
-  pc.src = src + pos;
-  pc.dst = dst + pos;
+  pc.src = cur.src + pos;
+  pc.dst = cur.dst + pos;
   pc.last_of_chunk = remain <= kCopyPiece;
   if (pc.last_of_chunk) {
     cur.i += 1;
@@ -314,6 +320,22 @@ __device__ __forceinline__ CopyPiece next_piece(const GemmKernelParams& p, int n
     cur.off += kCopyPiece;
   }
   return pc;
+}
+
+// A gated chunk is published (its completion counter bumped, the ready flag set by the last copy CTA)
+// once the stores of its last piece are complete. Waiting for that right away would drain the store
+// pipeline at every chunk; instead the chunk is queued and published kCopySignalLag pieces later,
+// when `cp.async.bulk.wait_group kCopySignalLag` guarantees that its group has completed.
+constexpr int kCopySignalLag = 3;
+
+__device__ __forceinline__ void publish_chunk(const GemmKernelParams& p, int chunk) {
+  fence_proxy_async_all();
+  __threadfence();
+  const uint32_t old = atomicAdd(&p.counters[chunk], 1u);
+  if (old + 1 == (uint32_t)p.n_copy_ctas) {
+    __threadfence();
+    st_release_gpu(&p.flags_ready[chunk], 1u);
+  }
 }
 
 __device__ inline void gather_copy_role(const GemmKernelParams& p) {
@@ -329,8 +351,11 @@ __device__ inline void gather_copy_role(const GemmKernelParams& p) {
   const int n_flags = p.gather_operand != 0 ? (p.total_rows + p.flag_rows - 1) / p.flag_rows : 0;
   const int first_local = p.gather_operand != 0 ? (p.rank * p.rows_per_rank) / p.flag_rows : 0;
   const int cta = blockIdx.x;
-  CopyCursor lc{0, 0}, sc{0, 0};
+  CopyCursor lc{0, 0, -1, 0, nullptr, nullptr, 0, 0}, sc{0, 0, -1, 0, nullptr, nullptr, 0, 0};
   int issued = 0;  // pieces whose load has been issued
+  // pending publications: chunk id and the piece index whose commit closed the chunk
+  int pend_chunk[8], pend_seq[8];
+  int pend_head = 0, pend_tail = 0;
   // prologue: fill the lookahead window
   for (; issued < kCopyLookahead; ++issued) {
     CopyPiece pc = next_piece(p, n_flags, first_local, cta, lc);
@@ -350,15 +375,17 @@ __device__ inline void gather_copy_role(const GemmKernelParams& p) {
     const uint32_t ph = (i / kCopyBufs) & 1;
     if (!mbar_wait(bar0 + 8u * slot, ph, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG)) break;
     if (pc.bytes) bulk_store(pc.dst, base + slot * kCopyPiece, pc.bytes);
-    tma_store_commit();
+    tma_store_commit();               // group i
     if (pc.last_of_chunk && pc.chunk >= 0) {
-      tma_store_wait_all<0>();
-      fence_proxy_async_all();
-      __threadfence();
-      const uint32_t old = atomicAdd(&p.counters[pc.chunk], 1u);
-      if (old + 1 == (uint32_t)p.n_copy_ctas) {
-        __threadfence();
-        st_release_gpu(&p.flags_ready[pc.chunk], 1u);
+      pend_chunk[pend_tail & 7] = pc.chunk;
+      pend_seq[pend_tail & 7] = i;
+      ++pend_tail;
+    }
+    if (pend_head != pend_tail && i - pend_seq[pend_head & 7] >= kCopySignalLag) {
+      tma_store_wait_all<kCopySignalLag>();     // every group up to i - kCopySignalLag is complete
+      while (pend_head != pend_tail && i - pend_seq[pend_head & 7] >= kCopySignalLag) {
+        publish_chunk(p, pend_chunk[pend_head & 7]);
+        ++pend_head;
       }
     }
     // keep the window full: the slot about to be reused was read by the store issued
@@ -377,6 +404,10 @@ __device__ inline void gather_copy_role(const GemmKernelParams& p) {
     }
   }
   tma_store_wait_all<0>();
+  while (pend_head != pend_tail) {
+    publish_chunk(p, pend_chunk[pend_head & 7]);
+    ++pend_head;
+  }
 }
 
 

@@ -57,48 +57,80 @@ struct ReduceSeg {
 
 // out[dst_off + i] = scale * sum_r bufs[r][src_off + i]   (bf16 in, bf16 or fp32 out)
 // found_inf is raised when a reduced value is not finite; sumsq accumulates the squared norm.
-template <typename OutT>
-__device__ __forceinline__ void rs_reduce_body(const PeerPtrs& bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out,
-                                               float sc, bool& bad, float& acc_sq) {
-  for (int s = 0; s < n_segs; ++s) {
-    const ReduceSeg sg = segs[s];
-    const long long nvec = sg.numel / 8;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-      float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      uint4 v[8];
-      // issue all peer loads first (start with the next rank so the links are used evenly)
+// Sum of the same 16-byte vector of all W buffers, for U vectors per thread at once: every peer load is issued
+// before the first use, so a thread keeps U * W loads of 16 bytes in flight over NVLink (the reductions are
+// bound by bytes in flight, not by arithmetic). MAXW bounds the unrolled rank loop.
+template <int U, int MAXW>
+__device__ __forceinline__ void peer_sum(const PeerPtrs& bufs, int world, int rank, long long elem_base, long long i0, long long stride,
+                                         long long nvec, float (&a)[U][8]) {
+  uint4 v[U][MAXW];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        if (k < world) {
-          int r = rank + 1 + k;
-          if (r >= world) r -= world;
-          v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[r]) + sg.src_off + i * 8);
-        }
-      }
+  for (int u = 0; u < U; ++u) {
+    const long long i = i0 + u * stride;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        if (k < world) {
-          float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
-          a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        a[j] *= sc;
-        if (!isfinite(a[j])) bad = true;
-        acc_sq += a[j] * a[j];
-      }
-      OutT* o = out + sg.dst_off + i * 8;
-      if (sizeof(OutT) == 2) {
-        uint4 w;
-        w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
-        *reinterpret_cast<uint4*>(o) = w;
-      } else {
-        reinterpret_cast<float4*>(o)[0] = make_float4(a[0], a[1], a[2], a[3]);
-        reinterpret_cast<float4*>(o)[1] = make_float4(a[4], a[5], a[6], a[7]);
+    for (int k = 0; k < MAXW; ++k) {
+      if (k < world && i < nvec) {
+        int r = rank + 1 + k;       // start with the next rank so the links are used evenly
+        if (r >= world) r -= world;
+        v[u][k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[r]) + elem_base + i * 8);
       }
     }
   }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[u][j] = 0.f;
+    const long long i = i0 + u * stride;
+#pragma unroll
+    for (int k = 0; k < MAXW; ++k) {
+      if (k < world && i < nvec) {
+        float2 f0 = unpack_bf16x2(v[u][k].x), f1 = unpack_bf16x2(v[u][k].y), f2 = unpack_bf16x2(v[u][k].z), f3 = unpack_bf16x2(v[u][k].w);
+        a[u][0] += f0.x; a[u][1] += f0.y; a[u][2] += f1.x; a[u][3] += f1.y; a[u][4] += f2.x; a[u][5] += f2.y; a[u][6] += f3.x; a[u][7] += f3.y;
+      }
+    }
+  }
+}
+
+template <typename OutT, int U, int MAXW>
+__device__ __forceinline__ void rs_reduce_span(const PeerPtrs& bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out,
+                                               float sc, bool& bad, float& acc_sq) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int s = 0; s < n_segs; ++s) {
+    const ReduceSeg sg = segs[s];
+    const long long nvec = sg.numel / 8;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+      float a[U][8];
+      peer_sum<U, MAXW>(bufs, world, rank, sg.src_off, i0, stride, nvec, a);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) break;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          a[u][j] *= sc;
+          if (!isfinite(a[u][j])) bad = true;
+          acc_sq += a[u][j] * a[u][j];
+        }
+        OutT* o = out + sg.dst_off + i * 8;
+        if (sizeof(OutT) == 2) {
+          uint4 w;
+          w.x = pack_bf16x2(a[u][0], a[u][1]); w.y = pack_bf16x2(a[u][2], a[u][3]); w.z = pack_bf16x2(a[u][4], a[u][5]); w.w = pack_bf16x2(a[u][6], a[u][7]);
+          *reinterpret_cast<uint4*>(o) = w;
+        } else {
+          reinterpret_cast<float4*>(o)[0] = make_float4(a[u][0], a[u][1], a[u][2], a[u][3]);
+          reinterpret_cast<float4*>(o)[1] = make_float4(a[u][4], a[u][5], a[u][6], a[u][7]);
+        }
+      }
+    }
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void rs_reduce_body(const PeerPtrs& bufs, int world, int rank, const ReduceSeg* segs, int n_segs, OutT* out,
+                                               float sc, bool& bad, float& acc_sq) {
+  if (world <= 2) rs_reduce_span<OutT, 4, 2>(bufs, world, rank, segs, n_segs, out, sc, bad, acc_sq);
+  else if (world <= 4) rs_reduce_span<OutT, 2, 4>(bufs, world, rank, segs, n_segs, out, sc, bad, acc_sq);
+  else rs_reduce_span<OutT, 2, 8>(bufs, world, rank, segs, n_segs, out, sc, bad, acc_sq);
 }
 
 template <typename OutT>
@@ -281,6 +313,34 @@ rs_reduce_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, PeerPtrs flag
   sync_leave_all(pads, st, rank, world, e, err);
 }
 
+template <int U, int MAXW>
+__device__ __forceinline__ void two_shot_span(const PeerPtrs& bufs, int world, int rank, long long lo, long long nvec, float sc, bool& bad) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    float a[U][8];
+    peer_sum<U, MAXW>(bufs, world, rank, lo, i0, stride, nvec, a);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) break;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[u][j] *= sc;
+        if (!isfinite(a[u][j])) bad = true;
+      }
+      uint4 w;
+      w.x = pack_bf16x2(a[u][0], a[u][1]); w.y = pack_bf16x2(a[u][2], a[u][3]); w.z = pack_bf16x2(a[u][4], a[u][5]); w.w = pack_bf16x2(a[u][6], a[u][7]);
+#pragma unroll
+      for (int k = 0; k < MAXW; ++k)
+        if (k < world) {
+          int r = rank + 1 + k;
+          if (r >= world) r -= world;
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[r]) + lo + i * 8) = w;
+        }
+    }
+  }
+}
+
 // Two-shot all-reduce of a gradient bucket with both synchronisations inside: rank r sums slice r of
 // all W copies, scales it, checks it for overflow (raising every rank's flag) and stores it into
 // slice r of every rank's buffer. When the kernel ends on a rank its whole buffer holds the result.
@@ -294,37 +354,9 @@ ar_two_shot_sync_kernel(PeerPtrs bufs, PeerPtrs pads, SyncState* st, PeerPtrs fl
   const long long hi = lo + per < numel ? lo + per : numel;
   const long long nvec = hi > lo ? (hi - lo) / 8 : 0;
   bool bad = false;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    uint4 v[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (k < world) {
-        int r = rank + 1 + k;
-        if (r >= world) r -= world;
-        v[k] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(bufs.p[r]) + lo + i * 8);
-      }
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (k < world) {
-        float2 f0 = unpack_bf16x2(v[k].x), f1 = unpack_bf16x2(v[k].y), f2 = unpack_bf16x2(v[k].z), f3 = unpack_bf16x2(v[k].w);
-        a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
-      }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      a[j] *= sc;
-      if (!isfinite(a[j])) bad = true;
-    }
-    uint4 w;
-    w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (k < world) {
-        int r = rank + 1 + k;
-        if (r >= world) r -= world;
-        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(bufs.p[r]) + lo + i * 8) = w;
-      }
-  }
+  if (world <= 2) two_shot_span<4, 2>(bufs, world, rank, lo, nvec, sc, bad);
+  else if (world <= 4) two_shot_span<2, 4>(bufs, world, rank, lo, nvec, sc, bad);
+  else two_shot_span<2, 8>(bufs, world, rank, lo, nvec, sc, bad);
   raise_flag_everywhere(flags, world, bad);
   sync_leave_all(pads, st, rank, world, e, err);
 }
@@ -572,7 +604,7 @@ struct CopySegHost {
   void* dst;
   long long bytes;
 };
-__global__ void __launch_bounds__(256) peer_copy_kernel(const CopySegHost* segs, int n_segs) {
+__global__ void __launch_bounds__(512) peer_copy_kernel(const CopySegHost* segs, int n_segs) {
   for (int s = 0; s < n_segs; ++s) {
     const CopySegHost sg = segs[s];
     const uint4* src = static_cast<const uint4*>(sg.src);
@@ -580,9 +612,13 @@ __global__ void __launch_bounds__(256) peer_copy_kernel(const CopySegHost* segs,
     const long long n = sg.bytes / 16;
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long step = (long long)gridDim.x * blockDim.x;
-    for (; i + 3 * step < n; i += 4 * step) {
-      const uint4 a = src[i], b = src[i + step], c = src[i + 2 * step], d = src[i + 3 * step];
-      dst[i] = a; dst[i + step] = b; dst[i + 2 * step] = c; dst[i + 3 * step] = d;
+    // eight 16-byte loads in flight per thread: a copy over NVLink is bound by bytes in flight
+    for (; i + 7 * step < n; i += 8 * step) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = src[i + k * step];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) dst[i + k * step] = v[k];
     }
     for (; i < n; i += step) dst[i] = src[i];
   }
@@ -844,8 +880,8 @@ MLF_API int mlf_sum_partials(const void* partial, int world, long long rows, int
 // segs: device array of {src, dst, bytes} (bytes multiple of 16).
 MLF_API int mlf_peer_copy(const void* segs, int n_segs, int ctas, uint64_t stream) {
   if (n_segs <= 0) return 0;
-  if (ctas <= 0) ctas = sm_count();
-  peer_copy_kernel<<<ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const CopySegHost*>(segs), n_segs);
+  if (ctas <= 0) ctas = sm_count() * 2;
+  peer_copy_kernel<<<ctas, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const CopySegHost*>(segs), n_segs);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -90,9 +90,34 @@ class CapturedOp:
     kind: str = "kernel"      # kernel | memcpy | memset | host | alloc | free | sync | io | branch
 
 
+# node kinds of a real capture (ml_framework_b200.hal.cuda_rt.NODE_KINDS) -> the kinds the rules speak about
+_NODE_TO_OP = {"kernel": "kernel", "memcpy": "memcpy", "memset": "memset", "host": "host", "graph": "kernel", "empty": "empty",
+               "wait_event": "event", "event_record": "event", "ext_semaphore_signal": "sync", "ext_semaphore_wait": "sync",
+               "mem_alloc": "alloc", "mem_free": "free", "batch_mem_op": "memset", "conditional": "branch"}
+
+
 class GraphValidator:
-    """Rules over a list of recorded ops: a graph must not be empty, allocate or free device memory,
-    depend on host-side control flow, perform host I/O, or synchronise the device."""
+    """Rules over the operations of a capture: a graph must not be empty, allocate or free device memory,
+    depend on host-side control flow, perform host I/O, or synchronise the device.
+
+    ``validate_graph`` reads the node list of a REAL captured ``cudaGraph_t`` through the native runtime binding
+    (``cudaGraphGetNodes`` + ``cudaGraphNodeGetType``, the reference's CudaGraphGetNodes,
+    src/MLFramework/HAL/CUDA/CudaApi.cs:184, feeding src/MLFramework/HAL/CUDA/Graphs/Validation/CUDAGraphValidator.cs)
+    and applies the same rules to what was actually recorded; ``validate`` takes a declared list, for callers that
+    describe a capture before making it."""
+
+    def ops_of_graph(self, graph) -> List["CapturedOp"]:
+        """``graph``: a :class:`ml_framework_b200.hal.cuda_rt.Graph` or a raw ``cudaGraph_t`` address."""
+        from . import cuda_rt
+        g = graph if isinstance(graph, cuda_rt.Graph) else cuda_rt.Graph(int(graph), owned=False)
+        return [CapturedOp(f"node{i}:{k}", _NODE_TO_OP.get(k, "kernel")) for i, k in enumerate(g.node_kinds())]
+
+    def validate_graph(self, graph) -> List[ValidationIssue]:
+        ops = self.ops_of_graph(graph)
+        issues = self.validate([o for o in ops if o.kind != "empty"])
+        if not any(o.kind in ("kernel", "memcpy", "memset") for o in ops) and not any(i.rule == "EmptyGraph" for i in issues):
+            issues.append(ValidationIssue("EmptyGraph", "capture holds no kernel, copy or memset node"))
+        return issues
 
     def validate(self, ops: Sequence[CapturedOp]) -> List[ValidationIssue]:
         issues: List[ValidationIssue] = []
@@ -109,6 +134,9 @@ class GraphValidator:
                 issues.append(ValidationIssue("Synchronization", f"{op.name}: device / stream synchronisation inside a capture"))
             elif op.kind == "host":
                 issues.append(ValidationIssue("HostCallback", f"{op.name}: host callback", ValidationSeverity.WARNING))
+            elif op.kind == "event":
+                issues.append(ValidationIssue("CrossStreamEvent", f"{op.name}: event node (a side stream joined the capture)",
+                                              ValidationSeverity.WARNING))
         return issues
 
     def is_valid(self, ops: Sequence[CapturedOp]) -> bool:
@@ -121,12 +149,22 @@ class CaptureOptions:
     pool_bytes: int = 512 << 20
     enable_fallback: bool = True
     max_capture_failures: int = 3
+    validate: bool = True             # inspect the captured graph's nodes; errors make the capture fail (-> fallback)
+
+
+class GraphValidationError(RuntimeError):
+    def __init__(self, issues: List[ValidationIssue]):
+        super().__init__("; ".join(f"{i.rule}: {i.message}" for i in issues))
+        self.issues = issues
 
 
 class CapturedGraph:
-    def __init__(self, graph, static_inputs: List[torch.Tensor], static_outputs, name: str):
+    def __init__(self, graph, static_inputs: List[torch.Tensor], static_outputs, name: str,
+                 node_kinds: Optional[List[str]] = None, issues: Optional[List[ValidationIssue]] = None):
         self.graph, self.static_inputs, self.static_outputs, self.name = graph, static_inputs, static_outputs, name
         self.replays = 0
+        self.node_kinds = node_kinds or []        # node types of the captured cudaGraph_t
+        self.issues = issues or []                # validator findings (warnings; errors abort the capture)
 
     def replay(self, *inputs: torch.Tensor):
         for dst, src in zip(self.static_inputs, inputs):
@@ -156,6 +194,7 @@ class CUDAGraphManager:
         self._failures: Dict[str, int] = {}
         self._pool_handle = None
         self.fallbacks = 0
+        self.validator = GraphValidator()
 
     @staticmethod
     def _sig(name: str, inputs: Sequence[torch.Tensor]) -> Tuple:
@@ -170,12 +209,24 @@ class CUDAGraphManager:
         with torch.cuda.stream(side):
             fn(*static_in)                                   # settle lazy initialisation off the main stream
         torch.cuda.current_stream().wait_stream(side)
-        g = torch.cuda.CUDAGraph()
+        inspect = self.opt.validate and hasattr(torch.cuda.CUDAGraph, "raw_cuda_graph")
+        g = torch.cuda.CUDAGraph(keep_graph=True) if inspect else torch.cuda.CUDAGraph()
         if self._pool_handle is None:
             self._pool_handle = torch.cuda.graph_pool_handle()
         with torch.cuda.graph(g, pool=self._pool_handle):
             out = fn(*static_in)
-        cg = CapturedGraph(g, static_in, out, name)
+        kinds, issues = [], []
+        if inspect:
+            # the cudaGraph_t is kept until instantiation: read its nodes back and judge what was recorded
+            from . import cuda_rt
+            raw = cuda_rt.Graph(int(g.raw_cuda_graph()), owned=False)
+            kinds = raw.node_kinds()
+            issues = self.validator.validate_graph(raw)
+            errors = [i for i in issues if i.severity == ValidationSeverity.ERROR]
+            if errors:
+                raise GraphValidationError(errors)
+            g.instantiate()
+        cg = CapturedGraph(g, static_in, out, name, kinds, issues)
         self._graphs[self._sig(name, inputs)] = cg
         return cg
 

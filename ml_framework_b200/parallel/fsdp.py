@@ -372,7 +372,7 @@ class FSDP:
                 return
             gemm_mod.clear_piggyback()               # a queued prefetch nobody picked up must not fire later
             tbl = self._copy_table(u, full)
-            self.symm.peer_copy(tbl, tbl.shape[0], ctas=32)
+            self.symm.peer_copy(tbl, tbl.shape[0])      # nothing else runs at this point: all SMs
             return
         if u.owner is not None:
             if self.rank == u.owner:
@@ -456,7 +456,7 @@ class FSDP:
         cs.wait_event(ready)
         with torch.cuda.stream(cs):
             self.symm.rs_reduce_sync(buf, u._red_segs, u._red_segs.shape[0], self.grad_shards, u._red_numel, flag=self._flag,
-                                     key=self._sync_key, max_ctas=32)
+                                     key=self._sync_key, max_ctas=64)
             done = torch.cuda.Event()
             done.record(cs)
         self._rs_done[gbuf.data_ptr()] = done

@@ -298,12 +298,22 @@ class _LocalView:
 
 
 class ProcessGroupPipelineCommunicator:
-    """Stage-to-stage transfers over a process group (stage s == group rank s)."""
+    """Stage-to-stage transfers over a process group (stage s == group rank s).
+
+    Over NCCL every transfer runs on a communication stream of its own and the compute stream is never made to wait
+    for a transfer as a whole (the reference's per-micro-batch compute / communication streams joined by events,
+    src/MLFramework/Pipeline/AsyncPipelineExecutor.cs:76-320, StreamManager.cs:51-141): the communication stream
+    waits for an event recorded after the producing kernels, a sent tensor is only kept alive until its transfer's
+    event has passed, and a received tensor carries an event that the compute stream waits for at the point where
+    the schedule consumes it (``wait_ready``). The host therefore queues the next compute phase while the
+    transfer is in flight, and sends overlap whatever compute follows them."""
 
     def __init__(self, pg, use_side_stream: bool = True):
         self.pg, self.rank = pg, pg.rank
         self.stream = None
         self._pending: list = []
+        self._ready: Dict[int, object] = {}       # received buffer address -> event of its transfer
+        self._inflight: list = []                 # (event, tensor) of sends not known to be complete
         if use_side_stream and torch.cuda.is_available() and str(getattr(pg, "backend", "")).lower().endswith("nccl"):
             self.stream = torch.cuda.Stream()
 
@@ -321,12 +331,31 @@ class ProcessGroupPipelineCommunicator:
             while len(self._pending) > 64:
                 self._pending.pop(0)[0].wait()
             return
-        self.stream.wait_stream(torch.cuda.current_stream())
+        produced = torch.cuda.Event()
+        produced.record()                          # after the kernels that wrote the tensors being sent
+        self.stream.wait_event(produced)
         with torch.cuda.stream(self.stream):
             works = self.pg.batch_isend_irecv(ops)
             for w in works:
-                w.wait()
-        torch.cuda.current_stream().wait_stream(self.stream)
+                w.wait()                           # orders the communication stream, not the host
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        for kind, t, _ in ops:
+            t.record_stream(self.stream)           # the allocator must not hand the memory out before the transfer ran
+            if kind == "recv":
+                self._ready[t.data_ptr()] = done
+            else:
+                self._inflight.append((done, t))
+        while self._inflight and (len(self._inflight) > 32 or self._inflight[0][0].query()):
+            self._inflight.pop(0)
+
+    def wait_ready(self, t: Optional[torch.Tensor]):
+        """Called by the schedule where a received tensor is first used: the compute stream waits for that transfer only."""
+        if t is None or self.stream is None:
+            return
+        ev = self._ready.pop(t.data_ptr(), None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
 
     def send_forward(self, t): self._run([("send", t.contiguous(), self.rank + 1)])
     def send_backward(self, t): self._run([("send", t.contiguous(), self.rank - 1)])
@@ -354,6 +383,9 @@ class ProcessGroupPipelineCommunicator:
     def barrier(self):
         while self._pending:
             self._pending.pop(0)[0].wait()
+        if self.stream is not None:
+            torch.cuda.current_stream().wait_stream(self.stream)
+            self._inflight.clear()
         self.pg.barrier()
 
 
@@ -369,6 +401,12 @@ class _ScheduleBase:
         self._saved: Dict[int, tuple] = {}
         self._out_spec: Dict[int, tuple] = {}
         self.losses: List[torch.Tensor] = []
+
+    def _consume(self, t):
+        """A tensor that arrived from a neighbour is about to be read: wait for its transfer (asynchronous communicators)."""
+        fn = getattr(self.comm, "wait_ready", None)
+        if fn is not None and t is not None:
+            fn(t)
 
     def _act_spec(self, x_local=None):
         st = self.stage
@@ -390,6 +428,7 @@ class _ScheduleBase:
         """Runs the stage on one micro-batch (input already here); returns the stage output."""
         st = self.stage
         t0 = time.perf_counter()
+        self._consume(x)
         if not st.is_first:
             x = x.detach().requires_grad_(True)
         recompute = self.ckpt.should_checkpoint(mb, x.numel() * x.element_size())
@@ -424,6 +463,7 @@ class _ScheduleBase:
         returns the gradient of the stage input (None on the first stage)."""
         st = self.stage
         t0 = time.perf_counter()
+        self._consume(g)
         x, y, recompute, target = self._saved.pop(mb)
         if recompute:
             y = st(x)
