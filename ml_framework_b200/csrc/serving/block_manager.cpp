@@ -173,6 +173,25 @@ MLF_API int mlf_bm_free_tail(void* h, long long seq, int keep_tokens) {
   return freed;
 }
 
+// Releases whole blocks beyond the first `keep_blocks` of a sequence that were reserved but hold no tokens
+// (cache compaction): never cuts into blocks that cover the sequence's tokens. Returns the number released.
+MLF_API int mlf_bm_free_tail_blocks(void* h, long long seq, int keep_blocks) {
+  auto* m = static_cast<BlockManager*>(h);
+  std::lock_guard<std::mutex> lk(m->mu);
+  auto it = m->seqs.find(seq);
+  if (it == m->seqs.end() || keep_blocks < 0) return -1;
+  auto& s = it->second;
+  const int needed = (s.tokens + m->block_size - 1) / m->block_size;
+  if (keep_blocks < needed) keep_blocks = needed;
+  int freed = 0;
+  while ((int)s.blocks.size() > keep_blocks) {
+    m->release(s.blocks.back());
+    s.blocks.pop_back();
+    ++freed;
+  }
+  return freed;
+}
+
 // dst shares the first ceil(prefix_tokens / block_size) blocks of src (reference counts go up).
 MLF_API int mlf_bm_fork(void* h, long long src, long long dst, int prefix_tokens) {
   auto* m = static_cast<BlockManager*>(h);

@@ -54,6 +54,8 @@ class FSDPCpuOffloadConfig:
     def validate(self):
         if not (0 <= self.prefetch_steps <= 10):
             raise ValueError("prefetch_steps must be in [0, 10]")
+        if self.enabled and self.offload_gradients and not self.offload_optimizer_states:
+            raise ValueError("offload_gradients needs offload_optimizer_states (the update then runs where the gradients are)")
 
 
 @dataclass
@@ -153,6 +155,73 @@ class _PostBackward(torch.autograd.Function):
         return g, None, None
 
 
+class FSDPPrefetchManager:
+    """Brings offloaded parameter shards back to the device ahead of their use.
+
+    With ``offload_parameters`` the bf16 shards a rank owns live in pinned host memory. ``request(i)`` starts the
+    host -> device copy of unit i's shard on a copy stream into one of ``prefetch_steps + 2`` staging buffers;
+    ``get(i)`` makes the compute stream wait for that copy only and returns the device view; ``release(i)`` gives
+    the buffer back once the kernels that read it are queued (the next copy into it waits for them through an
+    event). The reference does the same with a worker thread and a request queue
+    (src/MLFramework/Distributed/FSDP/FSDPCpuOffload.cs:398-569, worker loop :453; OffloadParameter /
+    PrefetchParameter :115-253); here the copy stream is the worker. On the CPU everything is synchronous."""
+
+    def __init__(self, device: torch.device, dtype: torch.dtype, max_numel: int, steps: int):
+        self.device, self.steps = device, steps
+        self.cuda = device.type == "cuda"
+        self.stream = torch.cuda.Stream(device=device) if self.cuda else None
+        self.free = [torch.empty(max_numel, dtype=dtype, device=device) for _ in range(steps + 2)]
+        self.resident: Dict[int, tuple] = {}     # unit index -> (buffer, event or None, numel)
+        self.freed_at: Dict[int, object] = {}    # buffer address -> event after its last reader
+        self.requests = self.hits = 0
+
+    def request(self, idx: int, host_shard: torch.Tensor):
+        if idx in self.resident or not self.free:
+            return
+        buf = self.free.pop()
+        n = host_shard.numel()
+        self.requests += 1
+        if self.cuda:
+            after = self.freed_at.pop(buf.data_ptr(), None)
+            if after is not None:
+                self.stream.wait_event(after)
+            with torch.cuda.stream(self.stream):
+                buf[:n].copy_(host_shard, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+        else:
+            buf[:n].copy_(host_shard)
+            ev = None
+        self.resident[idx] = (buf, ev, n)
+
+    def get(self, idx: int, host_shard: torch.Tensor) -> torch.Tensor:
+        if idx in self.resident:
+            self.hits += 1
+        else:
+            if not self.free:                     # every buffer is in use: drop the oldest prefetch nobody consumed
+                self.release(next(iter(self.resident)))
+            self.request(idx, host_shard)
+        buf, ev, n = self.resident[idx]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+        return buf[:n]
+
+    def release(self, idx: int):
+        ent = self.resident.pop(idx, None)
+        if ent is None:
+            return
+        buf = ent[0]
+        if self.cuda:
+            ev = torch.cuda.Event()
+            ev.record()                            # after the readers queued on the compute stream
+            self.freed_at[buf.data_ptr()] = ev
+        self.free.append(buf)
+
+    def release_all(self):
+        for idx in list(self.resident):
+            self.release(idx)
+
+
 class FSDP:
     """Wraps ``model`` (which must expose ``embed``, ``blocks`` and a ``forward(ids, targets,
     loss_scale)`` like the models in :mod:`ml_framework_b200.models`; any module with a
@@ -172,9 +241,16 @@ class FSDP:
         self.opt_kw.update(optimizer_kwargs or {})
         self.step_count = 0
         self._rot_owner = {}
+        self._pending_rs: list = []
+        self._rs_done: dict = {}
         self.symm = None
         self.fused = False
-        if (self.cfg.fused_comm and self.world > 1 and self.device.type == "cuda"
+        off = self.cfg.cpu_offload
+        self.offload_params = bool(off.enabled and off.offload_parameters and self.cfg.sharding_strategy == "full")
+        self.offload_grads = bool(off.enabled and off.offload_gradients)
+        # peers read parameter shards straight out of this rank's device memory on the fused path, so shards that
+        # live on the host go through process-group collectives instead
+        if (self.cfg.fused_comm and self.world > 1 and self.device.type == "cuda" and not self.offload_params
                 and self.cfg.sharding_strategy in ("full", "grad_op")):
             from ..dist.symm import SymmetricMemory
             self.symm = SymmetricMemory(process_group, self.device)
@@ -249,7 +325,15 @@ class FSDP:
                 self._symm_bufs[name] = b
                 return b.view(dt, numel)
             return torch.zeros(numel, dtype=dt, device=dev)
-        self.param_shards = symm_or_local("param_shards", total)      # bf16 working copy of what this rank owns
+        pin_p = torch.cuda.is_available()
+        if self.offload_params:
+            # owned bf16 shards on the (pinned) host; the small replicated tail keeps a device copy of its own
+            self.param_shards = torch.zeros(total, dtype=dt, device="cpu", pin_memory=pin_p)
+            self._rep_dev = torch.zeros(rep_pad, dtype=dt, device=dev)
+        else:
+            self.param_shards = symm_or_local("param_shards", total)      # bf16 working copy of what this rank owns
+            self._rep_dev = None
+        self.grad_host = torch.zeros(total, dtype=dt, device="cpu", pin_memory=pin_p) if self.offload_grads else None
         # reduced gradients of what this rank owns (symmetric on the fused path: its replicated tail is all-reduced in place)
         self.grad_shards = symm_or_local("grad_shards", total)
         max_full = max([u.full_numel for u in self.units], default=0)
@@ -259,7 +343,12 @@ class FSDP:
         self._rot_grad = [symm_or_local(f"rot_grad{k}", max_full) for k in range(2)] if max_full else []
         # One rank: a shard is the whole parameter, so block units compute on their shards and write
         # gradients into their gradient shards directly (nothing to gather, nothing to reduce).
-        self._alias_shards = self.world == 1 and self.cfg.sharding_strategy == "full"
+        self._alias_shards = self.world == 1 and self.cfg.sharding_strategy == "full" and not self.offload_params
+        self.prefetch = None
+        if self.offload_params:
+            max_shard = max([u.shard_numel for u in self.all_units()], default=0)
+            self.prefetch = FSDPPrefetchManager(dev, dt, max_shard, self.cfg.cpu_offload.prefetch_steps)
+            self._opt_stage = torch.zeros(max(max_shard, rep_pad, 8), dtype=dt, device=dev)
         with torch.no_grad():
             for u in self.all_units():
                 u.shard = self.param_shards[u.state_off:u.state_off + u.shard_numel]
@@ -290,11 +379,13 @@ class FSDP:
             # replicated small parameters: one flat buffer + flat gradient
             off = self.rep_off
             self.rep_grad = self.grad_shards[self.rep_off:self.rep_off + rep_pad]
-            self.rep_flat = self.param_shards[self.rep_off:self.rep_off + rep_pad]
+            self.rep_flat = self.param_shards[self.rep_off:self.rep_off + rep_pad] if self._rep_dev is None else self._rep_dev
             for _, p in self.replicated:
                 n = p.numel()
                 self.param_shards[off:off + n].copy_(p.data.reshape(-1))
-                p.data = self.param_shards[off:off + n].view(p.shape)
+                ro = off - self.rep_off
+                self.rep_flat[ro:ro + n].copy_(p.data.reshape(-1))
+                p.data = self.rep_flat[ro:ro + n].view(p.shape)
                 p.main_grad = self.grad_shards[off:off + n].view(p.shape)
                 p._main_grad_started = False
                 off += n
@@ -334,6 +425,13 @@ class FSDP:
 
     def _install_hooks(self):
         fs = self
+        if self.cfg.activation_checkpointing:
+            # each unit's forward keeps only its input and is recomputed in backward, inside the unit's
+            # gather / reduce hooks (which stay on the module call, outside the recomputed region)
+            from ..checkpoint.activation import checkpoint
+            for u in self.units:
+                inner = u.module.forward
+                u.module.forward = (lambda *a, _f=inner: checkpoint(_f, *a))
         for i, u in enumerate(self.units):
             def pre(mod, args, i=i):
                 fs._pre_forward(i)
@@ -361,9 +459,11 @@ class FSDP:
     def _gather_unit(self, u: FSDPUnit, full: torch.Tensor):
         """All-gather every sharded parameter of the unit into ``full`` (per-parameter collectives,
         rank-major inside each parameter == row sharding)."""
+        shard = self._device_shard(u)
         if self.world == 1:
             for sp in u.sharded:
-                full[sp.full_off:sp.full_off + sp.padded].copy_(u.shard[sp.shard_off:sp.shard_off + sp.shard_numel])
+                full[sp.full_off:sp.full_off + sp.padded].copy_(shard[sp.shard_off:sp.shard_off + sp.shard_numel])
+            self._done_with_shard(u)
             return
         if self.fused:
             from ..ops import gemm as gemm_mod
@@ -381,7 +481,31 @@ class FSDP:
             return
         for sp in u.sharded:
             self.pg.all_gather_into(full[sp.full_off:sp.full_off + sp.padded],
-                                    u.shard[sp.shard_off:sp.shard_off + sp.shard_numel])
+                                    shard[sp.shard_off:sp.shard_off + sp.shard_numel])
+        self._done_with_shard(u)
+
+    # ---- offloaded parameter shards
+    def _unit_index(self, u: FSDPUnit) -> int:
+        return len(self.units) if u is self.root_unit else self.units.index(u)
+
+    def _device_shard(self, u: FSDPUnit) -> torch.Tensor:
+        """The unit's owned pieces on the device: the shard itself, or its prefetched copy when shards live on the host."""
+        if self.prefetch is None:
+            return u.shard
+        return self.prefetch.get(self._unit_index(u), u.shard)
+
+    def _done_with_shard(self, u: FSDPUnit):
+        if self.prefetch is not None:
+            self.prefetch.release(self._unit_index(u))
+
+    def _prefetch_units(self, first: int, direction: int):
+        """Start the host -> device copies of the next ``prefetch_steps`` units in execution order."""
+        if self.prefetch is None:
+            return
+        for k in range(1, self.cfg.cpu_offload.prefetch_steps + 1):
+            j = first + direction * k
+            if 0 <= j < len(self.units):
+                self.prefetch.request(j, self.units[j].shard)
 
     def _schedule_prefetch(self, j: int):
         """Attach the gather of unit j to the next large GEMM: its copy CTAs pull unit j's shards
@@ -410,6 +534,7 @@ class FSDP:
         u.gathered = full
         self._point_params(u, full, None)
         self._schedule_prefetch(i + 1)
+        self._prefetch_units(i, +1)
 
     def _post_forward(self, i: int):
         pass  # the rotating buffer is simply reused two units later
@@ -431,6 +556,7 @@ class FSDP:
         if self._rot_owner.get(i % 2) != i:          # the last units of the forward pass are still resident
             self._gather_unit(u, full)
             self._rot_owner[i % 2] = i
+        self._prefetch_units(i, -1)
         u.gathered = full
         self._wait_grad_buffer(gbuf)
         self._point_params(u, full, gbuf)
@@ -463,6 +589,8 @@ class FSDP:
 
     def _wait_grad_buffer(self, gbuf: torch.Tensor):
         """Before a gradient buffer is written again: the reduction that read it (here and on the peers) must be over."""
+        if self._pending_rs:
+            self._drain_reductions(gbuf.data_ptr())
         ev = self._rs_done.pop(gbuf.data_ptr(), None) if self.fused else None
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
@@ -490,12 +618,42 @@ class FSDP:
                     u.owned_grad[sp.full_off:sp.full_off + sp.padded].copy_(view)
                 out.zero_()
             else:
-                red = self.pg.reduce_scatter(view, op=ReduceOp.SUM)
-                out.copy_(red)
+                # asynchronous: up to num_communication_workers units' reductions stay in flight behind the
+                # backward of the following units (the reference's communication workers, FSDPConfig.cs:8-58)
+                work = self.pg.reduce_scatter(view, op=ReduceOp.SUM, async_op=True)
+                self._pending_rs.append((gbuf.data_ptr(), work, out))
+        if self.world > 1 and u.owner is None:
+            limit = self.cfg.num_communication_workers * max(1, len(u.sharded))
+            while len(self._pending_rs) > limit:
+                self._complete_reduction(self._pending_rs.pop(0))
+
+    def _complete_reduction(self, ent):
+        _, work, out = ent
+        out.copy_(work.wait())
+
+    def _drain_reductions(self, buffer_ptr: Optional[int] = None):
+        """Completes the asynchronous reductions that read ``buffer_ptr`` (all of them when None)."""
+        keep = []
+        for ent in self._pending_rs:
+            if buffer_ptr is None or ent[0] == buffer_ptr:
+                self._complete_reduction(ent)
+            else:
+                keep.append(ent)
+        self._pending_rs = keep
 
     def _post_backward(self, i: int):
         u = self.units[i]
         self._reduce_unit(u, u._gbuf)
+        self._offload_unit_grads(u)
+
+    def _offload_unit_grads(self, u: FSDPUnit):
+        """``offload_gradients``: the reduced gradient pieces leave for pinned host memory as soon as they exist
+        (FSDPCpuOffload.OffloadGradient, FSDPCpuOffload.cs:175-214); the update then reads them there."""
+        if self.grad_host is None or self.fused:
+            return
+        self._drain_reductions(u._gbuf.data_ptr() if hasattr(u, "_gbuf") and u is not self.root_unit else None)
+        s0, n = u.state_off, u.shard_numel
+        self.grad_host[s0:s0 + n].copy_(self.grad_shards[s0:s0 + n], non_blocking=True)
 
     # ------------------------------------------------------------------ step
     def train_step(self, ids, targets, scaler=None):
@@ -516,11 +674,13 @@ class FSDP:
         loss.backward()
         if root is not None:
             self._reduce_unit(root, root.grad_full)
+            self._offload_unit_grads(root)
         self._finish_replicated()
         self.step(scaler)
         return loss
 
     def _finish_replicated(self):
+        self._drain_reductions()
         for _, p in self.replicated:
             if p.grad is not None:
                 if getattr(p, "_main_grad_started", False):
@@ -540,7 +700,10 @@ class FSDP:
                                                        offset_bytes=self.rep_off * self.rep_grad.element_size(),
                                                        key=self._sync_key, max_ctas=32)
             else:
-                self.pg.all_reduce(self.rep_grad, op=ReduceOp.SUM)
+                # bucket_size_mb bounds one all-reduce message (FSDPConfig.BucketSizeMB, FSDPConfig.cs:8-58)
+                per = max(8, int(self.cfg.bucket_size_mb * 1024 * 1024) // self.rep_grad.element_size())
+                for lo in range(0, self.rep_grad.numel(), per):
+                    self.pg.all_reduce(self.rep_grad[lo:lo + per], op=ReduceOp.SUM)
         if self.fused:
             torch.cuda.current_stream().wait_stream(self._comm_stream)   # every reduction of the step is in grad_shards
             self._rs_done.clear()
@@ -572,13 +735,34 @@ class FSDP:
             inv_scale, found = scaler.inv_scale_t, scaler.found_inf
         gscale = 1.0 / self.world
         b1, b2 = kw["betas"]
-        if self.master.is_cuda:
+        if self.master.is_cuda and self.offload_params:
+            # parameter shards live on the host: update unit by unit through a device staging buffer, each slice
+            # leaving for pinned memory right behind its kernel (stream order keeps the one buffer safe)
+            if self.prefetch is not None:
+                self.prefetch.release_all()
+            spans = [(u.state_off, u.shard_numel) for u in self.all_units() if u.shard_numel]
+            rep_n = self.rep_flat.numel()
+            for s0, n in spans + ([(self.rep_off, rep_n)] if rep_n else []):
+                stage = self._opt_stage[:n] if s0 != self.rep_off else self.rep_flat
+                native.adamw_(self.master[s0:s0 + n], self.m[s0:s0 + n], self.v[s0:s0 + n], g[s0:s0 + n], stage, lr=kw["lr"],
+                              beta1=b1, beta2=b2, eps=kw["eps"], weight_decay=kw["weight_decay"], step=self.step_count,
+                              grad_scale=gscale, inv_scale=inv_scale, found_inf=found)
+                self.param_shards[s0:s0 + n].copy_(stage, non_blocking=True)
+        elif self.master.is_cuda:
             native.adamw_(self.master, self.m, self.v, g, self.param_shards, lr=kw["lr"], beta1=b1, beta2=b2, eps=kw["eps"],
                           weight_decay=kw["weight_decay"], step=self.step_count, grad_scale=gscale, inv_scale=inv_scale,
                           found_inf=found)
         else:
             skip = found is not None and int(found.item()) != 0
             if not skip:
+                if self.grad_host is not None:
+                    # the sharded part arrived unit by unit during backward; the replicated tail follows now
+                    rn = self.rep_grad.numel()
+                    if rn:
+                        self.grad_host[self.rep_off:self.rep_off + rn].copy_(self.rep_grad)
+                    if g.is_cuda:
+                        torch.cuda.current_stream().synchronize()
+                    g = self.grad_host
                 gf = g.detach().to(self.state_device).float() * gscale
                 if inv_scale is not None:
                     gf = gf * float(inv_scale.item())
@@ -586,6 +770,11 @@ class FSDP:
                                               eps=kw["eps"], weight_decay=kw["weight_decay"], step=self.step_count)
                 self.master.copy_(p); self.m.copy_(m); self.v.copy_(v)
                 self.param_shards.copy_(self.master.to(self.param_shards.device, non_blocking=True).to(self.dtype))
+                if self._rep_dev is not None:
+                    rn = self._rep_dev.numel()
+                    self._rep_dev.copy_(self.param_shards[self.rep_off:self.rep_off + rn], non_blocking=True)
+            if self.prefetch is not None:
+                self.prefetch.release_all()
         for u in self.all_units():
             if u.owner is not None and u.owner == self.rank and self.world > 1:
                 self._step_owned(u, gscale, inv_scale, found)

@@ -103,6 +103,13 @@ class KVCacheBlockManager:
             raise KeyError(f"unknown sequence {seq_id} or bad length {keep_tokens}")
         return r
 
+    def truncate_blocks(self, seq_id: int, keep_blocks: int) -> int:
+        """Release reserved-but-empty blocks beyond the first ``keep_blocks`` (never blocks that hold tokens)."""
+        r = self._L.mlf_bm_free_tail_blocks(self._h, C.c_longlong(seq_id), int(keep_blocks))
+        if r < 0:
+            raise KeyError(f"unknown sequence {seq_id}")
+        return r
+
     def fork(self, src_seq: int, dst_seq: int, prefix_tokens: int = -1) -> int:
         r = self._L.mlf_bm_fork(self._h, C.c_longlong(src_seq), C.c_longlong(dst_seq), prefix_tokens)
         if r < 0:

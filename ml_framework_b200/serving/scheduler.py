@@ -465,6 +465,8 @@ class ContinuousBatchScheduler:
         self._thread: Optional[threading.Thread] = None
         self._stop = threading.Event()
         self.iterations = 0
+        self.warmup_done = 0              # iterations spent warming up the executor before the loop serves
+        self.timed_out_iterations = 0
 
     # ---- API
     def enqueue(self, req: Request) -> Future:
@@ -494,8 +496,28 @@ class ContinuousBatchScheduler:
             self._thread.join(timeout_s)
             self._thread = None
 
+    def warm_up(self) -> int:
+        """Runs ``warmup_iterations`` iterations of the executor's own warm-up work (``executor.warm_up(i)``, e.g.
+        capturing the decode graphs of the first batch buckets) before requests are served; executors without a
+        warm-up hook skip this. ContinuousBatchScheduler.cs:143-175 counts the first iterations of its loop as
+        warm-up and keeps them out of the idle accounting."""
+        fn = getattr(self.executor, "warm_up", None)
+        n = 0
+        for i in range(self.cfg.warmup_iterations if fn is not None else 0):
+            if self._stop.is_set():
+                break
+            try:
+                fn(i)
+            except Exception as e:  # noqa: BLE001
+                self.metrics.record_error(f"Warmup{type(e).__name__}")
+                break
+            n += 1
+        self.warmup_done = n
+        return n
+
     def _loop(self):
         idle = 0
+        self.warm_up()
         while not self._stop.is_set():
             did = self.execute_iteration()
             if did:
@@ -506,7 +528,14 @@ class ContinuousBatchScheduler:
 
     # ---- one iteration
     def execute_iteration(self) -> bool:
-        batch = self.batch_manager.prepare_next_iteration()
+        if getattr(self, "_skip_admission_once", False):
+            self._skip_admission_once = False
+            bm = self.batch_manager
+            prefill = [r for r in bm.running if r.state == RequestState.PREFILL][: bm.c.max_prefills_per_iteration]
+            decode = [r for r in bm.running if r.state == RequestState.DECODE]
+            batch = Batch(prefill + decode, prefill, decode)
+        else:
+            batch = self.batch_manager.prepare_next_iteration()
         if not batch.requests:
             return False
         t0 = self.clock()
@@ -517,6 +546,13 @@ class ContinuousBatchScheduler:
             self._fail(batch.requests, str(e))
             return True
         now = self.clock()
+        if self.cfg.iteration_timeout_ms > 0 and (now - t0) * 1e3 > self.cfg.iteration_timeout_ms:
+            # The iteration ran past its budget (SchedulerConfiguration.IterationTimeoutMs; the reference cancels the
+            # iteration's token, ContinuousBatchScheduler.cs:155-160). A device step cannot be cancelled half way, so
+            # its tokens are kept, the overrun is recorded, and the next iteration admits no new prefill work.
+            self.timed_out_iterations += 1
+            self.metrics.record_error("IterationTimeout")
+            self._skip_admission_once = True
         done = []
         for r in batch.requests:
             tok = out.generated_tokens.get(r.id)

@@ -93,3 +93,60 @@ def test_fsdp_overflow_skips_on_every_rank():
         return torch.equal(before, fs.master), scaler.scale
     outs = run_fake_world(W, run)
     assert all(o[0] for o in outs) and all(o[1] == 512.0 for o in outs)
+
+
+@pytest.mark.parametrize("offload", [dict(offload_parameters=True, prefetch_steps=1),
+                                     dict(offload_parameters=True, offload_gradients=True, prefetch_steps=2),
+                                     dict(offload_gradients=True)])
+def test_fsdp_cpu_offload_of_parameters_and_gradients_matches_plain_fsdp(offload):
+    """Parameter shards on the host with a prefetch manager, gradient shards leaving for the host after each unit's
+    reduction: the training result is the one of the same run without offload."""
+    W, steps = 2, 3
+    cfg = GPTConfig(n_layers=3, d_model=64, n_heads=2, d_ff=128, vocab_size=100, max_seq=16, vocab_multiple=8)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 100, (W, 2, 16), generator=g)
+    tgt = torch.randint(0, 100, (W, 2, 16), generator=g)
+    kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-4, weight_decay=0.01)
+    torch.manual_seed(0)
+    base = GPT(cfg)
+
+    def run(pg, off):
+        model = copy.deepcopy(base)
+        conf = FSDPConfig(min_shard_numel=64, cpu_offload=FSDPCpuOffloadConfig(enabled=off is not None, **(off or {})))
+        fs = FSDP(model, conf, pg, optimizer_kwargs=kw)
+        losses = [fs.train_step(ids[pg.rank], tgt[pg.rank]).item() for _ in range(steps)]
+        stats = (fs.prefetch.requests, fs.prefetch.hits) if fs.prefetch is not None else None
+        return losses, fs.full_state_dict(), stats, fs.param_shards.device.type
+    plain = run_fake_world(W, lambda pg: run(pg, None))
+    offl = run_fake_world(W, lambda pg: run(pg, offload))
+    for r in range(W):
+        assert all(abs(a - b) < 1e-5 for a, b in zip(plain[r][0], offl[r][0]))
+        for n, p in plain[r][1].items():
+            assert torch.allclose(offl[r][1][n], p, atol=1e-6), n
+        if offload.get("offload_parameters"):
+            req, hits = offl[r][2]
+            assert req > 0 and hits > 0          # units ahead were brought in before they were asked for
+            assert offl[r][3] == "cpu"
+    with pytest.raises(ValueError):
+        FSDPCpuOffloadConfig(enabled=True, offload_gradients=True, offload_optimizer_states=False).validate()
+
+
+def test_fsdp_activation_checkpointing_and_async_reductions_match():
+    W, steps = 2, 2
+    cfg = GPTConfig(n_layers=3, d_model=64, n_heads=2, d_ff=128, vocab_size=100, max_seq=16, vocab_multiple=8)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 100, (W, 2, 16), generator=g)
+    kw = dict(lr=1e-2, eps=1e-4)
+    torch.manual_seed(0)
+    base = GPT(cfg)
+
+    def run(pg, **conf):
+        model = copy.deepcopy(base)
+        fs = FSDP(model, FSDPConfig(min_shard_numel=64, **conf), pg, optimizer_kwargs=kw)
+        return [fs.train_step(ids[pg.rank], ids[pg.rank]).item() for _ in range(steps)], fs.full_state_dict()
+    a = run_fake_world(W, lambda pg: run(pg))
+    b = run_fake_world(W, lambda pg: run(pg, activation_checkpointing=True, num_communication_workers=1, bucket_size_mb=1))
+    for r in range(W):
+        assert all(abs(x - y) < 1e-5 for x, y in zip(a[r][0], b[r][0]))
+        for n, p in a[r][1].items():
+            assert torch.allclose(b[r][1][n], p, atol=1e-6), n

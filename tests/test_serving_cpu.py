@@ -192,3 +192,92 @@ def test_paged_llama_executor_matches_full_sequence_greedy():
             seq.append(int(logits[0, -1].argmax()))
         assert f.result(0).tokens == seq[len(p):], (p, f.result(0).tokens, seq[len(p):])
     assert kv.get_stats().allocated_blocks == 0          # everything released after completion
+
+
+def test_iteration_level_manager_memory_aware_queue_and_cache_manager():
+    from ml_framework_b200.serving.iteration import (ContinuousBatchKVCacheManager, ContinuousBatchManager, IterationScheduler,
+                                                     IterationSchedulerConfig, MemoryAwareScheduler, PendingRequest)
+    from ml_framework_b200.serving.kv_cache import KVCacheBlockManager
+    from ml_framework_b200.serving.scheduler import KVCacheConfiguration, PagedAttentionScheduler
+    bm = KVCacheBlockManager(total_blocks=16, block_size=4, allocate_cache=False)
+    mem = MemoryAwareScheduler(PagedAttentionScheduler(bm), max_queue_size=3)
+    assert all(mem.enqueue_request(PendingRequest(i, estimated_max_tokens=20, prompt_tokens=8)) for i in range(3))
+    assert not mem.enqueue_request(PendingRequest(9, 8))            # queue bound
+    batch = ContinuousBatchManager(bm, max_batch_size=2)
+    log = []
+
+    def prefill(seqs, ranges):
+        for s in seqs:
+            lo, hi = ranges[s]
+            bm.append_tokens(s, hi - lo)
+        log.append(("prefill", list(seqs), dict(ranges)))
+
+    def decode(seqs, lengths):
+        for s in seqs:
+            bm.append_tokens(s, 1)
+        log.append(("decode", list(seqs), dict(lengths)))
+    sch = IterationScheduler(batch, mem, prefill, decode, IterationSchedulerConfig(max_batch_size=2, max_prefill_per_iteration=4))
+    st = sch.run_iteration()
+    assert st.total_sequences == 2 and st.prefill_sequences == 2 and mem.queue_size() == 1
+    assert log[0] == ("prefill", [0, 1], {0: (0, 8), 1: (0, 8)})
+    sch.run_iteration()
+    assert log[-1] == ("decode", [0, 1], {0: 8, 1: 8}) and bm.get_sequence_length(0) == 9
+    batch.remove_sequence(0)
+    sch.run_iteration()                                            # the queued request takes the free slot
+    assert sorted(batch.current_batch()) == [1, 2] and batch.stats().utilization == 1.0
+    batch.clear()
+    assert bm.free_blocks == 16
+
+    # request-level cache allocations: growth, bounded pages, compaction that returns pages
+    cm = ContinuousBatchKVCacheManager(bm, KVCacheConfiguration(page_size_tokens=4, initial_pages=2, max_pages_per_request=6,
+                                                                target_utilization=0.5), bytes_per_token=10)
+    assert cm.allocate_cache(100, max_tokens=4) == 2 * 40           # initial pages
+    assert cm.allocate_cache(101, max_tokens=100) == 6 * 40         # capped
+    with pytest.raises(RuntimeError):
+        cm.allocate_cache(100, 4)
+    assert cm.try_extend_cache(100, 9) and cm.get_allocation(100).page_count == 5
+    assert cm.try_extend_cache(100, 100) and cm.get_allocation(100).page_count == 6
+    assert not cm.try_extend_cache(100, 1)                          # at the cap
+    assert cm.current_usage_bytes() == 12 * 40 and bm.free_blocks == 4
+    with pytest.raises(MemoryError):
+        cm.allocate_cache(102, max_tokens=40)
+    assert bm.free_blocks == 4                                     # nothing leaked by the failed allocation
+    bm.append_tokens(100, 5)                                        # request 100 really uses 2 pages
+    freed = cm.compact_cache()
+    assert freed == 4 + 4 and bm.free_blocks == 12                 # 100 keeps 2 pages, 101 (no tokens) keeps its initial 2
+    assert cm.get_allocation(100).page_count == 2 and cm.get_allocation(101).page_count == 2
+    cm.release_cache(100)
+    cm.release_cache(101)
+    assert cm.allocation_count == 0 and bm.free_blocks == 16
+
+
+def test_scheduler_warmup_iterations_and_iteration_timeout():
+    from ml_framework_b200.serving.scheduler import (BatchOutput, ContinuousBatchScheduler, Request, SchedulerConfiguration)
+    t = {"now": 0.0}
+
+    class SlowExecutor:
+        def __init__(self):
+            self.warm, self.calls = [], 0
+
+        def warm_up(self, i):
+            self.warm.append(i)
+
+        def execute_batch(self, batch):
+            self.calls += 1
+            t["now"] += 2.0 if self.calls == 1 else 0.001          # the first iteration overruns its budget
+            for r in batch.prefill:
+                r.prefilled = len(r.prompt_tokens)
+            return BatchOutput({r.id: 7 for r in batch.requests})
+    ex = SlowExecutor()
+    s = ContinuousBatchScheduler(ex, config=SchedulerConfiguration(iteration_timeout_ms=500.0, warmup_iterations=3, max_batch_size=4),
+                                 clock=lambda: t["now"])
+    assert s.warm_up() == 3 and ex.warm == [0, 1, 2]
+    r1 = Request([1, 2, 3], max_tokens=2)
+    f1 = s.enqueue(r1)
+    assert s.execute_iteration()
+    assert s.timed_out_iterations == 1 and s.metrics.snapshot()["errors"].get("IterationTimeout") == 1
+    f2 = s.enqueue(Request([4, 5], max_tokens=1))
+    assert s.execute_iteration()                                   # after an overrun: no admission in this iteration
+    assert [r.id for r in s.batch_manager.running] in ([r1.id], []) and not f2.done()
+    s.run_until_idle()
+    assert f1.result().tokens == [7, 7] and f2.result().tokens == [7]
