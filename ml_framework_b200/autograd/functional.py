@@ -315,3 +315,235 @@ def scale_by_batch_size(grads: Sequence[torch.Tensor], batch_size: int, referenc
 def weighted_average(grad_sets: Sequence[Sequence[torch.Tensor]], weights: Sequence[float]):
     tot = float(sum(weights))
     return [sum(w * g for w, g in zip(weights, gs)) / tot for gs in zip(*grad_sets)]
+
+
+# ------------------------------------------------------------------ accumulation with varying batch sizes
+class DynamicBatchAccumulator:
+    """Accumulates per-batch *mean* gradients of batches of different sizes into the gradient of their union:
+    each contribution is weighted by its batch size and the result is divided by the accumulated size
+    (src/MLFramework/Autograd/DynamicBatchAccumulator.cs:74-150). ``target_batch_size == 0`` leaves completion to
+    the caller (fixed step count)."""
+
+    def __init__(self, target_batch_size: int = 0):
+        if target_batch_size < 0:
+            raise ValueError("target_batch_size cannot be negative")
+        self.target_batch_size = target_batch_size
+        self._sum: Optional[torch.Tensor] = None
+        self.accumulated_batch_size = 0
+        self.current_step = 0
+        self.accumulation_count = 0
+
+    def accumulate(self, batch_gradient: torch.Tensor, batch_size: int):
+        if batch_size < 1:
+            raise ValueError("batch size must be at least 1")
+        contrib = batch_gradient.detach() * float(batch_size)
+        if self._sum is None:
+            self._sum = contrib.clone()
+        elif self._sum.shape != contrib.shape:
+            raise RuntimeError("gradient shape mismatch in accumulation")
+        else:
+            self._sum += contrib
+        self.accumulated_batch_size += batch_size
+        self.current_step += 1
+        self.accumulation_count += 1
+
+    def is_complete(self) -> bool:
+        return self.target_batch_size > 0 and self.accumulated_batch_size >= self.target_batch_size
+
+    def get_accumulated_gradient(self) -> torch.Tensor:
+        if self._sum is None:
+            raise RuntimeError("nothing accumulated")
+        return self._sum / float(self.accumulated_batch_size)
+
+    @property
+    def accumulated_gradient(self) -> Optional[torch.Tensor]:
+        return None if self._sum is None else self.get_accumulated_gradient()
+
+    def get_progress(self) -> float:
+        if self.target_batch_size <= 0:
+            return 0.0
+        return min(1.0, self.accumulated_batch_size / self.target_batch_size)
+
+    def set_target_batch_size(self, n: int):
+        if n < 0:
+            raise ValueError("target_batch_size cannot be negative")
+        self.target_batch_size = n
+
+    def reset(self):
+        self._sum, self.accumulated_batch_size, self.current_step = None, 0, 0
+
+
+class GradientAccumulatorDynamic:
+    """Named gradient slots whose tensors may have symbolic (dynamic) shapes: a slot accepts a gradient whose
+    concrete shape is compatible with the slot's symbolic shape (``None`` / ``-1`` dimensions match anything) and
+    sums it into the running total (src/MLFramework/Autograd/GradientAccumulatorDynamic.cs:36-265, whose AddGradients
+    is a placeholder returning the first operand; here the sum is real). Gradients of different concrete sizes in a
+    dynamic dimension are summed after zero-padding to the largest."""
+
+    def __init__(self):
+        self._slots: Dict[str, Dict] = {}
+        self._closed = False
+
+    @staticmethod
+    def _compatible(shape, sym) -> bool:
+        if sym is None:
+            return True
+        sym = tuple(sym)
+        return len(shape) == len(sym) and all(s is None or s == -1 or isinstance(s, str) or int(s) == d for d, s in zip(shape, sym))
+
+    def accumulate(self, identifier: str, grad: torch.Tensor, shape=None):
+        if self._closed:
+            raise RuntimeError("accumulator is disposed")
+        if identifier is None or grad is None:
+            raise ValueError("identifier and gradient are required")
+        if not self._compatible(tuple(grad.shape), shape):
+            raise ValueError(f"gradient of shape {tuple(grad.shape)} does not match the symbolic shape {tuple(shape)}")
+        slot = self._slots.get(identifier)
+        g = grad.detach()
+        if slot is None:
+            self._slots[identifier] = {"grad": g.clone(), "shape": None if shape is None else tuple(shape), "count": 1}
+            return
+        if not self._compatible(tuple(g.shape), slot["shape"]):
+            raise ValueError(f"gradient of shape {tuple(g.shape)} does not match slot {identifier!r} of shape {slot['shape']}")
+        acc = slot["grad"]
+        if acc.shape != g.shape:
+            tgt = tuple(max(a, b) for a, b in zip(acc.shape, g.shape))
+
+            def pad(t):
+                out = t.new_zeros(tgt)
+                out[tuple(slice(0, d) for d in t.shape)] = t
+                return out
+            acc, g = pad(acc), pad(g)
+        slot["grad"] = acc + g
+        slot["count"] += 1
+
+    def accumulate_batched(self, identifier: str, grads: Sequence[torch.Tensor], shapes: Sequence):
+        if len(grads) != len(shapes):
+            raise ValueError(f"gradients and shapes must have the same length, got {len(grads)} and {len(shapes)}")
+        for g, s in zip(grads, shapes):
+            self.accumulate(identifier, g, s)
+
+    def get_accumulated(self, identifier: str, shape=None) -> Optional[torch.Tensor]:
+        slot = self._slots.get(identifier)
+        if slot is None:
+            return None
+        if shape is not None and not self._compatible(tuple(slot["grad"].shape), shape):
+            return None
+        return slot["grad"]
+
+    def get_accumulation_count(self, identifier: str) -> int:
+        slot = self._slots.get(identifier)
+        return 0 if slot is None else slot["count"]
+
+    def get_identifiers(self) -> List[str]:
+        return list(self._slots)
+
+    def has_gradient(self, identifier: str) -> bool:
+        return identifier in self._slots
+
+    def remove(self, identifier: str) -> bool:
+        return self._slots.pop(identifier, None) is not None
+
+    def reset(self):
+        self._slots.clear()
+
+    @property
+    def count(self) -> int:
+        return len(self._slots)
+
+    def dispose(self):
+        self._slots.clear()
+        self._closed = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.dispose()
+
+
+class VariableBatchScheduler:
+    """A fixed schedule of micro-batch sizes for one accumulation window
+    (src/MLFramework/Autograd/VariableBatchScheduler.cs:38-160)."""
+
+    def __init__(self, *batch_sizes):
+        sched = list(batch_sizes[0]) if len(batch_sizes) == 1 and isinstance(batch_sizes[0], (list, tuple)) else list(batch_sizes)
+        if not sched or any(int(b) < 1 for b in sched):
+            raise ValueError("the schedule needs at least one batch size and every size must be at least 1")
+        self.batch_schedule = [int(b) for b in sched]
+        self.current_step = 0
+
+    @property
+    def total_steps(self) -> int:
+        return len(self.batch_schedule)
+
+    @property
+    def effective_batch_size(self) -> int:
+        return sum(self.batch_schedule)
+
+    @property
+    def is_complete(self) -> bool:
+        return self.current_step >= len(self.batch_schedule)
+
+    def get_current_batch_size(self) -> int:
+        if self.is_complete:
+            raise RuntimeError("the schedule is complete")
+        return self.batch_schedule[self.current_step]
+
+    def get_remaining_steps(self) -> int:
+        return max(0, len(self.batch_schedule) - self.current_step)
+
+    def get_effective_batch_size(self, window_size: int) -> int:
+        if window_size < 1:
+            raise ValueError("window size must be at least 1")
+        return sum(self.batch_schedule[self.current_step:self.current_step + window_size])
+
+    def advance(self) -> bool:
+        if self.is_complete:
+            return False
+        self.current_step += 1
+        return True
+
+    def get_accumulated_batch_size(self) -> int:
+        return sum(self.batch_schedule[:self.current_step])
+
+    def get_progress(self) -> float:
+        return self.current_step / len(self.batch_schedule)
+
+    def reset(self):
+        self.current_step = 0
+
+
+class AccumulationContext:
+    """Counts micro-steps towards ``target_steps`` and scales registered tensors by ``1 / target_steps`` when ready
+    (src/MLFramework/Autograd/AccumulationContext.cs:39-90)."""
+
+    def __init__(self, target_steps: int):
+        if target_steps < 1:
+            raise ValueError("target_steps must be at least 1")
+        self.target_steps, self.accumulation_steps = target_steps, 0
+        self._tensors: List[torch.Tensor] = []
+
+    @property
+    def is_ready(self) -> bool:
+        return self.accumulation_steps >= self.target_steps
+
+    @property
+    def scaling_factor(self) -> float:
+        return 1.0 / self.target_steps
+
+    def register_tensor(self, t: torch.Tensor):
+        self._tensors.append(t)
+
+    def step(self):
+        self.accumulation_steps += 1
+
+    def reset(self):
+        self.accumulation_steps = 0
+        self._tensors.clear()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.reset()

@@ -23,6 +23,7 @@ void set_error(const char* fmt, ...) {
 
 int check_cuda(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return 0;
+  (void)cudaGetLastError();   // a recoverable failure (e.g. out of memory) must not be reported again by the next launch check
   set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
   return -1;
 }

@@ -288,6 +288,12 @@ __device__ __forceinline__ void chunk_slice(const GemmKernelParams& p, int n_fla
   const int owner = min(row0 / p.rows_per_rank, p.world - 1);
   src = static_cast<const char*>(p.src[owner]) + (long long)(row0 - owner * p.rows_per_rank) * p.row_bytes;
   dst = static_cast<char*>(p.gathered) + (long long)row0 * p.row_bytes;
+  if (src == dst) {
+    // the owner's rows already sit in the gathered buffer (the shard is a region of it): nothing to move,
+    // one zero-byte piece still publishes the chunk
+    lo = hi = 0;
+    return;
+  }
   const long long n16 = (long long)rows * p.row_bytes / 16;
   const long long per = (n16 + p.n_copy_ctas - 1) / p.n_copy_ctas;
   lo = min(n16, per * cta) * 16;

@@ -22,6 +22,7 @@ import torch
 import torch.nn as nn
 
 from .amp.grad_scaler import DynamicLossScaler, DynamicScalerConfig
+from .obs.profiler import nvtx_range
 from .optim.optimizers import AdamW
 from .parallel.flat import FlatParams
 
@@ -116,15 +117,18 @@ class TrainEngine:
         flat = self.flat
         flat.zero_grad()
         scale_t = self.scaler.scale_t if self.scaler is not None else None
-        loss = self.model(ids, targets, loss_scale=scale_t)
-        loss.backward()
+        with nvtx_range("forward"):
+            loss = self.model(ids, targets, loss_scale=scale_t)
+        with nvtx_range("backward"):
+            loss.backward()
         flat.gather_missing_grads()
         grad_scale = 1.0
         checked = False
         if self.reducer is not None:
             # buckets were all-reduced (and averaged) from the gradient-ready hooks while backward ran;
             # this reduces what the hooks could not and waits for the communication stream
-            self.reducer.finish()
+            with nvtx_range("ddp.finish_reductions"):
+                self.reducer.finish()
             checked = self.symm is not None      # the in-kernel all-reduce checks every reduced value
         if self.scaler is not None:
             from .ops import native

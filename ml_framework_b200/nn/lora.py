@@ -79,6 +79,52 @@ def matches_target(name: str, patterns: Sequence[str]) -> bool:
     return False
 
 
+class _LoraLinearFn(torch.autograd.Function):
+    """``y = x W^T + b (+ residual) + s * (x B^T) A^T`` on the tcgen05 GEMM with the adapter's second product
+    accumulated into the base product's output by its own epilogue (``MLF_EPI_ACCUM`` with ``alpha = s``): no
+    separate pass adds the two. Backward mirrors it: ``dx = dy W`` then ``+= (s dy A) B`` accumulated the same
+    way; ``dA = s dy^T h``, ``dB = (s dy A)^T x``; the frozen base weight gets no gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, lora_a, lora_b, scaling, residual):
+        from .. import _lib
+        from ..ops.gemm import gemm
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+        h = gemm(x2, lora_b)                                                     # [M, r]
+        y = gemm(x2, w, bias=bias, aux_in=res2, flags=_lib.EPI_RESIDUAL if residual is not None else 0)
+        gemm(h, lora_a, out=y, flags=_lib.EPI_ACCUM, alpha=float(scaling))       # y += s * h A^T, in the epilogue
+        ctx.save_for_backward(x2, h, w, lora_a, lora_b)
+        ctx.scaling, ctx.x_shape, ctx.has_res = float(scaling), x.shape, residual is not None
+        ctx.bias_ref = bias
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .. import _lib
+        from ..ops.gemm import gemm
+        x2, h, w, lora_a, lora_b = ctx.saved_tensors
+        s = ctx.scaling
+        dy2 = dy.reshape(-1, w.shape[0])
+        if dy2.stride(-1) != 1 or (dy2.stride(0) % 8) != 0:
+            dy2 = dy2.contiguous()
+        dh = gemm(dy2, lora_a, b_mn=True, alpha=s)                                # [M, r] = s * dy A
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True)
+            gemm(dh, lora_b, b_mn=True, out=dx, flags=_lib.EPI_ACCUM)             # dx += dh B
+            dx = dx.view(ctx.x_shape)
+        da = gemm(dy2, h, a_mn=True, b_mn=True, alpha=s) if ctx.needs_input_grad[3] else None   # [out, r]
+        db = gemm(dh, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[4] else None            # [r, in]
+        dbias = None
+        if ctx.bias_ref is not None and ctx.needs_input_grad[2]:
+            dbias = Fm._bgrad(dy2, ctx.bias_ref)
+        return dx, None, dbias, da, db, None, (dy if ctx.has_res else None)
+
+
 class LoRAAdapterBase(nn.Module):
     merged: bool = False
     enabled: bool = True
@@ -121,9 +167,13 @@ class LoraLinear(LoRAAdapterBase):
         return getattr(self.base, "bias", None)
 
     def forward(self, x, residual=None):
-        y = self.base(x, residual) if residual is not None else self.base(x)
         if self.merged or not self.enabled:
-            return y
+            return self.base(x, residual) if residual is not None else self.base(x)
+        w, b = self.base.weight, getattr(self.base, "bias", None)
+        if (isinstance(self.dropout, nn.Identity) and self.cfg.rank % 8 == 0 and w.dim() == 2
+                and Fm._native(x, w, b, self.lora_A, self.lora_B, residual)):
+            return _LoraLinearFn.apply(x, w, b, self.lora_A, self.lora_B, self.scaling, residual)
+        y = self.base(x, residual) if residual is not None else self.base(x)
         h = Fm.linear(self.dropout(x), self.lora_B)          # [.., rank]
         return y + Fm.linear(h, self.lora_A) * self.scaling
 

@@ -205,3 +205,109 @@ class GpuUtilizationTracker:
             return {}
         ks = [k for k in self.samples[0] if k not in ("time", "throttle_reasons")]
         return {k: sum(s.get(k, 0) for s in self.samples) / len(self.samples) for k in ks}
+
+
+# ------------------------------------------------------------------ NVTX ranges and timeline export
+_NVTX_ENABLED = False
+
+
+def enable_nvtx(on: bool = True):
+    """NVTX ranges cost a push / pop each even with no tool attached; they are off until enabled (``MLF_NVTX=1`` in
+    the environment enables them at import)."""
+    global _NVTX_ENABLED
+    _NVTX_ENABLED = bool(on) and torch.cuda.is_available()
+
+
+def nvtx_enabled() -> bool:
+    return _NVTX_ENABLED
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """Named range on the calling thread, visible in Nsight Systems / Nsight Compute timelines and in
+    ``torch.profiler`` traces (as user annotations). The engine and the parallel wrappers mark forward, backward,
+    optimizer and each collective with it."""
+    if not _NVTX_ENABLED:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
+def nvtx_mark(name: str):
+    if _NVTX_ENABLED:
+        torch.cuda.nvtx.mark(name)
+
+
+class TimelineProfiler:
+    """Kernel-level timeline of a few steps through ``torch.profiler`` (CUPTI under the hood), exported as a Chrome
+    trace; ranges opened with :func:`nvtx_range` / ``record_function`` appear as annotations. For analysis only:
+    numbers measured while it runs are not benchmark results.
+
+        with TimelineProfiler("trace.json", steps=3) as tp:
+            for _ in range(3):
+                engine.step(ids, tgt); tp.step()
+        print(tp.top_kernels(10))
+    """
+
+    def __init__(self, path: Optional[str] = None, steps: int = 3, with_stack: bool = False, record_shapes: bool = False):
+        self.path, self.steps = path, steps
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if torch.cuda.is_available():
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self._prof = torch.profiler.profile(activities=acts, with_stack=with_stack, record_shapes=record_shapes)
+        self._n = 0
+
+    def __enter__(self):
+        self._prof.__enter__()
+        return self
+
+    def step(self):
+        self._n += 1
+
+    def __exit__(self, *a):
+        self._prof.__exit__(*a)
+        if self.path:
+            self._prof.export_chrome_trace(self.path)
+
+    def top_kernels(self, n: int = 10) -> List[Tuple[str, float, int]]:
+        """(name, total device microseconds, calls) of the kernels that took the most device time."""
+        rows = []
+        for e in self._prof.key_averages():
+            dev = getattr(e, "device_time_total", None)
+            if dev is None:
+                dev = getattr(e, "cuda_time_total", 0.0)
+            if dev and dev > 0:
+                rows.append((e.key, float(dev), int(e.count)))
+        rows.sort(key=lambda r: -r[1])
+        return rows[:n]
+
+
+class annotate(contextlib.ContextDecorator):
+    """``with annotate("forward"):`` = an NVTX range (when enabled) and a ``torch.profiler.record_function`` scope."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self._rf = None
+
+    def __enter__(self):
+        if _NVTX_ENABLED:
+            torch.cuda.nvtx.range_push(self.name)
+        self._rf = torch.profiler.record_function(self.name)
+        self._rf.__enter__()
+        return self
+
+    def __exit__(self, *a):
+        self._rf.__exit__(*a)
+        if _NVTX_ENABLED:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
+import os as _os  # noqa: E402
+
+if _os.environ.get("MLF_NVTX") == "1":
+    enable_nvtx(True)

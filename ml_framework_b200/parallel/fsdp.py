@@ -40,6 +40,7 @@ import torch
 import torch.nn as nn
 
 from ..dist.process_group import ReduceOp
+from ..obs.profiler import nvtx_range
 from ..ops import native, reference
 
 
@@ -643,8 +644,9 @@ class FSDP:
 
     def _post_backward(self, i: int):
         u = self.units[i]
-        self._reduce_unit(u, u._gbuf)
-        self._offload_unit_grads(u)
+        with nvtx_range(f"fsdp.reduce_scatter.{u.name}"):
+            self._reduce_unit(u, u._gbuf)
+            self._offload_unit_grads(u)
 
     def _offload_unit_grads(self, u: FSDPUnit):
         """``offload_gradients``: the reduced gradient pieces leave for pinned host memory as soon as they exist
@@ -670,13 +672,17 @@ class FSDP:
                 self._gather_unit(root, root.gathered)
             self._point_params(root, root.gathered, root.grad_full)
         scale_t = scaler.scale_t if scaler is not None else None
-        loss = self.model(ids, targets, loss_scale=scale_t)
-        loss.backward()
-        if root is not None:
-            self._reduce_unit(root, root.grad_full)
-            self._offload_unit_grads(root)
-        self._finish_replicated()
-        self.step(scaler)
+        with nvtx_range("fsdp.forward"):
+            loss = self.model(ids, targets, loss_scale=scale_t)
+        with nvtx_range("fsdp.backward"):
+            loss.backward()
+        with nvtx_range("fsdp.reduce_root_and_replicated"):
+            if root is not None:
+                self._reduce_unit(root, root.grad_full)
+                self._offload_unit_grads(root)
+            self._finish_replicated()
+        with nvtx_range("fsdp.optimizer"):
+            self.step(scaler)
         return loss
 
     def _finish_replicated(self):

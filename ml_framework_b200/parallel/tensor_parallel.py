@@ -156,27 +156,55 @@ def scatter_tokens(x, tp): return _ScatterTokens.apply(x, tp)
 
 
 # ------------------------------------------------------------------ fused kernels (GPU, peer memory)
+def _copy_ctas_for(tp: TPContext, flops: float, link_bytes: float) -> int:
+    """Copy CTAs of a gather GEMM: enough of them (about 40 GB/s each) to move the remote rows in the time the
+    product takes, or in the time the links need when those are the bound; between 8 and 32."""
+    t = max(flops / 1.4e15, link_bytes / 700e9, 1e-6)
+    return int(min(32, max(8, -(-link_bytes // (40e9 * t)))))
+
+
 def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: str, bias=None, flags=0, aux_out=None,
-                   b_mn: bool = False):
+                   b_mn: bool = False, persistent: bool = True):
     """out[T, N] = all_gather_tokens(x_shard)[T, K] @ B in one kernel, B = w[N, K]^T or, with ``b_mn``, w[K, N].
-    Returns (out, x_full)."""
+    Returns (out, x_full).
+
+    The gathered operand lives in a symmetric buffer ``[T, K]`` per ``key``: this rank's shard is written into its own
+    row range there, the peers pull exactly that range, and the copy CTAs of the GEMM fetch only the W - 1 remote
+    ranges (the local rows need no copy). ``persistent`` buffers are one per key (the forward operand is kept for the
+    weight gradient); otherwise two buffers per shape alternate between calls (backward operands are consumed at once)."""
     rows, K = x_shard.shape
     W, T = tp.world, x_shard.shape[0] * tp.world
-    stage = tp.symm_buffer(key + ".ag_stage", rows * K * 2)
-    stage.view(torch.bfloat16, rows * K).view(rows, K).copy_(x_shard)
-    tp.symm.barrier()                                   # every peer's stage is written
-    x_full = torch.empty(T, K, dtype=torch.bfloat16, device=x_shard.device)
+    live = tp.__dict__.setdefault("_ag_live", {})
+    if persistent and live.get(key, 0) > 0:
+        # the buffer of this key still holds an operand whose backward has not run (several micro-batches in flight
+        # without recomputation): this call gathers into memory of its own from a staged copy of the shard
+        stage = tp.symm_buffer(key + ".ag_stage", rows * K * 2)
+        stage.view(torch.bfloat16, rows * K).view(rows, K).copy_(x_shard)
+        x_full = torch.empty(T, K, dtype=torch.bfloat16, device=x_shard.device)
+        src = [stage.ptrs[r] for r in range(W)]
+    else:
+        if persistent:
+            buf = tp.symm_buffer(key + ".ag_full", T * K * 2)
+        else:
+            n = tp._ag_calls = getattr(tp, "_ag_calls", 0) + 1
+            buf = tp.symm_buffer(f"ag_tmp{n % 2}.{T}x{K}", T * K * 2)
+        x_full = buf.view(torch.bfloat16, T * K).view(T, K)
+        x_full[tp.rank * rows:(tp.rank + 1) * rows].copy_(x_shard)
+        src = [buf.ptrs[r] + r * rows * K * 2 for r in range(W)]     # rank r's own rows inside rank r's buffer
+    tp.symm.barrier()                                   # every peer's rows are written
     flag_rows = 128
     while rows % flag_rows:
         flag_rows //= 2
     nfl = T // max(flag_rows, 1)
     fl = tp.flags(nfl, x_shard.device)
     fl.zero_()
+    N = w.shape[1] if b_mn else w.shape[0]
     cm = _lib.GemmComm()
-    cm.gather_operand, cm.world, cm.rank, cm.n_copy_ctas = 1, W, tp.rank, tp.n_copy_ctas
+    cm.gather_operand, cm.world, cm.rank = 1, W, tp.rank
+    cm.n_copy_ctas = _copy_ctas_for(tp, 2.0 * T * K * N, (W - 1) * rows * K * 2.0)
     cm.rows_per_rank, cm.flag_rows, cm.row_bytes = rows, flag_rows, K * 2
     for r in range(W):
-        cm.src[r] = stage.ptrs[r]
+        cm.src[r] = src[r]
     cm.gathered, cm.flags, cm.counters = x_full.data_ptr(), fl.data_ptr(), fl[nfl:].data_ptr()
     out = gemm(x_shard, w, comm=cm, m_override=T, bias=bias, flags=flags, aux_out=aux_out, b_mn=b_mn)
     return out, x_full
@@ -216,6 +244,10 @@ class _ColumnSPFused(torch.autograd.Function):
         out, x_full = _fused_ag_gemm(tp, x_shard, w, key, bias=b)
         ctx.save_for_backward(x_full, w)
         ctx.tp, ctx.key, ctx.b = tp, key, b
+        ctx.counted = torch.is_grad_enabled() or any(ctx.needs_input_grad[:3])
+        if ctx.counted:
+            live = tp.__dict__.setdefault("_ag_live", {})
+            live[key] = live.get(key, 0) + 1          # the key's gathered buffer is spoken for until backward has read it
         return out
 
     @staticmethod
@@ -225,6 +257,9 @@ class _ColumnSPFused(torch.autograd.Function):
         dx_shard = _fused_gemm_rs(ctx.tp, dy, w, ctx.key + ".bwd", b_mn=True)
         dw = Fm._wgrad(dy, x_full, w)
         db = Fm._bgrad(dy, ctx.b)
+        if ctx.counted:
+            live = ctx.tp.__dict__.setdefault("_ag_live", {})
+            live[ctx.key] = max(0, live.get(ctx.key, 0) - 1)
         return dx_shard, dw, db, None, None
 
 
@@ -246,7 +281,7 @@ class _RowSPFused(torch.autograd.Function):
         tp = ctx.tp
         if tp.fused:
             # the gathered operand (dY rows) is K-major; W is read as [K = out, N = in/W] (MN-major B)
-            dx, dy_full = _fused_ag_gemm(tp, dy_shard, w, ctx.key + ".bwd", b_mn=True)
+            dx, dy_full = _fused_ag_gemm(tp, dy_shard, w, ctx.key + ".bwd", b_mn=True, persistent=False)
         else:
             dy_full = tp.pg.all_gather(dy_shard, dim=0)
             dx = gemm(dy_full, w, b_mn=True)

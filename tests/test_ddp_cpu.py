@@ -104,16 +104,23 @@ def test_launcher_env_logs_and_first_failure(tmp_path):
         launch_multi_node()
 
 
-@pytest.mark.timeout(180)
+@pytest.mark.timeout(360)
 def test_cpu_mlp_ddp_two_gloo_ranks(tmp_path):
-    l = ProcessLauncher(master_port=_free_port(), log_dir=str(tmp_path))
-    l.launch([sys.executable, os.path.join(ROOT, "baseline", "cpu_mlp_ddp.py"), "100"], 2)
-    ok = l.wait_for_all(timeout_s=150)
-    log = (tmp_path / "rank_0.log").read_text()
-    assert ok, log + (tmp_path / "rank_1.log").read_text()
+    log = ""
+    for attempt in range(2):          # a second rendezvous on a fresh port if the first one could not be set up
+        d = tmp_path / f"try{attempt}"
+        l = ProcessLauncher(master_port=_free_port(), log_dir=str(d))
+        l.launch([sys.executable, os.path.join(ROOT, "baseline", "cpu_mlp_ddp.py"), "100"], 2)
+        ok = l.wait_for_all(timeout_s=150)
+        log = (d / "rank_0.log").read_text()
+        if ok:
+            break
+        log += (d / "rank_1.log").read_text()
+        if "rendezvous" not in log.lower() and "address" not in log.lower() and "connect" not in log.lower():
+            break
+    assert ok, log[-4000:]
     res = json.loads([ln for ln in log.splitlines() if ln.startswith("{")][-1])
     assert res["gradients_equal_across_ranks"] and res["parameters_in_sync"] and res["steps"] == 100
-
 
 def test_ddp_no_sync_keeps_local_gradients_then_matches_big_batch():
     """One micro-step inside no_sync() plus one synchronised micro-step: inside, gradients stay local

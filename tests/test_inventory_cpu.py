@@ -572,3 +572,204 @@ def test_config_loader_file_env_and_validation(tmp_path):
     assert ec.max_batch == 64 and ec.use_cuda_graphs is True
     with pytest.raises(ValueError):
         load_config(FSDPConfig, {"sharding_strategy": "diagonal"})
+
+
+def test_mixed_precision_optimizer_skip_clip_fallback_and_monitor():
+    from ml_framework_b200.optim.mixed_precision import (MixedPrecisionOptimizer, MixedPrecisionOptions, PerformanceMonitor,
+                                                         PrecisionManager)
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.LayerNorm(16), torch.nn.Linear(16, 4))
+    opts = MixedPrecisionOptions(precision="bf16", initial_loss_scale=1024.0, max_consecutive_overflows=3, max_grad_norm=0.5)
+    mp = MixedPrecisionOptimizer(net, lambda ps: torch.optim.SGD(ps, lr=0.1), opts)
+    # linears train in bf16, the norm stays fp32 (sensitive-layer patterns), masters are fp32
+    assert net[0].weight.dtype == torch.bfloat16 and net[1].weight.dtype == torch.float32
+    assert all(m.dtype == torch.float32 for m in mp.masters.values())
+    x, y = torch.randn(32, 8), torch.randn(32, 4)
+
+    def fwd():
+        h = torch.nn.functional.linear(x.to(net[0].weight.dtype), net[0].weight, net[0].bias).float()
+        h = net[1](h)
+        return torch.nn.functional.linear(h.to(net[2].weight.dtype), net[2].weight, net[2].bias).float()
+    first = None
+    for _ in range(20):
+        mp.zero_grad()
+        loss = (fwd() - y).pow(2).mean()
+        first = first if first is not None else loss.item()
+        mp.scale_loss(loss).backward()
+        assert mp.step()
+        assert mp.last_grad_norm is not None
+    assert loss.item() < first and mp.get_stats().skipped_steps == 0 and mp.get_stats().performance.step_count == 20
+    # three overflowing steps in a row: skipped, scale backs off, then fp32 for good
+    before = {k: v.detach().clone() for k, v in mp.masters.items()}
+    for i in range(3):
+        mp.zero_grad()
+        (fwd() - y).pow(2).mean().backward()
+        net[0].weight.grad[0, 0] = float("inf")
+        assert not mp.step()
+    st = mp.get_stats()
+    assert st.skipped_steps == 3 and st.has_fallback and st.target_precision == "fp32" and st.loss_scale == 128.0
+    assert all(torch.equal(before[k], v) for k, v in mp.masters.items())
+    assert net[0].weight.dtype == torch.float32 and abs(st.skip_rate - 3 / 23) < 1e-9
+    mp.zero_grad()
+    (fwd() - y).pow(2).mean().backward()
+    assert mp.step()                                                  # trains on in fp32
+    sd = mp.state_dict()
+    assert sd["has_fallback"] and set(sd["masters"]) == set(mp.masters)
+    pm = PrecisionManager(MixedPrecisionOptions(precision="fp16"))
+    assert pm.should_exclude_layer("encoder.LayerNorm.weight") and not pm.should_exclude_layer("encoder.fc.weight")
+    pm.exclude_layers_matching("*head*")
+    assert pm.convert_to_training_precision(torch.ones(2), "lm_head.weight").dtype == torch.float32
+    assert pm.convert_to_training_precision(torch.ones(2), "fc.weight").dtype == torch.float16
+    assert pm.remove_exclusion("*head*") and pm.stats.excluded_layers == 1
+    t = iter([0.0, 0.010, 0.010, 0.040])
+    mon = PerformanceMonitor(clock=lambda: next(t))
+    mon.start_step(); mon.end_step(); mon.start_step(); mon.end_step()
+    s = mon.get_stats()
+    assert s.step_count == 2 and abs(s.average_step_time_ms - 20.0) < 1e-6 and abs(s.max_step_time_ms - 30.0) < 1e-6
+    with pytest.raises(ValueError):
+        MixedPrecisionOptions(precision="int8").validate()
+
+
+def test_dynamic_batch_accumulation_matches_big_batch_gradient():
+    from ml_framework_b200.autograd.functional import (AccumulationContext, DynamicBatchAccumulator, GradientAccumulatorDynamic,
+                                                       VariableBatchScheduler)
+    torch.manual_seed(0)
+    w = torch.randn(5, 3, requires_grad=True)
+    x, y = torch.randn(12, 5), torch.randn(12, 3)
+    ((x @ w - y) ** 2).mean(dim=1).mean().backward()
+    want = w.grad.clone()
+    sched = VariableBatchScheduler(2, 6, 4)
+    assert sched.effective_batch_size == 12 and sched.get_effective_batch_size(2) == 8
+    acc = DynamicBatchAccumulator(target_batch_size=12)
+    lo = 0
+    while not sched.is_complete:
+        b = sched.get_current_batch_size()
+        w.grad = None
+        ((x[lo:lo + b] @ w - y[lo:lo + b]) ** 2).mean(dim=1).mean().backward()     # mean over ITS batch
+        acc.accumulate(w.grad, b)
+        lo += b
+        sched.advance()
+    assert acc.is_complete() and acc.get_progress() == 1.0 and sched.get_accumulated_batch_size() == 12
+    assert torch.allclose(acc.get_accumulated_gradient(), want, atol=1e-6)
+    with pytest.raises(RuntimeError):
+        acc.accumulate(torch.zeros(2, 2), 1)
+    acc.reset()
+    assert acc.accumulated_gradient is None and not sched.advance()
+    # named slots with a dynamic leading dimension
+    with GradientAccumulatorDynamic() as dyn:
+        dyn.accumulate("emb", torch.ones(3, 4), ("batch", 4))
+        dyn.accumulate("emb", 2 * torch.ones(5, 4), (None, 4))
+        assert dyn.get_accumulation_count("emb") == 2 and dyn.count == 1
+        got = dyn.get_accumulated("emb")
+        assert got.shape == (5, 4) and got[:3].eq(3).all() and got[3:].eq(2).all()
+        with pytest.raises(ValueError):
+            dyn.accumulate("emb", torch.ones(3, 5), ("batch", 4))
+        with pytest.raises(ValueError):
+            dyn.accumulate_batched("x", [torch.ones(1)], [])
+        assert dyn.remove("emb") and not dyn.has_gradient("emb")
+    with pytest.raises(RuntimeError):
+        dyn.accumulate("emb", torch.ones(1, 4))
+    ctx = AccumulationContext(4)
+    for _ in range(4):
+        ctx.step()
+    assert ctx.is_ready and ctx.scaling_factor == 0.25
+
+
+def test_quantization_backend_factory_and_cpu_backend():
+    from ml_framework_b200.quantization.backends import BackendCapabilityFlags, BackendFactory, CPUBackend
+    from ml_framework_b200.quantization.core import compute_qparams
+    BackendFactory.clear_cache()
+    assert "CPU" in BackendFactory.get_available_backends()
+    assert isinstance(BackendFactory.create("x86"), CPUBackend) and BackendFactory.create("ARM NEON") is BackendFactory.create("cpu")
+    with pytest.raises(ValueError):
+        BackendFactory.create("tpu")
+    BackendFactory.set_preferred_backend("CPU")
+    be = BackendFactory.create_default()
+    assert be.get_name() == "CPU"
+    caps = be.get_capabilities()
+    assert caps.supports(BackendCapabilityFlags.INT8_MATMUL) and not caps.supports(BackendCapabilityFlags.MIXED_PRECISION)
+    assert "INT8_MATMUL" in str(caps)
+    torch.manual_seed(0)
+    a, b = torch.randn(6, 16), torch.randn(16, 5)
+    qa, qb = compute_qparams(a.min(), a.max()), compute_qparams(b.min(), b.max())
+    ia, ib = be.quantize(a, qa), be.quantize(b, qb)
+    y = be.matmul_int8(ia, ib, float(qa.scale * qb.scale))
+    assert torch.allclose(y, be.dequantize(ia, qa) @ be.dequantize(ib, qb), atol=1e-5)
+    assert (y - a @ b).abs().max() < 0.2
+    x, w = torch.randint(-20, 20, (1, 2, 5, 5), dtype=torch.int8), torch.randint(-20, 20, (3, 2, 3, 3), dtype=torch.int8)
+    yc = be.conv2d_int8(x, w, torch.ones(3), padding=(1, 1), output_scale=0.5)
+    ref = torch.nn.functional.conv2d(x.float(), w.float(), None, padding=1) * 0.5 + 1.0
+    assert torch.equal(yc, ref)
+    assert be.infer(torch.nn.Linear(4, 2), torch.ones(1, 4)).shape == (1, 2)
+    BackendFactory.set_preferred_backend(None)
+
+
+def test_external_hubs_with_a_fake_transport():
+    import json as _json
+    from ml_framework_b200.modelzoo.hubs import (ApiKeyAuth, HubError, HubRegistry, HuggingFaceHub, HuggingFaceHubConfiguration,
+                                                 ONNXHub, TensorFlowHub, is_local_model, parse_model_id)
+    c = parse_model_id("hub:huggingface/bert-base-uncased/v2/fp16")
+    assert (c.hub_name, c.model_name, c.version, c.variant) == ("huggingface", "bert-base-uncased", "v2", "fp16")
+    assert c.full_id == "hub:huggingface/bert-base-uncased/v2/fp16" and not c.is_local
+    assert parse_model_id("hub:corp:registry/model").hub_name == "corp" and parse_model_id("resnet50").is_local
+    assert is_local_model("resnet50") and not is_local_model("hub:hf/x")
+    with pytest.raises(ValueError):
+        parse_model_id("hub:nomodel")
+    calls, fail = [], {"n": 2}
+
+    def transport(method, url, headers, timeout):
+        calls.append((method, url, dict(headers)))
+        if "flaky" in url and fail["n"] > 0:
+            fail["n"] -= 1
+            raise OSError("connection reset")
+        if url.endswith("/api/models/org/tiny"):
+            body = _json.dumps({"modelId": "org/tiny", "author": "org", "downloads": 5, "likes": 1, "library_name": "pytorch",
+                                "config": {"model_type": "llama"}, "siblings": [{"rfilename": "config.json"}, {"rfilename": "model.safetensors"}]})
+            return 200, {}, body.encode()
+        if url.endswith("/org/tiny/resolve/main/model.safetensors") or "flaky" in url:
+            return 200, {}, b"WEIGHTS"
+        if "tfhub" in url and "google/bert" in url:
+            return 200, {"Content-Length": "7"}, b"TFMODEL"
+        if url.endswith("/validated/vision/latest/resnet/model/resnet.onnx"):
+            return 200, {}, b"ONNX"
+        return 404, {}, b""
+    hf = HuggingFaceHub(HuggingFaceHubConfiguration(api_token="tok", use_mirror=True, mirror_url="https://mirror.example",
+                                                    retry_delay_seconds=0.0), transport=transport, sleep=lambda s: None)
+    md = hf.get_model_metadata("hub:hf/org/tiny")
+    assert md.model_name == "org/tiny" and md.architecture == "llama" and md.custom["author"] == "org"
+    assert calls[-1][1] == "https://mirror.example/api/models/org/tiny" and calls[-1][2]["Authorization"] == "Bearer tok"
+    seen = []
+    assert hf.download_model("hub:huggingface/org/tiny", progress=seen.append) == b"WEIGHTS" and seen == [100.0]
+    assert hf.model_exists("org/tiny") and not hf.model_exists("org/none")
+    assert hf.download_model("org/flaky", filename="w.bin") == b"WEIGHTS" and fail["n"] == 0      # two transport errors, then success
+    with pytest.raises(HubError):
+        hf.get_model_metadata("org/none")
+    reg = HubRegistry()
+    reg.register_default_hubs(transport=transport)
+    assert reg.list_hubs() == ["huggingface", "tensorflow", "onnx"] and reg.get_default_hub().hub_name == "huggingface"
+    assert isinstance(reg.get_hub_for_model("hub:tfhub/google/bert"), TensorFlowHub)
+    assert isinstance(reg.get_hub_for_model("hub:onnx/resnet"), ONNXHub) and reg.get_hub_for_model("hub:other/x") is None
+    assert reg.download("hub:onnx/resnet") == b"ONNX"
+    tf = reg.get_hub("tensorflow")
+    assert tf.model_exists("hub:tf/google/bert") and tf.get_model_metadata("hub:tf/google/bert").custom["content_length"] == "7"
+    assert tf.download_model("hub:tf/google/bert") == b"TFMODEL"
+    assert reg.set_default_hub("onnx") and reg.unregister_hub("onnx") and reg.get_default_hub().hub_name == "huggingface"
+    with pytest.raises(ValueError):
+        reg.register_hub(HuggingFaceHub(transport=transport))
+    assert ApiKeyAuth("k").get_auth_header() == ("X-API-Key", "k")
+
+
+def test_nvtx_ranges_and_timeline_profiler_on_cpu(tmp_path):
+    from ml_framework_b200.obs.profiler import TimelineProfiler, annotate, enable_nvtx, nvtx_enabled, nvtx_mark, nvtx_range
+    enable_nvtx(True)
+    assert nvtx_enabled() == torch.cuda.is_available()         # without a GPU the ranges stay no-ops
+    with nvtx_range("outer"):
+        nvtx_mark("point")
+    out = tmp_path / "trace.json"
+    with TimelineProfiler(str(out), steps=1) as tp:
+        with annotate("matmul-step"):
+            (torch.randn(64, 64) @ torch.randn(64, 64)).sum()
+        tp.step()
+    text = out.read_text()
+    assert "traceEvents" in text and "matmul-step" in text
+    enable_nvtx(False)

@@ -78,3 +78,19 @@ def test_cuda_graph_manager_captures_and_replays():
     pool = GraphMemoryPool(1 << 20)
     a = pool.allocate((128, 4), torch.bfloat16)
     assert a.is_cuda and a.data_ptr() % 256 == 0
+
+
+def test_gpu_quantization_backend_int8_matmul_on_the_tensor_cores():
+    from ml_framework_b200.quantization.backends import B200Backend, BackendFactory
+    from ml_framework_b200.quantization.core import compute_qparams
+    BackendFactory.clear_cache()
+    be = BackendFactory.create_default()
+    assert isinstance(be, B200Backend) and be.get_name() == "GPU"
+    torch.manual_seed(0)
+    a, b = torch.randn(256, 512, device="cuda"), torch.randn(512, 384, device="cuda")
+    qa, qb = compute_qparams(a.min(), a.max()), compute_qparams(b.min(), b.max())
+    ia, ib = be.quantize(a, qa), be.quantize(b, qb)
+    y = be.matmul_int8(ia, ib, float(qa.scale * qb.scale))
+    exact = (ia.to(torch.int32).cpu() @ ib.to(torch.int32).cpu()).float().cuda() * float(qa.scale * qb.scale)
+    assert torch.allclose(y, exact, atol=1e-3, rtol=1e-4)          # int8 products accumulate exactly in fp32 up to rounding
+    assert (y - a @ b).abs().max() < 1.5
