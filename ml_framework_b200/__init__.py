@@ -7,6 +7,13 @@ compute+collective kernels.
 """
 __version__ = "0.1.0"
 
+import os as _os
+
+# Kernels of the native library wait on one another across GPUs (device barriers, gathered chunks). With lazy module
+# loading the first launch of a kernel may have to synchronise the context while such a wait is in progress, so all
+# modules are loaded when the library is (effective when set before the CUDA context exists; an explicit setting wins).
+_os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
 from . import _lib  # noqa: F401
 
 

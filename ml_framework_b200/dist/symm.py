@@ -74,6 +74,11 @@ class SymmetricMemory:
         nbytes = (nbytes + 255) // 256 * 256
         if self.emulate:
             raise RuntimeError("use alloc_emulated() in emulate mode")
+        if self.world > 1 and self.device.type == "cuda":
+            # Allocation, handle export and the handle exchange block the host. Every rank reaches this call at the
+            # same point of its program, so each one first lets its own queued kernels finish (their counterparts on
+            # the peers are queued before the peers' own call): no GPU is left spinning on a peer while hosts wait.
+            torch.cuda.synchronize(self.device)
         ptr = C.c_void_p()
         handle = (C.c_ubyte * 64)()
         _lib.check(self._lib.mlf_symm_alloc(C.c_longlong(nbytes), C.byref(ptr), handle), "mlf_symm_alloc")

@@ -34,6 +34,11 @@ from ..ops import functional as Fm
 from ..ops.gemm import gemm
 
 
+import os as _os
+
+_DEBUG_ALLOC = _os.environ.get("MLF_DEBUG_ALLOC") == "1"     # log every collective buffer allocation with its time
+
+
 # ------------------------------------------------------------------ context
 class TPContext:
     """Tensor-parallel group state: communicator, rank, and the fused-kernel resources."""
@@ -51,6 +56,9 @@ class TPContext:
     def symm_buffer(self, key: str, nbytes: int):
         k = (key, nbytes)
         if k not in self._bufs:
+            if _DEBUG_ALLOC:
+                import sys, time
+                print(f"[tp alloc] rank {self.rank} t={time.time() % 1000:.3f} {key} {nbytes}", file=sys.stderr, flush=True)
             self._bufs[k] = self.symm.alloc(nbytes)
         return self._bufs[k]
 
@@ -216,7 +224,9 @@ def _fused_gemm_rs(tp: TPContext, a: torch.Tensor, b: torch.Tensor, key: str, *,
     N = b.shape[1] if b_mn else b.shape[0]
     W = tp.world
     rows = T // W
-    part = tp.symm_buffer(key + ".rs_part", W * rows * N * 2)
+    # one partial buffer per shape, shared by every layer: the barrier below is exactly what makes reuse safe (all
+    # ranks have queued the previous call's local sum before anyone's GEMM writes new partial tiles)
+    part = tp.symm_buffer(f"rs_part.{rows}x{N}", W * rows * N * 2)
     tp.symm.barrier()                                   # previous consumers of the partial buffers are done
     cm = _lib.GemmComm()
     cm.scatter_out, cm.rows_per_owner, cm.world, cm.rank = 1, rows, W, tp.rank

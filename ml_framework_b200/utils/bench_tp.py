@@ -30,9 +30,13 @@ def main(argv=None):
     ap.add_argument("--no-fused", action="store_true")
     a = ap.parse_args(argv)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if os.environ.get("MLF_HANG_DUMP_S"):
+        # a rank that is still running after this many seconds prints every thread's Python stack and exits
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ["MLF_HANG_DUMP_S"]), exit=True)
     from ..dist.process_group import destroy_process_group, init_process_group
     from ..modelzoo.zoo import default_registry
-    pg = init_process_group("nccl")
+    pg = init_process_group("nccl", timeout_s=float(os.environ.get("MLF_PG_TIMEOUT_S", "120")))
     W, r = pg.world_size, pg.rank
     dev = torch.device("cuda", torch.cuda.current_device())
     info = default_registry().get(a.model)
