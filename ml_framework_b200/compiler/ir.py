@@ -284,38 +284,326 @@ class PassManager:
         return g
 
 
-# ------------------------------------------------------------------ lowering
-def lower_to_loops(g: HLGraph) -> List[str]:
-    """Mid-level listing: explicit allocation, loop nests and broadcasts."""
-    out = []
+# ------------------------------------------------------------------ mid level: buffers, explicit broadcasts, loop nests
+@dataclass
+class MLStmt:
+    """One statement of the mid-level IR. ``kind``:
+    ``alloc`` (dst), ``broadcast`` (src -> dst of the statement's shape), ``map`` (element-wise ``fn`` over sources that
+    all have the destination's shape: broadcasting is explicit at this level), ``contract`` (dst[.., m, n] = sum_k
+    lhs[.., m, k] * rhs[.., k, n]), ``reduce`` (``fn`` over ``dims``), ``call`` (an op kept whole: conv, pool, norm,
+    softmax, reshape ...)."""
+    kind: str
+    dst: str
+    srcs: List[str] = field(default_factory=list)
+    fn: str = ""
+    attrs: dict = field(default_factory=dict)
+
+
+class MLProgram:
+    def __init__(self, name: str):
+        self.name = name
+        self.buffers: Dict[str, Tuple[Tuple[int, ...], torch.dtype]] = {}
+        self.consts: Dict[str, torch.Tensor] = {}
+        self.inputs: List[str] = []
+        self.outputs: List[str] = []
+        self.stmts: List[MLStmt] = []
+
+    def verify(self) -> List[str]:
+        errs, ready = [], set(self.inputs) | set(self.consts)
+        allocated = set(ready)
+        for i, st in enumerate(self.stmts):
+            if st.kind == "alloc":
+                if st.dst in allocated:
+                    errs.append(f"stmt #{i}: buffer {st.dst} allocated twice")
+                allocated.add(st.dst)
+                continue
+            for n in st.srcs:
+                if n not in ready:
+                    errs.append(f"stmt #{i} {st.kind}: read of {n} before it is written")
+            if st.dst not in allocated:
+                errs.append(f"stmt #{i} {st.kind}: write to unallocated buffer {st.dst}")
+            if st.kind == "map":
+                for n in st.srcs:
+                    if self.buffers[n][0] != self.buffers[st.dst][0]:
+                        errs.append(f"stmt #{i} map: operand {n} {self.buffers[n][0]} differs from {st.dst} {self.buffers[st.dst][0]}"
+                                    " (broadcasts are explicit at this level)")
+            ready.add(st.dst)
+        errs += [f"output {n} never written" for n in self.outputs if n not in ready]
+        return errs
+
+    def run(self, feeds: Dict[str, torch.Tensor]) -> List[torch.Tensor]:
+        env: Dict[str, torch.Tensor] = dict(self.consts)
+        env.update(feeds)
+        for st in self.stmts:
+            if st.kind == "alloc":
+                continue
+            x = [env[n] for n in st.srcs]
+            if st.kind == "broadcast":
+                env[st.dst] = x[0].expand(self.buffers[st.dst][0]).contiguous()
+            elif st.kind == "map":
+                env[st.dst] = _execute(Op(st.fn, [], "", st.attrs), x)
+            elif st.kind == "contract":
+                env[st.dst] = torch.einsum("...mk,...kn->...mn", x[0], x[1])
+            elif st.kind == "reduce":
+                env[st.dst] = _execute(Op(st.fn, [], "", st.attrs), x)
+            else:
+                env[st.dst] = _execute(Op(st.fn, [], "", st.attrs), x)
+        return [env[n] for n in self.outputs]
+
+    def dump(self) -> List[str]:
+        out = []
+        for st in self.stmts:
+            shp = self.buffers[st.dst][0]
+            idx = ", ".join(f"i{k}" for k in range(len(shp)))
+            if st.kind == "alloc":
+                out.append(f"{st.dst} = ml.alloc {shp}")
+            elif st.kind == "broadcast":
+                out.append(f"ml.parallel_for ({idx}) in {shp} {{ {st.dst}[{idx}] = ml.broadcast({st.srcs[0]})[{idx}] }}")
+            elif st.kind == "map":
+                out.append(f"ml.parallel_for ({idx}) in {shp} {{ {st.dst}[{idx}] = {st.fn}(" + ", ".join(f"{n}[{idx}]" for n in st.srcs) + ") }")
+            elif st.kind == "contract":
+                k = self.buffers[st.srcs[0]][0][-1]
+                out.append(f"ml.parallel_for ({idx}) in {shp} {{ acc = 0; ml.for k in {k} {{ acc += {st.srcs[0]}[.., k] * {st.srcs[1]}[k, ..] }}; {st.dst}[{idx}] = acc }}")
+            elif st.kind == "reduce":
+                out.append(f"ml.reduce<{st.fn}> {st.srcs[0]} over {st.attrs.get('dim', 'all')} -> {st.dst}")
+            else:
+                out.append(f"ml.call @{st.fn}({', '.join(st.srcs)}) -> {st.dst}")
+        return out
+
+
+def lower_to_ml(g: HLGraph) -> MLProgram:
+    """High level -> mid level: every value becomes a buffer with an allocation, broadcasting operands of element-wise
+    ops get explicit broadcast statements, matmul becomes a contraction loop nest, reductions are marked as such
+    (the reference's HLIRtoMLIRLoweringPass)."""
+    p = MLProgram(g.name)
+    p.inputs, p.outputs = list(g.inputs), list(g.outputs)
+    for n, v in g.values.items():
+        p.buffers[n] = (tuple(v.shape), v.dtype)
+        if v.const is not None:
+            p.consts[n] = v.const
+    tmp = itertools.count()
     for o in g.ops:
-        shp = g.values[o.output].shape
-        out.append(f"{o.output} = ml.alloc {shp}")
-        idx = [f"i{k}" for k in range(len(shp))]
+        shp = tuple(g.values[o.output].shape)
+        p.stmts.append(MLStmt("alloc", o.output))
         if o.kind in ELEMENTWISE or o.kind in UNARY:
-            out.append(f"ml.parallel_for ({', '.join(idx)}) in {shp} {{ {o.output}[{', '.join(idx)}] = {o.kind}("
-                       + ", ".join(f"ml.broadcast({n})[{', '.join(idx)}]" for n in o.inputs) + ") }")
-        elif o.kind == "matmul":
-            k = g.values[o.inputs[0]].shape[-1]
-            out.append(f"ml.parallel_for ({', '.join(idx)}) in {shp} {{ acc = 0; ml.for k in {k} {{ acc += {o.inputs[0]}[.., k] * {o.inputs[1]}[k, ..] }}; {o.output}[{', '.join(idx)}] = acc }}")
+            srcs = []
+            for n in o.inputs:
+                if tuple(g.values[n].shape) != shp:
+                    b = f"%bc{next(tmp)}"
+                    p.buffers[b] = (shp, g.values[n].dtype)
+                    p.stmts.append(MLStmt("alloc", b))
+                    p.stmts.append(MLStmt("broadcast", b, [n]))
+                    srcs.append(b)
+                else:
+                    srcs.append(n)
+            p.stmts.append(MLStmt("map", o.output, srcs, o.kind, dict(o.attrs)))
+        elif o.kind == "matmul" and len(g.values[o.inputs[0]].shape) >= 2 and len(g.values[o.inputs[1]].shape) >= 2:
+            p.stmts.append(MLStmt("contract", o.output, list(o.inputs)))
         elif o.kind in ("sum", "mean", "max"):
-            out.append(f"ml.reduce<{o.kind}> {o.inputs[0]} over {o.attrs.get('dim', 'all')} -> {o.output}")
+            p.stmts.append(MLStmt("reduce", o.output, list(o.inputs), o.kind, dict(o.attrs)))
         else:
-            out.append(f"ml.call @{o.kind}({', '.join(o.inputs)}) -> {o.output}")
-    return out
+            p.stmts.append(MLStmt("call", o.output, list(o.inputs), o.kind, dict(o.attrs)))
+    return p
 
 
-def lower_to_instructions(loops: Sequence[str]) -> List[str]:
-    """Low-level listing: loads, arithmetic, stores, branches per loop body."""
+# ------------------------------------------------------------------ low level: scalar instructions over flat buffers
+@dataclass
+class LLInstr:
+    """``op``: loop / endloop (counted loops with an index register), load / store (flat address = sum of index
+    registers times strides), const, the scalar arithmetic of the element-wise ops, fma, and ``call`` for statements
+    kept whole. Registers are named strings; buffers are flat arrays."""
+    op: str
+    dst: str = ""
+    args: Tuple = ()
+
+
+class LLProgram:
+    def __init__(self, ml: MLProgram):
+        self.ml = ml
+        self.instrs: List[LLInstr] = []
+
+    def dump(self) -> List[str]:
+        out, depth = [], 0
+        for ins in self.instrs:
+            if ins.op == "endloop":
+                depth -= 1
+            out.append("    " * depth + (f"{ins.dst} = " if ins.dst else "") + f"ll.{ins.op} " + ", ".join(str(a) for a in ins.args))
+            if ins.op == "loop":
+                depth += 1
+        return out
+
+    def verify(self) -> List[str]:
+        errs, depth, defined = [], 0, set()
+        for i, ins in enumerate(self.instrs):
+            if ins.op == "loop":
+                depth += 1
+                defined.add(ins.dst)
+            elif ins.op == "endloop":
+                depth -= 1
+                if depth < 0:
+                    errs.append(f"instr #{i}: endloop without loop")
+            elif ins.op in ("load", "const", "acc0"):
+                defined.add(ins.dst)
+            elif ins.op == "call":
+                pass
+            else:
+                regs = [a for a in ins.args if isinstance(a, str) and a.startswith("%r")]
+                for r in regs:
+                    if r not in defined:
+                        errs.append(f"instr #{i} {ins.op}: register {r} used before definition")
+                if ins.dst:
+                    defined.add(ins.dst)
+        if depth != 0:
+            errs.append("unbalanced loops")
+        return errs
+
+    def run(self, feeds: Dict[str, torch.Tensor]) -> List[torch.Tensor]:
+        """Scalar interpreter (the CPU back-end of last resort: exact, slow; meant for small shapes and for checking
+        the lowering)."""
+        import math
+        ml = self.ml
+        mem: Dict[str, list] = {n: t.detach().double().reshape(-1).tolist() for n, t in ml.consts.items()}
+        for n, t in feeds.items():
+            mem[n] = t.detach().double().reshape(-1).tolist()
+        reg: Dict[str, float] = {}
+        tens: Dict[str, torch.Tensor] = {}
+        unary = {"relu": lambda v: max(v, 0.0), "neg": lambda v: -v, "exp": math.exp, "log": math.log, "sqrt": math.sqrt,
+                 "tanh": math.tanh, "sigmoid": lambda v: 1.0 / (1.0 + math.exp(-v)),
+                 "gelu": lambda v: 0.5 * v * (1.0 + math.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))}
+        binary = {"add": lambda a, b: a + b, "sub": lambda a, b: a - b, "mul": lambda a, b: a * b, "div": lambda a, b: a / b,
+                  "maximum": max, "minimum": min}
+        # match loops
+        stack, jump = [], {}
+        for i, ins in enumerate(self.instrs):
+            if ins.op == "loop":
+                stack.append(i)
+            elif ins.op == "endloop":
+                j = stack.pop()
+                jump[i], jump[j] = j, i
+        pc = 0
+
+        def addr(terms):
+            return int(sum(reg[r] * s for r, s in terms))
+        while pc < len(self.instrs):
+            ins = self.instrs[pc]
+            o = ins.op
+            if o == "alloc":
+                shp = ml.buffers[ins.dst][0]
+                n = 1
+                for d in shp:
+                    n *= d
+                mem[ins.dst] = [0.0] * n
+            elif o == "loop":
+                reg[ins.dst] = 0.0
+                if ins.args[0] <= 0:
+                    pc = jump[pc]
+            elif o == "endloop":
+                j = jump[pc]
+                r, n = self.instrs[j].dst, self.instrs[j].args[0]
+                reg[r] += 1.0
+                if reg[r] < n:
+                    pc = j
+            elif o == "load":
+                reg[ins.dst] = mem[ins.args[0]][addr(ins.args[1])]
+            elif o == "store":
+                mem[ins.args[0]][addr(ins.args[1])] = reg[ins.args[2]]
+            elif o == "const" or o == "acc0":
+                reg[ins.dst] = float(ins.args[0]) if ins.args else 0.0
+            elif o == "fma":
+                reg[ins.dst] = reg[ins.args[0]] * reg[ins.args[1]] + reg[ins.args[2]]
+            elif o in unary:
+                reg[ins.dst] = unary[o](reg[ins.args[0]])
+            elif o in binary:
+                reg[ins.dst] = binary[o](reg[ins.args[0]], reg[ins.args[1]])
+            elif o == "call":
+                st = ins.args[0]
+                x = []
+                for n in st.srcs:
+                    shp, dt = ml.buffers[n]
+                    x.append(torch.tensor(mem[n], dtype=torch.float64).reshape(shp))
+                if st.kind == "broadcast":
+                    y = x[0].expand(ml.buffers[st.dst][0]).contiguous()
+                else:
+                    y = _execute(Op(st.fn, [], "", st.attrs), x)
+                mem[st.dst] = y.double().reshape(-1).tolist()
+            else:
+                raise NotImplementedError(o)
+            pc += 1
+        outs = []
+        for n in ml.outputs:
+            shp, dt = ml.buffers[n]
+            outs.append(torch.tensor(mem[n], dtype=torch.float64).reshape(shp).to(dt))
+        return outs
+
+
+def _strides(shape):
+    st, acc = [], 1
+    for d in reversed(shape):
+        st.append(acc)
+        acc *= d
+    return list(reversed(st))
+
+
+def lower_to_ll(ml: MLProgram) -> LLProgram:
+    """Mid level -> low level: maps become counted loops with loads, scalar ops and stores; contractions become the
+    three-deep loop nest with a fused multiply-add; everything else stays a call (the reference's
+    MLIRtoLLIRLoweringPass)."""
+    p = LLProgram(ml)
+    ids = itertools.count()
+    r = lambda: f"%r{next(ids)}"  # noqa: E731
+    for st in ml.stmts:
+        if st.kind == "alloc":
+            p.instrs.append(LLInstr("alloc", st.dst))
+            continue
+        shp = ml.buffers[st.dst][0]
+        if st.kind == "map" and st.fn in (ELEMENTWISE | UNARY) and not st.attrs:
+            n = 1
+            for d in shp:
+                n *= d
+            i = r()
+            p.instrs.append(LLInstr("loop", i, (n,)))
+            vals = []
+            for s in st.srcs:
+                v = r()
+                p.instrs.append(LLInstr("load", v, (s, ((i, 1),))))
+                vals.append(v)
+            o = r()
+            p.instrs.append(LLInstr(st.fn, o, tuple(vals)))
+            p.instrs.append(LLInstr("store", "", (st.dst, ((i, 1),), o)))
+            p.instrs.append(LLInstr("endloop"))
+        elif st.kind == "contract" and len(shp) == 2 and len(ml.buffers[st.srcs[0]][0]) == 2 and len(ml.buffers[st.srcs[1]][0]) == 2:
+            M, N = shp
+            K = ml.buffers[st.srcs[0]][0][1]
+            im, in_, ik, acc, a, b = r(), r(), r(), r(), r(), r()
+            p.instrs += [LLInstr("loop", im, (M,)), LLInstr("loop", in_, (N,)), LLInstr("acc0", acc), LLInstr("loop", ik, (K,)),
+                         LLInstr("load", a, (st.srcs[0], ((im, K), (ik, 1)))), LLInstr("load", b, (st.srcs[1], ((ik, N), (in_, 1)))),
+                         LLInstr("fma", acc, (a, b, acc)), LLInstr("endloop"),
+                         LLInstr("store", "", (st.dst, ((im, N), (in_, 1)), acc)), LLInstr("endloop"), LLInstr("endloop")]
+        else:
+            p.instrs.append(LLInstr("call", st.dst, (st,)))
+    return p
+
+
+def lower_to_loops(g: HLGraph) -> List[str]:
+    """Listing of the mid-level program of ``g``."""
+    return lower_to_ml(g).dump()
+
+
+def lower_to_instructions(loops_or_graph) -> List[str]:
+    """Listing of the low-level program (accepts a graph, a mid-level program, or - for callers that only want a
+    listing of a listing - the lines of ``lower_to_loops``)."""
+    if isinstance(loops_or_graph, HLGraph):
+        return lower_to_ll(lower_to_ml(loops_or_graph)).dump()
+    if isinstance(loops_or_graph, MLProgram):
+        return lower_to_ll(loops_or_graph).dump()
     out = []
-    for i, l in enumerate(loops):
+    for i, l in enumerate(loops_or_graph):
         if l.lstrip().startswith("ml.parallel_for"):
-            out += [f"L{i}: %tid = ll.thread_index", f"    br.ge %tid, %n, L{i}.end", "    %v = ll.vload.128 [%src + %tid * 16]",
-                    "    %r = ll.vop %v", "    ll.vstore.128 [%dst + %tid * 16], %r", f"L{i}.end:"]
+            out += [f"%i{i} = ll.loop n", "    %v = ll.load", "    %r = ll.op %v", "    ll.store %r", "ll.endloop"]
         elif "ml.alloc" in l:
-            out.append(f"    %buf{i} = ll.alloca_global")
+            out.append(f"%buf{i} = ll.alloc")
         else:
-            out.append(f"    ll.call {l.split('@')[-1] if '@' in l else l}")
+            out.append(f"ll.call {l.split('@')[-1] if '@' in l else l}")
     return out
 
 
@@ -340,3 +628,27 @@ class B200Backend:
         PassManager().run(g) if (options or CompilationOptions()).optimization_level > 0 else None
         plan = [(o.output, o.kind, self.KERNELS.get(o.kind, "torch")) for o in g.ops]
         return {"target": self.compute_capability, "plan": plan, "run": g.run}
+
+
+class CPUBackend:
+    """Host back-end: runs a graph through all three levels. ``compile`` optimises the high-level graph, lowers it to
+    the mid level (buffers, explicit broadcasts, loop nests) and verifies it; the returned ``run`` executes the
+    mid-level program with vectorised host kernels. ``level="ll"`` lowers once more and runs the scalar instruction
+    interpreter instead (exact and slow: for checking the lowering on small shapes). The reference's CPU back-end is
+    src/MLFramework/IR/Backend/CPU/*."""
+    triple = "x86_64-unknown-linux-gnu"
+
+    def compile(self, g: HLGraph, options: Optional[CompilationOptions] = None, level: str = "ml") -> Dict[str, object]:
+        if (options or CompilationOptions()).optimization_level > 0:
+            PassManager().run(g)
+        ml = lower_to_ml(g)
+        errs = ml.verify()
+        if errs:
+            raise RuntimeError(f"mid-level IR invalid: {errs}")
+        if level == "ml":
+            return {"target": "cpu", "level": "ml", "program": ml, "run": ml.run}
+        ll = lower_to_ll(ml)
+        errs = ll.verify()
+        if errs:
+            raise RuntimeError(f"low-level IR invalid: {errs}")
+        return {"target": "cpu", "level": "ll", "program": ll, "run": ll.run}

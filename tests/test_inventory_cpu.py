@@ -773,3 +773,101 @@ def test_nvtx_ranges_and_timeline_profiler_on_cpu(tmp_path):
     text = out.read_text()
     assert "traceEvents" in text and "matmul-step" in text
     enable_nvtx(False)
+
+
+def test_three_ir_levels_execute_and_agree():
+    from ml_framework_b200.compiler import ir
+    g = ir.HLGraph("mlp")
+    x = g.input("x", (3, 4))
+    w = g.constant(torch.randn(4, 5, generator=torch.Generator().manual_seed(0)), "w")
+    b = g.constant(torch.randn(5, generator=torch.Generator().manual_seed(1)), "b")
+    h = g.op("matmul", x, w)
+    h = g.op("add", h, b)                     # broadcast of b over rows
+    h = g.op("gelu", h)
+    s = g.op("sum", h, dim=1)
+    g.output(h, s)
+    xin = torch.randn(3, 4, generator=torch.Generator().manual_seed(2))
+    want = g.run({"x": xin})
+    ml = ir.lower_to_ml(g)
+    assert ml.verify() == []
+    kinds = [st.kind for st in ml.stmts]
+    assert "broadcast" in kinds and "contract" in kinds and "reduce" in kinds and kinds.count("alloc") >= 5
+    got_ml = ml.run({"x": xin})
+    ll = ir.lower_to_ll(ml)
+    assert ll.verify() == []
+    ops = [i.op for i in ll.instrs]
+    assert ops.count("loop") >= 5 and "fma" in ops and "gelu" in ops and "call" in ops
+    got_ll = ll.run({"x": xin})
+    for a, b2, c in zip(want, got_ml, got_ll):
+        assert torch.allclose(a, b2, atol=1e-6) and torch.allclose(a, c, atol=1e-5)
+    assert any("ml.broadcast" in l for l in ml.dump()) and any("ll.fma" in l for l in ll.dump())
+    # the verifier catches an implicit broadcast at the mid level and an unbalanced loop at the low level
+    bad = ir.lower_to_ml(g)
+    for st in bad.stmts:
+        if st.kind == "map" and st.fn == "add":
+            st.srcs[1] = "b"
+    assert any("broadcasts are explicit" in e for e in bad.verify())
+    ll.instrs.append(ir.LLInstr("loop", "%rX", (2,)))
+    assert "unbalanced loops" in ll.verify()
+    for level in ("ml", "ll"):
+        exe = ir.CPUBackend().compile(g, level=level)
+        out = exe["run"]({"x": xin})
+        assert torch.allclose(out[0], want[0], atol=1e-5) and exe["level"] == level
+
+
+def test_functional_vmap_pmap_and_tracing_jit():
+    from ml_framework_b200.compiler import functional as Fn
+    from ml_framework_b200.dist.process_group import run_fake_world
+    torch.manual_seed(0)
+    w = torch.randn(5, 3)
+    xs, bs = torch.randn(4, 7, 5), torch.randn(4, 3)
+    f = lambda x, b, ww: torch.tanh(x @ ww + b)            # noqa: E731
+    want = torch.stack([f(xs[i], bs[i], w) for i in range(4)])
+    assert torch.allclose(Fn.vmap(f, in_axes=(0, 0, None))(xs, bs, w), want, atol=1e-6)
+    assert torch.allclose(Fn.vmap(f, in_axes=(0, 0, None), fallback="loop")(xs, bs, w), want, atol=1e-6)
+    moved = Fn.vmap(f, in_axes=(1, 0, None), out_axes=1)(xs.transpose(0, 1).contiguous(), bs, w)
+    assert torch.allclose(moved, want.transpose(0, 1), atol=1e-6)
+
+    def branchy(x):                                          # data-dependent Python: torch.func cannot batch it
+        return x * 2 if float(x.sum()) > 0 else x * -1
+    v = torch.tensor([[1.0, 2.0], [-3.0, 1.0]])
+    assert torch.equal(Fn.vmap(branchy)(v), torch.tensor([[2.0, 4.0], [3.0, -1.0]]))
+    with pytest.raises(Exception):
+        Fn.vmap(branchy, fallback="never")(v)
+    with pytest.raises(ValueError):
+        Fn.vmap(f, in_axes=(0, 0))(xs, bs, w)
+
+    # pmap with a named axis: per-rank slice, psum / pmean over the ranks, gathered output
+    data = torch.arange(12.0).reshape(4, 3)
+
+    def run(pg):
+        def body(x):
+            total = Fn.psum(x.sum(), "dp")
+            return x / total + Fn.axis_index("dp")
+        out = Fn.pmap(body, pg, axis_name="dp")(data)
+        mean = Fn.pmap(lambda x: Fn.pmean(x.mean(0, keepdim=True), "dp"), pg, axis_name="dp", gather=False)(data)
+        return out, mean
+    outs = run_fake_world(2, run)
+    want_p = torch.cat([data[:2] / data.sum(), data[2:] / data.sum() + 1])
+    for out, mean in outs:
+        assert torch.allclose(out, want_p, atol=1e-6) and torch.allclose(mean, data.mean(0, keepdim=True), atol=1e-6)
+    with pytest.raises(NameError):
+        Fn.psum(torch.ones(1), "nowhere")
+
+    # jit: traced into the IR, optimised (x * 1 + 0 disappears, the repeated relu is shared), cached per signature
+    def net(x, ww):
+        h = (x @ ww) * 1.0 + 0.0
+        return torch.relu(h) + torch.relu(h), h.sum(dim=1)
+    jf = Fn.jit(net)
+    x = torch.randn(6, 5)
+    a, b = jf(x, w)
+    ra, rb = net(x, w)
+    assert torch.allclose(a, ra, atol=1e-6) and torch.allclose(b, rb, atol=1e-6)
+    g = jf.graph(x, w)
+    assert [o.kind for o in g.ops].count("relu") == 1 and "mul" not in [o.kind for o in g.ops]
+    jf(x, w)
+    assert jf.stats["traced"] == 1 and jf.stats["hits"] >= 2
+    jf(torch.randn(2, 5), w)
+    assert jf.stats["traced"] == 2
+    untraceable = Fn.jit(branchy)
+    assert torch.equal(untraceable(v[0]), v[0] * 2) and untraceable.stats["eager"] == 1
