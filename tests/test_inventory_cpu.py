@@ -871,3 +871,34 @@ def test_functional_vmap_pmap_and_tracing_jit():
     assert jf.stats["traced"] == 2
     untraceable = Fn.jit(branchy)
     assert torch.equal(untraceable(v[0]), v[0] * 2) and untraceable.stats["eager"] == 1
+
+
+def test_operation_diagnostics_handlers_and_error_reporting_service():
+    from ml_framework_b200.compiler.diagnostics import (ErrorReportingService, OperationDiagnosticsRegistry, OperationExecutionContext)
+    from ml_framework_b200.compiler.shapes import ShapeMismatchException
+    reg = OperationDiagnosticsRegistry()
+    mm = reg.get_handler("matmul")
+    assert mm.validate([(4, 8), (8, 3)], {}).is_valid and reg.has_handler("linear") and not reg.has_handler("fft")
+    bad = mm.validate([(4, 8), (3, 8)], {})
+    assert not bad.is_valid and "inner dimensions" in bad.message
+    assert any("transpose the second operand" in s for s in mm.generate_suggestions([(4, 8), (3, 8)], {}))
+    assert any("multiple of 8" in s for s in mm.detect_issues([(4, 10), (10, 16)], {}))
+    conv = reg.get_handler("conv2d")
+    assert conv.validate([(1, 3, 8, 8), (4, 3, 3, 3)], {}).is_valid
+    assert "channels" in conv.validate([(1, 8, 8, 3), (4, 3, 3, 3)], {}).message
+    assert any("channels-last" in s for s in conv.generate_suggestions([(1, 8, 8, 3), (4, 3, 3, 3)], {}))
+    assert not conv.validate([(1, 3, 2, 2), (4, 3, 5, 5)], {"padding": 0}).is_valid
+    cat = reg.get_handler("concat")
+    assert cat.validate([(2, 3), (5, 3)], {"dim": 0}).is_valid and not cat.validate([(2, 3), (2, 4)], {"dim": 0}).is_valid
+    assert any("dimension 1 would work" in s for s in cat.generate_suggestions([(2, 3), (2, 4)], {"dim": 0}))
+    assert not reg.get_handler("maxpool2d").validate([(1, 1, 2, 2)], {"kernel": 3}).is_valid
+    svc = ErrorReportingService(reg)
+    svc.check("matmul", [(4, 8), (8, 3)], layer_name="ok")
+    with pytest.raises(ShapeMismatchException) as ei:
+        svc.check("linear", [(32, 100), (10, 100)], layer_name="classifier")
+    e = ei.value
+    assert "classifier" in str(e) and e.suggestions and svc.counts == {"linear": 1} and svc.get_current_context() is None
+    assert '"operation": "linear"' in svc.report(e, "json") and "<li>" in svc.report(e, "html")
+    svc.capture_context(OperationExecutionContext("conv2d", "stem", [(1, 8, 8, 3), (4, 3, 3, 3)], {}, previous_layer="input"))
+    assert "after 'input'" in str(svc.generate_shape_mismatch_exception())
+    assert len(svc.log) == 2 and svc.log[-1]["operation"] == "conv2d"

@@ -164,3 +164,26 @@ def test_fused_rope_and_cache_write_matches_separate_kernels():
     native.rope_kv_write_(qkv, pos, slots, cache, Hq, Hkv, 500000.0)
     torch.cuda.synchronize()
     assert torch.equal(qkv, ref) and torch.equal(cache, cache_ref)
+
+
+def test_paged_attention_layer_native_matches_reference_layer():
+    """The standalone layer on the native kernels (bf16, head dimension 128) against the same layer in fp32 PyTorch:
+    prefill in two chunks (the second attends to the cached prefix), then two decode steps."""
+    from ml_framework_b200.serving.kv_cache import KVCacheBlockManager
+    from ml_framework_b200.serving.paged_attention_layer import AttentionPhase, PagedAttentionLayer
+    torch.manual_seed(0)
+    d, hq, hkv, D = 512, 4, 2, 128
+    gpu = PagedAttentionLayer(d, hq, hkv, D, rope_theta=10000.0, dtype=torch.bfloat16, device="cuda")
+    cpu = PagedAttentionLayer(d, hq, hkv, D, rope_theta=10000.0)
+    cpu.load_state_dict({k: v.float().cpu() for k, v in gpu.state_dict().items()})
+    kv_g = KVCacheBlockManager(total_blocks=64, block_size=16, head_dim=D, num_layers=1, num_kv_heads=hkv, dtype=torch.bfloat16, device="cuda")
+    kv_c = KVCacheBlockManager(total_blocks=64, block_size=16, head_dim=D, num_layers=1, num_kv_heads=hkv, dtype=torch.float32, device="cpu")
+    x = (torch.randn(200, d) * 0.5)
+    xg = x.cuda().to(torch.bfloat16)
+    xc = xg.float().cpu()
+    steps = [(slice(0, 128), AttentionPhase.PREFILL), (slice(128, 198), AttentionPhase.PREFILL), (slice(198, 199), AttentionPhase.DECODE),
+             (slice(199, 200), AttentionPhase.DECODE)]
+    for sl, ph in steps:
+        og = gpu(xg[sl], kv_g, [3], ph)
+        oc = cpu(xc[sl], kv_c, [3], ph)
+        assert torch.allclose(og.float().cpu(), oc, atol=3e-2, rtol=3e-2), (sl, (og.float().cpu() - oc).abs().max())

@@ -281,3 +281,37 @@ def test_scheduler_warmup_iterations_and_iteration_timeout():
     assert [r.id for r in s.batch_manager.running] in ([r1.id], []) and not f2.done()
     s.run_until_idle()
     assert f1.result().tokens == [7, 7] and f2.result().tokens == [7]
+
+
+def test_paged_attention_layer_prefill_chunks_and_decode_match_contiguous_attention():
+    """The layer fed a prompt in two chunks and then token by token gives what one causal attention over the whole
+    sequence gives (the reference's paged-vs-contiguous equivalence)."""
+    import torch
+    from ml_framework_b200.ops import reference
+    from ml_framework_b200.serving.kv_cache import KVCacheBlockManager
+    from ml_framework_b200.serving.paged_attention_layer import AttentionPhase, PagedAttentionLayer
+    torch.manual_seed(0)
+    d, hq, hkv, D = 32, 4, 2, 8
+    layer = PagedAttentionLayer(d, hq, hkv, D, rope_theta=10000.0)
+    kv = KVCacheBlockManager(total_blocks=32, block_size=4, head_dim=D, num_layers=1, num_kv_heads=hkv, dtype=torch.float32, device="cpu")
+    xs = {7: torch.randn(11, d), 9: torch.randn(6, d)}
+
+    def contiguous(x):
+        qkv = torch.nn.functional.linear(x, layer.qkv.weight)
+        q, k, v = layer._split(qkv)
+        pos = torch.arange(x.shape[0])
+        q, k = reference.rope_ref(q, pos, 10000.0), reference.rope_ref(k, pos, 10000.0)
+        o, _ = reference.attention_ref(q[None].float(), k[None].float(), v[None].float(), causal=True)
+        return torch.nn.functional.linear(o[0].reshape(x.shape[0], hq * D), layer.proj.weight)
+    want = {s: contiguous(x) for s, x in xs.items()}
+    # first chunks of both sequences in one call, then the rest of sequence 7's prompt, then decode steps
+    out = layer(torch.cat([xs[7][:5], xs[9][:4]]), kv, [7, 9], AttentionPhase.PREFILL, n_tokens=[5, 4])
+    assert torch.allclose(out[:5], want[7][:5], atol=1e-5) and torch.allclose(out[5:], want[9][:4], atol=1e-5)
+    out = layer(xs[7][5:9], kv, [7], AttentionPhase.PREFILL)
+    assert torch.allclose(out, want[7][5:9], atol=1e-5)
+    for t in range(2):
+        out = layer(torch.stack([xs[7][9 + t], xs[9][4 + t]]), kv, [7, 9], AttentionPhase.DECODE)
+        assert torch.allclose(out[0], want[7][9 + t], atol=1e-5) and torch.allclose(out[1], want[9][4 + t], atol=1e-5)
+    assert kv.get_sequence_length(7) == 11 and kv.get_sequence_length(9) == 6
+    with pytest.raises(ValueError):
+        layer(xs[7][:3], kv, [7, 9], AttentionPhase.PREFILL)
