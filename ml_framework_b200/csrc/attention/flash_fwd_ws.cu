@@ -50,7 +50,15 @@ struct FlashWsParams {
   int causal;
   float scale_log2;
   int* err;
+  // paged keys / values: the K and V tensor maps then cover the KV cache as token rows
+  // [num_blocks * 2 * 16, Hkv * 128] (K rows of block b start at row b * 32, V rows at b * 32 + 16) with a box of
+  // 16 rows, and every 128-key tile is fetched page by page through this sequence's row of the block table
+  const int* block_table;      // [B, max_blocks] physical block ids, or null for contiguous K / V
+  int max_blocks, num_blocks;
 };
+
+constexpr int W_PAGE = 16;                      // tokens per KV-cache block on the paged path
+constexpr int W_PAGE_BYTES = W_PAGE * 128;      // one page of one 64-column half: 16 rows of 128 bytes
 
 __global__ void __launch_bounds__(W_THREADS, 1)
 flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -136,18 +144,51 @@ flash_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_2d(sQ + t * W_TILE_BYTES, &tmQ, h * W_D, qrow, q_full(t));
         tma_load_2d(sQ + t * W_TILE_BYTES + W_TILE_BYTES / 2, &tmQ, h * W_D + 64, qrow, q_full(t));
       }
+      const int* bt = p.block_table ? p.block_table + (long long)b * p.max_blocks : nullptr;
+      const int seq_pages = (p.Skv + W_PAGE - 1) / W_PAGE;
       for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int krow = (int)(kv_row_base + j * W_BKV);
+        int blk[W_BKV / W_PAGE];
+        if (bt) {
+          // the eight table entries of this tile first (independent loads); pages past the end of the sequence
+          // repeat its first page: their keys are masked, they only have to be readable
+#pragma unroll
+          for (int g = 0; g < W_BKV / W_PAGE; ++g) {
+            const int pg = j * (W_BKV / W_PAGE) + g;
+            blk[g] = bt[pg < seq_pages && pg < p.max_blocks ? pg : 0];
+          }
+#pragma unroll
+          for (int g = 0; g < W_BKV / W_PAGE; ++g)
+            if (blk[g] < 0 || blk[g] >= p.num_blocks) { atomicCAS(p.err, 0, ERR_BAD_INDEX); blk[g] = 0; }
+        }
         if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_ATTN)) break;
         mbar_expect_tx(k_full(s), W_TILE_BYTES);
-        tma_load_2d(sK + s * W_TILE_BYTES, &tmK, hkv * W_D, krow, k_full(s));
-        tma_load_2d(sK + s * W_TILE_BYTES + W_TILE_BYTES / 2, &tmK, hkv * W_D + 64, krow, k_full(s));
+        if (bt) {
+#pragma unroll
+          for (int g = 0; g < W_BKV / W_PAGE; ++g) {
+            const uint32_t dst = sK + s * W_TILE_BYTES + g * W_PAGE_BYTES;
+            tma_load_2d(dst, &tmK, hkv * W_D, blk[g] * 2 * W_PAGE, k_full(s));
+            tma_load_2d(dst + W_TILE_BYTES / 2, &tmK, hkv * W_D + 64, blk[g] * 2 * W_PAGE, k_full(s));
+          }
+        } else {
+          tma_load_2d(sK + s * W_TILE_BYTES, &tmK, hkv * W_D, krow, k_full(s));
+          tma_load_2d(sK + s * W_TILE_BYTES + W_TILE_BYTES / 2, &tmK, hkv * W_D + 64, krow, k_full(s));
+        }
         if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag, p.err, ERR_WAIT_ATTN)) break;
         mbar_expect_tx(v_full(s), W_TILE_BYTES);
-        tma_load_2d(sV + s * W_TILE_BYTES, &tmV, hkv * W_D, krow, v_full(s));
-        tma_load_2d(sV + s * W_TILE_BYTES + W_TILE_BYTES / 2, &tmV, hkv * W_D + 64, krow, v_full(s));
+        if (bt) {
+#pragma unroll
+          for (int g = 0; g < W_BKV / W_PAGE; ++g) {
+            const uint32_t dst = sV + s * W_TILE_BYTES + g * W_PAGE_BYTES;
+            tma_load_2d(dst, &tmV, hkv * W_D, (blk[g] * 2 + 1) * W_PAGE, v_full(s));
+            tma_load_2d(dst + W_TILE_BYTES / 2, &tmV, hkv * W_D + 64, (blk[g] * 2 + 1) * W_PAGE, v_full(s));
+          }
+        } else {
+          tma_load_2d(sV + s * W_TILE_BYTES, &tmV, hkv * W_D, krow, v_full(s));
+          tma_load_2d(sV + s * W_TILE_BYTES + W_TILE_BYTES / 2, &tmV, hkv * W_D + 64, krow, v_full(s));
+        }
       }
     }
   } else if (warp == 1) {
@@ -374,6 +415,8 @@ MLF_API int mlf_flash_fwd_prefix(const void* q, const void* k, const void* v, vo
   p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = device_status_word();
+  p.block_table = nullptr;
+  p.max_blocks = p.num_blocks = 0;
   MLF_REQUIRE(p.err != nullptr, "no device status word");
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -384,6 +427,53 @@ MLF_API int mlf_flash_fwd_prefix(const void* q, const void* k, const void* v, vo
   }
   dim3 grid(((S + 2 * W_BQ - 1) / (2 * W_BQ)) * Hq * B);
   flash_fwd_ws_kernel<<<grid, W_THREADS, W_SMEM, st>>>(tq, tk, tv, p);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Prefill attention whose keys and values are read straight out of the paged KV cache: queries [B * Sq rows] are the
+// LAST Sq positions of sequences of Skv cached tokens each (the chunk's own K / V are already in the cache), and
+// every 128-key tile is fetched page by page through the sequence's row of the block table by the kernel's TMA
+// producer - no gather of the cached prefix into a contiguous buffer. cache: [num_blocks, 2, 16, Hkv, 128] bf16;
+// block_table: int32 [B, max_blocks]. The reference walks the block table per token
+// (src/MLFramework/Inference/PagedAttention/Layers/PagedAttentionLayer.cs:332-389, Phases/PrefillOrchestrator.cs:62-78).
+MLF_API int mlf_flash_fwd_paged(const void* q, const void* cache, const int* block_table, void* out, float* lse, int B, int Sq, int Skv,
+                                int Hq, int Hkv, long long ldq, long long ldo, int num_blocks, int block_size, int max_blocks, float scale,
+                                int causal, uint64_t stream) {
+  MLF_REQUIRE(B > 0 && Sq > 0 && Skv >= Sq && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "flash_fwd_paged: bad shape");
+  MLF_REQUIRE(block_size == W_PAGE, "flash_fwd_paged: the block size must be %d tokens", W_PAGE);
+  MLF_REQUIRE(block_table != nullptr && num_blocks > 0 && (long long)max_blocks * W_PAGE >= Skv,
+              "flash_fwd_paged: %d table entries cannot describe %d tokens", max_blocks, Skv);
+  MLF_REQUIRE(scale > 0.f, "flash_fwd_paged: softmax scale must be positive");
+  MLF_REQUIRE(ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "flash_fwd_paged: out must be 16-byte aligned");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tkv;
+  int rc;
+  if ((rc = cached_tmap_bf16(&tq, q, (uint64_t)Hq * W_D, (uint64_t)B * Sq, ldq, 64, W_BQ))) return rc;
+  if ((rc = cached_tmap_bf16(&tkv, cache, (uint64_t)Hkv * W_D, (uint64_t)num_blocks * 2 * W_PAGE, (uint64_t)Hkv * W_D, 64, W_PAGE))) return rc;
+  FlashWsParams p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.ldo = ldo;
+  p.B = B; p.S = Sq; p.Hq = Hq; p.Hkv = Hkv;
+  p.Skv = Skv; p.qoff = Skv - Sq;
+  p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = device_status_word();
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.num_blocks = num_blocks;
+  MLF_REQUIRE(p.err != nullptr, "no device status word");
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    MLF_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM));
+    attr_set[dev & 63] = true;
+  }
+  dim3 grid(((Sq + 2 * W_BQ - 1) / (2 * W_BQ)) * Hq * B);
+  flash_fwd_ws_kernel<<<grid, W_THREADS, W_SMEM, st>>>(tq, tkv, tkv, p);
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -335,13 +335,12 @@ __device__ __forceinline__ CopyPiece next_piece(const GemmKernelParams& p, int n
 constexpr int kCopySignalLag = 3;
 
 __device__ __forceinline__ void publish_chunk(const GemmKernelParams& p, int chunk) {
+  // The copy thread must not wait for an answer here: a returning atomic costs a round trip to L2 per chunk and CTA,
+  // which at a megabyte per chunk is as long as the copy itself. The bulk stores of the chunk are complete (the
+  // caller waited for their group); the proxy fence makes them visible to the generic proxy, and a releasing
+  // reduction bumps the chunk's counter without returning. Consumers wait for the counter to reach n_copy_ctas.
   fence_proxy_async_all();
-  __threadfence();
-  const uint32_t old = atomicAdd(&p.counters[chunk], 1u);
-  if (old + 1 == (uint32_t)p.n_copy_ctas) {
-    __threadfence();
-    st_release_gpu(&p.flags_ready[chunk], 1u);
-  }
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&p.counters[chunk]) : "memory");
 }
 
 __device__ inline void gather_copy_role(const GemmKernelParams& p) {

@@ -123,7 +123,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int r0 = p.gather_operand == 1 ? m0 : n0;
           const int r1 = min(p.total_rows, r0 + (p.gather_operand == 1 ? BM : BN)) - 1;
           for (int c = r0 / p.flag_rows; c <= r1 / p.flag_rows && ok; ++c)
-            ok = wait_flag_ge_gpu(&p.flags_ready[c], 1u, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
+            ok = wait_flag_ge_gpu(&p.counters[c], (uint32_t)p.n_copy_ctas, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
           if (!ok) break;
           fence_proxy_async_all();
         }

@@ -294,6 +294,25 @@ def flash_fwd_prefix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, B: int, 
     return out
 
 
+def flash_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, B: int, Sq: int, Skv: int, *,
+                    causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
+    """Attention of the LAST ``Sq`` positions of each of ``B`` sequences over their ``Skv`` cached tokens, keys and
+    values read page by page through ``block_table`` inside the kernel (the chunk's own K / V must already be in the
+    cache). q [B*Sq, Hq, 128]; kv_cache [num_blocks, 2, 16, Hkv, 128] bf16; block_table int32 [B, max_blocks]."""
+    T, Hq, D = q.shape
+    nb, two, bs, Hkv, Dc = kv_cache.shape
+    assert D == 128 and Dc == 128 and two == 2 and T == B * Sq and Skv >= Sq
+    assert q.stride(2) == 1 and q.stride(1) == D and q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
+    assert kv_cache.is_contiguous() and block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.shape[0] == B
+    table = block_table.contiguous()
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    scale = scale if scale is not None else D ** -0.5
+    rc = _L().mlf_flash_fwd_paged(_p(q), _p(kv_cache), _p(table), _p(out), None, B, Sq, Skv, Hq, Hkv, C.c_longlong(q.stride(0)),
+                                  C.c_longlong(Hq * D), int(nb), int(bs), int(table.shape[1]), C.c_float(scale), int(causal), _st())
+    _lib.check(rc, "mlf_flash_fwd_paged")
+    return out
+
+
 def flash_bwd(q, k, v, o, dout, lse, B: int, S: int, *, causal: bool = True, scale: Optional[float] = None,
               dq: Optional[torch.Tensor] = None, dk: Optional[torch.Tensor] = None, dv: Optional[torch.Tensor] = None):
     """Gradients of :func:`flash_fwd`. ``dq/dk/dv`` may be views into a packed dQKV buffer."""

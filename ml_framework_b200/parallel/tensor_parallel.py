@@ -165,10 +165,10 @@ def scatter_tokens(x, tp): return _ScatterTokens.apply(x, tp)
 
 # ------------------------------------------------------------------ fused kernels (GPU, peer memory)
 def _copy_ctas_for(tp: TPContext, flops: float, link_bytes: float) -> int:
-    """Copy CTAs of a gather GEMM: enough of them (about 40 GB/s each) to move the remote rows in the time the
-    product takes, or in the time the links need when those are the bound; between 8 and 32."""
+    """Copy CTAs of a gather GEMM: enough of them (about 25 GB/s each over NVLink) to move the remote rows in the
+    time the product takes, or in the time the links need when those are the bound; between 8 and 40."""
     t = max(flops / 1.4e15, link_bytes / 700e9, 1e-6)
-    return int(min(32, max(8, -(-link_bytes // (40e9 * t)))))
+    return int(min(40, max(8, -(-link_bytes // (25e9 * t)))))
 
 
 def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: str, bias=None, flags=0, aux_out=None,

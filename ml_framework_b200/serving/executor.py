@@ -212,7 +212,13 @@ class PagedLlamaExecutor:
         table, _ = self.kv.build_tables([r.id], self.max_blocks, dev)
         total = start + n
 
+        paged_prefill = self.native and start > 0 and self.kv.block_size == 16
+
         def attend(li, q, k, v):
+            if paged_prefill:
+                # a later chunk: K / V of the cached prefix and of this chunk are read page by page through the
+                # block table inside the attention kernel (the chunk's own rows were written by the block just before)
+                return native.flash_fwd_paged(q, self.kv.caches[li], table, 1, n, total, causal=True)
             if start == 0:
                 kk, vv = k, v
             elif self.native:

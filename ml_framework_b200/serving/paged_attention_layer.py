@@ -108,6 +108,8 @@ class PagedAttentionLayer(nn.Module):
                 total = st + n
                 if nat and st == 0:
                     o, _ = native.flash_fwd(qi, k[off:off + n], v[off:off + n], 1, n, causal=True, want_lse=False)
+                elif nat and kv.block_size == 16:
+                    o = native.flash_fwd_paged(qi, cache, table[i:i + 1], 1, n, total, causal=True)    # pages read in the kernel
                 elif nat:
                     kk, vv = native.kv_gather(cache, table[i], total)
                     o = native.flash_fwd_prefix(qi, kk, vv, 1, n, total, causal=True)

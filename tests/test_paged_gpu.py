@@ -187,3 +187,29 @@ def test_paged_attention_layer_native_matches_reference_layer():
         og = gpu(xg[sl], kv_g, [3], ph)
         oc = cpu(xc[sl], kv_c, [3], ph)
         assert torch.allclose(og.float().cpu(), oc, atol=3e-2, rtol=3e-2), (sl, (og.float().cpu() - oc).abs().max())
+
+
+@pytest.mark.parametrize("Sq,Skv,Hq,Hkv", [(128, 128, 4, 2), (70, 198, 4, 1), (256, 700, 8, 2), (300, 300, 2, 2)])
+def test_prefill_attention_through_the_block_table_matches_gathered_attention(Sq, Skv, Hq, Hkv):
+    """Queries = the last Sq positions of a sequence of Skv cached tokens; K / V fetched page by page through a
+    shuffled block table inside the tcgen05 kernel, against fp32 attention over the gathered pages."""
+    from ml_framework_b200.ops import native, reference
+    torch.manual_seed(0)
+    B, bs, D = 2, 16, 128
+    pages = (Skv + bs - 1) // bs
+    nb = B * pages + 5
+    cache = torch.zeros(nb, 2, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    perm = torch.randperm(nb)[: B * pages].reshape(B, pages)
+    table = torch.full((B, pages + 3), -1, dtype=torch.int32)
+    table[:, :pages] = perm.to(torch.int32)
+    k = (torch.randn(B, Skv, Hkv, D, device="cuda") * 0.5).to(torch.bfloat16)
+    v = (torch.randn(B, Skv, Hkv, D, device="cuda") * 0.5).to(torch.bfloat16)
+    for b in range(B):
+        for pg in range(pages):
+            lo, hi = pg * bs, min((pg + 1) * bs, Skv)
+            cache[perm[b, pg], 0, : hi - lo] = k[b, lo:hi]
+            cache[perm[b, pg], 1, : hi - lo] = v[b, lo:hi]
+    q = (torch.randn(B * Sq, Hq, D, device="cuda") * 0.5).to(torch.bfloat16)
+    out = native.flash_fwd_paged(q, cache, table.cuda(), B, Sq, Skv, causal=True)
+    ref, _ = reference.attention_ref(q.view(B, Sq, Hq, D).float(), k.float(), v.float(), causal=True, start_pos=Skv - Sq)
+    assert torch.allclose(out.view(B, Sq, Hq, D).float(), ref, atol=2e-2, rtol=2e-2), (out.view(B, Sq, Hq, D).float() - ref).abs().max()

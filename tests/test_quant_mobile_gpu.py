@@ -93,4 +93,5 @@ def test_gpu_quantization_backend_int8_matmul_on_the_tensor_cores():
     y = be.matmul_int8(ia, ib, float(qa.scale * qb.scale))
     exact = (ia.to(torch.int32).cpu() @ ib.to(torch.int32).cpu()).float().cuda() * float(qa.scale * qb.scale)
     assert torch.allclose(y, exact, atol=1e-3, rtol=1e-4)          # int8 products accumulate exactly in fp32 up to rounding
-    assert (y - a @ b).abs().max() < 1.5
+    ref = a @ b
+    assert (y - ref).abs().max() < 0.08 * ref.abs().max()          # int8 quantisation error of a 512-term dot product
