@@ -27,6 +27,7 @@ struct GemmKernelParams {
   int* err;
   // gather
   int gather_operand, world, rank, n_copy_ctas, rows_per_rank, flag_rows, row_bytes, total_rows;
+  int copy_group;    // copy CTAs that share one gated chunk (n_copy_ctas is a multiple of it); consumers wait for this count
   const void* src[8];
   void* gathered;
   uint32_t* flags_ready;
@@ -245,6 +246,17 @@ __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32
                : "memory");
 }
 
+// Copy CTAs that share one gated chunk: enough that a chunk arrives quickly, few enough that each CTA moves a run of
+// at least kCopyLookahead pieces per chunk (per-chunk work -- slice arithmetic, the publication fence -- is then small
+// beside the copy). The result divides n_copy.
+inline int copy_group_size(int n_copy, long long chunk_bytes) {
+  long long g = chunk_bytes / ((long long)kCopyLookahead * kCopyPiece);
+  if (g < 1) g = 1;
+  if (g > n_copy) g = n_copy;
+  while (n_copy % g) --g;
+  return (int)g;
+}
+
 struct CopyCursor {
   int i;            // chunk iteration (rotated order)
   long long off;    // byte offset inside this CTA's slice of the chunk
@@ -281,6 +293,9 @@ __device__ __forceinline__ void chunk_slice(const GemmKernelParams& p, int n_fla
     hi = min(n16e, pere * (cta + 1)) * 16;
     return;
   }
+  // gated chunk: the `copy_group` CTAs of this CTA's group split it; the groups take the chunks round-robin
+  const int g = p.copy_group;
+  const int mem = cta % g;
   c = first_local + i;
   if (c >= n_flags) c -= n_flags;
   const int row0 = c * p.flag_rows;
@@ -295,9 +310,21 @@ __device__ __forceinline__ void chunk_slice(const GemmKernelParams& p, int n_fla
     return;
   }
   const long long n16 = (long long)rows * p.row_bytes / 16;
-  const long long per = (n16 + p.n_copy_ctas - 1) / p.n_copy_ctas;
-  lo = min(n16, per * cta) * 16;
-  hi = min(n16, per * (cta + 1)) * 16;
+  const long long per = (n16 + g - 1) / g;
+  lo = min(n16, per * mem) * 16;
+  hi = min(n16, per * (mem + 1)) * 16;
+}
+
+// First chunk iteration of a copy CTA and the step to its next one: group k of n_copy_ctas / copy_group takes the
+// gated iterations k, k + groups, ...; the un-gated extra segments that follow are split over all copy CTAs.
+__device__ __forceinline__ int first_chunk_iter(const GemmKernelParams& p, int n_flags, int cta) {
+  const int grp = cta / p.copy_group;
+  return grp < n_flags ? grp : n_flags;
+}
+__device__ __forceinline__ int next_chunk_iter(const GemmKernelParams& p, int n_flags, int i) {
+  if (i >= n_flags) return i + 1;
+  const int nx = i + p.n_copy_ctas / p.copy_group;
+  return nx < n_flags ? nx : n_flags;
 }
 
 // Returns the piece at the cursor and advances it. Chunks whose slice is empty for this CTA
@@ -320,7 +347,7 @@ __device__ __forceinline__ CopyPiece next_piece(const GemmKernelParams& p, int n
   pc.dst = cur.dst + pos;
   pc.last_of_chunk = remain <= kCopyPiece;
   if (pc.last_of_chunk) {
-    cur.i += 1;
+    cur.i = next_chunk_iter(p, n_flags, cur.i);
     cur.off = 0;
   } else {
     cur.off += kCopyPiece;
@@ -338,7 +365,7 @@ __device__ __forceinline__ void publish_chunk(const GemmKernelParams& p, int chu
   // The copy thread must not wait for an answer here: a returning atomic costs a round trip to L2 per chunk and CTA,
   // which at a megabyte per chunk is as long as the copy itself. The bulk stores of the chunk are complete (the
   // caller waited for their group); the proxy fence makes them visible to the generic proxy, and a releasing
-  // reduction bumps the chunk's counter without returning. Consumers wait for the counter to reach n_copy_ctas.
+  // reduction bumps the chunk's counter without returning. Consumers wait for the counter to reach copy_group.
   fence_proxy_async_all();
   asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&p.counters[chunk]) : "memory");
 }
@@ -356,7 +383,8 @@ __device__ inline void gather_copy_role(const GemmKernelParams& p) {
   const int n_flags = p.gather_operand != 0 ? (p.total_rows + p.flag_rows - 1) / p.flag_rows : 0;
   const int first_local = p.gather_operand != 0 ? (p.rank * p.rows_per_rank) / p.flag_rows : 0;
   const int cta = blockIdx.x;
-  CopyCursor lc{0, 0, -1, 0, nullptr, nullptr, 0, 0}, sc{0, 0, -1, 0, nullptr, nullptr, 0, 0};
+  const int i0 = first_chunk_iter(p, n_flags, cta);
+  CopyCursor lc{i0, 0, -1, 0, nullptr, nullptr, 0, 0}, sc{i0, 0, -1, 0, nullptr, nullptr, 0, 0};
   int issued = 0;  // pieces whose load has been issued
   // pending publications: chunk id and the piece index whose commit closed the chunk
   int pend_chunk[8], pend_seq[8];

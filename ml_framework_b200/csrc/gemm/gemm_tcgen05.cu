@@ -123,7 +123,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int r0 = p.gather_operand == 1 ? m0 : n0;
           const int r1 = min(p.total_rows, r0 + (p.gather_operand == 1 ? BM : BN)) - 1;
           for (int c = r0 / p.flag_rows; c <= r1 / p.flag_rows && ok; ++c)
-            ok = wait_flag_ge_gpu(&p.counters[c], (uint32_t)p.n_copy_ctas, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
+            ok = wait_flag_ge_gpu(&p.counters[c], (uint32_t)p.copy_group, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
           if (!ok) break;
           fence_proxy_async_all();
         }
@@ -388,6 +388,7 @@ MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
   if (cm && !cm->gather_operand && cm->n_extra > 0) {
     MLF_REQUIRE(cm->n_copy_ctas >= 1 && cm->n_copy_ctas < sms, "n_copy_ctas out of range");
     p.n_copy_ctas = n_copy = cm->n_copy_ctas;
+    p.copy_group = 1;
     p.extra_segs = cm->extra_segs;
     p.n_extra = cm->n_extra;
   }
@@ -404,6 +405,7 @@ MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
     p.gather_operand = cm->gather_operand;
     p.world = cm->world; p.rank = cm->rank;
     p.n_copy_ctas = n_copy = cm->n_copy_ctas;
+    p.copy_group = copy_group_size(n_copy, (long long)cm->flag_rows * cm->row_bytes);
     p.rows_per_rank = cm->rows_per_rank; p.flag_rows = cm->flag_rows; p.row_bytes = cm->row_bytes;
     p.total_rows = gatherA ? a->M : a->N;
     for (int r = 0; r < 8; ++r) p.src[r] = cm->src[r];

@@ -185,7 +185,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const int r0 = p.gather_operand == 1 ? m0 : n0;
           const int r1 = min(p.total_rows, r0 + 128) - 1;
           for (int c = r0 / p.flag_rows; c <= r1 / p.flag_rows && ok; ++c)
-            ok = wait_flag_ge_gpu(&p.counters[c], (uint32_t)p.n_copy_ctas, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
+            ok = wait_flag_ge_gpu(&p.counters[c], (uint32_t)p.copy_group, abort_flag, p.err, ERR_WAIT_CHUNK_FLAG);
           if (!ok) break;
           fence_proxy_async_all();
         }
@@ -490,6 +490,7 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
     MLF_REQUIRE(cm->n_copy_ctas >= 1 && cm->n_copy_ctas + 2 < sms_all, "n_copy_ctas out of range");
     n_copy = (cm->n_copy_ctas + 1) & ~1;          // whole clusters
     p.n_copy_ctas = n_copy;
+    p.copy_group = 1;
     p.extra_segs = cm->extra_segs;
     p.n_extra = cm->n_extra;
   }
@@ -501,6 +502,7 @@ MLF_API int mlf_gemm_bf16_2cta(const MlfGemmArgs* a, uint64_t stream) {
     p.gather_operand = cm->gather_operand;
     p.world = cm->world; p.rank = cm->rank;
     p.rows_per_rank = cm->rows_per_rank; p.flag_rows = cm->flag_rows; p.row_bytes = cm->row_bytes;
+    p.copy_group = copy_group_size(n_copy, (long long)cm->flag_rows * cm->row_bytes);
     p.total_rows = gatherA ? a->M : a->N;
     for (int r = 0; r < 8; ++r) p.src[r] = cm->src[r];
     p.gathered = cm->gathered;

@@ -15,6 +15,7 @@ overflow flag and the skip decision all kept on the device.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -63,7 +64,9 @@ class TrainEngine:
         if strategy in ("fsdp", "zero2"):
             from .parallel.fsdp import FSDP, FSDPConfig
             self.reducer = None
-            self.fsdp = FSDP(model, FSDPConfig(fused_comm=self.cfg.fused_comm, sharding_strategy="full" if strategy == "fsdp" else "grad_op"), process_group,
+            self.fsdp = FSDP(model, FSDPConfig(fused_comm=self.cfg.fused_comm, sharding_strategy="full" if strategy == "fsdp" else "grad_op",
+                                                     reduce_ctas=int(os.environ.get("MLF_FSDP_REDUCE_CTAS", "64")),
+                                                     gather_copy_ctas=int(os.environ.get("MLF_FSDP_COPY_CTAS", "16"))), process_group,
                              optimizer_kwargs=dict(lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps,
                                                    weight_decay=self.cfg.weight_decay))
             self.flat = None

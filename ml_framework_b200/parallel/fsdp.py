@@ -68,6 +68,8 @@ class FSDPConfig:
     bucket_size_mb: int = 25
     num_communication_workers: int = 2
     fused_comm: bool = True
+    reduce_ctas: int = 64                  # CTAs of a unit's reduce-scatter kernel (it overlaps the next unit's backward)
+    gather_copy_ctas: int = 16             # CTAs a GEMM lends to the parameter gather of the next unit
     min_shard_numel: int = 4096            # smaller / 1-D parameters stay replicated
     hybrid_full_patterns: Sequence[str] = ("transformer", "attention", "attn", "mlp", "blocks")
     hybrid_layerwise_patterns: Sequence[str] = ("classifier", "head")
@@ -517,7 +519,7 @@ class FSDP:
         u = self.units[j]
         full = self._rot_full[j % 2]
         tbl = self._copy_table(u, full)
-        gemm_mod.set_piggyback(tbl, tbl.shape[0], n_copy_ctas=16,
+        gemm_mod.set_piggyback(tbl, tbl.shape[0], n_copy_ctas=self.cfg.gather_copy_ctas,
                                on_attached=lambda u=u, full=full: setattr(u, "_prefetched_into", full.data_ptr()))
 
     def _pre_forward(self, i: int):
@@ -583,7 +585,7 @@ class FSDP:
         cs.wait_event(ready)
         with torch.cuda.stream(cs):
             self.symm.rs_reduce_sync(buf, u._red_segs, u._red_segs.shape[0], self.grad_shards, u._red_numel, flag=self._flag,
-                                     key=self._sync_key, max_ctas=64)
+                                     key=self._sync_key, max_ctas=self.cfg.reduce_ctas)
             done = torch.cuda.Event()
             done.record(cs)
         self._rs_done[gbuf.data_ptr()] = done

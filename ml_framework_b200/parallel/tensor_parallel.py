@@ -166,9 +166,11 @@ def scatter_tokens(x, tp): return _ScatterTokens.apply(x, tp)
 # ------------------------------------------------------------------ fused kernels (GPU, peer memory)
 def _copy_ctas_for(tp: TPContext, flops: float, link_bytes: float) -> int:
     """Copy CTAs of a gather GEMM: enough of them (about 25 GB/s each over NVLink) to move the remote rows in the
-    time the product takes, or in the time the links need when those are the bound; between 8 and 40."""
+    time the product takes, or in the time the links need when those are the bound; a multiple of 8 between 8 and 40
+    (the kernel forms groups of up to 8 copy CTAs per row chunk, and the group size has to divide the count)."""
     t = max(flops / 1.4e15, link_bytes / 700e9, 1e-6)
-    return int(min(40, max(8, -(-link_bytes // (25e9 * t)))))
+    n = int(min(40, max(8, -(-link_bytes // (25e9 * t)))))
+    return (n + 7) // 8 * 8
 
 
 def _fused_ag_gemm(tp: TPContext, x_shard: torch.Tensor, w: torch.Tensor, key: str, bias=None, flags=0, aux_out=None,
