@@ -9,11 +9,13 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+GROUP = None        # tensor-parallel process group (None = the default group); set by the pipeline arm
+
 
 class _AllReduce(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):
-        dist.all_reduce(x)
+        dist.all_reduce(x, group=GROUP)
         return x
 
     @staticmethod
@@ -28,7 +30,7 @@ class _CopyIn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        dist.all_reduce(g)
+        dist.all_reduce(g, group=GROUP)
         return g
 
 
@@ -89,7 +91,7 @@ class Model(nn.Module):
         logits = self.head(_CopyIn.apply(self.nf(x))).float()                  # [B, S, V / W]
         # vocab-parallel cross entropy: max and sum-exp reduced over the group
         m = logits.detach().amax(-1)
-        dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=GROUP)
         se = (logits - m[..., None]).exp().sum(-1)
         se = _AllReduce.apply(se)
         tmask = (tgt >= lo) & (tgt < lo + self.Vl)

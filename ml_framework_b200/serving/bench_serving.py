@@ -33,7 +33,12 @@ def _max_len(spec) -> int:
 
 
 def run(model_name: str = "llama-tiny", n_requests: int = 32, rate: float = 0.0, prompt_len=64, max_tokens=16,
-        max_batch: int = 32, block_size: int = 16, device: str = "cpu", seed: int = 0, kv_fraction: float = 0.5, pg=None, fused: bool = True):
+        max_batch: int = 32, block_size: int = 16, device: str = "cpu", seed: int = 0, kv_fraction: float = 0.5, pg=None, fused: bool = True,
+        torch_ops: bool = False):
+    """``torch_ops``: the comparison arm -- the same scheduler, block manager and request stream, with every operator of
+    the model step taken from torch (cuBLAS linears, ``F.rms_norm``, SDPA over pages gathered by indexing the block
+    table, NCCL reductions), launched eagerly."""
+    fused = fused and not torch_ops
     from ..modelzoo.zoo import build_model, default_registry
     from .executor import ExecutorConfig, PagedLlamaExecutor
     from .kv_cache import KVCacheBlockManager
@@ -73,7 +78,7 @@ def run(model_name: str = "llama-tiny", n_requests: int = 32, rate: float = 0.0,
         need = int(t.item())
     kv = KVCacheBlockManager(need, block_size, mc.head_dim, mc.n_layers, kv_heads, device=dev, dtype=dtype)
     ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=max_batch, max_seq_len=p_max + t_max + block_size,
-                                                      prefill_chunk=max(p_max, 16)), tp=tp)
+                                                      prefill_chunk=max(p_max, 16), torch_ops=torch_ops), tp=tp)
     leader = None
     if W > 1:
         from .tp_driver import TPLeaderExecutor, follower_loop
@@ -116,7 +121,7 @@ def run(model_name: str = "llama-tiny", n_requests: int = 32, rate: float = 0.0,
     gen = sum(len(r.tokens) for r in results)
     pct = lambda v, q: v[min(len(v) - 1, int(q * len(v)))] if v else float("nan")
     snap = sched.metrics.snapshot()
-    return {"model": model_name, "tensor_parallel": W, "fused_reduce": bool(tp is not None and tp.fused), "requests": n_requests, "arrival_rate": rate,
+    return {"impl": "torch" if torch_ops else "ours", "model": model_name, "tensor_parallel": W, "fused_reduce": bool(tp is not None and tp.fused), "requests": n_requests, "arrival_rate": rate,
             "prompt_len": prompt_len, "max_tokens": max_tokens,
             "max_batch": max_batch, "wall_s": wall, "generated_tokens": gen, "decode_tokens_per_s": gen / wall,
             "total_tokens_per_s": (gen + n_prompt_tokens) / wall, "ttft_p50_ms": pct(ttft, 0.5) * 1e3, "ttft_p99_ms": pct(ttft, 0.99) * 1e3,
@@ -126,6 +131,8 @@ def run(model_name: str = "llama-tiny", n_requests: int = 32, rate: float = 0.0,
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch"],
+                    help="torch: same scheduler and block tables, model step from torch operators only (the comparison arm)")
     ap.add_argument("--model", default="llama-tiny")
     ap.add_argument("--requests", type=int, default=32)
     ap.add_argument("--rate", type=float, default=0.0, help="Poisson arrival rate in requests/s (0 = all at once)")
@@ -143,7 +150,8 @@ def main(argv=None):
         from ..dist.process_group import init_process_group
         pg = init_process_group("nccl")
         a.device = f"cuda:{torch.cuda.current_device()}"
-    out = run(a.model, a.requests, a.rate, spec(a.prompt_len), spec(a.max_tokens), a.max_batch, device=a.device, pg=pg, fused=not a.no_fused)
+    out = run(a.model, a.requests, a.rate, spec(a.prompt_len), spec(a.max_tokens), a.max_batch, device=a.device, pg=pg, fused=not a.no_fused,
+              torch_ops=a.impl == "torch")
     if pg is None or pg.rank == 0:
         print(json.dumps(out))
     if pg is not None:

@@ -39,6 +39,8 @@ class ExecutorConfig:
     max_prefill_tokens: int = 8192        # first chunks of equal length are prefilled together up to this many tokens
     use_cuda_graphs: bool = True       # decode steps replay a captured graph per (batch bucket, length bucket)
     graph_warmup_steps: int = 2
+    torch_ops: bool = False            # comparison arm: same scheduler and block tables, every operator from torch (cuBLAS
+                                       # linears, F.rms_norm, SDPA over pages gathered by indexing), eager, NCCL reductions
 
 
 class PagedLlamaExecutor:
@@ -47,7 +49,7 @@ class PagedLlamaExecutor:
         self.mc: LlamaConfig = model.cfg
         p = next(model.parameters())
         self.device, self.dtype = p.device, p.dtype
-        self.native = p.is_cuda and p.dtype == torch.bfloat16 and self.mc.head_dim == 128
+        self.native = p.is_cuda and p.dtype == torch.bfloat16 and self.mc.head_dim == 128 and not self.cfg.torch_ops
         W = tp.world if tp is not None else 1
         self.hq, self.hkv = self.mc.n_heads // W, self.mc.n_kv_heads // W
         self.max_blocks = (self.cfg.max_seq_len + kv.block_size - 1) // kv.block_size
@@ -139,6 +141,8 @@ class PagedLlamaExecutor:
             if few_rows:
                 return gemm(hid, dn_w, out=x, flags=_lib.EPI_ACCUM)
             return gemm(hid, dn_w, aux_in=x, flags=_lib.EPI_RESIDUAL)
+        if self.cfg.torch_ops:
+            return self._block_torch(x, blk, qkv_w, o_w, gu_w, dn_w, cache, positions, slots, attend, li)
         # ---- PyTorch statement of the same block (CPU / fp32)
         h, _ = reference.rms_norm_ref(x, blk.norm1.weight, mc.norm_eps)
         qkv = F.linear(h.to(x.dtype), qkv_w)
@@ -158,6 +162,59 @@ class PagedLlamaExecutor:
         gu = F.linear(h.to(x.dtype), gu_w)
         hid = (F.silu(gu[:, 0::2].float()) * gu[:, 1::2].float()).to(x.dtype)
         return self._reduce(F.linear(hid, dn_w), x)
+
+    def _block_torch(self, x, blk, qkv_w, o_w, gu_w, dn_w, cache, positions, slots, attend, li):
+        """The block from torch operators in the model's dtype (the comparison arm on a GPU)."""
+        mc, D, T = self.mc, self.mc.head_dim, x.shape[0]
+        qkv = F.linear(F.rms_norm(x, (x.shape[-1],), blk.norm1.weight, mc.norm_eps), qkv_w)
+        q = qkv[:, :self.hq * D].reshape(T, self.hq, D)
+        k = qkv[:, self.hq * D:(self.hq + self.hkv) * D].reshape(T, self.hkv, D)
+        v = qkv[:, (self.hq + self.hkv) * D:].reshape(T, self.hkv, D)
+        inv = mc.rope_theta ** (-torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D)
+        ang = positions.float()[:, None] * inv[None, :]
+        c, sn = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+        def rope(t):
+            a, b = t[..., 0::2].float(), t[..., 1::2].float()
+            return torch.stack((a * c - b * sn, a * sn + b * c), -1).flatten(-2).to(t.dtype)
+        q, k = rope(q), rope(k)
+        flat = cache.view(-1, 2, self.kv.block_size, self.hkv, D)
+        ok = slots >= 0
+        blk_i, off = slots[ok] // self.kv.block_size, slots[ok] % self.kv.block_size
+        flat[blk_i, 0, off] = k[ok]
+        flat[blk_i, 1, off] = v[ok]
+        a = attend(li, q, k, v)
+        x = self._reduce(F.linear(a.reshape(T, self.hq * D), o_w), x)
+        gu = F.linear(F.rms_norm(x, (x.shape[-1],), blk.norm2.weight, mc.norm_eps), gu_w)
+        return self._reduce(F.linear(F.silu(gu[:, 0::2]) * gu[:, 1::2], dn_w), x)
+
+    def _attend_torch_prefill(self, li, q, k, v, table, start, total):
+        """Causal SDPA of a prompt chunk against the pages gathered by indexing (comparison arm)."""
+        D, n = self.mc.head_dim, q.shape[0]
+        if start > 0:
+            nb = (total + self.kv.block_size - 1) // self.kv.block_size
+            c = self.kv.caches[li].view(-1, 2, self.kv.block_size, self.hkv, D)[table[0, :nb].long()]
+            k = c[:, 0].reshape(-1, self.hkv, D)[:total]
+            v = c[:, 1].reshape(-1, self.hkv, D)[:total]
+        qh, kh, vh = q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None]
+        if start == 0:
+            o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=self.hq != self.hkv)
+        else:
+            mask = torch.arange(total, device=q.device)[None, :] <= (start + torch.arange(n, device=q.device))[:, None]
+            o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, enable_gqa=self.hq != self.hkv)
+        return o[0].transpose(0, 1).contiguous()
+
+    def _attend_torch_decode(self, li, q, table, lens, max_len):
+        """One query row per sequence against its pages: gather [B, L, Hkv, D] by indexing the block table, SDPA
+        with a length mask (comparison arm)."""
+        D, B = self.mc.head_dim, q.shape[0]
+        nb = (max_len + self.kv.block_size - 1) // self.kv.block_size
+        c = self.kv.caches[li].view(-1, 2, self.kv.block_size, self.hkv, D)[table[:, :nb].long()]   # [B, nb, 2, bs, Hkv, D]
+        kk = c[:, :, 0].reshape(B, nb * self.kv.block_size, self.hkv, D).transpose(1, 2)
+        vv = c[:, :, 1].reshape(B, nb * self.kv.block_size, self.hkv, D).transpose(1, 2)
+        mask = (torch.arange(nb * self.kv.block_size, device=q.device)[None, :] < lens[:, None].long())[:, None, None, :]
+        o = F.scaled_dot_product_attention(q[:, :, None, :], kk, vv, attn_mask=mask, enable_gqa=self.hq != self.hkv)
+        return o[:, :, 0, :]
 
     def _embed(self, ids: torch.Tensor) -> torch.Tensor:
         tp = self.tp
@@ -233,6 +290,8 @@ class PagedLlamaExecutor:
                 return out
             if self.native:                  # a later chunk: its rows are the last n positions of the gathered pages
                 return native.flash_fwd_prefix(q, kk, vv, 1, n, total, causal=True)
+            if self.cfg.torch_ops:
+                return self._attend_torch_prefill(li, q, k, v, table, start, total)
             o, _ = reference.attention_ref(q[None], kk[None], vv[None], causal=True, start_pos=start)
             return o[0].to(q.dtype)
         x = self._embed(ids[None])[0]
@@ -282,6 +341,8 @@ class PagedLlamaExecutor:
             if self.native:
                 return native.paged_decode(q, self.kv.caches[li], table, lens, max_len,
                                            split_tokens=self.cfg.decode_split_tokens)
+            if self.cfg.torch_ops:
+                return self._attend_torch_decode(li, q, table, lens, max_len)
             return reference.paged_attention_ref(q, self.kv.caches[li], table.cpu(), lens.cpu().tolist()).to(q.dtype)
         x = self._embed(last[None])[0]
         for li, blk in enumerate(self.m.blocks):

@@ -58,6 +58,57 @@ class _Stage(nn.Module):
         return vocab_parallel_lm_loss(hidden, self.lm_head, targets, self.tp, self.cfg.vocab_size, None)
 
 
+def _torch_arm(a):
+    """The comparison arm: same model, layout, micro-batches and timing, built from torch ops and NCCL only."""
+    import sys
+    import torch.distributed as dist
+    from ..modelzoo.zoo import default_registry
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "baseline"))
+    import llama_pp_tp as base
+    lr = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(lr)
+    dev = torch.device("cuda", lr)
+    dist.init_process_group("nccl", device_id=dev)
+    W, r = dist.get_world_size(), dist.get_rank()
+    cfgd = dict(default_registry().get(a.model).config)
+    if a.layers:
+        cfgd["n_layers"] = a.layers
+    for kv in a.override:
+        k, v = kv.split("=")
+        cfgd[k] = int(v)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfgd["vocab_size"], (a.micro_batches, a.seq), generator=g).to(dev)
+    tgt = torch.randint(0, cfgd["vocab_size"], (a.micro_batches, a.seq), generator=g).to(dev)
+    torch.manual_seed(1 + r)
+    step, n_local = base.build(cfgd, dev, ids, tgt, a.pp, a.tp, a.micro_batches)
+    loss = None
+    for _ in range(a.warmup):
+        loss = step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    lt = loss.float().reshape(1).clone()
+    dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    npar = torch.tensor([float(n_local)], device=dev)
+    dist.all_reduce(npar)
+    if r == 0:
+        tok = a.micro_batches * a.seq
+        print(json.dumps({"metric": "train tokens/s (pipeline x tensor parallel, bf16)", "impl": "torch", "fused_comm": False,
+                          "value": tok / (ms.item() / 1e3), "unit": "tokens/s", "n_gpus": W, "ms_per_step": ms.item(), "steps": a.steps,
+                          "warmup": a.warmup, "final_loss": lt.item(),
+                          "config": {"model": a.model, "layers": cfgd["n_layers"], "params": int(npar.item()), "micro_batches": a.micro_batches,
+                                     "seq_len": a.seq, "schedule": "1f1b", "recompute": True, "parallelism": f"pp{a.pp} x tp{a.tp}"}}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama-2-13b")
@@ -71,11 +122,15 @@ def main(argv=None):
     ap.add_argument("--schedule", default="1f1b", choices=["1f1b", "gpipe"])
     ap.add_argument("--no-recompute", action="store_true")
     ap.add_argument("--no-fused", action="store_true")
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch"],
+                    help="torch: the plain torch.distributed 1F1B x Megatron tensor-parallel arm under baseline/ (none of this package's kernels)")
     ap.add_argument("--override", action="append", default=[], help="model config override key=int (repeatable), e.g. n_kv_heads=2")
     ap.add_argument("--backend", default=None)
     ap.add_argument("--device", default="cuda")
     a = ap.parse_args(argv)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if a.impl == "torch":
+        return _torch_arm(a)
     from ..dist.mesh import ParallelismDimension, init_device_mesh
     from ..dist.process_group import ReduceOp, destroy_process_group, init_process_group
     from ..models.llama import LlamaConfig

@@ -173,12 +173,13 @@ def test_scheduler_survives_executor_failure_and_background_loop():
         s.stop()
 
 
-def test_paged_llama_executor_matches_full_sequence_greedy():
+@pytest.mark.parametrize("torch_ops", [False, True])
+def test_paged_llama_executor_matches_full_sequence_greedy(torch_ops):
     torch.manual_seed(0)
     cfg = LlamaConfig(n_layers=2, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16, d_ff=128, vocab_size=50, max_seq=64, vocab_multiple=8)
     model = Llama(cfg).eval()
     kv = KVCacheBlockManager(64, 4, head_dim=16, num_layers=2, num_kv_heads=2, device="cpu", dtype=torch.float32)
-    ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=64, prefill_chunk=5))
+    ex = PagedLlamaExecutor(model, kv, ExecutorConfig(max_batch=8, max_seq_len=64, prefill_chunk=5, torch_ops=torch_ops))
     s = ContinuousBatchScheduler(ex, kv, SchedulerConfiguration(max_batch_size=4), completion=CompletionConfiguration(eos_token_id=-1))
     prompts = [[3, 7, 11, 2, 9, 30, 4], [5, 6], [40, 41, 42, 43, 44, 45, 46, 47, 48, 1, 2]]
     reqs = [Request(p, max_tokens=6) for p in prompts]
