@@ -56,10 +56,7 @@ def build(cfg, dev, ids, tgt, pp, tp, micro_batches):
     hi = lo + per + (1 if stage_i < extra else 0)
     first, last = stage_i == 0, stage_i == pp - 1
     mod = Stage(cfg, tp, tp_rank, lo, hi, first, last, dev)
-    with torch.no_grad():
-        for prm in mod.parameters():
-            if prm.dim() >= 2:
-                prm.normal_(0.0, 0.02)
+    L.init_weights(mod, cfg)
     opt = torch.optim.AdamW(mod.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
     S, d = ids.shape[1], cfg["d_model"]
     prev_r, next_r = rank - tp, rank + tp

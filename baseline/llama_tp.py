@@ -100,13 +100,28 @@ class Model(nn.Module):
         return (m + se.log() - tl).mean()
 
 
+def init_weights(model, c):
+    """Embedding and head N(0, 0.02); every linear N(0, 2 / (fan_in + fan_out)) over its FULL (unsharded) shape --
+    the initialisation of the package's tensor-parallel layers, so that the loss curves of the two arms are
+    comparable (with 0.02 everywhere this model memorises the fixed synthetic batch within three AdamW steps)."""
+    d, D = c["d_model"], c["head_dim"]
+    full = {"qkv": (d, (c["n_heads"] + 2 * c["n_kv_heads"]) * D), "o": (c["n_heads"] * D, d), "gu": (d, 2 * c["d_ff"]),
+            "down": (c["d_ff"], d)}
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if prm.dim() < 2:
+                continue
+            kind = name.split(".")[-2]
+            if kind in full:
+                prm.normal_(0.0, math.sqrt(2.0 / sum(full[kind])))
+            else:
+                prm.normal_(0.0, 0.02)
+
+
 def build(cfg, dev, ids, tgt):
     W, rank = dist.get_world_size(), dist.get_rank()
     model = Model(cfg, W, rank, dev)
-    with torch.no_grad():
-        for prm in model.parameters():
-            if prm.dim() >= 2:
-                prm.normal_(0.0, 0.02)
+    init_weights(model, cfg)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
     n_params = sum(p.numel() for p in model.parameters()) * W
 

@@ -598,6 +598,42 @@ sum_partials_kernel(const __nv_bfloat16* partial, int world, long long rows, int
   }
 }
 
+// The same sum with the arrival synchronisation inside: every rank has queued this launch, so its GEMM (earlier on its
+// stream) has finished storing partial tiles into the peers' buffers. Nothing waits at the end; callers alternate
+// between two partial buffers, and the arrival wait of call n + 1 is what tells a rank that every peer has finished
+// the sum of call n - 1 before new tiles are stored over it.
+__global__ void __launch_bounds__(256)
+sum_partials_sync_kernel(PeerPtrs pads, SyncState* st, int world, int rank, const __nv_bfloat16* partial, long long rows, int cols,
+                         __nv_bfloat16* out, long long ldo, const __nv_bfloat16* bias, const __nv_bfloat16* residual, long long ldr,
+                         int* err) {
+  const uint32_t e = sync_enter(pads, st, rank, world, err);
+  const int vpr = cols / 8;
+  const long long total = rows * vpr;
+  const long long plane = rows * (long long)cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    auto add8 = [&](const uint4 v) {
+      float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+      a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+    };
+    uint4 v[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < world) v[w] = *reinterpret_cast<const uint4*>(partial + w * plane + r * cols + c);      // all W loads in flight before the first add
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < world) add8(v[w]);
+    if (bias) add8(*reinterpret_cast<const uint4*>(bias + c));
+    if (residual) add8(*reinterpret_cast<const uint4*>(residual + r * ldr + c));
+    uint4 w;
+    w.x = pack_bf16x2(a[0], a[1]); w.y = pack_bf16x2(a[2], a[3]); w.z = pack_bf16x2(a[4], a[5]); w.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = w;
+  }
+  sync_leave(st, e);
+}
+
 // Plain multi-segment copy from peers (all-gather without a GEMM attached).
 struct CopySegHost {
   const void* src;
@@ -872,6 +908,23 @@ MLF_API int mlf_sum_partials(const void* partial, int world, long long rows, int
   sum_partials_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(partial), world, rows, cols, static_cast<__nv_bfloat16*>(out), ldo,
       static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual), ldr);
+  count_launch();
+  MLF_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+MLF_API int mlf_sum_partials_sync(const void* partial, void* const* pads, void* state, int world, int rank, long long rows, int cols,
+                                  void* out, long long ldo, const void* bias, const void* residual, long long ldr, uint64_t stream) {
+  MLF_REQUIRE(cols % 8 == 0 && ldo % 8 == 0, "sum_partials: cols and pitch must be multiples of 8");
+  MLF_REQUIRE(world >= 1 && world <= 8 && state != nullptr, "sum_partials_sync: bad arguments");
+  long long g = (rows * (cols / 8) + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  sum_partials_sync_kernel<<<(int)g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      to_peers(pads, world), static_cast<SyncState*>(state), world, rank, static_cast<const __nv_bfloat16*>(partial), rows, cols,
+      static_cast<__nv_bfloat16*>(out), ldo, static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual), ldr,
+      device_status_word());
   count_launch();
   MLF_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -214,6 +214,20 @@ class SymmetricMemory:
                                             C.c_uint64(_lib.stream_handle()))
         _lib.check(rc, "mlf_ar_one_shot_sync")
 
+    def sum_partials_sync(self, part: SymmBuffer, rows: int, cols: int, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                          residual: Optional[torch.Tensor] = None, offset_bytes: int = 0):
+        """``out[rows, cols]`` = sum over the W planes the peers stored into this rank's ``part`` (+ bias, + residual),
+        after waiting inside the kernel for every rank to reach the call (their stores, earlier on their streams, have
+        then landed). Nothing waits at the end: alternate between two partial buffers from one call to the next."""
+        pad = self._sync_pad()
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+        rc = self._lib.mlf_sum_partials_sync(C.c_void_p(part.ptrs[self.rank] + offset_bytes), pad.peer_table(),
+                                             C.c_void_p(pad.ptrs[self.rank] + 1024), self.world, self.rank, C.c_longlong(rows), cols,
+                                             p(out), C.c_longlong(out.stride(0)), p(bias), p(residual),
+                                             C.c_longlong(residual.stride(0) if residual is not None else 0),
+                                             C.c_uint64(_lib.stream_handle()))
+        _lib.check(rc, "mlf_sum_partials_sync")
+
     def tp_argmax(self, logits: torch.Tensor, index_base: int, vocab: int, cand: SymmBuffer) -> torch.Tensor:
         """Arg-max over a vocabulary split across ranks (``logits`` = this rank's columns starting at ``index_base``)."""
         pad = self._sync_pad()

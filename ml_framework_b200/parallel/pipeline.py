@@ -432,6 +432,12 @@ class _ScheduleBase:
         if not st.is_first:
             x = x.detach().requires_grad_(True)
         recompute = self.ckpt.should_checkpoint(mb, x.numel() * x.element_size())
+        if recompute and st.is_last and self.loss_fn is not None:
+            # nothing downstream needs this stage's output now, and the backward pass runs the forward again anyway:
+            # the last stage only remembers its input (its loss is recorded when the micro-batch is recomputed)
+            self._saved[mb] = (x, None, True, target)
+            self.stats.forward_time_s += time.perf_counter() - t0
+            return None
         if recompute:
             with torch.no_grad():
                 y = st(x)

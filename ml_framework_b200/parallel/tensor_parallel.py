@@ -226,25 +226,20 @@ def _fused_gemm_rs(tp: TPContext, a: torch.Tensor, b: torch.Tensor, key: str, *,
     N = b.shape[1] if b_mn else b.shape[0]
     W = tp.world
     rows = T // W
-    # one partial buffer per shape, shared by every layer: the barrier below is exactly what makes reuse safe (all
-    # ranks have queued the previous call's local sum before anyone's GEMM writes new partial tiles)
-    part = tp.symm_buffer(f"rs_part.{rows}x{N}", W * rows * N * 2)
-    tp.symm.barrier()                                   # previous consumers of the partial buffers are done
+    # two partial buffers per shape, shared by every layer and used alternately: the arrival wait inside the sum of
+    # call n - 1 tells this rank that every peer has finished the sum of call n - 2, i.e. is done reading the buffer
+    # that this call's epilogue is about to store into -- no barrier launch before or after the product
+    n = tp.__dict__.setdefault("_rs_calls", {})
+    n[(rows, N)] = n.get((rows, N), 0) + 1
+    part = tp.symm_buffer(f"rs_part{n[(rows, N)] % 2}.{rows}x{N}", W * rows * N * 2)
     cm = _lib.GemmComm()
     cm.scatter_out, cm.rows_per_owner, cm.world, cm.rank = 1, rows, W, tp.rank
     for r in range(W):
         cm.out_peer[r] = part.ptrs[r]
     dummy = part.view(torch.bfloat16, rows * N).view(rows, N)
     gemm(a, b, b_mn=b_mn, out=dummy, comm=cm, m_override=T)
-    tp.symm.barrier()                                   # every peer's partial tiles have landed
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)
-    import ctypes as C
-    rc = _lib.get().mlf_sum_partials(C.c_void_p(part.local.data_ptr()), W, C.c_longlong(rows), N, C.c_void_p(out.data_ptr()),
-                                     C.c_longlong(N), C.c_void_p(bias.data_ptr()) if bias is not None else None,
-                                     C.c_void_p(residual.data_ptr()) if residual is not None else None,
-                                     C.c_longlong(residual.stride(0) if residual is not None else 0),
-                                     C.c_uint64(_lib.stream_handle()))
-    _lib.check(rc, "mlf_sum_partials")
+    tp.symm.sum_partials_sync(part, rows, N, out, bias, residual)
     return out
 
 

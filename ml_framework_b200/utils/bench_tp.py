@@ -75,8 +75,11 @@ def main(argv=None):
             flat.gather_missing_grads()
             opt.step()
             return loss
+    trace = [] if os.environ.get("MLF_LOSS_TRACE") else None      # per-step losses of the warm-up steps (reads the device)
     for _ in range(a.warmup):
         loss = step()
+        if trace is not None:
+            trace.append(round(float(loss.detach()), 4))
     torch.cuda.synchronize()
     pg.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -93,7 +96,7 @@ def main(argv=None):
         tok = a.batch * a.seq
         print(json.dumps({"metric": "train tokens/s (tensor parallel, sequence parallel, bf16)", "impl": a.impl, "fused_comm": a.impl == "ours" and not a.no_fused,
                           "value": tok / (ms.item() / 1e3), "unit": "tokens/s", "n_gpus": W, "ms_per_step": ms.item(), "steps": a.steps, "warmup": a.warmup,
-                          "final_loss": float(loss.detach()), "config": {"model": a.model, "layers": cfgd["n_layers"], "params": n_params, "global_batch": a.batch,
+                          "final_loss": float(loss.detach()), **({"warmup_losses": trace} if trace is not None else {}), "config": {"model": a.model, "layers": cfgd["n_layers"], "params": n_params, "global_batch": a.batch,
                                                                           "seq_len": a.seq, "parallelism": f"tp{W}"}}))
     destroy_process_group()
 

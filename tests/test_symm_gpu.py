@@ -111,6 +111,17 @@ def test_in_kernel_synchronised_reductions_single_rank():
         sm.all_reduce_two_shot_sync(buf, n, scale=0.25, flag=flag, key="t")
         assert torch.allclose(buf.view(torch.bfloat16, n).float(), x.float() * 0.25, atol=1e-2, rtol=1e-2)
         assert fl.item() == 0
+    # sum of partial planes with the arrival wait inside (world of one: a single plane), twice in a row
+    rows, cols = 96, 256
+    part = sm.alloc(rows * cols * 2)
+    pv = part.view(torch.bfloat16, rows * cols).view(rows, cols)
+    bias = torch.randn(cols, device="cuda").to(torch.bfloat16)
+    res = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    for it in range(2):
+        pv.copy_(torch.randn(rows, cols, device="cuda"))
+        o = torch.empty(rows, cols, device="cuda", dtype=torch.bfloat16)
+        sm.sum_partials_sync(part, rows, cols, o, bias, res)
+        assert torch.allclose(o.float(), pv.float() + bias.float() + res.float(), atol=0.1, rtol=2e-2)
     buf.view(torch.bfloat16, n)[17] = float("nan")
     sm.all_reduce_two_shot_sync(buf, n, flag=flag, key="t")
     assert fl.item() == 1
