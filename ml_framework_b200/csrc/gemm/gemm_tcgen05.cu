@@ -333,8 +333,20 @@ static int g_small_m_split = 1;
 // Routes plain GEMMs with M <= 256 and a large weight to the split-K CTA-pair kernel.
 MLF_API void mlf_set_gemm_small_m_split(int on) { g_small_m_split = on; }
 
+MLF_API int mlf_gemm_fewrow(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw, long long ldo,
+                            int accumulate, int max_ctas, uint64_t stream);
+static int g_fewrow = 1;
+// Routes plain products with at most 128 rows against a K-major weight to the weight-as-M stream-K kernel.
+MLF_API void mlf_set_gemm_fewrow(int on) { g_fewrow = on; }
+
 MLF_API int mlf_gemm_bf16(const MlfGemmArgs* a, uint64_t stream) {
   MLF_REQUIRE(a != nullptr, "null args");
+  if (g_fewrow && a->tile_n == 0 && a->comm == nullptr && (a->flags & ~MLF_EPI_ACCUM) == 0 && !a->a_mn && !a->b_mn && a->M <= 128 &&
+      a->N >= 1024 && a->K >= 512 && a->alpha == 1.0f) {
+    const int rcf = mlf_gemm_fewrow(a->a, a->b, a->out, a->M, a->N, a->K, a->lda, a->ldb, a->ldo, (a->flags & MLF_EPI_ACCUM) ? 1 : 0,
+                                    a->max_ctas, stream);
+    if (rcf != -4) return rcf;
+  }
   // CTA pairs for everything with at least 16 pair tiles (split-K fills the GPU when tiles alone cannot).
   // Few rows against a large weight (a decode step: M <= 256) is a weight-streaming problem: one row of
   // tiles cannot occupy the GPU, so the pair kernel splits K and every SM streams a slice of the weight.

@@ -178,27 +178,33 @@ DECODE_SHAPES = [
 
 def bench_gemm_decode(args) -> list[dict]:
     """Few-row GEMMs of a decode step: the weight is read once, so the bound is weight bytes / HBM bandwidth.
-    Columns: the split-K CTA-pair route, the single-CTA route, and torch.matmul (cuBLAS)."""
+    Columns: the weight-as-M stream-K route (the default up to 128 rows), the split-K CTA-pair route, the single-CTA
+    route, and torch.matmul (cuBLAS)."""
     from .. import _lib
     from ..ops.gemm import gemm
     pk = peaks()
     rows = []
     lib = _lib.get()
-    for M in (64, 256):
+    for M in (16, 64, 128, 256):
         for name, N, K in DECODE_SHAPES:
             a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
             b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
             out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            lib.mlf_set_gemm_fewrow(1)
+            ms_fr = time_cuda(lambda: gemm(a, b, out=out), iters=20)           # weight-as-M stream-K route (M <= 128)
+            lib.mlf_set_gemm_fewrow(0)
             lib.mlf_set_gemm_small_m_split(1)
             ms = time_cuda(lambda: gemm(a, b, out=out), iters=20)
             lib.mlf_set_gemm_small_m_split(0)
             ms_1 = time_cuda(lambda: gemm(a, b, out=out), iters=20)
             lib.mlf_set_gemm_small_m_split(1)
+            lib.mlf_set_gemm_fewrow(1)
             ms_ref = time_cuda(lambda: torch.matmul(a, b.t(), out=out), iters=20)
             bound_ms = (N * K + M * K + M * N) * 2 / (pk["hbm_gbs"] * 1e9) * 1e3
-            rows.append({"shape": name, "M": M, "N": N, "K": K, "split_k_ms": round(ms, 4), "single_cta_ms": round(ms_1, 4),
+            rows.append({"shape": name, "M": M, "N": N, "K": K, "fewrow_ms": round(ms_fr, 4) if M <= 128 else None,
+                         "split_k_ms": round(ms, 4), "single_cta_ms": round(ms_1, 4),
                          "cublas_ms": round(ms_ref, 4), "hbm_bound_ms": round(bound_ms, 4),
-                         "frac_of_" + pk["source"] + "_hbm": round(bound_ms / ms, 3)})
+                         "frac_of_" + pk["source"] + "_hbm": round(bound_ms / min(ms_fr, ms), 3)})
             print(rows[-1], flush=True)
     return rows
 

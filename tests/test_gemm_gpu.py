@@ -169,11 +169,21 @@ def test_split_k_and_accumulate_pair_kernel(M, N, K, a_mn, b_mn):
     _check(out2, ref + prev.float(), K)
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (64, 6144, 4096), (200, 1024, 14336), (256, 3584, 4096)])
-def test_few_rows_split_k(M, N, K):
-    """A decode-step product (few rows, a large weight) takes the split-K CTA-pair route; also as an
-    accumulation into the residual stream."""
+@pytest.mark.parametrize("route", ["fewrow", "split_k"])
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (33, 1096, 4096), (64, 6144, 4096), (100, 28672, 1024), (128, 4096, 14336),
+                                   (200, 1024, 14336), (256, 3584, 4096)])
+def test_few_rows_split_k(M, N, K, route):
+    """A decode-step product (few rows, a large weight): up to 128 rows take the weight-as-M stream-K kernel, more rows
+    (or that route switched off) the split-K CTA-pair route; also as an accumulation into the residual stream."""
     torch.manual_seed(6)
+    _lib.get().mlf_set_gemm_fewrow(1 if route == "fewrow" else 0)
+    try:
+        _few_rows_case(M, N, K)
+    finally:
+        _lib.get().mlf_set_gemm_fewrow(1)
+
+
+def _few_rows_case(M, N, K):
     a = _mk(M, K, False, "cuda", 0.25)
     b = _mk(N, K, False, "cuda", 0.25)
     ref, _ = gemm_reference(a, b)
