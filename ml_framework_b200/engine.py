@@ -64,9 +64,7 @@ class TrainEngine:
         if strategy in ("fsdp", "zero2"):
             from .parallel.fsdp import FSDP, FSDPConfig
             self.reducer = None
-            self.fsdp = FSDP(model, FSDPConfig(fused_comm=self.cfg.fused_comm, sharding_strategy="full" if strategy == "fsdp" else "grad_op",
-                                                     reduce_ctas=int(os.environ.get("MLF_FSDP_REDUCE_CTAS", "64")),
-                                                     gather_copy_ctas=int(os.environ.get("MLF_FSDP_COPY_CTAS", "16"))), process_group,
+            self.fsdp = FSDP(model, FSDPConfig(fused_comm=self.cfg.fused_comm, sharding_strategy="full" if strategy == "fsdp" else "grad_op"), process_group,
                              optimizer_kwargs=dict(lr=self.cfg.lr, betas=self.cfg.betas, eps=self.cfg.eps,
                                                    weight_decay=self.cfg.weight_decay))
             self.flat = None

@@ -28,13 +28,28 @@ __all__ = ["gemm", "gemm_reference", "gelu_tanh_ref", "dgelu_tanh_ref"]
 
 _piggyback = None
 
+# bytes per second one copy CTA moves over NVLink (bulk async copies, eight 16 KB pieces in flight) and the GEMM rate
+# used to estimate how long a product keeps its grid busy: together they decide how many parts of a queued copy
+# table one GEMM carries
+_COPY_CTA_BPS = 20e9
+_GEMM_FLOPS = 1.2e15
 
-def set_piggyback(segs: torch.Tensor, n_segs: int, n_copy_ctas: int = 16, on_attached=None, min_flops: float = 2e10):
-    """Queue a table of {src, dst, bytes} peer copies to ride on the next large plain GEMM: that
-    launch gives ``n_copy_ctas`` of its CTAs to the copies (bulk async copies over NVLink) while
-    the rest compute. Used to prefetch the next FSDP unit's parameters."""
+
+def set_piggyback(segs: torch.Tensor, n_segs: int, n_copy_ctas: int = 16, on_attached=None, min_flops: float = 2e10,
+                  part_rows: Optional[list] = None, part_bytes: Optional[list] = None, tag=None):
+    """Queue a table of {src, dst, bytes} peer copies to ride on the next large plain GEMMs: such a launch gives
+    ``n_copy_ctas`` of its CTAs to the copies (bulk async copies over NVLink) while the rest compute. Used to
+    prefetch the next FSDP unit's parameters.
+
+    With ``part_rows`` (row offsets ``[0, r1, ..., n_segs]`` of consecutive parts of the table) and ``part_bytes``
+    (bytes per part) every qualifying GEMM takes only as many parts as its copy CTAs can move in the time the product
+    takes, so the copies spread over the unit's GEMMs instead of stretching the first one; ``on_attached`` runs when
+    the last part has been handed out. Without them the whole table rides on one GEMM."""
     global _piggyback
-    _piggyback = (segs, n_segs, n_copy_ctas, on_attached, min_flops)
+    if part_rows is None:
+        part_rows, part_bytes = [0, n_segs], [0]
+    _piggyback = {"segs": segs, "rows": list(part_rows), "bytes": list(part_bytes), "next": 0, "ctas": n_copy_ctas,
+                  "cb": on_attached, "min_flops": min_flops, "tag": tag}
 
 
 def clear_piggyback():
@@ -43,16 +58,43 @@ def clear_piggyback():
     _piggyback = None
 
 
+def pending_piggyback(tag=None):
+    """(table, first_row, n_rows) of the queued copies that no GEMM has taken yet (for ``tag`` when given), or None.
+    The queue is cleared: the caller copies the rest itself."""
+    global _piggyback
+    pb = _piggyback
+    if pb is None or (tag is not None and pb["tag"] != tag):
+        return None
+    _piggyback = None
+    first = pb["rows"][pb["next"]]
+    n = pb["rows"][-1] - first
+    return (pb["segs"], first, n) if n > 0 else None
+
+
 def _take_piggyback(M, N, K, comm):
     global _piggyback
-    if _piggyback is None or comm is not None or 2.0 * M * N * K < _piggyback[4]:
+    pb = _piggyback
+    flops = 2.0 * M * N * K
+    if pb is None or comm is not None or flops < pb["min_flops"]:
         return None
-    segs, n, ctas, cb, _ = _piggyback
-    _piggyback = None
+    n_parts = len(pb["rows"]) - 1
+    i = pb["next"]
+    # as many parts as the copy CTAs move while the product runs (at least one)
+    budget = flops / _GEMM_FLOPS * pb["ctas"] * _COPY_CTA_BPS
+    j, moved = i + 1, pb["bytes"][i]
+    while j < n_parts and moved + pb["bytes"][j] <= budget:
+        moved += pb["bytes"][j]
+        j += 1
+    first, n = pb["rows"][i], pb["rows"][j] - pb["rows"][i]
+    pb["next"] = j
+    if j >= n_parts:
+        _piggyback = None
+        if pb["cb"] is not None:
+            pb["cb"]()
+    if n <= 0:
+        return None
     cm = GemmComm()
-    cm.n_copy_ctas, cm.extra_segs, cm.n_extra = ctas, segs.data_ptr(), n
-    if cb is not None:
-        cb()
+    cm.n_copy_ctas, cm.extra_segs, cm.n_extra = pb["ctas"], pb["segs"].data_ptr() + first * 24, n
     return cm
 
 

@@ -32,6 +32,7 @@ issued on a side stream one unit ahead of compute.
 """
 from __future__ import annotations
 
+import os
 import zlib
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -68,8 +69,13 @@ class FSDPConfig:
     bucket_size_mb: int = 25
     num_communication_workers: int = 2
     fused_comm: bool = True
-    reduce_ctas: int = 64                  # CTAs of a unit's reduce-scatter kernel (it overlaps the next unit's backward)
-    gather_copy_ctas: int = 16             # CTAs a GEMM lends to the parameter gather of the next unit
+    # tuning knobs of the fused paths; each default can be overridden from the environment (MLF_FSDP_REDUCE_CTAS,
+    # MLF_FSDP_COPY_CTAS, MLF_FSDP_GATHER_PARTS) without touching the code that builds the config
+    reduce_ctas: int = field(default_factory=lambda: int(os.environ.get("MLF_FSDP_REDUCE_CTAS", "64")))   # CTAs of a unit's reduce-scatter kernel (it overlaps the next unit's backward)
+    gather_copy_ctas: int = field(default_factory=lambda: int(os.environ.get("MLF_FSDP_COPY_CTAS", "16")))  # CTAs a GEMM lends to the parameter gather of the next unit
+    # the next unit's gather is cut into this many parts; each large GEMM of the current unit carries as many parts as
+    # its copy CTAs move while it runs (1: the first GEMM carries all)
+    gather_parts: int = field(default_factory=lambda: int(os.environ.get("MLF_FSDP_GATHER_PARTS", "1")))
     min_shard_numel: int = 4096            # smaller / 1-D parameters stay replicated
     hybrid_full_patterns: Sequence[str] = ("transformer", "attention", "attn", "mlp", "blocks")
     hybrid_layerwise_patterns: Sequence[str] = ("classifier", "head")
@@ -420,10 +426,33 @@ class FSDP:
         self._sync_key = "fsdp"
 
     def _copy_table(self, u: "FSDPUnit", full: torch.Tensor) -> torch.Tensor:
+        return self._copy_parts(u, full)[0]
+
+    def _copy_parts(self, u: "FSDPUnit", full: torch.Tensor):
+        """The unit's peer-copy table for the gathered buffer ``full`` laid out as ``cfg.gather_parts`` consecutive parts of
+        about equal bytes (every large segment is cut into that many 16-byte aligned slices, small ones stay whole in
+        the first part): returns (table, row offsets of the parts, bytes per part). Copying all rows copies the unit;
+        copying the rows of some parts copies those slices."""
         from ..dist.symm import make_copy_segs
         key = full.data_ptr()
         if key not in u._copy_tables:
-            u._copy_tables[key] = make_copy_segs([(s, key + d, n) for s, d, n in u._copy_rel], self.device)
+            P = max(1, int(self.cfg.gather_parts))
+            parts = [[] for _ in range(P)]
+            for s, d, n in u._copy_rel:
+                if n < P * 65536:
+                    parts[0].append((s, key + d, n))
+                    continue
+                per = (n // 16 + P - 1) // P * 16
+                for k in range(P):
+                    lo, hi = min(n, k * per), min(n, (k + 1) * per)
+                    if hi > lo:
+                        parts[k].append((s + lo, key + d + lo, hi - lo))
+            rows, nbytes, flat = [0], [], []
+            for part in parts:
+                flat.extend(part)
+                rows.append(len(flat))
+                nbytes.append(sum(x[2] for x in part))
+            u._copy_tables[key] = (make_copy_segs(flat, self.device), rows, nbytes)
         return u._copy_tables[key]
 
     def _install_hooks(self):
@@ -473,6 +502,12 @@ class FSDP:
             if getattr(u, "_prefetched_into", None) == full.data_ptr():
                 u._prefetched_into = None            # already gathered by copy CTAs riding on an earlier GEMM
                 return
+            rest = gemm_mod.pending_piggyback((id(u), full.data_ptr()))
+            if rest is not None:
+                # the unit's GEMM-carried prefetch was only partly handed out: copy the parts nobody took
+                tbl, first, n = rest
+                self.symm.peer_copy(tbl[first:], n)
+                return
             gemm_mod.clear_piggyback()               # a queued prefetch nobody picked up must not fire later
             tbl = self._copy_table(u, full)
             self.symm.peer_copy(tbl, tbl.shape[0])      # nothing else runs at this point: all SMs
@@ -518,9 +553,10 @@ class FSDP:
         from ..ops import gemm as gemm_mod
         u = self.units[j]
         full = self._rot_full[j % 2]
-        tbl = self._copy_table(u, full)
+        tbl, rows, nbytes = self._copy_parts(u, full)
         gemm_mod.set_piggyback(tbl, tbl.shape[0], n_copy_ctas=self.cfg.gather_copy_ctas,
-                               on_attached=lambda u=u, full=full: setattr(u, "_prefetched_into", full.data_ptr()))
+                               on_attached=lambda u=u, full=full: setattr(u, "_prefetched_into", full.data_ptr()),
+                               part_rows=rows, part_bytes=nbytes, tag=(id(u), full.data_ptr()))
 
     def _pre_forward(self, i: int):
         u = self.units[i]

@@ -150,3 +150,27 @@ def test_fsdp_activation_checkpointing_and_async_reductions_match():
         assert all(abs(x - y) < 1e-5 for x, y in zip(a[r][0], b[r][0]))
         for n, p in a[r][1].items():
             assert torch.allclose(b[r][1][n], p, atol=1e-6), n
+
+
+def test_piggyback_parts_are_spread_over_gemms_by_their_size():
+    """A queued copy table in parts: every qualifying GEMM takes as many parts as its copy CTAs move while it runs,
+    the callback fires with the last part, and what nobody took can be fetched back."""
+    import torch
+    from ml_framework_b200.ops import gemm as G
+    segs = torch.zeros(10, 3, dtype=torch.int64)
+    rows, nbytes = [0, 3, 4, 6, 10], [8 << 20, 8 << 20, 8 << 20, 8 << 20]
+    fired = []
+    G.set_piggyback(segs, 10, n_copy_ctas=16, on_attached=lambda: fired.append(1), part_rows=rows, part_bytes=nbytes, tag="u")
+    assert G._take_piggyback(64, 64, 64, None) is None                    # too small a product: nothing attached
+    cm = G._take_piggyback(8192, 2048, 2048, None)                        # ~57 us of product: 18 MB of copies = two parts
+    assert cm.n_extra == 4 and cm.extra_segs == segs.data_ptr() and not fired
+    assert G.pending_piggyback("other") is None
+    cm = G._take_piggyback(8192, 8192, 2048, None)                        # a long product takes the rest
+    assert cm.n_extra == 6 and cm.extra_segs == segs.data_ptr() + 4 * 24 and fired == [1]
+    assert G._take_piggyback(8192, 8192, 2048, None) is None
+    G.set_piggyback(segs, 10, part_rows=rows, part_bytes=nbytes, tag="u")
+    G._take_piggyback(8192, 1024, 2048, None)                             # a short product: one part
+    tbl, first, n = G.pending_piggyback("u")
+    assert (first, n) == (3, 7) and G.pending_piggyback("u") is None
+    G.set_piggyback(segs, 10)                                             # no parts: the whole table rides on one GEMM
+    assert G._take_piggyback(8192, 2048, 2048, None).n_extra == 10
