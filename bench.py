@@ -79,6 +79,15 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
 
+    # Kernels of the package wait on one another across GPUs; every module is loaded when its library is, so that no
+    # first launch has to load code while such a wait is in progress (must be set before the CUDA context exists).
+    os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+    # A rank that is still running after this many seconds prints every thread's Python stack and exits: a stalled
+    # run ends with a record of where it stood instead of waiting for the process-group watchdog.
+    hang_s = int(os.environ.get("MLF_HANG_DUMP_S", "900"))
+    if hang_s > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(hang_s, exit=True)
     import torch
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     rank = int(os.environ.get("RANK", "0"))
@@ -97,7 +106,7 @@ def main():
     pg = None
     if world > 1:
         from ml_framework_b200.dist.process_group import init_process_group
-        pg = init_process_group("nccl")
+        pg = init_process_group("nccl", timeout_s=float(os.environ.get("MLF_PG_TIMEOUT_S", "300")))
 
     from ml_framework_b200.models.gpt import GPT, GPTConfig
     cfg = GPTConfig.gpt_1_3b() if args.model == "gpt-1.3b" else GPTConfig.tiny()
