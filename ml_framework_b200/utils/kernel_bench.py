@@ -248,6 +248,23 @@ def run_paged_small() -> list[dict]:
     return [{"ran": "paged decode B256 ctx1024 x2"}]
 
 
+def run_fewrow_small() -> list[dict]:
+    """Three launches of the few-row GEMM at the Llama-8B gate_up shape (64 rows against a 28672 x 4096 weight, 235 MB
+    > L2), accumulating into the output so that no zeroing launch sits in between: the case profiled with ncu."""
+    from .. import _lib
+    from ..ops.gemm import gemm
+    M, N, K = 64, 28672, 4096
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        gemm(a, b, out=out, flags=_lib.EPI_ACCUM)
+    torch.cuda.synchronize()
+    ref = 3.0 * (a.float() @ b.float().t())
+    err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+    return [{"ran": "few-row GEMM 64 x 28672 x 4096, three accumulating launches", "max_rel_err": round(err, 5)}]
+
+
 def run_decode_step_small() -> list[dict]:
     """Llama-8B layer shapes, 4 layers, 64 sequences with 576 cached tokens: a batched prefill, then three decode steps
     launched eagerly (no graph replay), so that a launch list shows every kernel of a decode step."""
@@ -308,7 +325,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small", "elementwise_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small", "elementwise_small", "fewrow_small"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -331,6 +348,8 @@ def main():
         rows = run_paged_small()
     elif args.what == "decode_step_small":
         rows = run_decode_step_small()
+    elif args.what == "fewrow_small":
+        rows = run_fewrow_small()
     elif args.what == "elementwise_small":
         rows = run_elementwise_small()
     elif args.what == "attn":
