@@ -8,7 +8,7 @@
 //
 // Graph inspection is what the validator works on: after a capture the node list of the real
 // cudaGraph_t is read back with its node types (kernel, memcpy, memset, host callback, memory
-// allocation / free, event wait / record, child graph), so validation rules judge what the capture
+// allocation / free, event wait / record, child graph), so validation rules apply to what the capture
 // recorded rather than what a caller declares.
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -217,7 +217,7 @@ class CUDAGraphManager:
             out = fn(*static_in)
         kinds, issues = [], []
         if inspect:
-            # the cudaGraph_t is kept until instantiation: read its nodes back and judge what was recorded
+            # the cudaGraph_t is kept until instantiation: read its nodes back and check what was recorded
             from . import cuda_rt
             raw = cuda_rt.Graph(int(g.raw_cuda_graph()), owned=False)
             kinds = raw.node_kinds()

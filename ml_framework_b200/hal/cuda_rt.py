@@ -7,7 +7,7 @@ safe-handle wrappers (CudaSafeHandles.cs, CudaStream.cs, CudaEvent.cs, CudaDevic
 collection; failures raise :class:`CudaRuntimeError` with the runtime's message.
 
 ``Graph.node_kinds()`` returns the node types of a real captured ``cudaGraph_t``; the graph validator
-(:mod:`ml_framework_b200.hal.cuda_graphs`) judges captures by that list.
+(:mod:`ml_framework_b200.hal.cuda_graphs`) validates captures against that list.
 """
 from __future__ import annotations
 
