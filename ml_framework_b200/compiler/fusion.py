@@ -7,12 +7,13 @@ Fusion/Validation/**), decision logging (Fusion/Profiling/**), and a CUDA text g
 templates are one-thread-per-element scalar fp32 (Fusion/KernelCode/Cuda/CudaKernelTemplates.cs:8-160)
 behind Triton / XLA adapter interfaces with no compiler attached (Fusion/Backends/*.cs).
 
-Here fusion does not generate code. The fused kernels exist, hand-written: a GEMM's epilogue takes
-bias, GELU, SwiGLU, residual add, dGELU, dSwiGLU and accumulate; normalisation takes the residual;
-conv + batch-norm folds into the conv's weights. The planner's job is to recognise those shapes in a
-graph and rewrite them to the fused op; what it cannot map stays as separate ops. ``CudaSourceGenerator``
-renders vectorised element-wise CUDA source (16-byte loads, grid-stride) for chains the hand-written
-set does not cover; it returns text for an offline ``nvcc`` build and nothing in the hot path uses it.
+Here the hot fused kernels exist, hand-written: a GEMM's epilogue takes bias, GELU, SwiGLU, residual add,
+dGELU, dSwiGLU and accumulate; normalisation takes the residual; conv + batch-norm folds into the conv's
+weights. The planner's job is to recognise those shapes in a graph and rewrite them to the fused op. Chains
+of element-wise ops that the hand-written set does not cover are rewritten to one ``fused_elementwise`` op,
+which the graph executor runs as ONE kernel generated, compiled with ``nvcc`` and cached at run time
+(:mod:`ml_framework_b200.compiler.jit_cuda`); ``FusionEngine.compile_chain`` gives the callable directly.
+``CudaSourceGenerator`` is the older text-only renderer kept for listings.
 """
 from __future__ import annotations
 
@@ -133,6 +134,13 @@ class FusionEngine:
         w2 = w * s.view(-1, 1, 1, 1)
         b2 = (b if b is not None else torch.zeros_like(mean)) - mean
         return w2, b2 * s + beta
+
+    @staticmethod
+    def compile_chain(spec: Sequence[Tuple[str, bool]], **kw):
+        """The callable of a fused element-wise chain (``spec`` as stored in a ``fused_elementwise`` op's attributes):
+        one generated CUDA kernel on GPU tensors, the same chain in PyTorch elsewhere."""
+        from .jit_cuda import compile_chain
+        return compile_chain([kind for kind, _ in spec], **kw)
 
     def plan(self, g: HLGraph) -> Dict[str, object]:
         return {"gemm_epilogues": self.find_gemm_epilogues(g), "elementwise_chains": self.find_elementwise_chains(g),

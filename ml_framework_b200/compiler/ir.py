@@ -156,12 +156,25 @@ def _execute(o: Op, x: List[torch.Tensor]) -> torch.Tensor:
         return r
     if k == "layer_norm": return F.layer_norm(x[0], x[0].shape[-1:], x[1] if len(x) > 1 else None, x[2] if len(x) > 2 else None, a.get("eps", 1e-5))
     if k == "fused_elementwise":
+        if x[0].is_cuda and a.get("jit", True) and all(t.shape == x[0].shape and t.dtype == x[0].dtype for t in x[1:]) \
+                and x[0].dtype in (torch.bfloat16, torch.float16, torch.float32):
+            # one generated kernel for the whole chain (compiled on first use, cached per chain and dtype)
+            from .jit_cuda import SNIPPETS, compile_chain
+            kinds = tuple(kind for kind, _ in a["chain"])
+            if all(kd in SNIPPETS for kd in kinds):
+                fn = _JIT_CHAINS.get(kinds)
+                if fn is None:
+                    fn = _JIT_CHAINS[kinds] = compile_chain(kinds)
+                return fn(*x)
         v = x[0]
         rest = iter(x[1:])
         for kind, binary in a["chain"]:
             v = _execute(Op(kind, [], ""), [v, next(rest)] if binary else [v])
         return v
     raise NotImplementedError(k)
+
+
+_JIT_CHAINS: Dict[tuple, object] = {}       # fused element-wise chains compiled at run time, by op-name tuple
 
 
 # ------------------------------------------------------------------ passes
