@@ -55,6 +55,8 @@ def _summarise_clocks(samples):
 
 
 def reference_unavailable():
+    if int(os.environ.get("RANK", "0")) != 0:        # launched one process per GPU: one line is enough
+        return
     print(json.dumps({"impl": "reference", "unavailable": "the reference is a C#/.NET project with no Python package "
                       "(pip: 'neither setup.py nor pyproject.toml found'), dotnet is not installed, and its NCCL path "
                       "pins host arrays and cannot touch device memory"}))
