@@ -128,6 +128,10 @@ class KVCacheBlockManager:
         cap = 4096
         out = (C.c_int * cap)()
         n = self._L.mlf_bm_seq_blocks(self._h, C.c_longlong(seq_id), out, cap)
+        if n > cap:                                   # a very long sequence: ask again with room for all of it
+            cap = n
+            out = (C.c_int * cap)()
+            n = self._L.mlf_bm_seq_blocks(self._h, C.c_longlong(seq_id), out, cap)
         return [] if n < 0 else list(out[:min(n, cap)])
 
     def get_sequence_length(self, seq_id: int) -> int:
