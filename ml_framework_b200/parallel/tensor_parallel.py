@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, Iterable, List, Optional, Sequence
 
 import torch
 import torch.nn as nn
@@ -605,9 +605,58 @@ class TPGradientManager:
 
     def __init__(self, tp: TPContext, dp_group=None):
         self.tp, self.dp = tp, dp_group
+        self.reducer = None
+        self.dp_symm = None
+
+    def attach_flat(self, params: Sequence[nn.Parameter], bucket_size_mb: float = 25.0, fused: bool = True,
+                    grad_dtype: Optional[torch.dtype] = None):
+        """Re-homes ``params`` (this rank's tensor-parallel shards and replicated parameters) into one flat buffer
+        whose gradients are averaged over the DATA-parallel group bucket by bucket while backward runs: the same
+        hook-driven reducer as DDP (:class:`ml_framework_b200.parallel.ddp.FlatGradReducer`). With ``fused`` and a
+        data-parallel group whose ranks can map each other's memory, the flat gradient buffer lives in symmetric memory
+        of that group and every bucket is one launch of the in-kernel two-shot all-reduce (1/W scaling and overflow
+        check included); otherwise buckets are process-group all-reduces. Returns the ``FlatParams``; call
+        ``finish_gradient_sync()`` after backward."""
+        from .ddp import FlatGradReducer, fused_comm_possible
+        from .flat import FlatParams
+        params = list(params)
+        dev = params[0].device
+        gdt = grad_dtype or params[0].dtype
+        grad_alloc, holder, flag = None, {}, None
+        multi = self.dp is not None and self.dp.world_size > 1
+        if multi and fused and fused_comm_possible(self.dp, dev, True, gdt):
+            from ..dist.symm import SymmetricMemory
+            self.dp_symm = SymmetricMemory(self.dp, dev)
+
+            def grad_alloc(n, dt, holder=holder):
+                holder["buf"] = self.dp_symm.alloc(n * torch.empty(0, dtype=dt).element_size())
+                return holder["buf"].view(dt, n)
+        flat = FlatParams(params, grad_dtype=grad_dtype, grad_alloc=grad_alloc)
+        if multi:
+            self.dp.broadcast(flat.flat, src=0)            # data-parallel replicas start from the same values
+            if self.dp_symm is not None:
+                flag = self.dp_symm.alloc_flag()
+            self.reducer = FlatGradReducer(flat, self.dp, bucket_size_mb, symm=self.dp_symm, symm_buf=holder.get("buf"), flag=flag)
+        self.flat, self.overflow_flag = flat, flag
+        return flat
+
+    def finish_gradient_sync(self):
+        """Reduces what the gradient-ready hooks could not and waits for the communication stream (after backward)."""
+        if getattr(self, "flat", None) is not None:
+            self.flat.gather_missing_grads()
+        if self.reducer is not None:
+            self.reducer.finish()
+
+    def close(self):
+        if self.dp_symm is not None:
+            self.dp_symm.close()
+            self.dp_symm = None
 
     def synchronize_gradients(self, params: Iterable[nn.Parameter]):
         if self.dp is None or self.dp.world_size == 1:
+            return
+        if self.reducer is not None:                       # flat path: the buckets are (being) reduced already
+            self.finish_gradient_sync()
             return
         grads = [p.grad for p in params if p.grad is not None]
         if not grads:

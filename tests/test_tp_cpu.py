@@ -170,3 +170,51 @@ def test_llama_tp_sequence_parallel_matches_plain_tensor_parallel():
         assert abs(l0 - l1) < 1e-5
         for n in g0:
             assert torch.allclose(g0[n], g1[n], atol=2e-5, rtol=1e-4), (n, (g0[n] - g1[n]).abs().max())
+
+
+def test_tp_gradient_manager_flat_path_averages_over_the_data_parallel_group():
+    """TP x DP: each data-parallel replica holds the same shard; gradients of different micro-batches are averaged over
+    the data-parallel group through the flat, bucketed, hook-driven reducer (several buckets)."""
+    W = 2
+
+    def make():                                                  # fake ranks are threads: no use of the global generator
+        g = torch.Generator().manual_seed(0)
+        lin1, lin2 = nn.Linear(16, 32), nn.Linear(32, 16)
+        with torch.no_grad():
+            for p in list(lin1.parameters()) + list(lin2.parameters()):
+                p.copy_(torch.randn(p.shape, generator=g) * 0.2)
+        return lin1, lin2
+
+    def run(dp_pg):
+        lin1, lin2 = make()
+        gm = tpm.TPGradientManager(tpm.TPContext(None, None, False), dp_pg)
+        params = list(lin1.parameters()) + list(lin2.parameters())
+        flat = gm.attach_flat(params, bucket_size_mb=0.002, fused=True)      # CPU tensors: process-group all-reduces
+        assert gm.reducer is not None and len(gm.reducer.ranges) >= 2
+        g = torch.Generator().manual_seed(100 + dp_pg.rank)
+        outs = []
+        for step in range(2):
+            flat.zero_grad()
+            x = torch.randn(8, 16, generator=g)
+            lin2(torch.relu(lin1(x))).pow(2).mean().backward()
+            gm.synchronize_gradients(params)
+            outs.append([p.main_grad.clone() for p in params])
+        gm.close()
+        return outs
+
+    res = run_fake_world(W, run)
+    for step in range(2):
+        for k in range(4):
+            assert torch.allclose(res[0][step][k], res[1][step][k], atol=1e-6)           # replicas agree
+    # and the agreed value is the mean of the per-replica gradients
+    gens = [torch.Generator().manual_seed(100 + r) for r in range(W)]
+    for step in range(2):
+        want = None
+        for r in range(W):
+            lin1, lin2 = make()
+            x = torch.randn(8, 16, generator=gens[r])
+            lin2(torch.relu(lin1(x))).pow(2).mean().backward()
+            gr = [p.grad / W for p in list(lin1.parameters()) + list(lin2.parameters())]
+            want = gr if want is None else [a + b for a, b in zip(want, gr)]
+        for k in range(4):
+            assert torch.allclose(res[0][step][k], want[k], atol=1e-5), (step, k)
