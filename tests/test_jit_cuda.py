@@ -69,6 +69,8 @@ def test_graph_executor_runs_fused_chain_op():
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_fused_chain_kernel_matches_fp32_reference(dtype, tmp_path):
+    if not J.NvccCompiler().available():
+        pytest.skip("no nvcc on this machine: nothing to compile the generated source with")
     torch.manual_seed(2)
     comp = J.NvccCompiler(cache_dir=str(tmp_path))
     f = J.FusedElementwise(["mul", "add", "silu", "maximum"], compiler=comp)
@@ -93,6 +95,8 @@ def test_fused_chain_kernel_matches_fp32_reference(dtype, tmp_path):
 
 @pytest.mark.gpu
 def test_graph_fusion_pass_runs_the_generated_kernel_on_gpu():
+    if not J.NvccCompiler().available():
+        pytest.skip("no nvcc on this machine: nothing to compile the generated source with")
     from ml_framework_b200.compiler.ir import Op, _execute
     a, b = torch.randn(2, 4096, device="cuda").to(torch.bfloat16)
     op = Op("fused_elementwise", ["a", "b"], "y", {"chain": [("add", True), ("relu", False)]})
