@@ -159,13 +159,16 @@ def _execute(o: Op, x: List[torch.Tensor]) -> torch.Tensor:
         if x[0].is_cuda and a.get("jit", True) and all(t.shape == x[0].shape and t.dtype == x[0].dtype for t in x[1:]) \
                 and x[0].dtype in (torch.bfloat16, torch.float16, torch.float32):
             # one generated kernel for the whole chain (compiled on first use, cached per chain and dtype)
-            from .jit_cuda import SNIPPETS, compile_chain
+            from .jit_cuda import SNIPPETS, CompileError, compile_chain
             kinds = tuple(kind for kind, _ in a["chain"])
-            if all(kd in SNIPPETS for kd in kinds):
+            if all(kd in SNIPPETS for kd in kinds) and _JIT_CHAINS.get(kinds) is not False:
                 fn = _JIT_CHAINS.get(kinds)
                 if fn is None:
                     fn = _JIT_CHAINS[kinds] = compile_chain(kinds)
-                return fn(*x)
+                try:
+                    return fn(*x)
+                except CompileError:
+                    _JIT_CHAINS[kinds] = False       # no compiler here: this chain runs op by op from now on
         v = x[0]
         rest = iter(x[1:])
         for kind, binary in a["chain"]:
