@@ -248,6 +248,32 @@ def run_paged_small() -> list[dict]:
     return [{"ran": "paged decode B256 ctx1024 x2"}]
 
 
+def bench_jit_chain(args) -> list[dict]:
+    """A fused element-wise chain compiled at run time (``compiler.jit_cuda``): relu(a * b + c) on 64 Mi bf16 elements
+    per tensor (three reads and one write of 128 MB each), default configuration and the autotuner's pick, against the
+    same chain as three PyTorch kernels. Bound = bytes moved / copy bandwidth."""
+    from ..compiler.jit_cuda import FusedElementwise
+    pk = peaks()
+    n = 64 * 1024 * 1024
+    a, b, c = (torch.randn(n, device="cuda").to(torch.bfloat16) for _ in range(3))
+    out = torch.empty_like(a)
+    rows = []
+    bound = 4 * n * 2 / (pk["hbm_gbs"] * 1e9) * 1e3
+    f = FusedElementwise(["mul", "add", "relu"])
+    ms = time_cuda(lambda: f(a, b, c, out=out), iters=10)
+    ft = FusedElementwise(["mul", "add", "relu"], autotune=True)
+    ft(a, b, c, out=out)
+    ms_t = time_cuda(lambda: ft(a, b, c, out=out), iters=10)
+    ms_torch = time_cuda(lambda: torch.relu(a * b + c), iters=10)
+    ref = torch.relu(a.float() * b.float() + c.float())
+    err = (out.float() - ref).abs().max().item()
+    rows.append({"chain": "relu(a * b + c)", "elements": n, "generated_ms": round(ms, 4), "autotuned_ms": round(ms_t, 4),
+                 "autotuned_config": next(iter(ft.chosen.values())).key(), "torch_three_kernels_ms": round(ms_torch, 4),
+                 "hbm_bound_ms": round(bound, 4), "frac_of_" + pk["source"] + "_hbm": round(bound / min(ms, ms_t), 3), "max_abs_err": err})
+    print(rows[-1], flush=True)
+    return rows
+
+
 def run_fewrow_small() -> list[dict]:
     """Three launches of the few-row GEMM at the Llama-8B gate_up shape (64 rows against a 28672 x 4096 weight, 235 MB
     > L2), accumulating into the output so that no zeroing launch sits in between: the case profiled with ncu."""
@@ -325,7 +351,7 @@ def run_gemm_small() -> list[dict]:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small", "elementwise_small", "fewrow_small"])
+    ap.add_argument("what", choices=["gemm", "gemm_epi", "attn", "elementwise", "attn_small", "gemm_small", "fused_small", "gemm_decode", "paged", "paged_small", "decode_step_small", "elementwise_small", "fewrow_small", "jit_chain"])
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     if args.what == "gemm":
@@ -350,6 +376,8 @@ def main():
         rows = run_decode_step_small()
     elif args.what == "fewrow_small":
         rows = run_fewrow_small()
+    elif args.what == "jit_chain":
+        rows = bench_jit_chain(args)
     elif args.what == "elementwise_small":
         rows = run_elementwise_small()
     elif args.what == "attn":
