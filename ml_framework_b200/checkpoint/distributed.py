@@ -569,8 +569,9 @@ class DistributedCheckpoint:
 
     def delete(self, tag: str):
         p = self._prefix(tag)
+        base = os.path.basename(p)
         for f in os.listdir(self.dir):
-            if f == os.path.basename(manifest_path(p)) or (f.startswith(os.path.basename(p) + "_shard_") and f.endswith(SHARD_EXT)):
+            if f == os.path.basename(manifest_path(p)) or f == base + ".ckpt" or (f.startswith(base + "_shard_") and f.endswith(SHARD_EXT)):
                 os.remove(os.path.join(self.dir, f))
 
 

@@ -137,3 +137,55 @@ def test_retry_and_circuit_breaker():
         import time
         FaultToleranceHandler().execute_with_timeout(lambda: time.sleep(1.0), 0.05)
     assert RetryPolicy().delay(10) == 30.0
+
+
+def test_storage_backend_rollback_manager_cancel_and_timeouts(tmp_path):
+    from ml_framework_b200.checkpoint.distributed import (CheckpointCorruptError, CheckpointRollbackManager, LocalFileSystemStorage,
+                                                          StorageFactory, manifest_path, shard_path)
+    st = StorageFactory.create("local", root=str(tmp_path / "store"))
+    assert isinstance(st, LocalFileSystemStorage) and st.list() == []
+    st.write("a/b.bin", b"hello")
+    st.write("top.bin", b"12345678")
+    assert st.exists("a/b.bin") and st.read("a/b.bin") == b"hello" and st.get_metadata("top.bin")["size"] == 8
+    assert st.list("top") == ["top.bin"] and st.path("/abs/x") == "/abs/x"
+    st.delete("top.bin")
+    st.delete("top.bin")                                            # deleting what is gone is not an error
+    assert not st.exists("top.bin")
+    with pytest.raises(ValueError):
+        StorageFactory.create("s3")
+    ck = DistributedCheckpoint(str(tmp_path / "ck"), max_to_keep=0)
+    s0 = _state(2)
+    ck.save_model_only("good", s0, step=7)
+    assert set(ck.load("good").tensors) == {"model." + k for k in s0} and ck.load("good").metadata.Training.Step == 7
+    rb = CheckpointRollbackManager(ck)
+    with pytest.raises(CheckpointError):
+        rb.rollback()                                               # nothing verified yet
+    rb.mark_good("good")
+    ck.save("bad", {"w": s0["w"] * 2})
+    with open(shard_path(ck._prefix("bad"), 0), "r+b") as f:         # damage the newer checkpoint
+        f.seek(200)
+        f.write(b"\\xff" * 16)
+    with pytest.raises(CheckpointCorruptError):
+        rb.mark_good("bad")
+    back = rb.rollback()
+    assert rb.last_good == "good" and torch.equal(back.tensors["model.w"], s0["w"])
+    ck.save("one", s0, options=SaveOptions(format="singlefile"))
+    assert os.path.exists(ck._prefix("one") + ".ckpt")
+    ck.delete("one")
+    ck.delete("bad")
+    assert not os.path.exists(ck._prefix("one") + ".ckpt") and not os.path.exists(manifest_path(ck._prefix("bad")))
+    assert ck.list_checkpoints() == ["good"]
+    mgr = AsyncCheckpointManager(ck, max_pending=4)
+    mgr.cancel_checkpoint("skip-me")
+    mgr.queue_save("keep-me", s0)
+    mgr.queue_save("skip-me", s0)
+    mgr.wait_for_completion()
+    mgr.shutdown()
+    assert "keep-me" in ck.list_checkpoints() and "skip-me" not in ck.list_checkpoints()
+    h = FaultToleranceHandler(RetryPolicy(max_retries=0), sleep=lambda s: None)
+    import time as _t
+    with pytest.raises(CheckpointError, match="timed out"):
+        h.execute_with_timeout(lambda: _t.sleep(1.0), 0.05)
+    assert h.execute_with_timeout(lambda a, b=1: a + b, 1.0, 2, b=3) == 5
+    with pytest.raises(KeyError):
+        h.execute_with_timeout(lambda: {}["x"], 1.0)
