@@ -1,0 +1,133 @@
+"""Hardware abstraction layer on CPU: device ids, streams and events of the CPU backend, the operation table of both
+backends against PyTorch, the registry, dynamic-shape memory (bounds, adaptive padding, predictive allocation,
+pressure handling)."""
+import pytest
+import torch
+
+from ml_framework_b200.hal import core as H
+
+
+def test_device_ids_streams_events_and_properties_on_cpu():
+    did = H.DeviceId(H.DeviceType.CUDA, 3)
+    assert str(did) == "cuda:3" and did.torch() == torch.device("cuda", 3) and str(H.DeviceId(H.DeviceType.CPU)) == "cpu:0"
+    be = H.BackendRegistry.get("cpu")
+    d = be.device(0)
+    assert not d.is_cuda and d.properties()["name"] == "cpu" and d.properties()["cores"] >= 1
+    d.synchronize()
+    s = d.create_stream(priority=-1)
+    order = []
+    s.enqueue(lambda: order.append("a"))
+    s.enqueue(lambda: order.append("b"))
+    assert order == ["a", "b"] and s.handle == 0
+    ev = d.create_event()
+    assert not ev.query()
+    ev.record(s)
+    assert ev.query() and ev.elapsed_ms(s.record_event()) == 0.0
+    ev.synchronize()
+    s.wait_event(ev)
+    s.synchronize()
+    b = d.allocate(100)
+    assert b.ptr == b.tensor.data_ptr() and b.size >= 100
+    b.free()
+    assert b.freed
+    d.allocator.empty_cache()
+    with pytest.raises(ValueError):
+        d.allocate(0)
+    with pytest.raises(NotImplementedError):
+        H.MemoryAllocator(d).allocate(8)
+
+
+def test_operation_table_matches_torch_on_both_backends():
+    torch.manual_seed(0)
+    a, b = torch.randn(4, 6), torch.randn(4, 6)
+    O = H.Operation
+    for name in ("cpu", "b200"):                                   # the B200 backend falls back to PyTorch for CPU tensors
+        be = H.BackendRegistry.get(name)
+        assert all(be.supports(op) for op in O)
+        assert torch.equal(be.execute(O.ADD, [a, b]), a + b) and torch.equal(be.execute(O.SUBTRACT, [a, b]), a - b)
+        assert torch.equal(be.execute(O.MULTIPLY, [a, b]), a * b) and torch.equal(be.execute(O.DIVIDE, [a, b]), a / b)
+        assert torch.equal(be.execute(O.MATMUL, [a, b.t()]), a @ b.t()) and torch.equal(be.execute(O.TRANSPOSE, [a]), a.t())
+        assert torch.equal(be.execute(O.SUM, [a], dim=1), a.sum(1)) and torch.equal(be.execute(O.SUM, [a]), a.sum())
+        assert torch.equal(be.execute(O.MEAN, [a], dim=0), a.mean(0)) and torch.equal(be.execute(O.MAX, [a]), a.max())
+        assert torch.equal(be.execute(O.MIN, [a], dim=1), a.amin(1)) and torch.equal(be.execute(O.MAX, [a], dim=0), a.amax(0))
+        c = be.execute(O.COPY, [a])
+        assert torch.equal(c, a) and c.data_ptr() != a.data_ptr()
+        assert torch.equal(be.execute(O.FILL, [a], value=2.5), torch.full_like(a, 2.5))
+        assert torch.equal(be.execute(O.RELU, [a]), torch.relu(a)) and torch.equal(be.execute(O.SIGMOID, [a]), torch.sigmoid(a))
+        assert torch.equal(be.execute(O.TANH, [a]), torch.tanh(a))
+        x, w, bias = torch.randn(1, 2, 8, 8), torch.randn(3, 2, 3, 3), torch.randn(3)
+        assert torch.allclose(be.execute(O.CONV2D, [x, w, bias], padding=1), torch.nn.functional.conv2d(x, w, bias, padding=1))
+        assert torch.equal(be.execute(O.MAXPOOL2D, [x]), torch.nn.functional.max_pool2d(x, 2))
+        assert be.execute(O.CAST, [a], dtype=torch.float64).dtype == torch.float64
+        assert be.execute(O.RESHAPE, [a], shape=(6, 4)).shape == (6, 4)
+    assert "cpu" in H.BackendRegistry.available() and H.BackendRegistry.best().name in ("cpu", "b200")
+    assert H.BackendRegistry.get("b200").is_available() == torch.cuda.is_available()
+    assert H.BackendRegistry.get("b200").device_count() == torch.cuda.device_count() and H.Backend().device_count() == 1
+    with pytest.raises(KeyError):
+        H.BackendRegistry.get("tpu")
+
+    class Custom(H.Backend):
+        name = "custom"
+    H.BackendRegistry.register(Custom())
+    assert H.BackendRegistry.get("custom").is_available() and "custom" in H.BackendRegistry.available()
+
+
+def test_shape_bounds_adaptive_padding_and_predictive_allocation():
+    bnd = H.ShapeBounds((1, 8), (64, 8), expected_shape=(16, 8))
+    assert bnd.contains((32, 8)) and not bnd.contains((65, 8)) and not bnd.contains((4,)) and bnd.max_elements() == 512
+    with pytest.raises(ValueError):
+        H.ShapeBounds((2, 2), (1, 2))
+    with pytest.raises(ValueError):
+        H.ShapeBounds((1,), (1, 2))
+    pad = H.AdaptivePaddingStrategy(initial=1.2, lo=1.0, hi=1.5)
+    assert pad.padded(100) == 120
+    for _ in range(16):
+        pad.observe(True)                                           # re-allocating all the time: pad more
+    grown = pad.factor
+    assert grown > 1.2
+    for _ in range(64):
+        pad.observe(True)
+    assert pad.factor == 1.5                                        # capped
+    for _ in range(16 * 60):
+        pad.observe(False)                                          # padding never needed: shrink to the floor
+    assert pad.factor == 1.0
+    d = H.BackendRegistry.get("cpu").device(0)
+    pa = H.PredictiveAllocator(H.SimpleAllocator(d), padding=H.AdaptivePaddingStrategy(1.5))
+    t = pa.get("kv", (10, 4), torch.float32)
+    t.fill_(3.0)
+    assert t.shape == (10, 4) and pa.reallocations == 0
+    t2 = pa.get("kv", (14, 4), torch.float32)                       # fits the padded capacity (15 rows): same storage
+    assert t2.data_ptr() == t.data_ptr() and pa.reallocations == 0 and float(t2[0, 0]) == 3.0
+    t3 = pa.get("kv", (40, 4), torch.float32)
+    assert pa.reallocations == 1 and t3.shape == (40, 4) and pa.predict_elements("kv") == 160
+    t4 = pa.get("kv", (8, 4), torch.bfloat16)                       # another dtype needs its own buffer
+    assert t4.dtype == torch.bfloat16 and pa.reallocations == 2
+    capped = pa.get("bounded", (60, 8), torch.float32, H.ShapeBounds((1, 8), (64, 8)))
+    assert capped.shape == (60, 8) and pa._handles["bounded"].capacity_elements == 512      # never beyond the bound
+    with pytest.raises(ValueError):
+        pa._handles["bounded"].view((65, 8))
+    pa.release("kv")
+    pa.release("kv")                                                # releasing twice is harmless
+    assert "kv" not in pa._handles and pa.predict_elements("nothing") == 0
+
+
+def test_memory_pressure_handler_releases_low_priority_first_until_below_the_low_mark():
+    used = [95]
+    log = []
+
+    def rel(name, amount):
+        def f():
+            log.append(name)
+            used[0] -= amount
+            return amount
+        return f
+    h = H.MemoryPressureHandler(100, high=0.9, low=0.75, usage_fn=lambda: used[0])
+    h.register(rel("important", 50), priority=10)
+    h.register(rel("cache", 10), priority=0)
+    h.register(rel("scratch", 15), priority=5)
+    assert h.pressure() == 0.95 and h.check() == 25 and log == ["cache", "scratch"] and used[0] == 70 and h.events == 1
+    assert h.check() == 0 and h.events == 1                         # below the high mark: nothing to do
+    used[0] = 99
+    assert h.check() == 25 and used[0] == 74 and h.events == 2      # stops as soon as usage is under the low mark
+    used[0] = 140
+    assert h.check() == 75 and log[-1] == "important" and used[0] == 65
