@@ -217,6 +217,11 @@ class Tracer:
     def __bool__(self):
         raise TraceError("the truth value of a traced tensor is not known while tracing (data-dependent control flow)")
 
+    def _compare(self, other):
+        raise TraceError("comparisons of traced tensors are not traceable (their result would steer Python control flow)")
+
+    __lt__ = __le__ = __gt__ = __ge__ = _compare
+
     def _concrete(self, *a, **k):
         raise TraceError("the value of a traced tensor is not known while tracing")
 
@@ -303,7 +308,8 @@ class JitFunction:
                 g, many = self._trace(inputs)
                 ent = ("graph", (g, many))
                 self.stats["traced"] += 1
-            except TraceError:
+            except (TraceError, TypeError, AttributeError, NotImplementedError):
+                # not expressible in the IR (an operation or a method the tracer does not know, control flow on values)
                 if all(t.is_cuda for t in inputs) and torch.cuda.is_available():
                     ent = ("capture", _graph_manager())
                     self.stats["captured"] += 1
