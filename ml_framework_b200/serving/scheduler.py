@@ -359,6 +359,7 @@ class SchedulerMetricsCollector:
     def __init__(self, capacity: int = 10000):
         self.iter_ms, self.batch_sizes = CircularBuffer(capacity), CircularBuffer(capacity)
         self.ttft, self.latency, self.tokens_per_req = CircularBuffer(capacity), CircularBuffer(capacity), CircularBuffer(capacity)
+        self.utilization = CircularBuffer(capacity)
         self.tokens = SlidingWindowCounter()
         self.errors: Dict[str, int] = {}
         self.completed = 0
@@ -383,7 +384,8 @@ class SchedulerMetricsCollector:
         self.tokens_per_req.add(len(res.tokens))
 
     def record_batch_utilization(self, used: int, capacity: int):
-        pass
+        """Share of the batch slots an iteration filled (SchedulerMetricsCollector.RecordBatchUtilization)."""
+        self.utilization.add(used / capacity if capacity > 0 else 0.0)
 
     def record_error(self, kind: str):
         self.errors[kind] = self.errors.get(kind, 0) + 1
@@ -392,6 +394,7 @@ class SchedulerMetricsCollector:
         it = self.iter_ms.values()
         return {"iterations": len(it), "iteration_ms_p50": _pct(it, 0.5), "iteration_ms_p99": _pct(it, 0.99),
                 "mean_batch": (sum(self.batch_sizes.values()) / len(self.batch_sizes)) if len(self.batch_sizes) else 0.0,
+                "mean_batch_utilization": (sum(self.utilization.values()) / len(self.utilization)) if len(self.utilization) else 0.0,
                 "completed": self.completed, "total_tokens": self.total_tokens,
                 "decode_tokens_per_s": self.total_tokens / self.decode_time_s if self.decode_time_s else 0.0,
                 "ttft_p50_s": _pct(self.ttft.values(), 0.5), "ttft_p99_s": _pct(self.ttft.values(), 0.99),
@@ -571,6 +574,7 @@ class ContinuousBatchScheduler:
         self.batch_manager.remove_completed([r for r, _ in done])
         self.iterations += 1
         self.metrics.record_iteration((now - t0) * 1e3, len(batch.requests), len(out.generated_tokens))
+        self.metrics.record_batch_utilization(len(batch.requests), self.batch_manager.c.max_batch_size)
         return True
 
     def _complete(self, r: Request, reason: CompletionReason, now: float, error: Optional[str] = None):

@@ -316,3 +316,110 @@ def test_paged_attention_layer_prefill_chunks_and_decode_match_contiguous_attent
     assert kv.get_sequence_length(7) == 11 and kv.get_sequence_length(9) == 6
     with pytest.raises(ValueError):
         layer(xs[7][:3], kv, [7, 9], AttentionPhase.PREFILL)
+
+
+def test_queue_priorities_capacity_accounting_metrics_windows_and_client_helpers():
+    from ml_framework_b200.serving.scheduler import (CapacityConstraints, CapacityManager, Priority, RequestQueue, SchedulerMetricsCollector,
+                                                     SlidingWindowCounter)
+    q = RequestQueue(max_size=3)
+    lo, hi, mid = Request([1], priority=Priority.LOW), Request([2], priority=Priority.HIGH), Request([3], priority=Priority.NORMAL)
+    for r in (lo, hi, mid):
+        q.enqueue(r)
+    with pytest.raises(OverflowError):
+        q.enqueue(Request([4]))
+    mid.cancelled = True
+    assert q.dequeue() is hi and q.dequeue() is lo and q.dequeue() is None       # the cancelled one is skipped and resolved
+    assert mid.future.result(0).reason == CompletionReason.CANCELLED
+    cap = CapacityManager(CapacityConstraints(max_batch_size=2, max_memory_bytes=1000, buffer_ratio=0.1, max_concurrent_requests=8), bytes_per_token=10)
+    a, b, c = Request([0] * 10, max_tokens=20), Request([0] * 30, max_tokens=20), Request([0] * 5, max_tokens=5)
+    assert cap.usable_memory == 900 and cap.estimate_required_memory(a) == 300
+    assert cap.can_fit_batch([a, b]) and not cap.can_fit_batch([a, b, c])          # three requests: over the slot limit
+    assert cap.try_allocate(a) and cap.active_slots == 1 and cap.utilization == pytest.approx(300 / 900)
+    assert not cap.can_fit_batch([b, c]) and cap.can_fit_batch([b])
+    assert cap.try_allocate(b) and not cap.try_allocate(c)                          # slots exhausted
+    cap.release(a.id)
+    assert cap.try_allocate(c) and cap.active_slots == 2
+    big = Request([0] * 100, max_tokens=100)
+    cap.release(c.id)
+    assert not cap.try_allocate(big)                                                # 2000 bytes never fit 900
+    assert CapacityManager().estimate_required_memory(Request([0] * 4, max_tokens=4)) == 8 * 1024
+    now = [0.0]
+    w = SlidingWindowCounter(10.0, clock=lambda: now[0])
+    w.add(5)
+    now[0] = 4.0
+    w.add(3)
+    assert w.total() == 8 and w.rate() == 0.8
+    now[0] = 12.0
+    assert w.total() == 3
+    m = SchedulerMetricsCollector(capacity=4)
+    for i in range(6):
+        m.record_iteration(2.0 + i, 4, 4)
+        m.record_batch_utilization(4, 8)
+    m.record_batch_utilization(8, 8)
+    m.record_error("oom")
+    m.record_error("oom")
+    snap = m.snapshot()
+    assert snap["iterations"] == 4 and snap["mean_batch"] == 4 and snap["errors"] == {"oom": 2} and snap["total_tokens"] == 24
+    assert snap["mean_batch_utilization"] == pytest.approx((0.5 * 3 + 1.0) / 4)     # the buffer keeps the last four
+    ex = MockExecutor(eos_after=3)
+    s = ContinuousBatchScheduler(ex, None, SchedulerConfiguration(max_batch_size=2))
+    client = ContinuousBatchSchedulerClient(s, Tok())
+    assert client.estimate_wait_time_s() == 0.0 and client.status()["queued"] == 0
+    s.start()
+    try:
+        res = client.generate_batch(["ab", "cde", "f"], max_tokens=8, timeout_s=10)
+        assert [r.tokens for r in res] == [[100, 101, 2]] * 3
+        assert client.statistics()["completed"] == 3 and 0 < client.statistics()["mean_batch_utilization"] <= 1.0
+    finally:
+        s.stop()
+    ph = PrefillHandler(PrefillConfiguration(chunk_size=4, prompt_cache_entries=2, prompt_cache_ttl_s=5.0), clock=lambda: now[0])
+    assert ph.estimate_prefill_memory(Request(list(range(10))), 16) == 160
+    ph.cache_store([1], "x")
+    now[0] += 6.0
+    assert ph.cache_lookup([1]) is None                                             # expired
+
+
+def test_block_table_beam_and_speculative_helpers():
+    from ml_framework_b200.serving.kv_cache import BeamSearchBlockSharing, BlockTable, SpeculativeDecodingSharing
+    m = KVCacheBlockManager(32, 4, allocate_cache=False)
+    bt = BlockTable(m)
+    first = bt.allocate_and_append_block(1)
+    assert bt.get_sequence_blocks(1) == [first] and bt.get_sequence_length(1) == 0
+    m.append_tokens(1, 6)
+    assert bt.get_sequence_length(1) == 6 and len(bt.get_sequence_blocks(1)) == 2 and bt.get_block(1, 5) == bt.get_sequence_blocks(1)[1]
+    beams = BeamSearchBlockSharing(m)
+    beams.initialize_beams(1, [10, 11, 12])
+    shared = m.get_sequence_blocks(1)
+    assert all(m.get_sequence_blocks(b) == shared for b in (10, 11, 12)) and m.reference_count(shared[0]) == 4
+    slots, cow = beams.on_beam_divergence(10)
+    assert cow is not None and cow[0] == shared[1] and m.get_sequence_blocks(10)[0] == shared[0]     # the half-full block is copied
+    beams.replace_beam(11, 10)                                                      # beam 11 died: continue from beam 10
+    assert m.get_sequence_blocks(11) == m.get_sequence_blocks(10) and m.get_sequence_length(11) == 7
+    beams.cleanup_beams(1)
+    assert m.reference_count(shared[0]) == 1 and beams.beams == {}
+    spec = SpeculativeDecodingSharing(m)
+    free0 = m.free_blocks
+    slots, _ = spec.allocate_speculative_blocks(1, 7)                               # 6 + 7 = 13 tokens: two more blocks
+    assert len(slots) == 7 and m.free_blocks == free0 - 2
+    assert spec.verify_speculation(1, 3) >= 1 and m.get_sequence_length(1) == 9
+    spec.allocate_speculative_blocks(1, 4)
+    spec.reject_all_speculation(1)
+    assert m.get_sequence_length(1) == 9 and m.free_blocks == free0 - 1
+    assert bt.remove_sequence(1) == 3 and m.free_blocks == 32
+    full = KVCacheBlockManager(1, 4, allocate_cache=False)
+    BlockTable(full).allocate_and_append_block(5)
+    with pytest.raises(MemoryError):
+        BlockTable(full).allocate_and_append_block(6)
+
+
+def test_memory_aware_queue_accessors():
+    from ml_framework_b200.serving.iteration import MemoryAwareScheduler, PendingRequest
+    m = KVCacheBlockManager(10, 16, allocate_cache=False)
+    q = MemoryAwareScheduler(PagedAttentionScheduler(m), max_queue_size=2)
+    assert q.enqueue_request(PendingRequest(1, 64, 32)) and q.enqueue_request(PendingRequest(2, 32, 16))
+    assert not q.enqueue_request(PendingRequest(3, 32, 16)) and q.queue_size() == 2
+    assert [p.request_id for p in q.queued_requests()] == [1, 2] and not q.should_apply_backpressure()
+    m.allocate_blocks(9, 9)
+    assert q.should_apply_backpressure() and q.try_admit_next_request() is None      # the head does not fit: nothing is admitted
+    q.clear_queue()
+    assert q.queue_size() == 0 and q.try_admit_next_request() is None
