@@ -138,3 +138,93 @@ def test_pipeline_times_tensor_parallel_composition_gloo():
     rec = json.loads(line)
     assert rec["config"]["parallelism"] == "pp2 x tp2" and rec["n_gpus"] == 4
     assert 0 < rec["final_loss"] < 7.2          # ln(1024) = 6.93 at initialisation, falling
+
+
+def test_async_executor_two_stages_matches_single_device_gradients():
+    """Two stages on two threads through the stream-aware executor (on CPU every stream is the host): forward
+    activations and backward gradients cross the in-process communicator; parameter gradients equal the unsplit model's."""
+    import threading
+    from ml_framework_b200.parallel.pipeline import AsyncPipelineExecutor, LocalPipelineCommunicator, PipelineStage, StreamManager
+    torch.manual_seed(0)
+    l0, l1 = nn.Sequential(nn.Linear(6, 8), nn.Tanh()), nn.Linear(8, 3)
+    ref0, ref1 = copy.deepcopy(l0), copy.deepcopy(l1)
+    xs = [torch.randn(4, 6) for _ in range(3)]
+    for x in xs:
+        ref1(ref0(x)).pow(2).sum().backward()
+    comm = LocalPipelineCommunicator(2, timeout_s=20.0)
+    errs = []
+
+    def stage0():
+        try:
+            ex = AsyncPipelineExecutor(PipelineStage(l0, 0, 2), comm.view(0), StreamManager("cpu"))
+            for i, x in enumerate(xs):
+                y = ex.forward_async(x, i)
+                ex.send_async(y.detach(), i, "forward")
+            for i in range(len(xs)):
+                g = ex.receive_async(torch.empty(4, 8), i, "backward")
+                assert ex.backward_async(g, i) is None               # the first stage's input needs no gradient
+            ex.sync_compute()
+            ex.sync_comm()
+        except Exception as e:  # noqa: BLE001
+            errs.append(repr(e))
+
+    def stage1():
+        try:
+            ex = AsyncPipelineExecutor(PipelineStage(l1, 1, 2), comm.view(1), StreamManager("cpu"))
+            for i in range(len(xs)):
+                h = ex.receive_async(torch.empty(4, 8), i, "forward").requires_grad_(True)
+                y = ex.forward_async(h, i)
+                gx = ex.backward_async(2 * y.detach(), i)              # d/dy of sum(y^2)
+                ex.send_async(gx, i, "backward")
+            ex.streams.synchronize()
+        except Exception as e:  # noqa: BLE001
+            errs.append(repr(e))
+    ths = [threading.Thread(target=f) for f in (stage0, stage1)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join(60)
+    assert not errs, errs
+    for a, b in zip(list(l0.parameters()) + list(l1.parameters()), list(ref0.parameters()) + list(ref1.parameters())):
+        assert torch.allclose(a.grad, b.grad, atol=1e-5)
+
+
+def test_pipeline_optimizer_ties_validator_and_activation_budget():
+    from ml_framework_b200.dist.process_group import run_fake_world
+    from ml_framework_b200.parallel.pipeline import (ActivationCheckpointManager, CheckpointStrategy, GradientSyncMode, PipelineConfig,
+                                                     PipelineOptimizer, PipelineOptimizerConfig, PipelineValidator)
+
+    def run(pg):
+        torch.manual_seed(0)
+        tied = nn.Parameter(torch.ones(3) * (pg.rank + 1))              # the stages hold different copies at first
+        own = nn.Parameter(torch.zeros(2))
+        opt = torch.optim.SGD([tied, own], lr=0.5)
+        po = PipelineOptimizer(opt, [tied], pg, PipelineOptimizerConfig(GradientSyncMode.SUM), dp_group=pg)
+        po.broadcast_parameters(src=0)
+        start = tied.detach().clone()
+        tied.grad = torch.full((3,), float(pg.rank + 1))
+        own.grad = torch.full((2,), 1.0)
+        po.step([own])
+        return start, tied.detach().clone(), own.detach().clone()
+    out = run_fake_world(2, run)
+    for start, tied, own in out:
+        assert torch.equal(start, torch.ones(3))                         # broadcast from stage 0
+        assert torch.equal(tied, torch.ones(3) - 0.5 * 3.0)              # gradients 1 + 2 summed over the tie group
+        assert torch.equal(own, torch.zeros(2) - 0.5 * 2.0)              # data-parallel SUM over the two ranks
+    none = PipelineOptimizer(torch.optim.SGD([nn.Parameter(torch.ones(1))], lr=1.0))
+    none.synchronize_gradients()
+    none.broadcast_parameters()
+    errs = PipelineValidator.validate_configuration(PipelineConfig(num_stages=4, micro_batches=8), num_layers=2, batch=4)
+    assert "more stages than layers" in errs and "batch smaller than the number of micro-batches" in errs
+    assert PipelineValidator.validate_configuration(PipelineConfig(num_stages=2, micro_batches=2), 4, 8) == []
+    assert PipelineValidator.validate_numerical_stability([torch.ones(2), None]) and not PipelineValidator.validate_numerical_stability([torch.tensor([float("nan")])])
+    assert PipelineValidator.validate_gradients([torch.ones(2)], [torch.ones(2) + 1e-7]) and not PipelineValidator.validate_gradients([torch.ones(2)], [])
+    mem = ActivationCheckpointManager(CheckpointStrategy.MEMORY_BASED, memory_budget_bytes=100)
+    assert [mem.should_checkpoint(i, 40) for i in range(4)] == [False, False, True, True] and mem.stored_bytes == 80
+    mem.release(40)
+    assert not mem.should_checkpoint(4, 40) and mem.stored_bytes == 80
+    mem.release(1000)
+    assert mem.stored_bytes == 0
+    sel = ActivationCheckpointManager(CheckpointStrategy.SELECTIVE, interval=3)
+    assert [sel.should_checkpoint(i) for i in range(4)] == [False, True, True, False]
+    assert not ActivationCheckpointManager(CheckpointStrategy.MEMORY_BASED).should_checkpoint(0, 1 << 40)    # no budget: keep everything
