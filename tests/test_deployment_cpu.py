@@ -1,0 +1,132 @@
+"""Model deployment on CPU: semantic versions, metadata, registry, checksum-verified loading, hot swap with draining
+and concurrent requests, automatic rollback on error rate, header / version routing, traffic splitting, experiments."""
+import threading
+import time
+
+import pytest
+
+from ml_framework_b200.serving import deployment as D
+
+
+def test_semantic_versions_metadata_and_registry():
+    V = D.SemanticVersion.parse
+    assert V("1.2.3") == V("1.2.3+build.7") and hash(V("1.2.3")) == hash(V("1.2.3+x")) and V("1.2.3") != V("1.2.4")
+    assert V("1.0.0-alpha") < V("1.0.0-alpha.1") < V("1.0.0-beta") < V("1.0.0-rc.1") < V("1.0.0") < V("1.0.1")
+    assert V("1.0.0-rc.2") < V("1.0.0-rc.10")                                   # numeric identifiers compare as numbers
+    assert V("1.4.0").compatible_with(V("1.2.0")) and not V("2.0.0").compatible_with(V("1.2.0")) and not V("1.1.0").compatible_with(V("1.2.0"))
+    assert str(V(" 3.1.4-rc.1+sha ")) == "3.1.4-rc.1+sha" and len({V("1.0.0"), V("1.0.0+a"), V("1.0.1")}) == 2
+    assert str(V("v1.2.3")) == "1.2.3"                                            # a leading v is accepted
+    for bad in ("1.2", "1.2.x", "1.2.3.4", ""):
+        with pytest.raises(ValueError):
+            V(bad)
+    meta = D.ModelMetadata("llm", "1.0.0", tags={"team": "a"})
+    back = D.ModelMetadata.from_json(meta.to_json())
+    assert back == meta
+    reg = D.ModelRegistry()
+    for v in ("1.10.0", "1.2.0", "1.9.1"):
+        reg.register(f"model-{v}", D.ModelMetadata("llm", v))
+    assert reg.versions("llm") == ["1.2.0", "1.9.1", "1.10.0"] and reg.latest("llm") == "1.10.0" and reg.get("llm", "1.9.1") == "model-1.9.1"
+    with pytest.raises(ValueError):
+        reg.register("dup", D.ModelMetadata("llm", "1.2.0"))
+    reg.unregister("llm", "1.10.0")
+    reg.unregister("llm", "1.10.0")
+    assert reg.latest("llm") == "1.9.1"
+    with pytest.raises(KeyError):
+        reg.get("llm", "1.10.0")
+    with pytest.raises(KeyError):
+        reg.latest("nothing")
+
+
+def test_loader_verifies_the_recorded_checksum(tmp_path):
+    p = tmp_path / "w.bin"
+    p.write_bytes(b"weights-v1")
+    loader = D.ModelLoader(lambda path: open(path, "rb").read())
+    sha = D.ModelLoader.checksum(str(p))
+    assert len(sha) == 64 and loader.load(str(p), D.ModelMetadata("m", "1.0.0", checksum=sha)) == b"weights-v1"
+    assert loader.load(str(p)) == b"weights-v1"                                 # no metadata: nothing to verify
+    p.write_bytes(b"weights-v2")
+    with pytest.raises(IOError):
+        loader.load(str(p), D.ModelMetadata("m", "1.0.0", checksum=sha))
+
+
+def test_hot_swap_drains_in_flight_requests_and_rollback_restores_the_previous_version():
+    reg = D.ModelRegistry()
+    reg.register(lambda x: ("v1", x), D.ModelMetadata("llm", "1.0.0"))
+    reg.register(lambda x: ("v2", x), D.ModelMetadata("llm", "2.0.0"))
+    sw = D.ModelHotSwapper(reg)
+    sw.activate("llm", "1.0.0")
+    with pytest.raises(KeyError):
+        sw.activate("llm", "9.9.9")
+    started, release, results = threading.Event(), threading.Event(), []
+
+    def slow_request():
+        def call(m):
+            started.set()
+            release.wait(5)
+            return m(1)
+        results.append(sw.serve("llm", call))
+    t = threading.Thread(target=slow_request)
+    t.start()
+    started.wait(5)
+    assert not sw.swap("llm", "2.0.0", drain_timeout=0.05)                      # the old version still has a request in flight
+    assert sw.serve("llm", lambda m: m(2)) == ("v2", 2)                         # new requests already see the new version
+    release.set()
+    t.join(5)
+    assert results == [("v1", 1)]                                               # the in-flight request finished on the old one
+    assert sw.swap("llm", "1.0.0", drain_timeout=1.0) and sw.swap("llm", "1.0.0")
+    assert sw.swap("llm", "2.0.0", drain_timeout=1.0, unload_old=True)
+    with pytest.raises(KeyError):
+        reg.get("llm", "1.0.0")                                                 # drained and unloaded
+    assert sw.serve("llm", lambda m: m(3), version="2.0.0") == ("v2", 3)
+    reg.register(lambda x: ("v3", x), D.ModelMetadata("llm", "3.0.0"))
+    sw.swap("llm", "3.0.0")
+    rb = D.RollbackManager(sw, error_threshold=0.3, window=10, min_samples=5)
+    outcomes = [rb.record("llm", ok) for ok in (True, True, False, False)]
+    assert outcomes == [False] * 4 and rb.error_rate("llm") == 0.5              # not enough samples yet
+    assert rb.record("llm", False) and sw.active["llm"] == "2.0.0" and rb.rollbacks == [("llm", "3.0.0", "2.0.0")]
+    assert rb.error_rate("llm") == 0.0                                          # the window restarts after a rollback
+    fresh = D.ModelHotSwapper(reg)
+    fresh.activate("llm", "2.0.0")
+    assert not D.RollbackManager(fresh).rollback("llm")                         # nothing to go back to
+
+
+def test_header_and_version_routing_traffic_split_and_experiments():
+    hr = D.HeaderRouter([D.RoutingRule("x-tier", "gold*", "2.0.0", priority=1)], default="1.0.0")
+    hr.add(D.RoutingRule("X-Tier", "gold-beta", "3.0.0-rc.1", priority=5))
+    assert hr.route({"X-TIER": "gold-beta"}) == "3.0.0-rc.1" and hr.route({"x-tier": "gold-7"}) == "2.0.0"
+    assert hr.route({"x-tier": "silver"}) == "1.0.0" and hr.route({}) == "1.0.0" and D.HeaderRouter().route({"a": "b"}) is None
+    reg = D.ModelRegistry()
+    for v in ("1.0.0", "1.3.0", "2.1.0"):
+        reg.register(v, D.ModelMetadata("m", v))
+    vr = D.VersionRouter(reg)
+    assert vr.resolve("m") == "2.1.0" and vr.resolve("m", "^1.0.0") == "1.3.0" and vr.resolve("m", "1.0.0") == "1.0.0"
+    for bad in ("^3.0.0", "1.1.0"):
+        with pytest.raises(KeyError):
+            vr.resolve("m", bad)
+    with pytest.raises(KeyError):
+        vr.resolve("other")
+    ts = D.TrafficSplitter({"a": 3, "b": 1}, seed=1)
+    picks = [ts.choose() for _ in range(4000)]
+    assert 0.70 < picks.count("a") / 4000 < 0.80 and ts.counts["a"] + ts.counts["b"] == 4000
+    assert len({ts.choose("user-42") for _ in range(20)}) == 1                  # sticky
+    ts.set_weights({"a": 0, "b": 1})
+    assert {ts.choose() for _ in range(50)} == {"b"}
+    for bad in ({"a": 0, "b": 0}, {"a": -1, "b": 2}):
+        with pytest.raises(ValueError):
+            D.TrafficSplitter(bad)
+    ex = D.ExperimentTracker()
+    for i in range(50):
+        ex.record("control", "latency", 10.0 + (i % 5) * 0.1)
+        ex.record("treatment", "latency", 9.0 + (i % 5) * 0.1)
+    s = ex.summary("control", "latency")
+    assert s["n"] == 50 and s["mean"] == pytest.approx(10.2) and s["var"] > 0
+    cmp_ = ex.compare("control", "treatment", "latency")
+    assert cmp_["diff"] == pytest.approx(-1.0) and cmp_["t"] < -20 and cmp_["n_a"] == cmp_["n_b"] == 50
+    assert ex.summary("nobody", "latency") == {"n": 0, "mean": 0.0, "var": 0.0} and ex.compare("nobody", "nothing", "x")["t"] == 0.0
+    it = D.InferenceTracker()
+    with it.track("ok"):
+        time.sleep(0.002)
+    with pytest.raises(RuntimeError):
+        with it.track("bad"):
+            raise RuntimeError("boom")
+    assert it.errors["bad"] == 1 and it.errors["ok"] == 0 and it.p("ok", 50) >= 0.002 and it.p("none", 99) == 0.0
