@@ -18,7 +18,7 @@
 from __future__ import annotations
 
 import enum
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, Iterable, List, Optional, Sequence
 
 import torch
 import torch.func as tf

@@ -12,7 +12,7 @@ memory saved (MemoryTracking.cs).
 from __future__ import annotations
 
 import enum
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch

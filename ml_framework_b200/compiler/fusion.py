@@ -17,7 +17,7 @@ which the graph executor runs as ONE kernel generated, compiled with ``nvcc`` an
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -7,7 +7,7 @@ src/RitterFramework.Core/Diagnostics/* and Exceptions/ShapeMismatchException.cs.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 
 

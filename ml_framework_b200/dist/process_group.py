@@ -18,7 +18,6 @@ from __future__ import annotations
 import enum
 import os
 import threading
-from dataclasses import dataclass
 from datetime import timedelta
 from typing import Callable, Dict, List, Optional, Sequence
 

@@ -15,7 +15,6 @@ overflow flag and the skip decision all kept on the device.
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass, field
 from typing import Optional
 

@@ -14,7 +14,7 @@ pool; ``replay`` copies new inputs in, launches and returns the static outputs.
 from __future__ import annotations
 
 import enum
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -15,7 +15,7 @@ import hashlib
 import json
 import struct
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional
 
 import numpy as np
 import torch

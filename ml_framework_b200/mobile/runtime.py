@@ -11,8 +11,7 @@ from __future__ import annotations
 
 import ctypes as C
 import time
-from dataclasses import dataclass
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence
 
 import torch
 import torch.nn as nn

@@ -15,8 +15,7 @@ import torch.nn as nn
 
 from ..nn.layers import RMSNorm
 from ..ops import functional as Fm
-from ..parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear, TPContext, VocabParallelEmbedding,
-                                        gather_tokens, scatter_tokens, vocab_parallel_lm_loss)
+from ..parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear, TPContext, VocabParallelEmbedding, gather_tokens, vocab_parallel_lm_loss)
 from .llama import LlamaConfig
 
 

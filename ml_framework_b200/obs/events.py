@@ -12,12 +12,11 @@ from __future__ import annotations
 import enum
 import json
 import os
-import queue
 import threading
 import time
 from collections import defaultdict, deque
 from dataclasses import asdict, dataclass, field
-from typing import Any, Callable, Deque, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Deque, Dict, List, Optional, Sequence, Tuple
 
 
 class EventType(enum.Enum):

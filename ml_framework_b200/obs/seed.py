@@ -9,7 +9,7 @@ import hashlib
 import os
 import random
 from dataclasses import dataclass
-from typing import Dict, List, Optional
+from typing import List, Optional
 
 import numpy as np
 import torch

@@ -6,13 +6,12 @@ from __future__ import annotations
 import json
 import math
 import os
-from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence
+from dataclasses import dataclass
+from typing import Any, Dict, Optional
 
 import torch
 
-from .events import (AsyncEventCollector, Event, EventCollector, EventCollectorConfig, EventFactory, EventSystem, EventType,
-                     FileStorageBackend, MemoryStorageBackend, ScalarLogger, StorageBackend)
+from .events import (AsyncEventCollector, Event, EventCollector, EventCollectorConfig, EventSystem, EventType, FileStorageBackend, MemoryStorageBackend, ScalarLogger, StorageBackend)
 from .profiler import Profiler
 
 

@@ -7,7 +7,6 @@ compare the CUDA kernels against, and executable documentation of the math.
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 import torch.nn.functional as F

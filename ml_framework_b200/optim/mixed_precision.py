@@ -17,7 +17,7 @@ import fnmatch
 import math
 import time
 from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, List, Optional
 
 import torch
 import torch.nn as nn

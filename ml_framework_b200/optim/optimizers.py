@@ -9,7 +9,7 @@ On CUDA one fused kernel updates each flat buffer; on CPU the same math runs in 
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional, Sequence, Union
+from typing import Dict, Iterable, List, Optional, Union
 
 import torch
 import torch.nn as nn

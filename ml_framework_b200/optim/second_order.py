@@ -7,7 +7,7 @@ double backward (Hessian-vector product) without forming the Hessian.
 from __future__ import annotations
 
 from collections import deque
-from typing import Callable, Deque, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Deque, Iterable, List, Sequence, Tuple
 
 import torch
 

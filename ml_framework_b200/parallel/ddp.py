@@ -26,7 +26,7 @@ from typing import Dict, Iterable, List, Optional
 import torch
 import torch.nn as nn
 
-from ..dist.process_group import ProcessGroup, ReduceOp, default_group
+from ..dist.process_group import ReduceOp, default_group
 
 DEFAULT_BUCKET_MB = 25
 

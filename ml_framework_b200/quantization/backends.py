@@ -18,7 +18,7 @@ from __future__ import annotations
 import enum
 import os
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional
 
 import torch
 import torch.nn.functional as F

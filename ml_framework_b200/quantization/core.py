@@ -12,8 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 import enum
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch

@@ -15,9 +15,7 @@ from __future__ import annotations
 import argparse
 import json
 import random
-import threading
 import time
-from typing import Dict, List
 
 import torch
 

@@ -27,7 +27,7 @@ from ..ops import native, reference
 from ..ops.gemm import gemm
 from .. import _lib
 from .kv_cache import KVCacheBlockManager
-from .scheduler import Batch, BatchOutput, Request, RequestState
+from .scheduler import Batch, BatchOutput, Request
 
 
 @dataclass

@@ -20,7 +20,7 @@ import threading
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, List, Optional, Sequence
+from typing import Callable, Deque, Dict, List, Optional
 
 from .kv_cache import KVCacheBlockManager
 from .scheduler import KVCacheConfiguration, PagedAttentionScheduler

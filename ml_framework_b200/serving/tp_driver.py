@@ -10,7 +10,7 @@ sums inside ``PagedLlamaExecutor._reduce`` (one-shot peer-memory kernel or a pro
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict
 
 from .executor import PagedLlamaExecutor
 from .scheduler import Batch, BatchOutput, Request
