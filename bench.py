@@ -129,11 +129,17 @@ def main():
             torch.distributed.barrier(device_ids=[local])
         torch.cuda.synchronize()
 
-    def run_arm(step_fn, launches_fn):
+    def run_arm(step_fn, launches_fn, status_fn=None):
         """Warm-up, the device-timed region, then the end-to-end region; returns per-step times (max over ranks)."""
         for i in range(args.warmup):
             loss = step_fn(dev_ids[i % n_batches], dev_tgt[i % n_batches])
         barrier()
+        if status_fn is not None:
+            # a bounded device-side wait that ran out during warm-up (a peer that never arrived) would make every later
+            # collective wait out its budget too: stop here with the code instead of timing a broken run
+            code = status_fn()
+            if code:
+                raise RuntimeError(f"rank {rank}: kernel status {code} after warm-up (a device-side wait ran out of its budget)")
         # ---- device-timed region (inputs resident; 2.6 GB of weights + 30 GB of activations per step
         # stream through a 126 MB L2, so every step starts cold)
         stop, samples = threading.Event(), []
@@ -195,7 +201,7 @@ def main():
         lib = _lib.get()
         import ctypes
         lib.mlf_launch_count.restype = ctypes.c_longlong
-        res = run_arm(eng.step, lambda: int(lib.mlf_launch_count()))
+        res = run_arm(eng.step, lambda: int(lib.mlf_launch_count()), lambda: _lib.read_status(False))
         status = _lib.read_status(True)
         if not args.no_baseline:
             # The comparison arm on the same box, in the same process: the plain torch.distributed (NCCL) +
