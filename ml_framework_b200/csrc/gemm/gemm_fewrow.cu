@@ -69,7 +69,8 @@ gemm_fewrow_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_al + (bar_base - smem_base) + 8 * (2 * kStages + 4));
+  const uint32_t epi_bar = bar_base + 8u * (2 * kStages + 4);            // meeting point of the four epilogue warps
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_al + (bar_base - smem_base) + 8 * (2 * kStages + 5));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -84,6 +85,7 @@ gemm_fewrow_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 4);
     }
+    mbar_init(epi_bar, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -176,7 +178,16 @@ gemm_fewrow_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int col = n_loc & 63;
     const bool elected = warp == 2 && lane == 0;
     int it = 0;
+    uint32_t meets = 0;                             // uses of the meeting point (its phase parity)
     bool ok = true;
+    // The four warps meet on an mbarrier with a bounded wait, not on a hardware barrier: should one warp give up
+    // (a wait elsewhere in the CTA ran out), the others time out here too and unwind instead of waiting for ever.
+    auto meet = [&]() -> bool {
+      mbar_arrive(epi_bar);
+      const bool good = mbar_wait_warp(epi_bar, meets & 1u, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      ++meets;
+      return good;
+    };
     for (long long u = u_begin; u < u_end && ok; ++it) {
       const int tile = (int)(u / p.num_kb);
       const long long seg_end = min(u_end, (long long)(tile + 1) * p.num_kb);
@@ -186,7 +197,7 @@ gemm_fewrow_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       tc_fence_after_sync();
       // the staging tiles are free once the previous run's reduction stores have read them
       if (elected) tma_store_wait_read<0>();
-      named_barrier_sync(1, 128);
+      if (!meet()) break;
       const uint32_t box = stg_base + half * Cfg::kStgBox;
       const uint32_t cb = (uint32_t)(col >> 3), ce = (uint32_t)(col & 7) * 2u;
 #pragma unroll 1
@@ -207,7 +218,7 @@ gemm_fewrow_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       fence_proxy_async_smem();
-      named_barrier_sync(1, 128);
+      if (!meet()) break;
       if (elected) {
         fr_reduce_add_2d(&tmOut, stg_base, tile * FR_WT, 0);
         if (tile * FR_WT + 64 < p.N) fr_reduce_add_2d(&tmOut, stg_base + Cfg::kStgBox, tile * FR_WT + 64, 0);
