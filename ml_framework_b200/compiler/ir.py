@@ -49,12 +49,13 @@ class HLGraph:
         self.ops: List[Op] = []
         self.inputs: List[str] = []
         self.outputs: List[str] = []
-        self._ids = itertools.count()
+        self._next_id = 0
         self._shape = ShapeInferenceEngine()
 
     # ---- builder
     def _fresh(self, hint: str) -> str:
-        return f"%{hint}{next(self._ids)}"
+        self._next_id += 1
+        return f"%{hint}{self._next_id - 1}"
 
     def input(self, name: str, shape: Sequence[int], dtype=torch.float32) -> str:
         self.values[name] = Value(name, tuple(shape), dtype)
@@ -133,17 +134,35 @@ def _execute(o: Op, x: List[torch.Tensor]) -> torch.Tensor:
     if k == "neg": return -x[0]
     if k == "cast": return x[0].to(a["dtype"])
     if k == "softmax": return torch.softmax(x[0], a.get("dim", -1))
-    if k == "matmul":
-        if x[0].is_cuda and x[0].dtype == torch.bfloat16 and x[0].dim() == 2 and x[1].dim() == 2:
-            from ..ops.gemm import gemm
-            return gemm(x[0], x[1], b_mn=True)
-        return x[0] @ x[1]
-    if k == "linear":
-        if x[0].is_cuda and x[0].dtype == torch.bfloat16:
+    if k in ("matmul", "linear"):
+        # ``epilogue`` (set by the fusion rewrite): "gelu", or "residual" with the residual as the LAST input
+        epi = a.get("epilogue")
+        res = x[-1] if epi == "residual" else None
+        if res is not None:
+            x = x[:-1]
+        bias = x[2] if k == "linear" and len(x) > 2 else None
+        if epi is None and k == "linear" and x[0].is_cuda and x[0].dtype == torch.bfloat16:
             from ..ops import functional as Fn
-            return Fn.linear(x[0], x[1], x[2] if len(x) > 2 else None)
-        return F.linear(x[0], x[1], x[2] if len(x) > 2 else None)
-    if k == "conv2d": return F.conv2d(x[0], x[1], x[2] if len(x) > 2 else None, a.get("stride", 1), a.get("padding", 0), a.get("dilation", 1), a.get("groups", 1))
+            return Fn.linear(x[0], x[1], bias)
+        if x[0].is_cuda and x[0].dtype == torch.bfloat16 and x[1].dim() == 2 and (k == "linear" or x[0].dim() == 2):
+            # one tensor-core GEMM whose epilogue applies bias / GELU / residual
+            from ..ops.gemm import EPI_BIAS, EPI_GELU, EPI_RESIDUAL, gemm
+            x2 = x[0].reshape(-1, x[0].shape[-1])
+            flags = (EPI_BIAS if bias is not None else 0) | (EPI_GELU if epi == "gelu" else 0) | (EPI_RESIDUAL if res is not None else 0)
+            n_out = x[1].shape[0] if k == "linear" else x[1].shape[1]
+            y = gemm(x2, x[1], b_mn=(k == "matmul"), bias=bias, flags=flags,
+                     aux_in=res.reshape(-1, n_out).contiguous() if res is not None else None)
+            return y.reshape(*x[0].shape[:-1], n_out)
+        y = F.linear(x[0], x[1], bias) if k == "linear" else x[0] @ x[1]
+        if epi == "gelu":
+            y = F.gelu(y, approximate="tanh")
+        return y + res if res is not None else y
+    if k == "conv2d":
+        y = F.conv2d(x[0], x[1], x[2] if len(x) > 2 else None, a.get("stride", 1), a.get("padding", 0), a.get("dilation", 1), a.get("groups", 1))
+        act = a.get("activation")
+        return _execute(Op(act, [], ""), [y]) if act else y
+    if k == "batchnorm":      # inputs: x, gamma, beta, running mean, running variance (inference form)
+        return F.batch_norm(x[0], x[3], x[4], x[1], x[2], False, 0.0, a.get("eps", 1e-5))
     if k == "maxpool2d": return F.max_pool2d(x[0], a.get("kernel", 2), a.get("stride", a.get("kernel", 2)), a.get("padding", 0))
     if k == "avgpool2d": return F.avg_pool2d(x[0], a.get("kernel", 2), a.get("stride", a.get("kernel", 2)), a.get("padding", 0))
     if k == "reshape": return x[0].reshape(a["shape"])

@@ -145,7 +145,7 @@ class ShapeInferenceEngine:
         self.rules: Dict[str, Callable[[Sequence[SymbolicShape], dict], SymbolicShape]] = {}
         for n in ("add", "sub", "mul", "div", "maximum", "minimum"):
             self.rules[n] = lambda s, a: broadcast_shapes(s[0], s[1])
-        for n in ("relu", "gelu", "sigmoid", "tanh", "exp", "log", "sqrt", "neg", "cast", "softmax", "layer_norm", "rms_norm", "dropout"):
+        for n in ("relu", "gelu", "sigmoid", "tanh", "exp", "log", "sqrt", "neg", "cast", "softmax", "layer_norm", "rms_norm", "dropout", "batchnorm"):
             self.rules[n] = lambda s, a: s[0]
         self.rules["matmul"] = self._matmul
         self.rules["linear"] = self._linear
