@@ -78,6 +78,33 @@ class HLGraph:
     def output(self, *names: str):
         self.outputs.extend(names)
 
+    # ---- structured control flow (the reference's high-level If / Loop ops, IR/HLIR/ControlFlow/*.cs)
+    def cond(self, pred: str, then_graph: "HLGraph", else_graph: "HLGraph", *args: str) -> str:
+        """``then_graph(*args)`` where the scalar ``pred`` is non-zero, else ``else_graph(*args)``. Both branches take
+        ``args`` as their inputs (in order) and return one value of the same shape and dtype."""
+        for b in (then_graph, else_graph):
+            if len(b.inputs) != len(args) or len(b.outputs) != 1:
+                raise ValueError("a branch takes the op's arguments and returns one value")
+        t, e = then_graph.values[then_graph.outputs[0]], else_graph.values[else_graph.outputs[0]]
+        if t.shape != e.shape or t.dtype != e.dtype:
+            raise ValueError(f"branches disagree: {t.shape} {t.dtype} vs {e.shape} {e.dtype}")
+        out = self._fresh("if")
+        self.values[out] = Value(out, t.shape, t.dtype)
+        self.ops.append(Op("if", [pred, *args], out, {"then": then_graph, "else": else_graph}))
+        return out
+
+    def loop(self, count: int, body: "HLGraph", init: str, *invariants: str) -> str:
+        """``carry = body(carry, *invariants)`` repeated ``count`` times, starting from ``init``."""
+        if len(body.inputs) != 1 + len(invariants) or len(body.outputs) != 1:
+            raise ValueError("a loop body takes (carry, *invariants) and returns the next carry")
+        c0, c1 = self.values[init], body.values[body.outputs[0]]
+        if c0.shape != c1.shape or c0.dtype != c1.dtype:
+            raise ValueError(f"the body changes the carried value: {c0.shape} {c0.dtype} -> {c1.shape} {c1.dtype}")
+        out = self._fresh("loop")
+        self.values[out] = Value(out, c0.shape, c0.dtype)
+        self.ops.append(Op("loop", [init, *invariants], out, {"count": int(count), "body": body}))
+        return out
+
     # ---- analysis
     def users(self) -> Dict[str, List[int]]:
         u: Dict[str, List[int]] = {}
@@ -118,6 +145,17 @@ class HLGraph:
 def _execute(o: Op, x: List[torch.Tensor]) -> torch.Tensor:
     import torch.nn.functional as F
     k, a = o.kind, o.attrs
+    if k == "if":
+        br = a["then"] if bool(x[0].reshape(-1)[0] != 0) else a["else"]
+        return br.run(dict(zip(br.inputs, x[1:])))[0]
+    if k == "loop":
+        body, carry = a["body"], x[0]
+        for _ in range(a["count"]):
+            carry = body.run(dict(zip(body.inputs, [carry, *x[1:]])))[0]
+        return carry
+    if k.endswith("_scalar"):     # a binary op whose constant scalar operand was inlined into the attributes
+        c = torch.tensor(a["scalar"], dtype=x[0].dtype, device=x[0].device)
+        return _execute(Op(k[:-7], [], ""), [c, x[0]] if a.get("scalar_side") == "lhs" else [x[0], c])
     if k == "add": return x[0] + x[1]
     if k == "sub": return x[0] - x[1]
     if k == "mul": return x[0] * x[1]
