@@ -81,7 +81,61 @@ class SyntheticTokenDataset(Dataset):
         return t[:-1], t[1:]
 
 
+class ArrayDataset(Dataset):
+    """Row ``i`` of one or several NumPy arrays (shared first dimension), as tensors that alias the arrays."""
+
+    def __init__(self, *arrays):
+        import numpy as np
+        self.arrays = [np.ascontiguousarray(a) for a in arrays]
+        if not self.arrays or any(a.shape[0] != self.arrays[0].shape[0] for a in self.arrays):
+            raise ValueError("arrays must share their first dimension")
+
+    def __len__(self):
+        return self.arrays[0].shape[0]
+
+    def __getitem__(self, i):
+        out = tuple(torch.from_numpy(a[i]) if a[i].ndim else torch.tensor(a[i]) for a in self.arrays)
+        return out if len(out) > 1 else out[0]
+
+
+class InMemoryDataset(Dataset):
+    """Materialises another dataset (map-style or iterable) once, optionally through ``transform``; later epochs read
+    the cached items."""
+
+    def __init__(self, source, transform: Optional[Callable[[Any], Any]] = None, limit: Optional[int] = None):
+        it = (source[i] for i in range(len(source))) if hasattr(source, "__getitem__") and hasattr(source, "__len__") else iter(source)
+        self.items = []
+        for k, x in enumerate(it):
+            if limit is not None and k >= limit:
+                break
+            self.items.append(transform(x) if transform is not None else x)
+
+    def __len__(self):
+        return len(self.items)
+
+    def __getitem__(self, i):
+        return self.items[i]
+
+
 # ------------------------------------------------------------------ collate
+def stack_collate(items: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Tensors of one shape stacked along a new first dimension; anything else is an error (no silent lists)."""
+    if not items or not all(isinstance(t, torch.Tensor) for t in items):
+        raise TypeError("stack_collate takes tensors")
+    if any(t.shape != items[0].shape for t in items):
+        raise ValueError(f"shapes differ: {sorted({tuple(t.shape) for t in items})}")
+    return torch.stack(list(items), 0)
+
+
+def dict_collate(items: Sequence[Dict[str, Any]], per_key: Optional[Dict[str, Callable]] = None) -> Dict[str, Any]:
+    """Dictionaries with the same keys, collated key by key (``per_key`` overrides the default for a key)."""
+    keys = list(items[0])
+    if any(list(it) != keys for it in items):
+        raise KeyError("samples disagree on their keys")
+    per_key = per_key or {}
+    return {k: per_key.get(k, default_collate)([it[k] for it in items]) for k in keys}
+
+
 def default_collate(items: Sequence[Any]):
     x = items[0]
     if isinstance(x, torch.Tensor):
@@ -386,3 +440,42 @@ class DataLoader:
     def metrics(self) -> Dict[str, float]:
         return {"batches": self.batches_served, "wait_seconds": self.wait_seconds, "worker_restarts": self.worker_restarts,
                 "errors": len(self.errors.errors), "pinned_allocations": self.pool.allocations, "pinned_reuses": self.pool.reuses}
+
+
+class AdvancedDataLoader(DataLoader):
+    """The same loader for ``async`` programs: ``async for batch in loader`` and ``await loader.next_batch_async()``
+    hand the blocking wait for the next batch to a helper thread, so an event loop that also serves requests keeps
+    running while workers fill the queue (reference: src/MLFramework/Data/AdvancedDataLoader.cs, async enumerators)."""
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self._it: Optional[Iterator[Any]] = None
+        self._done = object()
+
+    def reset(self):
+        self._it = None
+
+    def _next_blocking(self):
+        if self._it is None:
+            self._it = iter(self)
+        try:
+            return next(self._it)
+        except StopIteration:
+            self._it = None
+            return self._done
+
+    async def next_batch_async(self):
+        """The next batch, or ``None`` at the end of the epoch (the following call starts the next epoch)."""
+        import asyncio
+        b = await asyncio.get_running_loop().run_in_executor(None, self._next_blocking)
+        return None if b is self._done else b
+
+    def __aiter__(self):
+        self._it = None
+        return self
+
+    async def __anext__(self):
+        b = await self.next_batch_async()
+        if b is None:
+            raise StopAsyncIteration
+        return b

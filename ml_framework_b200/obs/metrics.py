@@ -90,6 +90,105 @@ class MetricsCollector:
                                 for k, v in self.timings.items()}}
 
 
+class PerformanceCounter:
+    """One named duration series: count, total, min, max, mean and the last value
+    (src/MLFramework/Data/Metrics/PerformanceCounter.cs)."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.count, self.total_s, self.min_s, self.max_s, self.last_s = 0, 0.0, float("inf"), 0.0, 0.0
+        self._lock = threading.Lock()
+
+    def record(self, seconds: float):
+        with self._lock:
+            self.count += 1
+            self.total_s += seconds
+            self.min_s, self.max_s, self.last_s = min(self.min_s, seconds), max(self.max_s, seconds), seconds
+
+    @property
+    def mean_s(self) -> float:
+        return self.total_s / self.count if self.count else 0.0
+
+    def reset(self):
+        with self._lock:
+            self.count, self.total_s, self.min_s, self.max_s, self.last_s = 0, 0.0, float("inf"), 0.0, 0.0
+
+    def as_dict(self) -> Dict[str, float]:
+        return {"count": self.count, "total_s": self.total_s, "mean_s": self.mean_s, "min_s": self.min_s if self.count else 0.0,
+                "max_s": self.max_s, "last_s": self.last_s}
+
+
+class ProfilingScope:
+    """``with ProfilingScope(counter_or_collector, name):`` records the block's wall time on exit, also when it raises
+    (src/MLFramework/Data/Metrics/ProfilingScope.cs)."""
+
+    def __init__(self, sink, name: Optional[str] = None):
+        self.sink, self.name = sink, name
+        self.elapsed_s = 0.0
+
+    def __enter__(self):
+        self._t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc):
+        self.elapsed_s = time.perf_counter() - self._t0
+        if isinstance(self.sink, PerformanceCounter):
+            self.sink.record(self.elapsed_s)
+        else:
+            self.sink.timing(self.name or "scope", self.elapsed_s)
+        return False
+
+
+class DataLoadingMetrics:
+    """The input pipeline's own numbers: time per stage (fetch, collate, transfer), batches and samples served, the
+    consumer's wait, queue depth, and whether the trainer or the loader is the bottleneck
+    (src/MLFramework/Data/Metrics/DataLoadingMetrics.cs)."""
+    STAGES = ("fetch", "collate", "transfer", "wait")
+
+    def __init__(self):
+        self.stages = {k: PerformanceCounter(k) for k in self.STAGES}
+        self.batches = self.samples = 0
+        self.queue_depth = CircularBuffer(256)
+        self._t0 = time.perf_counter()
+
+    def scope(self, stage: str) -> ProfilingScope:
+        return ProfilingScope(self.stages[stage])
+
+    def record_batch(self, n_samples: int, queue_depth: Optional[int] = None):
+        self.batches += 1
+        self.samples += n_samples
+        if queue_depth is not None:
+            self.queue_depth.add(queue_depth)
+
+    def samples_per_second(self) -> float:
+        dt = time.perf_counter() - self._t0
+        return self.samples / dt if dt > 0 else 0.0
+
+    def wait_fraction(self) -> float:
+        """Share of the elapsed time the consumer spent waiting for a batch."""
+        dt = time.perf_counter() - self._t0
+        return min(1.0, self.stages["wait"].total_s / dt) if dt > 0 else 0.0
+
+    def bottleneck(self) -> str:
+        if self.wait_fraction() > 0.1:
+            busy = {k: c.total_s for k, c in self.stages.items() if k != "wait"}
+            return "loader:" + max(busy, key=busy.get) if any(busy.values()) else "loader"
+        return "consumer"
+
+    def snapshot(self) -> Dict[str, object]:
+        return {"batches": self.batches, "samples": self.samples, "samples_per_second": self.samples_per_second(),
+                "wait_fraction": self.wait_fraction(), "mean_queue_depth": self.queue_depth.mean(), "bottleneck": self.bottleneck(),
+                "stages": {k: c.as_dict() for k, c in self.stages.items()}}
+
+    def publish(self, collector: "MetricsCollector", prefix: str = "data"):
+        collector.gauge(f"{prefix}.samples_per_second", self.samples_per_second())
+        collector.gauge(f"{prefix}.wait_fraction", self.wait_fraction())
+        collector.inc(f"{prefix}.batches", 0)
+        collector.counters[f"{prefix}.batches"] = float(self.batches)
+        for k, c in self.stages.items():
+            collector.gauge(f"{prefix}.{k}_mean_ms", c.mean_s * 1e3)
+
+
 def _prom_name(n: str) -> str:
     return "".join(c if c.isalnum() else "_" for c in n)
 
