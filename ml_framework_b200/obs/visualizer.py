@@ -28,7 +28,7 @@ class VisualizationConfiguration:
     def validate(self):
         if self.buffer_capacity <= 0 or self.histogram_bins <= 0 or self.flush_interval_s <= 0:
             raise ValueError("buffer_capacity, histogram_bins and flush_interval_s must be positive")
-        if self.storage not in ("file", "memory"):
+        if self.storage not in ("file", "memory", "binary"):
             raise ValueError(f"unknown storage {self.storage!r}")
 
 
@@ -85,13 +85,36 @@ class Visualizer:
         self.cfg.validate()
         self.events = EventSystem()
         if backend is None:
-            backend = FileStorageBackend(self.cfg.log_dir) if self.cfg.storage == "file" else MemoryStorageBackend()
+            if self.cfg.storage == "binary":
+                from .event_file import BinaryFileStorageBackend
+                backend = BinaryFileStorageBackend(self.cfg.log_dir)
+            else:
+                backend = FileStorageBackend(self.cfg.log_dir) if self.cfg.storage == "file" else MemoryStorageBackend()
         self.backend = backend
         ccfg = EventCollectorConfig(buffer_capacity=self.cfg.buffer_capacity, flush_interval_s=self.cfg.flush_interval_s)
         self.collector = (AsyncEventCollector if self.cfg.async_collection else EventCollector)(backend, ccfg)
         self.events.subscribe(self.collector.collect)
         self.scalars = ScalarLogger(self.events)
         self.profiler = Profiler()
+        from .graphs import GraphLogger
+        from .histograms import HistogramBinConfig, HistogramLogger
+        self.histograms = HistogramLogger(default_bins=HistogramBinConfig(self.cfg.histogram_bins))
+        self.graphs = GraphLogger()
+
+    def log_distribution(self, name: str, values: torch.Tensor, step: int = -1):
+        """Moments, quantiles, outlier and dead-value counts of a tensor, kept by name and step (``self.histograms``)."""
+        if self.cfg.enabled:
+            return self.histograms.log_distribution(name, values, step)
+
+    def log_autograd_graph(self, output: torch.Tensor, model: Optional[torch.nn.Module] = None, name: str = "step"):
+        """The operation graph autograd recorded behind ``output`` (the loss), as a graph event plus an analysis."""
+        if not self.cfg.enabled:
+            return None
+        from .graphs import GraphSerializer, graph_from_autograd
+        g = graph_from_autograd(output, dict(model.named_parameters()) if model is not None else None, name)
+        self.graphs.log_graph(g)
+        self.events.publish(Event(EventType.GRAPH, name, 0, GraphSerializer.to_dict(g)))
+        return self.graphs.analyze_graph(name)
 
     def log_scalar(self, name: str, value: float, step: int = 0):
         if self.cfg.enabled:
