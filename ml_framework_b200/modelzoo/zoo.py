@@ -36,6 +36,11 @@ class ModelInfo:
     sha256: Optional[str] = None
     tags: Tuple[str, ...] = ()
     description: str = ""
+    license: str = ""
+    metrics: Optional[Dict[str, float]] = None       # e.g. {"accuracy": 0.76, "perplexity": 12.3}
+    file_size: Optional[int] = None                  # bytes of the weight file when known
+    pretrained_dataset: str = ""
+    framework_version: str = ""
 
     def num_params(self) -> int:
         return _build_config(self).num_params() if self.architecture in ("gpt", "llama") else 0
