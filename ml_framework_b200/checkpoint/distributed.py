@@ -481,8 +481,12 @@ class CheckpointLoader:
             tensors = MultiShardCheckpointFormat.read_shard(os.path.join(os.path.dirname(prefix) or ".", sm.FilePath), sm, verify,
                                                             device=device)
             return CheckpointLoadResult(tensors, meta, False, meta.WorldSize, W)
-        plan = ReshardingStrategy.create_plan(meta, W, r)
-        tensors = ReshardingStrategy.execute(plan, meta, prefix, device, verify)
+        if opt.resharding_strategy == "simple":
+            from .validation import SimpleReshardingStrategy       # reads every shard; the parallel plan reads overlaps only
+            tensors = SimpleReshardingStrategy().load(meta, prefix, W, r, device, verify)
+        else:
+            plan = ReshardingStrategy.create_plan(meta, W, r)
+            tensors = ReshardingStrategy.execute(plan, meta, prefix, device, verify)
         return CheckpointLoadResult(tensors, meta, True, meta.WorldSize, W)
 
 
