@@ -26,7 +26,9 @@ _DTYPES = {"float32": torch.float32, "float16": torch.float16, "int8": torch.int
 _NP = {"float32": np.float32, "float16": np.float16, "int8": np.int8, "uint8": np.uint8, "int32": np.int32, "int64": np.int64}
 
 OPERATOR_TYPES = ("conv2d", "fully_connected", "relu", "max_pool2d", "avg_pool2d", "batch_norm", "softmax", "add", "mul", "flatten",
-                  "reshape", "concat", "sigmoid", "tanh", "global_avg_pool")
+                  "reshape", "concat", "sigmoid", "tanh", "global_avg_pool",
+                  # the reference runtime's tensor operator set (src/MobileRuntime/Tensors/TensorOperations.cs:19-434)
+                  "sub", "div", "abs", "sqrt", "square", "log", "exp", "sum", "mean", "max", "min", "matmul", "transpose", "cast", "copy")
 
 
 @dataclass

@@ -156,7 +156,42 @@ class MobileRuntime:
         if t == "flatten": return x.reshape(x.shape[0], -1)
         if t == "reshape": return x.reshape(op.attrs["shape"])
         if t == "concat": return torch.cat([get(n) for n in op.inputs], op.attrs.get("dim", 1))
+        if t == "sub": return x - get(op.inputs[1])
+        if t == "div": return x / get(op.inputs[1])
+        if t == "matmul": return x @ get(op.inputs[1])
+        if t in ("abs", "sqrt", "square", "log", "exp"): return getattr(torch, t)(x)
+        if t in ("sum", "mean", "max", "min"):
+            ax = op.attrs.get("axis")
+            if ax is None:
+                return getattr(x, t)().reshape(1)
+            r = getattr(x, {"max": "amax", "min": "amin"}.get(t, t))(ax, keepdim=op.attrs.get("keepdims", False))
+            return r
+        if t == "transpose": return x.permute(op.attrs["perm"]).contiguous() if "perm" in op.attrs else x.transpose(-1, -2).contiguous()
+        if t == "cast": return x.to(getattr(torch, op.attrs["dtype"]))
+        if t == "copy": return x.clone()
         raise NotImplementedError(t)
+
+    @torch.no_grad()
+    def profile_operators(self, *inputs: torch.Tensor, iters: int = 5) -> List[Dict[str, object]]:
+        """Time per operator (device-synchronised around every operator, so the sum exceeds an unprofiled ``predict``):
+        ``[{index, type, output, mean_ms, share}]`` sorted by cost."""
+        if self.model is None:
+            raise RuntimeError("no model loaded")
+        acc = [0.0] * len(self.model.operators)
+        for _ in range(iters):
+            env = {spec["name"]: x.to(self.device, torch.float32) for spec, x in zip(self.model.inputs, inputs)}
+            for k, op in enumerate(self.model.operators):
+                if self.native:
+                    torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                env[op.outputs[0]] = self._run_op(op, env)
+                if self.native:
+                    torch.cuda.synchronize()
+                acc[k] += (time.perf_counter() - t0) * 1e3
+        total = sum(acc) or 1.0
+        rows = [{"index": k, "type": op.type, "output": op.outputs[0], "mean_ms": acc[k] / iters, "share": acc[k] / total}
+                for k, op in enumerate(self.model.operators)]
+        return sorted(rows, key=lambda r: -r["mean_ms"])
 
     @torch.no_grad()
     def predict(self, *inputs: torch.Tensor) -> List[torch.Tensor]:
@@ -280,6 +315,29 @@ def optimize(model: MobModel) -> MobModel:
     return MobModel(model.inputs, model.outputs, out, {k: v for k, v in model.tensors.items() if k in used}, dict(model.metadata, optimized=True))
 
 
+def fold_constants(model: MobModel) -> MobModel:
+    """Constant folder: an operator whose inputs are all stored tensors (no graph input reaches it) is evaluated once
+    here and its result stored as a tensor; operators left without readers disappear with it."""
+    rt = MobileRuntime("cpu")
+    rt.model = model
+    rt.weights = {n: (t.data.float() - (t.zero_point or 0)) * t.scale if t.scale is not None else t.data for n, t in model.tensors.items()}
+    const = set(model.tensors)
+    tensors = dict(model.tensors)
+    kept: List[MobOperator] = []
+    with torch.no_grad():
+        for o in model.operators:
+            if o.inputs and all(n in const for n in o.inputs) and o.type not in ("copy",):
+                val = rt._run_op(o, {})
+                rt.weights[o.outputs[0]] = val
+                tensors[o.outputs[0]] = MobTensor(o.outputs[0], val)
+                const.add(o.outputs[0])
+            else:
+                kept.append(o)
+    used = {n for o in kept for n in o.inputs} | set(model.outputs)
+    return MobModel(model.inputs, model.outputs, kept, {k: v for k, v in tensors.items() if k in used},
+                    dict(model.metadata, constants_folded=len(model.operators) - len(kept)))
+
+
 def quantize_weights(model: MobModel, mode: str = "int8") -> MobModel:
     """Stores conv / fc weights as int8 / uint8 (per tensor, affine) or fp16; biases and norm parameters stay fp32."""
     weight_names = {o.inputs[1] for o in model.operators if o.type in ("conv2d", "fully_connected")}
@@ -311,7 +369,7 @@ def convert(in_path: str, out_path: str, quantize: Optional[str] = None, verbose
         obj = torch.load(in_path, weights_only=False)
         m = convert_sequential(obj["model"].eval(), obj["input_shape"])
     n0 = len(m.operators)
-    m = optimize(m)
+    m = optimize(fold_constants(m))
     if quantize:
         m = quantize_weights(m, quantize)
     errs = m.validate()
