@@ -13,6 +13,7 @@ pool; ``replay`` copies new inputs in, launches and returns the static outputs.
 """
 from __future__ import annotations
 
+import contextlib
 import enum
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
@@ -270,3 +271,190 @@ def capture_graph(manager: CUDAGraphManager, name: Optional[str] = None):
         wrapped.__wrapped__ = fn
         return wrapped
     return deco
+
+
+# ------------------------------------------------------------------ fall-back handler, proxy, allocator, static facade
+class CUDAGraphFallbackHandler:
+    """``execute_with_fallback(graph_fn, eager_fn)``: try the graph path; on an exception run the eager path, count the
+    failure by exception type, and stop trying the graph path after ``max_failures`` consecutive failures
+    (src/MLFramework/HAL/CUDA/Graphs/Fallback/CUDAGraphFallbackHandler.cs:56)."""
+
+    def __init__(self, max_failures: int = 3, on_fallback: Optional[Callable[[BaseException], None]] = None):
+        self.max_failures, self.on_fallback = max_failures, on_fallback
+        self.consecutive_failures = 0
+        self.total_fallbacks = 0
+        self.successes = 0
+        self.by_type: Dict[str, int] = {}
+        self.last_error: Optional[BaseException] = None
+
+    @property
+    def graph_path_enabled(self) -> bool:
+        return self.consecutive_failures < self.max_failures
+
+    def execute_with_fallback(self, graph_fn: Callable, eager_fn: Callable):
+        if self.graph_path_enabled:
+            try:
+                out = graph_fn()
+                self.successes += 1
+                self.consecutive_failures = 0
+                return out
+            except Exception as e:       # noqa: BLE001 - any capture / replay failure goes to the eager path
+                self.consecutive_failures += 1
+                self.by_type[type(e).__name__] = self.by_type.get(type(e).__name__, 0) + 1
+                self.last_error = e
+                if self.on_fallback is not None:
+                    self.on_fallback(e)
+        self.total_fallbacks += 1
+        return eager_fn()
+
+    def reset(self):
+        self.consecutive_failures = 0
+        self.last_error = None
+
+    def stats(self) -> Dict[str, object]:
+        return {"successes": self.successes, "fallbacks": self.total_fallbacks, "consecutive_failures": self.consecutive_failures,
+                "graph_path_enabled": self.graph_path_enabled, "by_type": dict(self.by_type)}
+
+
+class CUDAGraphProxy:
+    """A callable (function or module) behind a graph manager: calls go through capture-and-replay per input signature,
+    with the eager callable as the fall-back (Graphs/Proxies/CUDAGraphProxy.cs). ``invalidate()`` drops the captures
+    (after a shape-changing edit of the module); ``update_weights`` refreshes parameters in place so captures stay
+    valid (ICUDAGraphWeightUpdater.cs)."""
+
+    def __init__(self, fn: Callable, manager: Optional["CUDAGraphManager"] = None, name: Optional[str] = None, enabled: bool = True):
+        self.fn, self.manager = fn, manager or CUDAGraphManager()
+        self.name = name or getattr(fn, "__name__", type(fn).__name__)
+        self.enabled = enabled
+        self.calls = 0
+
+    def __call__(self, *inputs: torch.Tensor):
+        self.calls += 1
+        if not self.enabled:
+            return self.fn(*inputs)
+        return self.manager.run(self.name, self.fn, *inputs)
+
+    @property
+    def captured_signatures(self) -> int:
+        return sum(1 for k in self.manager._graphs if k[0] == self.name)
+
+    @property
+    def is_captured(self) -> bool:
+        return self.captured_signatures > 0
+
+    def invalidate(self):
+        for k in [k for k in self.manager._graphs if k[0] == self.name]:
+            del self.manager._graphs[k]
+        for k in [k for k in self.manager._calls if k[0] == self.name]:
+            del self.manager._calls[k]
+
+    def update_weights(self, new_state: Dict[str, torch.Tensor]) -> int:
+        """Copies ``new_state`` into the wrapped module's parameters / buffers in place; returns how many were written."""
+        if not isinstance(self.fn, torch.nn.Module):
+            raise TypeError("update_weights needs a module")
+        own, n = self.fn.state_dict(), 0
+        with torch.no_grad():
+            for k, v in new_state.items():
+                if k in own:
+                    if own[k].shape != v.shape:
+                        raise ValueError(f"{k}: shape {tuple(v.shape)} does not match {tuple(own[k].shape)}; invalidate() and recapture instead")
+                    own[k].copy_(v)
+                    n += 1
+        return n
+
+
+@dataclass
+class MemoryUsageStats:
+    pool_capacity: int = 0
+    pool_used: int = 0
+    pool_peak: int = 0
+    pool_blocks: int = 0
+    pool_allocations: int = 0
+    fallback_allocations: int = 0
+    fallback_bytes: int = 0
+
+    @property
+    def pool_utilization(self) -> float:
+        return self.pool_used / self.pool_capacity if self.pool_capacity else 0.0
+
+
+class GraphCompatibleMemoryAllocator:
+    """Allocation front for code that may run under capture: inside ``capture_scope()`` tensors come from the
+    fixed-address pool (their addresses are what the graph records); outside they come from the caching allocator
+    (Memory/GraphCompatibleMemoryAllocator.cs). A pool that is full raises inside a capture (a silent fall-back
+    allocation there would be freed and reused under the graph's feet)."""
+
+    def __init__(self, pool: Optional[GraphMemoryPool] = None):
+        self.pool = pool or GraphMemoryPool()
+        self._in_capture = 0
+        self._s = MemoryUsageStats()
+
+    @contextlib.contextmanager
+    def capture_scope(self):
+        self._in_capture += 1
+        try:
+            yield self
+        finally:
+            self._in_capture -= 1
+
+    @property
+    def in_capture(self) -> bool:
+        return self._in_capture > 0
+
+    def allocate(self, shape: Sequence[int], dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        if self.in_capture:
+            t = self.pool.allocate(shape, dtype)
+            self._s.pool_allocations += 1
+            return t
+        t = torch.empty(tuple(shape), dtype=dtype, device=self.pool.device)
+        self._s.fallback_allocations += 1
+        self._s.fallback_bytes += t.numel() * t.element_size()
+        return t
+
+    def free(self, t: torch.Tensor) -> bool:
+        """Returns a pool block when it is the most recent one; other tensors are left to the caching allocator."""
+        return self.pool.return_block(t) if self.pool._slab is not None else False
+
+    def reset_pool(self):
+        if self.in_capture:
+            raise RuntimeError("the pool cannot be rewound during a capture")
+        self.pool.reset()
+
+    def stats(self) -> MemoryUsageStats:
+        p = self.pool.stats()
+        s = MemoryUsageStats(**{**self._s.__dict__})
+        s.pool_capacity, s.pool_used, s.pool_peak, s.pool_blocks = p["capacity"], p["used"], p["peak"], p["blocks"]
+        return s
+
+
+class CUDAGraphStatic:
+    """Process-wide default manager for code that does not carry one around (Graphs/CUDAGraphStatic.cs)."""
+    _manager: Optional[CUDAGraphManager] = None
+    enabled = True
+
+    @classmethod
+    def manager(cls) -> CUDAGraphManager:
+        if cls._manager is None:
+            cls._manager = CUDAGraphManager()
+        return cls._manager
+
+    @classmethod
+    def configure(cls, options: CaptureOptions):
+        cls._manager = CUDAGraphManager(options)
+
+    @classmethod
+    def run(cls, name: str, fn: Callable, *inputs: torch.Tensor):
+        return cls.manager().run(name, fn, *inputs) if cls.enabled else fn(*inputs)
+
+    @classmethod
+    def proxy(cls, fn: Callable, name: Optional[str] = None) -> CUDAGraphProxy:
+        return CUDAGraphProxy(fn, cls.manager(), name)
+
+    @classmethod
+    def stats(cls) -> Dict[str, int]:
+        return cls.manager().stats()
+
+    @classmethod
+    def reset(cls):
+        cls._manager = None
+        cls.enabled = True

@@ -131,3 +131,65 @@ def test_memory_pressure_handler_releases_low_priority_first_until_below_the_low
     assert h.check() == 25 and used[0] == 74 and h.events == 2      # stops as soon as usage is under the low mark
     used[0] = 140
     assert h.check() == 75 and log[-1] == "important" and used[0] == 65
+
+
+def test_graph_fallback_handler_proxy_allocator_and_static_facade():
+    import torch
+    import torch.nn as nn
+    from ml_framework_b200.hal import cuda_graphs as cg
+    seen = []
+    fb = cg.CUDAGraphFallbackHandler(max_failures=2, on_fallback=seen.append)
+    assert fb.execute_with_fallback(lambda: "graph", lambda: "eager") == "graph"
+
+    def boom():
+        raise RuntimeError("capture failed")
+    assert fb.execute_with_fallback(boom, lambda: "eager") == "eager" and fb.graph_path_enabled
+    assert fb.execute_with_fallback(boom, lambda: "eager") == "eager" and not fb.graph_path_enabled
+    calls = []
+    assert fb.execute_with_fallback(lambda: calls.append(1), lambda: "eager") == "eager" and calls == []      # graph path is off
+    st = fb.stats()
+    assert st["successes"] == 1 and st["fallbacks"] == 3 and st["by_type"] == {"RuntimeError": 2} and len(seen) == 2
+    fb.reset()
+    assert fb.graph_path_enabled and fb.last_error is None
+
+    lin = nn.Linear(3, 2)
+    px = cg.CUDAGraphProxy(lin, name="lin")
+    x = torch.randn(4, 3)
+    for _ in range(5):
+        assert torch.equal(px(x), lin(x))                    # CPU tensors: warm-up, then the eager fall-back
+    assert px.calls == 5 and not px.is_captured and px.manager.fallbacks == 2
+    assert px.update_weights({"weight": torch.zeros(2, 3), "other": torch.zeros(1)}) == 1 and float(lin.weight.detach().abs().sum()) == 0.0
+    with __import__("pytest").raises(ValueError):
+        px.update_weights({"weight": torch.zeros(3, 3)})
+    with __import__("pytest").raises(TypeError):
+        cg.CUDAGraphProxy(lambda t: t).update_weights({})
+    px.invalidate()
+    px.enabled = False
+    px(x)
+    assert px.manager._calls == {}
+
+    al = cg.GraphCompatibleMemoryAllocator(cg.GraphMemoryPool(4096, torch.device("cpu")))
+    a = al.allocate((8,), torch.float32)
+    with al.capture_scope():
+        b = al.allocate((100,), torch.float32)
+        c = al.allocate((10,), torch.bfloat16)
+        assert al.in_capture and c.data_ptr() - b.data_ptr() == 512
+        with __import__("pytest").raises(RuntimeError):
+            al.reset_pool()
+        with __import__("pytest").raises(MemoryError):
+            al.allocate((2000,), torch.float32)
+    s = al.stats()
+    assert (s.pool_allocations, s.fallback_allocations, s.fallback_bytes, s.pool_used, s.pool_blocks) == (2, 1, 32, 768, 2) and abs(s.pool_utilization - 768 / 4096) < 1e-9
+    assert al.free(c) and not al.free(a) and al.stats().pool_used == 512
+    al.reset_pool()
+    assert al.stats().pool_used == 0 and al.stats().pool_peak == 768
+
+    cg.CUDAGraphStatic.reset()
+    f = lambda t: t * 2      # noqa: E731
+    assert torch.equal(cg.CUDAGraphStatic.run("dbl", f, x), x * 2) and cg.CUDAGraphStatic.stats()["graphs"] == 0
+    p2 = cg.CUDAGraphStatic.proxy(f, "dbl2")
+    assert p2.manager is cg.CUDAGraphStatic.manager() and torch.equal(p2(x), x * 2)
+    cg.CUDAGraphStatic.enabled = False
+    assert torch.equal(cg.CUDAGraphStatic.run("dbl", f, x), x * 2)
+    cg.CUDAGraphStatic.configure(cg.CaptureOptions())
+    cg.CUDAGraphStatic.reset()
