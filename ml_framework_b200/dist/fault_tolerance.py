@@ -255,6 +255,13 @@ class RingAllReduce:
     def __init__(self, pg):
         self.pg = pg
 
+    def _swap(self, out: torch.Tensor, dst: int, buf: torch.Tensor, src: int):
+        """Send to the next rank and receive from the previous one with both transfers posted before either is waited
+        for: every rank of the ring sends at the same moment, so a blocking send would wait for a receive that its
+        peer only posts after its own send."""
+        for w in self.pg.batch_isend_irecv([("send", out, dst), ("recv", buf, src)]):
+            w.wait()
+
     def all_reduce(self, t: torch.Tensor, op: ReduceOp = ReduceOp.SUM) -> torch.Tensor:
         W, r = self.pg.world_size, self.pg.rank
         if W == 1:
@@ -265,8 +272,7 @@ class RingAllReduce:
         for step in range(W - 1):                 # reduce-scatter
             si, ri = (r - step) % W, (r - step - 1) % W
             buf = torch.empty_like(cm.chunk(flat, ri))
-            self.pg.send(cm.chunk(flat, si).clone(), nxt, tag=step)
-            self.pg.recv(buf, prv, tag=step)
+            self._swap(cm.chunk(flat, si).clone(), nxt, buf, prv)
             c = cm.chunk(flat, ri)
             if op in (ReduceOp.SUM, ReduceOp.AVG):
                 c.add_(buf)
@@ -279,8 +285,7 @@ class RingAllReduce:
         for step in range(W - 1):                 # all-gather
             si, ri = (r + 1 - step) % W, (r - step) % W
             buf = torch.empty_like(cm.chunk(flat, ri))
-            self.pg.send(cm.chunk(flat, si).clone(), nxt, tag=100 + step)
-            self.pg.recv(buf, prv, tag=100 + step)
+            self._swap(cm.chunk(flat, si).clone(), nxt, buf, prv)
             cm.chunk(flat, ri).copy_(buf)
         if op == ReduceOp.AVG:
             flat.div_(W)
