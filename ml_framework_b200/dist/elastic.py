@@ -163,6 +163,40 @@ class ElasticCoordinator:
             raise ElasticError(f"{self.failed_total} of {self.peak_workers} workers failed: above the "
                                f"{self.cfg.failure_tolerance_percentage}% tolerance")
 
+    def start_health_timer(self, period_s: Optional[float] = None):
+        """Polls on a background thread every ``period_s`` (default: half the heartbeat timeout, as the reference's
+        timer does). Errors raised by a poll (tolerance exceeded, too few workers) are kept in ``timer_error`` and stop
+        the timer; the training loop reads them with ``raise_timer_error()``."""
+        import threading
+        if getattr(self, "_timer", None) is not None:
+            return
+        period = period_s if period_s is not None else self.cfg.worker_heartbeat_timeout_ms / 2e3
+        self._timer_stop = threading.Event()
+        self.timer_error: Optional[BaseException] = None
+
+        def loop():
+            while not self._timer_stop.wait(period):
+                try:
+                    self.poll()
+                except ElasticError as e:
+                    self.timer_error = e
+                    return
+        self._timer = threading.Thread(target=loop, daemon=True, name="mlf-elastic-health")
+        self._timer.start()
+
+    def stop_health_timer(self):
+        t = getattr(self, "_timer", None)
+        if t is not None:
+            self._timer_stop.set()
+            t.join(timeout=2.0)
+            self._timer = None
+
+    def raise_timer_error(self):
+        e = getattr(self, "timer_error", None)
+        if e is not None:
+            self.timer_error = None
+            raise e
+
     def poll(self) -> Optional[RescalingEvent]:
         """Health check + debounce: raises at most one rescaling event once the membership has been
         stable for the stability window."""
@@ -213,6 +247,68 @@ class AdaptiveLearningRateScheduler:
         if transition_steps <= 0 or step >= transition_steps:
             return new_lr
         return old_lr + (new_lr - old_lr) * step / transition_steps
+
+
+class LearningRateTransitionManager:
+    """Moves an optimizer's learning rate from its current value to a target over ``transition_steps`` optimizer steps
+    (linear or half-cosine) instead of jumping on a rescale; a new target mid-way restarts from the rate in force
+    (reference: src/MLFramework/Distributed/Scheduling/LearningRateTransitionManager.cs)."""
+
+    def __init__(self, optimizer=None, transition_steps: int = 100, mode: str = "linear"):
+        if transition_steps < 0:
+            raise ValueError("transition_steps must be non-negative")
+        if mode not in ("linear", "cosine"):
+            raise ValueError(f"unknown mode {mode!r}")
+        self.optimizer, self.transition_steps, self.mode = optimizer, transition_steps, mode
+        self._from = self._to = None
+        self._k = 0
+        self.history: List[Tuple[float, float]] = []        # (from, to) of every transition started
+
+    @property
+    def in_transition(self) -> bool:
+        return self._to is not None
+
+    def current_lr(self) -> Optional[float]:
+        if self.optimizer is not None:
+            g = self.optimizer.param_groups[0] if hasattr(self.optimizer, "param_groups") else None
+            return g["lr"] if g is not None else getattr(self.optimizer, "lr", None)
+        return self._value() if self.in_transition else None
+
+    def _value(self) -> float:
+        if self.transition_steps == 0 or self._k >= self.transition_steps:
+            return self._to
+        f = self._k / self.transition_steps
+        if self.mode == "cosine":
+            f = 0.5 * (1.0 - math.cos(math.pi * f))
+        return self._from + (self._to - self._from) * f
+
+    def _apply(self, lr: float):
+        if self.optimizer is None:
+            return
+        if hasattr(self.optimizer, "param_groups"):
+            for g in self.optimizer.param_groups:
+                g["lr"] = lr
+        else:
+            self.optimizer.lr = lr
+
+    def start_transition(self, target_lr: float, from_lr: Optional[float] = None):
+        start = from_lr if from_lr is not None else (self._value() if self.in_transition else self.current_lr())
+        if start is None:
+            raise ElasticError("no starting learning rate: give from_lr or an optimizer")
+        self._from, self._to, self._k = float(start), float(target_lr), 0
+        self.history.append((self._from, self._to))
+        self._apply(self._value())
+
+    def step(self) -> Optional[float]:
+        """Call once per optimizer step; returns the rate now in force (``None`` when no transition is running)."""
+        if not self.in_transition:
+            return None
+        self._k += 1
+        lr = self._value()
+        self._apply(lr)
+        if self._k >= self.transition_steps:
+            self._from = self._to = None
+        return lr
 
 
 @dataclass

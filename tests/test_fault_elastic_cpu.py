@@ -167,3 +167,45 @@ def test_lr_adaptation_and_data_plan():
     assert moved == 75 and all(t.src_rank != t.dst_rank for t in plan)
     with pytest.raises(ValueError):
         ElasticTrainingConfig(min_workers=0).validate()
+
+
+def test_learning_rate_transition_manager_and_health_timer():
+    import time as _t
+    import torch
+    from ml_framework_b200.dist.elastic import ElasticCoordinator, ElasticError, ElasticTrainingConfig, LearningRateTransitionManager
+    opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1)
+    m = LearningRateTransitionManager(opt, transition_steps=4)
+    assert not m.in_transition and m.step() is None and m.current_lr() == 0.1
+    m.start_transition(0.5)
+    lrs = [m.step() for _ in range(4)]
+    assert [round(x, 6) for x in lrs] == [0.2, 0.3, 0.4, 0.5] and not m.in_transition and opt.param_groups[0]["lr"] == 0.5
+    m.start_transition(0.1)
+    m.step(); m.step()                                   # half way: 0.3
+    m.start_transition(0.9)                              # a second rescale restarts from the rate in force
+    assert m.history[:2] == [(0.1, 0.5), (0.5, 0.1)] and abs(m.history[2][0] - 0.3) < 1e-12 and m.history[2][1] == 0.9 and abs(m.step() - 0.45) < 1e-9
+    cos = LearningRateTransitionManager(None, transition_steps=2, mode="cosine")
+    cos.start_transition(1.0, from_lr=0.0)
+    assert abs(cos.step() - 0.5) < 1e-12 and cos.step() == 1.0 and cos.current_lr() is None
+    jump = LearningRateTransitionManager(opt, transition_steps=0)
+    jump.start_transition(0.01)
+    assert opt.param_groups[0]["lr"] == 0.01
+    import pytest as _p
+    with _p.raises(ElasticError):
+        LearningRateTransitionManager(None).start_transition(1.0)
+    with _p.raises(ValueError):
+        LearningRateTransitionManager(None, mode="step")
+
+    now = {"t": 0.0}
+    co = ElasticCoordinator(ElasticTrainingConfig(min_workers=1, stability_window_ms=0, worker_heartbeat_timeout_ms=50, failure_tolerance_percentage=40),
+                            clock=lambda: now["t"])
+    for w in ("a", "b", "c"):
+        co.register_worker(w)
+    co.start_health_timer(period_s=0.01)
+    _t.sleep(0.05)
+    assert co.topology.world_size == 3                   # the timer's poll raised the first rescaling event
+    now["t"] = 1.0                                       # every heartbeat is stale now: all three fail -> above tolerance
+    _t.sleep(0.1)
+    co.stop_health_timer()
+    with _p.raises(ElasticError):
+        co.raise_timer_error()
+    co.raise_timer_error()                               # reported once
