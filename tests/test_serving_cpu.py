@@ -423,3 +423,55 @@ def test_memory_aware_queue_accessors():
     assert q.should_apply_backpressure() and q.try_admit_next_request() is None      # the head does not fit: nothing is admitted
     q.clear_queue()
     assert q.queue_size() == 0 and q.try_admit_next_request() is None
+
+
+def test_tokenizers_request_tracker_and_batch_builder_pieces():
+    import threading
+    import time
+    from concurrent.futures import Future
+    from ml_framework_b200.serving import interfaces as I
+    bt = I.ByteTokenizer()
+    ids = bt.encode("héllo", add_eos=True)
+    assert ids[0] == 1 and ids[-1] == 2 and bt.decode(ids) == "héllo" and bt.vocab_size == 259 and isinstance(bt, I.Tokenizer)
+    ws = I.WhitespaceTokenizer()
+    a = ws.encode("the cat sat on the mat")
+    assert a[0] == a[4] and ws.decode(a) == "the cat sat on the mat" and ws.vocab_size == 8
+    ws.freeze()
+    assert ws.encode("the dog") == [a[0], 1] and ws.decode([a[1], 99, 2]) == "cat <unk>"
+    now = {"t": 0.0}
+    tr = I.RequestTracker(clock=lambda: now["t"])
+    tr.start("r1", "m1"); tr.start("r2", "m2")
+    now["t"] = 2.0
+    assert tr.in_flight() == 2 and tr.in_flight("m1") == 1 and tr.oldest_age_s() == 2.0 and not tr.wait_idle(0.01)
+    tr.finish("r1"); tr.finish("r2", ok=False, error="boom")
+    st = tr.statistics()
+    assert st["finished"] == 2 and st["failed"] == 1 and st["error_rate"] == 0.5 and st["mean_s"] == 2.0 and tr.wait_idle(0.01) and tr.statistics("m1")["failed"] == 0
+    import pytest as _p
+    with _p.raises(KeyError):
+        tr.finish("r1")
+    tr.start("x")
+    with _p.raises(KeyError):
+        tr.start("x")
+    q = I.BoundedRequestQueue(3)
+    assert all(q.try_enqueue(i) for i in range(3)) and not q.try_enqueue(9) and len(q) == 3
+    bb = I.BatchBuilder(q, max_batch_size=2, max_wait_s=0.01)
+    assert bb.build() == [0, 1] and bb.build() == [2] and bb.build(idle_wait_s=0.01) == []
+    q2 = I.BoundedRequestQueue(16)
+    late = threading.Timer(0.02, lambda: q2.try_enqueue("b"))
+    q2.try_enqueue("a")
+    late.start()
+    t0 = time.monotonic()
+    got = I.BatchBuilder(q2, max_batch_size=4, max_wait_s=0.2, prefer_batch_size=2).build()
+    assert got == ["a", "b"] and time.monotonic() - t0 < 0.15                  # dispatched at the preferred size, not at the deadline
+    fs = [Future(), Future()]
+    I.ResponseScatterer.scatter(fs, ["x", "y"])
+    assert [f.result() for f in fs] == ["x", "y"]
+    fs = [Future(), Future()]
+    with _p.raises(ValueError):
+        I.ResponseScatterer.scatter(fs, ["only one"])
+    assert all(isinstance(f.exception(), ValueError) for f in fs)
+    fs = [Future()]
+    I.ResponseScatterer.fail_all(fs, RuntimeError("down"))
+    assert isinstance(fs[0].exception(), RuntimeError)
+    s = I.SchedulerStatistics.from_snapshot({"requests_completed": 5, "iteration_ms_p50": 4.5, "errors": 1})
+    assert s.completed_requests == 5 and s.p50_iteration_ms == 4.5 and s.errors == 1 and I.SchedulerStatus(1, 2, 3, 0.5).is_running
