@@ -1,0 +1,349 @@
+"""Higher-order derivative toolkit beyond the basic calls: options and results, sparse / partial / regularised Hessians,
+eigenvalues, batched and numerical Hessian-vector products with validation, numerical gradients, a function registry,
+and a context that tracks differentiation order.
+
+Reference (src/MLFramework/Autograd/): Hessian.cs:233-470 (Compute with options, ComputeDiagonal,
+ComputeVectorHessianProduct, ComputeNumerical, ComputeWithRegularization), Jacobian.cs:183-698 (options with modes
+Auto / Forward / Reverse, numerical, Validate), HessianVectorProduct.cs:105-484 (batch, checkpointing, numerical,
+Validate), HigherOrderExtensions.cs:95-193 (HessianWithEigenvalues, SparseHessian, PartialHessian, GradOfGrad),
+HigherOrderContext.cs, GradientComputer.cs:90-276 (numerical gradients, error measures), FunctionRegistry.cs:26-182.
+
+All of it is built on ``torch.func`` transforms, so every call works on GPU tensors and composes with this
+package's custom autograd functions (which define ``setup_context`` where needed).
+"""
+from __future__ import annotations
+
+import contextlib
+import enum
+import threading
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Type
+
+import torch
+import torch.func as tf
+
+from .functional import CustomFunction, hvp as _hvp
+
+
+# ------------------------------------------------------------------ options / results
+class JacobianMode(enum.Enum):
+    AUTO = "auto"
+    FORWARD = "forward"
+    REVERSE = "reverse"
+
+
+@dataclass
+class JacobianOptions:
+    mode: JacobianMode = JacobianMode.AUTO
+    chunk_size: Optional[int] = None         # rows (reverse) or columns (forward) per vectorised sweep; None = all at once
+    validate: bool = False
+    tolerance: float = 1e-4
+
+
+@dataclass
+class JacobianResult:
+    jacobian: torch.Tensor
+    mode_used: JacobianMode
+    sweeps: int
+    max_numerical_error: Optional[float] = None
+
+
+@dataclass
+class HessianOptions:
+    sparse: bool = False
+    sparsity_threshold: float = 1e-8         # |entry| <= threshold counts as zero
+    symmetrize: bool = True
+    eigenvalues: bool = False
+    regularization: float = 0.0
+    indices: Optional[Sequence[int]] = None  # partial Hessian over these flat coordinates only
+
+
+@dataclass
+class HessianResult:
+    hessian: torch.Tensor                    # dense, or a sparse COO tensor when ``sparse``
+    is_sparse: bool
+    nonzeros: int
+    density: float
+    eigenvalues: Optional[torch.Tensor] = None
+
+    @property
+    def condition_number(self) -> Optional[float]:
+        if self.eigenvalues is None:
+            return None
+        a = self.eigenvalues.abs()
+        return float(a.max() / a.min().clamp_min(1e-30))
+
+    @property
+    def is_positive_definite(self) -> Optional[bool]:
+        return None if self.eigenvalues is None else bool((self.eigenvalues > 0).all())
+
+
+# ------------------------------------------------------------------ Jacobian
+def jacobian_with_options(f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor, options: Optional[JacobianOptions] = None) -> JacobianResult:
+    o = options or JacobianOptions()
+    y = f(x)
+    n_in, n_out = x.numel(), y.numel()
+    mode = o.mode
+    if mode == JacobianMode.AUTO:                       # one sweep per input (forward) or per output (reverse)
+        mode = JacobianMode.FORWARD if n_in <= n_out else JacobianMode.REVERSE
+    if mode == JacobianMode.FORWARD:
+        J = tf.jacfwd(f, chunk_size=o.chunk_size)(x) if o.chunk_size else tf.jacfwd(f)(x)
+        sweeps = -(-n_in // o.chunk_size) if o.chunk_size else 1
+    else:
+        J = tf.jacrev(f, chunk_size=o.chunk_size)(x) if o.chunk_size else tf.jacrev(f)(x)
+        sweeps = -(-n_out // o.chunk_size) if o.chunk_size else 1
+    err = None
+    if o.validate:
+        num = numerical_jacobian(f, x)
+        err = float((J.reshape(n_out, n_in) - num).abs().max())
+        if err > o.tolerance * max(1.0, float(num.abs().max())):
+            raise ArithmeticError(f"Jacobian differs from finite differences by {err:.3e}")
+    return JacobianResult(J, mode, sweeps, err)
+
+
+def numerical_jacobian(f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor, eps: Optional[float] = None) -> torch.Tensor:
+    """Central differences; ``[outputs, inputs]``. The step defaults to eps^(1/3) of the dtype times the input scale."""
+    x = x.detach()
+    h = eps if eps is not None else float(torch.finfo(x.dtype).eps) ** (1 / 3)
+    flat = x.reshape(-1)
+    cols = []
+    for i in range(flat.numel()):
+        s = h * max(1.0, abs(float(flat[i])))
+        e = torch.zeros_like(flat)
+        e[i] = s
+        cols.append(((f((flat + e).view_as(x)) - f((flat - e).view_as(x))) / (2 * s)).reshape(-1))
+    return torch.stack(cols, 1)
+
+
+def numerical_gradient(f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor, eps: Optional[float] = None) -> torch.Tensor:
+    return numerical_jacobian(lambda t: f(t).reshape(1), x, eps).reshape(x.shape)
+
+
+def numerical_gradients(f: Callable[..., torch.Tensor], inputs: Sequence[torch.Tensor], eps: Optional[float] = None) -> List[torch.Tensor]:
+    out = []
+    for k in range(len(inputs)):
+        def fk(t, k=k):
+            args = list(inputs)
+            args[k] = t
+            return f(*args)
+        out.append(numerical_gradient(fk, inputs[k], eps))
+    return out
+
+
+def relative_error(analytical: torch.Tensor, numerical: torch.Tensor) -> float:
+    d = (analytical - numerical).norm()
+    return float(d / (analytical.norm() + numerical.norm()).clamp_min(1e-30))
+
+
+def mean_squared_error(analytical: torch.Tensor, numerical: torch.Tensor) -> float:
+    return float(((analytical - numerical) ** 2).mean())
+
+
+def validate_gradient(analytical: torch.Tensor, numerical: torch.Tensor, tolerance: float = 1e-4) -> bool:
+    return analytical.shape == numerical.shape and relative_error(analytical, numerical) <= tolerance
+
+
+# ------------------------------------------------------------------ Hessian
+def hessian_with_options(f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor, options: Optional[HessianOptions] = None) -> HessianResult:
+    o = options or HessianOptions()
+    n = x.numel()
+    if o.indices is not None:
+        H = partial_hessian(f, x, o.indices)
+    else:
+        H = tf.hessian(f)(x).reshape(n, n)
+    if o.symmetrize:
+        H = 0.5 * (H + H.t())
+    if o.regularization:
+        H = H + o.regularization * torch.eye(H.shape[0], dtype=H.dtype, device=H.device)
+    ev = torch.linalg.eigvalsh(H) if o.eigenvalues else None
+    mask = H.abs() > o.sparsity_threshold
+    nnz = int(mask.sum())
+    out = H
+    if o.sparse:
+        idx = mask.nonzero().t()
+        out = torch.sparse_coo_tensor(idx, H[mask], H.shape, check_invariants=False).coalesce()
+    return HessianResult(out, o.sparse, nnz, nnz / max(H.numel(), 1), ev)
+
+
+def partial_hessian(f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor, indices: Sequence[int]) -> torch.Tensor:
+    """The rows and columns ``indices`` (flat coordinates of ``x``) of the Hessian: one Hessian-vector product per index."""
+    idx = list(indices)
+    n = x.numel()
+    if any(not (0 <= i < n) for i in idx):
+        raise IndexError("index outside the input")
+    rows = []
+    for i in idx:
+        e = torch.zeros(n, dtype=x.dtype, device=x.device)
+        e[i] = 1.0
+        rows.append(_hvp(f, x, e.view_as(x)).reshape(-1)[idx])
+    return torch.stack(rows)
+
+
+def hessian_with_eigenvalues(f, x) -> Tuple[torch.Tensor, torch.Tensor]:
+    r = hessian_with_options(f, x, HessianOptions(eigenvalues=True))
+    return r.hessian, r.eigenvalues
+
+
+def sparse_hessian(f, x, threshold: float = 1e-8) -> HessianResult:
+    return hessian_with_options(f, x, HessianOptions(sparse=True, sparsity_threshold=threshold))
+
+
+def regularized_hessian(f, x, regularization: float = 1e-6) -> torch.Tensor:
+    return hessian_with_options(f, x, HessianOptions(regularization=regularization)).hessian
+
+
+def top_eigenvalue(f, x, iters: int = 50, tol: float = 1e-6, seed: int = 0) -> Tuple[float, torch.Tensor]:
+    """Largest-magnitude Hessian eigenvalue by power iteration on Hessian-vector products (no Hessian is formed)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    v = torch.randn(x.shape, generator=g, dtype=x.dtype).to(x.device)
+    v = v / v.norm()
+    lam = 0.0
+    for _ in range(iters):
+        w = _hvp(f, x, v)
+        new = float((v * w).sum())
+        nw = w.norm()
+        if float(nw) == 0.0:
+            return 0.0, v
+        v = w / nw
+        if abs(new - lam) <= tol * max(1.0, abs(new)):
+            lam = new
+            break
+        lam = new
+    return lam, v
+
+
+def grad_of_grad(f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor) -> torch.Tensor:
+    """d/dx of sum(df/dx): the row sums of the Hessian, in one extra backward pass."""
+    return tf.grad(lambda t: tf.grad(f)(t).sum())(x)
+
+
+# ------------------------------------------------------------------ Hessian-vector products
+@dataclass
+class HVPOptions:
+    checkpoint: bool = False         # recompute the gradient graph per product instead of holding it for the batch
+    validate: bool = False
+    tolerance: float = 1e-3
+
+
+def hvp_batch(f, x: torch.Tensor, vectors: Sequence[torch.Tensor], options: Optional[HVPOptions] = None) -> List[torch.Tensor]:
+    """Products with several vectors. Without ``checkpoint`` they are one vectorised sweep (``vmap`` over the tangent);
+    with it they run one at a time, holding one gradient graph at most."""
+    o = options or HVPOptions()
+    if not vectors:
+        return []
+    if o.checkpoint:
+        out = [_hvp(f, x, v) for v in vectors]
+    else:
+        V = torch.stack(list(vectors))
+        out = list(torch.vmap(lambda v: tf.jvp(tf.grad(f), (x,), (v,))[1])(V))
+    if o.validate:
+        for v, r in zip(vectors, out):
+            if not validate_hvp(f, x, v, o.tolerance, analytical=r):
+                raise ArithmeticError("Hessian-vector product differs from finite differences")
+    return out
+
+
+def numerical_hvp(f, x: torch.Tensor, v: torch.Tensor, eps: Optional[float] = None) -> torch.Tensor:
+    """(grad f(x + h v) - grad f(x - h v)) / 2h."""
+    h = eps if eps is not None else float(torch.finfo(x.dtype).eps) ** (1 / 3)
+    g = tf.grad(f)
+    return (g(x + h * v) - g(x - h * v)) / (2 * h)
+
+
+def validate_hvp(f, x, v, tolerance: float = 1e-3, analytical: Optional[torch.Tensor] = None) -> bool:
+    a = analytical if analytical is not None else _hvp(f, x, v)
+    return relative_error(a, numerical_hvp(f, x, v)) <= tolerance
+
+
+# ------------------------------------------------------------------ order tracking
+class HigherOrderContext:
+    """Tracks how deeply differentiation is nested on this thread (``with ctx.order():`` around each level) and caps it;
+    ``create_graph`` is what a backward call inside the block needs: True below the top level."""
+    _tls = threading.local()
+
+    def __init__(self, max_order: int = 4):
+        if max_order < 1:
+            raise ValueError("max_order must be at least 1")
+        self.max_order = max_order
+
+    @property
+    def current_order(self) -> int:
+        return getattr(self._tls, "depth", 0)
+
+    @property
+    def create_graph(self) -> bool:
+        return self.current_order < self.max_order and getattr(self._tls, "want", 1) > self.current_order
+
+    @contextlib.contextmanager
+    def order(self, target_order: Optional[int] = None):
+        d = self.current_order + 1
+        if d > self.max_order:
+            raise RecursionError(f"differentiation order {d} exceeds the limit {self.max_order}")
+        prev_want = getattr(self._tls, "want", 1)
+        if target_order is not None:
+            if target_order > self.max_order:
+                raise RecursionError(f"requested order {target_order} exceeds the limit {self.max_order}")
+            self._tls.want = target_order
+        self._tls.depth = d
+        try:
+            yield d
+        finally:
+            self._tls.depth = d - 1
+            self._tls.want = prev_want
+
+    def nth_derivative(self, f: Callable[[torch.Tensor], torch.Tensor], x: torch.Tensor, n: int) -> torch.Tensor:
+        """n-th derivative of a scalar-to-scalar function applied element-wise (sum trick), n <= max_order."""
+        if n < 0 or n > self.max_order:
+            raise RecursionError(f"order {n} outside [0, {self.max_order}]")
+        g = f
+        for _ in range(n):
+            g = (lambda h: (lambda t: tf.grad(lambda u: h(u).sum())(t)))(g)
+        return g(x)
+
+
+# ------------------------------------------------------------------ function registry
+class FunctionRegistry:
+    """Named custom-function TYPES; ``create_instance`` builds a fresh one per use (functions may keep state)."""
+    _types: Dict[str, Type[CustomFunction]] = {}
+    _lock = threading.Lock()
+
+    @classmethod
+    def register(cls, name: str, fn_type: Type[CustomFunction], overwrite: bool = False):
+        if not (isinstance(fn_type, type) and issubclass(fn_type, CustomFunction)):
+            raise TypeError("expected a CustomFunction subclass")
+        with cls._lock:
+            if name in cls._types and not overwrite:
+                raise KeyError(f"function {name!r} is already registered")
+            cls._types[name] = fn_type
+
+    @classmethod
+    def is_registered(cls, name: str) -> bool:
+        return name in cls._types
+
+    @classmethod
+    def get_function_type(cls, name: str) -> Type[CustomFunction]:
+        if name not in cls._types:
+            raise KeyError(f"no function named {name!r}; registered: {sorted(cls._types)}")
+        return cls._types[name]
+
+    @classmethod
+    def create_instance(cls, name: str, *a, **k) -> CustomFunction:
+        return cls.get_function_type(name)(*a, **k)
+
+    @classmethod
+    def unregister(cls, name: str) -> bool:
+        with cls._lock:
+            return cls._types.pop(name, None) is not None
+
+    @classmethod
+    def names(cls) -> List[str]:
+        return sorted(cls._types)
+
+    @classmethod
+    def clear_all(cls):
+        with cls._lock:
+            cls._types.clear()
+
+    @classmethod
+    def apply_function(cls, name: str, *inputs, init_args: Sequence = ()):
+        return cls.create_instance(name, *init_args).apply(*inputs)
