@@ -130,3 +130,81 @@ def test_header_and_version_routing_traffic_split_and_experiments():
         with it.track("bad"):
             raise RuntimeError("boom")
     assert it.errors["bad"] == 1 and it.errors["ok"] == 0 and it.p("ok", 50) >= 0.002 and it.p("none", 99) == 0.0
+
+
+def test_version_loader_lineage_monitor_and_guarded_swaps():
+    import threading
+    import time
+    import pytest
+    import torch.nn as nn
+    from ml_framework_b200.serving import version_ops as V
+    from ml_framework_b200.serving.deployment import ModelHotSwapper
+
+    loader = V.VersionLoader()
+    info = loader.load_version("clf", "1.0.0", lambda: nn.Linear(4, 2), source="mem://a", stage="prod")
+    loader.load_version("clf", "1.1.0", lambda: nn.Linear(4, 2))
+    assert info.memory_bytes == 4 * (8 + 2) and info.load_seconds >= 0 and info.source == "mem://a" and loader.loaded_versions("clf") == ["1.0.0", "1.1.0"]
+    import torch
+    w = loader.warm_up_version("clf", "1.1.0", [torch.zeros(1, 4)] * 3)
+    assert w.warmed_up and w.warmup_requests == 3 and loader.total_memory_bytes() == 80 and not loader.get_load_info("clf", "1.0.0").warmed_up
+    with pytest.raises(ValueError):
+        loader.load_version("clf", "1.0.0", lambda: None)
+    with pytest.raises(KeyError):
+        loader.get_load_info("clf", "9.9.9")
+
+    lin = V.ModelLineage()
+    lin.tag("clf", "1.0.0", "stable"); lin.tag("clf", "1.1.0", "candidate"); lin.tag("clf", "1.1.0", "stable")
+    assert lin.resolve("clf", "stable") == "1.1.0" and lin.tags_of("clf", "1.1.0") == ["candidate", "stable"] and lin.tags_of("clf", "1.0.0") == []
+    lin.set_parent("clf", "1.1.0", "clf", "1.0.0"); lin.set_parent("clf", "1.2.0", "clf", "1.1.0")
+    assert lin.ancestry("clf", "1.2.0") == [("clf", "1.1.0"), ("clf", "1.0.0")] and lin.children("clf", "1.0.0") == [("clf", "1.1.0")] and lin.parent("clf", "1.0.0") is None
+    with pytest.raises(ValueError):
+        lin.set_parent("clf", "1.0.0", "clf", "1.2.0")
+    assert lin.untag("clf", "candidate") and not lin.untag("clf", "candidate")
+
+    now = {"t": 100.0}
+    mon = V.TimedVersionMonitor(min_samples=10, error_rate_threshold=0.1, latency_p99_ms_threshold=50.0, cooldown_s=30.0, clock=lambda: now["t"])
+    got = []
+    mon.subscribe_to_alerts(got.append)
+    for i in range(20):
+        now["t"] += 1.0
+        mon.record("clf", "1.0.0", latency_ms=10.0 + i % 3, success=True, memory_mb=100.0)
+        mon.record("clf", "1.1.0", latency_ms=8.0 if i < 15 else 200.0, success=i % 4 != 0, memory_mb=90.0)
+    kinds = [(a.type, a.severity) for a in got]
+    assert (V.AlertType.HIGH_ERROR_RATE, V.AlertSeverity.CRITICAL) in kinds and any(t == V.AlertType.HIGH_LATENCY for t, _ in kinds) and all(a.version == "1.1.0" for a in got)
+    assert len([a for a in got if a.type == V.AlertType.HIGH_ERROR_RATE]) == 1                # cooldown
+    m = mon.get_metrics("clf", "1.0.0")
+    assert m.total_requests == 20 and m.error_rate == 0.0 and abs(m.throughput_rps - 1.0) < 1e-9 and m.latency_p50_ms == 11.0
+    early = mon.get_metrics("clf", "1.1.0", V.TimeRange(0, 110.0))
+    assert early.total_requests == 10 and early.latency_p99_ms == 8.0
+    cmp_ = mon.compare_versions("clf", "1.0.0", "1.1.0")
+    assert "error_rate" in cmp_.regressions() and "memory_mean_mb" not in cmp_.regressions() and cmp_.deltas["memory_mean_mb"].improved and not cmp_.v2_is_better
+    assert mon.unsubscribe_from_alerts(got.append) is True and mon.unsubscribe_from_alerts(got.append) is False
+    mon.clear_metrics("clf", "1.1.0")
+    assert mon.get_metrics("clf", "1.1.0").total_requests == 0
+
+    sw = ModelHotSwapper(loader.reg)
+    sw.activate("clf", "1.0.0")
+    g = V.GuardedVersionSwapper(sw, loader, mon, max_error_rate=0.1)
+    assert g.check_version_health("clf", "1.0.0").healthy and not g.check_version_health("clf", "3.0.0").healthy
+    r = g.swap_version("clf", "1.1.0", canary=lambda model: model(torch.zeros(1, 4)).shape == (1, 2))
+    assert r.success and r.from_version == "1.0.0" and r.drained and sw.active["clf"] == "1.1.0" and g.get_swap_status("clf").state == V.SwapState.COMPLETED
+    bad = g.swap_version("clf", "1.0.0", canary=lambda model: 1 / 0)
+    assert not bad.success and "canary raised" in bad.message and sw.active["clf"] == "1.1.0" and g.get_swap_status("clf").state == V.SwapState.FAILED
+    calls = {"n": 0}
+
+    def flaky(model):                      # healthy before the switch, unhealthy on the live path
+        calls["n"] += 1
+        return calls["n"] == 1
+    rb = g.swap_version("clf", "1.0.0", canary=flaky)
+    assert not rb.success and rb.message.startswith("rolled back") and sw.active["clf"] == "1.1.0" and g.get_swap_status("clf").state == V.SwapState.ROLLED_BACK
+    g.increment_in_flight("clf", "1.1.0")
+    t = threading.Timer(0.05, lambda: g.decrement_in_flight("clf", "1.1.0"))
+    t.start()
+    assert g.get_swap_status("clf").in_flight == {"1.1.0": 1} and not g.drain_version("clf", "1.1.0", 0.01) and g.drain_version("clf", "1.1.0", 1.0)
+    with pytest.raises(ValueError):
+        g.decrement_in_flight("clf", "1.1.0")
+    back = g.rollback_version("clf")
+    assert back.success and back.to_version == "1.0.0" and sw.active["clf"] == "1.0.0"
+    assert not g.rollback_version("clf", "7.7.7").success and not V.GuardedVersionSwapper(ModelHotSwapper(loader.reg)).rollback_version("other").success
+    loader.unload_version("clf", "1.1.0")
+    assert not loader.is_version_loaded("clf", "1.1.0") and not g.check_version_health("clf", "1.1.0").healthy
