@@ -475,3 +475,55 @@ def test_tokenizers_request_tracker_and_batch_builder_pieces():
     assert isinstance(fs[0].exception(), RuntimeError)
     s = I.SchedulerStatistics.from_snapshot({"requests_completed": 5, "iteration_ms_p50": 4.5, "errors": 1})
     assert s.completed_requests == 5 and s.p50_iteration_ms == 4.5 and s.errors == 1 and I.SchedulerStatus(1, 2, 3, 0.5).is_running
+
+
+def test_paged_kernel_interface_and_orchestrators():
+    import pytest as _p
+    from ml_framework_b200.ops import reference
+    from ml_framework_b200.serving import paged_kernels as PK
+    from ml_framework_b200.serving.kv_cache import KVCacheBlockManager
+    from ml_framework_b200.serving.paged_attention_layer import AttentionPhase, PagedAttentionLayer
+    torch.manual_seed(0)
+    B, Q, C, H, Hkv, D = 2, 3, 7, 4, 2, 8
+    q, k, v = torch.randn(B, Q, H, D), torch.randn(B, C, Hkv, D), torch.randn(B, C, Hkv, D)
+    std, fused = PK.create_kernel("standard"), PK.create_kernel("fused")
+    a = std.compute_paged_attention(q, k, v, AttentionPhase.DECODE)
+    want, _ = reference.attention_ref(q.float(), k.float(), v.float(), causal=True, start_pos=C - Q)
+    assert torch.allclose(a, want, atol=1e-5) and torch.allclose(fused.compute_paged_attention(q, k, v, AttentionPhase.DECODE), a, atol=1e-5)
+    one = std.compute_paged_attention(q[:, :1], k, v, AttentionPhase.DECODE, scale=0.5)
+    s = PK.StandardPagedAttentionKernel
+    w = s.softmax(s.scale_tensor(s.matmul_query_key(q[:, :1], k), 0.5))
+    assert torch.allclose(one, s.matmul_weight_value(w, v), atol=1e-6) and torch.allclose(w.sum(-1), torch.ones(B, H, 1))
+    assert torch.allclose(fused.compute_paged_attention(q[:, :1], k, v, AttentionPhase.DECODE, scale=0.5), one, atol=1e-5)
+    m = s.apply_causal_mask(torch.zeros(1, 1, 2, 4), start_pos=1)
+    assert torch.isinf(m[0, 0, 0, 2:]).all() and torch.isfinite(m[0, 0, 1, :3]).all() and torch.isinf(m[0, 0, 1, 3])
+    assert isinstance(PK.create_kernel("auto"), PK.StandardPagedAttentionKernel)
+    for bad in (lambda: std.compute_paged_attention(q[0], k, v), lambda: std.compute_paged_attention(q, k, v[:, :5]), lambda: std.compute_paged_attention(torch.randn(B, Q, 3, D), k, v)):
+        with _p.raises(ValueError):
+            bad()
+    with _p.raises(KeyError):
+        PK.create_kernel("metal")
+
+    d = 32
+    layer = PagedAttentionLayer(d, 4, 2, 8, rope_theta=10000.0)
+    kv = KVCacheBlockManager(total_blocks=8, block_size=4, head_dim=8, num_layers=1, num_kv_heads=2, dtype=torch.float32, device="cpu")
+    pre, dec = PK.PrefillOrchestrator(kv, chunk_size=4), PK.DecodeOrchestrator(kv)
+    x = torch.randn(10, d)
+    assert pre.blocks_for(10) == 3 and pre.prefill_allocate_blocks(1, 10) and not pre.prefill_allocate_blocks(2, 100)
+    whole = PK.PrefillOrchestrator(KVCacheBlockManager(total_blocks=8, block_size=4, head_dim=8, num_layers=1, num_kv_heads=2, dtype=torch.float32, device="cpu"))
+    ref_out = whole.compute_prefill_attention(layer, x, 1)
+    out = pre.compute_prefill_attention(layer, x, 1)                       # three chunks
+    assert torch.allclose(out, ref_out, atol=1e-5) and kv.get_sequence_length(1) == 10
+    assert not dec.needs_new_block(1) and dec.allocate_decode_block(1)
+    y = dec.compute_decode_attention(layer, torch.randn(1, d), 1)
+    assert y.shape == (1, d) and kv.get_sequence_length(1) == 11
+    outs = pre.batch_prefill(layer, [torch.randn(3, d), torch.randn(4, d)], [5, 6])
+    assert [o.shape[0] for o in outs] == [3, 4] and dec.needs_new_block(6)
+    yb = dec.batch_decode(layer, torch.randn(3, d), [1, 5, 6])
+    assert yb.shape == (3, d) and kv.get_sequence_length(6) == 5
+    with _p.raises(MemoryError):
+        pre.batch_prefill(layer, [torch.randn(20, d)], [9])
+    with _p.raises(ValueError):
+        dec.compute_decode_attention(layer, torch.randn(2, d), 1)
+    with _p.raises(ValueError):
+        pre.prefill_allocate_blocks(3, 0)
