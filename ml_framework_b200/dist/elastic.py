@@ -20,8 +20,8 @@ from __future__ import annotations
 import enum
 import math
 import time
-from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional, Tuple
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 
 class WorkerStatus(enum.Enum):
@@ -410,3 +410,142 @@ class ElasticCheckpointManager:
                 return None
             self.latest = tags[-1]
         return self.ckpt.load(self.latest, device=device)
+
+
+# ------------------------------------------------------------------ state records and plan execution
+@dataclass
+class DataShard:
+    shard_id: int
+    start_index: int
+    end_index: int
+
+    @property
+    def size(self) -> int:
+        return self.end_index - self.start_index
+
+    @staticmethod
+    def split(dataset_size: int, world: int) -> List["DataShard"]:
+        return [DataShard(r, *DataRedistributor.shard_range(dataset_size, world, r)) for r in range(world)]
+
+
+@dataclass
+class WorkerMetadata:
+    """What the cluster knows about a worker beyond its status (src/MLFramework/Distributed/Models/WorkerMetadata.cs)."""
+    worker_id: str
+    status: WorkerStatus
+    join_time: float
+    last_heartbeat: float
+    rank: int = -1
+    local_world_size: int = 1
+    custom_attributes: Dict[str, str] = field(default_factory=dict)
+
+    def is_healthy(self, timeout_s: float, now: Optional[float] = None) -> bool:
+        return self.status not in (WorkerStatus.FAILED, WorkerStatus.LEAVING) and ((now if now is not None else time.time()) - self.last_heartbeat) <= timeout_s
+
+
+@dataclass
+class GlobalTrainingState:
+    """The state every worker must agree on after a rescale (Models/GlobalTrainingState.cs)."""
+    current_epoch: int = 0
+    current_step: int = 0
+    learning_rate: float = 0.0
+    global_batch_size: int = 0
+    active_worker_count: int = 0
+    consumed_samples: int = 0
+    state_timestamp: float = field(default_factory=time.time)
+    optimizer_state: Optional[bytes] = None
+
+    def to_json(self) -> str:
+        import base64
+        import json
+        d = dict(self.__dict__)
+        d["optimizer_state"] = base64.b64encode(self.optimizer_state).decode() if self.optimizer_state is not None else None
+        return json.dumps(d)
+
+    @staticmethod
+    def from_json(text: str) -> "GlobalTrainingState":
+        import base64
+        import json
+        d = json.loads(text)
+        if d.get("optimizer_state") is not None:
+            d["optimizer_state"] = base64.b64decode(d["optimizer_state"])
+        return GlobalTrainingState(**d)
+
+    def after_rescale(self, new_world: int, lr: Optional[float] = None, per_worker_batch: Optional[int] = None) -> "GlobalTrainingState":
+        """The state the new topology starts from: same progress, new worker count (and batch / rate when given)."""
+        pw = per_worker_batch if per_worker_batch is not None else (self.global_batch_size // self.active_worker_count if self.active_worker_count else 0)
+        return GlobalTrainingState(self.current_epoch, self.current_step, lr if lr is not None else self.learning_rate, pw * new_world, new_world,
+                                   self.consumed_samples, time.time(), self.optimizer_state)
+
+
+@dataclass
+class SamplerState:
+    """Position of an elastic sampler, enough to rebuild it on any topology (Data/SamplerState.cs)."""
+    dataset_size: int
+    worker_count: int
+    worker_rank: int
+    epoch: int
+    consumed: int
+    seed: int
+    shuffle: bool
+    drop_last: bool
+
+    @staticmethod
+    def capture(sampler) -> "SamplerState":
+        return SamplerState(sampler.dataset_size, sampler.num_replicas, sampler.rank, sampler.epoch, getattr(sampler, "consumed", 0), sampler.seed,
+                            sampler.shuffle, sampler.drop_last)
+
+    def restore(self, worker_count: Optional[int] = None, worker_rank: Optional[int] = None):
+        """A sampler at the recorded position; with a new ``worker_count`` / ``worker_rank`` the remaining samples of the
+        epoch are re-split over the new topology."""
+        from ..data.samplers import ElasticDistributedSampler
+        W = worker_count if worker_count is not None else self.worker_count
+        r = worker_rank if worker_rank is not None else self.worker_rank
+        s = ElasticDistributedSampler(self.dataset_size, W, r, self.shuffle, self.seed, self.drop_last)
+        s.set_epoch(self.epoch)
+        s.consumed = self.consumed
+        if self.consumed or W != self.worker_count:
+            s.update_topology(W, r)
+        return s
+
+
+class DataTransferManager:
+    """Carries out a redistribution plan: every transfer is ``copy(transfer)`` (whatever moves samples between ranks:
+    a file copy, a point-to-point send, nothing at all for a shared file system), at most ``max_concurrent`` at a time,
+    each retried up to ``max_retries`` times; the outcome per transfer is kept (Data/DataTransferManager.cs:12-20)."""
+
+    def __init__(self, max_concurrent_transfers: int = 4, max_retries: int = 2):
+        if max_concurrent_transfers <= 0:
+            raise ValueError("max_concurrent_transfers must be positive")
+        self.max_concurrent, self.max_retries = max_concurrent_transfers, max_retries
+        self.completed: List[DataTransfer] = []
+        self.failed: List[Tuple[DataTransfer, str]] = []
+        self.bytes_moved = 0
+
+    def execute_plan(self, plan: Sequence[DataTransfer], copy: Callable[[DataTransfer], Optional[int]], only_rank: Optional[int] = None,
+                     cancel: Optional[Callable[[], bool]] = None) -> bool:
+        """``only_rank``: run just the transfers this rank takes part in. Returns True when every transfer succeeded."""
+        from concurrent.futures import ThreadPoolExecutor
+        todo = [t for t in plan if only_rank is None or only_rank in (t.src_rank, t.dst_rank)]
+
+        def one(t: DataTransfer):
+            err = ""
+            for _ in range(self.max_retries + 1):
+                if cancel is not None and cancel():
+                    return t, None, "cancelled"
+                try:
+                    return t, copy(t), ""
+                except Exception as e:       # noqa: BLE001 - retried, then reported
+                    err = str(e)
+            return t, None, err
+        with ThreadPoolExecutor(max_workers=self.max_concurrent, thread_name_prefix="mlf-data-transfer") as ex:
+            for t, moved, err in ex.map(one, todo):
+                if err:
+                    self.failed.append((t, err))
+                else:
+                    self.completed.append(t)
+                    self.bytes_moved += int(moved or 0)
+        return not self.failed
+
+    def progress(self, plan_size: int) -> float:
+        return (len(self.completed) + len(self.failed)) / plan_size if plan_size else 1.0

@@ -209,3 +209,55 @@ def test_learning_rate_transition_manager_and_health_timer():
     with _p.raises(ElasticError):
         co.raise_timer_error()
     co.raise_timer_error()                               # reported once
+
+
+def test_elastic_state_records_sampler_state_and_transfer_manager():
+    import threading
+    from ml_framework_b200.data.samplers import ElasticDistributedSampler
+    from ml_framework_b200.dist import elastic as E
+    shards = E.DataShard.split(10, 3)
+    assert [(s.start_index, s.end_index, s.size) for s in shards] == [(0, 4, 4), (4, 8, 4), (8, 10, 2)]
+    wm = E.WorkerMetadata("w0", E.WorkerStatus.ACTIVE, 0.0, 100.0, rank=0, custom_attributes={"zone": "a"})
+    assert wm.is_healthy(10.0, now=105.0) and not wm.is_healthy(10.0, now=120.0)
+    wm.status = E.WorkerStatus.FAILED
+    assert not wm.is_healthy(10.0, now=100.0)
+    st = E.GlobalTrainingState(2, 500, 3e-4, 64, 4, consumed_samples=1200, optimizer_state=b"\x00\x01")
+    back = E.GlobalTrainingState.from_json(st.to_json())
+    assert back.current_step == 500 and back.optimizer_state == b"\x00\x01" and back.learning_rate == 3e-4
+    nxt = st.after_rescale(6, lr=4.5e-4)
+    assert (nxt.global_batch_size, nxt.active_worker_count, nxt.learning_rate, nxt.current_step, nxt.consumed_samples) == (96, 6, 4.5e-4, 500, 1200)
+    assert st.after_rescale(2, per_worker_batch=8).global_batch_size == 16
+
+    s = ElasticDistributedSampler(100, 4, 1, shuffle=True, seed=3)
+    s.set_epoch(2)
+    s.record_consumed(40)
+    snap = E.SamplerState.capture(s)
+    assert (snap.worker_count, snap.worker_rank, snap.epoch, snap.consumed) == (4, 1, 2, 40)
+    parts = [list(snap.restore(worker_count=3, worker_rank=r)) for r in range(3)]
+    s.update_topology(4, 1)
+    assert sorted(i for p in parts for i in p) == sorted(list(snap.restore(4, 0)) + list(snap.restore(4, 1)) + list(snap.restore(4, 2)) + list(snap.restore(4, 3)))
+    assert len({i for p in parts for i in p}) == 60 and list(snap.restore()) == list(s)
+
+    plan = E.DataRedistributor().calculate_plan(100, 4, 2)
+    mgr = E.DataTransferManager(max_concurrent_transfers=2, max_retries=1)
+    attempts, lock = {}, threading.Lock()
+
+    def copy(t):
+        with lock:
+            attempts[(t.src_rank, t.dst_rank)] = attempts.get((t.src_rank, t.dst_rank), 0) + 1
+            n = attempts[(t.src_rank, t.dst_rank)]
+        if t.src_rank == 3 and n == 1:
+            raise OSError("transient")
+        if t.src_rank == 2:
+            raise OSError("gone")
+        return (t.end - t.start) * 4
+    ok = mgr.execute_plan(plan, copy)
+    assert not ok and [t.src_rank for t, _ in mgr.failed] == [2] and mgr.failed[0][1] == "gone" and attempts[(3, 1)] == 2 and attempts[(2, 1)] == 2
+    assert mgr.bytes_moved == sum((t.end - t.start) * 4 for t in mgr.completed) and mgr.progress(len(plan)) == 1.0
+    mine = E.DataTransferManager()
+    assert mine.execute_plan(plan, lambda t: 0, only_rank=0) and all(0 in (t.src_rank, t.dst_rank) for t in mine.completed)
+    stop = E.DataTransferManager()
+    assert not stop.execute_plan(plan, lambda t: 0, cancel=lambda: True) and all(e == "cancelled" for _, e in stop.failed)
+    import pytest as _p
+    with _p.raises(ValueError):
+        E.DataTransferManager(0)
