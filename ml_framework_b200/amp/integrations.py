@@ -18,7 +18,7 @@ from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tupl
 
 import torch
 
-from .autocast import AmpConfig, AmpRegistry, AutoCast, OpPrecision
+from .autocast import AmpConfig, AutoCast, OpPrecision
 from .grad_scaler import DynamicLossScaler, GradScaler, StaticLossScaler
 
 LOW_PRECISION = (torch.float16, torch.bfloat16)

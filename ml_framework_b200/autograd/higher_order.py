@@ -16,8 +16,8 @@ from __future__ import annotations
 import contextlib
 import enum
 import threading
-from dataclasses import dataclass, field
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Type
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Sequence, Tuple, Type
 
 import torch
 import torch.func as tf

@@ -13,12 +13,11 @@ import enum
 import hashlib
 import os
 from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .distributed import (FORMAT_VERSION, CheckpointError, CheckpointLoader, CheckpointMetadata, DistributedCheckpoint, LoadOptions,
-                          MetadataValidator, MultiShardCheckpointFormat, ReshardingStrategy, SaveOptions, manifest_path)
+from .distributed import (FORMAT_VERSION, CheckpointError, CheckpointMetadata, DistributedCheckpoint, LoadOptions, MetadataValidator, MultiShardCheckpointFormat, ReshardingStrategy, SaveOptions, manifest_path)
 
 
 class CheckpointFormat(enum.Enum):

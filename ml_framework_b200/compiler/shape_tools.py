@@ -10,8 +10,7 @@ Tensors/TensorShapeRegistry.cs:44-148 (dimension-name bindings).
 from __future__ import annotations
 
 import enum
-from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 

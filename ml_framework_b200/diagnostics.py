@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import contextlib
 import threading
-from dataclasses import dataclass, field, fields
+from dataclasses import dataclass, fields
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
 import torch

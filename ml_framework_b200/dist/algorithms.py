@@ -13,11 +13,11 @@ is handed back.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .fault_tolerance import AlgorithmSelector, ChunkManager, CollectiveAlgorithm, RingAllReduce
+from .fault_tolerance import AlgorithmSelector, CollectiveAlgorithm, RingAllReduce
 from .process_group import ReduceOp
 
 

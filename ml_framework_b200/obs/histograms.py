@@ -8,8 +8,8 @@ inter-quartile rules, dead-neuron count)}. Statistics are computed with tensor o
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 

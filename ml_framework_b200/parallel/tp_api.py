@@ -10,7 +10,7 @@ TensorParallelMeshContext.cs:39-58, TPMeshLayerFactory.cs (returns placeholder l
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Optional
 
 import torch
 import torch.nn as nn

@@ -17,8 +17,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .core import (Calibrator, FakeQuantize, MinMaxCalibrator, PTQQuantizer, QATLinear, QuantizationMode, QuantizationParameters, QuantizedLinear,
-                   compute_qparams, convert_qat, dequantize, mae, prepare_qat, quantize, rmse, sqnr_db, top_k_accuracy)
+from .core import (Calibrator, FakeQuantize, MinMaxCalibrator, PTQQuantizer, QuantizationMode, QuantizationParameters, QuantizedLinear, compute_qparams, dequantize, mae, quantize, rmse, sqnr_db, top_k_accuracy)
 
 
 # ------------------------------------------------------------------ per-channel helpers

@@ -9,7 +9,7 @@ from __future__ import annotations
 import threading
 import time
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Deque, Dict, Generic, List, Optional, Protocol, Sequence, Tuple, TypeVar, runtime_checkable
 
 T = TypeVar("T")

@@ -14,7 +14,7 @@ the oracle the GPU kernels are checked against.
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 
