@@ -42,17 +42,24 @@ class ProcessLauncher:
         self.ranks: List[RankProcess] = []
         self._failed_first: Optional[RankProcess] = None   # the rank whose non-zero exit was observed first
 
-    def launch(self, argv: Sequence[str], num_processes: int, extra_env: Optional[Dict[str, str]] = None) -> List[RankProcess]:
+    def launch(self, argv: Sequence[str], num_processes: int, extra_env: Optional[Dict[str, str]] = None, rank_offset: int = 0,
+               world_size: Optional[int] = None) -> List[RankProcess]:
+        """Starts ``num_processes`` local ranks. On one node of a multi-node job ``rank_offset`` is the global rank of
+        this node's first process and ``world_size`` the job's total; ``LOCAL_RANK`` always counts from zero."""
         if num_processes <= 0:
             raise ValueError("num_processes must be positive")
+        world = num_processes if world_size is None else world_size
+        if rank_offset < 0 or rank_offset + num_processes > world:
+            raise ValueError(f"ranks {rank_offset}..{rank_offset + num_processes - 1} do not fit a world of {world}")
         if self.log_dir:
             self.log_dir.mkdir(parents=True, exist_ok=True)
-        for rank in range(num_processes):
+        for local in range(num_processes):
+            rank = rank_offset + local
             env = dict(os.environ)
-            env.update({"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(num_processes),
+            env.update({"RANK": str(rank), "LOCAL_RANK": str(local), "WORLD_SIZE": str(world), "LOCAL_WORLD_SIZE": str(num_processes),
                         "MASTER_ADDR": self.master_addr, "MASTER_PORT": str(self.master_port)})
             if self.assign_gpus:
-                env["CUDA_VISIBLE_DEVICES"] = str(rank)
+                env["CUDA_VISIBLE_DEVICES"] = str(local)
                 env["LOCAL_RANK"] = "0"
             if extra_env:
                 env.update(extra_env)
@@ -139,6 +146,22 @@ def launch_local(script: str, num_processes: int, script_args: Sequence[str] = (
     return launcher
 
 
-def launch_multi_node(*_a, **_k):
-    raise NotImplementedError("use torchrun (--nnodes, --rdzv-endpoint) for multi-node jobs; every rank then calls "
-                              "init_process_group() which reads the torchrun environment")
+def launch_multi_node(script: str, nnodes: int, node_rank: int, nproc_per_node: int, master_addr: str, master_port: int = 29500,
+                      script_args: Sequence[str] = (), log_dir: Optional[str] = None, assign_gpus: bool = False,
+                      timeout_s: Optional[float] = None, extra_env: Optional[Dict[str, str]] = None) -> ProcessLauncher:
+    """This node's share of a multi-node job: run the same call on every node with its own ``node_rank`` (0 .. nnodes-1)
+    and the address of node 0. Local processes get global ranks ``node_rank * nproc_per_node + local``; rendezvous is
+    the TCP store at ``master_addr:master_port`` that ``init_process_group`` opens. (The reference's
+    ``LaunchMultiNode`` is a NotImplemented stub: src/MLFramework/Distributed/DistributedLauncher.cs:76-122.)"""
+    if nnodes <= 0 or not (0 <= node_rank < nnodes) or nproc_per_node <= 0:
+        raise ValueError(f"invalid layout: {nnodes} nodes, node rank {node_rank}, {nproc_per_node} processes per node")
+    launcher = ProcessLauncher(master_addr=master_addr, master_port=master_port, log_dir=log_dir, assign_gpus=assign_gpus)
+    env = {"GROUP_RANK": str(node_rank), "NNODES": str(nnodes)}
+    env.update(extra_env or {})
+    launcher.launch([sys.executable, script, *script_args], nproc_per_node, env, rank_offset=node_rank * nproc_per_node,
+                    world_size=nnodes * nproc_per_node)
+    if not launcher.wait_for_all(timeout_s):
+        bad = launcher.first_failed_process()
+        raise DistributedTrainingError(f"node {node_rank}: rank {bad.rank if bad else '?'} failed with exit code {bad.exit_code if bad else '?'}",
+                                       bad.rank if bad else None, bad.exit_code if bad else None)
+    return launcher

@@ -100,8 +100,10 @@ def test_launcher_env_logs_and_first_failure(tmp_path):
         launch_local(str(script), 2, ["fail"], log_dir=str(tmp_path / "logs2"), master_port=29612)
     assert e.value.rank == 1 and e.value.exit_code == 3
     from ml_framework_b200.dist.launcher import launch_multi_node
-    with pytest.raises(NotImplementedError):
-        launch_multi_node()
+    with pytest.raises(ValueError):
+        launch_multi_node(str(script), nnodes=2, node_rank=2, nproc_per_node=1, master_addr="127.0.0.1")
+    with pytest.raises(ValueError):
+        ProcessLauncher().launch(["true"], 2, rank_offset=3, world_size=4)
 
 
 @pytest.mark.timeout(360)
@@ -230,3 +232,44 @@ def test_static_grad_scaler_through_the_grad_scaler_api():
     assert not gs.prepare_gradients([torch.tensor([float("nan")])])
     gs.update()
     assert gs.scaler.get_stats().skipped_steps == 1
+
+
+@pytest.mark.timeout(300)
+def test_two_emulated_nodes_rendezvous_and_all_reduce(tmp_path):
+    """Two ``launch_multi_node`` calls on this machine stand for two nodes (two processes each): global ranks, local ranks
+    and the world size come out right and a gloo all-reduce spans all four."""
+    import threading
+    from ml_framework_b200.dist.launcher import launch_multi_node
+    script = tmp_path / "node.py"
+    script.write_text(
+        "import json, os, sys\n"
+        f"sys.path.insert(0, {ROOT!r})\n"
+        "import torch\n"
+        "from ml_framework_b200.dist.process_group import BackendType, destroy_process_group, init_process_group\n"
+        "pg = init_process_group(BackendType.GLOO)\n"
+        "t = torch.tensor([float(pg.rank)])\n"
+        "pg.all_reduce(t)\n"
+        "print(json.dumps({'rank': pg.rank, 'local': int(os.environ['LOCAL_RANK']), 'world': pg.world_size, 'node': int(os.environ['GROUP_RANK']), 'sum': float(t)}))\n"
+        "destroy_process_group()\n")
+    port = _free_port()
+    errs = []
+
+    def node(k):
+        try:
+            launch_multi_node(str(script), nnodes=2, node_rank=k, nproc_per_node=2, master_addr="127.0.0.1", master_port=port,
+                              log_dir=str(tmp_path / f"node{k}"), timeout_s=120)
+        except Exception as e:       # noqa: BLE001
+            errs.append(e)
+    ts = [threading.Thread(target=node, args=(k,)) for k in range(2)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(200)
+    assert not errs, errs
+    rows = []
+    for k in range(2):
+        for r in (2 * k, 2 * k + 1):
+            log = (tmp_path / f"node{k}" / f"rank_{r}.log").read_text()
+            rows.append(json.loads([ln for ln in log.splitlines() if ln.startswith("{")][-1]))
+    assert sorted((x["rank"], x["local"], x["node"]) for x in rows) == [(0, 0, 0), (1, 1, 0), (2, 0, 1), (3, 1, 1)]
+    assert all(x["world"] == 4 and x["sum"] == 6.0 for x in rows)
