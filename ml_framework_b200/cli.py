@@ -48,7 +48,10 @@ def _bench(a):
 
 
 def _launch(a):
-    from .dist.launcher import launch_local
+    from .dist.launcher import launch_local, launch_multi_node
+    if a.nnodes > 1:
+        rc = launch_multi_node(a.script, a.nnodes, a.node_rank, a.nproc, a.master_addr, a.port, a.script_args)
+        return
     rc = launch_local(a.script, a.nproc, a.script_args, master_port=a.port)
     sys.exit(rc if isinstance(rc, int) else 0)
 
@@ -77,6 +80,7 @@ def main(argv=None):
     s.add_argument("--max-batch", type=int, default=16); s.add_argument("--device", default="cpu"); s.set_defaults(fn=_serve)
     b = sub.add_parser("bench"); b.add_argument("what", choices=["gemm", "gemm_epi", "gemm_decode", "attn", "paged", "elementwise"]); b.add_argument("--json", default=None); b.set_defaults(fn=_bench)
     l = sub.add_parser("launch"); l.add_argument("--nproc", type=int, required=True); l.add_argument("--port", type=int, default=29500)
+    l.add_argument("--nnodes", type=int, default=1); l.add_argument("--node-rank", type=int, default=0); l.add_argument("--master-addr", default="127.0.0.1")
     l.add_argument("script"); l.add_argument("script_args", nargs=argparse.REMAINDER); l.set_defaults(fn=_launch)
     c = sub.add_parser("convert"); c.add_argument("-i", "--input", required=True); c.add_argument("-o", "--output", required=True)
     c.add_argument("-q", "--quantize", choices=["int8", "uint8", "fp16"], default=None); c.add_argument("-v", "--verbose", action="store_true"); c.set_defaults(fn=_convert)

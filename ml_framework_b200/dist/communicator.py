@@ -234,3 +234,94 @@ class ProcessGroupManager:
 
     def names(self) -> List[str]:
         return sorted(self._groups)
+
+
+# ------------------------------------------------------------------ MPI-style facade
+@dataclass
+class MPIConfig:
+    """src/MLFramework/Communication/Backends/MPIConfig.cs: CUDA-aware transfers, thread level, eager buffer size."""
+    use_cuda_aware: bool = True          # device tensors are sent as they are (NCCL p2p); False stages them through the host
+    thread_level: str = "multiple"       # single | funneled | serialized | multiple
+    buffer_size: int = 64 * 1024
+
+    def validate(self):
+        if self.thread_level not in ("single", "funneled", "serialized", "multiple"):
+            raise ValueError(f"unknown thread level {self.thread_level!r}")
+        if self.buffer_size <= 0:
+            raise ValueError("buffer_size must be positive")
+
+
+class MPIStyleBackend:
+    """The reference's MPI back-end surface (collectives plus ``send`` / ``receive`` / ``probe`` / async variants:
+    Communication/Backends/MPIBackend.cs:54-218) on this package's process groups. No MPI library is involved: the
+    point-to-point calls are the group's (NCCL or gloo), messages carry a small header so that ``receive`` can size its
+    buffer and ``probe`` can look before it takes."""
+    name = "mpi"
+
+    def __init__(self, pg, config: Optional[MPIConfig] = None):
+        self.pg, self.cfg = pg, config or MPIConfig()
+        self.cfg.validate()
+
+    @property
+    def rank(self) -> int:
+        return self.pg.rank
+
+    @property
+    def world_size(self) -> int:
+        return self.pg.world_size
+
+    def _stage(self, t: torch.Tensor) -> torch.Tensor:
+        return t if self.cfg.use_cuda_aware or not t.is_cuda else t.cpu()
+
+    # ---- collectives
+    def broadcast(self, t: torch.Tensor, root: int = 0) -> torch.Tensor:
+        self.pg.broadcast(t, root)
+        return t
+
+    def reduce(self, t: torch.Tensor, root: int = 0, op: ReduceOp = ReduceOp.SUM) -> torch.Tensor:
+        self.pg.reduce(t, root, op)
+        return t
+
+    def all_reduce(self, t: torch.Tensor, op: ReduceOp = ReduceOp.SUM) -> torch.Tensor:
+        self.pg.all_reduce(t, op)
+        return t
+
+    def all_gather(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        return self.pg.all_gather(t, dim)
+
+    def reduce_scatter(self, t: torch.Tensor, op: ReduceOp = ReduceOp.SUM, dim: int = 0) -> torch.Tensor:
+        return self.pg.reduce_scatter(t, op, dim)
+
+    def barrier(self):
+        self.pg.barrier()
+
+    # ---- point to point
+    def send(self, t: torch.Tensor, dst: int, tag: int = 0):
+        send_with_header(self.pg, self._stage(t), dst, tag)
+
+    def probe(self, src: int, tag: int = 0, device="cpu") -> MessageInfo:
+        return probe(self.pg, src, tag, device)
+
+    def receive(self, src: int, tag: int = 0, device="cpu", info: Optional[MessageInfo] = None) -> torch.Tensor:
+        """The next message from ``src`` (its shape and dtype come from the header, or from an earlier ``probe``)."""
+        info = info or self.probe(src, tag, "cpu" if not self.cfg.use_cuda_aware else device)
+        t = recv_probed(self.pg, info, "cpu" if not self.cfg.use_cuda_aware else device)
+        return t.to(device)
+
+    def send_async(self, t: torch.Tensor, dst: int, tag: int = 0):
+        import concurrent.futures as cf
+        ex = cf.ThreadPoolExecutor(max_workers=1)
+        f = ex.submit(self.send, t, dst, tag)
+        ex.shutdown(wait=False)
+        return f
+
+    def receive_async(self, src: int, tag: int = 0, device="cpu"):
+        import concurrent.futures as cf
+        ex = cf.ThreadPoolExecutor(max_workers=1)
+        f = ex.submit(self.receive, src, tag, device)
+        ex.shutdown(wait=False)
+        return f
+
+    def send_receive(self, t: torch.Tensor, dst: int, src: int) -> torch.Tensor:
+        """Exchange of equal-shaped tensors (both directions in flight at once)."""
+        return send_recv(self.pg, self._stage(t), dst, torch.empty_like(self._stage(t)), src).to(t.device)

@@ -122,3 +122,38 @@ def test_profiler_pinned_pool_queue_and_overlap_helper():
         return [t.item() for t in ts], res, red.item(), outs
     out = run_fake_world(2, body)
     assert out[0] == ([1.0, 3.0, 5.0], "computed", 2.0, [0, 1, 4]) and out[1][0] == [1.0, 3.0, 5.0]
+
+
+def test_mpi_style_backend_on_simulated_ranks():
+    import pytest as _p
+    import torch
+    from ml_framework_b200.dist.communicator import MPIConfig, MPIStyleBackend
+    from ml_framework_b200.dist.process_group import ReduceOp, run_fake_world
+
+    def run(pg):
+        mpi = MPIStyleBackend(pg, MPIConfig(use_cuda_aware=False))
+        out = {}
+        if pg.rank == 0:
+            mpi.send(torch.arange(6, dtype=torch.int32).view(2, 3), 1, tag=7)
+            out["echo"] = mpi.receive(1, tag=8)
+        else:
+            info = mpi.probe(0, tag=7)
+            out["info"] = (info.shape, info.dtype, info.count)
+            got = mpi.receive(0, tag=7, info=info)
+            mpi.send_async(got.float() * 2, 0, tag=8).result(10)
+        out["xchg"] = mpi.send_receive(torch.full((2,), float(pg.rank)), 1 - pg.rank, 1 - pg.rank)
+        out["ar"] = mpi.all_reduce(torch.ones(2))
+        out["ag"] = mpi.all_gather(torch.full((1,), float(pg.rank)))
+        out["rs"] = mpi.reduce_scatter(torch.arange(4.0), ReduceOp.SUM)
+        out["bc"] = mpi.broadcast(torch.full((1,), float(pg.rank + 3)), root=1)
+        out["red"] = mpi.reduce(torch.ones(1), 0)
+        mpi.barrier()
+        return out
+    r0, r1 = run_fake_world(2, run)
+    assert r1["info"] == ((2, 3), torch.int32, 6) and r0["echo"].tolist() == [[0.0, 2.0, 4.0], [6.0, 8.0, 10.0]]
+    assert r0["xchg"].tolist() == [1.0, 1.0] and r1["xchg"].tolist() == [0.0, 0.0] and r0["ar"].tolist() == [2.0, 2.0] and r0["ag"].tolist() == [0.0, 1.0]
+    assert r1["rs"].tolist() == [4.0, 6.0] and r0["bc"].tolist() == [4.0] and r0["red"].tolist() == [2.0]
+    with _p.raises(ValueError):
+        MPIConfig(thread_level="many").validate()
+    with _p.raises(ValueError):
+        MPIConfig(buffer_size=0).validate()
