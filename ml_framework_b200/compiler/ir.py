@@ -156,6 +156,20 @@ def _execute(o: Op, x: List[torch.Tensor]) -> torch.Tensor:
     if k.endswith("_scalar"):     # a binary op whose constant scalar operand was inlined into the attributes
         c = torch.tensor(a["scalar"], dtype=x[0].dtype, device=x[0].device)
         return _execute(Op(k[:-7], [], ""), [c, x[0]] if a.get("scalar_side") == "lhs" else [x[0], c])
+    # ---- ops that only gradient graphs produce (compiler/autodiff.py)
+    if k == "ones_like": return torch.ones_like(x[0])
+    if k == "broadcast_to": return x[0].reshape(a["view"]).expand(a["shape"]).contiguous() if "view" in a else x[0].expand(a["shape"]).contiguous()
+    if k == "sum_to": return x[0].sum_to_size(a["shape"]) if tuple(x[0].shape) != tuple(a["shape"]) else x[0]
+    if k == "scale": return x[0] * a["factor"]
+    if k == "pow": return torch.pow(x[0], a["exponent"])
+    if k == "relu_grad": return x[0] * (x[1] > 0).to(x[0].dtype)
+    if k == "sigmoid_grad": return x[0] * x[1] * (1 - x[1])                    # (upstream, sigmoid output)
+    if k == "tanh_grad": return x[0] * (1 - x[1] * x[1])                        # (upstream, tanh output)
+    if k == "gelu_grad":
+        g, t = x[0], x[1].detach().clone().requires_grad_(True)
+        with torch.enable_grad():
+            (d,) = torch.autograd.grad(F.gelu(t, approximate="tanh").sum(), t)
+        return g * d
     if k == "add": return x[0] + x[1]
     if k == "sub": return x[0] - x[1]
     if k == "mul": return x[0] * x[1]
