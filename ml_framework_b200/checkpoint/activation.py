@@ -189,3 +189,77 @@ def apply_activation_checkpointing(layers: nn.ModuleList, manager: Optional[Chec
             layers[i] = CheckpointedModuleWrapper(layer)
             n += 1
     return n
+
+
+# ------------------------------------------------------------------ scopes and selective wrapping
+import contextlib as _contextlib
+import threading as _threading
+
+_scope = _threading.local()
+
+
+@_contextlib.contextmanager
+def checkpoint_scope(enabled: bool = True):
+    """Inside the block ``maybe_checkpoint`` recomputes; outside it runs the function normally. Scopes nest; the
+    innermost decides (src/MLFramework/Autograd/CheckpointScope.cs:40)."""
+    prev = getattr(_scope, "on", False)
+    _scope.on = bool(enabled)
+    try:
+        yield
+    finally:
+        _scope.on = prev
+
+
+def in_checkpoint_scope() -> bool:
+    return getattr(_scope, "on", False)
+
+
+def maybe_checkpoint(fn: Callable, *args):
+    return checkpoint(fn, *args) if in_checkpoint_scope() else fn(*args)
+
+
+def checkpoint_sequential(functions: Sequence[Callable], segments: int, x):
+    """Runs ``functions`` one after the other in ``segments`` groups, keeping only the activations between groups."""
+    fs = list(functions)
+    if segments <= 0:
+        raise ValueError("segments must be positive")
+    per = max(1, -(-len(fs) // segments))
+
+    def run(group):
+        def f(t):
+            for fn in group:
+                t = fn(t)
+            return t
+        return f
+    for i in range(0, len(fs), per):
+        x = checkpoint(run(fs[i:i + per]), x)
+    return x
+
+
+def selective_checkpointing(model: nn.Module, predicate: Callable[[str, nn.Module], bool]) -> List[str]:
+    """Wraps every sub-module for which ``predicate(path, module)`` holds (outermost match wins); returns their paths
+    (src/MLFramework/Autograd/CheckpointManager.cs:158)."""
+    wrapped: List[str] = []
+
+    def walk(parent: nn.Module, prefix: str):
+        for name, child in list(parent.named_children()):
+            path = f"{prefix}.{name}" if prefix else name
+            if isinstance(child, CheckpointedModuleWrapper):
+                continue
+            if predicate(path, child):
+                setattr(parent, name, CheckpointedModuleWrapper(child))
+                wrapped.append(path)
+            else:
+                walk(child, path)
+    walk(model, "")
+    return wrapped
+
+
+def tensor_checkpoint_bytes(*tensors: torch.Tensor) -> int:
+    """Bytes a set of saved activations holds (what recomputing them would free)."""
+    seen, n = set(), 0
+    for t in tensors:
+        if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+            seen.add(t.data_ptr())
+            n += t.numel() * t.element_size()
+    return n

@@ -248,3 +248,95 @@ class GlobalShapeProfiler:
             if h.coverage(k) >= coverage:
                 return [s for s, _ in h.top(k)]
         return [s for s, _ in h.top(max_k)]
+
+
+@dataclass
+class ShapeStatistics:
+    """Summary of the shapes one operation was called with (src/MLFramework/Profiling/ShapeStatistics.cs)."""
+    op: str
+    calls: int
+    distinct_shapes: int
+    most_common: Tuple[int, ...]
+    most_common_share: float
+    min_dims: Tuple[int, ...]
+    max_dims: Tuple[int, ...]
+    mean_elements: float
+    dynamic_dims: Tuple[int, ...]            # positions that varied between calls
+
+    @staticmethod
+    def from_histogram(op: str, h: ShapeHistogram) -> Optional["ShapeStatistics"]:
+        if not h.counts:
+            return None
+        calls = sum(h.counts.values())
+        (top, n), = h.top(1)
+        rank = len(top)
+        same = [s for s in h.counts if len(s) == rank]
+        mins = tuple(min(s[i] for s in same) for i in range(rank))
+        maxs = tuple(max(s[i] for s in same) for i in range(rank))
+
+        def numel(s):
+            k = 1
+            for d in s:
+                k *= d
+            return k
+        mean = sum(numel(s) * c for s, c in h.counts.items()) / calls
+        return ShapeStatistics(op, calls, len(h.counts), top, n / calls, mins, maxs, mean, tuple(i for i in range(rank) if mins[i] != maxs[i]))
+
+
+@dataclass
+class ShapeSpecializationPlan:
+    op: str
+    specialize: List[Tuple[int, ...]]         # compile a variant for each of these exact shapes
+    bucket_dims: Dict[int, List[int]]          # dynamic positions -> bucket upper bounds for the generic variants
+    expected_hit_rate: float
+
+
+class ShapeProfileOptimizer:
+    """Turns recorded shapes into a compilation plan: exact variants for the few shapes that make up most calls,
+    power-of-two buckets (capped at the largest seen) along the dimensions that vary for everything else
+    (src/MLFramework/Profiling/ShapeProfileOptimizer.cs)."""
+
+    def __init__(self, profiler: Optional[GlobalShapeProfiler] = None, coverage: float = 0.9, max_variants: int = 8, min_calls: int = 10):
+        self.prof = profiler or GlobalShapeProfiler.instance()
+        self.coverage, self.max_variants, self.min_calls = coverage, max_variants, min_calls
+
+    def statistics(self, op: str) -> Optional[ShapeStatistics]:
+        h = self.prof.hist.get(op)
+        return ShapeStatistics.from_histogram(op, h) if h is not None else None
+
+    def plan(self, op: str) -> Optional[ShapeSpecializationPlan]:
+        st = self.statistics(op)
+        if st is None or st.calls < self.min_calls:
+            return None
+        spec = self.prof.specialisations(op, self.coverage, self.max_variants)
+        h = self.prof.hist[op]
+        hit = sum(h.counts[s] for s in spec) / st.calls
+        buckets: Dict[int, List[int]] = {}
+        for i in st.dynamic_dims:
+            b, out = 1, []
+            while b < st.max_dims[i]:
+                if b >= st.min_dims[i]:
+                    out.append(b)
+                b *= 2
+            out.append(st.max_dims[i])
+            buckets[i] = out
+        return ShapeSpecializationPlan(op, spec, buckets, hit)
+
+    def plan_all(self) -> Dict[str, ShapeSpecializationPlan]:
+        out = {}
+        for op in self.prof.hist:
+            p = self.plan(op)
+            if p is not None:
+                out[op] = p
+        return out
+
+    def apply(self, manager, op: str, compile_fn: Callable[[Tuple[int, ...]], object]) -> int:
+        """Pre-compiles the planned exact variants through ``compile_fn(shape)``; returns how many were built."""
+        p = self.plan(op)
+        if p is None:
+            return 0
+        n = 0
+        for shape in p.specialize:
+            compile_fn(shape)
+            n += 1
+        return n

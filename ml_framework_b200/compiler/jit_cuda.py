@@ -40,6 +40,7 @@ SNIPPETS: Dict[str, Tuple[str, bool]] = {
     "relu": ("fmaxf(v, 0.f)", False), "sigmoid": ("1.f / (1.f + __expf(-v))", False), "tanh": ("tanhf(v)", False),
     "exp": ("__expf(v)", False), "log": ("__logf(v)", False), "sqrt": ("sqrtf(v)", False), "neg": ("-v", False),
     "abs": ("fabsf(v)", False), "square": ("v * v", False), "silu": ("v / (1.f + __expf(-v))", False),
+    "leaky_relu": ("(v > 0.f ? v : 0.01f * v)", False),
     "gelu": ("0.5f * v * (1.f + tanhf(0.7978845608f * (v + 0.044715f * v * v * v)))", False),
 }
 
@@ -47,6 +48,7 @@ _TORCH_OPS: Dict[str, Callable] = {
     "add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div, "maximum": torch.maximum, "minimum": torch.minimum,
     "relu": torch.relu, "sigmoid": torch.sigmoid, "tanh": torch.tanh, "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt,
     "neg": torch.neg, "abs": torch.abs, "square": torch.square, "silu": torch.nn.functional.silu,
+    "leaky_relu": lambda t: torch.nn.functional.leaky_relu(t, 0.01),
     "gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
 }
 

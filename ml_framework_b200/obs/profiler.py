@@ -311,3 +311,84 @@ import os as _os  # noqa: E402
 
 if _os.environ.get("MLF_NVTX") == "1":
     enable_nvtx(True)
+
+
+class PercentileCalculator:
+    """Percentiles of a sample set with linear interpolation between order statistics
+    (src/MLFramework.Visualization/Profiling/Statistics/PercentileCalculator.cs)."""
+
+    def __init__(self, values: Sequence[float] = ()):
+        self._v = sorted(float(x) for x in values)
+
+    def add(self, x: float):
+        import bisect
+        bisect.insort(self._v, float(x))
+
+    def __len__(self):
+        return len(self._v)
+
+    def percentile(self, q: float) -> float:
+        if not (0.0 <= q <= 100.0):
+            raise ValueError("percentile lies in [0, 100]")
+        return percentile(self._v, q)
+
+    def percentiles(self, qs: Sequence[float]) -> Dict[float, float]:
+        return {q: self.percentile(q) for q in qs}
+
+    def summary(self) -> Dict[str, float]:
+        if not self._v:
+            return {"count": 0}
+        return {"count": len(self._v), "min": self._v[0], "max": self._v[-1], "mean": sum(self._v) / len(self._v),
+                "p50": self.percentile(50), "p90": self.percentile(90), "p95": self.percentile(95), "p99": self.percentile(99)}
+
+
+class DurationTracker:
+    """Durations by name in nanoseconds: totals, counts, extremes and percentiles; ``track(name)`` times a block
+    (src/MLFramework.Visualization/Profiling/Statistics/DurationTracker.cs)."""
+
+    def __init__(self, max_samples_per_name: int = 10_000):
+        self.max_samples = max_samples_per_name
+        self._d: Dict[str, List[int]] = {}
+        self._total: Dict[str, int] = {}
+        self._count: Dict[str, int] = {}
+        self._lock = threading.Lock()
+
+    def record(self, name: str, duration_ns: int):
+        if duration_ns < 0:
+            raise ValueError("a duration cannot be negative")
+        with self._lock:
+            lst = self._d.setdefault(name, [])
+            lst.append(int(duration_ns))
+            if len(lst) > self.max_samples:
+                del lst[:len(lst) - self.max_samples]
+            self._total[name] = self._total.get(name, 0) + int(duration_ns)
+            self._count[name] = self._count.get(name, 0) + 1
+
+    @contextlib.contextmanager
+    def track(self, name: str):
+        t0 = time.perf_counter_ns()
+        try:
+            yield
+        finally:
+            self.record(name, time.perf_counter_ns() - t0)
+
+    def names(self) -> List[str]:
+        with self._lock:
+            return sorted(self._d)
+
+    def statistics(self, name: str) -> Dict[str, float]:
+        with self._lock:
+            v = list(self._d.get(name, ()))
+            total, count = self._total.get(name, 0), self._count.get(name, 0)
+        if not v:
+            return {"count": 0}
+        pc = PercentileCalculator(v)
+        return {"count": count, "total_ns": total, "mean_ns": total / count, "min_ns": min(v), "max_ns": max(v),
+                "p50_ns": pc.percentile(50), "p95_ns": pc.percentile(95), "p99_ns": pc.percentile(99)}
+
+    def reset(self, name: Optional[str] = None):
+        with self._lock:
+            if name is None:
+                self._d.clear(); self._total.clear(); self._count.clear()
+            else:
+                self._d.pop(name, None); self._total.pop(name, None); self._count.pop(name, None)

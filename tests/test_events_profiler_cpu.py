@@ -144,3 +144,47 @@ def test_memory_gc_and_utilisation_trackers_with_a_fake_nvml():
     none = P.GpuUtilizationTracker(0)
     none._nv = None
     assert none.sample() == {} and none.stop() == {}
+
+
+def test_percentile_calculator_duration_tracker_and_shape_profile_optimizer():
+    import pytest as _p
+    from ml_framework_b200.compiler.cache import GlobalShapeProfiler, ShapeProfileOptimizer
+    from ml_framework_b200.obs.profiler import DurationTracker, PercentileCalculator
+    pc = PercentileCalculator([5, 1, 3])
+    pc.add(2); pc.add(4)
+    assert len(pc) == 5 and pc.percentile(50) == 3.0 and pc.percentile(0) == 1.0 and pc.percentile(100) == 5.0 and pc.percentiles([25, 75]) == {25: 2.0, 75: 4.0}
+    assert pc.summary()["mean"] == 3.0 and PercentileCalculator().summary() == {"count": 0}
+    with _p.raises(ValueError):
+        pc.percentile(101)
+    dt = DurationTracker(max_samples_per_name=3)
+    for v in (10, 20, 30, 40):
+        dt.record("step", v)
+    with dt.track("blk"):
+        pass
+    st = dt.statistics("step")
+    assert st["count"] == 4 and st["total_ns"] == 100 and st["mean_ns"] == 25 and st["min_ns"] == 20 and st["p50_ns"] == 30 and dt.names() == ["blk", "step"]
+    assert dt.statistics("blk")["count"] == 1 and dt.statistics("none") == {"count": 0}
+    with _p.raises(ValueError):
+        dt.record("x", -1)
+    dt.reset("step")
+    assert dt.names() == ["blk"]
+    dt.reset()
+    assert dt.names() == []
+    prof = GlobalShapeProfiler()
+    for _ in range(60):
+        prof.record("linear", (8, 4096))
+    for _ in range(30):
+        prof.record("linear", (64, 4096))
+    for b in (3, 5, 7, 100, 200):
+        for _ in range(2):
+            prof.record("linear", (b, 4096))
+    opt = ShapeProfileOptimizer(prof, coverage=0.9, max_variants=4)
+    st = opt.statistics("linear")
+    assert st.calls == 100 and st.distinct_shapes == 7 and st.most_common == (8, 4096) and st.most_common_share == 0.6 and st.dynamic_dims == (0,)
+    assert st.min_dims == (3, 4096) and st.max_dims == (200, 4096)
+    plan = opt.plan("linear")
+    assert plan.specialize[:2] == [(8, 4096), (64, 4096)] and plan.expected_hit_rate >= 0.9 and plan.bucket_dims == {0: [4, 8, 16, 32, 64, 128, 200]}
+    built = []
+    assert opt.apply(None, "linear", built.append) == len(plan.specialize) and built == plan.specialize
+    prof.record("rare", (1,))
+    assert opt.plan("rare") is None and set(opt.plan_all()) == {"linear"} and opt.statistics("none") is None

@@ -258,3 +258,42 @@ def test_model_and_pipeline_parallel_variants():
     assert pp.stage_checkpoints(1) == []
     with pytest.raises(ValueError):
         pp.register_stage_checkpoint(5, "x", a)
+
+
+def test_checkpoint_scopes_sequential_and_selective_wrapping():
+    import torch.nn as nn
+    from ml_framework_b200.checkpoint import activation as act
+    calls = {"n": 0}
+
+    def f(t):
+        calls["n"] += 1
+        return torch.tanh(t) * 2
+    x = torch.randn(4, requires_grad=True)
+    act.maybe_checkpoint(f, x).sum().backward()
+    assert calls["n"] == 1 and not act.in_checkpoint_scope()
+    g_plain = x.grad.clone()
+    x.grad = None
+    with act.checkpoint_scope():
+        assert act.in_checkpoint_scope()
+        with act.checkpoint_scope(False):
+            assert not act.in_checkpoint_scope()
+        y = act.maybe_checkpoint(f, x)
+    y.sum().backward()
+    assert calls["n"] == 3 and torch.allclose(x.grad, g_plain)                  # forward once more during backward
+    layers = [nn.Linear(4, 4) for _ in range(5)]
+    x2 = torch.randn(2, 4, requires_grad=True)
+    ref = x2
+    for l in layers:
+        ref = l(ref)
+    out = act.checkpoint_sequential(layers, 2, x2)
+    assert torch.allclose(out, ref)
+    out.sum().backward()
+    assert all(l.weight.grad is not None for l in layers)
+    with pytest.raises(ValueError):
+        act.checkpoint_sequential(layers, 0, x2)
+    model = nn.Sequential(nn.Sequential(nn.Linear(4, 4), nn.ReLU()), nn.Linear(4, 2))
+    assert act.selective_checkpointing(model, lambda path, m: isinstance(m, nn.Sequential)) == ["0"]
+    assert isinstance(model[0], act.CheckpointedModuleWrapper) and act.selective_checkpointing(model, lambda p, m: True) == ["1"]
+    model(torch.randn(3, 4, requires_grad=True)).sum().backward()
+    a = torch.zeros(10)
+    assert act.tensor_checkpoint_bytes(a, a, torch.zeros(3, dtype=torch.float64)) == 40 + 24
