@@ -188,6 +188,37 @@ class BlockTable:
     def remove_sequence(self, seq_id: int) -> int:
         return self.m.free_sequence_blocks(seq_id)
 
+    def get_stats(self, seq_ids: Sequence[int]) -> "BlockTableStats":
+        """Occupancy of the given sequences' tables: blocks held, tokens stored, slack in the last blocks."""
+        blocks = tokens = 0
+        longest = 0
+        for s in seq_ids:
+            nb, nt = len(self.m.get_sequence_blocks(s)), self.m.get_sequence_length(s)
+            blocks += nb
+            tokens += nt
+            longest = max(longest, nt)
+        cap = blocks * self.m.block_size
+        return BlockTableStats(len(list(seq_ids)), blocks, tokens, cap - tokens, tokens / cap if cap else 0.0, longest)
+
+
+@dataclass
+class BlockTableStats:
+    sequences: int
+    total_blocks: int
+    total_tokens: int
+    unused_slots: int           # allocated but empty positions (internal fragmentation)
+    fill_ratio: float
+    longest_sequence: int
+
+
+@dataclass
+class ShareStats:
+    """What sharing saves: blocks referenced by more than one sequence, and the blocks that would exist without it."""
+    shared_blocks: int
+    total_references: int
+    blocks_saved: int
+    registered_prefixes: int
+
 
 class BlockShareManager:
     """Prompt-prefix sharing: sequences with a common prefix point at the same blocks."""
@@ -219,6 +250,14 @@ class BlockShareManager:
 
     def get_reference_count(self, block: int) -> int:
         return self.m.reference_count(block)
+
+    def get_stats(self, seq_ids: Sequence[int]) -> ShareStats:
+        seen: Dict[int, int] = {}
+        for s in seq_ids:
+            for b in self.m.get_sequence_blocks(s):
+                seen[b] = seen.get(b, 0) + 1
+        shared = {b: n for b, n in seen.items() if n > 1}
+        return ShareStats(len(shared), sum(shared.values()), sum(n - 1 for n in shared.values()), len(self._prefix_owner))
 
 
 class BeamSearchBlockSharing:

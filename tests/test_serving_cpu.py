@@ -527,3 +527,19 @@ def test_paged_kernel_interface_and_orchestrators():
         dec.compute_decode_attention(layer, torch.randn(2, d), 1)
     with _p.raises(ValueError):
         pre.prefill_allocate_blocks(3, 0)
+
+
+def test_block_table_and_share_statistics():
+    from ml_framework_b200.serving.kv_cache import BlockShareManager, BlockTable, KVCacheBlockManager
+    kv = KVCacheBlockManager(total_blocks=16, block_size=4, head_dim=8, num_layers=1, num_kv_heads=1, dtype=torch.float32, device="cpu")
+    kv.append_tokens(1, 10)
+    sh = BlockShareManager(kv)
+    sh.register_prefix(list(range(8)), 1)
+    assert sh.share_prefix(1, 2, 9) == 2                      # two whole blocks
+    kv.append_tokens(2, 3)
+    st = BlockTable(kv).get_stats([1, 2])
+    assert (st.sequences, st.total_blocks, st.total_tokens, st.unused_slots, st.longest_sequence) == (2, 6, 21, 3, 11) and abs(st.fill_ratio - 21 / 24) < 1e-9
+    ss = sh.get_stats([1, 2])
+    assert (ss.shared_blocks, ss.total_references, ss.blocks_saved, ss.registered_prefixes) == (2, 4, 2, 1)
+    sh.release_sequence(1)
+    assert sh.get_stats([2]).shared_blocks == 0 and sh.get_stats([2]).registered_prefixes == 0
