@@ -195,6 +195,17 @@ class ProcessGroup:
             post()
         return out
 
+    def all_to_all(self, t: torch.Tensor, async_op: bool = False):
+        """Equal-split exchange along dim 0: chunk ``j`` of ``t`` goes to rank ``j``; chunk ``j`` of
+        the result came from rank ``j``."""
+        W = self.world_size
+        if t.shape[0] % W != 0:
+            raise ValueError(f"all_to_all: dim 0 of size {t.shape[0]} not divisible by {W}")
+        src = t.contiguous()
+        out = torch.empty_like(src)
+        w = dist.all_to_all_single(out, src, group=self._pg, async_op=async_op)
+        return Work(w, out) if async_op else out
+
     def barrier(self, async_op: bool = False):
         if self.backend == BackendType.NCCL and torch.cuda.is_available():
             w = dist.barrier(group=self._pg, async_op=async_op, device_ids=[torch.cuda.current_device()])
@@ -398,6 +409,16 @@ class FakeProcessGroup:
                 s = s / len(xs)
             return [c.clone() for c in s.chunk(len(xs), dim=dim)]
         r = self._rendezvous("reduce_scatter", t, comb)
+        return Work(None, r) if async_op else r
+
+    def all_to_all(self, t, async_op: bool = False):
+        def comb(xs):
+            W = len(xs)
+            parts = [x.chunk(W, dim=0) for x in xs]
+            return [torch.cat([parts[src][dst].clone() for src in range(W)], dim=0) for dst in range(W)]
+        if t.shape[0] % self.world_size != 0:
+            raise ValueError(f"all_to_all: dim 0 of size {t.shape[0]} not divisible by {self.world_size}")
+        r = self._rendezvous("all_to_all", t, comb)
         return Work(None, r) if async_op else r
 
     def barrier(self, async_op: bool = False):
