@@ -252,3 +252,61 @@ def test_gpu_trackers_on_a_fake_nvml():
     none.start_tracking()
     with pytest.raises(RuntimeError):
         none.device_info(0)
+
+
+def test_seed_manager_device_worker_seeds_scopes_registry_and_validation(tmp_path):
+    import io
+    import random
+
+    from ml_framework_b200.obs.seed import DeterministicModeFlags as F, SeedManager
+    sm = SeedManager()
+    with pytest.raises(ValueError):
+        sm.seed_workers(2)                                  # no base seed yet
+    sm.set_global_seed(11)
+    sm.seed_all_devices(device_count=3)
+    assert len({sm.device_seed(d) for d in range(3)}) == 3 and sm.current_seed == 11
+    with pytest.raises(KeyError):
+        sm.device_seed(7)
+    assert sm.seed_workers(2) == [sm.worker_seed(0), sm.worker_seed(1)]
+    # a seeded scope repeats, and the outer stream continues as if the scope had not been there
+    torch.manual_seed(5); random.seed(5)
+    a0 = torch.rand(1)
+    with sm.with_global_seed(99):
+        inner1 = (torch.rand(2), random.random())
+    a1 = torch.rand(1)
+    with sm.with_global_seed(99):
+        inner2 = (torch.rand(2), random.random())
+    torch.manual_seed(5)
+    assert torch.equal(torch.rand(1), a0) and torch.equal(torch.rand(1), a1)
+    assert torch.equal(inner1[0], inner2[0]) and inner1[1] == inner2[1] and sm.current_seed == 11
+    # snapshots survive a file
+    snap = sm.capture_rng_state()
+    x = torch.rand(3)
+    sm.save_rng_snapshot(snap, str(tmp_path / "rng.pt"))
+    torch.rand(10)
+    sm.restore_rng_state(sm.load_rng_snapshot(str(tmp_path / "rng.pt")))
+    assert torch.equal(torch.rand(3), x)
+    # flags
+    assert sm.check_performance_impact() is None and "no performance impact" in sm.performance_impact()
+    with sm.with_deterministic_mode(F.NO_ATOMIC_REDUCTIONS):
+        assert sm.is_deterministic_mode_enabled(F.NO_ATOMIC_REDUCTIONS) and "reported, not replaced" in sm.check_performance_impact()
+        sm.register_non_deterministic_operation("matmul")
+        sm.register_non_deterministic_operation("matmul")
+        sm.register_non_deterministic_operation("scatter_add")
+        res = sm.validate_configuration()
+        assert not res.is_valid and len(res.errors) == 1 and "scatter_add" in res.errors[0]
+        assert sum("matmul" in w for w in res.warnings) == 1 and any("flash_bwd" in w for w in res.warnings)
+        assert "2 workers seeded" in res.messages and "3 devices seeded" in res.messages
+    assert sm.flags == F.NONE and sm.validate_configuration().is_valid
+    sm.enable_deterministic_mode(F.NO_TF32)
+    sm.disable_deterministic_mode(F.NO_TF32)
+    assert not sm.is_deterministic_mode_enabled(F.NO_TF32)
+    assert sm.non_deterministic_operations() == ["matmul", "scatter_add"]
+    assert sm.can_be_deterministic("dropout") and not sm.can_be_deterministic("atomic_add") and not sm.can_be_deterministic(" ")
+    with pytest.raises(ValueError):
+        sm.register_non_deterministic_operation("")
+    buf = io.StringIO()
+    sm.print_diagnostics(file=buf)
+    assert "scatter_add (non-determinizable)" in buf.getvalue() and "current seed: 11" in buf.getvalue()
+    info = sm.diagnostic_info()
+    assert info.device_count == 3 and info.worker_count == 2
