@@ -24,6 +24,8 @@ from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 import torch
 import torch.nn as nn
 
+from .errors import ChecksumMismatchError, DownloadFailedError, ModelNotFoundError, VersionNotFoundError
+
 
 @dataclass
 class ModelInfo:
@@ -56,6 +58,19 @@ def _build_config(info: ModelInfo):
     raise KeyError(f"unknown architecture {info.architecture!r}")
 
 
+def _version_key(v: str):
+    """Orders versions: numeric fields compare as numbers, a pre-release ("1.2.0-rc.1") comes before its
+    release, anything unparsable sorts lowest by its text."""
+    core, _, pre = v.split("+")[0].partition("-")
+    nums = []
+    for part in core.split(".")[:3]:
+        digits = "".join(ch for ch in part if ch.isdigit())
+        if not digits:
+            return (0, (), 0, v)
+        nums.append(int(digits))
+    return (1, tuple(nums), 0 if pre else 1, pre)
+
+
 class ZooRegistry:
     def __init__(self):
         self._m: Dict[Tuple[str, str], ModelInfo] = {}
@@ -69,14 +84,17 @@ class ZooRegistry:
             if (name, version) in self._m:
                 return self._m[(name, version)]
         else:
-            vs = sorted((v for n, v in self._m if n == name), key=lambda s: tuple(int(x) for x in s.split(".")[:3]))
+            vs = sorted((v for n, v in self._m if n == name), key=_version_key)
             if vs:
                 return self._m[(name, vs[-1])]
         for p in self._plugins:
             info = p.lookup(name, version)
             if info is not None:
                 return info
-        raise KeyError(f"model {name!r}" + (f" version {version}" if version else "") + " is not registered")
+        known = sorted(v for n, v in self._m if n == name)
+        if version is not None and known:
+            raise VersionNotFoundError(name, version, known)
+        raise ModelNotFoundError(name)
 
     def list(self) -> List[ModelInfo]:
         return list(self._m.values())
@@ -124,6 +142,7 @@ class ModelCacheManager:
 
     def __init__(self, root: str, max_bytes: int = 200 << 30):
         self.root, self.max_bytes = root, max_bytes
+        self.hits = self.loads = 0                  # fetches served from the cache / all fetches
         os.makedirs(root, exist_ok=True)
         self._index_path = os.path.join(root, "index.json")
 
@@ -163,6 +182,7 @@ class ModelCacheManager:
         key = f"{name}-{version}"
         idx.setdefault(key, {})["last_used"] = time.time()
         idx[key]["bytes"] = os.path.getsize(self.path(name, version))
+        idx[key]["access_count"] = idx[key].get("access_count", 0) + 1
         self._save(idx)
 
     def evict(self) -> List[str]:
@@ -198,7 +218,10 @@ class ModelDownloadService:
     def fetch(self, info: ModelInfo, progress: Optional[Callable[[int, int], None]] = None) -> str:
         dst = self.cache.path(info.name, info.version)
         with self.cache.lock(info.name, info.version):
-            if not self.cache.contains(info.name, info.version):
+            self.cache.loads += 1
+            if self.cache.contains(info.name, info.version):
+                self.cache.hits += 1
+            else:
                 src = info.source or ""
                 if src.startswith("file://"):
                     src = src[7:]
@@ -223,10 +246,11 @@ class ModelDownloadService:
                     except OSError as e:
                         last = e
                 if last is not None:
-                    raise last
-            if info.sha256 and sha256_file(dst) != info.sha256:
+                    raise DownloadFailedError([src], self.retries, f"{info.name}: copying {src!r} failed {self.retries} times: {last}") from last
+            actual = sha256_file(dst) if info.sha256 else None
+            if info.sha256 and actual != info.sha256:
                 os.remove(dst)
-                raise IOError(f"{info.name}: checksum mismatch")
+                raise ChecksumMismatchError(dst, info.sha256, actual)
             self.cache.touch(info.name, info.version)
         self.cache.evict()
         return dst
@@ -286,6 +310,18 @@ class ModelZoo:
             else:
                 model.load_state_dict(torch.load(path, map_location="cpu", weights_only=True))
         return model
+
+    def load_progressive(self, name: str, version: Optional[str] = None, options=None, device="cpu",
+                         dtype: Optional[torch.dtype] = None):
+        """The model on ``meta`` with a ``progressive.ProgressiveModelLoader`` attached: layers come in
+        from the cached weight file as the forward pass (or the chosen background strategy) wants
+        them. Returns (model, loader)."""
+        from .progressive import load_progressive
+        info = self.registry.get(name, version)
+        if not info.source:
+            raise ValueError(f"model {name!r} has no weights to load progressively")
+        path = self.downloads.fetch(info)
+        return load_progressive(lambda: build_model(info, "meta", dtype or torch.float32), path, options, device, dtype, info)
 
     def save(self, model: nn.Module, info: ModelInfo, path: str) -> ModelInfo:
         torch.save(model.state_dict(), path)
