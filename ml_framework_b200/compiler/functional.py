@@ -17,7 +17,9 @@ mesh with named axes and collectives, ``JITTransform`` with tracing and a per-si
 from __future__ import annotations
 
 import contextlib
+import enum
 import threading
+import weakref
 from typing import Callable, Dict, Optional, Sequence, Tuple, Union
 
 import torch
@@ -35,6 +37,248 @@ def compose(*fns: Callable) -> Callable:
             x = f(x)
         return x
     return run
+
+
+# ------------------------------------------------------------------ combinators (Functional/Composition.cs:11-334)
+def pipe(value, *fns: Callable):
+    """``pipe(x, f, g)`` = ``g(f(x))``."""
+    for f in fns:
+        value = f(value)
+    return value
+
+
+def partial(fn: Callable, first) -> Callable:
+    """Fixes the first argument."""
+    return lambda *rest, **kw: fn(first, *rest, **kw)
+
+
+def partial_second(fn: Callable, second) -> Callable:
+    """Fixes the second argument."""
+    return lambda first, *rest, **kw: fn(first, second, *rest, **kw)
+
+
+def curry(fn: Callable, arity: int = 2) -> Callable:
+    """``curry(f)(a)(b) == f(a, b)`` (``arity`` arguments, one call each)."""
+    if arity < 1:
+        raise ValueError("arity must be at least 1")
+
+    def take(args):
+        return (lambda x: take(args + (x,))) if len(args) + 1 < arity else (lambda x: fn(*args, x))
+    return take(())
+
+
+def uncurry(fn: Callable) -> Callable:
+    def run(*args):
+        out = fn
+        for a in args:
+            out = out(a)
+        return out
+    return run
+
+
+def identity(value):
+    return value
+
+
+def constant(value) -> Callable:
+    return lambda *a, **k: value
+
+
+def tap(value, action: Callable):
+    """Runs ``action(value)`` for its side effect (logging, a check) and passes the value on."""
+    action(value)
+    return value
+
+
+def tap_if(value, condition: bool, action: Callable):
+    if condition:
+        action(value)
+    return value
+
+
+# ------------------------------------------------------------------ transformation bookkeeping
+class TransformationType(enum.Enum):
+    VECTORIZATION = "vectorization"
+    PARALLELIZATION = "parallelization"
+    COMPILATION = "compilation"
+    COMPOSITION = "composition"
+
+
+class MeshAxisNames:
+    """Conventional axis names of a device mesh (Functional/Distributed/MeshAxisNames.cs)."""
+    DATA = "data"
+    MODEL = "model"
+    PIPELINE = "pipeline"
+
+
+class TransformationContext:
+    """Settings shared by nested transformations; a child sees its parents' metadata
+    (Functional/TransformationContext.cs:6-90)."""
+
+    def __init__(self, parent: Optional["TransformationContext"] = None):
+        self.parent = parent
+        self.metadata: Dict[str, object] = {}
+        self.debug_mode = parent.debug_mode if parent is not None else False
+
+    def get_metadata(self, key: str, default=None, search_parents: bool = True):
+        if key in self.metadata:
+            return self.metadata[key]
+        if search_parents and self.parent is not None:
+            return self.parent.get_metadata(key, default, True)
+        return default
+
+    def set_metadata(self, key: str, value) -> None:
+        self.metadata[key] = value
+
+    def create_child_context(self) -> "TransformationContext":
+        return TransformationContext(self)
+
+
+def tensor_function(fn: Optional[Callable] = None, *, is_pure: bool = True, input_shapes: Optional[Sequence[str]] = None,
+                    output_shape: Optional[str] = None, description: str = ""):
+    """Marks a function of tensors: whether it is pure (no side effects: transformations may re-run,
+    reorder or cache it) and, optionally, its symbolic shapes (Functional/TensorFunctionAttribute.cs)."""
+    def mark(f):
+        f.__tensor_function__ = {"is_pure": is_pure, "input_shapes": tuple(input_shapes or ()),
+                                 "output_shape": output_shape, "description": description}
+        return f
+    return mark(fn) if fn is not None else mark
+
+
+def is_function_pure(fn: Callable) -> bool:
+    """Unmarked functions are taken to be pure, as the reference does."""
+    return getattr(fn, "__tensor_function__", {"is_pure": True})["is_pure"]
+
+
+class BaseTransformation:
+    """A named transformation of a function; ``__call__`` applies it and records the fact in the
+    registry (Functional/BaseTransformation.cs:8-110)."""
+
+    def __init__(self, name: str, type: TransformationType, context: Optional[TransformationContext] = None):
+        self.name, self.type = name, type
+        self.context = context or TransformationContext()
+
+    def transform(self, original: Callable) -> Callable:
+        raise NotImplementedError
+
+    def validate(self, fn: Callable) -> None:
+        if not callable(fn):
+            raise TypeError(f"{self.name}: expected a function, got {type(fn).__name__}")
+        if self.type is not TransformationType.COMPOSITION and not is_function_pure(fn):
+            raise ValueError(f"{self.name}: function {getattr(fn, '__name__', fn)!r} is marked impure and cannot be transformed")
+
+    def __call__(self, fn: Callable) -> Callable:
+        self.validate(fn)
+        out = self.transform(fn)
+        TransformationRegistry.register(fn, self)
+        if self.context.debug_mode:
+            self.context.set_metadata("last_applied", (self.name, getattr(fn, "__name__", repr(fn))))
+        return out
+
+
+class VMapTransformation(BaseTransformation):
+    def __init__(self, in_axes=0, out_axes: int = 0, chunk_size: Optional[int] = None, context=None):
+        super().__init__("vmap", TransformationType.VECTORIZATION, context)
+        self.in_axes, self.out_axes, self.chunk_size = in_axes, out_axes, chunk_size
+
+    def transform(self, original):
+        return vmap(original, self.in_axes, self.out_axes, self.chunk_size)
+
+
+class PMapTransformation(BaseTransformation):
+    def __init__(self, pg=None, axis_name: str = MeshAxisNames.DATA, in_axes=0, context=None):
+        super().__init__("pmap", TransformationType.PARALLELIZATION, context)
+        self.pg, self.axis_name, self.in_axes = pg, axis_name, in_axes
+
+    def transform(self, original):
+        return pmap(original, self.pg, self.axis_name, self.in_axes)
+
+
+class JITTransformation(BaseTransformation):
+    def __init__(self, optimize: bool = True, context=None):
+        super().__init__("jit", TransformationType.COMPILATION, context)
+        self.optimize = optimize
+
+    def transform(self, original):
+        return jit(original, optimize=self.optimize)
+
+
+class TransformationRegistry:
+    """Which transformations have been applied to which function (Functional/TransformationRegistry.cs).
+    Functions are held weakly where they allow it, so the registry does not keep closures alive."""
+
+    _lock = threading.Lock()
+    _by_id: Dict[int, Tuple[object, list]] = {}
+
+    @classmethod
+    def _key(cls, fn) -> int:
+        return id(fn)
+
+    @classmethod
+    def register(cls, original: Callable, transform: BaseTransformation) -> None:
+        if original is None or transform is None:
+            raise ValueError("function and transformation are required")
+        with cls._lock:
+            k = cls._key(original)
+            if k not in cls._by_id:
+                try:
+                    ref = weakref.ref(original, lambda _r, k=k: cls._by_id.pop(k, None))
+                except TypeError:
+                    ref = lambda o=original: o                       # noqa: E731 - objects without weak references stay alive
+                cls._by_id[k] = (ref, [])
+            lst = cls._by_id[k][1]
+            if not any(t.name == transform.name and t.type == transform.type for t in lst):
+                lst.append(transform)
+
+    @classmethod
+    def get_transformations(cls, original: Callable) -> list:
+        with cls._lock:
+            e = cls._by_id.get(cls._key(original))
+            return list(e[1]) if e is not None and e[0]() is original else []
+
+    @classmethod
+    def get_transformations_by_type(cls, original: Callable, type: TransformationType) -> list:
+        return [t for t in cls.get_transformations(original) if t.type == type]
+
+    @classmethod
+    def has_transformations(cls, original: Callable) -> bool:
+        return bool(cls.get_transformations(original))
+
+    @classmethod
+    def has_transformation_of_type(cls, original: Callable, type: TransformationType) -> bool:
+        return bool(cls.get_transformations_by_type(original, type))
+
+    @classmethod
+    def unregister(cls, original: Callable) -> bool:
+        with cls._lock:
+            return cls._by_id.pop(cls._key(original), None) is not None
+
+    @classmethod
+    def clear(cls) -> None:
+        with cls._lock:
+            cls._by_id.clear()
+
+    @classmethod
+    def count(cls) -> int:
+        return len(cls._by_id)
+
+    @classmethod
+    def total_transformation_count(cls) -> int:
+        with cls._lock:
+            return sum(len(e[1]) for e in cls._by_id.values())
+
+
+def vectorize(fn: Callable, in_axes=0, out_axes: int = 0) -> Callable:
+    """``vmap`` that also records itself in the registry."""
+    return VMapTransformation(in_axes, out_axes)(fn)
+
+
+def parallelize(fn: Callable, pg=None, axis_name: str = MeshAxisNames.DATA, in_axes=0) -> Callable:
+    return PMapTransformation(pg, axis_name, in_axes)(fn)
+
+
+def compile_function(fn: Callable, optimize: bool = True) -> Callable:
+    return JITTransformation(optimize)(fn)
 
 
 # ------------------------------------------------------------------ vmap
@@ -268,6 +512,17 @@ class Tracer:
         raise TraceError(f"operation {name!r} is not traceable")
 
 
+_live_jit_functions: "weakref.WeakSet" = weakref.WeakSet()
+
+
+def clear_jit_cache() -> int:
+    """Clears the caches of all live jitted functions (Functional.ClearJITCache); returns how many."""
+    fns = list(_live_jit_functions)
+    for f in fns:
+        f.clear_cache()
+    return len(fns)
+
+
 class JitFunction:
     """Result of ``jit(fn)``: per input signature either a traced + optimised graph, a CUDA-graph capture, or ``fn`` itself."""
 
@@ -276,6 +531,11 @@ class JitFunction:
         self._cache: Dict[Tuple, Tuple[str, object]] = {}
         self.stats = {"traced": 0, "captured": 0, "eager": 0, "hits": 0}
         self.__wrapped__ = fn
+        _live_jit_functions.add(self)
+
+    def clear_cache(self) -> None:
+        """Forgets every traced graph and capture: the next call of each signature traces again."""
+        self._cache.clear()
 
     @staticmethod
     def _sig(inputs) -> Tuple:
