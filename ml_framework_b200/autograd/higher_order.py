@@ -255,6 +255,194 @@ def validate_hvp(f, x, v, tolerance: float = 1e-3, analytical: Optional[torch.Te
     return relative_error(a, numerical_hvp(f, x, v)) <= tolerance
 
 
+# ------------------------------------------------------------------ Jacobian-vector and vector-Jacobian products
+@dataclass
+class JVPOptions:
+    """Options of ``JacobianVectorProduct`` (JacobianVectorProduct.cs:31-70)."""
+    exploit_sparsity: bool = True        # a zero tangent gives a zero product after one plain forward pass (for the shape)
+    cache_tangents: bool = False         # remember products per (function, point, tangent)
+    sparsity_threshold: float = 1e-10
+    enable_parallel: bool = True         # batches as one vectorised sweep instead of a loop
+    max_parallel_tasks: int = -1         # chunk size of that sweep; -1 = everything at once
+    output_buffer: Optional[torch.Tensor] = None
+    clear_cache: bool = False
+
+
+@dataclass
+class VJPOptions:
+    """Options of ``VectorJacobianProduct`` (VectorJacobianProduct.cs:31-70)."""
+    exploit_sparsity: bool = True
+    cache_gradients: bool = False
+    sparsity_threshold: float = 1e-10
+    enable_parallel: bool = True
+    max_parallel_tasks: int = -1
+    output_buffer: Optional[torch.Tensor] = None
+    clear_cache: bool = False
+
+
+def _cache_key(f, x: torch.Tensor, v: torch.Tensor):
+    return (id(f), tuple(x.shape), x.dtype, hash(x.detach().cpu().numpy().tobytes()), hash(v.detach().cpu().numpy().tobytes()))
+
+
+def _emit(result: torch.Tensor, buffer: Optional[torch.Tensor]) -> torch.Tensor:
+    if buffer is None:
+        return result
+    if buffer.shape != result.shape:
+        raise ValueError(f"output buffer has shape {list(buffer.shape)}, the product {list(result.shape)}")
+    buffer.copy_(result)
+    return buffer
+
+
+class JacobianVectorProduct:
+    """``J(x) v`` by forward-mode differentiation: one pass, no Jacobian (JacobianVectorProduct.cs:14-460)."""
+
+    _cache: Dict[tuple, torch.Tensor] = {}
+    _lock = threading.Lock()
+
+    @classmethod
+    def compute(cls, f, x: torch.Tensor, v: torch.Tensor, options: Optional[JVPOptions] = None) -> torch.Tensor:
+        o = options or JVPOptions()
+        if v.shape != x.shape:
+            raise ValueError(f"the tangent has shape {list(v.shape)}, the point {list(x.shape)}")
+        if o.clear_cache:
+            cls.clear_tangent_cache()
+        if o.exploit_sparsity and (v.numel() == 0 or float(v.abs().max()) <= o.sparsity_threshold):
+            with torch.no_grad():                                        # a plain forward pass gives the output's shape
+                y = f(x.detach())
+            return _emit(torch.zeros_like(y), o.output_buffer)
+        key = _cache_key(f, x, v) if o.cache_tangents else None
+        if key is not None:
+            with cls._lock:
+                hit = cls._cache.get(key)
+            if hit is not None:
+                return _emit(hit.clone(), o.output_buffer)
+        res = tf.jvp(f, (x,), (v,))[1]
+        if key is not None:
+            with cls._lock:
+                cls._cache[key] = res.detach().clone()
+        return _emit(res, o.output_buffer)
+
+    @classmethod
+    def compute_batch(cls, f, x: torch.Tensor, vectors: Sequence[torch.Tensor], options: Optional[JVPOptions] = None) -> List[torch.Tensor]:
+        o = options or JVPOptions()
+        if not len(vectors):
+            return []
+        if not o.enable_parallel:
+            return [cls.compute(f, x, v, o) for v in vectors]
+        V = torch.stack(list(vectors))
+        chunk = None if o.max_parallel_tasks <= 0 else o.max_parallel_tasks
+        return list(torch.vmap(lambda v: tf.jvp(f, (x,), (v,))[1], chunk_size=chunk)(V))
+
+    @classmethod
+    def compute_multiple(cls, f, inputs: Sequence[torch.Tensor], v: torch.Tensor, input_index: int = 0,
+                         options: Optional[JVPOptions] = None) -> torch.Tensor:
+        """Product with respect to ``inputs[input_index]`` of a function of several tensors (given as a list)."""
+        if not 0 <= input_index < len(inputs):
+            raise IndexError(f"input index {input_index} of {len(inputs)} inputs")
+        inputs = list(inputs)
+
+        def g(xi):
+            return f(inputs[:input_index] + [xi] + inputs[input_index + 1:])
+        return cls.compute(g, inputs[input_index], v, options)
+
+    @classmethod
+    def clear_tangent_cache(cls) -> None:
+        with cls._lock:
+            cls._cache.clear()
+
+    @classmethod
+    def get_cache_size(cls) -> int:
+        return len(cls._cache)
+
+    @staticmethod
+    def compute_numerical(f, x: torch.Tensor, v: torch.Tensor, epsilon: Optional[float] = None) -> torch.Tensor:
+        h = epsilon if epsilon is not None else float(torch.finfo(x.dtype).eps) ** (1 / 3)
+        return (f(x + h * v) - f(x - h * v)) / (2 * h)
+
+    @classmethod
+    def validate(cls, f, x, v, tolerance: float = 1e-3, epsilon: Optional[float] = None) -> bool:
+        return relative_error(cls.compute(f, x, v, JVPOptions(exploit_sparsity=False)), cls.compute_numerical(f, x, v, epsilon)) <= tolerance
+
+    @classmethod
+    def compute_jacobian(cls, f, x: torch.Tensor) -> torch.Tensor:
+        """The Jacobian column by column: one product per input element ([*out, *in])."""
+        eye = torch.eye(x.numel(), dtype=x.dtype, device=x.device).view(x.numel(), *x.shape)
+        cols = torch.vmap(lambda e: tf.jvp(f, (x,), (e,))[1])(eye)
+        return cols.movedim(0, -1).reshape(*cols.shape[1:], *x.shape)
+
+
+class VectorJacobianProduct:
+    """``v^T J(x)`` by reverse-mode differentiation (VectorJacobianProduct.cs:14-500)."""
+
+    _cache: Dict[tuple, torch.Tensor] = {}
+    _lock = threading.Lock()
+
+    @classmethod
+    def compute(cls, f, x: torch.Tensor, v: torch.Tensor, options: Optional[VJPOptions] = None) -> torch.Tensor:
+        o = options or VJPOptions()
+        if o.clear_cache:
+            cls.clear_gradient_cache()
+        if o.exploit_sparsity and (v.numel() == 0 or float(v.abs().max()) <= o.sparsity_threshold):
+            return _emit(torch.zeros_like(x), o.output_buffer)
+        key = _cache_key(f, x, v) if o.cache_gradients else None
+        if key is not None:
+            with cls._lock:
+                hit = cls._cache.get(key)
+            if hit is not None:
+                return _emit(hit.clone(), o.output_buffer)
+        y, pull = tf.vjp(f, x)
+        if v.shape != y.shape:
+            raise ValueError(f"the cotangent has shape {list(v.shape)}, the output {list(y.shape)}")
+        res = pull(v)[0]
+        if key is not None:
+            with cls._lock:
+                cls._cache[key] = res.detach().clone()
+        return _emit(res, o.output_buffer)
+
+    @classmethod
+    def compute_batch(cls, f, x: torch.Tensor, vectors: Sequence[torch.Tensor], options: Optional[VJPOptions] = None) -> List[torch.Tensor]:
+        o = options or VJPOptions()
+        if not len(vectors):
+            return []
+        if not o.enable_parallel:
+            return [cls.compute(f, x, v, o) for v in vectors]
+        _, pull = tf.vjp(f, x)                                           # one forward pass serves every cotangent
+        chunk = None if o.max_parallel_tasks <= 0 else o.max_parallel_tasks
+        return list(torch.vmap(lambda v: pull(v)[0], chunk_size=chunk)(torch.stack(list(vectors))))
+
+    @classmethod
+    def compute_multiple(cls, f, inputs: Sequence[torch.Tensor], v: torch.Tensor, options: Optional[VJPOptions] = None) -> List[torch.Tensor]:
+        """One pull-back gives the product for every input of ``f(list_of_tensors)``."""
+        _, pull = tf.vjp(lambda *xs: f(list(xs)), *inputs)
+        return list(pull(v))
+
+    @classmethod
+    def clear_gradient_cache(cls) -> None:
+        with cls._lock:
+            cls._cache.clear()
+
+    @classmethod
+    def get_cache_size(cls) -> int:
+        return len(cls._cache)
+
+    @staticmethod
+    def compute_numerical(f, x: torch.Tensor, v: torch.Tensor, epsilon: Optional[float] = None) -> torch.Tensor:
+        """Element ``i`` is ``v . (f(x + h e_i) - f(x - h e_i)) / 2h``."""
+        h = epsilon if epsilon is not None else float(torch.finfo(x.dtype).eps) ** (1 / 3)
+        out = torch.zeros_like(x)
+        flat = out.view(-1)
+        for i in range(x.numel()):
+            e = torch.zeros_like(x).view(-1)
+            e[i] = h
+            e = e.view_as(x)
+            flat[i] = ((f(x + e) - f(x - e)) * v).sum() / (2 * h)
+        return out
+
+    @classmethod
+    def validate(cls, f, x, v, tolerance: float = 1e-3, epsilon: Optional[float] = None) -> bool:
+        return relative_error(cls.compute(f, x, v, VJPOptions(exploit_sparsity=False)), cls.compute_numerical(f, x, v, epsilon)) <= tolerance
+
+
 # ------------------------------------------------------------------ order tracking
 class HigherOrderContext:
     """Tracks how deeply differentiation is nested on this thread (``with ctx.order():`` around each level) and caps it;

@@ -118,3 +118,55 @@ def test_function_registry():
     assert H.FunctionRegistry.unregister("ste") and not H.FunctionRegistry.unregister("ste")
     H.FunctionRegistry.clear_all()
     assert H.FunctionRegistry.names() == []
+
+
+def test_jvp_vjp_products_options_batches_and_validation():
+    from ml_framework_b200.autograd.higher_order import JacobianVectorProduct as JVP, JVPOptions, VectorJacobianProduct as VJP, VJPOptions
+    torch.manual_seed(0)
+    A = torch.randn(3, 4, dtype=torch.float64)
+    f = lambda x: torch.tanh(A @ x)                                     # noqa: E731
+    x, v, u = torch.randn(4, dtype=torch.float64), torch.randn(4, dtype=torch.float64), torch.randn(3, dtype=torch.float64)
+    J = torch.autograd.functional.jacobian(f, x)
+    torch.testing.assert_close(JVP.compute(f, x, v), J @ v)
+    torch.testing.assert_close(VJP.compute(f, x, u), u @ J)
+    torch.testing.assert_close(JVP.compute_jacobian(f, x), J)
+    assert JVP.validate(f, x, v) and VJP.validate(f, x, u)
+    torch.testing.assert_close(JVP.compute_numerical(f, x, v), J @ v, rtol=1e-6, atol=1e-8)
+    # zero vectors short-circuit; buffers are filled in place
+    calls = []
+    g = lambda t: (calls.append(1), f(t))[1]                            # noqa: E731
+    assert float(JVP.compute(g, x, torch.zeros_like(x)).abs().sum()) == 0 and float(VJP.compute(g, x, torch.zeros(3, dtype=torch.float64)).abs().sum()) == 0
+    assert len(calls) == 1                                              # one plain forward for the shape; the pull-back needs none
+    buf = torch.empty(3, dtype=torch.float64)
+    assert JVP.compute(f, x, v, JVPOptions(output_buffer=buf)) is buf and torch.allclose(buf, J @ v)
+    with pytest.raises(ValueError):
+        JVP.compute(f, x, v, JVPOptions(output_buffer=torch.empty(2, dtype=torch.float64)))
+    with pytest.raises(ValueError):
+        JVP.compute(f, x, torch.ones(3, dtype=torch.float64))
+    with pytest.raises(ValueError):
+        VJP.compute(f, x, torch.ones(4, dtype=torch.float64))
+    # caches
+    JVP.clear_tangent_cache(); VJP.clear_gradient_cache()
+    JVP.compute(f, x, v, JVPOptions(cache_tangents=True)); JVP.compute(f, x, v, JVPOptions(cache_tangents=True))
+    VJP.compute(f, x, u, VJPOptions(cache_gradients=True))
+    assert JVP.get_cache_size() == 1 and VJP.get_cache_size() == 1
+    JVP.compute(f, x, v, JVPOptions(clear_cache=True))
+    assert JVP.get_cache_size() == 0
+    # batches: vectorised, chunked and looped agree
+    vs = [torch.randn(4, dtype=torch.float64) for _ in range(5)]
+    us = [torch.randn(3, dtype=torch.float64) for _ in range(5)]
+    for opts_j, opts_v in ((None, None), (JVPOptions(max_parallel_tasks=2), VJPOptions(max_parallel_tasks=2)),
+                           (JVPOptions(enable_parallel=False), VJPOptions(enable_parallel=False))):
+        for got, vec in zip(JVP.compute_batch(f, x, vs, opts_j), vs):
+            torch.testing.assert_close(got, J @ vec)
+        for got, vec in zip(VJP.compute_batch(f, x, us, opts_v), us):
+            torch.testing.assert_close(got, vec @ J)
+    assert JVP.compute_batch(f, x, []) == [] and VJP.compute_batch(f, x, []) == []
+    # several inputs
+    h = lambda ts: ts[0] * ts[1].sin()                                  # noqa: E731
+    a, b, t = torch.randn(4, dtype=torch.float64), torch.randn(4, dtype=torch.float64), torch.randn(4, dtype=torch.float64)
+    torch.testing.assert_close(JVP.compute_multiple(h, [a, b], t, input_index=1), a * b.cos() * t)
+    da, db = VJP.compute_multiple(h, [a, b], t)
+    torch.testing.assert_close(da, t * b.sin()); torch.testing.assert_close(db, t * a * b.cos())
+    with pytest.raises(IndexError):
+        JVP.compute_multiple(h, [a, b], t, input_index=2)
