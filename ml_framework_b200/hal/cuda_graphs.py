@@ -97,6 +97,166 @@ _NODE_TO_OP = {"kernel": "kernel", "memcpy": "memcpy", "memset": "memset", "host
                "mem_alloc": "alloc", "mem_free": "free", "batch_mem_op": "memset", "conditional": "branch"}
 
 
+class ValidationRule:
+    """One check over the operations of a capture (Graphs/Validation/IValidationRule.cs)."""
+
+    rule_name = "rule"
+    description = ""
+
+    def validate(self, ops: Sequence[CapturedOp]) -> List[ValidationIssue]:
+        raise NotImplementedError
+
+    def _each(self, ops, kinds, message: str, severity=ValidationSeverity.ERROR) -> List[ValidationIssue]:
+        return [ValidationIssue(self.rule_name, f"{op.name}: {message}", severity) for op in ops if op.kind in kinds]
+
+
+class EmptyGraphRule(ValidationRule):
+    rule_name, description = "EmptyGraph", "a capture must record at least one operation"
+
+    def validate(self, ops):
+        return [] if ops else [ValidationIssue(self.rule_name, "capture recorded no operations")]
+
+
+class DynamicMemoryRule(ValidationRule):
+    rule_name, description = "DynamicMemory", "device memory may not be allocated or freed inside a capture"
+
+    def validate(self, ops):
+        return self._each(ops, ("alloc", "free"), "device memory management inside a capture")
+
+
+class ControlFlowRule(ValidationRule):
+    rule_name, description = "ControlFlow", "host control flow on device data cannot be replayed"
+
+    def validate(self, ops):
+        return self._each(ops, ("branch",), "data-dependent host control flow cannot be replayed")
+
+
+class IOOperationRule(ValidationRule):
+    rule_name, description = "IOOperation", "host input / output does not belong in a capture"
+
+    def validate(self, ops):
+        return self._each(ops, ("io",), "host I/O inside a capture")
+
+
+class SynchronizationRule(ValidationRule):
+    rule_name, description = "Synchronization", "device or stream synchronisation ends a capture"
+
+    def validate(self, ops):
+        return self._each(ops, ("sync",), "device / stream synchronisation inside a capture")
+
+
+class HostCallbackRule(ValidationRule):
+    rule_name, description = "HostCallback", "host callbacks serialise the replay on the CPU"
+
+    def validate(self, ops):
+        return self._each(ops, ("host",), "host callback", ValidationSeverity.WARNING)
+
+
+class CrossStreamEventRule(ValidationRule):
+    rule_name, description = "CrossStreamEvent", "event nodes show that a side stream joined the capture"
+
+    def validate(self, ops):
+        return self._each(ops, ("event",), "event node (a side stream joined the capture)", ValidationSeverity.WARNING)
+
+
+def default_validation_rules() -> List[ValidationRule]:
+    return [EmptyGraphRule(), DynamicMemoryRule(), ControlFlowRule(), IOOperationRule(), SynchronizationRule(),
+            HostCallbackRule(), CrossStreamEventRule()]
+
+
+@dataclass
+class CUDAGraphValidationResult:
+    is_valid: bool
+    errors: List[str]
+    warnings: List[str]
+    operation_count: int = 0
+
+    @classmethod
+    def success(cls, operation_count: int):
+        return cls(True, [], [], operation_count)
+
+    @classmethod
+    def failure(cls, errors: Sequence[str], operation_count: int = 0):
+        return cls(False, list(errors), [], operation_count)
+
+
+class CUDAGraphValidationContext:
+    """Collects what a capture does while it is being described: operation names with their kinds and the
+    addresses it allocates (Graphs/Validation/CUDAGraphValidationContext.cs); ``ops()`` feeds a validator."""
+
+    def __init__(self):
+        self._ops: List[CapturedOp] = []
+        self._memory: set = set()
+        self._counts: Dict[str, int] = {}
+
+    def record_operation(self, name: str, kind: str = "kernel") -> None:
+        if not name:
+            return
+        self._ops.append(CapturedOp(name, kind))
+        self._counts[name] = self._counts.get(name, 0) + 1
+
+    def record_memory_allocation(self, ptr: int) -> None:
+        if ptr:
+            self._memory.add(int(ptr))
+            self._ops.append(CapturedOp(f"alloc@{int(ptr):#x}", "alloc"))
+
+    @property
+    def captured_operations(self) -> List[str]:
+        return [o.name for o in self._ops if o.kind != "alloc" or not o.name.startswith("alloc@")]
+
+    @property
+    def allocated_memory(self) -> frozenset:
+        return frozenset(self._memory)
+
+    @property
+    def operation_counts(self) -> Dict[str, int]:
+        return dict(self._counts)
+
+    def get_operation_count(self, name: str) -> int:
+        return self._counts.get(name, 0)
+
+    def has_operation(self, name: str) -> bool:
+        return name in self._counts
+
+    def ops(self) -> List[CapturedOp]:
+        return list(self._ops)
+
+    def clear(self) -> None:
+        self._ops.clear(); self._memory.clear(); self._counts.clear()
+
+
+class GraphPhase(enum.Enum):
+    """Which part of a training step a capture covers (Graphs/GraphPhase.cs)."""
+    FORWARD = "forward"
+    BACKWARD = "backward"
+    OPTIMIZER_STEP = "optimizer_step"
+    FORWARD_BACKWARD = "forward_backward"
+    FULL_TRAINING_STEP = "full_training_step"
+
+
+class CUDAGraphState(enum.Enum):
+    CREATED = "created"
+    CAPTURING = "capturing"
+    READY = "ready"
+    EXECUTING = "executing"
+    INVALIDATED = "invalidated"
+    DISPOSED = "disposed"
+
+
+class CUDAGraphFallbackStrategy(enum.Enum):
+    NEVER_CAPTURE = "never_capture"                    # always the eager path
+    CAPTURE_OR_FALLBACK = "capture_or_fallback"        # try the graph every call; on failure run eagerly
+    CAPTURE_ONLY = "capture_only"                      # failures propagate
+    TRY_ONCE_THEN_FALLBACK = "try_once_then_fallback"  # one failure switches to eager for good
+    RETRY_THEN_FALLBACK = "retry_then_fallback"        # ``max_failures`` consecutive failures switch to eager
+
+
+class CUDAGraphCaptureException(RuntimeError):
+    def __init__(self, message: str, graph_name: str = "", cause: Optional[BaseException] = None):
+        super().__init__(f"{graph_name}: {message}" if graph_name else message)
+        self.graph_name, self.cause = graph_name, cause
+
+
 class GraphValidator:
     """Rules over the operations of a capture: a graph must not be empty, allocate or free device memory,
     depend on host-side control flow, perform host I/O, or synchronise the device.
@@ -120,25 +280,31 @@ class GraphValidator:
             issues.append(ValidationIssue("EmptyGraph", "capture holds no kernel, copy or memset node"))
         return issues
 
+    def __init__(self, rules: Optional[Sequence["ValidationRule"]] = None):
+        self.rules: List[ValidationRule] = list(rules) if rules is not None else default_validation_rules()
+
+    def add_rule(self, rule: "ValidationRule") -> None:
+        if any(r.rule_name == rule.rule_name for r in self.rules):
+            raise ValueError(f"a rule named {rule.rule_name!r} is already installed")
+        self.rules.append(rule)
+
+    def remove_rule(self, rule_name: str) -> bool:
+        n = len(self.rules)
+        self.rules = [r for r in self.rules if r.rule_name != rule_name]
+        return len(self.rules) < n
+
     def validate(self, ops: Sequence[CapturedOp]) -> List[ValidationIssue]:
         issues: List[ValidationIssue] = []
-        if not ops:
-            issues.append(ValidationIssue("EmptyGraph", "capture recorded no operations"))
-        for op in ops:
-            if op.kind in ("alloc", "free"):
-                issues.append(ValidationIssue("DynamicMemory", f"{op.name}: device memory management inside a capture"))
-            elif op.kind == "branch":
-                issues.append(ValidationIssue("ControlFlow", f"{op.name}: data-dependent host control flow cannot be replayed"))
-            elif op.kind == "io":
-                issues.append(ValidationIssue("IOOperation", f"{op.name}: host I/O inside a capture"))
-            elif op.kind == "sync":
-                issues.append(ValidationIssue("Synchronization", f"{op.name}: device / stream synchronisation inside a capture"))
-            elif op.kind == "host":
-                issues.append(ValidationIssue("HostCallback", f"{op.name}: host callback", ValidationSeverity.WARNING))
-            elif op.kind == "event":
-                issues.append(ValidationIssue("CrossStreamEvent", f"{op.name}: event node (a side stream joined the capture)",
-                                              ValidationSeverity.WARNING))
+        for rule in self.rules:
+            issues += rule.validate(ops)
         return issues
+
+    def validation_result(self, ops: Sequence[CapturedOp]) -> "CUDAGraphValidationResult":
+        """Errors and warnings as text, with the operation count (CUDAGraphValidationResult.cs)."""
+        issues = self.validate(ops)
+        errors = [f"[{i.rule}] {i.message}" for i in issues if i.severity == ValidationSeverity.ERROR]
+        warnings = [f"[{i.rule}] {i.message}" for i in issues if i.severity == ValidationSeverity.WARNING]
+        return CUDAGraphValidationResult(not errors, errors, warnings, len(ops))
 
     def is_valid(self, ops: Sequence[CapturedOp]) -> bool:
         return not any(i.severity == ValidationSeverity.ERROR for i in self.validate(ops))
@@ -279,7 +445,11 @@ class CUDAGraphFallbackHandler:
     failure by exception type, and stop trying the graph path after ``max_failures`` consecutive failures
     (src/MLFramework/HAL/CUDA/Graphs/Fallback/CUDAGraphFallbackHandler.cs:56)."""
 
-    def __init__(self, max_failures: int = 3, on_fallback: Optional[Callable[[BaseException], None]] = None):
+    def __init__(self, max_failures: int = 3, on_fallback: Optional[Callable[[BaseException], None]] = None,
+                 strategy: CUDAGraphFallbackStrategy = CUDAGraphFallbackStrategy.RETRY_THEN_FALLBACK):
+        self.strategy = strategy
+        if strategy is CUDAGraphFallbackStrategy.TRY_ONCE_THEN_FALLBACK:
+            max_failures = 1
         self.max_failures, self.on_fallback = max_failures, on_fallback
         self.consecutive_failures = 0
         self.total_fallbacks = 0
@@ -289,6 +459,11 @@ class CUDAGraphFallbackHandler:
 
     @property
     def graph_path_enabled(self) -> bool:
+        S = CUDAGraphFallbackStrategy
+        if self.strategy is S.NEVER_CAPTURE:
+            return False
+        if self.strategy in (S.CAPTURE_OR_FALLBACK, S.CAPTURE_ONLY):
+            return True
         return self.consecutive_failures < self.max_failures
 
     def execute_with_fallback(self, graph_fn: Callable, eager_fn: Callable):
@@ -296,9 +471,12 @@ class CUDAGraphFallbackHandler:
             try:
                 out = graph_fn()
                 self.successes += 1
-                self.consecutive_failures = 0
+                if self.strategy is not CUDAGraphFallbackStrategy.TRY_ONCE_THEN_FALLBACK:
+                    self.consecutive_failures = 0
                 return out
             except Exception as e:       # noqa: BLE001 - any capture / replay failure goes to the eager path
+                if self.strategy is CUDAGraphFallbackStrategy.CAPTURE_ONLY:
+                    raise CUDAGraphCaptureException(str(e), cause=e) from e
                 self.consecutive_failures += 1
                 self.by_type[type(e).__name__] = self.by_type.get(type(e).__name__, 0) + 1
                 self.last_error = e

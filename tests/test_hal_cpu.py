@@ -193,3 +193,60 @@ def test_graph_fallback_handler_proxy_allocator_and_static_facade():
     assert torch.equal(cg.CUDAGraphStatic.run("dbl", f, x), x * 2)
     cg.CUDAGraphStatic.configure(cg.CaptureOptions())
     cg.CUDAGraphStatic.reset()
+
+
+def test_graph_validation_rules_context_result_and_fallback_strategies():
+    from ml_framework_b200.hal import cuda_graphs as cg
+    ctx = cg.CUDAGraphValidationContext()
+    for name, kind in (("gemm", "kernel"), ("gemm", "kernel"), ("print", "io"), ("if x.item()", "branch"), ("cudaDeviceSynchronize", "sync"),
+                       ("callback", "host"), ("", "kernel")):
+        ctx.record_operation(name, kind)
+    ctx.record_memory_allocation(0x7000)
+    ctx.record_memory_allocation(0)
+    assert ctx.get_operation_count("gemm") == 2 and ctx.has_operation("print") and not ctx.has_operation("nope")
+    assert ctx.allocated_memory == frozenset({0x7000}) and len(ctx.captured_operations) == 6 and ctx.operation_counts["gemm"] == 2
+    v = cg.GraphValidator()
+    res = v.validation_result(ctx.ops())
+    assert not res.is_valid and res.operation_count == 7 and len(res.errors) == 4 and len(res.warnings) == 1
+    assert {e.split("]")[0][1:] for e in res.errors} == {"IOOperation", "ControlFlow", "Synchronization", "DynamicMemory"}
+    assert v.validation_result([]).errors == ["[EmptyGraph] capture recorded no operations"]
+    assert [r.rule_name for r in v.rules][:5] == ["EmptyGraph", "DynamicMemory", "ControlFlow", "IOOperation", "Synchronization"]
+    assert all(r.description for r in v.rules)
+
+    class TooManyKernels(cg.ValidationRule):
+        rule_name, description = "KernelBudget", "a capture should stay small"
+
+        def validate(self, ops):
+            n = sum(o.kind == "kernel" for o in ops)
+            return [cg.ValidationIssue(self.rule_name, f"{n} kernels", cg.ValidationSeverity.WARNING)] if n > 1 else []
+    v.add_rule(TooManyKernels())
+    with pytest.raises(ValueError):
+        v.add_rule(TooManyKernels())
+    assert any("KernelBudget" in w for w in v.validation_result(ctx.ops()).warnings)
+    assert v.remove_rule("IOOperation") and not v.remove_rule("IOOperation") and len(v.validation_result(ctx.ops()).errors) == 3
+    only = cg.GraphValidator([cg.EmptyGraphRule()])
+    assert only.is_valid(ctx.ops())
+    ctx.clear()
+    assert ctx.ops() == [] and cg.CUDAGraphValidationResult.success(3).is_valid and not cg.CUDAGraphValidationResult.failure(["x"]).is_valid
+    assert cg.GraphPhase.FULL_TRAINING_STEP.value == "full_training_step" and cg.CUDAGraphState.INVALIDATED.value == "invalidated"
+
+    S = cg.CUDAGraphFallbackStrategy
+
+    def boom():
+        raise RuntimeError("capture failed")
+    never = cg.CUDAGraphFallbackHandler(strategy=S.NEVER_CAPTURE)
+    assert never.execute_with_fallback(boom, lambda: "eager") == "eager" and never.by_type == {}
+    always = cg.CUDAGraphFallbackHandler(max_failures=1, strategy=S.CAPTURE_OR_FALLBACK)
+    for _ in range(3):
+        assert always.execute_with_fallback(boom, lambda: "eager") == "eager"
+    assert always.by_type == {"RuntimeError": 3} and always.graph_path_enabled          # keeps trying
+    strict = cg.CUDAGraphFallbackHandler(strategy=S.CAPTURE_ONLY)
+    with pytest.raises(cg.CUDAGraphCaptureException, match="capture failed"):
+        strict.execute_with_fallback(boom, lambda: "eager")
+    once = cg.CUDAGraphFallbackHandler(max_failures=5, strategy=S.TRY_ONCE_THEN_FALLBACK)
+    assert once.execute_with_fallback(lambda: "graph", lambda: "eager") == "graph"
+    assert once.execute_with_fallback(boom, lambda: "eager") == "eager" and not once.graph_path_enabled
+    assert once.execute_with_fallback(lambda: "graph", lambda: "eager") == "eager"
+    retry = cg.CUDAGraphFallbackHandler(max_failures=2)
+    retry.execute_with_fallback(boom, lambda: 0); assert retry.graph_path_enabled
+    retry.execute_with_fallback(boom, lambda: 0); assert not retry.graph_path_enabled
