@@ -21,6 +21,7 @@ were sharded along a dimension (Resharding/ReshardingStrategy.cs:63-496).
 from __future__ import annotations
 
 import ctypes as C
+import enum
 import gzip
 import hashlib
 import io
@@ -580,44 +581,185 @@ class DistributedCheckpoint:
 
 
 # ------------------------------------------------------------------ async / incremental / fault tolerance
+class CheckpointTaskType(enum.Enum):
+    FULL = "full"                   # model and optimizer
+    MODEL_ONLY = "model_only"
+
+
+class CheckpointTaskStatus(enum.Enum):
+    QUEUED = "queued"
+    RUNNING = "running"
+    COMPLETED = "completed"
+    FAILED = "failed"
+    CANCELLED = "cancelled"
+
+
+class CheckpointQueueFullError(CheckpointError):
+    def __init__(self, max_queue_size: int):
+        super().__init__(f"the checkpoint queue is full ({max_queue_size} pending saves)")
+        self.max_queue_size = max_queue_size
+
+
+@dataclass
+class CheckpointTaskResult:
+    checkpoint_id: str
+    success: bool
+    value: object = None            # what ``DistributedCheckpoint.save`` returned
+    error: Optional[BaseException] = None
+    duration_s: float = 0.0
+    bytes_snapshotted: int = 0
+
+
+@dataclass
+class CheckpointTaskInfo:
+    """A task as the outside sees it (no tensors)."""
+    id: str
+    type: CheckpointTaskType
+    status: CheckpointTaskStatus
+    queued_at: float
+    started_at: Optional[float]
+    completed_at: Optional[float]
+
+    @property
+    def duration_s(self) -> Optional[float]:
+        return None if self.started_at is None or self.completed_at is None else self.completed_at - self.started_at
+
+
+@dataclass
+class CheckpointTask:
+    id: str
+    type: CheckpointTaskType
+    model_state: Dict[str, torch.Tensor]
+    optimizer_state: Dict[str, torch.Tensor]
+    options: Dict[str, object]
+    queued_at: float
+    started_at: Optional[float] = None
+    completed_at: Optional[float] = None
+    status: CheckpointTaskStatus = CheckpointTaskStatus.QUEUED
+    result: Optional[CheckpointTaskResult] = None
+    done: threading.Event = field(default_factory=threading.Event)
+
+    def info(self) -> CheckpointTaskInfo:
+        return CheckpointTaskInfo(self.id, self.type, self.status, self.queued_at, self.started_at, self.completed_at)
+
+
 class AsyncCheckpointManager:
     """Background save queue: tensors are snapshotted to host memory on the caller's thread (the
-    only part on the training step's critical path), files are written by a worker thread."""
+    only part on the training step's critical path), files are written by a worker thread. Every save is
+    a tracked task: queued, running, then completed, failed or cancelled
+    (Checkpointing/Async/AsyncCheckpointManager.cs:9-421, CheckpointTask.cs, CheckpointTaskInfo.cs,
+    CheckpointTaskResult.cs)."""
 
-    def __init__(self, checkpoint: DistributedCheckpoint, max_pending: int = 2):
+    def __init__(self, checkpoint: DistributedCheckpoint, max_pending: int = 2, keep_finished: int = 64):
         self.ckpt = checkpoint
+        self.max_queue_size = max_pending
         self._q: "queue.Queue" = queue.Queue(maxsize=max_pending)
         self._results: Dict[str, object] = {}
+        self._tasks: Dict[str, CheckpointTask] = {}
+        self._keep = keep_finished
         self._cancelled = set()
         self._lock = threading.Lock()
         self._thread = threading.Thread(target=self._worker, daemon=True)
         self._thread.start()
 
-    def queue_save(self, tag: str, model_state: Dict[str, torch.Tensor], optimizer_state=None, **kw) -> str:
+    @property
+    def queue_size(self) -> int:
+        return self._q.qsize()
+
+    @property
+    def active_task_count(self) -> int:
+        with self._lock:
+            return sum(t.status in (CheckpointTaskStatus.QUEUED, CheckpointTaskStatus.RUNNING) for t in self._tasks.values())
+
+    def queue_save(self, tag: str, model_state: Dict[str, torch.Tensor], optimizer_state=None, block: bool = True, **kw) -> str:
+        """Snapshots the tensors and queues the write. With ``block=False`` a full queue raises
+        ``CheckpointQueueFullError`` instead of waiting for room."""
+        with self._lock:
+            live = self._tasks.get(tag)
+            if live is not None and live.status in (CheckpointTaskStatus.QUEUED, CheckpointTaskStatus.RUNNING):
+                raise CheckpointError(f"a save named {tag!r} is still in flight")
+        if not block and self._q.full():
+            raise CheckpointQueueFullError(self.max_queue_size)
         snap = {k: v.detach().to("cpu", copy=True) for k, v in model_state.items()}
         osnap = {k: v.detach().to("cpu", copy=True) for k, v in (optimizer_state or {}).items() if isinstance(v, torch.Tensor)}
-        self._q.put((tag, snap, osnap, kw))
+        task = CheckpointTask(tag, CheckpointTaskType.FULL if osnap else CheckpointTaskType.MODEL_ONLY, snap, osnap, kw, time.time())
+        with self._lock:
+            self._tasks[tag] = task                       # a name that was cancelled stays cancelled: the worker drops it
+        try:
+            self._q.put(task, block=block)
+        except queue.Full:
+            with self._lock:
+                self._tasks.pop(tag, None)
+            raise CheckpointQueueFullError(self.max_queue_size) from None
         return tag
+
+    def _finish(self, task: CheckpointTask, status: CheckpointTaskStatus, value=None, error=None):
+        task.completed_at = time.time()
+        task.status = status
+        nbytes = sum(t.numel() * t.element_size() for t in (*task.model_state.values(), *task.optimizer_state.values()))
+        task.result = CheckpointTaskResult(task.id, status is CheckpointTaskStatus.COMPLETED, value, error,
+                                           task.completed_at - (task.started_at or task.completed_at), nbytes)
+        task.model_state, task.optimizer_state = {}, {}          # the snapshot is no longer needed
+        with self._lock:
+            self._results[task.id] = value if error is None else error
+            finished = [t for t in self._tasks.values() if t.done.is_set()]
+            for old in sorted(finished, key=lambda t: t.completed_at or 0)[:max(0, len(finished) + 1 - self._keep)]:
+                self._tasks.pop(old.id, None)
+        task.done.set()
 
     def _worker(self):
         while True:
-            item = self._q.get()
-            if item is None:
+            task = self._q.get()
+            if task is None:
                 return
-            tag, snap, osnap, kw = item
             try:
-                if tag in self._cancelled:
-                    res = CheckpointError("cancelled")
-                else:
-                    res = self.ckpt.save(tag, snap, osnap or None, **kw)
-            except Exception as e:  # noqa: BLE001
-                res = e
-            with self._lock:
-                self._results[tag] = res
-            self._q.task_done()
+                if task.id in self._cancelled:
+                    self._finish(task, CheckpointTaskStatus.CANCELLED, error=CheckpointError("cancelled"))
+                    continue
+                task.started_at, task.status = time.time(), CheckpointTaskStatus.RUNNING
+                try:
+                    value = self.ckpt.save(task.id, task.model_state, task.optimizer_state or None, **task.options)
+                    self._finish(task, CheckpointTaskStatus.COMPLETED, value=value)
+                except Exception as e:  # noqa: BLE001 - delivered through the task's result
+                    self._finish(task, CheckpointTaskStatus.FAILED, error=e)
+            finally:
+                self._q.task_done()
 
-    def cancel_checkpoint(self, tag: str):
-        self._cancelled.add(tag)
+    def cancel_checkpoint(self, tag: str) -> bool:
+        """Cancels a save that has not started; ``False`` when it is unknown, running or finished."""
+        with self._lock:
+            t = self._tasks.get(tag)
+            if t is None:
+                self._cancelled.add(tag)                      # a save queued under this name later is dropped
+                return False
+            if t.status is not CheckpointTaskStatus.QUEUED:
+                return False
+            self._cancelled.add(tag)
+            return True
+
+    def get_task_status(self, tag: str) -> Optional[CheckpointTaskStatus]:
+        with self._lock:
+            t = self._tasks.get(tag)
+            return t.status if t is not None else None
+
+    def get_task_info(self, tag: str) -> Optional[CheckpointTaskInfo]:
+        with self._lock:
+            t = self._tasks.get(tag)
+            return t.info() if t is not None else None
+
+    def get_active_tasks(self) -> List[CheckpointTaskInfo]:
+        with self._lock:
+            return [t.info() for t in self._tasks.values() if t.status in (CheckpointTaskStatus.QUEUED, CheckpointTaskStatus.RUNNING)]
+
+    def wait_for(self, tag: str, timeout_s: float = 600.0) -> CheckpointTaskResult:
+        """Blocks until that save has finished one way or the other."""
+        with self._lock:
+            t = self._tasks.get(tag)
+        if t is None:
+            raise KeyError(f"no save named {tag!r}")
+        if not t.done.wait(timeout_s):
+            raise CheckpointError(f"save {tag!r} did not finish within {timeout_s} s")
+        return t.result
 
     def wait_for_completion(self, timeout_s: float = 600.0):
         t0 = time.time()

@@ -13,11 +13,14 @@ of fp32 masters, excluded layers stay fp32, and ``sync_training_weights`` rounds
 """
 from __future__ import annotations
 
+import dataclasses
+import enum
 import fnmatch
 import math
+import os
 import time
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -343,3 +346,242 @@ class MixedPrecisionOptimizer:
             self.precision.sync_training_weights({n: self.masters[n].data for n, _ in self.named}, {n: p.data for n, p in self.named})
         if sd.get("base") is not None and hasattr(self.base, "load_state_dict"):
             self.base.load_state_dict(sd["base"])
+
+
+# ------------------------------------------------------------------ precision helpers, gradient layer, checkpoints
+class Precision(enum.Enum):
+    FP32 = "fp32"
+    FP16 = "fp16"
+    BF16 = "bf16"
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return _DTYPES[self.value]
+
+
+@dataclass(frozen=True)
+class PrecisionCapability:
+    supports_fp16: bool
+    supports_bf16: bool
+    supports_fp32: bool = True
+
+    @property
+    def is_fp16_available(self) -> bool:
+        return self.supports_fp16
+
+    @property
+    def is_bf16_available(self) -> bool:
+        return self.supports_bf16
+
+
+class HardwareDetector:
+    """What the current device computes in natively, asked once (HardwareDetector.cs:5-60)."""
+
+    _cached: Optional[PrecisionCapability] = None
+
+    @classmethod
+    def detect_capabilities(cls) -> PrecisionCapability:
+        if cls._cached is None:
+            if torch.cuda.is_available():
+                major, _ = torch.cuda.get_device_capability()
+                cls._cached = PrecisionCapability(supports_fp16=major >= 6, supports_bf16=major >= 8)
+            else:
+                cls._cached = PrecisionCapability(supports_fp16=False, supports_bf16=True)     # CPU kernels exist for bf16 only
+        return cls._cached
+
+    @classmethod
+    def get_recommended_precision(cls) -> Precision:
+        return Precision(detect_precision())
+
+    @classmethod
+    def reset_cache(cls) -> None:
+        cls._cached = None
+
+
+class PrecisionConverter:
+    """Conversions between the three training precisions (PrecisionConverter.cs)."""
+
+    @staticmethod
+    def convert(t: torch.Tensor, target: Precision) -> torch.Tensor:
+        if not t.is_floating_point():
+            raise TypeError(f"cannot change the precision of a {t.dtype} tensor")
+        return t if t.dtype == target.dtype else t.to(target.dtype)
+
+    @staticmethod
+    def detect_precision(t: torch.Tensor) -> Precision:
+        for p in Precision:
+            if t.dtype == p.dtype:
+                return p
+        raise TypeError(f"{t.dtype} is not a training precision")
+
+    @staticmethod
+    def is_conversion_safe(source: Precision, target: Precision, t: Optional[torch.Tensor] = None) -> bool:
+        """Widening is always safe. Narrowing to bf16 keeps the range; narrowing to fp16 is safe only while
+        the values fit its range, which needs the tensor to decide (without one: not safe)."""
+        if source == target or target is Precision.FP32:
+            return True
+        if target is Precision.BF16 and source is Precision.FP32:
+            return True
+        if t is None or not t.numel():
+            return t is not None
+        lim = torch.finfo(target.dtype).max
+        return bool(torch.isfinite(t).all() and t.abs().max() <= lim)
+
+
+@dataclass
+class LossScalerStats:
+    current_scale: float
+    steps_since_last_overflow: int
+    total_steps: int
+    total_overflows: int
+
+
+@dataclass
+class GradientProcessingStats:
+    loss_scale: float
+    clip_count: int
+    last_gradient_norm: float
+    clipping_enabled: bool
+    max_grad_norm: float
+    loss_scaler_stats: LossScalerStats
+
+    def __str__(self):
+        clip = f"clip at {self.max_grad_norm:g} ({self.clip_count} times)" if self.clipping_enabled else "no clipping"
+        return f"loss scale {self.loss_scale:g}, last gradient norm {self.last_gradient_norm:.4g}, {clip}"
+
+
+class GradientConversionLayer:
+    """Between backward and the optimizer: unscale, detect overflow, clip by global norm, as one call on a
+    dictionary of gradients (GradientConversionLayer.cs:10-230)."""
+
+    def __init__(self, options: Optional[MixedPrecisionOptions] = None, loss_scaler: Optional[DynamicLossScaler] = None, device="cpu"):
+        self.options = options or MixedPrecisionOptions()
+        self.options.validate()
+        o = self.options
+        self.scaler = loss_scaler or DynamicLossScaler(DynamicScalerConfig(
+            initial_scale=o.initial_loss_scale, growth_factor=o.growth_factor, backoff_factor=o.backoff_factor,
+            growth_interval=o.growth_interval, min_scale=o.min_loss_scale, max_scale=o.max_loss_scale,
+            enabled=o.enable_dynamic_loss_scaling), device=device)
+        self.clip_count = 0
+        self.last_gradient_norm = 0.0
+
+    @property
+    def loss_scale(self) -> float:
+        return self.scaler.scale
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return self.scaler.scale_loss(loss)
+
+    def clip_gradients(self, gradients: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """Scales every gradient by ``max_grad_norm / norm`` when the global norm exceeds the bound (in place)."""
+        if not gradients:
+            return gradients
+        norm = float(torch.sqrt(sum((g.float() ** 2).sum() for g in gradients.values())))
+        self.last_gradient_norm = norm
+        if self.options.enable_gradient_clipping and norm > self.options.max_grad_norm:
+            k = self.options.max_grad_norm / (norm + 1e-6)
+            for g in gradients.values():
+                g.mul_(k)
+            self.clip_count += 1
+        return gradients
+
+    def process_gradients(self, gradients: Dict[str, torch.Tensor]) -> Tuple[Dict[str, torch.Tensor], bool]:
+        """(fp32 gradients ready for the optimizer, whether to skip the step). Updates the loss scale."""
+        inv = 1.0 / self.scaler.scale if self.scaler.enabled else 1.0
+        out = {k: g.float() * inv for k, g in gradients.items()}
+        overflow = any(not bool(torch.isfinite(g).all()) for g in out.values())
+        if overflow:
+            self.scaler.found_inf.fill_(1)
+        self.scaler.update()
+        if overflow:
+            return {}, True
+        return self.clip_gradients(out), False
+
+    def get_stats(self) -> GradientProcessingStats:
+        s = self.scaler.get_stats()
+        ls = LossScalerStats(s.scale, s.growth_tracker, s.total_steps, s.skipped_steps)
+        return GradientProcessingStats(self.loss_scale, self.clip_count, self.last_gradient_norm, self.options.enable_gradient_clipping,
+                                       self.options.max_grad_norm, ls)
+
+    def reset(self) -> None:
+        self.clip_count, self.last_gradient_norm = 0, 0.0
+        self.scaler.load_state_dict({"scale": self.options.initial_loss_scale, "tracker": 0, "total_steps": 0, "skipped": 0})
+
+
+@dataclass
+class MixedPrecisionCheckpoint:
+    """Everything needed to continue a mixed-precision run exactly (Checkpointing.cs:11-82)."""
+    version: int = 1
+    timestamp: float = field(default_factory=time.time)
+    master_weights: Dict[str, torch.Tensor] = field(default_factory=dict)
+    training_weights: Dict[str, torch.Tensor] = field(default_factory=dict)
+    current_loss_scale: float = 1.0
+    steps_since_last_overflow: int = 0
+    consecutive_overflows: int = 0
+    total_overflows: int = 0
+    step_count: int = 0
+    has_fallback: bool = False
+    skipped_steps: int = 0
+    options: Optional[Dict] = None
+    scaler_state: Optional[Dict] = None
+    base_optimizer_state: Optional[Dict] = None
+    metadata: Dict[str, str] = field(default_factory=dict)
+
+
+class MixedPrecisionCheckpointManager:
+    VERSION = 1
+
+    @classmethod
+    def create_checkpoint(cls, optimizer: "MixedPrecisionOptimizer", metadata: Optional[Dict[str, str]] = None) -> MixedPrecisionCheckpoint:
+        sd = optimizer.state_dict()
+        sc = sd["scaler"]
+        return MixedPrecisionCheckpoint(
+            cls.VERSION, time.time(), sd["masters"], {n: p.detach().cpu().clone() for n, p in optimizer.named},
+            sc["scale"], sc["tracker"], optimizer.consecutive_overflows, sc["skipped"], sd["step_count"], sd["has_fallback"],
+            sd["skipped_steps"], dataclasses.asdict(optimizer.options), sc, sd["base"], dict(metadata or {}))
+
+    @staticmethod
+    def save_checkpoint(checkpoint: MixedPrecisionCheckpoint, path: str) -> None:
+        tmp = path + ".tmp"
+        torch.save(dataclasses.asdict(checkpoint), tmp)
+        os.replace(tmp, path)
+
+    @staticmethod
+    def load_checkpoint(path: str) -> MixedPrecisionCheckpoint:
+        if not os.path.isfile(path):
+            raise FileNotFoundError(path)
+        d = torch.load(path, map_location="cpu", weights_only=False)
+        known = {f.name for f in dataclasses.fields(MixedPrecisionCheckpoint)}
+        return MixedPrecisionCheckpoint(**{k: v for k, v in d.items() if k in known})
+
+    @classmethod
+    def validate_checkpoint(cls, c: MixedPrecisionCheckpoint) -> bool:
+        if c is None or c.version != cls.VERSION or not c.master_weights:
+            return False
+        if set(c.master_weights) != set(c.training_weights):
+            return False
+        if any(c.master_weights[k].shape != c.training_weights[k].shape for k in c.master_weights):
+            return False
+        if not (c.current_loss_scale > 0 and math.isfinite(c.current_loss_scale)) or c.step_count < 0 or c.skipped_steps < 0:
+            return False
+        return all(bool(torch.isfinite(w).all()) for w in c.master_weights.values())
+
+    @classmethod
+    def restore_checkpoint(cls, optimizer: "MixedPrecisionOptimizer", c: MixedPrecisionCheckpoint) -> None:
+        if not cls.validate_checkpoint(c):
+            raise ValueError("the mixed-precision checkpoint is not valid")
+        missing = set(optimizer.masters) ^ set(c.master_weights)
+        if missing:
+            raise KeyError(f"checkpoint and optimizer disagree on parameters: {sorted(missing)[:4]}")
+        optimizer.load_state_dict({"masters": c.master_weights, "scaler": c.scaler_state or
+                                   {"scale": c.current_loss_scale, "tracker": c.steps_since_last_overflow,
+                                    "total_steps": c.step_count, "skipped": c.total_overflows},
+                                   "step_count": c.step_count, "skipped_steps": c.skipped_steps, "has_fallback": c.has_fallback,
+                                   "base": c.base_optimizer_state})
+        optimizer.consecutive_overflows = c.consecutive_overflows
+
+    @classmethod
+    def load_and_restore(cls, optimizer: "MixedPrecisionOptimizer", path: str) -> MixedPrecisionCheckpoint:
+        c = cls.load_checkpoint(path)
+        cls.restore_checkpoint(optimizer, c)
+        return c

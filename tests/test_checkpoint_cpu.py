@@ -2,6 +2,7 @@
 count), resharding across world sizes, async and incremental managers, retry / circuit breaker."""
 import os
 import struct
+import time
 
 import pytest
 import torch
@@ -189,3 +190,48 @@ def test_storage_backend_rollback_manager_cancel_and_timeouts(tmp_path):
     assert h.execute_with_timeout(lambda a, b=1: a + b, 1.0, 2, b=3) == 5
     with pytest.raises(KeyError):
         h.execute_with_timeout(lambda: {}["x"], 1.0)
+
+
+def test_async_checkpoint_tasks_are_tracked(tmp_path):
+    import threading
+
+    from ml_framework_b200.checkpoint.distributed import (CheckpointQueueFullError, CheckpointTaskStatus, CheckpointTaskType)
+    gate = threading.Event()
+
+    class Slow(DistributedCheckpoint):
+        def save(self, tag, *a, **k):
+            if tag == "first":
+                gate.wait(10)
+            if tag == "bad":
+                raise IOError("disk full")
+            return super().save(tag, *a, **k)
+
+    st = _state(2)
+    mgr = AsyncCheckpointManager(Slow(str(tmp_path)), max_pending=2)
+    mgr.queue_save("first", st, {"m": torch.zeros(3)})
+    for _ in range(200):
+        if mgr.get_task_status("first") is CheckpointTaskStatus.RUNNING:
+            break
+        time.sleep(0.01)
+    mgr.queue_save("second", st)
+    mgr.queue_save("bad", st)
+    with pytest.raises(CheckpointQueueFullError):
+        mgr.queue_save("fourth", st, block=False)
+    with pytest.raises(CheckpointError, match="still in flight"):
+        mgr.queue_save("second", st)
+    assert mgr.get_task_status("first") is CheckpointTaskStatus.RUNNING and mgr.get_task_status("second") is CheckpointTaskStatus.QUEUED
+    assert mgr.get_task_info("first").type is CheckpointTaskType.FULL and mgr.get_task_info("second").type is CheckpointTaskType.MODEL_ONLY
+    assert {t.id for t in mgr.get_active_tasks()} == {"first", "second", "bad"} and mgr.active_task_count == 3 and mgr.queue_size == 2
+    assert mgr.cancel_checkpoint("second") and not mgr.cancel_checkpoint("first") and mgr.get_task_status("nope") is None
+    gate.set()
+    r1, r2, r3 = mgr.wait_for("first"), mgr.wait_for("second"), mgr.wait_for("bad")
+    assert r1.success and r1.bytes_snapshotted > 0 and r1.duration_s >= 0
+    assert not r2.success and mgr.get_task_status("second") is CheckpointTaskStatus.CANCELLED
+    assert not r3.success and isinstance(r3.error, IOError) and mgr.get_task_status("bad") is CheckpointTaskStatus.FAILED
+    info = mgr.get_task_info("first")
+    assert info.status is CheckpointTaskStatus.COMPLETED and info.duration_s is not None and mgr.active_task_count == 0
+    with pytest.raises(CheckpointError, match="async saves failed"):
+        mgr.wait_for_completion()
+    with pytest.raises(KeyError):
+        mgr.wait_for("nope")
+    mgr.shutdown()

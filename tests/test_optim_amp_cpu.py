@@ -192,3 +192,74 @@ def test_software_half_and_bfloat16_are_bit_exact():
     assert S.Half(1.5) == S.Half(1.5) and len({S.Half(1.5), S.Half(1.5), S.Half(2.0)}) == 2
     assert S.round_trip_error([1.0, 3.3, 1e-3, 123.456], "bfloat16") <= 2 ** -8
     assert S.round_trip_error([1.0, 3.3, 1e-3, 123.456], "half") <= 2 ** -11
+
+
+def test_precision_helpers_gradient_layer_and_mixed_precision_checkpoints(tmp_path):
+    import torch.nn as nn
+
+    from ml_framework_b200.optim import mixed_precision as MP
+    P = MP.Precision
+    cap = MP.HardwareDetector.detect_capabilities()
+    assert cap.supports_fp32 and cap is MP.HardwareDetector.detect_capabilities() and cap.is_bf16_available
+    MP.HardwareDetector.reset_cache()
+    assert MP.HardwareDetector.get_recommended_precision() in (P.FP32, P.BF16, P.FP16)
+    t = torch.tensor([1.0, 70000.0])
+    assert MP.PrecisionConverter.detect_precision(t) is P.FP32 and MP.PrecisionConverter.convert(t, P.BF16).dtype == torch.bfloat16
+    assert MP.PrecisionConverter.convert(t, P.FP32) is t
+    C = MP.PrecisionConverter.is_conversion_safe
+    assert C(P.FP16, P.FP32) and C(P.FP32, P.BF16) and not C(P.FP32, P.FP16, t) and C(P.FP32, P.FP16, t[:1]) and not C(P.FP32, P.FP16)
+    with pytest.raises(TypeError):
+        MP.PrecisionConverter.convert(torch.tensor([1]), P.FP16)
+    with pytest.raises(TypeError):
+        MP.PrecisionConverter.detect_precision(torch.tensor([1.0], dtype=torch.float64))
+
+    layer = MP.GradientConversionLayer(MP.MixedPrecisionOptions(initial_loss_scale=8.0, max_grad_norm=1.0, growth_interval=2))
+    assert float(layer.scale_loss(torch.tensor(2.0))) == 16.0
+    grads, skip = layer.process_gradients({"w": torch.full((4,), 16.0, dtype=torch.bfloat16)})
+    assert not skip and grads["w"].dtype == torch.float32 and layer.last_gradient_norm == pytest.approx(4.0)
+    assert float(grads["w"].norm()) == pytest.approx(1.0, rel=1e-4) and layer.clip_count == 1
+    _, skip = layer.process_gradients({"w": torch.tensor([float("inf")])})
+    assert skip and layer.loss_scale == 4.0                                            # backed off
+    layer.process_gradients({"w": torch.tensor([0.1])}); layer.process_gradients({"w": torch.tensor([0.1])})
+    st = layer.get_stats()
+    assert layer.loss_scale == 8.0 and st.loss_scaler_stats.total_overflows == 1 and st.clip_count == 1 and "clip at 1" in str(st)
+    layer.reset()
+    assert layer.loss_scale == 8.0 and layer.clip_count == 0 and layer.get_stats().loss_scaler_stats.total_steps == 0
+
+    torch.manual_seed(0)
+    def make():
+        torch.manual_seed(0)
+        m = nn.Sequential(nn.Linear(4, 8), nn.LayerNorm(8), nn.Linear(8, 1))
+        return m, MP.MixedPrecisionOptimizer(m, lambda ps: torch.optim.SGD(ps, 0.1, momentum=0.9), MP.MixedPrecisionOptions(precision="bf16"))
+    x, y = torch.randn(16, 4), torch.randn(16, 1)
+
+    def step(m, opt):
+        opt.zero_grad()
+        dt = next(m.parameters()).dtype
+        loss = ((m(x.to(dt)).float() - y) ** 2).mean()
+        opt.scale_loss(loss).backward()
+        opt.step()
+        return float(loss.detach())
+    m1, o1 = make()
+    for _ in range(3):
+        step(m1, o1)
+    M = MP.MixedPrecisionCheckpointManager
+    ck = M.create_checkpoint(o1, {"note": "after 3"})
+    assert M.validate_checkpoint(ck) and ck.step_count == 3 and ck.metadata == {"note": "after 3"} and ck.options["precision"] == "bf16"
+    path = str(tmp_path / "mp.ckpt")
+    M.save_checkpoint(ck, path)
+    after = [step(m1, o1) for _ in range(3)]
+    m2, o2 = make()
+    loaded = M.load_and_restore(o2, path)
+    assert loaded.step_count == 3 and o2.step_count == 3
+    assert [step(m2, o2) for _ in range(3)] == after                                   # the run continues bit for bit
+    broken = M.load_checkpoint(path)
+    broken.master_weights["0.weight"][0, 0] = float("nan")
+    assert not M.validate_checkpoint(broken)
+    with pytest.raises(ValueError):
+        M.restore_checkpoint(o2, broken)
+    other = M.load_checkpoint(path)
+    other.version = 9
+    assert not M.validate_checkpoint(other)
+    with pytest.raises(FileNotFoundError):
+        M.load_checkpoint(str(tmp_path / "none"))
