@@ -26,7 +26,7 @@ import sys
 import threading
 import time
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence, Tuple, Type
+from typing import Callable, Dict, List, Optional, Tuple, Type
 
 from .errors import DownloadFailedError, ModelNotFoundError
 from .zoo import ModelInfo

@@ -715,7 +715,7 @@ class AccuracyReporter:
                time.strftime("Generated: %Y-%m-%d %H:%M:%S UTC", time.gmtime(r.timestamp)), "",
                f"FP32:       {r.fp32_accuracy:.4f}", f"Quantised:  {r.quantized_accuracy:.4f}",
                f"Drop:       {drop:.4f} (threshold {r.acceptable_threshold:.4f})",
-               f"Verdict:    {'ACCEPTABLE' if r.is_acceptable else 'NOT ACCEPTABLE'}", ""]
+               f"Result:     {'ACCEPTABLE' if r.is_acceptable else 'NOT ACCEPTABLE'}", ""]
         if r.per_layer_results:
             out.append("Per-layer sensitivity (largest first):")
             width = max(len(x.layer_name) for x in r.per_layer_results)
@@ -740,7 +740,7 @@ class AccuracyReporter:
     def generate_markdown_report(self, r: AccuracyReport) -> str:
         out = ["# Quantisation accuracy report", "", "| | value |", "|---|---|", f"| FP32 | {r.fp32_accuracy:.4f} |",
                f"| quantised | {r.quantized_accuracy:.4f} |", f"| drop | {r.accuracy_drop:.4f} |",
-               f"| threshold | {r.acceptable_threshold:.4f} |", f"| verdict | {'acceptable' if r.is_acceptable else '**not acceptable**'} |", ""]
+               f"| threshold | {r.acceptable_threshold:.4f} |", f"| result | {'acceptable' if r.is_acceptable else '**not acceptable**'} |", ""]
         if r.per_layer_results:
             out += ["| layer | impact | sensitive | action |", "|---|---|---|---|"]
             out += [f"| `{x.layer_name}` | {x.accuracy_impact:+.4f} | {'yes' if x.is_sensitive else 'no'} | {x.recommended_action} |"

@@ -201,7 +201,7 @@ def test_accuracy_comparison_and_reporter(tmp_path):
     rep.per_layer_results[0].recommended_action = "keep in fp32"
     R = Q.AccuracyReporter()
     text = R.generate_text_report(rep)
-    assert "Verdict:    ACCEPTABLE" in text and "SENSITIVE" in text and f"Keep in fp32: {rep.per_layer_results[0].layer_name}" in text
+    assert "Result:     ACCEPTABLE" in text and "SENSITIVE" in text and f"Keep in fp32: {rep.per_layer_results[0].layer_name}" in text
     js = json.loads(R.generate_json_report(rep))
     assert js["is_acceptable"] and js["recommended_fp32_layers"] == [rep.per_layer_results[0].layer_name] and len(js["quantizable_layers"]) == 2
     md = R.generate_markdown_report(rep)
