@@ -220,6 +220,9 @@ def _execute(o: Op, x: List[torch.Tensor]) -> torch.Tensor:
     if k == "reshape": return x[0].reshape(a["shape"])
     if k == "transpose": return x[0].transpose(a.get("dim0", -2), a.get("dim1", -1))
     if k == "concat": return torch.cat(x, a.get("dim", 0))
+    if k == "slice":
+        steps = a.get("steps", [1] * len(a["starts"]))
+        return x[0][tuple(slice(b, e, st) for b, e, st in zip(a["starts"], a["ends"], steps))].contiguous()
     if k in ("sum", "mean", "max"):
         if "dim" not in a:
             return getattr(x[0], k)()

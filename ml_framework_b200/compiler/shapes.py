@@ -155,6 +155,8 @@ class ShapeInferenceEngine:
         self.rules["reshape"] = self._reshape
         self.rules["transpose"] = self._transpose
         self.rules["concat"] = self._concat
+        self.rules["slice"] = self._slice
+        self.rules["broadcast_to"] = lambda s, a: SymbolicShape(list(a["shape"]))
         self.rules["sum"] = self._reduce
         self.rules["mean"] = self._reduce
         self.rules["max"] = self._reduce
@@ -167,6 +169,28 @@ class ShapeInferenceEngine:
             raise KeyError(f"no shape rule for op {op!r}")
         shapes = [s if isinstance(s, SymbolicShape) else SymbolicShape(s) for s in shapes]
         return self.rules[op](shapes, attrs)
+
+    @staticmethod
+    def _slice(s, a):
+        """``starts`` / ``ends`` / optional ``steps`` per leading dimension (missing trailing dimensions are kept whole)."""
+        x = s[0]
+        starts, ends = list(a["starts"]), list(a["ends"])
+        steps = list(a.get("steps", [1] * len(starts)))
+        if not (len(starts) == len(ends) == len(steps)) or len(starts) > x.rank:
+            raise ShapeMismatchException("slice", s, f"{len(starts)} starts, {len(ends)} ends, {len(steps)} steps for rank {x.rank}")
+        dims: List[Dim] = []
+        for i, d in enumerate(x.dims):
+            if i >= len(starts):
+                dims.append(d)
+                continue
+            if steps[i] <= 0:
+                raise ShapeMismatchException("slice", s, f"step {steps[i]} of dimension {i} must be positive")
+            if not d.is_known:
+                dims.append(SymbolicDimension(f"slice({d.name})"))
+                continue
+            lo, hi, _ = slice(starts[i], ends[i], steps[i]).indices(d.value)
+            dims.append(max(0, -(-(hi - lo) // steps[i])))
+        return SymbolicShape(dims)
 
     @staticmethod
     def _matmul(s, a):
@@ -259,11 +283,12 @@ class ShapeInferenceEngine:
         d = list(s[0].dims)
         if "dim" not in a:
             return SymbolicShape([])
-        ax = a["dim"] % len(d)
-        if a.get("keepdim", False):
-            d[ax] = _d(1)
-        else:
-            d.pop(ax)
+        axes = sorted({ax % len(d) for ax in ((a["dim"],) if isinstance(a["dim"], int) else a["dim"])}, reverse=True)
+        for ax in axes:                                    # from the back, so that earlier positions stay valid
+            if a.get("keepdim", False):
+                d[ax] = _d(1)
+            else:
+                d.pop(ax)
         return SymbolicShape(d)
 
 
