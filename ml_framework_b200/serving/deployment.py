@@ -9,17 +9,19 @@ per model version so a swap waits for in-flight requests); InferenceTracker.cs, 
 from __future__ import annotations
 
 import contextlib
+import enum
 import fnmatch
 import functools
 import hashlib
 import json
+import math
 import random
 import re
 import threading
 import time
 from collections import defaultdict, deque
 from dataclasses import asdict, dataclass, field
-from typing import Any, Callable, Deque, Dict, List, Optional, Tuple
+from typing import Any, Callable, Deque, Dict, List, Optional, Sequence, Tuple
 
 
 @functools.total_ordering
@@ -351,3 +353,230 @@ class InferenceTracker:
     def p(self, key: str, q: float) -> float:
         v = sorted(self.latencies[key])
         return v[min(len(v) - 1, int(q / 100 * len(v)))] if v else 0.0
+
+
+# ------------------------------------------------------------------ request routing end to end, records
+class MatchType(enum.Enum):
+    """How a routing rule compares a header value (Serving/Routing/MatchType.cs)."""
+    EXACT = "exact"
+    PREFIX = "prefix"
+    REGEX = "regex"
+    GLOB = "glob"
+
+
+class RoutingError(LookupError):
+    def __init__(self, message: str, model_name: str = "", context: Optional["RoutingContext"] = None):
+        super().__init__(message)
+        self.model_name, self.context = model_name, context
+
+
+class ReferenceLeakError(RuntimeError):
+    """A version was released while requests still held it (Serving/ReferenceLeakException.cs)."""
+
+    def __init__(self, key: str, count: int):
+        super().__init__(f"{key} still has {count} request(s) in flight")
+        self.key, self.count = key, count
+
+
+@dataclass
+class TypedRoutingRule:
+    header: str
+    pattern: str
+    version: str
+    match_type: MatchType = MatchType.EXACT
+    priority: int = 0
+
+    def matches(self, value: str) -> bool:
+        if self.match_type is MatchType.EXACT:
+            return value == self.pattern
+        if self.match_type is MatchType.PREFIX:
+            return value.startswith(self.pattern)
+        if self.match_type is MatchType.REGEX:
+            return re.search(self.pattern, value) is not None
+        return fnmatch.fnmatch(value, self.pattern)
+
+
+@dataclass
+class RoutingContext:
+    """What a routing decision may look at (Serving/Routing/RoutingContext.cs)."""
+    headers: Dict[str, str] = field(default_factory=dict)
+    user_id: Optional[str] = None
+    experiment_id: Optional[str] = None
+    requested_version: Optional[str] = None          # "1.2.3", "^1.2.0" or "latest"
+    metadata: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass
+class TrafficSplitConfig:
+    """Percentages per version, summing to 100 (Serving/Traffic/TrafficSplitConfig.cs)."""
+    model_name: str
+    version_percentages: Dict[str, float]
+    sticky: bool = True
+
+    def validate(self) -> None:
+        if not self.version_percentages:
+            raise ValueError("a traffic split needs at least one version")
+        if any(p < 0 for p in self.version_percentages.values()):
+            raise ValueError("percentages cannot be negative")
+        total = sum(self.version_percentages.values())
+        if abs(total - 100.0) > 1e-6:
+            raise ValueError(f"percentages sum to {total:g}, not 100")
+
+    def to_splitter(self, seed: int = 0) -> "TrafficSplitter":
+        self.validate()
+        return TrafficSplitter({k: v for k, v in self.version_percentages.items() if v > 0}, seed)
+
+
+class RequestRouter:
+    """One decision per request, in this order: an explicit version constraint, the first matching header
+    rule, the model's traffic split (sticky per user when the split says so), the active version."""
+
+    def __init__(self, registry: ModelRegistry, swapper: Optional[ModelHotSwapper] = None):
+        self.registry, self.swapper = registry, swapper
+        self.versions = VersionRouter(registry)
+        self._rules: Dict[str, List[TypedRoutingRule]] = defaultdict(list)
+        self._splits: Dict[str, Tuple[TrafficSplitConfig, TrafficSplitter]] = {}
+        self.decisions: Dict[str, int] = defaultdict(int)
+
+    def add_rule(self, model_name: str, rule: TypedRoutingRule) -> None:
+        self._rules[model_name].append(rule)
+        self._rules[model_name].sort(key=lambda r: -r.priority)
+
+    def set_traffic_split(self, config: TrafficSplitConfig, seed: int = 0) -> None:
+        for v in config.version_percentages:
+            self.registry.get(config.model_name, v)
+        self._splits[config.model_name] = (config, config.to_splitter(seed))
+
+    def clear_traffic_split(self, model_name: str) -> bool:
+        return self._splits.pop(model_name, None) is not None
+
+    def route(self, model_name: str, context: Optional[RoutingContext] = None) -> str:
+        ctx = context or RoutingContext()
+        try:
+            if ctx.requested_version:
+                self.decisions["explicit"] += 1
+                return self.versions.resolve(model_name, ctx.requested_version)
+            low = {k.lower(): v for k, v in ctx.headers.items()}
+            for r in self._rules.get(model_name, ()):
+                v = low.get(r.header.lower())
+                if v is not None and r.matches(v):
+                    self.registry.get(model_name, r.version)
+                    self.decisions["rule"] += 1
+                    return r.version
+            if model_name in self._splits:
+                cfg, splitter = self._splits[model_name]
+                self.decisions["split"] += 1
+                return splitter.choose(ctx.user_id if cfg.sticky else None)
+            self.decisions["default"] += 1
+            if self.swapper is not None and model_name in self.swapper.active:
+                return self.swapper.active[model_name]
+            return self.registry.latest(model_name)
+        except KeyError as e:
+            raise RoutingError(f"cannot route {model_name}: {e.args[0]}", model_name, ctx) from e
+
+
+@dataclass
+class ExperimentMetrics:
+    """One arm of an experiment, summarised (Serving/ExperimentMetrics.cs)."""
+    experiment_id: str
+    version: str
+    request_count: int = 0
+    success_count: int = 0
+    mean_latency_ms: float = 0.0
+    p95_latency_ms: float = 0.0
+    custom: Dict[str, float] = field(default_factory=dict)
+
+    @property
+    def success_rate(self) -> float:
+        return self.success_count / self.request_count if self.request_count else 0.0
+
+    @property
+    def error_rate(self) -> float:
+        return 1.0 - self.success_rate if self.request_count else 0.0
+
+    @classmethod
+    def from_samples(cls, experiment_id: str, version: str, latencies_ms: Sequence[float], successes: Sequence[bool],
+                     custom: Optional[Dict[str, float]] = None) -> "ExperimentMetrics":
+        if len(latencies_ms) != len(successes):
+            raise ValueError("one success flag per latency sample")
+        lat = sorted(latencies_ms)
+        p95 = lat[min(len(lat) - 1, int(math.ceil(0.95 * len(lat))) - 1)] if lat else 0.0
+        return cls(experiment_id, version, len(lat), sum(bool(s) for s in successes), sum(lat) / len(lat) if lat else 0.0, p95,
+                   dict(custom or {}))
+
+
+class DeploymentStatus(enum.Enum):
+    PENDING = "pending"
+    ACTIVE = "active"
+    DRAINING = "draining"
+    RETIRED = "retired"
+    FAILED = "failed"
+    ROLLED_BACK = "rolled_back"
+
+
+@dataclass
+class DeploymentRecord:
+    model_name: str
+    version: str
+    status: DeploymentStatus
+    deployed_at: float
+    retired_at: Optional[float] = None
+    previous_version: Optional[str] = None
+    note: str = ""
+
+
+class DeploymentLog:
+    """What was deployed when, on top of a hot swapper: ``deploy`` swaps and records, ``rollback`` goes back
+    to the previous record; releasing a version that still serves requests raises ``ReferenceLeakError``."""
+
+    def __init__(self, swapper: ModelHotSwapper, clock: Callable[[], float] = time.time):
+        self.swapper, self._clock = swapper, clock
+        self.records: List[DeploymentRecord] = []
+
+    def current(self, model_name: str) -> Optional[DeploymentRecord]:
+        return next((r for r in reversed(self.records) if r.model_name == model_name and r.status is DeploymentStatus.ACTIVE), None)
+
+    def history(self, model_name: str) -> List[DeploymentRecord]:
+        return [r for r in self.records if r.model_name == model_name]
+
+    def deploy(self, model_name: str, version: str, drain_timeout: float = 30.0, note: str = "") -> DeploymentRecord:
+        prev = self.current(model_name)
+        rec = DeploymentRecord(model_name, version, DeploymentStatus.PENDING, self._clock(), None, prev.version if prev else None, note)
+        self.records.append(rec)
+        try:
+            if prev is None:
+                self.swapper.activate(model_name, version)
+                drained = True
+            else:
+                prev.status = DeploymentStatus.DRAINING
+                drained = self.swapper.swap(model_name, version, drain_timeout)
+        except KeyError:
+            rec.status = DeploymentStatus.FAILED
+            if prev is not None:
+                prev.status = DeploymentStatus.ACTIVE
+            raise
+        rec.status = DeploymentStatus.ACTIVE
+        if prev is not None and drained:
+            prev.status, prev.retired_at = DeploymentStatus.RETIRED, self._clock()
+        return rec
+
+    def rollback(self, model_name: str, drain_timeout: float = 30.0) -> Optional[DeploymentRecord]:
+        cur = self.current(model_name)
+        if cur is None or cur.previous_version is None:
+            return None
+        target = cur.previous_version
+        self.swapper.swap(model_name, target, drain_timeout)
+        cur.status, cur.retired_at = DeploymentStatus.ROLLED_BACK, self._clock()
+        rec = DeploymentRecord(model_name, target, DeploymentStatus.ACTIVE, self._clock(), None, cur.version, f"rollback from {cur.version}")
+        self.records.append(rec)
+        return rec
+
+    def release(self, model_name: str, version: str) -> None:
+        """Unregisters a version that is no longer active; refuses while requests still hold it."""
+        if self.swapper.active.get(model_name) == version:
+            raise ValueError(f"{model_name}:{version} is the active version")
+        key = f"{model_name}:{version}"
+        n = self.swapper.refs.count(key)
+        if n > 0:
+            raise ReferenceLeakError(key, n)
+        self.swapper.reg.unregister(model_name, version)

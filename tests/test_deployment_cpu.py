@@ -208,3 +208,70 @@ def test_version_loader_lineage_monitor_and_guarded_swaps():
     assert not g.rollback_version("clf", "7.7.7").success and not V.GuardedVersionSwapper(ModelHotSwapper(loader.reg)).rollback_version("other").success
     loader.unload_version("clf", "1.1.0")
     assert not loader.is_version_loaded("clf", "1.1.0") and not g.check_version_health("clf", "1.1.0").healthy
+
+
+def test_request_router_split_config_experiment_metrics_and_deployment_log():
+    import threading
+
+    from ml_framework_b200.serving import deployment as D
+    reg = D.ModelRegistry()
+    for v in ("1.0.0", "1.1.0", "2.0.0"):
+        reg.register(f"model-{v}", D.ModelMetadata("m", v))
+    sw = D.ModelHotSwapper(reg)
+    log = D.DeploymentLog(sw, clock=iter(range(100)).__next__)
+    first = log.deploy("m", "1.0.0")
+    assert first.status is D.DeploymentStatus.ACTIVE and first.previous_version is None and log.current("m") is first
+    router = D.RequestRouter(reg, sw)
+    assert router.route("m") == "1.0.0"                                               # the active version
+    assert router.route("m", D.RoutingContext(requested_version="^1.0.0")) == "1.1.0" and router.route("m", D.RoutingContext(requested_version="latest")) == "2.0.0"
+    router.add_rule("m", D.TypedRoutingRule("X-Client", "beta-", "2.0.0", D.MatchType.PREFIX, priority=5))
+    router.add_rule("m", D.TypedRoutingRule("X-Client", r"^internal-\d+$", "1.1.0", D.MatchType.REGEX, priority=9))
+    router.add_rule("m", D.TypedRoutingRule("X-Tier", "gold", "1.1.0"))
+    router.add_rule("m", D.TypedRoutingRule("X-Region", "eu-*", "1.0.0", D.MatchType.GLOB))
+    R = lambda **h: router.route("m", D.RoutingContext(headers=h))                     # noqa: E731
+    assert R(**{"x-client": "beta-7"}) == "2.0.0" and R(**{"X-Client": "internal-42"}) == "1.1.0" and R(**{"X-Tier": "gold"}) == "1.1.0"
+    assert R(**{"X-Tier": "golden"}) == "1.0.0" and R(**{"X-Region": "eu-west"}) == "1.0.0"
+    cfg = D.TrafficSplitConfig("m", {"1.0.0": 80.0, "2.0.0": 20.0})
+    router.set_traffic_split(cfg, seed=1)
+    picks = [router.route("m", D.RoutingContext(user_id=f"u{i}")) for i in range(2000)]
+    assert 0.15 < picks.count("2.0.0") / 2000 < 0.25
+    assert len({router.route("m", D.RoutingContext(user_id="same")) for _ in range(20)}) == 1      # sticky per user
+    assert router.decisions["split"] == 2020 and router.decisions["rule"] == 4 and router.clear_traffic_split("m") and not router.clear_traffic_split("m")
+    for bad in ({"1.0.0": 50.0}, {"1.0.0": 120.0, "2.0.0": -20.0}, {}):
+        with pytest.raises(ValueError):
+            D.TrafficSplitConfig("m", bad).validate()
+    with pytest.raises(KeyError):
+        router.set_traffic_split(D.TrafficSplitConfig("m", {"9.9.9": 100.0}))
+    with pytest.raises(D.RoutingError) as ei:
+        router.route("m", D.RoutingContext(requested_version="3.0.0"))
+    assert ei.value.model_name == "m" and ei.value.context.requested_version == "3.0.0"
+    with pytest.raises(D.RoutingError):
+        router.route("unknown")
+
+    em = D.ExperimentMetrics.from_samples("exp1", "2.0.0", [10.0] * 18 + [50.0, 90.0], [True] * 19 + [False], {"ctr": 0.2})
+    assert em.request_count == 20 and em.success_rate == 0.95 and em.error_rate == pytest.approx(0.05) and em.p95_latency_ms == 50.0
+    assert em.mean_latency_ms == pytest.approx((180 + 140) / 20) and D.ExperimentMetrics("e", "v").success_rate == 0.0
+    with pytest.raises(ValueError):
+        D.ExperimentMetrics.from_samples("e", "v", [1.0], [])
+
+    second = log.deploy("m", "2.0.0", note="canary won")
+    assert second.previous_version == "1.0.0" and first.status is D.DeploymentStatus.RETIRED and first.retired_at is not None
+    assert sw.active["m"] == "2.0.0" and [r.version for r in log.history("m")] == ["1.0.0", "2.0.0"]
+    with pytest.raises(KeyError):
+        log.deploy("m", "7.7.7")
+    assert log.records[-1].status is D.DeploymentStatus.FAILED and log.current("m") is second
+    back = log.rollback("m")
+    assert back.version == "1.0.0" and second.status is D.DeploymentStatus.ROLLED_BACK and sw.active["m"] == "1.0.0" and "rollback from 2.0.0" in back.note
+    # a version that still serves a request cannot be released
+    started, finish = threading.Event(), threading.Event()
+    t = threading.Thread(target=lambda: sw.serve("m", lambda model: (started.set(), finish.wait(10)), version="2.0.0"))
+    t.start(); started.wait(5)
+    with pytest.raises(D.ReferenceLeakError) as leak:
+        log.release("m", "2.0.0")
+    assert leak.value.count == 1
+    finish.set(); t.join(5)
+    log.release("m", "2.0.0")
+    assert reg.versions("m") == ["1.0.0", "1.1.0"]
+    with pytest.raises(ValueError):
+        log.release("m", "1.0.0")
+    assert D.DeploymentLog(sw).rollback("nothing") is None
