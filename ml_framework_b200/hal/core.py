@@ -17,6 +17,7 @@ from __future__ import annotations
 import enum
 import math
 import threading
+import time
 from collections import defaultdict, deque
 from dataclasses import dataclass
 from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
@@ -419,6 +420,15 @@ class PredictiveAllocator:
         self._hist: Dict[str, Deque[int]] = defaultdict(lambda: deque(maxlen=window))
         self._handles: Dict[str, MemoryHandle] = {}
         self.reallocations = 0
+        self._allocations = 0
+        self._bytes_allocated = 0
+        self._bytes_wasted = 0
+        self._util_sum, self._util_n = 0.0, 0
+
+    def stats(self) -> "AllocationStats":
+        """Allocation counts, bytes handed out, bytes that padding left unused, mean utilisation of a request."""
+        return AllocationStats(self._allocations, self.reallocations, self._bytes_allocated, self._bytes_wasted,
+                               self._util_sum / self._util_n if self._util_n else 0.0)
 
     def predict_elements(self, name: str) -> int:
         h = self._hist[name]
@@ -442,6 +452,11 @@ class PredictiveAllocator:
             esz = torch.empty((), dtype=dtype).element_size()
             h = MemoryHandle(self.alloc.allocate(want * esz), tuple(shape), dtype)
             self._handles[name] = h
+            self._allocations += 1
+            self._bytes_allocated += want * esz
+            self._bytes_wasted += (want - n) * esz
+        self._util_sum += n / max(1, h.capacity_elements)
+        self._util_n += 1
         self.padding.observe(resized)
         return h.view(shape)
 
@@ -478,3 +493,134 @@ class MemoryPressureHandler:
             if self.pressure() < self.low:
                 break
         return freed
+
+
+# ------------------------------------------------------------------ allocation statistics, model-level memory pressure
+@dataclass
+class AllocationStats:
+    """Reference: src/MLFramework/Memory/AllocationStats.cs."""
+    total_allocations: int = 0
+    total_resizes: int = 0
+    total_bytes_allocated: int = 0
+    total_bytes_wasted: int = 0
+    average_utilization: float = 0.0
+
+    def to_report(self) -> str:
+        waste = 100.0 * self.total_bytes_wasted / self.total_bytes_allocated if self.total_bytes_allocated else 0.0
+        return (f"allocations: {self.total_allocations} ({self.total_resizes} resizes), {self.total_bytes_allocated} bytes, "
+                f"{self.total_bytes_wasted} bytes of padding ({waste:.1f} %), mean utilisation {self.average_utilization * 100:.1f} %")
+
+
+class ModelMemoryInfo:
+    """One loaded model version as the eviction policy sees it (src/MLFramework/Memory/ModelMemoryInfo.cs): the weight
+    falls with the time since the last use and rises with the number of uses, a day per use."""
+
+    SECONDS_PER_USE = 86400.0
+
+    def __init__(self, model_name: str, version: str, memory_bytes: int, clock: Callable[[], float] = time.time):
+        if memory_bytes < 0:
+            raise ValueError("memory_bytes cannot be negative")
+        self.model_name, self.version, self.memory_bytes = model_name, version, int(memory_bytes)
+        self._clock = clock
+        self.last_access_time = clock()
+        self.access_count = 0
+        self.is_pinned = False
+
+    @property
+    def weight(self) -> float:
+        """Lower = a better candidate for eviction."""
+        return self.last_access_time + self.access_count * self.SECONDS_PER_USE
+
+    def record_access(self) -> None:
+        self.last_access_time = self._clock()
+        self.access_count += 1
+
+
+@dataclass
+class EvictionResult:
+    evicted_versions: List[str]
+    bytes_freed: int
+    sufficient: bool
+
+    def __str__(self):
+        return f"evicted {len(self.evicted_versions)} model(s), freed {self.bytes_freed} bytes, {'enough' if self.sufficient else 'NOT enough'}"
+
+
+class ModelMemoryPressureHandler:
+    """Keeps the loaded model versions under a byte threshold: ``evict_if_needed(required)`` unloads unpinned versions,
+    lowest weight first, skipping those the ``can_evict`` callback protects (requests in flight), until usage plus the
+    requirement fits (src/MLFramework/Memory/MemoryPressureHandler.cs:9-180)."""
+
+    def __init__(self, memory_threshold_bytes: int, unload_model: Callable[[str, str], None],
+                 can_evict: Optional[Callable[[str, str], bool]] = None, clock: Callable[[], float] = time.time):
+        if memory_threshold_bytes <= 0:
+            raise ValueError("the memory threshold must be positive")
+        self._threshold, self._unload, self._can_evict, self._clock = int(memory_threshold_bytes), unload_model, can_evict, clock
+        self._models: Dict[str, ModelMemoryInfo] = {}
+        self._lock = threading.RLock()
+        self.evictions = 0
+
+    @staticmethod
+    def _key(name: str, version: str) -> str:
+        return f"{name}:{version}"
+
+    def track_model_load(self, model_name: str, version: str, memory_bytes: int) -> None:
+        with self._lock:
+            self._models[self._key(model_name, version)] = ModelMemoryInfo(model_name, version, memory_bytes, self._clock)
+
+    def track_model_access(self, model_name: str, version: str) -> None:
+        with self._lock:
+            m = self._models.get(self._key(model_name, version))
+            if m is not None:
+                m.record_access()
+
+    def _pin(self, model_name: str, version: str, value: bool) -> None:
+        with self._lock:
+            k = self._key(model_name, version)
+            if k not in self._models:
+                raise KeyError(f"model {k} is not tracked")
+            self._models[k].is_pinned = value
+
+    def pin_model(self, model_name: str, version: str) -> None:
+        self._pin(model_name, version, True)
+
+    def unpin_model(self, model_name: str, version: str) -> None:
+        self._pin(model_name, version, False)
+
+    def untrack_model(self, model_name: str, version: str) -> bool:
+        with self._lock:
+            return self._models.pop(self._key(model_name, version), None) is not None
+
+    def get_total_memory_usage(self) -> int:
+        with self._lock:
+            return sum(m.memory_bytes for m in self._models.values())
+
+    def set_memory_threshold(self, threshold_bytes: int) -> None:
+        if threshold_bytes <= 0:
+            raise ValueError("the memory threshold must be positive")
+        self._threshold = int(threshold_bytes)
+
+    def get_loaded_models_info(self) -> List[ModelMemoryInfo]:
+        with self._lock:
+            return list(self._models.values())
+
+    def evict_if_needed(self, required_bytes: int = 0) -> EvictionResult:
+        """Makes room for ``required_bytes`` more under the threshold."""
+        with self._lock:
+            usage = self.get_total_memory_usage()
+            target = self._threshold - max(0, int(required_bytes))
+            if usage <= target:
+                return EvictionResult([], 0, True)
+            gone, freed = [], 0
+            for m in sorted((m for m in self._models.values() if not m.is_pinned), key=lambda m: m.weight):
+                if usage - freed <= target:
+                    break
+                if self._can_evict is not None and not self._can_evict(m.model_name, m.version):
+                    continue
+                k = self._key(m.model_name, m.version)
+                self._models.pop(k)
+                self._unload(m.model_name, m.version)
+                gone.append(k)
+                freed += m.memory_bytes
+                self.evictions += 1
+            return EvictionResult(gone, freed, usage - freed <= target)

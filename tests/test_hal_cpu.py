@@ -250,3 +250,43 @@ def test_graph_validation_rules_context_result_and_fallback_strategies():
     retry = cg.CUDAGraphFallbackHandler(max_failures=2)
     retry.execute_with_fallback(boom, lambda: 0); assert retry.graph_path_enabled
     retry.execute_with_fallback(boom, lambda: 0); assert not retry.graph_path_enabled
+
+
+def test_allocation_stats_and_model_memory_pressure():
+    from ml_framework_b200.hal import core as H
+    alloc = H.PredictiveAllocator(H.SimpleAllocator(H.BackendRegistry.get("cpu").device(0)))
+    for n in (100, 110, 300, 120):
+        alloc.get("act", (n,), torch.float32)
+    st = alloc.stats()
+    assert st.total_allocations >= 2 and st.total_resizes >= 1 and st.total_bytes_allocated >= 300 * 4 and st.total_bytes_wasted > 0
+    assert 0 < st.average_utilization <= 1 and "resizes" in st.to_report()
+
+    now = [0.0]
+    unloaded, busy = [], {("m", "2")}
+    h = H.ModelMemoryPressureHandler(1000, lambda n, v: unloaded.append((n, v)), lambda n, v: (n, v) not in busy, clock=lambda: now[0])
+    for i, v in enumerate(("1", "2", "3", "4")):
+        now[0] = float(i)
+        h.track_model_load("m", v, 300)
+    assert h.get_total_memory_usage() == 1200 and len(h.get_loaded_models_info()) == 4
+    now[0] = 10.0
+    h.track_model_access("m", "1")                         # the oldest load becomes the most recently used
+    h.pin_model("m", "3")
+    r = h.evict_if_needed()
+    assert r.evicted_versions == ["m:4"] and r.bytes_freed == 300 and r.sufficient and unloaded == [("m", "4")]   # 2 is busy, 3 pinned
+    assert "freed 300 bytes" in str(r) and h.evict_if_needed().evicted_versions == []
+    r = h.evict_if_needed(required_bytes=400)               # 900 used, 600 allowed: only version 1 can go
+    assert r.evicted_versions == ["m:1"] and r.sufficient
+    r = h.evict_if_needed(required_bytes=900)               # nothing evictable is left
+    assert r.evicted_versions == [] and not r.sufficient and "NOT enough" in str(r)
+    busy.clear()
+    h.unpin_model("m", "3")
+    assert h.evict_if_needed(required_bytes=900).evicted_versions == ["m:2", "m:3"] and h.get_total_memory_usage() == 0 and h.evictions == 4
+    assert not h.untrack_model("m", "9")
+    with pytest.raises(KeyError):
+        h.pin_model("m", "9")
+    with pytest.raises(ValueError):
+        h.set_memory_threshold(0)
+    info = H.ModelMemoryInfo("a", "1", 10, clock=lambda: 5.0)
+    w0 = info.weight
+    info.record_access()
+    assert info.weight == w0 + 86400.0 and info.access_count == 1
